@@ -1,0 +1,235 @@
+/* q3b200 — C ABI of the B200 (sm_100a) training-kernel library behind the qwen3_triton operator API.
+ *
+ * The reference project (wuyii8941/qwen3-triton) has no FFI: its operators are Python
+ * torch.autograd.Function classes that launch Triton kernels. This header is the boundary a
+ * binding would target instead: one extern "C" entry per kernel family and direction, taking raw
+ * device pointers, int64 sizes, a stream and (where the device can detect a violation) a device
+ * status word. Each declaration cites the reference function it stands in for (paths are relative
+ * to the reference repository).
+ *
+ * Common rules
+ *   - all pointers are device pointers unless a parameter is documented as host memory;
+ *   - tensors are contiguous unless strides are passed explicitly;
+ *   - return 0 (Q3_OK) on success; a negative Q3_ERR_* value means the call was rejected on the
+ *     host and nothing was launched; values <= Q3_ERR_CUDA encode (Q3_ERR_CUDA - cudaError_t);
+ *   - kernels run on `stream`; the library keeps no mutable global state except per-device caches;
+ *   - `status` (may be NULL) is an int32 device word; kernels OR Q3_STATUS_* bits into it and never
+ *     trap. The caller clears and reads it.
+ *   - outputs are fully overwritten; workspaces are caller-allocated, sized by the *_workspace_bytes
+ *     query of the same family, and need no initialisation.
+ */
+#ifndef Q3B200_H_
+#define Q3B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct CUstream_st* q3_stream_t;
+
+/* element types */
+enum { Q3_F32 = 0, Q3_BF16 = 1, Q3_F16 = 2 };
+
+/* return codes */
+enum {
+  Q3_OK = 0,
+  Q3_ERR_ARG = -1,       /* null pointer or non-positive size */
+  Q3_ERR_SHAPE = -2,     /* unsupported shape */
+  Q3_ERR_DTYPE = -3,     /* unsupported element type */
+  Q3_ERR_WORKSPACE = -4, /* workspace missing or too small */
+  Q3_ERR_ALIGN = -5,     /* pointer or stride alignment not supported by any path */
+  Q3_ERR_DRIVER = -6,    /* a required driver entry point is unavailable */
+  Q3_ERR_CUDA = -1000    /* Q3_ERR_CUDA - cudaError_t */
+};
+
+/* device status bits */
+enum {
+  Q3_STATUS_ID_RANGE = 1,    /* embedding id outside [0, V) */
+  Q3_STATUS_LABEL_RANGE = 2, /* label outside [0, V) and not ignore_index */
+  Q3_STATUS_WAIT_TIMEOUT = 4,/* a bounded barrier wait inside a kernel gave up */
+  Q3_STATUS_EMPTY_TARGETS = 8/* cross-entropy saw no valid target */
+};
+
+int q3_abi_version(void);
+const char* q3_error_string(int code);
+int q3_device_sm_count(void);
+
+/* ---- elementwise --------------------------------------------------------------------------- */
+
+/* out = a + b in fp32, rounded once. Reference: qwen3_triton/kernels/residual.py:7-11,29-30. */
+int q3_residual_add(const void* a, const void* b, void* out, int64_t n, int dtype, q3_stream_t stream);
+
+/* y = cast(x). Reference: qwen3_triton/kernels/attention.py:10-18 (cast_tensor). */
+int q3_cast(const void* x, int src_dtype, void* y, int dst_dtype, int64_t n, q3_stream_t stream);
+
+/* y = silu(gate) * up. Reference: qwen3_triton/kernels/activation.py:7-11,
+ * kernels/math_precision.py:67-71, ops/triton/silu_and_mul.py:111-121; math of ops/reference/swiglu.py:9-21. */
+int q3_swiglu_fwd(const void* gate, const void* up, void* y, int64_t n, int dtype, q3_stream_t stream);
+
+/* dgate = dy*up*s*(1+gate*(1-s)), dup = dy*gate*s, s = sigmoid(gate).
+ * Reference: qwen3_triton/kernels/activation.py:14-20, kernels/math_precision.py:73-81. */
+int q3_swiglu_bwd(const void* gate, const void* up, const void* dy, void* dgate, void* dup, int64_t n, int dtype,
+                  q3_stream_t stream);
+
+/* pos[i] = i % seq (int64). Reference: qwen3_triton/_model.py:30-32 (_positions). */
+int q3_positions(int64_t* pos, int64_t n, int64_t seq, q3_stream_t stream);
+
+/* ---- RMSNorm ------------------------------------------------------------------------------- */
+
+/* y = x * rsqrt(mean(x^2) + eps) * weight over rows of H (H <= 8192); inv_rms[rows] fp32 is saved.
+ * Reference: qwen3_triton/kernels/norm.py:7-13,39-66; math_precision.py:16-37; ops/triton/rms_norm.py:136-138. */
+int q3_rmsnorm_fwd(const void* x, const void* weight, void* y, float* inv_rms, int64_t rows, int64_t H, double eps,
+                   int dtype, q3_stream_t stream);
+
+int64_t q3_rmsnorm_bwd_workspace_bytes(int64_t rows, int64_t H);
+
+/* dx and a deterministic dweight (per-CTA partial rows in the workspace, summed in fixed order).
+ * Reference: qwen3_triton/kernels/norm.py:16-37,53-63. */
+int q3_rmsnorm_bwd(const void* x, const void* weight, const void* dy, const float* inv_rms, void* dx, void* dweight,
+                   void* workspace, int64_t workspace_bytes, int64_t rows, int64_t H, int dtype, q3_stream_t stream);
+
+/* residual_out = x + residual (rounded to dtype); y = RMSNorm(residual_out) * weight.
+ * Fuses reference qwen3_triton/kernels/residual.py:7-11 with kernels/norm.py:7-13 (one pass over HBM). */
+int q3_add_rmsnorm_fwd(const void* x, const void* residual, const void* weight, void* y, void* residual_out,
+                       float* inv_rms, int64_t rows, int64_t H, double eps, int dtype, q3_stream_t stream);
+
+/* dx = RMSNorm-backward(dy) on residual_out [+ dresidual if not NULL]; the result is the gradient of both
+ * x and residual. Fuses reference kernels/norm.py:16-37 with the residual fan-in of residual.py:26-27. */
+int q3_add_rmsnorm_bwd(const void* residual_out, const void* weight, const void* dy, const void* dresidual,
+                       const float* inv_rms, void* dx, void* dweight, void* workspace, int64_t workspace_bytes,
+                       int64_t rows, int64_t H, int dtype, q3_stream_t stream);
+
+/* ---- per-head RMSNorm + RoPE, RoPE ---------------------------------------------------------- */
+
+/* x [tokens, heads, D] -> y = rope(RMSNorm_D(x) * weight); cos/sin [tokens, D] in `dtype`.
+ * Split-half rotation: y1 = n1*cos1 - n2*sin1, y2 = n2*cos2 + n1*sin2.
+ * Reference: qwen3_triton/kernels/norm_rope.py:12-27,52-71; math_precision.py:40-64;
+ * ops/triton/fused_qk_norm_rope.py:263-273; math of ops/reference/fused_qk_norm_rope.py:9-33. */
+int q3_norm_rope_fwd(const void* x, const void* weight, const void* cos_t, const void* sin_t, void* y,
+                     float* inv_rms, int64_t tokens, int64_t heads, int64_t D, double eps, int dtype,
+                     q3_stream_t stream);
+
+int64_t q3_norm_rope_bwd_workspace_bytes(int64_t tokens, int64_t heads, int64_t D);
+
+/* Reference: qwen3_triton/kernels/norm_rope.py:30-50,63-69; ops/reference/fused_qk_norm_rope.py:36-80. */
+int q3_norm_rope_bwd(const void* x, const void* weight, const void* cos_t, const void* sin_t, const void* dy,
+                     const float* inv_rms, void* dx, void* dweight, void* workspace, int64_t workspace_bytes,
+                     int64_t tokens, int64_t heads, int64_t D, int dtype, q3_stream_t stream);
+
+/* RoPE (backward != 0: its transpose). layout 0: x [batch, seq, heads, D]; layout 1: x [batch, heads, seq, D];
+ * cos/sin [batch, seq, D]. Reference: qwen3_triton/kernels/rotary.py:20-34,47-66; ops/triton/rope.py:164-170;
+ * ops/reference/rope.py:13-55. */
+int q3_rope_apply(const void* x, const void* cos_t, const void* sin_t, void* y, int64_t batch, int64_t seq,
+                  int64_t heads, int64_t D, int backward, int layout, int dtype, q3_stream_t stream);
+
+/* cos/sin [tokens, D] = cos/sin(float(pos) * inv_freq[i % (D/2)]); positions int32 or int64.
+ * Reference: qwen3_triton/kernels/rotary.py:12-17,36-45. */
+int q3_rope_tables(const void* positions, int positions_are_int64, const float* inv_freq, void* cos_t, void* sin_t,
+                   int64_t tokens, int64_t D, int dtype, q3_stream_t stream);
+
+/* ---- embedding ------------------------------------------------------------------------------ */
+
+/* y[t, :] = weight[ids[t], :]; ids int32 or int64; an id outside [0, vocab) yields a zero row and sets
+ * Q3_STATUS_ID_RANGE. Reference: qwen3_triton/kernels/embedding.py:13-20,49-66. */
+int q3_embedding_fwd(const void* ids, int ids_are_int64, const void* weight, void* y, int64_t tokens, int64_t H,
+                     int64_t vocab, int dtype, int* status, q3_stream_t stream);
+
+/* Dense dweight [vocab, H]: zero-filled, then one writer per token id sums its dy rows in position order
+ * (deterministic, no float atomics). Reference: qwen3_triton/kernels/embedding.py:24-46,68-77. */
+int q3_embedding_bwd(const void* ids, int ids_are_int64, const void* dy, void* dweight, int64_t tokens, int64_t H,
+                     int64_t vocab, int dtype, q3_stream_t stream);
+
+/* ---- cross-entropy over materialised logits ------------------------------------------------- */
+
+/* Causal (internally shifted) token-mean CE: row (b,s), s < S-1, is scored against labels[b,s+1].
+ * logits [B,S,V] in `dtype`, labels [B,S] int64. Outputs: lse/target/losses [B*(S-1)] fp32, loss fp32 scalar,
+ * count int32 scalar. Reference: qwen3_triton/kernels/loss.py:7-32,46-62. */
+int q3_ce_fwd(const void* logits, const int64_t* labels, float* lse, float* target, float* losses, float* loss,
+              int* count, int64_t B, int64_t S, int64_t V, int64_t ignore_index, int dtype, int* status,
+              q3_stream_t stream);
+
+/* Vocabulary-slice statistics: lse over V_local columns per shifted row and the target logit when the slice
+ * [vocab_start, vocab_start+V_local) owns the label (else 0). logits [physical_rows, V_local].
+ * Reference: qwen3_triton/kernels/loss.py:7-13 + kernels/vocab_ce.py:15-22,78-87 (local_statistics). */
+int q3_ce_local_rows(const void* logits, const int64_t* labels, float* lse_local, float* target,
+                     int64_t physical_rows, int64_t S, int64_t V_local, int64_t vocab_start, int64_t vocab_total,
+                     int64_t ignore_index, int dtype, int* status, q3_stream_t stream);
+
+/* dlogits = (softmax - onehot) * upstream[source] / counts[source] on scored rows, 0 elsewhere;
+ * source = physical_row / rows_per_rank (single GPU: rows_per_rank = physical_rows, one count, one upstream).
+ * Reference: qwen3_triton/kernels/loss.py:35-44,64-68 and kernels/vocab_ce.py:57-67,107-112 (logit_gradient). */
+int q3_ce_grad(const void* logits, const int64_t* labels, const float* lse, const int* counts, const float* upstream,
+               void* dlogits, int64_t physical_rows, int64_t rows_per_rank, int64_t S, int64_t V_local,
+               int64_t vocab_start, int64_t vocab_total, int64_t ignore_index, int dtype, q3_stream_t stream);
+
+/* pack[0,:] = exp(lse_local - maximum), pack[1,:] = target. Reference: kernels/vocab_ce.py:26-30,88-91. */
+int q3_vce_pack(const float* lse_local, const float* maximum, const float* target, float* pack, int64_t n,
+                q3_stream_t stream);
+
+/* lse = maximum + log(pack[0]); losses; per-data-rank counts and means.
+ * Reference: kernels/vocab_ce.py:34-53,92-106 (finish_statistics). */
+int q3_vce_finish(const float* maximum, const float* pack, const int64_t* labels, float* lse, float* losses,
+                  int* counts, float* means, int64_t n, int64_t rows_per_rank, int64_t S, int64_t world,
+                  int64_t ignore_index, int* status, q3_stream_t stream);
+
+/* out = (first ? 0 : out) + partial / world, fp32. Reference: kernels/vocab_ce.py:71-75,113-114. */
+int q3_vce_accumulate(const void* partial, int partial_dtype, float* out, int64_t n, int64_t world, int first,
+                      q3_stream_t stream);
+
+/* ---- AdamW ---------------------------------------------------------------------------------- */
+
+/* Multi-tensor AdamW over fp32 tensors. meta: device int64 [n_tensors][7] =
+ * {param, grad, exp_avg, exp_avg_sq, step (fp32 scalar) device addresses, numel, first_block};
+ * coeff: device fp32 [n_tensors][3] scratch; total_blocks = sum ceil(numel / block_elems).
+ * Increments each step scalar, then updates p, m, v in place.
+ * Reference: qwen3_triton/runtime/adamw.py:20-61,118-159. */
+int q3_adamw_multi(const int64_t* meta, float* coeff, int64_t n_tensors, int64_t total_blocks, int block_elems,
+                   double lr, double beta1, double beta2, double weight_decay, double eps, q3_stream_t stream);
+
+/* ---- GEMM ----------------------------------------------------------------------------------- */
+
+/* C[M,N] (contiguous, out_dtype) = A * B with A(m,k) at a[m*a_sm + k*a_sk] and B(k,n) at b[k*b_sk + n*b_sn],
+ * fp32 accumulation. bf16/fp16 operands whose unit-stride dimension and 16-byte alignment allow TMA run on the
+ * tcgen05 tensor cores (forward X*W^T, input gradient dY*W and weight gradient dY^T*X all qualify without a
+ * copy); everything else runs on CUDA cores. Reference: qwen3_triton/kernels/linear.py:14-77 (matmul). */
+int q3_gemm(const void* a, int64_t a_sm, int64_t a_sk, const void* b, int64_t b_sk, int64_t b_sn, void* c, int64_t M,
+            int64_t N, int64_t K, int in_dtype, int out_dtype, int* status, q3_stream_t stream);
+
+/* 1 if q3_gemm would use the tensor-core kernel for these arguments, else 0. */
+int q3_gemm_path(const void* a, int64_t a_sm, int64_t a_sk, const void* b, int64_t b_sk, int64_t b_sn, const void* c,
+                 int64_t M, int64_t N, int64_t K, int in_dtype, int out_dtype);
+
+/* G = X*Wg^T, U = X*Wu^T (both rounded to dtype and stored), Y = silu(G)*U; X [M,K], Wg/Wu [N,K], outputs [M,N].
+ * Reference: qwen3_triton/kernels/mlp_precision.py:17-52, kernels/mlp.py:14-45, ops/triton/gate_up_swiglu.py:274-288. */
+int q3_gate_up_swiglu_fwd(const void* x, const void* w_gate, const void* w_up, void* gate, void* up, void* y,
+                          int64_t M, int64_t N, int64_t K, int dtype, int* status, q3_stream_t stream);
+int q3_gate_up_path(const void* x, const void* w_gate, const void* w_up, const void* gate, const void* up,
+                    const void* y, int64_t M, int64_t N, int64_t K, int dtype);
+
+/* ---- attention ------------------------------------------------------------------------------ */
+
+/* Causal grouped-query attention. q/out [B,Hq,S,D], k/v [B,Hkv,S,D] contiguous, kv head = q head / (Hq/Hkv);
+ * lse [B,Hq,S] fp32 (natural log). D even, <= 256.
+ * Reference: qwen3_triton/kernels/attention.py:20-36,49-50; kernels/attention_precision.py:147-158,181-182;
+ * ops/triton/attention.py:136-199; math of ops/reference/attention.py:10-54. */
+int q3_attn_fwd(const void* q, const void* k, const void* v, void* out, float* lse, int64_t B, int64_t Hq,
+                int64_t Hkv, int64_t S, int64_t D, double scale, int dtype, int* status, q3_stream_t stream);
+
+int64_t q3_attn_bwd_workspace_bytes(int64_t B, int64_t Hq, int64_t Hkv, int64_t S, int64_t D);
+
+/* dq, dk, dv (dk/dv already summed over the query heads of each group; deterministic).
+ * Reference: qwen3_triton/kernels/attention.py:37-47; kernels/attention_precision.py:159-179;
+ * ops/triton/attention_backward.py:196-236; math of ops/reference/attention.py:57-124. */
+int q3_attn_bwd(const void* q, const void* k, const void* v, const void* out, const void* dout, const float* lse,
+                void* dq, void* dk, void* dv, void* workspace, int64_t workspace_bytes, int64_t B, int64_t Hq,
+                int64_t Hkv, int64_t S, int64_t D, double scale, int dtype, int* status, q3_stream_t stream);
+
+/* 1 if the tensor-core attention kernels run for these arguments, else 0. */
+int q3_attn_path(const void* q, const void* k, const void* v, const void* out, int64_t D, int dtype);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* Q3B200_H_ */

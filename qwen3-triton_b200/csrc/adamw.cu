@@ -1,0 +1,106 @@
+// Multi-tensor AdamW on fp32 master parameters with fp32 moments: one launch updates every tensor
+// of a parameter group. Streaming kernel: 16 B read per element (p, g, m, v) and 12 B written
+// (p, m, v), 128-bit vector accesses, one CTA per `block`-element chunk of one tensor.
+//
+// Table layout (device, int64[rows][7]): {p, g, m, v, step pointers, numel, first_block}.
+// Math order: decoupled decay, moments, bias corrections bc1 = 1-b1^t, sqrt(bc2) = sqrt(1-b2^t),
+// step_size = lr/bc1, denom = sqrt(v)/sqrt(bc2) + eps; the coefficient arithmetic is fp64 and each
+// stored quantity is rounded to fp32 once.
+//
+// Replaces, in the reference: qwen3_triton/runtime/adamw.py:20-30 (_adamw_prepare) and
+// runtime/adamw.py:34-61 (_adamw_update).
+#include "common.cuh"
+
+namespace q3 {
+
+__global__ void adamw_prepare_kernel(const int64_t* __restrict__ meta, float* __restrict__ coeff, int64_t rows,
+                                     double lr, double b1, double b2) {
+  const int64_t r = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+  if (r >= rows) return;
+  float* step_ptr = reinterpret_cast<float*>(meta[r * 7 + 4]);
+  const float step = *step_ptr + 1.f;
+  *step_ptr = step;
+  const float bc1 = (float)(1.0 - pow(b1, (double)step));
+  const float bc2 = (float)sqrt(1.0 - pow(b2, (double)step));
+  coeff[r * 3 + 0] = bc1;
+  coeff[r * 3 + 1] = bc2;
+  coeff[r * 3 + 2] = (float)(lr / (double)bc1);
+}
+
+__device__ __forceinline__ void adamw_one(float& p, float g, float& m, float& v, double lr, double b1, double b2,
+                                          double decay, double eps, float bc2, float size) {
+  p = (float)((double)p - lr * decay * (double)p);
+  m = (float)fma(b1, (double)m, (1.0 - b1) * (double)g);
+  v = (float)(b2 * (double)v + (1.0 - b2) * (double)g * (double)g);
+  const float root = __fsqrt_rn(v);
+  const float denom = (float)((double)__fdiv_rn(root, bc2) + eps);
+  p = p - __fdiv_rn(size * m, denom);
+}
+
+__global__ void __launch_bounds__(256) adamw_update_kernel(const int64_t* __restrict__ meta,
+                                                           const float* __restrict__ coeff, int64_t rows, double lr,
+                                                           double b1, double b2, double decay, double eps,
+                                                           int block_elems) {
+  // Find the tensor that owns this block: last row whose first_block <= blockIdx.x.
+  const int64_t blk = blockIdx.x;
+  int64_t lo = 0, hi = rows;
+  while (lo + 1 < hi) {
+    const int64_t mid = (lo + hi) >> 1;
+    if (meta[mid * 7 + 6] <= blk) lo = mid; else hi = mid;
+  }
+  const int64_t r = lo;
+  float* __restrict__ p = reinterpret_cast<float*>(meta[r * 7 + 0]);
+  const float* __restrict__ g = reinterpret_cast<const float*>(meta[r * 7 + 1]);
+  float* __restrict__ m = reinterpret_cast<float*>(meta[r * 7 + 2]);
+  float* __restrict__ v = reinterpret_cast<float*>(meta[r * 7 + 3]);
+  const int64_t n = meta[r * 7 + 5];
+  const int64_t begin = (blk - meta[r * 7 + 6]) * (int64_t)block_elems;
+  const int64_t end = begin + block_elems < n ? begin + block_elems : n;
+  const float bc2 = coeff[r * 3 + 1], size = coeff[r * 3 + 2];
+  const bool vec = ((reinterpret_cast<uintptr_t>(p) | reinterpret_cast<uintptr_t>(g) | reinterpret_cast<uintptr_t>(m) |
+                     reinterpret_cast<uintptr_t>(v)) & 15u) == 0;
+  if (vec) {
+    const int64_t vend = begin + ((end - begin) & ~(int64_t)3);
+    for (int64_t i = begin + threadIdx.x * 4; i < vend; i += blockDim.x * 4) {
+      float4 pp = *reinterpret_cast<const float4*>(p + i);
+      const float4 gg = *reinterpret_cast<const float4*>(g + i);
+      float4 mm = *reinterpret_cast<const float4*>(m + i);
+      float4 vv = *reinterpret_cast<const float4*>(v + i);
+      adamw_one(pp.x, gg.x, mm.x, vv.x, lr, b1, b2, decay, eps, bc2, size);
+      adamw_one(pp.y, gg.y, mm.y, vv.y, lr, b1, b2, decay, eps, bc2, size);
+      adamw_one(pp.z, gg.z, mm.z, vv.z, lr, b1, b2, decay, eps, bc2, size);
+      adamw_one(pp.w, gg.w, mm.w, vv.w, lr, b1, b2, decay, eps, bc2, size);
+      *reinterpret_cast<float4*>(p + i) = pp;
+      *reinterpret_cast<float4*>(m + i) = mm;
+      *reinterpret_cast<float4*>(v + i) = vv;
+    }
+    for (int64_t i = vend + threadIdx.x; i < end; i += blockDim.x) {
+      float pp = p[i], mm = m[i], vv = v[i];
+      adamw_one(pp, g[i], mm, vv, lr, b1, b2, decay, eps, bc2, size);
+      p[i] = pp; m[i] = mm; v[i] = vv;
+    }
+  } else {
+    for (int64_t i = begin + threadIdx.x; i < end; i += blockDim.x) {
+      float pp = p[i], mm = m[i], vv = v[i];
+      adamw_one(pp, g[i], mm, vv, lr, b1, b2, decay, eps, bc2, size);
+      p[i] = pp; m[i] = mm; v[i] = vv;
+    }
+  }
+}
+
+}  // namespace q3
+
+using namespace q3;
+
+extern "C" int q3_adamw_multi(const int64_t* meta, float* coeff, int64_t n_tensors, int64_t total_blocks,
+                              int block_elems, double lr, double beta1, double beta2, double weight_decay, double eps,
+                              q3_stream_t stream) {
+  if (!meta || !coeff) return Q3_ERR_ARG;
+  if (n_tensors < 1 || total_blocks < 1 || total_blocks > 2147483647LL || block_elems < 256 || (block_elems & 3))
+    return Q3_ERR_SHAPE;
+  cudaStream_t st = (cudaStream_t)stream;
+  adamw_prepare_kernel<<<(int)cdiv(n_tensors, 128), 128, 0, st>>>(meta, coeff, n_tensors, lr, beta1, beta2);
+  adamw_update_kernel<<<(unsigned)total_blocks, 256, 0, st>>>(meta, coeff, n_tensors, lr, beta1, beta2, weight_decay,
+                                                             eps, block_elems);
+  return launch_status();
+}

@@ -1,0 +1,74 @@
+// C-ABI entry points of causal grouped-query attention: argument checks and path selection between
+// the tensor-core kernels (bf16/fp16, head_dim 128) and the general CUDA-core kernels.
+//
+// Stand in for reference qwen3_triton/kernels/attention.py:20-50 (_Attention / causal_attention),
+// kernels/attention_precision.py:147-182 (_NativePrecision / candidate), ops/triton/attention.py:136-199
+// and ops/triton/attention_backward.py:196-236.
+#include "common.cuh"
+
+namespace q3 {
+int attn_fwd_simt(const void* q, const void* k, const void* v, void* out, float* lse, int64_t B, int64_t Hq,
+                  int64_t Hkv, int64_t S, int64_t D, float scale, int dtype, cudaStream_t st);
+int attn_delta(const void* out, const void* dout, float* delta, int64_t rows, int64_t D, int dtype, cudaStream_t st);
+int attn_bwd_simt(const void* q, const void* k, const void* v, const void* dout, const float* lse, const float* delta,
+                  void* dq, void* dk, void* dv, int64_t B, int64_t Hq, int64_t Hkv, int64_t S, int64_t D, float scale,
+                  int dtype, cudaStream_t st);
+int attn_fwd_tc(const void* q, const void* k, const void* v, void* out, float* lse, int64_t B, int64_t Hq, int64_t Hkv,
+                int64_t S, float scale, int dtype, int* status, cudaStream_t st);
+int attn_bwd_tc(const void* q, const void* k, const void* v, const void* dout, const float* lse, const float* delta,
+                void* dq, void* dk, void* dv, int64_t B, int64_t Hq, int64_t Hkv, int64_t S, float scale, int dtype,
+                int* status, cudaStream_t st);
+bool attn_tc_available();
+
+static int check_shape(int64_t B, int64_t Hq, int64_t Hkv, int64_t S, int64_t D) {
+  if (B < 1 || Hq < 1 || Hkv < 1 || S < 1 || D < 2 || D > 256 || (D & 1) || Hq % Hkv) return Q3_ERR_SHAPE;
+  if (B * Hq > 65535) return Q3_ERR_SHAPE;
+  return Q3_OK;
+}
+static bool tc_eligible(const void* q, const void* k, const void* v, const void* o, int64_t D, int dtype) {
+  return attn_tc_available() && D == 128 && (dtype == Q3_BF16 || dtype == Q3_F16) && aligned16(q) && aligned16(k) &&
+         aligned16(v) && aligned16(o);
+}
+}  // namespace q3
+
+using namespace q3;
+
+// 1 if the tensor-core attention kernels run for these arguments, 0 for the CUDA-core kernels.
+extern "C" int q3_attn_path(const void* q, const void* k, const void* v, const void* out, int64_t D, int dtype) {
+  return tc_eligible(q, k, v, out, D, dtype) ? 1 : 0;
+}
+
+extern "C" int q3_attn_fwd(const void* q, const void* k, const void* v, void* out, float* lse, int64_t B, int64_t Hq,
+                           int64_t Hkv, int64_t S, int64_t D, double scale, int dtype, int* status,
+                           q3_stream_t stream) {
+  if (!q || !k || !v || !out || !lse) return Q3_ERR_ARG;
+  int rc = check_shape(B, Hq, Hkv, S, D);
+  if (rc != Q3_OK) return rc;
+  if (dtype < Q3_F32 || dtype > Q3_F16) return Q3_ERR_DTYPE;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (tc_eligible(q, k, v, out, D, dtype)) return attn_fwd_tc(q, k, v, out, lse, B, Hq, Hkv, S, (float)scale, dtype, status, st);
+  return attn_fwd_simt(q, k, v, out, lse, B, Hq, Hkv, S, D, (float)scale, dtype, st);
+}
+
+extern "C" int64_t q3_attn_bwd_workspace_bytes(int64_t B, int64_t Hq, int64_t Hkv, int64_t S, int64_t D) {
+  (void)Hkv; (void)D;
+  return B * Hq * S * 4;  // delta = rowsum(dO * O), fp32
+}
+
+extern "C" int q3_attn_bwd(const void* q, const void* k, const void* v, const void* out, const void* dout,
+                           const float* lse, void* dq, void* dk, void* dv, void* workspace, int64_t workspace_bytes,
+                           int64_t B, int64_t Hq, int64_t Hkv, int64_t S, int64_t D, double scale, int dtype,
+                           int* status, q3_stream_t stream) {
+  if (!q || !k || !v || !out || !dout || !lse || !dq || !dk || !dv) return Q3_ERR_ARG;
+  int rc = check_shape(B, Hq, Hkv, S, D);
+  if (rc != Q3_OK) return rc;
+  if (dtype < Q3_F32 || dtype > Q3_F16) return Q3_ERR_DTYPE;
+  if (!workspace || workspace_bytes < q3_attn_bwd_workspace_bytes(B, Hq, Hkv, S, D)) return Q3_ERR_WORKSPACE;
+  cudaStream_t st = (cudaStream_t)stream;
+  float* delta = (float*)workspace;
+  rc = attn_delta(out, dout, delta, B * Hq * S, D, dtype, st);
+  if (rc != Q3_OK) return rc;
+  if (tc_eligible(q, k, v, dout, D, dtype) && aligned16(dq) && aligned16(dk) && aligned16(dv))
+    return attn_bwd_tc(q, k, v, dout, lse, delta, dq, dk, dv, B, Hq, Hkv, S, (float)scale, dtype, status, st);
+  return attn_bwd_simt(q, k, v, dout, lse, delta, dq, dk, dv, B, Hq, Hkv, S, D, (float)scale, dtype, st);
+}

@@ -1,0 +1,418 @@
+// Dense bf16/fp16 GEMM on the 5th-generation tensor cores (tcgen05) with fp32 accumulators in
+// tensor memory, operands staged by TMA into 128-byte-swizzled shared memory.
+//
+//   C[M,N] = A[M,K] * B[K,N]   (contiguous C in bf16 / fp16 / fp32)
+//
+// Either operand may be stored with the contraction dimension contiguous ("K-major": A as [M,K]
+// row-major, B as [N,K] row-major) or with its outer dimension contiguous ("MN-major": A as [K,M]
+// row-major, B as [K,N] row-major). That covers the three products of a linear layer without a
+// transpose copy: forward X*W^T (K-major, K-major), input gradient dY*W (K-major, MN-major) and
+// weight gradient dY^T*X (MN-major, MN-major).
+//
+// Kernel structure (persistent, one CTA per SM, 192 threads):
+//   warp 0   : TMA producer - fills a ring of {A tile 128x64, B tile BNx64} stages
+//   warp 1   : MMA issuer  - one thread issues tcgen05.mma (M=128, N=BN, K=16) x4 per stage into one
+//              of two TMEM accumulators, releases stages with tcgen05.commit
+//   warps 2-5: epilogue    - tcgen05.ld the finished accumulator (32 lanes per warp), convert and
+//              store while the MMA warp already works on the next tile in the other accumulator
+// Tiles are visited in grouped-M order so that CTAs running together share operand tiles in L2.
+// TMA loads are plain per-CTA loads (no cluster multicast).
+//
+// The fused gate/up variant loads W_gate and W_up rows into one 256-row B tile, so one N=256 MMA
+// produces gate in accumulator columns [0,128) and up in [128,256); its epilogue stores G, U and
+// Y = silu(G)*U.
+//
+// Replaces, in the reference: qwen3_triton/kernels/linear.py:14-77 (_gemm / matmul),
+// kernels/mlp.py:14-32 and kernels/mlp_precision.py:17-35 (_gate_up).
+#include "tcgen05.cuh"
+
+namespace q3 {
+
+int gemm_simt(const void* a, int64_t a_sm, int64_t a_sk, const void* b, int64_t b_sk, int64_t b_sn, void* c,
+              int64_t M, int64_t N, int64_t K, int in_dtype, int out_dtype, cudaStream_t st);
+
+namespace tc {
+
+constexpr int BM = 128, BK = 64, UK = 16;
+constexpr int kGemmThreads = 192;
+constexpr int kGroupM = 8;
+
+struct GemmParams {
+  void* c0;   // C, or G for the gate/up variant
+  void* c1;   // U
+  void* c2;   // Y
+  int64_t M, N, K;  // N = output columns (per matrix for gate/up)
+  int tiles_m, tiles_n, kblocks;
+  uint32_t idesc;
+  int a_mn, b_mn;   // operand is MN-major
+  int* status;
+};
+
+template <int BN> struct Cfg {
+  static constexpr int A_BYTES = BM * BK * 2;
+  static constexpr int B_BYTES = BN * BK * 2;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int STAGES = (BN == 256) ? 4 : 6;
+  static constexpr int TMEM_COLS = 2 * BN;  // two accumulators
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+};
+
+__device__ __forceinline__ float silu_f(float g) { return g / (1.f + __expf(-g)); }
+
+template <typename TO> __device__ __forceinline__ void store_chunk32(TO* dst, const uint32_t (&r)[32], int64_t col0, int64_t N);
+
+template <> __device__ __forceinline__ void store_chunk32<float>(float* dst, const uint32_t (&r)[32], int64_t col0, int64_t N) {
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    if (col0 + 4 * j + 4 <= N)
+      *reinterpret_cast<float4*>(dst + 4 * j) = make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
+                                                            __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
+  }
+}
+template <> __device__ __forceinline__ void store_chunk32<__nv_bfloat16>(__nv_bfloat16* dst, const uint32_t (&r)[32], int64_t col0, int64_t N) {
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    if (col0 + 8 * j + 8 <= N) {
+      uint4 v;
+      __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&v);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) h[e] = __floats2bfloat162_rn(__uint_as_float(r[8 * j + 2 * e]), __uint_as_float(r[8 * j + 2 * e + 1]));
+      *reinterpret_cast<uint4*>(dst + 8 * j) = v;
+    }
+  }
+}
+template <> __device__ __forceinline__ void store_chunk32<__half>(__half* dst, const uint32_t (&r)[32], int64_t col0, int64_t N) {
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    if (col0 + 8 * j + 8 <= N) {
+      uint4 v;
+      __half2* h = reinterpret_cast<__half2*>(&v);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) h[e] = __floats2half2_rn(__uint_as_float(r[8 * j + 2 * e]), __uint_as_float(r[8 * j + 2 * e + 1]));
+      *reinterpret_cast<uint4*>(dst + 8 * j) = v;
+    }
+  }
+}
+
+__device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int& mi, int& ni) {
+  const int group = kGroupM * tiles_n;
+  const int g = tile / group, first = g * kGroupM;
+  const int height = (tiles_m - first) < kGroupM ? (tiles_m - first) : kGroupM;
+  const int in = tile - g * group;
+  mi = first + in % height;
+  ni = in / height;
+}
+
+// GATE_UP = false: C = A*B.  GATE_UP = true: BN must be 256; B tile = [W_gate rows | W_up rows].
+template <int BN, typename TO, bool GATE_UP>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+               const __grid_constant__ CUtensorMap tmB2, const GemmParams p) {
+  using C = Cfg<BN>;
+  extern __shared__ uint8_t smem_raw[];
+  // 1024-byte alignment keeps the 128-byte swizzle phase identical for TMA and UMMA.
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem = smem_raw + (smem_base - smem_u32(smem_raw));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::STAGES * C::STAGE_BYTES);
+  // barrier slots: full[STAGES], empty[STAGES], tfull[2], tempty[2], done
+  const uint32_t bar0 = smem_u32(bars);
+  auto full_bar = [&](int s) { return bar0 + 8u * s; };
+  auto empty_bar = [&](int s) { return bar0 + 8u * (C::STAGES + s); };
+  auto tfull_bar = [&](int a) { return bar0 + 8u * (2 * C::STAGES + a); };
+  auto tempty_bar = [&](int a) { return bar0 + 8u * (2 * C::STAGES + 2 + a); };
+  const uint32_t done_bar = bar0 + 8u * (2 * C::STAGES + 4);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * C::STAGES + 5);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int total_tiles = p.tiles_m * p.tiles_n;
+
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    for (int s = 0; s < C::STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+    for (int a = 0; a < 2; ++a) { mbar_init(tfull_bar(a), 1); mbar_init(tempty_bar(a), 4); }
+    mbar_init(done_bar, 1);
+    fence_barrier_init();
+    prefetch_tmap(&tmA);
+    prefetch_tmap(&tmB);
+    if (GATE_UP) prefetch_tmap(&tmB2);
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(tmem_slot), C::TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------- TMA producer
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+        int mi, ni;
+        tile_coords(tile, p.tiles_m, p.tiles_n, mi, ni);
+        const int m0 = mi * BM, n0 = ni * (GATE_UP ? BN / 2 : BN);
+        for (int kb = 0; kb < p.kblocks; ++kb, ++it) {
+          const int s = it % C::STAGES;
+          const uint32_t ph = (it / C::STAGES) & 1u;
+          if (!mbar_wait(empty_bar(s), ph ^ 1u, abort_flag)) { ok = false; break; }
+          const uint32_t a_dst = smem_base + s * C::STAGE_BYTES, b_dst = a_dst + C::A_BYTES;
+          mbar_expect_tx(full_bar(s), C::STAGE_BYTES);
+          const int k0 = kb * BK;
+          if (!p.a_mn) {
+            tma_load_2d(a_dst, &tmA, k0, m0, full_bar(s));
+          } else {
+#pragma unroll
+            for (int j = 0; j < BM / 64; ++j) tma_load_2d(a_dst + j * (BK * 128), &tmA, m0 + 64 * j, k0, full_bar(s));
+          }
+          if (GATE_UP) {
+            tma_load_2d(b_dst, &tmB, k0, n0, full_bar(s));
+            tma_load_2d(b_dst + (BN / 2) * 128, &tmB2, k0, n0, full_bar(s));
+          } else if (!p.b_mn) {
+            tma_load_2d(b_dst, &tmB, k0, n0, full_bar(s));
+          } else {
+#pragma unroll
+            for (int j = 0; j < BN / 64; ++j) tma_load_2d(b_dst + j * (BK * 128), &tmB, n0 + 64 * j, k0, full_bar(s));
+          }
+        }
+      }
+      // Do not leave the CTA while bulk copies may still be landing in its shared memory.
+      const uint32_t pending = it < (uint32_t)C::STAGES ? it : (uint32_t)C::STAGES;
+      for (uint32_t j = it - pending; j < it; ++j) {
+        const int s = j % C::STAGES;
+        const uint32_t ph = (j / C::STAGES) & 1u;
+        for (uint32_t spin = 0; spin < kSpinLimit && !mbar_try_wait(full_bar(s), ph); ++spin) __nanosleep(64);
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      uint32_t it = 0, tl = 0;
+      bool ok = true;
+      const uint32_t a_lbo = p.a_mn ? BK * 128 : 0, b_lbo = p.b_mn ? BK * 128 : 0;
+      const uint32_t a_kadv = p.a_mn ? (UK * 128) >> 4 : (UK * 2) >> 4;  // descriptor units of 16 B
+      const uint32_t b_kadv = p.b_mn ? (UK * 128) >> 4 : (UK * 2) >> 4;
+      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++tl) {
+        const int acc = tl & 1;
+        const uint32_t aph = (tl >> 1) & 1u;
+        if (!mbar_wait(tempty_bar(acc), aph ^ 1u, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < p.kblocks; ++kb, ++it) {
+          const int s = it % C::STAGES;
+          const uint32_t ph = (it / C::STAGES) & 1u;
+          if (!mbar_wait(full_bar(s), ph, abort_flag)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t a_src = smem_base + s * C::STAGE_BYTES, b_src = a_src + C::A_BYTES;
+          const uint64_t adesc = make_smem_desc(a_src, a_lbo, 1024);
+          const uint64_t bdesc = make_smem_desc(b_src, b_lbo, 1024);
+#pragma unroll
+          for (int k = 0; k < BK / UK; ++k)
+            mma_f16_ss(d_tmem, adesc + (uint64_t)(k * a_kadv), bdesc + (uint64_t)(k * b_kadv), p.idesc,
+                       (kb | k) != 0 ? 1u : 0u);
+          mma_commit(empty_bar(s));
+        }
+        if (ok) mma_commit(tfull_bar(acc));
+      }
+      // Everything issued must have completed before tensor memory is released.
+      mma_commit(done_bar);
+      for (uint32_t spin = 0; spin < kSpinLimit && !mbar_try_wait(done_bar, 0); ++spin) __nanosleep(64);
+    }
+  } else {
+    // ------------------------------------------------------------- epilogue (warps 2..5)
+    const int q = warp & 3;  // TMEM lane quarter this warp may access
+    uint32_t tl = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++tl) {
+      int mi, ni;
+      tile_coords(tile, p.tiles_m, p.tiles_n, mi, ni);
+      const int acc = tl & 1;
+      const uint32_t aph = (tl >> 1) & 1u;
+      if (!mbar_wait(tfull_bar(acc), aph, abort_flag)) { ok = false; break; }
+      tc_fence_after();
+      const int64_t row = (int64_t)mi * BM + q * 32 + lane;
+      const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN;
+      if constexpr (!GATE_UP) {
+        const int64_t n0 = (int64_t)ni * BN;
+        TO* crow = reinterpret_cast<TO*>(p.c0) + row * p.N + n0;
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld32(t_row + c * 32, r);
+          tmem_ld_wait();
+          if (row < p.M && n0 + c * 32 < p.N) store_chunk32<TO>(crow + c * 32, r, n0 + c * 32, p.N);
+        }
+      } else {
+        const int64_t n0 = (int64_t)ni * (BN / 2);
+        TO* grow = reinterpret_cast<TO*>(p.c0) + row * p.N + n0;
+        TO* urow = reinterpret_cast<TO*>(p.c1) + row * p.N + n0;
+        TO* yrow = reinterpret_cast<TO*>(p.c2) + row * p.N + n0;
+#pragma unroll 1
+        for (int c = 0; c < BN / 64; ++c) {
+          uint32_t g[32], u[32];
+          tmem_ld32(t_row + c * 32, g);
+          tmem_ld32(t_row + BN / 2 + c * 32, u);
+          tmem_ld_wait();
+          if (row < p.M && n0 + c * 32 < p.N) {
+            store_chunk32<TO>(grow + c * 32, g, n0 + c * 32, p.N);
+            store_chunk32<TO>(urow + c * 32, u, n0 + c * 32, p.N);
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              // the saved (rounded) gate/up values define Y, so backward reproduces it exactly
+              const float gr = to_f32<TO>(from_f32<TO>(__uint_as_float(g[j])));
+              const float ur = to_f32<TO>(from_f32<TO>(__uint_as_float(u[j])));
+              g[j] = __float_as_uint(silu_f(gr) * ur);
+            }
+            store_chunk32<TO>(yrow + c * 32, g, n0 + c * 32, p.N);
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(tempty_bar(acc));
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, C::TMEM_COLS);
+  }
+  if (threadIdx.x == 0 && *abort_flag) flag_status(p.status, Q3_STATUS_WAIT_TIMEOUT);
+}
+
+struct Operand {
+  const void* ptr;
+  bool mn_major;
+  int64_t ld;  // leading dimension in elements
+};
+
+// Classify an operand given the strides of its (outer, contraction) dimensions.
+inline bool classify(const void* ptr, int64_t s_outer, int64_t s_k, int64_t outer, int64_t k, Operand* o) {
+  if (!aligned16(ptr)) return false;
+  if (s_k == 1 && (s_outer % 8 == 0 || outer == 1) && s_outer >= k) { *o = {ptr, false, s_outer}; return true; }
+  if (s_outer == 1 && (s_k % 8 == 0 || k == 1) && s_k >= outer) { *o = {ptr, true, s_k}; return true; }
+  return false;
+}
+
+template <int BN, typename TO, bool GATE_UP>
+int launch_gemm(const Operand& A, const Operand& B, const void* b2, GemmParams& p, bool bf16, cudaStream_t st) {
+  using C = Cfg<BN>;
+  CUtensorMap tmA, tmB, tmB2;
+  int rc;
+  if (!A.mn_major) rc = make_tmap_2d(&tmA, A.ptr, bf16, p.M, p.K, A.ld, BK, BM);
+  else rc = make_tmap_2d(&tmA, A.ptr, bf16, p.K, p.M, A.ld, 64, BK);
+  if (rc != Q3_OK) return rc;
+  if (!B.mn_major) rc = make_tmap_2d(&tmB, B.ptr, bf16, p.N, p.K, B.ld, BK, GATE_UP ? BN / 2 : BN);
+  else rc = make_tmap_2d(&tmB, B.ptr, bf16, p.K, p.N, B.ld, 64, BK);
+  if (rc != Q3_OK) return rc;
+  tmB2 = tmB;
+  if (GATE_UP) {
+    rc = make_tmap_2d(&tmB2, b2, bf16, p.N, p.K, B.ld, BK, BN / 2);
+    if (rc != Q3_OK) return rc;
+  }
+  const int n_per_tile = GATE_UP ? BN / 2 : BN;
+  p.tiles_m = (int)cdiv(p.M, BM);
+  p.tiles_n = (int)cdiv(p.N, n_per_tile);
+  p.kblocks = (int)cdiv(p.K, BK);
+  p.a_mn = A.mn_major;
+  p.b_mn = B.mn_major;
+  p.idesc = make_idesc_f16(BM, BN, bf16, A.mn_major, B.mn_major);
+  const int64_t tiles = (int64_t)p.tiles_m * p.tiles_n;
+  const int grid = (int)(tiles < sm_count() ? tiles : sm_count());
+  auto kern = gemm_tc_kernel<BN, TO, GATE_UP>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
+    if (e != cudaSuccess) return Q3_ERR_CUDA - (int)e;
+    configured = true;
+  }
+  kern<<<grid, kGemmThreads, C::SMEM_BYTES, st>>>(tmA, tmB, tmB2, p);
+  return launch_status();
+}
+
+inline int pick_bn(int64_t M, int64_t N) {
+  if (N <= 128) return 128;
+  const int64_t sms = sm_count();
+  const int64_t t256 = cdiv(M, BM) * cdiv(N, 256), t128 = cdiv(M, BM) * cdiv(N, 128);
+  // cost ~ waves * tile width
+  const int64_t c256 = cdiv(t256, sms) * 2, c128 = cdiv(t128, sms);
+  return c128 < c256 ? 128 : 256;
+}
+
+}  // namespace tc
+}  // namespace q3
+
+using namespace q3;
+
+// Which path q3_gemm takes for these arguments: 1 = tcgen05 tensor cores, 0 = CUDA-core fallback.
+extern "C" int q3_gemm_path(const void* a, int64_t a_sm, int64_t a_sk, const void* b, int64_t b_sk, int64_t b_sn,
+                            const void* c, int64_t M, int64_t N, int64_t K, int in_dtype, int out_dtype) {
+  if (in_dtype != Q3_BF16 && in_dtype != Q3_F16) return 0;
+  if (out_dtype != Q3_F32 && out_dtype != in_dtype) return 0;
+  if (M < 1 || N < 1 || K < 1 || M > 2147483647LL / 2 || N > 2147483647LL / 2 || K > 2147483647LL / 2) return 0;
+  if (!aligned16(c) || N % (out_dtype == Q3_F32 ? 4 : 8)) return 0;
+  tc::Operand A, B;
+  if (!tc::classify(a, a_sm, a_sk, M, K, &A)) return 0;
+  if (!tc::classify(b, b_sn, b_sk, N, K, &B)) return 0;
+  return 1;
+}
+
+extern "C" int q3_gemm(const void* a, int64_t a_sm, int64_t a_sk, const void* b, int64_t b_sk, int64_t b_sn, void* c,
+                       int64_t M, int64_t N, int64_t K, int in_dtype, int out_dtype, int* status,
+                       q3_stream_t stream) {
+  if (!a || !b || !c) return Q3_ERR_ARG;
+  if (M < 1 || N < 1 || K < 1 || a_sm < 1 || a_sk < 1 || b_sk < 1 || b_sn < 1) return Q3_ERR_SHAPE;
+  if (in_dtype < Q3_F32 || in_dtype > Q3_F16 || out_dtype < Q3_F32 || out_dtype > Q3_F16) return Q3_ERR_DTYPE;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (!q3_gemm_path(a, a_sm, a_sk, b, b_sk, b_sn, c, M, N, K, in_dtype, out_dtype))
+    return gemm_simt(a, a_sm, a_sk, b, b_sk, b_sn, c, M, N, K, in_dtype, out_dtype, st);
+  tc::Operand A, B;
+  tc::classify(a, a_sm, a_sk, M, K, &A);
+  tc::classify(b, b_sn, b_sk, N, K, &B);
+  tc::GemmParams p{};
+  p.c0 = c; p.M = M; p.N = N; p.K = K; p.status = status;
+  const bool bf16 = in_dtype == Q3_BF16;
+  const int bn = tc::pick_bn(M, N);
+  if (out_dtype == Q3_F32)
+    return bn == 256 ? tc::launch_gemm<256, float, false>(A, B, nullptr, p, bf16, st)
+                     : tc::launch_gemm<128, float, false>(A, B, nullptr, p, bf16, st);
+  if (bf16)
+    return bn == 256 ? tc::launch_gemm<256, __nv_bfloat16, false>(A, B, nullptr, p, bf16, st)
+                     : tc::launch_gemm<128, __nv_bfloat16, false>(A, B, nullptr, p, bf16, st);
+  return bn == 256 ? tc::launch_gemm<256, __half, false>(A, B, nullptr, p, bf16, st)
+                   : tc::launch_gemm<128, __half, false>(A, B, nullptr, p, bf16, st);
+}
+
+// 1 if q3_gate_up_swiglu_fwd runs the fused tensor-core kernel for these arguments.
+extern "C" int q3_gate_up_path(const void* x, const void* wg, const void* wu, const void* g, const void* u,
+                               const void* y, int64_t M, int64_t N, int64_t K, int dtype) {
+  if (dtype != Q3_BF16 && dtype != Q3_F16) return 0;
+  if (M < 1 || N < 1 || K < 1 || (K % 8) || (N % 8)) return 0;
+  return aligned16(x) && aligned16(wg) && aligned16(wu) && aligned16(g) && aligned16(u) && aligned16(y);
+}
+
+extern "C" int q3_gate_up_swiglu_fwd(const void* x, const void* w_gate, const void* w_up, void* gate, void* up,
+                                     void* y, int64_t M, int64_t N, int64_t K, int dtype, int* status,
+                                     q3_stream_t stream) {
+  if (!x || !w_gate || !w_up || !gate || !up || !y) return Q3_ERR_ARG;
+  if (M < 1 || N < 1 || K < 1) return Q3_ERR_SHAPE;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (!q3_gate_up_path(x, w_gate, w_up, gate, up, y, M, N, K, dtype)) {
+    // unfused: two CUDA-core GEMMs and the SwiGLU kernel
+    int rc = gemm_simt(x, K, 1, w_gate, 1, K, gate, M, N, K, dtype, dtype, st);
+    if (rc != Q3_OK) return rc;
+    rc = gemm_simt(x, K, 1, w_up, 1, K, up, M, N, K, dtype, dtype, st);
+    if (rc != Q3_OK) return rc;
+    return q3_swiglu_fwd(gate, up, y, M * N, dtype, stream);
+  }
+  tc::Operand A{x, false, K}, B{w_gate, false, K};
+  tc::GemmParams p{};
+  p.c0 = gate; p.c1 = up; p.c2 = y; p.M = M; p.N = N; p.K = K; p.status = status;
+  if (dtype == Q3_BF16) return tc::launch_gemm<256, __nv_bfloat16, true>(A, B, w_up, p, true, st);
+  return tc::launch_gemm<256, __half, true>(A, B, w_up, p, false, st);
+}

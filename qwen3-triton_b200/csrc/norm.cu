@@ -1,0 +1,599 @@
+// Row-wise bandwidth-bound kernels: RMSNorm fwd/bwd, residual-add + RMSNorm fused fwd/bwd,
+// per-head RMSNorm + split-half RoPE fwd/bwd, rotary tables and rotary application.
+//
+// Layout: rows of H (or D) contiguous elements. A row is owned by `tpr` consecutive threads,
+// each caching a few 16-byte vectors of the row in registers, so every input byte is read from
+// HBM exactly once. fp32 math, one rounding on store. Weight gradients are deterministic:
+// each CTA keeps per-column partial sums in registers over all of its rows, combines its row
+// slots through shared memory in a fixed order, writes one partial row to the workspace and a
+// second kernel sums the partial rows in a fixed order. No atomics.
+//
+// Replaces, in the reference: qwen3_triton/kernels/norm.py:7-37 (_forward/_backward/_reduce_rows),
+// kernels/math_precision.py:16-21 (_hf_norm_forward), kernels/norm_rope.py:12-50 and
+// math_precision.py:40-50 (norm+RoPE fwd/bwd), kernels/rotary.py:12-34 (_tables/_apply),
+// ops/triton/rms_norm.py, ops/triton/rope.py, ops/triton/fused_qk_norm_rope.py.
+// Math follows ops/reference/rms_norm.py:6-13, ops/reference/rope.py:6-55 and
+// ops/reference/fused_qk_norm_rope.py:9-80 (fp32 internally, single rounding).
+#include "common.cuh"
+
+namespace q3 {
+
+constexpr int kRowThreads = 256;
+constexpr int kPartialRowsPerSm = 4;  // partial dW rows written per SM (workspace bound)
+
+// Sum over the `tpr` threads that own one row. tpr is a power of two; rows never straddle a
+// warp when tpr <= 32. For tpr > 32 every thread of the block must call this (it synchronises).
+__device__ __forceinline__ float row_sum(float v, int tpr, float* sm) {
+  if (tpr <= 32) {
+    for (int o = tpr >> 1; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+  }
+  v = warp_sum(v);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, wpr = tpr >> 5;
+  __syncthreads();
+  if (lane == 0) sm[warp] = v;
+  __syncthreads();
+  const int first = (warp / wpr) * wpr;
+  float t = 0.f;
+  for (int i = 0; i < wpr; ++i) t += sm[first + i];
+  return t;
+}
+
+// Per-thread register cache depth and the widest row group, by vector width. The scalar path
+// (odd H or unaligned pointers) may use 1024-thread blocks; the vector paths stay at 256.
+template <int V> struct MaxVec {
+  static constexpr int N = (V == 8) ? 4 : 8;
+  static constexpr int MAX_TPR = (V == 1) ? 1024 : 256;
+};
+
+// ------------------------------------------------------------------ RMSNorm forward
+template <typename T, int V, bool ADD>
+__global__ void __launch_bounds__(MaxVec<V>::MAX_TPR) rmsnorm_fwd_kernel(const T* __restrict__ x, const T* __restrict__ res,
+                                                           const T* __restrict__ w, T* __restrict__ y,
+                                                           T* __restrict__ res_out, float* __restrict__ inv,
+                                                           int64_t rows, int H, float eps, int tpr) {
+  constexpr int MV = MaxVec<V>::N;
+  __shared__ float sm[32];
+  const int rpb = blockDim.x / tpr, rib = threadIdx.x / tpr, t = threadIdx.x % tpr, nvec = H / V;
+  for (int64_t base = (int64_t)blockIdx.x * rpb; base < rows; base += (int64_t)gridDim.x * rpb) {
+    const int64_t row = base + rib;
+    const bool valid = row < rows;
+    float c[MV][V];
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < MV; ++i) {
+      const int v = t + i * tpr;
+      if (valid && v < nvec) {
+        VecIO<T, V>::load(x + row * H + (int64_t)v * V, c[i]);
+        if constexpr (ADD) {
+          float r[V];
+          VecIO<T, V>::load(res + row * H + (int64_t)v * V, r);
+#pragma unroll
+          for (int j = 0; j < V; ++j) c[i][j] = to_f32<T>(from_f32<T>(c[i][j] + r[j]));  // the stored value is what is normalised
+          VecIO<T, V>::store(res_out + row * H + (int64_t)v * V, c[i]);
+        }
+#pragma unroll
+        for (int j = 0; j < V; ++j) ss += c[i][j] * c[i][j];
+      }
+    }
+    ss = row_sum(ss, tpr, sm);
+    const float r = rsqrtf(ss / (float)H + eps);
+#pragma unroll
+    for (int i = 0; i < MV; ++i) {
+      const int v = t + i * tpr;
+      if (valid && v < nvec) {
+        float ww[V], o[V];
+        VecIO<T, V>::load(w + (int64_t)v * V, ww);
+#pragma unroll
+        for (int j = 0; j < V; ++j) o[j] = c[i][j] * r * ww[j];
+        VecIO<T, V>::store(y + row * H + (int64_t)v * V, o);
+      }
+    }
+    if (valid && t == 0) inv[row] = r;
+  }
+}
+
+// ------------------------------------------------------------------ RMSNorm backward
+// dx = inv * (dy*w - x * inv^2 * mean(dy*w*x)) [+ dres];  dW[c] = sum_rows dy * x * inv.
+template <typename T, int V, bool ADD>
+__global__ void __launch_bounds__(MaxVec<V>::MAX_TPR) rmsnorm_bwd_kernel(const T* __restrict__ x, const T* __restrict__ w,
+                                                           const T* __restrict__ dy, const T* __restrict__ dres,
+                                                           const float* __restrict__ inv, T* __restrict__ dx,
+                                                           float* __restrict__ partial, int64_t rows, int H, int tpr) {
+  constexpr int MV = MaxVec<V>::N;
+  extern __shared__ float dsm[];  // [32] reduction scratch, then [rpb][H] combine buffer
+  float* sm = dsm;
+  float* comb = dsm + 32;
+  const int rpb = blockDim.x / tpr, rib = threadIdx.x / tpr, t = threadIdx.x % tpr, nvec = H / V;
+  float acc[MV][V];
+#pragma unroll
+  for (int i = 0; i < MV; ++i)
+#pragma unroll
+    for (int j = 0; j < V; ++j) acc[i][j] = 0.f;
+
+  for (int64_t base = (int64_t)blockIdx.x * rpb; base < rows; base += (int64_t)gridDim.x * rpb) {
+    const int64_t row = base + rib;
+    const bool valid = row < rows;
+    float cx[MV][V], cg[MV][V];
+    float s = 0.f;
+    const float r = valid ? inv[row] : 0.f;
+#pragma unroll
+    for (int i = 0; i < MV; ++i) {
+      const int v = t + i * tpr;
+      if (valid && v < nvec) {
+        float ww[V];
+        VecIO<T, V>::load(x + row * H + (int64_t)v * V, cx[i]);
+        VecIO<T, V>::load(dy + row * H + (int64_t)v * V, cg[i]);
+        VecIO<T, V>::load(w + (int64_t)v * V, ww);
+#pragma unroll
+        for (int j = 0; j < V; ++j) {
+          acc[i][j] += cg[i][j] * cx[i][j] * r;
+          cg[i][j] *= ww[j];
+          s += cg[i][j] * cx[i][j];
+        }
+      }
+    }
+    s = row_sum(s, tpr, sm);
+    const float coef = s * r * r / (float)H;
+#pragma unroll
+    for (int i = 0; i < MV; ++i) {
+      const int v = t + i * tpr;
+      if (valid && v < nvec) {
+        float o[V];
+#pragma unroll
+        for (int j = 0; j < V; ++j) o[j] = (cg[i][j] - cx[i][j] * coef) * r;
+        if constexpr (ADD) {
+          if (dres != nullptr) {
+            float d[V];
+            VecIO<T, V>::load(dres + row * H + (int64_t)v * V, d);
+#pragma unroll
+            for (int j = 0; j < V; ++j) o[j] += d[j];
+          }
+        }
+        VecIO<T, V>::store(dx + row * H + (int64_t)v * V, o);
+      }
+    }
+  }
+  // Combine the row slots of this CTA in a fixed order, then write one partial row.
+  __syncthreads();
+#pragma unroll
+  for (int i = 0; i < MV; ++i) {
+    const int v = t + i * tpr;
+    if (v < nvec) {
+#pragma unroll
+      for (int j = 0; j < V; ++j) comb[(int64_t)rib * H + v * V + j] = acc[i][j];
+    }
+  }
+  __syncthreads();
+  for (int c = threadIdx.x; c < H; c += blockDim.x) {
+    float tsum = 0.f;
+    for (int r2 = 0; r2 < rpb; ++r2) tsum += comb[(int64_t)r2 * H + c];
+    partial[(int64_t)blockIdx.x * H + c] = tsum;
+  }
+}
+
+// Sum `parts` partial rows of width H in a fixed order; output in dtype T.
+template <typename T>
+__global__ void __launch_bounds__(256) reduce_partials_kernel(const float* __restrict__ partial, T* __restrict__ out,
+                                                              int parts, int H) {
+  __shared__ float sm[8][33];
+  const int col = blockIdx.x * 32 + threadIdx.x;  // blockDim = (32, 8)
+  float s = 0.f;
+  if (col < H)
+    for (int p = threadIdx.y; p < parts; p += 8) s += partial[(int64_t)p * H + col];
+  sm[threadIdx.y][threadIdx.x] = s;
+  __syncthreads();
+  if (threadIdx.y == 0 && col < H) {
+    float t = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) t += sm[i][threadIdx.x];
+    out[col] = from_f32<T>(t);
+  }
+}
+
+// ------------------------------------------------------------------ per-head RMSNorm + RoPE
+// Row = (token, head) of D elements; each thread owns vector pairs (c, c + D/2).
+//   y1 = n1*cos1 - n2*sin1 ; y2 = n2*cos2 + n1*sin2, n = x * inv * w
+template <typename T, int V, bool NORM>
+__global__ void __launch_bounds__(kRowThreads) norm_rope_fwd_kernel(
+    const T* __restrict__ x, const T* __restrict__ w, const T* __restrict__ cs, const T* __restrict__ sn,
+    T* __restrict__ y, float* __restrict__ inv, int64_t rows, int heads, int64_t seq, int D, float eps, int tpr,
+    int layout) {
+  constexpr int MP = 4;
+  const int rpb = blockDim.x / tpr, rib = threadIdx.x / tpr, t = threadIdx.x % tpr, half = D / 2, npair = half / V;
+  for (int64_t base = (int64_t)blockIdx.x * rpb; base < rows; base += (int64_t)gridDim.x * rpb) {
+    const int64_t row = base + rib;
+    const bool valid = row < rows;
+    // layout 0: x is [tokens, heads, D]; layout 1: x is [batch, heads, seq, D]
+    int64_t token = 0;
+    if (valid) token = layout == 0 ? row / heads : (row / ((int64_t)heads * seq)) * seq + row % seq;
+    float a[MP][V], b[MP][V];
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < MP; ++i) {
+      const int p = t + i * tpr;
+      if (valid && p < npair) {
+        VecIO<T, V>::load(x + row * D + (int64_t)p * V, a[i]);
+        VecIO<T, V>::load(x + row * D + half + (int64_t)p * V, b[i]);
+        if constexpr (NORM) {
+#pragma unroll
+          for (int j = 0; j < V; ++j) ss += a[i][j] * a[i][j] + b[i][j] * b[i][j];
+        }
+      }
+    }
+    float r = 1.f;
+    if constexpr (NORM) {
+      for (int o = tpr >> 1; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+      r = rsqrtf(ss / (float)D + eps);
+    }
+#pragma unroll
+    for (int i = 0; i < MP; ++i) {
+      const int p = t + i * tpr;
+      if (valid && p < npair) {
+        float c1[V], c2[V], s1[V], s2[V], o1[V], o2[V];
+        VecIO<T, V>::load(cs + token * D + (int64_t)p * V, c1);
+        VecIO<T, V>::load(cs + token * D + half + (int64_t)p * V, c2);
+        VecIO<T, V>::load(sn + token * D + (int64_t)p * V, s1);
+        VecIO<T, V>::load(sn + token * D + half + (int64_t)p * V, s2);
+        if constexpr (NORM) {
+          float w1[V], w2[V];
+          VecIO<T, V>::load(w + (int64_t)p * V, w1);
+          VecIO<T, V>::load(w + half + (int64_t)p * V, w2);
+#pragma unroll
+          for (int j = 0; j < V; ++j) { a[i][j] *= r * w1[j]; b[i][j] *= r * w2[j]; }
+        }
+#pragma unroll
+        for (int j = 0; j < V; ++j) {
+          o1[j] = a[i][j] * c1[j] - b[i][j] * s1[j];
+          o2[j] = b[i][j] * c2[j] + a[i][j] * s2[j];
+        }
+        VecIO<T, V>::store(y + row * D + (int64_t)p * V, o1);
+        VecIO<T, V>::store(y + row * D + half + (int64_t)p * V, o2);
+      }
+    }
+    if constexpr (NORM) {
+      if (valid && t == 0) inv[row] = r;
+    }
+  }
+}
+
+// Backward: dn1 = g1*cos1 + g2*sin2 ; dn2 = g2*cos2 - g1*sin1 (transpose of the rotation),
+// then the RMSNorm backward of that on x (NORM) or dn itself is the answer (!NORM).
+template <typename T, int V, bool NORM>
+__global__ void __launch_bounds__(kRowThreads) norm_rope_bwd_kernel(
+    const T* __restrict__ x, const T* __restrict__ w, const T* __restrict__ cs, const T* __restrict__ sn,
+    const T* __restrict__ dy, const float* __restrict__ inv, T* __restrict__ dx, float* __restrict__ partial,
+    int64_t rows, int heads, int64_t seq, int D, int tpr, int layout) {
+  constexpr int MP = 4;
+  extern __shared__ float comb[];  // [rpb][D]
+  const int rpb = blockDim.x / tpr, rib = threadIdx.x / tpr, t = threadIdx.x % tpr, half = D / 2, npair = half / V;
+  float acc1[MP][V], acc2[MP][V];
+#pragma unroll
+  for (int i = 0; i < MP; ++i)
+#pragma unroll
+    for (int j = 0; j < V; ++j) { acc1[i][j] = 0.f; acc2[i][j] = 0.f; }
+
+  for (int64_t base = (int64_t)blockIdx.x * rpb; base < rows; base += (int64_t)gridDim.x * rpb) {
+    const int64_t row = base + rib;
+    const bool valid = row < rows;
+    int64_t token = 0;
+    if (valid) token = layout == 0 ? row / heads : (row / ((int64_t)heads * seq)) * seq + row % seq;
+    float d1[MP][V], d2[MP][V], x1[MP][V], x2[MP][V];
+    float s = 0.f;
+    float r = 1.f;
+    if constexpr (NORM) r = valid ? inv[row] : 0.f;
+#pragma unroll
+    for (int i = 0; i < MP; ++i) {
+      const int p = t + i * tpr;
+      if (valid && p < npair) {
+        float g1[V], g2[V], c1[V], c2[V], s1[V], s2[V];
+        VecIO<T, V>::load(dy + row * D + (int64_t)p * V, g1);
+        VecIO<T, V>::load(dy + row * D + half + (int64_t)p * V, g2);
+        VecIO<T, V>::load(cs + token * D + (int64_t)p * V, c1);
+        VecIO<T, V>::load(cs + token * D + half + (int64_t)p * V, c2);
+        VecIO<T, V>::load(sn + token * D + (int64_t)p * V, s1);
+        VecIO<T, V>::load(sn + token * D + half + (int64_t)p * V, s2);
+#pragma unroll
+        for (int j = 0; j < V; ++j) {
+          d1[i][j] = g1[j] * c1[j] + g2[j] * s2[j];
+          d2[i][j] = g2[j] * c2[j] - g1[j] * s1[j];
+        }
+        if constexpr (NORM) {
+          float w1[V], w2[V];
+          VecIO<T, V>::load(x + row * D + (int64_t)p * V, x1[i]);
+          VecIO<T, V>::load(x + row * D + half + (int64_t)p * V, x2[i]);
+          VecIO<T, V>::load(w + (int64_t)p * V, w1);
+          VecIO<T, V>::load(w + half + (int64_t)p * V, w2);
+#pragma unroll
+          for (int j = 0; j < V; ++j) {
+            acc1[i][j] += d1[i][j] * x1[i][j] * r;
+            acc2[i][j] += d2[i][j] * x2[i][j] * r;
+            d1[i][j] *= w1[j];
+            d2[i][j] *= w2[j];
+            s += d1[i][j] * x1[i][j] + d2[i][j] * x2[i][j];
+          }
+        }
+      }
+    }
+    float coef = 0.f;
+    if constexpr (NORM) {
+      for (int o = tpr >> 1; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+      coef = s * r * r / (float)D;
+    }
+#pragma unroll
+    for (int i = 0; i < MP; ++i) {
+      const int p = t + i * tpr;
+      if (valid && p < npair) {
+        if constexpr (NORM) {
+#pragma unroll
+          for (int j = 0; j < V; ++j) {
+            d1[i][j] = (d1[i][j] - x1[i][j] * coef) * r;
+            d2[i][j] = (d2[i][j] - x2[i][j] * coef) * r;
+          }
+        }
+        VecIO<T, V>::store(dx + row * D + (int64_t)p * V, d1[i]);
+        VecIO<T, V>::store(dx + row * D + half + (int64_t)p * V, d2[i]);
+      }
+    }
+  }
+  if constexpr (NORM) {
+    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < MP; ++i) {
+      const int p = t + i * tpr;
+      if (p < npair) {
+#pragma unroll
+        for (int j = 0; j < V; ++j) {
+          comb[rib * D + p * V + j] = acc1[i][j];
+          comb[rib * D + half + p * V + j] = acc2[i][j];
+        }
+      }
+    }
+    __syncthreads();
+    for (int c = threadIdx.x; c < D; c += blockDim.x) {
+      float tsum = 0.f;
+      for (int r2 = 0; r2 < rpb; ++r2) tsum += comb[r2 * D + c];
+      partial[(int64_t)blockIdx.x * D + c] = tsum;
+    }
+  }
+}
+
+// cos/sin tables [tokens, D]: angle = float(pos) * inv_freq[i % (D/2)].
+template <typename T, typename P>
+__global__ void rope_tables_kernel(const P* __restrict__ pos, const float* __restrict__ freq, T* __restrict__ cs,
+                                   T* __restrict__ sn, int64_t tokens, int D) {
+  const int half = D / 2;
+  const int64_t total = tokens * half;
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t tkn = i / half;
+    const int f = (int)(i % half);
+    const float angle = (float)pos[tkn] * freq[f];
+    float s, c;
+    sincosf(angle, &s, &c);
+    const T cv = from_f32<T>(c), sv = from_f32<T>(s);
+    cs[tkn * D + f] = cv; cs[tkn * D + half + f] = cv;
+    sn[tkn * D + f] = sv; sn[tkn * D + half + f] = sv;
+  }
+}
+
+// ------------------------------------------------------------------ host-side planning
+inline int pow2ceil(int v) { int p = 1; while (p < v) p <<= 1; return p; }
+
+struct RowPlan { int tpr, block, rpb, grid; };
+
+inline RowPlan plan_rows(int64_t rows, int nvec, int per_thread, int max_per_thread, int max_tpr, int grid_per_sm) {
+  RowPlan p;
+  p.tpr = pow2ceil((int)cdiv(nvec, per_thread));
+  if (p.tpr > max_tpr) p.tpr = max_tpr;
+  if (cdiv(nvec, p.tpr) > max_per_thread) { p.tpr = -1; return p; }
+  p.block = p.tpr > kRowThreads ? p.tpr : kRowThreads;
+  p.rpb = p.block / p.tpr;
+  int64_t g = cdiv(rows, p.rpb), cap = (int64_t)sm_count() * grid_per_sm;
+  p.grid = (int)(g > cap ? cap : g);
+  return p;
+}
+
+template <typename T, bool ADD>
+int rmsnorm_fwd_launch(const void* x, const void* res, const void* w, void* y, void* res_out, float* inv,
+                       int64_t rows, int64_t H, float eps, cudaStream_t st) {
+  constexpr int VF = Vec16<T>::N;
+  const bool vec = (H % VF == 0) && aligned16(x) && aligned16(w) && aligned16(y) && (!ADD || (aligned16(res) && aligned16(res_out)));
+  if (vec) {
+    RowPlan p = plan_rows(rows, (int)(H / VF), 2, MaxVec<VF>::N, MaxVec<VF>::MAX_TPR, 8);
+    if (p.tpr < 0) return Q3_ERR_SHAPE;
+    rmsnorm_fwd_kernel<T, VF, ADD><<<p.grid, p.block, 0, st>>>((const T*)x, (const T*)res, (const T*)w, (T*)y,
+                                                               (T*)res_out, inv, rows, (int)H, eps, p.tpr);
+  } else {
+    RowPlan p = plan_rows(rows, (int)H, 2, MaxVec<1>::N, MaxVec<1>::MAX_TPR, 8);
+    if (p.tpr < 0) return Q3_ERR_SHAPE;
+    rmsnorm_fwd_kernel<T, 1, ADD><<<p.grid, p.block, 0, st>>>((const T*)x, (const T*)res, (const T*)w, (T*)y,
+                                                              (T*)res_out, inv, rows, (int)H, eps, p.tpr);
+  }
+  return launch_status();
+}
+
+template <typename T, bool ADD>
+int rmsnorm_bwd_launch(const void* x, const void* w, const void* dy, const void* dres, const float* inv, void* dx,
+                       void* dw, float* ws, int64_t ws_bytes, int64_t rows, int64_t H, cudaStream_t st) {
+  constexpr int VF = Vec16<T>::N;
+  const bool vec = (H % VF == 0) && aligned16(x) && aligned16(w) && aligned16(dy) && aligned16(dx) &&
+                   (!ADD || dres == nullptr || aligned16(dres));
+  RowPlan p = vec ? plan_rows(rows, (int)(H / VF), 2, MaxVec<VF>::N, MaxVec<VF>::MAX_TPR, kPartialRowsPerSm)
+                  : plan_rows(rows, (int)H, 2, MaxVec<1>::N, MaxVec<1>::MAX_TPR, kPartialRowsPerSm);
+  if (p.tpr < 0) return Q3_ERR_SHAPE;
+  if (ws == nullptr || ws_bytes < (int64_t)p.grid * H * 4) return Q3_ERR_WORKSPACE;
+  const size_t smem = (32 + (size_t)p.rpb * H) * sizeof(float);
+  if (vec) {
+    if (smem > 48 * 1024)
+      cudaFuncSetAttribute(rmsnorm_bwd_kernel<T, VF, ADD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    rmsnorm_bwd_kernel<T, VF, ADD><<<p.grid, p.block, smem, st>>>((const T*)x, (const T*)w, (const T*)dy,
+                                                                  (const T*)dres, inv, (T*)dx, ws, rows, (int)H, p.tpr);
+  } else {
+    if (smem > 48 * 1024)
+      cudaFuncSetAttribute(rmsnorm_bwd_kernel<T, 1, ADD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    rmsnorm_bwd_kernel<T, 1, ADD><<<p.grid, p.block, smem, st>>>((const T*)x, (const T*)w, (const T*)dy,
+                                                                 (const T*)dres, inv, (T*)dx, ws, rows, (int)H, p.tpr);
+  }
+  reduce_partials_kernel<T><<<(int)cdiv(H, 32), dim3(32, 8), 0, st>>>(ws, (T*)dw, p.grid, (int)H);
+  return launch_status();
+}
+
+template <typename T, bool NORM>
+int norm_rope_fwd_launch(const void* x, const void* w, const void* cs, const void* sn, void* y, float* inv,
+                         int64_t batch, int64_t seq, int64_t heads, int64_t D, float eps, int layout, cudaStream_t st) {
+  constexpr int VF = Vec16<T>::N;
+  const int64_t rows = batch * seq * heads, half = D / 2;
+  const bool vec = (half % VF == 0) && aligned16(x) && aligned16(cs) && aligned16(sn) && aligned16(y) && (!NORM || aligned16(w));
+  if (vec) {
+    RowPlan p = plan_rows(rows, (int)(half / VF), 1, 4, 32, 16);
+    if (p.tpr < 0 || p.tpr > 32) return Q3_ERR_SHAPE;
+    norm_rope_fwd_kernel<T, VF, NORM><<<p.grid, p.block, 0, st>>>((const T*)x, (const T*)w, (const T*)cs, (const T*)sn,
+                                                                  (T*)y, inv, rows, (int)heads, seq, (int)D, eps, p.tpr, layout);
+  } else {
+    RowPlan p = plan_rows(rows, (int)half, 1, 4, 32, 16);
+    if (p.tpr < 0 || p.tpr > 32) return Q3_ERR_SHAPE;
+    norm_rope_fwd_kernel<T, 1, NORM><<<p.grid, p.block, 0, st>>>((const T*)x, (const T*)w, (const T*)cs, (const T*)sn,
+                                                                 (T*)y, inv, rows, (int)heads, seq, (int)D, eps, p.tpr, layout);
+  }
+  return launch_status();
+}
+
+template <typename T, bool NORM>
+int norm_rope_bwd_launch(const void* x, const void* w, const void* cs, const void* sn, const void* dy,
+                         const float* inv, void* dx, void* dw, float* ws, int64_t ws_bytes, int64_t batch, int64_t seq,
+                         int64_t heads, int64_t D, int layout, cudaStream_t st) {
+  constexpr int VF = Vec16<T>::N;
+  const int64_t rows = batch * seq * heads, half = D / 2;
+  const bool vec = (half % VF == 0) && aligned16(cs) && aligned16(sn) && aligned16(dy) && aligned16(dx) &&
+                   (!NORM || (aligned16(x) && aligned16(w)));
+  RowPlan p = vec ? plan_rows(rows, (int)(half / VF), 1, 4, 32, kPartialRowsPerSm * 2)
+                  : plan_rows(rows, (int)half, 1, 4, 32, kPartialRowsPerSm * 2);
+  if (p.tpr < 0 || p.tpr > 32) return Q3_ERR_SHAPE;
+  if (NORM && (ws == nullptr || ws_bytes < (int64_t)p.grid * D * 4)) return Q3_ERR_WORKSPACE;
+  const size_t smem = NORM ? (size_t)p.rpb * D * sizeof(float) : 0;
+  if (vec) {
+    if (smem > 48 * 1024)
+      cudaFuncSetAttribute(norm_rope_bwd_kernel<T, VF, NORM>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    norm_rope_bwd_kernel<T, VF, NORM><<<p.grid, p.block, smem, st>>>((const T*)x, (const T*)w, (const T*)cs, (const T*)sn,
+                                                                     (const T*)dy, inv, (T*)dx, ws, rows, (int)heads, seq,
+                                                                     (int)D, p.tpr, layout);
+  } else {
+    if (smem > 48 * 1024)
+      cudaFuncSetAttribute(norm_rope_bwd_kernel<T, 1, NORM>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    norm_rope_bwd_kernel<T, 1, NORM><<<p.grid, p.block, smem, st>>>((const T*)x, (const T*)w, (const T*)cs, (const T*)sn,
+                                                                    (const T*)dy, inv, (T*)dx, ws, rows, (int)heads, seq,
+                                                                    (int)D, p.tpr, layout);
+  }
+  if (NORM) reduce_partials_kernel<T><<<(int)cdiv(D, 32), dim3(32, 8), 0, st>>>(ws, (T*)dw, p.grid, (int)D);
+  return launch_status();
+}
+
+}  // namespace q3
+
+using namespace q3;
+
+extern "C" int q3_rmsnorm_fwd(const void* x, const void* weight, void* y, float* inv_rms, int64_t rows, int64_t H,
+                              double eps, int dtype, q3_stream_t stream) {
+  if (!x || !weight || !y || !inv_rms) return Q3_ERR_ARG;
+  if (rows < 1 || H < 1 || H > 8192 || !(eps > 0)) return Q3_ERR_SHAPE;
+  Q3_DISPATCH_FLOAT(dtype, T, return (rmsnorm_fwd_launch<T, false>(x, nullptr, weight, y, nullptr, inv_rms, rows, H,
+                                                                   (float)eps, (cudaStream_t)stream)));
+  return Q3_OK;
+}
+
+extern "C" int64_t q3_rmsnorm_bwd_workspace_bytes(int64_t rows, int64_t H) {
+  (void)rows;
+  return (int64_t)sm_count() * kPartialRowsPerSm * 2 * H * 4;
+}
+
+extern "C" int q3_rmsnorm_bwd(const void* x, const void* weight, const void* dy, const float* inv_rms, void* dx,
+                              void* dweight, void* workspace, int64_t workspace_bytes, int64_t rows, int64_t H,
+                              int dtype, q3_stream_t stream) {
+  if (!x || !weight || !dy || !inv_rms || !dx || !dweight) return Q3_ERR_ARG;
+  if (rows < 1 || H < 1 || H > 8192) return Q3_ERR_SHAPE;
+  Q3_DISPATCH_FLOAT(dtype, T, return (rmsnorm_bwd_launch<T, false>(x, weight, dy, nullptr, inv_rms, dx, dweight,
+                                                                   (float*)workspace, workspace_bytes, rows, H,
+                                                                   (cudaStream_t)stream)));
+  return Q3_OK;
+}
+
+extern "C" int q3_add_rmsnorm_fwd(const void* x, const void* residual, const void* weight, void* y,
+                                  void* residual_out, float* inv_rms, int64_t rows, int64_t H, double eps, int dtype,
+                                  q3_stream_t stream) {
+  if (!x || !residual || !weight || !y || !residual_out || !inv_rms) return Q3_ERR_ARG;
+  if (rows < 1 || H < 1 || H > 8192 || !(eps > 0)) return Q3_ERR_SHAPE;
+  Q3_DISPATCH_FLOAT(dtype, T, return (rmsnorm_fwd_launch<T, true>(x, residual, weight, y, residual_out, inv_rms, rows,
+                                                                  H, (float)eps, (cudaStream_t)stream)));
+  return Q3_OK;
+}
+
+extern "C" int q3_add_rmsnorm_bwd(const void* residual_out, const void* weight, const void* dy, const void* dresidual,
+                                  const float* inv_rms, void* dx, void* dweight, void* workspace,
+                                  int64_t workspace_bytes, int64_t rows, int64_t H, int dtype, q3_stream_t stream) {
+  if (!residual_out || !weight || !dy || !inv_rms || !dx || !dweight) return Q3_ERR_ARG;
+  if (rows < 1 || H < 1 || H > 8192) return Q3_ERR_SHAPE;
+  Q3_DISPATCH_FLOAT(dtype, T, return (rmsnorm_bwd_launch<T, true>(residual_out, weight, dy, dresidual, inv_rms, dx,
+                                                                  dweight, (float*)workspace, workspace_bytes, rows, H,
+                                                                  (cudaStream_t)stream)));
+  return Q3_OK;
+}
+
+extern "C" int q3_norm_rope_fwd(const void* x, const void* weight, const void* cos_t, const void* sin_t, void* y,
+                                float* inv_rms, int64_t tokens, int64_t heads, int64_t D, double eps, int dtype,
+                                q3_stream_t stream) {
+  if (!x || !weight || !cos_t || !sin_t || !y || !inv_rms) return Q3_ERR_ARG;
+  if (tokens < 1 || heads < 1 || D < 2 || (D & 1) || !(eps > 0)) return Q3_ERR_SHAPE;
+  Q3_DISPATCH_FLOAT(dtype, T, return (norm_rope_fwd_launch<T, true>(x, weight, cos_t, sin_t, y, inv_rms, 1, tokens,
+                                                                    heads, D, (float)eps, 0, (cudaStream_t)stream)));
+  return Q3_OK;
+}
+
+extern "C" int64_t q3_norm_rope_bwd_workspace_bytes(int64_t tokens, int64_t heads, int64_t D) {
+  (void)tokens; (void)heads;
+  return (int64_t)sm_count() * kPartialRowsPerSm * 2 * D * 4;
+}
+
+extern "C" int q3_norm_rope_bwd(const void* x, const void* weight, const void* cos_t, const void* sin_t,
+                                const void* dy, const float* inv_rms, void* dx, void* dweight, void* workspace,
+                                int64_t workspace_bytes, int64_t tokens, int64_t heads, int64_t D, int dtype,
+                                q3_stream_t stream) {
+  if (!x || !weight || !cos_t || !sin_t || !dy || !inv_rms || !dx || !dweight) return Q3_ERR_ARG;
+  if (tokens < 1 || heads < 1 || D < 2 || (D & 1)) return Q3_ERR_SHAPE;
+  Q3_DISPATCH_FLOAT(dtype, T, return (norm_rope_bwd_launch<T, true>(x, weight, cos_t, sin_t, dy, inv_rms, dx, dweight,
+                                                                    (float*)workspace, workspace_bytes, 1, tokens,
+                                                                    heads, D, 0, (cudaStream_t)stream)));
+  return Q3_OK;
+}
+
+extern "C" int q3_rope_apply(const void* x, const void* cos_t, const void* sin_t, void* y, int64_t batch, int64_t seq,
+                             int64_t heads, int64_t D, int backward, int layout, int dtype, q3_stream_t stream) {
+  if (!x || !cos_t || !sin_t || !y) return Q3_ERR_ARG;
+  if (batch < 1 || seq < 1 || heads < 1 || D < 2 || (D & 1) || (layout != 0 && layout != 1)) return Q3_ERR_SHAPE;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (backward) {
+    Q3_DISPATCH_FLOAT(dtype, T, return (norm_rope_bwd_launch<T, false>(nullptr, nullptr, cos_t, sin_t, x, nullptr, y,
+                                                                       nullptr, nullptr, 0, batch, seq, heads, D,
+                                                                       layout, st)));
+  } else {
+    Q3_DISPATCH_FLOAT(dtype, T, return (norm_rope_fwd_launch<T, false>(x, nullptr, cos_t, sin_t, y, nullptr, batch,
+                                                                       seq, heads, D, 0.f, layout, st)));
+  }
+  return Q3_OK;
+}
+
+extern "C" int q3_rope_tables(const void* positions, int positions_are_int64, const float* inv_freq, void* cos_t,
+                              void* sin_t, int64_t tokens, int64_t D, int dtype, q3_stream_t stream) {
+  if (!positions || !inv_freq || !cos_t || !sin_t) return Q3_ERR_ARG;
+  if (tokens < 1 || D < 2 || (D & 1)) return Q3_ERR_SHAPE;
+  cudaStream_t st = (cudaStream_t)stream;
+  const int64_t total = tokens * (D / 2);
+  int64_t g = cdiv(total, 256), cap = (int64_t)sm_count() * 8;
+  const int grid = (int)(g > cap ? cap : g);
+  Q3_DISPATCH_FLOAT(dtype, T, {
+    if (positions_are_int64)
+      rope_tables_kernel<T, int64_t><<<grid, 256, 0, st>>>((const int64_t*)positions, inv_freq, (T*)cos_t, (T*)sin_t, tokens, (int)D);
+    else
+      rope_tables_kernel<T, int32_t><<<grid, 256, 0, st>>>((const int32_t*)positions, inv_freq, (T*)cos_t, (T*)sin_t, tokens, (int)D);
+  });
+  return launch_status();
+}

@@ -1,0 +1,143 @@
+"""ctypes binding of the q3b200 C-ABI library (csrc/libq3b200.so).
+
+Every operator in this package reaches the GPU through this module: it declares the argument
+types of each `extern "C"` entry point listed in include/q3b200.h, converts torch tensors to raw
+device pointers, and raises when the library is missing or a call is rejected. There is no CPU or
+eager-PyTorch fallback.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_char_p, c_double, c_int, c_int64, c_void_p
+from pathlib import Path
+
+import torch
+
+Q3_F32, Q3_BF16, Q3_F16 = 0, 1, 2
+STATUS_ID_RANGE, STATUS_LABEL_RANGE, STATUS_WAIT_TIMEOUT, STATUS_EMPTY_TARGETS = 1, 2, 4, 8
+
+_DTYPES = {torch.float32: Q3_F32, torch.bfloat16: Q3_BF16, torch.float16: Q3_F16}
+FLOAT_DTYPES = tuple(_DTYPES)
+
+LIB_PATH = Path(__file__).resolve().parent.parent / "csrc" / "libq3b200.so"
+
+P, I, L, D = c_void_p, c_int, c_int64, c_double
+
+# name -> (restype, argtypes); must list every symbol declared in include/q3b200.h
+SIGNATURES = {
+    "q3_abi_version": (I, []),
+    "q3_error_string": (c_char_p, [I]),
+    "q3_device_sm_count": (I, []),
+    "q3_residual_add": (I, [P, P, P, L, I, P]),
+    "q3_cast": (I, [P, I, P, I, L, P]),
+    "q3_swiglu_fwd": (I, [P, P, P, L, I, P]),
+    "q3_swiglu_bwd": (I, [P, P, P, P, P, L, I, P]),
+    "q3_positions": (I, [P, L, L, P]),
+    "q3_rmsnorm_fwd": (I, [P, P, P, P, L, L, D, I, P]),
+    "q3_rmsnorm_bwd_workspace_bytes": (L, [L, L]),
+    "q3_rmsnorm_bwd": (I, [P, P, P, P, P, P, P, L, L, L, I, P]),
+    "q3_add_rmsnorm_fwd": (I, [P, P, P, P, P, P, L, L, D, I, P]),
+    "q3_add_rmsnorm_bwd": (I, [P, P, P, P, P, P, P, P, L, L, L, I, P]),
+    "q3_norm_rope_fwd": (I, [P, P, P, P, P, P, L, L, L, D, I, P]),
+    "q3_norm_rope_bwd_workspace_bytes": (L, [L, L, L]),
+    "q3_norm_rope_bwd": (I, [P, P, P, P, P, P, P, P, P, L, L, L, L, I, P]),
+    "q3_rope_apply": (I, [P, P, P, P, L, L, L, L, I, I, I, P]),
+    "q3_rope_tables": (I, [P, I, P, P, P, L, L, I, P]),
+    "q3_embedding_fwd": (I, [P, I, P, P, L, L, L, I, P, P]),
+    "q3_embedding_bwd": (I, [P, I, P, P, L, L, L, I, P]),
+    "q3_ce_fwd": (I, [P, P, P, P, P, P, P, L, L, L, L, I, P, P]),
+    "q3_ce_local_rows": (I, [P, P, P, P, L, L, L, L, L, L, I, P, P]),
+    "q3_ce_grad": (I, [P, P, P, P, P, P, L, L, L, L, L, L, L, I, P]),
+    "q3_vce_pack": (I, [P, P, P, P, L, P]),
+    "q3_vce_finish": (I, [P, P, P, P, P, P, P, L, L, L, L, L, P, P]),
+    "q3_vce_accumulate": (I, [P, I, P, L, L, I, P]),
+    "q3_adamw_multi": (I, [P, P, L, L, I, D, D, D, D, D, P]),
+    "q3_gemm": (I, [P, L, L, P, L, L, P, L, L, L, I, I, P, P]),
+    "q3_gemm_path": (I, [P, L, L, P, L, L, P, L, L, L, I, I]),
+    "q3_gate_up_swiglu_fwd": (I, [P, P, P, P, P, P, L, L, L, I, P, P]),
+    "q3_gate_up_path": (I, [P, P, P, P, P, P, L, L, L, I]),
+    "q3_attn_fwd": (I, [P, P, P, P, P, L, L, L, L, L, D, I, P, P]),
+    "q3_attn_bwd_workspace_bytes": (L, [L, L, L, L, L]),
+    "q3_attn_bwd": (I, [P, P, P, P, P, P, P, P, P, P, L, L, L, L, L, L, D, I, P, P]),
+    "q3_attn_path": (I, [P, P, P, P, L, I]),
+}
+
+_lib = None
+
+
+class Q3Error(RuntimeError):
+    """A q3b200 entry point rejected the call or a kernel reported a device-side violation."""
+
+
+def lib() -> ctypes.CDLL:
+    """Load libq3b200.so once. Raises if it has not been built: nothing runs without it."""
+    global _lib
+    if _lib is None:
+        if not LIB_PATH.exists():
+            raise Q3Error(f"{LIB_PATH} is missing: build it with `python {LIB_PATH.parent / 'build.py'}`; "
+                          "there is no fallback path")
+        handle = ctypes.CDLL(str(LIB_PATH))
+        for name, (res, args) in SIGNATURES.items():
+            fn = getattr(handle, name)  # AttributeError here means header and library disagree
+            fn.restype, fn.argtypes = res, args
+        _lib = handle
+    return _lib
+
+
+def dt(dtype: torch.dtype) -> int:
+    try:
+        return _DTYPES[dtype]
+    except KeyError:
+        raise TypeError(f"unsupported dtype {dtype}; float32, bfloat16 or float16 required") from None
+
+
+def ptr(t):
+    return None if t is None else t.data_ptr()
+
+
+def stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def check(code: int, what: str) -> None:
+    if code != 0:
+        msg = lib().q3_error_string(code).decode()
+        raise Q3Error(f"{what}: {msg} (code {code})")
+
+
+def call(name: str, *args) -> None:
+    check(getattr(lib(), name)(*args), name)
+
+
+def workspace(nbytes: int, device) -> torch.Tensor:
+    return torch.empty(max(int(nbytes), 16), dtype=torch.uint8, device=device)
+
+
+_status = {}
+
+
+def status_word(device) -> torch.Tensor:
+    """Per-device int32 word that kernels OR violation bits into (never a trap)."""
+    key = torch.device(device).index if torch.device(device).index is not None else torch.cuda.current_device()
+    word = _status.get(key)
+    if word is None:
+        word = torch.zeros(1, dtype=torch.int32, device=torch.device("cuda", key))
+        _status[key] = word
+    return word
+
+
+def read_status(device=None, *, clear=True) -> int:
+    """Synchronising read of the device status word."""
+    word = status_word(device if device is not None else torch.cuda.current_device())
+    value = int(word.item())
+    if clear and value:
+        word.zero_()
+    return value
+
+
+def raise_on_status(device=None) -> None:
+    value = read_status(device)
+    if value:
+        names = [n for bit, n in ((1, "embedding id out of range"), (2, "label out of range"),
+                                  (4, "kernel wait timed out"), (8, "no valid cross-entropy target")) if value & bit]
+        raise Q3Error("device status: " + ", ".join(names))

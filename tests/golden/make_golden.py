@@ -1,0 +1,85 @@
+"""Generate tests/golden/*.npz by RUNNING THE REFERENCE's own CPU code (ops/reference and model/).
+
+Run in a container that has the reference checkout:
+    python tests/golden/make_golden.py /path/to/reference
+The outputs are committed; tests never need the reference at run time.
+"""
+from __future__ import annotations
+
+import sys
+from pathlib import Path
+
+import numpy as np
+import torch
+
+HERE = Path(__file__).resolve().parent
+sys.path.insert(0, str(HERE))
+import recipe  # noqa: E402
+
+
+def main(ref_root):
+    sys.path.insert(0, ref_root)
+    from ops.reference.attention import (scaled_dot_product_attention_backward_reference,
+                                         scaled_dot_product_attention_reference)
+    from ops.reference.fused_qk_norm_rope import fused_qk_norm_rope_backward_reference, fused_qk_norm_rope_reference
+    from ops.reference.rms_norm import rms_norm_reference
+    from ops.reference.rope import apply_rope_backward_reference, apply_rope_reference, rotate_half_reference
+    from ops.reference.swiglu import swiglu_reference
+    from model import TinyQwenConfig, TinyQwenForCausalLM
+
+    torch.set_num_threads(1)
+    d = recipe.op_inputs()
+    out = {}
+    out['rms_norm'] = rms_norm_reference(d['norm_x'], d['norm_w'], 1e-6)
+    x = d['norm_x'].clone().requires_grad_(True)
+    w = d['norm_w'].clone().requires_grad_(True)
+    rms_norm_reference(x, w, 1e-6).backward(d['norm_dy'])
+    out['rms_norm_dx'], out['rms_norm_dw'] = x.grad, w.grad
+    out['rotate_half_arange8'] = rotate_half_reference(torch.arange(8.))
+    q_r, k_r = apply_rope_reference(d['q'], d['k'], d['cos'], d['sin'])
+    out['rope_q'], out['rope_k'] = q_r, k_r
+    gq, gk = apply_rope_backward_reference(d['do'], d['k'], d['cos'], d['sin'])
+    out['rope_bwd_q'], out['rope_bwd_k'] = gq, gk
+    fq, fk = fused_qk_norm_rope_reference(d['qn'], d['kn'], d['qw'], d['kw'], d['cos'], d['sin'], 1e-6)
+    out['fused_q'], out['fused_k'] = fq, fk
+    dq, dk, dqw, dkw = fused_qk_norm_rope_backward_reference(d['qn'], d['kn'], d['qw'], d['kw'], d['cos'], d['sin'],
+                                                             d['dqn'], d['dkn'], 1e-6)
+    out['fused_dq'], out['fused_dk'], out['fused_dqw'], out['fused_dkw'] = dq, dk, dqw, dkw
+    out['swiglu'] = swiglu_reference(d['gate'], d['up'])
+    g = d['gate'].clone().requires_grad_(True)
+    u = d['up'].clone().requires_grad_(True)
+    swiglu_reference(g, u).backward(d['dy_act'])
+    out['swiglu_dg'], out['swiglu_du'] = g.grad, u.grad
+    out['attn'] = scaled_dot_product_attention_reference(d['q'], d['k'], d['v'], is_causal=True, enable_gqa=True)
+    aq, ak, av = scaled_dot_product_attention_backward_reference(d['q'], d['k'], d['v'], d['do'], is_causal=True,
+                                                                 enable_gqa=True)
+    out['attn_dq'], out['attn_dk'], out['attn_dv'] = aq, ak, av
+    np.savez_compressed(HERE / 'ops.npz', **{k: v.detach().numpy() for k, v in out.items()})
+
+    # BASELINE config 1: the tiny decoder, one forward + CE + backward + AdamW step on CPU in fp32.
+    c = recipe.tiny_config()
+    cfg = TinyQwenConfig(vocab_size=c.vocab_size, hidden_size=c.hidden_size, intermediate_size=c.intermediate_size,
+                         num_hidden_layers=c.num_hidden_layers, num_attention_heads=c.num_attention_heads,
+                         num_key_value_heads=c.num_key_value_heads, head_dim=c.head_dim, rope_theta=c.rope_theta,
+                         rms_norm_eps=c.rms_norm_eps, tie_word_embeddings=False)
+    model = TinyQwenForCausalLM(cfg)
+    model.load_state_dict(recipe.seeded_state(c), strict=True)
+    ids = recipe.seeded_ids(c)
+    opt = torch.optim.AdamW(model.parameters(), **recipe.ADAMW)
+    res = model(ids, labels=ids)
+    res['loss'].backward()
+    tiny = {'loss': res['loss'].detach().numpy(), 'logits_slice': res['logits'][0, :4, :16].detach().numpy()}
+    for name, p in model.named_parameters():
+        tiny['gradnorm/' + name] = p.grad.norm().numpy()
+        tiny['gradslice/' + name] = p.grad.reshape(-1)[:32].clone().numpy()
+    opt.step()
+    for name, p in model.named_parameters():
+        tiny['stepslice/' + name] = p.detach().reshape(-1)[:32].clone().numpy()
+    loss2 = model(ids, labels=ids)['loss']
+    tiny['loss_after_step'] = loss2.detach().numpy()
+    np.savez_compressed(HERE / 'tiny_model.npz', **tiny)
+    print('wrote', HERE / 'ops.npz', HERE / 'tiny_model.npz')
+
+
+if __name__ == '__main__':
+    main(sys.argv[1] if len(sys.argv) > 1 else '/root/reference')
