@@ -1,0 +1,298 @@
+#!/usr/bin/env python
+"""Training-step throughput of the Qwen3-8B-shaped hot path on B200, one JSON line on stdout.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+N = 1: BASELINE config 4 - a 4-layer slice of the Qwen3-8B architecture (hidden 4096, 32/8 heads, head_dim 128,
+intermediate 12288, vocab 151936, untied lm_head), bf16 compute with fp32 master weights, microbatch 4 x 2048,
+forward + cross-entropy + backward + AdamW every step, synthetic uniform token ids, weights ~ N(0, 0.02).
+N > 1 (launched with torch.distributed.run): the full 36-layer model under FSDP2, microbatch 1 x 2048 per GPU.
+
+`value` = tokens/s over all GPUs with the token ids already resident in HBM; `e2e.value` = the same step driven
+with pinned-host ids copied in and the loss read back every step. `--impl reference` times the CPU oracle
+restatement of the reference's model on a bounded sample of the same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT / "qwen3-triton_b200"))
+sys.path.insert(0, str(ROOT))
+
+import torch  # noqa: E402
+
+METRIC = "train_tokens_per_s"
+UNIT = "tokens/s"
+
+# kernels launched by one call of each C-ABI entry (for the gpu_launches claim)
+LAUNCHES = {"q3_rmsnorm_bwd": 2, "q3_add_rmsnorm_bwd": 2, "q3_norm_rope_bwd": 2, "q3_adamw_multi": 2, "q3_ce_fwd": 2,
+            "q3_attn_bwd": 3, "q3_vce_finish": 2, "q3_embedding_bwd": 1}
+
+
+def slice_config(layers):
+    from qwen3_triton import Qwen3Config
+    return Qwen3Config(num_hidden_layers=layers)
+
+
+def model_flops_per_token(cfg, seq):
+    """Model FLOPs per token for fwd+bwd (3x forward), no recompute: 2*matmul params + causal attention."""
+    c = cfg
+    layer = (c.hidden_size * c.head_dim * (2 * c.num_attention_heads + 2 * c.num_key_value_heads)
+             + 3 * c.hidden_size * c.intermediate_size)
+    fwd = c.num_hidden_layers * (2 * layer + 2 * seq * c.head_dim * c.num_attention_heads) + 2 * c.hidden_size * c.vocab_size
+    return 3 * fwd
+
+
+class ClockSampler:
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.proc = None
+        self.path = ROOT / "gpurun_out" / f"clocks_bench_{index}.csv"
+        try:
+            self.path.parent.mkdir(exist_ok=True)
+            self.fh = open(self.path, "w")
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(index), f"--query-gpu={self.FIELDS}",
+                                          "--format=csv,noheader,nounits", "-lms", "200"], stdout=self.fh,
+                                         stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        self.fh.close()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.path.read_text().splitlines():
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 8:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[4:8]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def measured_peaks():
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        data = json.loads(path.read_text())
+        return data.get("bf16_tflops_sustained", 1395.4), data.get("hbm_gbs", 6540.8), "measured"
+    return 1400.0, 6650.0, "fallback"
+
+
+# ---------------------------------------------------------------------------------------- CPU reference arm
+def cpu_reference_step_tokens_per_s(layers, sample_tokens, steps, warmup):
+    """The oracle restatement of the reference's CPU model (same architecture, fp32, torch CPU kernels on all
+    host threads): forward + CE + backward + AdamW on a bounded sample of `sample_tokens` tokens per step."""
+    from oracle.model import OracleQwen3
+    torch.set_num_threads(os.cpu_count() or 1)
+    cfg = slice_config(layers)
+    model = OracleQwen3(cfg, seed=1)
+    opt = torch.optim.AdamW(model.parameters(), lr=1e-4, betas=(0.9, 0.95), weight_decay=0.1)
+    gen = torch.Generator().manual_seed(2)
+    ids = torch.randint(0, cfg.vocab_size, (1, sample_tokens), generator=gen)
+    times = []
+    for i in range(warmup + steps):
+        t0 = time.perf_counter()
+        opt.zero_grad(set_to_none=True)
+        loss, _ = model(ids, ids)
+        loss.backward()
+        opt.step()
+        if i >= warmup:
+            times.append(time.perf_counter() - t0)
+    sec = statistics.median(times)
+    return sample_tokens / sec, sec
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    layers = 4
+    sample = 128
+    steps, warmup = max(1, min(args.steps, 3)), 1
+    tps, sec = cpu_reference_step_tokens_per_s(layers, sample, steps, warmup)
+    cores = os.cpu_count() or 1
+    line = {"impl": "reference", "metric": METRIC, "value": tps, "unit": UNIT, "n_gpus": args.gpus, "steps": steps,
+            "warmup": warmup, "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "f32", "data": "synthetic",
+            "config": {"workload": "qwen3-8b 4-layer slice fwd+bwd+AdamW (CPU sample 1x%d tokens)" % sample},
+            "cpu_baseline": {"value": tps, "unit": UNIT, "cores": cores, "kind": "port",
+                             "sample": f"oracle model, 4 layers, 1 x {sample} tokens per step, median of {steps}"},
+            "e2e": {"value": tps, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line), flush=True)
+
+
+# ---------------------------------------------------------------------------------------- GPU arm
+class Counter:
+    """Counts C-ABI calls / kernel launches and, when `profile` is on, times every call with CUDA events."""
+
+    def __init__(self):
+        from qwen3_triton import _abi
+        self.abi = _abi
+        self.orig = _abi.call
+        self.launches = 0
+        self.profile = False
+        self.records = []
+        _abi.call = self
+        # modules bound `call` through the module object, so patching the attribute is enough
+
+    def __call__(self, name, *a):
+        self.launches += LAUNCHES.get(name, 1)
+        if self.profile:
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s.record()
+            self.orig(name, *a)
+            e.record()
+            self.records.append((name, a, s, e))
+        else:
+            self.orig(name, *a)
+
+
+def build_single_gpu(cfg, device):
+    from qwen3_triton import model_for_variant
+    from qwen3_triton.runtime.adamw import TritonAdamW
+    from qwen3_triton.runtime.mixed_precision import MasterWeights
+    torch.manual_seed(20261114)
+    with torch.device(device):
+        model = model_for_variant(cfg, "triton_optimized")
+    model.to(device)   # buffers created on the CPU on purpose (rotary frequencies) move here
+    masters = MasterWeights(model)
+    opt = TritonAdamW(masters.parameters(), lr=1e-4, betas=(0.9, 0.95), weight_decay=0.1)
+    return model, masters, opt
+
+
+def run_ours(args):
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if world > 1:
+        from qwen3_triton.runtime.bench_fsdp import run_fsdp_bench   # multi-GPU path lives with the runtime
+        return run_fsdp_bench(args, METRIC, UNIT, model_flops_per_token, ClockSampler, measured_peaks)
+    device = torch.device("cuda", 0)
+    torch.cuda.set_device(device)
+    counter = Counter()
+    layers, batch, seq = 4, 4, 2048
+    cfg = slice_config(layers)
+    model, masters, opt = build_single_gpu(cfg, device)
+    gen = torch.Generator().manual_seed(3)
+    nbatches = args.warmup + args.steps
+    host_ids = [torch.randint(0, cfg.vocab_size, (batch, seq), generator=gen).pin_memory() for _ in range(min(nbatches, 8))]
+    dev_ids = [h.to(device) for h in host_ids]
+
+    def step(ids):
+        masters.sync_working()
+        out = model(ids, labels=ids)
+        out.loss.backward()
+        masters.collect_grads()
+        opt.step()
+        return out.loss
+
+    for i in range(args.warmup):
+        step(dev_ids[i % len(dev_ids)])
+    torch.cuda.synchronize()
+    sampler = ClockSampler(0)
+    counter.launches = 0
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    start.record()
+    for i in range(args.steps):
+        loss = step(dev_ids[i % len(dev_ids)])
+    end.record()
+    torch.cuda.synchronize()
+    launches = counter.launches
+    ms = start.elapsed_time(end) / args.steps
+    tokens = batch * seq
+    value = tokens / (ms * 1e-3)
+
+    # end to end: pinned host ids copied in, loss read back, every step
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for i in range(args.steps):
+        ids = host_ids[i % len(host_ids)].to(device, non_blocking=True)
+        last = float(step(ids).item())
+    torch.cuda.synchronize()
+    e2e_ms = (time.perf_counter() - t0) * 1e3 / args.steps
+    clocks = sampler.stop()
+
+    # per-kernel census of one more step with CUDA events around every C-ABI call
+    counter.profile = True
+    step(dev_ids[0])
+    torch.cuda.synchronize()
+    counter.profile = False
+    by_name = {}
+    gemm_flops = 0.0
+    for name, a, s, e in counter.records:
+        t = s.elapsed_time(e)
+        by_name[name] = by_name.get(name, 0.0) + t
+        if name == "q3_gemm":
+            gemm_flops += 2.0 * a[7] * a[8] * a[9]
+        elif name == "q3_gate_up_swiglu_fwd":
+            gemm_flops += 4.0 * a[6] * a[7] * a[8]
+    gemm_ms = by_name.get("q3_gemm", 0.0) + by_name.get("q3_gate_up_swiglu_fwd", 0.0)
+    peak_tf, _, peak_kind = measured_peaks()
+    achieved = gemm_flops / (gemm_ms * 1e-3) / 1e12 if gemm_ms > 0 else 0.0
+    total_ms = sum(by_name.values())
+    census = {k: round(v, 3) for k, v in sorted(by_name.items(), key=lambda kv: -kv[1])}
+
+    flops_tok = model_flops_per_token(cfg, seq)
+    mfu = value * flops_tok / (peak_tf * 1e12)
+    cpu_tps, cpu_sec = cpu_reference_step_tokens_per_s(layers, 128, 1, 1)
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic",
+        "config": {"workload": "qwen3-8b 4-layer slice fwd+bwd+AdamW, microbatch 4x2048 (BASELINE config 4)",
+                   "global_batch": batch, "seq_len": seq, "parallelism": "single", "l2": "inputs+weights >> L2 (4 GB bf16 weights)",
+                   "attention_path": "see kernel census", "mfu_of_%s_peak" % peak_kind: mfu, "last_loss": last},
+        "e2e": {"value": tokens / (e2e_ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": batch * seq * 8,
+                "d2h_bytes_per_step": 4},
+        "gpu_launches": launches,
+        "clocks": clocks,
+        "roofline": {"bound": "tensor", "kernel": "gemm_tc_kernel (all q3_gemm + q3_gate_up_swiglu_fwd launches of a step)",
+                     "achieved": achieved, "peak": peak_tf, "unit": "TFLOP/s", "frac": achieved / peak_tf,
+                     "peak_kind": peak_kind + " bf16_tflops_sustained", "traffic": None,
+                     "gemm_ms_per_step": gemm_ms, "all_kernels_ms_per_step": total_ms, "census_ms": census},
+        "cpu_baseline": {"value": cpu_tps, "unit": UNIT, "cores": os.cpu_count() or 1, "kind": "port",
+                         "sample": "oracle model, 4 layers, 1 x 128 tokens, one timed step after one warm-up"},
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=8)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return run_reference(args)
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the product has no CPU path")
+    run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

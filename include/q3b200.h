@@ -41,6 +41,7 @@ enum {
   Q3_ERR_WORKSPACE = -4, /* workspace missing or too small */
   Q3_ERR_ALIGN = -5,     /* pointer or stride alignment not supported by any path */
   Q3_ERR_DRIVER = -6,    /* a required driver entry point is unavailable */
+  Q3_ERR_TMAP = -7,      /* the driver rejected a TMA tensor-map description */
   Q3_ERR_CUDA = -1000    /* Q3_ERR_CUDA - cudaError_t */
 };
 

@@ -184,7 +184,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       for (uint32_t j = it - pending; j < it; ++j) {
         const int s = j % C::STAGES;
         const uint32_t ph = (j / C::STAGES) & 1u;
-        for (uint32_t spin = 0; spin < kSpinLimit && !mbar_try_wait(full_bar(s), ph); ++spin) __nanosleep(64);
+        mbar_wait_drain(full_bar(s), ph);
       }
     }
   } else if (warp == 1) {
@@ -219,7 +219,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       }
       // Everything issued must have completed before tensor memory is released.
       mma_commit(done_bar);
-      for (uint32_t spin = 0; spin < kSpinLimit && !mbar_try_wait(done_bar, 0); ++spin) __nanosleep(64);
+      mbar_wait_drain(done_bar, 0);
     }
   } else {
     // ------------------------------------------------------------- epilogue (warps 2..5)

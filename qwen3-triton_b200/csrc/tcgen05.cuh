@@ -7,12 +7,13 @@
 // Q3_STATUS_WAIT_TIMEOUT into the caller's status word, frees its tensor memory and returns.
 #pragma once
 #include <cuda.h>
+#include <stdio.h>
+#include <stdlib.h>
 #include "common.cuh"
 
 namespace q3 {
 namespace tc {
 
-constexpr uint32_t kSpinLimit = 1u << 22;  // ~seconds with the back-off below
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -39,13 +40,40 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
   return ok;
 }
 
-// Bounded wait. Returns false if it gave up (own limit reached, or another thread of the CTA did).
+__device__ __forceinline__ uint64_t global_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+
+constexpr uint64_t kWaitLimitNs = 2000000000ull;  // 2 s: far beyond any legitimate wait in these kernels
+
+// Bounded wait. Returns false if it gave up (own time limit reached, or another thread of the CTA did).
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  uint64_t t0 = 0;
   for (uint32_t it = 0;; ++it) {
     if (mbar_try_wait(bar, parity)) return true;
-    if (it > 2048u) __nanosleep(128);
-    if ((it & 127u) == 127u && *abort_flag) return false;
-    if (it > kSpinLimit) { *abort_flag = 1; return false; }
+    if (it > 1024u) __nanosleep(128);
+    if ((it & 63u) == 63u) {
+      if (*abort_flag) return false;
+      const uint64_t now = global_ns();
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > kWaitLimitNs) { *abort_flag = 1; return false; }
+    }
+  }
+}
+
+// Bounded wait that ignores the abort flag (used while draining in-flight work before exit).
+__device__ __forceinline__ bool mbar_wait_drain(uint32_t bar, uint32_t parity) {
+  uint64_t t0 = 0;
+  for (uint32_t it = 0;; ++it) {
+    if (mbar_try_wait(bar, parity)) return true;
+    __nanosleep(64);
+    if ((it & 63u) == 63u) {
+      const uint64_t now = global_ns();
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > kWaitLimitNs) return false;
+    }
   }
 }
 
@@ -193,7 +221,10 @@ inline int make_tmap_2d(CUtensorMap* map, const void* base, bool bf16, int64_t r
   CUresult r = fn(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2,
                   const_cast<void*>(base), gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS ? Q3_OK : Q3_ERR_DRIVER;
+  if (r != CUDA_SUCCESS && getenv("Q3_DEBUG"))
+    fprintf(stderr, "q3: tensor map encode failed (%d): base=%p rows=%lld cols=%lld ld=%lld box=%dx%d\n", (int)r, base,
+            (long long)rows, (long long)cols, (long long)ld, box_cols, box_rows);
+  return r == CUDA_SUCCESS ? Q3_OK : Q3_ERR_TMAP;
 }
 
 // 3-D map over [d2, rows, cols] with strides ld1 (rows) and ld2 (outer), in elements.
@@ -208,7 +239,7 @@ inline int make_tmap_3d(CUtensorMap* map, const void* base, bool bf16, int64_t d
   CUresult r = fn(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3,
                   const_cast<void*>(base), gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS ? Q3_OK : Q3_ERR_DRIVER;
+  return r == CUDA_SUCCESS ? Q3_OK : Q3_ERR_TMAP;
 }
 
 }  // namespace tc

@@ -6,7 +6,9 @@ import torch
 TOL = {torch.bfloat16: 2e-2, torch.float16: 4e-3, torch.float32: 2e-4}
 
 
-def close(actual, expected, dtype=None, scale=None, what=""):
+def close(actual, expected, dtype=None, scale=None, what="", atol_mult=2.0):
+    """|actual - expected| <= tol * |expected| + tol * atol_mult * scale, scale = mean |expected| by default
+    (with a floor of 1e-5 so an exactly-zero expectation admits rounding noise)."""
     dtype = dtype or actual.dtype
     tol = TOL[dtype]
     expected = expected.detach().float().cpu()
@@ -14,7 +16,8 @@ def close(actual, expected, dtype=None, scale=None, what=""):
     assert actual.shape == expected.shape, (what, actual.shape, expected.shape)
     assert torch.isfinite(actual).all(), what
     s = float(expected.abs().mean()) if scale is None else scale
-    torch.testing.assert_close(actual, expected, rtol=tol, atol=tol * max(s, 1e-6) * 2, msg=lambda m: f"{what}: {m}")
+    torch.testing.assert_close(actual, expected, rtol=tol, atol=max(tol * s * atol_mult, 1e-5),
+                               msg=lambda m: f"{what}: {m}")
 
 
 def rel_l2(actual, expected):

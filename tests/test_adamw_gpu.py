@@ -1,0 +1,90 @@
+"""Multi-tensor AdamW against the fp64 oracle and torch.optim.AdamW: non-zero initial moments, skipped and
+zero gradients, odd tensor sizes, state_dict round trip, fp32-only enforcement."""
+import pytest
+import torch
+
+import recipe
+from oracle import ops as O
+
+pytestmark = pytest.mark.gpu
+HYPER = dict(lr=1e-3, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1)
+SIZES = [(1,), (7,), (1031,), (4099,), (128, 130), (4096,), (3, 4097)]
+
+
+def make_params(seed):
+    g = torch.Generator().manual_seed(seed)
+    return [torch.randn(*s, generator=g) for s in SIZES]
+
+
+def test_matches_fp64_oracle_over_steps():
+    from qwen3_triton.runtime.adamw import TritonAdamW
+    cpu = make_params(1)
+    params = [torch.nn.Parameter(p.clone().cuda()) for p in cpu]
+    opt = TritonAdamW(params, **HYPER)
+    ref = [(p.clone(), torch.zeros_like(p), torch.zeros_like(p)) for p in cpu]
+    g = torch.Generator().manual_seed(2)
+    steps = [0] * len(cpu)
+    for it in range(1, 9):
+        for i, p in enumerate(params):
+            if i == 1 and it % 2 == 0:
+                p.grad = None                       # skipped gradient: state must not advance
+                continue
+            grad = torch.zeros_like(cpu[i]) if (i == 2 and it == 3) else torch.randn(cpu[i].shape, generator=g) * 1e-2
+            p.grad = grad.cuda()
+            steps[i] += 1
+            pp, m, v = ref[i]
+            ref[i] = O.adamw_step(pp, grad, m, v, steps[i], HYPER['lr'], *HYPER['betas'], HYPER['eps'], HYPER['weight_decay'])
+        opt.step()
+    for i, p in enumerate(params):
+        st = opt.state[p]
+        assert float(st['step']) == steps[i] and st['step'].dtype == torch.float32 and st['step'].ndim == 0
+        # AdamW state within 1e-5 (stated tolerance); observed differences are a few fp32 ulps
+        torch.testing.assert_close(p.detach().cpu(), ref[i][0], rtol=1e-5, atol=1e-7)
+        torch.testing.assert_close(st['exp_avg'].cpu(), ref[i][1], rtol=1e-5, atol=1e-9)
+        torch.testing.assert_close(st['exp_avg_sq'].cpu(), ref[i][2], rtol=1e-5, atol=1e-12)
+
+
+def test_matches_torch_adamw_and_state_dict_roundtrip():
+    from qwen3_triton.runtime.adamw import TritonAdamW
+    cpu = make_params(3)
+    a = [torch.nn.Parameter(p.clone().cuda()) for p in cpu]
+    b = [torch.nn.Parameter(p.clone()) for p in cpu]
+    oa, ob = TritonAdamW(a, **HYPER), torch.optim.AdamW(b, **HYPER)
+    g = torch.Generator().manual_seed(4)
+    for it in range(6):
+        for pa, pb in zip(a, b):
+            grad = torch.randn(pb.shape, generator=g) * 1e-2
+            pa.grad, pb.grad = grad.cuda(), grad.clone()
+        oa.step()
+        ob.step()
+        if it == 2:                                   # save -> CPU -> restore into a fresh optimizer
+            saved = {'state': {k: {n: t.detach().cpu().clone() for n, t in s.items()} for k, s in oa.state_dict()['state'].items()},
+                     'param_groups': oa.state_dict()['param_groups']}
+            oa = TritonAdamW(a, **HYPER)
+            oa.load_state_dict(saved)
+    for pa, pb in zip(a, b):
+        torch.testing.assert_close(pa.detach().cpu(), pb.detach(), rtol=1e-5, atol=1e-7)
+    assert oa.kernel_steps == 3
+
+
+def test_rejects_bf16_and_gradscaler():
+    from qwen3_triton.runtime.adamw import TritonAdamW
+    p = torch.nn.Parameter(torch.zeros(8, device='cuda', dtype=torch.bfloat16))
+    p.grad = torch.zeros_like(p)
+    with pytest.raises(ValueError):
+        TritonAdamW([p]).step()
+    q = torch.nn.Parameter(torch.zeros(8, device='cuda'))
+    q.grad = torch.zeros_like(q)
+    opt = TritonAdamW([q])
+    opt.grad_scale = torch.ones(1)
+    with pytest.raises(ValueError):
+        opt.step()
+
+
+def test_version_counter_bumped():
+    from qwen3_triton.runtime.adamw import TritonAdamW
+    p = torch.nn.Parameter(torch.ones(64, device='cuda'))
+    p.grad = torch.ones_like(p)
+    before = p._version
+    TritonAdamW([p]).step()
+    assert p._version > before

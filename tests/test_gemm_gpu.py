@@ -1,0 +1,111 @@
+"""GEMM parity: the tcgen05 tensor-core kernel in all three operand layouts (forward X*W^T, input gradient
+dY*W, weight gradient dY^T*X), tails in M, N and K, fp32 output, the fused gate/up+SwiGLU kernel, and the
+CUDA-core fallback; all against fp32 torch.mm on the same bf16-quantised inputs."""
+import pytest
+import torch
+
+from helpers import close, randn
+from oracle import ops as O
+
+pytestmark = pytest.mark.gpu
+
+
+def ref_mm(a, b):
+    return a.float().cpu() @ b.float().cpu()
+
+
+SHAPES = [(128, 256, 64), (256, 512, 128), (200, 264, 72), (1, 8, 8), (129, 1000, 520), (512, 4096, 4096), (300, 136, 1024)]
+
+
+@pytest.mark.parametrize('M,N,K', SHAPES)
+@pytest.mark.parametrize('dtype', [torch.bfloat16, torch.float16])
+def test_forward_layout_tensor_cores(M, N, K, dtype):
+    from qwen3_triton.kernels.linear import gemm_path, matmul
+    x, w = randn((M, K), 1, dtype).cuda(), randn((N, K), 2, dtype).cuda()
+    assert gemm_path(x, w.t()) == 'tcgen05'
+    y = matmul(x, w.t())
+    close(y, ref_mm(x, w.t()).to(dtype), scale=K ** 0.5, what='X*W^T')
+
+
+@pytest.mark.parametrize('M,N,K', SHAPES)
+def test_input_gradient_layout_tensor_cores(M, N, K):
+    from qwen3_triton.kernels.linear import gemm_path, matmul
+    dy, w = randn((M, K), 3, torch.bfloat16).cuda(), randn((K, N), 4, torch.bfloat16).cuda()   # B row-major [K,N]
+    assert gemm_path(dy, w) == 'tcgen05'
+    close(matmul(dy, w), ref_mm(dy, w).to(torch.bfloat16), scale=K ** 0.5, what='dY*W')
+
+
+@pytest.mark.parametrize('M,N,K', SHAPES)
+def test_weight_gradient_layout_tensor_cores(M, N, K):
+    from qwen3_triton.kernels.linear import gemm_path, matmul
+    # C[M,N] = A^T-view [M,K] * B [K,N] with both stored token-major, as dY^T * X
+    dy, x = randn((K, M), 5, torch.bfloat16).cuda(), randn((K, N), 6, torch.bfloat16).cuda()
+    if M % 8 == 0:
+        assert gemm_path(dy.t(), x) == 'tcgen05'
+    close(matmul(dy.t(), x), ref_mm(dy.t(), x).to(torch.bfloat16), scale=K ** 0.5, what='dY^T*X')
+
+
+def test_fp32_output_and_determinism():
+    from qwen3_triton.kernels.linear import matmul
+    a, b = randn((384, 1536), 7, torch.bfloat16).cuda(), randn((1536, 520), 8, torch.bfloat16).cuda()
+    c = matmul(a, b, output_dtype=torch.float32)
+    assert c.dtype == torch.float32
+    torch.testing.assert_close(c.cpu(), ref_mm(a, b), rtol=1e-4, atol=1e-2)
+    assert torch.equal(c, matmul(a, b, output_dtype=torch.float32))
+
+
+@pytest.mark.parametrize('dtype', [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize('M,N,K', [(1, 1, 1), (17, 129, 33), (65, 7, 257)])
+def test_fallback_path_odd_shapes_and_fp32(dtype, M, N, K):
+    from qwen3_triton.kernels.linear import gemm_path, matmul
+    a, b = randn((M, K), 9, dtype).cuda(), randn((K, N), 10, dtype).cuda()
+    assert gemm_path(a, b) == 'simt'
+    close(matmul(a, b), ref_mm(a, b).to(dtype), scale=K ** 0.5)
+    close(matmul(a.t().contiguous().t(), b.t().contiguous().t()), ref_mm(a, b).to(dtype), scale=K ** 0.5)
+
+
+def test_tensor_core_and_fallback_agree():
+    from qwen3_triton import _abi
+    from qwen3_triton.kernels.linear import matmul
+    a, b = randn((256, 512), 11, torch.bfloat16).cuda(), randn((512, 384), 12, torch.bfloat16).cuda()
+    tc = matmul(a, b, output_dtype=torch.float32)
+    a32, b32 = a.float(), b.float()
+    simt = matmul(a32, b32)                 # fp32 operands take the CUDA-core kernel
+    torch.testing.assert_close(tc, simt, rtol=1e-4, atol=1e-3)
+
+
+@pytest.mark.parametrize('shape', [(2, 17, 256), (4, 128, 1024)])
+def test_linear_autograd(shape):
+    from qwen3_triton.kernels.linear import linear
+    K, N = shape[-1], 520
+    x, w, dy = randn(shape, 13, torch.bfloat16), randn((N, K), 14, torch.bfloat16, 0.05), randn((*shape[:-1], N), 15, torch.bfloat16)
+    xg, wg = x.cuda().requires_grad_(True), w.cuda().requires_grad_(True)
+    y = linear(xg, wg)
+    y.backward(dy.cuda())
+    close(y, O.linear(x, w).to(torch.bfloat16), what='y')
+    close(xg.grad, (dy.float().reshape(-1, N) @ w.float()).reshape(shape).to(torch.bfloat16), what='dx')
+    close(wg.grad, (dy.float().reshape(-1, N).t() @ x.float().reshape(-1, K)).to(torch.bfloat16), what='dw')
+    with pytest.raises(ValueError):
+        linear(xg.transpose(0, 1), wg)
+
+
+@pytest.mark.parametrize('M,N,K', [(128, 128, 64), (200, 344, 256), (512, 1536, 1024), (64, 688, 256)])
+def test_fused_gate_up_swiglu(M, N, K):
+    from qwen3_triton import _abi
+    from qwen3_triton.kernels.mlp import gate_up_swiglu
+    from ops.triton.gate_up_swiglu import gate_up_swiglu_triton
+    dt = torch.bfloat16
+    x, wg, wu, dy = randn((M, K), 16, dt), randn((N, K), 17, dt, 0.05), randn((N, K), 18, dt, 0.05), randn((M, N), 19, dt)
+    xg, g_, u_ = x.cuda().requires_grad_(True), wg.cuda().requires_grad_(True), wu.cuda().requires_grad_(True)
+    assert _abi.lib().q3_gate_up_path(xg.data_ptr(), g_.data_ptr(), u_.data_ptr(), xg.data_ptr(), xg.data_ptr(),
+                                      xg.data_ptr(), M, N, K, _abi.Q3_BF16) == 1
+    y = gate_up_swiglu(xg, g_, u_)
+    y.backward(dy.cuda())
+    gate, up = O.linear(x, wg), O.linear(x, wu)
+    close(y, O.swiglu(gate.to(dt), up.to(dt)).to(dt), what='y')
+    xr, gr, ur = x.float().requires_grad_(True), wg.float().requires_grad_(True), wu.float().requires_grad_(True)
+    (torch.nn.functional.silu(xr @ gr.t()) * (xr @ ur.t())).backward(dy.float())
+    close(xg.grad, xr.grad.to(dt), what='dx')
+    close(g_.grad, gr.grad.to(dt), what='dWg')
+    close(u_.grad, ur.grad.to(dt), what='dWu')
+    close(gate_up_swiglu_triton(x.cuda(), wg.cuda(), wu.cuda()), y, what='ops.triton')
