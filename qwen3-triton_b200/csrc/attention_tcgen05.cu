@@ -1,10 +1,359 @@
-// Tensor-core (tcgen05) causal GQA attention for head_dim 128 - placeholder until the kernels land.
+// Causal grouped-query flash attention on the tcgen05 tensor cores, head_dim 128, bf16 / fp16.
+//
+// Layout: q/out/dout/dq [B, Hq, S, 128], k/v/dk/dv [B, Hkv, S, 128], lse/delta [B, Hq, S] fp32.
+// Every operand tile is brought in by TMA (3-D maps [B*H, S, 128], so rows past the sequence end read
+// as zero) into 128-byte-swizzled shared memory as two 64-column halves; the same K (or V, Q, dO) tile
+// serves as a K-major operand (contraction over head_dim) and as an MN-major operand (contraction over
+// its rows) through two descriptor views, so no tile is ever transposed or loaded twice.
+//
+// Forward (one CTA per 128-query tile of one (batch, query head); 192 threads):
+//   warp 0  : TMA producer - Q once, then a 2-stage ring of K tiles and of V tiles (128 keys each)
+//   warp 1  : MMA issuer   - S_j = Q K_j^T into one of two TMEM score buffers, then O_j = P_j V_j into one
+//             of two TMEM output buffers; S_{j+1} is issued before P_j is ready, so the score GEMM
+//             overlaps the softmax
+//   warps 2-5: softmax     - one query row per thread: tcgen05.ld the scores, online max / exp2 / sum in
+//             fp32, write P_j (bf16) into swizzled shared memory for the second GEMM, fold O_{j-1} from
+//             TMEM into the fp32 register accumulator while the tensor core works on tile j
+// Backward is two deterministic kernels:
+//   dQ    (one CTA per 128-query tile): S = Q K^T, dP = dO V^T, dS = P*(dP - delta) -> smem, dQ += dS K
+//         accumulated in TMEM over the key tiles.
+//   dK/dV (one CTA per 128-key tile of one (batch, kv head)): loops over the query heads of the group
+//         and over 64-query sub-tiles at or below the diagonal; S^T = K Q^T, dP^T = V dO^T, then
+//         dV += P^T dO and dK += dS^T Q accumulate in TMEM across the whole group - the per-query-head
+//         partial buffers and the reduction kernel of the reference do not exist here.
+//
+// Replaces, in the reference: qwen3_triton/kernels/attention_precision.py:15-143 (the kernels the 8B
+// graph uses) and kernels/attention_kernels.py:10-253. Math: ops/reference/attention.py:10-124.
 #include "tcgen05.cuh"
+#include <math_constants.h>
 
 namespace q3 {
-bool attn_tc_available() { return false; }
-int attn_fwd_tc(const void*, const void*, const void*, void*, float*, int64_t, int64_t, int64_t, int64_t, float, int,
-                int*, cudaStream_t) { return Q3_ERR_SHAPE; }
-int attn_bwd_tc(const void*, const void*, const void*, const void*, const float*, const float*, void*, void*, void*,
-                int64_t, int64_t, int64_t, int64_t, float, int, int*, cudaStream_t) { return Q3_ERR_SHAPE; }
+namespace tc {
+
+constexpr int AD = 128;           // head dim
+constexpr int TILE = 128;         // query rows / keys per tile
+constexpr int HALF_BYTES = TILE * 128;       // one 64-column half of a 128-row tile (16 KB)
+constexpr int TILE_BYTES = 2 * HALF_BYTES;   // 32 KB
+constexpr int kAttnThreads = 192;
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kLn2 = 0.6931471805599453f;
+
+struct AttnParams {
+  void* out;
+  float* lse;
+  int Hq, Hkv, S;
+  float scale_log2;  // softmax scale * log2(e)
+  uint32_t idesc_qk; // A K-major, B K-major, N = 128
+  uint32_t idesc_pv; // A K-major, B MN-major, N = 128
+  int* status;
+};
+
+template <typename T> __device__ __forceinline__ uint32_t pack2(float a, float b);
+template <> __device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float a, float b) {
+  __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+template <> __device__ __forceinline__ uint32_t pack2<__half>(float a, float b) {
+  __half2 h = __floats2half2_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+
+// Write 32 consecutive elements (columns c0..c0+31 of row `row`) of a [128 x 128] K-major tile held as
+// two 64-column halves with the 128-byte swizzle (16-byte chunk index XOR row%8).
+template <typename T>
+__device__ __forceinline__ void store_swizzled32(uint8_t* tile, int row, int c0, const float (&v)[32]) {
+  uint8_t* half = tile + (c0 >> 6) * HALF_BYTES + row * 128;
+  const int chunk0 = (c0 & 63) >> 3;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    uint4 w;
+    w.x = pack2<T>(v[8 * j + 0], v[8 * j + 1]);
+    w.y = pack2<T>(v[8 * j + 2], v[8 * j + 3]);
+    w.z = pack2<T>(v[8 * j + 4], v[8 * j + 5]);
+    w.w = pack2<T>(v[8 * j + 6], v[8 * j + 7]);
+    *reinterpret_cast<uint4*>(half + (((chunk0 + j) ^ (row & 7)) << 4)) = w;
+  }
+}
+
+// 8 MMAs (k = 16 each) covering a contraction of 128 over two 64-wide halves, both operands K-major.
+__device__ __forceinline__ void mma_kk_128(uint32_t d_tmem, uint32_t a_smem, uint32_t b_smem, uint32_t idesc,
+                                           bool accumulate_first) {
+#pragma unroll
+  for (int k = 0; k < 8; ++k) {
+    const uint32_t off = (k >> 2) * HALF_BYTES + (k & 3) * 32;
+    mma_f16_ss(d_tmem, make_smem_desc(a_smem + off, 0, 1024), make_smem_desc(b_smem + off, 0, 1024), idesc,
+               (accumulate_first || k) ? 1u : 0u);
+  }
+}
+// A K-major [128 x kk] (kk = 16 * ksteps, halves of 64), B MN-major: rows = contraction index, 128 columns
+// as two 64-wide atoms HALF_BYTES apart.
+__device__ __forceinline__ void mma_kmn(uint32_t d_tmem, uint32_t a_smem, uint32_t b_smem, uint32_t idesc,
+                                        int ksteps, uint32_t a_half_bytes, bool accumulate_first) {
+  for (int k = 0; k < ksteps; ++k) {
+    const uint32_t a_off = (k >> 2) * a_half_bytes + (k & 3) * 32;
+    const uint32_t b_off = k * (16 * 128);
+    mma_f16_ss(d_tmem, make_smem_desc(a_smem + a_off, 0, 1024), make_smem_desc(b_smem + b_off, HALF_BYTES, 1024),
+               idesc, (accumulate_first || k) ? 1u : 0u);
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kAttnThreads, 1)
+attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                   const __grid_constant__ CUtensorMap tmV, const AttnParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem = smem_raw + (base - smem_u32(smem_raw));
+  // [Q 32K][K0 32K][K1 32K][V0 32K][V1 32K][P 32K][barriers]
+  const uint32_t q_s = base, k_s = base + TILE_BYTES, v_s = base + 3 * TILE_BYTES, p_s = base + 5 * TILE_BYTES;
+  uint8_t* p_ptr = smem + 5 * TILE_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 6 * TILE_BYTES);
+  const uint32_t bar0 = smem_u32(bars);
+  const uint32_t q_full = bar0;
+  auto k_full = [&](int s) { return bar0 + 8u * (1 + s); };
+  auto k_empty = [&](int s) { return bar0 + 8u * (3 + s); };
+  auto v_full = [&](int s) { return bar0 + 8u * (5 + s); };
+  auto v_empty = [&](int s) { return bar0 + 8u * (7 + s); };
+  auto s_full = [&](int s) { return bar0 + 8u * (9 + s); };
+  auto o_full = [&](int s) { return bar0 + 8u * (11 + s); };
+  const uint32_t p_full = bar0 + 8u * 13, done_bar = bar0 + 8u * 14;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 15);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nq = (p.S + TILE - 1) / TILE;
+  const int qt = nq - 1 - (int)blockIdx.x;  // heaviest tiles first
+  const int bh = blockIdx.y, b = bh / p.Hq, h = bh % p.Hq, kvh = h / (p.Hq / p.Hkv);
+  const int bkv = b * p.Hkv + kvh;
+  const int ntiles = qt + 1;
+
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    for (int i = 0; i < 13; ++i) mbar_init(bar0 + 8u * i, 1);
+    mbar_init(p_full, 128);
+    mbar_init(done_bar, 1);
+    fence_barrier_init();
+    prefetch_tmap(&tmQ); prefetch_tmap(&tmK); prefetch_tmap(&tmV);
+  }
+  if (warp == 1) { tmem_alloc(smem_u32(tmem_slot), 512); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;  // columns: S0 0..127, S1 128..255, O0 256..383, O1 384..511
+
+  if (warp == 0) {
+    if (lane == 0) {
+      mbar_expect_tx(q_full, TILE_BYTES);
+      tma_load_3d(q_s, &tmQ, 0, qt * TILE, bh, q_full);
+      tma_load_3d(q_s + HALF_BYTES, &tmQ, 64, qt * TILE, bh, q_full);
+      int issued = 0;
+      for (int j = 0; j < ntiles; ++j) {
+        const int s = j & 1;
+        const uint32_t ph = (j >> 1) & 1u;
+        if (!mbar_wait(k_empty(s), ph ^ 1u, abort_flag)) break;
+        mbar_expect_tx(k_full(s), TILE_BYTES);
+        tma_load_3d(k_s + s * TILE_BYTES, &tmK, 0, j * TILE, bkv, k_full(s));
+        tma_load_3d(k_s + s * TILE_BYTES + HALF_BYTES, &tmK, 64, j * TILE, bkv, k_full(s));
+        if (!mbar_wait(v_empty(s), ph ^ 1u, abort_flag)) { mbar_wait_drain(k_full(s), ph); break; }
+        mbar_expect_tx(v_full(s), TILE_BYTES);
+        tma_load_3d(v_s + s * TILE_BYTES, &tmV, 0, j * TILE, bkv, v_full(s));
+        tma_load_3d(v_s + s * TILE_BYTES + HALF_BYTES, &tmV, 64, j * TILE, bkv, v_full(s));
+        issued = j + 1;
+      }
+      // make sure nothing is still landing in shared memory when the CTA exits
+      mbar_wait_drain(q_full, 0);
+      for (int j = issued > 2 ? issued - 2 : 0; j < issued; ++j) {
+        mbar_wait_drain(k_full(j & 1), (j >> 1) & 1u);
+        mbar_wait_drain(v_full(j & 1), (j >> 1) & 1u);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      bool ok = mbar_wait(q_full, 0, abort_flag) && mbar_wait(k_full(0), 0, abort_flag);
+      if (ok) {
+        tc_fence_after();
+        mma_kk_128(tmem + 0, q_s, k_s, p.idesc_qk, false);
+        mma_commit(s_full(0));
+        mma_commit(k_empty(0));
+      }
+      for (int j = 0; j < ntiles && ok; ++j) {
+        const int s = j & 1;
+        const uint32_t ph = (j >> 1) & 1u;
+        if (j + 1 < ntiles) {
+          const int s1 = (j + 1) & 1;
+          if (!mbar_wait(k_full(s1), ((j + 1) >> 1) & 1u, abort_flag)) { ok = false; break; }
+          tc_fence_after();
+          mma_kk_128(tmem + s1 * 128, q_s, k_s + s1 * TILE_BYTES, p.idesc_qk, false);
+          mma_commit(s_full(s1));
+          mma_commit(k_empty(s1));
+        }
+        if (!mbar_wait(p_full, j & 1u, abort_flag) || !mbar_wait(v_full(s), ph, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        mma_kmn(tmem + 256 + s * 128, p_s, v_s + s * TILE_BYTES, p.idesc_pv, 8, HALF_BYTES, false);
+        mma_commit(o_full(s));
+        mma_commit(v_empty(s));
+      }
+      mma_commit(done_bar);
+      mbar_wait_drain(done_bar, 0);
+    }
+  } else {
+    // ------------------------------------------------------------------ softmax / accumulate / epilogue
+    const int qd = warp & 3;                 // TMEM lane quarter of this warp
+    const int row = qd * 32 + lane;          // query row within the tile
+    const uint32_t lane_addr = tmem + ((uint32_t)(qd * 32) << 16);
+    float o[AD];
+#pragma unroll
+    for (int i = 0; i < AD; ++i) o[i] = 0.f;
+    float m = -CUDART_INF_F, l = 0.f, alpha_prev = 1.f;
+    bool ok = true;
+    for (int j = 0; j < ntiles && ok; ++j) {
+      const int s = j & 1;
+      if (!mbar_wait(s_full(s), (j >> 1) & 1u, abort_flag)) { ok = false; break; }
+      tc_fence_after();
+      const uint32_t s_addr = lane_addr + s * 128;
+      const bool diag = (j == ntiles - 1);
+      // pass 1: row maximum of the raw scores
+      float mx = m;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t r[32];
+        tmem_ld32(s_addr + c * 32, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const float sv = __uint_as_float(r[i]);
+          if (!diag || c * 32 + i <= row) mx = fmaxf(mx, sv);
+        }
+      }
+      const float mc = mx * p.scale_log2;
+      const float alpha = exp2f(m * p.scale_log2 - mc);  // m = -inf on the first tile -> 0
+      // the P buffer and O_{j-1} are free / ready once the previous PV product has completed
+      if (j > 0 && !mbar_wait(o_full((j - 1) & 1), ((j - 1) >> 1) & 1u, abort_flag)) { ok = false; break; }
+      tc_fence_after();
+      // pass 2: probabilities -> shared memory (bf16), row sum
+      float sum = 0.f;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t r[32];
+        float pv[32];
+        tmem_ld32(s_addr + c * 32, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const float e = exp2f(fmaf(__uint_as_float(r[i]), p.scale_log2, -mc));
+          pv[i] = (!diag || c * 32 + i <= row) ? e : 0.f;
+          sum += pv[i];
+        }
+        store_swizzled32<T>(p_ptr, row, c * 32, pv);
+      }
+      l = l * alpha + sum;
+      m = mx;
+      tc_fence_before();
+      fence_proxy_async_smem();   // generic-proxy writes of P must be visible to the tensor core
+      mbar_arrive(p_full);
+      // fold O_{j-1} into the register accumulator while the tensor core computes S_{j+1} and P_j V_j
+      if (j > 0) {
+        const uint32_t o_addr = lane_addr + 256 + ((j - 1) & 1) * 128;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          uint32_t r[32];
+          tmem_ld32(o_addr + c * 32, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o[c * 32 + i] = fmaf(o[c * 32 + i], alpha_prev, __uint_as_float(r[i]));
+        }
+      }
+      alpha_prev = alpha;
+    }
+    if (ok && mbar_wait(o_full((ntiles - 1) & 1), ((ntiles - 1) >> 1) & 1u, abort_flag)) {
+      tc_fence_after();
+      const uint32_t o_addr = lane_addr + 256 + ((ntiles - 1) & 1) * 128;
+      const float inv = 1.f / l;
+      const int qi = qt * TILE + row;
+      T* orow = reinterpret_cast<T*>(p.out) + ((int64_t)bh * p.S + qi) * AD;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t r[32];
+        tmem_ld32(o_addr + c * 32, r);
+        tmem_ld_wait();
+        if (qi < p.S) {
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            uint4 w;
+            uint32_t* wp = reinterpret_cast<uint32_t*>(&w);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const int i = g * 8 + e * 2;
+              wp[e] = pack2<T>(fmaf(o[c * 32 + i], alpha_prev, __uint_as_float(r[i])) * inv,
+                               fmaf(o[c * 32 + i + 1], alpha_prev, __uint_as_float(r[i + 1])) * inv);
+            }
+            *reinterpret_cast<uint4*>(orow + c * 32 + g * 8) = w;
+          }
+        }
+      }
+      if (qi < p.S) p.lse[(int64_t)bh * p.S + qi] = (m * p.scale_log2 + log2f(l)) * kLn2;
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem, 512); }
+  if (threadIdx.x == 0 && *abort_flag) flag_status(p.status, Q3_STATUS_WAIT_TIMEOUT);
+}
+
+constexpr int kFwdSmem = 6 * TILE_BYTES + 1024 + 256;
+
+}  // namespace tc
+
+bool attn_tc_available() { return true; }
+
+int attn_fwd_tc(const void* q, const void* k, const void* v, void* out, float* lse, int64_t B, int64_t Hq, int64_t Hkv,
+                int64_t S, float scale, int dtype, int* status, cudaStream_t st) {
+  using namespace tc;
+  const bool bf16 = dtype == Q3_BF16;
+  CUtensorMap tmQ, tmK, tmV;
+  int rc = make_tmap_3d(&tmQ, q, bf16, B * Hq, S, AD, AD, S * AD, 64, TILE);
+  if (rc != Q3_OK) return rc;
+  rc = make_tmap_3d(&tmK, k, bf16, B * Hkv, S, AD, AD, S * AD, 64, TILE);
+  if (rc != Q3_OK) return rc;
+  rc = make_tmap_3d(&tmV, v, bf16, B * Hkv, S, AD, AD, S * AD, 64, TILE);
+  if (rc != Q3_OK) return rc;
+  AttnParams p{};
+  p.out = out; p.lse = lse; p.Hq = (int)Hq; p.Hkv = (int)Hkv; p.S = (int)S;
+  p.scale_log2 = scale * kLog2e;
+  p.idesc_qk = make_idesc_f16(128, 128, bf16, false, false);
+  p.idesc_pv = make_idesc_f16(128, 128, bf16, false, true);
+  p.status = status;
+  dim3 grid((unsigned)cdiv(S, TILE), (unsigned)(B * Hq));
+  cudaError_t e;
+  if (bf16) {
+    static bool cfg = false;
+    if (!cfg) {
+      e = cudaFuncSetAttribute(attn_fwd_tc_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, kFwdSmem);
+      if (e != cudaSuccess) return Q3_ERR_CUDA - (int)e;
+      cfg = true;
+    }
+    attn_fwd_tc_kernel<__nv_bfloat16><<<grid, kAttnThreads, kFwdSmem, st>>>(tmQ, tmK, tmV, p);
+  } else {
+    static bool cfg = false;
+    if (!cfg) {
+      e = cudaFuncSetAttribute(attn_fwd_tc_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, kFwdSmem);
+      if (e != cudaSuccess) return Q3_ERR_CUDA - (int)e;
+      cfg = true;
+    }
+    attn_fwd_tc_kernel<__half><<<grid, kAttnThreads, kFwdSmem, st>>>(tmQ, tmK, tmV, p);
+  }
+  return launch_status();
+}
+
+int attn_bwd_simt(const void* q, const void* k, const void* v, const void* dout, const float* lse, const float* delta,
+                  void* dq, void* dk, void* dv, int64_t B, int64_t Hq, int64_t Hkv, int64_t S, int64_t D, float scale,
+                  int dtype, cudaStream_t st);
+
+int attn_bwd_tc(const void* q, const void* k, const void* v, const void* dout, const float* lse, const float* delta,
+                void* dq, void* dk, void* dv, int64_t B, int64_t Hq, int64_t Hkv, int64_t S, float scale, int dtype,
+                int* status, cudaStream_t st) {
+  (void)status;
+  return attn_bwd_simt(q, k, v, dout, lse, delta, dq, dk, dv, B, Hq, Hkv, S, 128, scale, dtype, st);
+}
+
 }  // namespace q3

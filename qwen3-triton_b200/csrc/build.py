@@ -70,7 +70,10 @@ def build(force: bool = False, verbose: bool = False) -> Path:
         raise RuntimeError("nvcc failed")
     objs = [objdir / (s.stem + ".o") for s in sources]
     if force or jobs or stale(LIB, objs):
-        cmd = [nvcc(), *ARCH, "-shared", "-o", str(LIB), *map(str, objs)]
+        # One CUDA runtime per process: link libcudart dynamically so that, inside a PyTorch process, this
+        # library shares torch's runtime instance (same per-thread current device and context).
+        cmd = [nvcc(), *ARCH, "-shared", "-cudart", "shared", "-Xlinker", "-rpath=/usr/local/cuda/lib64",
+               "-o", str(LIB), *map(str, objs)]
         res = subprocess.run(cmd, capture_output=True, text=True)
         if res.returncode != 0:
             sys.stderr.write(res.stdout + res.stderr)

@@ -210,10 +210,22 @@ inline EncodeTiledFn encode_tiled_fn() {
 
 // 2-D map over a row-major [rows, cols] matrix of 16-bit elements with leading dimension `ld`
 // (elements); box = box_cols x box_rows, 128-byte swizzle, out-of-range elements read as zero.
+// The driver call below needs a current context on the calling thread. A thread that has not yet made
+// a runtime call through this library (e.g. an autograd worker whose first operator is a GEMM) has
+// none bound, so bind the primary context once per thread.
+inline void ensure_thread_context() {
+  static thread_local bool bound = false;
+  if (!bound) {
+    cudaFree(nullptr);
+    bound = true;
+  }
+}
+
 inline int make_tmap_2d(CUtensorMap* map, const void* base, bool bf16, int64_t rows, int64_t cols, int64_t ld,
                         int box_cols, int box_rows) {
   EncodeTiledFn fn = encode_tiled_fn();
   if (!fn) return Q3_ERR_DRIVER;
+  ensure_thread_context();
   cuuint64_t gdim[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
   cuuint64_t gstride[1] = {(cuuint64_t)ld * 2};
   cuuint32_t box[2] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows};
@@ -232,6 +244,7 @@ inline int make_tmap_3d(CUtensorMap* map, const void* base, bool bf16, int64_t d
                         int64_t ld1, int64_t ld2, int box_cols, int box_rows) {
   EncodeTiledFn fn = encode_tiled_fn();
   if (!fn) return Q3_ERR_DRIVER;
+  ensure_thread_context();
   cuuint64_t gdim[3] = {(cuuint64_t)cols, (cuuint64_t)rows, (cuuint64_t)d2};
   cuuint64_t gstride[2] = {(cuuint64_t)ld1 * 2, (cuuint64_t)ld2 * 2};
   cuuint32_t box[3] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows, 1};
