@@ -302,6 +302,392 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
 
 constexpr int kFwdSmem = 6 * TILE_BYTES + 1024 + 256;
 
+// ====================================================================================== backward
+struct AttnBwdParams {
+  const float* lse;
+  const float* delta;
+  void* dq;
+  void* dk;
+  void* dv;
+  int Hq, Hkv, S;
+  float scale, scale_log2;
+  uint32_t idesc_kk128;  // A K-major, B K-major, N = 128
+  uint32_t idesc_kk64;   // A K-major, B K-major, N = 64
+  uint32_t idesc_kmn;    // A K-major, B MN-major, N = 128
+  int* status;
+};
+
+// Generic helpers with explicit half strides. A/B K-major, contraction 16*ksteps over 64-wide halves.
+__device__ __forceinline__ void mma_kk(uint32_t d_tmem, uint32_t a_smem, uint32_t a_half, uint32_t b_smem,
+                                       uint32_t b_half, uint32_t idesc, int ksteps, bool accumulate_first) {
+  for (int k = 0; k < ksteps; ++k) {
+    mma_f16_ss(d_tmem, make_smem_desc(a_smem + (k >> 2) * a_half + (k & 3) * 32, 0, 1024),
+               make_smem_desc(b_smem + (k >> 2) * b_half + (k & 3) * 32, 0, 1024), idesc,
+               (accumulate_first || k) ? 1u : 0u);
+  }
+}
+// A K-major, B MN-major with `b_lbo` bytes between its 64-wide column atoms; contraction over B's rows.
+__device__ __forceinline__ void mma_kmn2(uint32_t d_tmem, uint32_t a_smem, uint32_t a_half, uint32_t b_smem,
+                                         uint32_t b_lbo, uint32_t idesc, int ksteps, bool accumulate_first) {
+  for (int k = 0; k < ksteps; ++k) {
+    mma_f16_ss(d_tmem, make_smem_desc(a_smem + (k >> 2) * a_half + (k & 3) * 32, 0, 1024),
+               make_smem_desc(b_smem + k * (16 * 128), b_lbo, 1024), idesc, (accumulate_first || k) ? 1u : 0u);
+  }
+}
+
+// ------------------------------------------------------------------ dQ: one CTA per 128-query tile
+// smem: [Q][dO][K0][K1][V0][V1][dS] 32 KB each. TMEM columns: S 0..127, dP 128..255, dQ 256..383.
+template <typename T>
+__global__ void __launch_bounds__(kAttnThreads, 1)
+attn_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                  const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
+                  const AttnBwdParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem = smem_raw + (base - smem_u32(smem_raw));
+  const uint32_t q_s = base, do_s = base + TILE_BYTES, k_s = base + 2 * TILE_BYTES, v_s = base + 4 * TILE_BYTES,
+                 ds_s = base + 6 * TILE_BYTES;
+  uint8_t* ds_ptr = smem + 6 * TILE_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 7 * TILE_BYTES);
+  const uint32_t bar0 = smem_u32(bars);
+  const uint32_t q_full = bar0;
+  auto k_full = [&](int s) { return bar0 + 8u * (1 + s); };
+  auto k_empty = [&](int s) { return bar0 + 8u * (3 + s); };
+  auto v_full = [&](int s) { return bar0 + 8u * (5 + s); };
+  auto v_empty = [&](int s) { return bar0 + 8u * (7 + s); };
+  const uint32_t sdp_full = bar0 + 8u * 9, dq_full = bar0 + 8u * 10, ds_full = bar0 + 8u * 11, done_bar = bar0 + 8u * 12;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 13);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nq = (p.S + TILE - 1) / TILE;
+  const int qt = nq - 1 - (int)blockIdx.x;
+  const int bh = blockIdx.y, b = bh / p.Hq, h = bh % p.Hq, kvh = h / (p.Hq / p.Hkv);
+  const int bkv = b * p.Hkv + kvh;
+  const int ntiles = qt + 1;
+
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    for (int i = 0; i < 11; ++i) mbar_init(bar0 + 8u * i, 1);
+    mbar_init(ds_full, 128);
+    mbar_init(done_bar, 1);
+    fence_barrier_init();
+    prefetch_tmap(&tmQ); prefetch_tmap(&tmK); prefetch_tmap(&tmV); prefetch_tmap(&tmDO);
+  }
+  if (warp == 1) { tmem_alloc(smem_u32(tmem_slot), 512); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      mbar_expect_tx(q_full, 2 * TILE_BYTES);
+      tma_load_3d(q_s, &tmQ, 0, qt * TILE, bh, q_full);
+      tma_load_3d(q_s + HALF_BYTES, &tmQ, 64, qt * TILE, bh, q_full);
+      tma_load_3d(do_s, &tmDO, 0, qt * TILE, bh, q_full);
+      tma_load_3d(do_s + HALF_BYTES, &tmDO, 64, qt * TILE, bh, q_full);
+      int issued = 0;
+      for (int j = 0; j < ntiles; ++j) {
+        const int s = j & 1;
+        const uint32_t ph = (j >> 1) & 1u;
+        if (!mbar_wait(k_empty(s), ph ^ 1u, abort_flag)) break;
+        mbar_expect_tx(k_full(s), TILE_BYTES);
+        tma_load_3d(k_s + s * TILE_BYTES, &tmK, 0, j * TILE, bkv, k_full(s));
+        tma_load_3d(k_s + s * TILE_BYTES + HALF_BYTES, &tmK, 64, j * TILE, bkv, k_full(s));
+        if (!mbar_wait(v_empty(s), ph ^ 1u, abort_flag)) { mbar_wait_drain(k_full(s), ph); break; }
+        mbar_expect_tx(v_full(s), TILE_BYTES);
+        tma_load_3d(v_s + s * TILE_BYTES, &tmV, 0, j * TILE, bkv, v_full(s));
+        tma_load_3d(v_s + s * TILE_BYTES + HALF_BYTES, &tmV, 64, j * TILE, bkv, v_full(s));
+        issued = j + 1;
+      }
+      mbar_wait_drain(q_full, 0);
+      for (int j = issued > 2 ? issued - 2 : 0; j < issued; ++j) {
+        mbar_wait_drain(k_full(j & 1), (j >> 1) & 1u);
+        mbar_wait_drain(v_full(j & 1), (j >> 1) & 1u);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      bool ok = mbar_wait(q_full, 0, abort_flag);
+      for (int j = 0; j < ntiles && ok; ++j) {
+        const int s = j & 1;
+        const uint32_t ph = (j >> 1) & 1u;
+        if (!mbar_wait(k_full(s), ph, abort_flag) || !mbar_wait(v_full(s), ph, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        mma_kk(tmem + 0, q_s, HALF_BYTES, k_s + s * TILE_BYTES, HALF_BYTES, p.idesc_kk128, 8, false);     // S
+        mma_kk(tmem + 128, do_s, HALF_BYTES, v_s + s * TILE_BYTES, HALF_BYTES, p.idesc_kk128, 8, false);  // dP
+        mma_commit(sdp_full);
+        mma_commit(v_empty(s));
+        if (!mbar_wait(ds_full, j & 1u, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        mma_kmn2(tmem + 256, ds_s, HALF_BYTES, k_s + s * TILE_BYTES, HALF_BYTES, p.idesc_kmn, 8, j > 0);   // dQ += dS K
+        mma_commit(k_empty(s));
+      }
+      if (ok) mma_commit(dq_full);
+      mma_commit(done_bar);
+      mbar_wait_drain(done_bar, 0);
+    }
+  } else {
+    const int qd = warp & 3, row = qd * 32 + lane;
+    const uint32_t lane_addr = tmem + ((uint32_t)(qd * 32) << 16);
+    const int qi = qt * TILE + row;
+    const float lse2 = (qi < p.S ? p.lse[(int64_t)bh * p.S + qi] : 0.f) * kLog2e;
+    const float dl = qi < p.S ? p.delta[(int64_t)bh * p.S + qi] : 0.f;
+    bool ok = true;
+    for (int j = 0; j < ntiles && ok; ++j) {
+      if (!mbar_wait(sdp_full, j & 1u, abort_flag)) { ok = false; break; }
+      tc_fence_after();
+      const bool diag = (j == ntiles - 1);
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t rs[32], rp[32];
+        float ds[32];
+        tmem_ld32(lane_addr + c * 32, rs);
+        tmem_ld32(lane_addr + 128 + c * 32, rp);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const float pr = exp2f(fmaf(__uint_as_float(rs[i]), p.scale_log2, -lse2));
+          const bool keep = (!diag || c * 32 + i <= row) && qi < p.S;
+          ds[i] = keep ? pr * (__uint_as_float(rp[i]) - dl) : 0.f;
+        }
+        store_swizzled32<T>(ds_ptr, row, c * 32, ds);
+      }
+      tc_fence_before();
+      fence_proxy_async_smem();
+      mbar_arrive(ds_full);
+    }
+    if (ok && mbar_wait(dq_full, 0, abort_flag)) {
+      tc_fence_after();
+      T* orow = reinterpret_cast<T*>(p.dq) + ((int64_t)bh * p.S + qi) * AD;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t r[32];
+        tmem_ld32(lane_addr + 256 + c * 32, r);
+        tmem_ld_wait();
+        if (qi < p.S) {
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            uint4 w;
+            uint32_t* wp = reinterpret_cast<uint32_t*>(&w);
+#pragma unroll
+            for (int e = 0; e < 4; ++e)
+              wp[e] = pack2<T>(__uint_as_float(r[g * 8 + 2 * e]) * p.scale, __uint_as_float(r[g * 8 + 2 * e + 1]) * p.scale);
+            *reinterpret_cast<uint4*>(orow + c * 32 + g * 8) = w;
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem, 512); }
+  if (threadIdx.x == 0 && *abort_flag) flag_status(p.status, Q3_STATUS_WAIT_TIMEOUT);
+}
+constexpr int kDqSmem = 7 * TILE_BYTES + 1024 + 256;
+
+// ------------------------------------------------------------------ dK/dV: one CTA per 128-key tile of (b, kv head)
+// Work items: (query head g of the group) x (64-query sub-tile i >= 2*kt). Shared memory:
+//   [K 32K][V 32K] resident, 3 stages of {Q_i 16K, dO_i 16K}, [P^T 16K][dS^T 16K], lse/delta 2 x 64 floats.
+// TMEM columns: S^T buffers 0..63 / 64..127, dP^T buffers 128..191 / 192..255, dK 256..383, dV 384..511.
+constexpr int QSUB = 64;
+constexpr int SUB_HALF = QSUB * 128;        // 8 KB: one 64-column half of a 64-row tile
+constexpr int SUB_BYTES = 2 * SUB_HALF;     // 16 KB
+constexpr int KV_STAGES = 3;
+
+template <typename T>
+__global__ void __launch_bounds__(kAttnThreads, 1)
+attn_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                    const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
+                    const AttnBwdParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem = smem_raw + (base - smem_u32(smem_raw));
+  const uint32_t k_s = base, v_s = base + TILE_BYTES, st_s = base + 2 * TILE_BYTES;
+  const uint32_t pt_off = 2 * TILE_BYTES + KV_STAGES * 2 * SUB_BYTES;
+  const uint32_t pt_s = base + pt_off, dst_s = pt_s + SUB_BYTES;
+  uint8_t* pt_ptr = smem + pt_off;
+  uint8_t* dst_ptr = pt_ptr + SUB_BYTES;
+  float* stat = reinterpret_cast<float*>(dst_ptr + SUB_BYTES);   // [2][64]: lse*log2e, delta
+  uint64_t* bars = reinterpret_cast<uint64_t*>(stat + 2 * QSUB);
+  const uint32_t bar0 = smem_u32(bars);
+  const uint32_t kv_full = bar0;
+  auto st_full = [&](int s) { return bar0 + 8u * (1 + s); };
+  auto st_empty = [&](int s) { return bar0 + 8u * (4 + s); };
+  auto sdp_full = [&](int s) { return bar0 + 8u * (7 + s); };
+  const uint32_t pds_empty = bar0 + 8u * 9, acc_full = bar0 + 8u * 10, done_bar = bar0 + 8u * 11,
+                 pds_full = bar0 + 8u * 12;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 13);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int kt = blockIdx.x, bk = blockIdx.y, b = bk / p.Hkv, kvh = bk % p.Hkv, G = p.Hq / p.Hkv;
+  const int nsub = (p.S + QSUB - 1) / QSUB, first = kt * (TILE / QSUB);
+  const int per_head = nsub - first, total = G * per_head;
+
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    for (int i = 0; i < 12; ++i) mbar_init(bar0 + 8u * i, 1);
+    mbar_init(pds_full, 128);
+    fence_barrier_init();
+    prefetch_tmap(&tmQ); prefetch_tmap(&tmK); prefetch_tmap(&tmV); prefetch_tmap(&tmDO);
+  }
+  if (warp == 1) { tmem_alloc(smem_u32(tmem_slot), 512); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      mbar_expect_tx(kv_full, 2 * TILE_BYTES);
+      tma_load_3d(k_s, &tmK, 0, kt * TILE, bk, kv_full);
+      tma_load_3d(k_s + HALF_BYTES, &tmK, 64, kt * TILE, bk, kv_full);
+      tma_load_3d(v_s, &tmV, 0, kt * TILE, bk, kv_full);
+      tma_load_3d(v_s + HALF_BYTES, &tmV, 64, kt * TILE, bk, kv_full);
+      int issued = 0;
+      for (int it = 0; it < total; ++it) {
+        const int s = it % KV_STAGES;
+        const uint32_t ph = (it / KV_STAGES) & 1u;
+        if (!mbar_wait(st_empty(s), ph ^ 1u, abort_flag)) break;
+        const int g = it / per_head, i = first + it % per_head;
+        const int bh = (b * p.Hkv + kvh) * G + g;   // query head = kvh * G + g
+        const uint32_t dst = st_s + s * 2 * SUB_BYTES;
+        mbar_expect_tx(st_full(s), 2 * SUB_BYTES);
+        tma_load_3d(dst, &tmQ, 0, i * QSUB, bh, st_full(s));
+        tma_load_3d(dst + SUB_HALF, &tmQ, 64, i * QSUB, bh, st_full(s));
+        tma_load_3d(dst + SUB_BYTES, &tmDO, 0, i * QSUB, bh, st_full(s));
+        tma_load_3d(dst + SUB_BYTES + SUB_HALF, &tmDO, 64, i * QSUB, bh, st_full(s));
+        issued = it + 1;
+      }
+      mbar_wait_drain(kv_full, 0);
+      for (int it = issued > KV_STAGES ? issued - KV_STAGES : 0; it < issued; ++it)
+        mbar_wait_drain(st_full(it % KV_STAGES), (it / KV_STAGES) & 1u);
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      bool ok = mbar_wait(kv_full, 0, abort_flag) && mbar_wait(st_full(0), 0, abort_flag);
+      if (ok) {
+        tc_fence_after();
+        mma_kk(tmem + 0, k_s, HALF_BYTES, st_s, SUB_HALF, p.idesc_kk64, 8, false);                 // S^T = K Q^T
+        mma_kk(tmem + 128, v_s, HALF_BYTES, st_s + SUB_BYTES, SUB_HALF, p.idesc_kk64, 8, false);   // dP^T = V dO^T
+        mma_commit(sdp_full(0));
+      }
+      for (int it = 0; it < total && ok; ++it) {
+        const int s = it % KV_STAGES;
+        if (it + 1 < total) {
+          const int s1 = (it + 1) % KV_STAGES, buf = (it + 1) & 1;
+          if (!mbar_wait(st_full(s1), ((it + 1) / KV_STAGES) & 1u, abort_flag)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t st1 = st_s + s1 * 2 * SUB_BYTES;
+          mma_kk(tmem + buf * 64, k_s, HALF_BYTES, st1, SUB_HALF, p.idesc_kk64, 8, false);
+          mma_kk(tmem + 128 + buf * 64, v_s, HALF_BYTES, st1 + SUB_BYTES, SUB_HALF, p.idesc_kk64, 8, false);
+          mma_commit(sdp_full(buf));
+        }
+        if (!mbar_wait(pds_full, it & 1u, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t st0 = st_s + s * 2 * SUB_BYTES;
+        mma_kmn2(tmem + 384, pt_s, 0, st0 + SUB_BYTES, SUB_HALF, p.idesc_kmn, 4, it > 0);   // dV += P^T dO
+        mma_kmn2(tmem + 256, dst_s, 0, st0, SUB_HALF, p.idesc_kmn, 4, it > 0);             // dK += dS^T Q
+        mma_commit(st_empty(s));
+        mma_commit(pds_empty);
+      }
+      if (ok) mma_commit(acc_full);
+      mma_commit(done_bar);
+      mbar_wait_drain(done_bar, 0);
+    }
+  } else {
+    const int qd = warp & 3, row = qd * 32 + lane;   // key row within the tile
+    const int tid = threadIdx.x - 64;                // 0..127 among the compute threads
+    const uint32_t lane_addr = tmem + ((uint32_t)(qd * 32) << 16);
+    const int kj = kt * TILE + row;
+    bool ok = true;
+    for (int it = 0; it < total; ++it) {
+      const int g = it / per_head, i = first + it % per_head;
+      const int bh = (b * p.Hkv + kvh) * G + g;
+      // stage the 64 lse / delta values of this query sub-tile (previous readers are past their loop).
+      // A thread whose wait gave up keeps arriving at these barriers, so the group leaves together.
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (*abort_flag) { ok = false; break; }
+      {
+        const int qi = i * QSUB + (tid & 63);
+        float val = 0.f;
+        if (qi < p.S) val = tid < 64 ? p.lse[(int64_t)bh * p.S + qi] * kLog2e : p.delta[(int64_t)bh * p.S + qi];
+        stat[tid] = val;
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (!mbar_wait(sdp_full(it & 1), (it >> 1) & 1u, abort_flag)) { ok = false; continue; }
+      tc_fence_after();
+      // P^T / dS^T of the previous item must have been consumed before they are overwritten
+      if (!mbar_wait(pds_empty, (it & 1u) ^ 1u, abort_flag)) { ok = false; continue; }
+      const bool diag = (i * QSUB < kt * TILE + TILE);   // sub-tile overlaps the diagonal block
+#pragma unroll 1
+      for (int c = 0; c < 2; ++c) {
+        uint32_t rs[32], rp[32];
+        float pv[32], dsv[32];
+        tmem_ld32(lane_addr + (it & 1) * 64 + c * 32, rs);
+        tmem_ld32(lane_addr + 128 + (it & 1) * 64 + c * 32, rp);
+        tmem_ld_wait();
+#pragma unroll
+        for (int e = 0; e < 32; ++e) {
+          const int col = c * 32 + e, qi = i * QSUB + col;
+          const float pr = exp2f(fmaf(__uint_as_float(rs[e]), p.scale_log2, -stat[col]));
+          const bool keep = qi < p.S && (!diag || kj <= qi);
+          pv[e] = keep ? pr : 0.f;
+          dsv[e] = keep ? pr * (__uint_as_float(rp[e]) - stat[QSUB + col]) : 0.f;
+        }
+        store_swizzled32<T>(pt_ptr, row, c * 32, pv);
+        store_swizzled32<T>(dst_ptr, row, c * 32, dsv);
+      }
+      tc_fence_before();
+      fence_proxy_async_smem();
+      mbar_arrive(pds_full);
+    }
+    if (ok && mbar_wait(acc_full, 0, abort_flag)) {
+      tc_fence_after();
+      T* krow = reinterpret_cast<T*>(p.dk) + ((int64_t)bk * p.S + kj) * AD;
+      T* vrow = reinterpret_cast<T*>(p.dv) + ((int64_t)bk * p.S + kj) * AD;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t rk[32], rv[32];
+        tmem_ld32(lane_addr + 256 + c * 32, rk);
+        tmem_ld32(lane_addr + 384 + c * 32, rv);
+        tmem_ld_wait();
+        if (kj < p.S) {
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            uint4 wk, wv;
+            uint32_t* pk = reinterpret_cast<uint32_t*>(&wk);
+            uint32_t* pv2 = reinterpret_cast<uint32_t*>(&wv);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              pk[e] = pack2<T>(__uint_as_float(rk[g * 8 + 2 * e]) * p.scale, __uint_as_float(rk[g * 8 + 2 * e + 1]) * p.scale);
+              pv2[e] = pack2<T>(__uint_as_float(rv[g * 8 + 2 * e]), __uint_as_float(rv[g * 8 + 2 * e + 1]));
+            }
+            *reinterpret_cast<uint4*>(krow + c * 32 + g * 8) = wk;
+            *reinterpret_cast<uint4*>(vrow + c * 32 + g * 8) = wv;
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem, 512); }
+  if (threadIdx.x == 0 && *abort_flag) flag_status(p.status, Q3_STATUS_WAIT_TIMEOUT);
+}
+constexpr int kDkdvSmem = 2 * TILE_BYTES + KV_STAGES * 2 * SUB_BYTES + 2 * SUB_BYTES + 2 * QSUB * 4 + 1024 + 256;
+
+template <typename K> int configure_smem(K kern, int bytes, bool* done) {
+  if (!*done) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    if (e != cudaSuccess) return Q3_ERR_CUDA - (int)e;
+    *done = true;
+  }
+  return Q3_OK;
+}
+
 }  // namespace tc
 
 bool attn_tc_available() { return true; }
@@ -345,15 +731,41 @@ int attn_fwd_tc(const void* q, const void* k, const void* v, void* out, float* l
   return launch_status();
 }
 
-int attn_bwd_simt(const void* q, const void* k, const void* v, const void* dout, const float* lse, const float* delta,
-                  void* dq, void* dk, void* dv, int64_t B, int64_t Hq, int64_t Hkv, int64_t S, int64_t D, float scale,
-                  int dtype, cudaStream_t st);
-
 int attn_bwd_tc(const void* q, const void* k, const void* v, const void* dout, const float* lse, const float* delta,
                 void* dq, void* dk, void* dv, int64_t B, int64_t Hq, int64_t Hkv, int64_t S, float scale, int dtype,
                 int* status, cudaStream_t st) {
-  (void)status;
-  return attn_bwd_simt(q, k, v, dout, lse, delta, dq, dk, dv, B, Hq, Hkv, S, 128, scale, dtype, st);
+  using namespace tc;
+  const bool bf16 = dtype == Q3_BF16;
+  CUtensorMap tmQ, tmK, tmV, tmDO, tmQs, tmDOs;
+  int rc;
+  if ((rc = make_tmap_3d(&tmQ, q, bf16, B * Hq, S, AD, AD, S * AD, 64, TILE)) != Q3_OK) return rc;
+  if ((rc = make_tmap_3d(&tmDO, dout, bf16, B * Hq, S, AD, AD, S * AD, 64, TILE)) != Q3_OK) return rc;
+  if ((rc = make_tmap_3d(&tmK, k, bf16, B * Hkv, S, AD, AD, S * AD, 64, TILE)) != Q3_OK) return rc;
+  if ((rc = make_tmap_3d(&tmV, v, bf16, B * Hkv, S, AD, AD, S * AD, 64, TILE)) != Q3_OK) return rc;
+  if ((rc = make_tmap_3d(&tmQs, q, bf16, B * Hq, S, AD, AD, S * AD, 64, QSUB)) != Q3_OK) return rc;
+  if ((rc = make_tmap_3d(&tmDOs, dout, bf16, B * Hq, S, AD, AD, S * AD, 64, QSUB)) != Q3_OK) return rc;
+  AttnBwdParams p{};
+  p.lse = lse; p.delta = delta; p.dq = dq; p.dk = dk; p.dv = dv;
+  p.Hq = (int)Hq; p.Hkv = (int)Hkv; p.S = (int)S; p.scale = scale; p.scale_log2 = scale * kLog2e;
+  p.idesc_kk128 = make_idesc_f16(128, 128, bf16, false, false);
+  p.idesc_kk64 = make_idesc_f16(128, 64, bf16, false, false);
+  p.idesc_kmn = make_idesc_f16(128, 128, bf16, false, true);
+  p.status = status;
+  dim3 gq((unsigned)cdiv(S, TILE), (unsigned)(B * Hq)), gk((unsigned)cdiv(S, TILE), (unsigned)(B * Hkv));
+  if (bf16) {
+    static bool c1 = false, c2 = false;
+    if ((rc = configure_smem(attn_dq_tc_kernel<__nv_bfloat16>, kDqSmem, &c1)) != Q3_OK) return rc;
+    if ((rc = configure_smem(attn_dkdv_tc_kernel<__nv_bfloat16>, kDkdvSmem, &c2)) != Q3_OK) return rc;
+    attn_dkdv_tc_kernel<__nv_bfloat16><<<gk, kAttnThreads, kDkdvSmem, st>>>(tmQs, tmK, tmV, tmDOs, p);
+    attn_dq_tc_kernel<__nv_bfloat16><<<gq, kAttnThreads, kDqSmem, st>>>(tmQ, tmK, tmV, tmDO, p);
+  } else {
+    static bool c1 = false, c2 = false;
+    if ((rc = configure_smem(attn_dq_tc_kernel<__half>, kDqSmem, &c1)) != Q3_OK) return rc;
+    if ((rc = configure_smem(attn_dkdv_tc_kernel<__half>, kDkdvSmem, &c2)) != Q3_OK) return rc;
+    attn_dkdv_tc_kernel<__half><<<gk, kAttnThreads, kDkdvSmem, st>>>(tmQs, tmK, tmV, tmDOs, p);
+    attn_dq_tc_kernel<__half><<<gq, kAttnThreads, kDqSmem, st>>>(tmQ, tmK, tmV, tmDO, p);
+  }
+  return launch_status();
 }
 
 }  // namespace q3
