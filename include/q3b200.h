@@ -42,6 +42,7 @@ enum {
   Q3_ERR_ALIGN = -5,     /* pointer or stride alignment not supported by any path */
   Q3_ERR_DRIVER = -6,    /* a required driver entry point is unavailable */
   Q3_ERR_TMAP = -7,      /* the driver rejected a TMA tensor-map description */
+  Q3_ERR_LIMIT = -8,     /* size beyond the fixed capacity of a no-allocation entry point */
   Q3_ERR_CUDA = -1000    /* Q3_ERR_CUDA - cudaError_t */
 };
 
@@ -90,6 +91,17 @@ int64_t q3_rmsnorm_bwd_workspace_bytes(int64_t rows, int64_t H);
  * Reference: qwen3_triton/kernels/norm.py:16-37,53-63. */
 int q3_rmsnorm_bwd(const void* x, const void* weight, const void* dy, const float* inv_rms, void* dx, void* dweight,
                    void* workspace, int64_t workspace_bytes, int64_t rows, int64_t H, int dtype, q3_stream_t stream);
+
+/* q3_rmsnorm_bwd for callers that cannot allocate device memory when they need it (inside an allocator or
+ * memory-pool callback, in a host that fixes its whole HBM plan up front, in a latency-critical loop that must
+ * not risk cudaMalloc/cudaFree): the partial-row scratch is a fixed 16 MiB device array inside the library
+ * instead of a caller workspace, and the call allocates nothing. Limit: H <= 4096 (Q3_ERR_LIMIT beyond that).
+ * The first call on each device resolves the array's device address; make that call before starting any
+ * stream capture. All calls on a device share the array, so calls that overlap on the GPU (different streams)
+ * race: serialise them. Same results as q3_rmsnorm_bwd.
+ * This entry point has no counterpart in the reference. */
+int q3_rmsnorm_bwd_noalloc(const void* x, const void* weight, const void* dy, const float* inv_rms, void* dx,
+                           void* dweight, int64_t rows, int64_t H, int dtype, q3_stream_t stream);
 
 /* residual_out = x + residual (rounded to dtype); y = RMSNorm(residual_out) * weight.
  * Fuses reference qwen3_triton/kernels/residual.py:7-11 with kernels/norm.py:7-13 (one pass over HBM). */

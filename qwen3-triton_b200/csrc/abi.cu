@@ -12,6 +12,7 @@ extern "C" const char* q3_error_string(int code) {
     case Q3_ERR_WORKSPACE: return "workspace missing or too small";
     case Q3_ERR_ALIGN: return "unsupported pointer or stride alignment";
     case Q3_ERR_DRIVER: return "required CUDA driver entry point unavailable";
+    case Q3_ERR_LIMIT: return "size beyond the fixed scratch capacity of this no-allocation entry point";
     case Q3_ERR_TMAP: return "TMA tensor-map description rejected by the driver";
     default: break;
   }

@@ -414,13 +414,15 @@ int rmsnorm_fwd_launch(const void* x, const void* res, const void* w, void* y, v
 
 template <typename T, bool ADD>
 int rmsnorm_bwd_launch(const void* x, const void* w, const void* dy, const void* dres, const float* inv, void* dx,
-                       void* dw, float* ws, int64_t ws_bytes, int64_t rows, int64_t H, cudaStream_t st) {
+                       void* dw, float* ws, int64_t ws_bytes, int64_t rows, int64_t H, cudaStream_t st,
+                       int max_partial_rows = 1 << 30) {
   constexpr int VF = Vec16<T>::N;
   const bool vec = (H % VF == 0) && aligned16(x) && aligned16(w) && aligned16(dy) && aligned16(dx) &&
                    (!ADD || dres == nullptr || aligned16(dres));
   RowPlan p = vec ? plan_rows(rows, (int)(H / VF), 2, MaxVec<VF>::N, MaxVec<VF>::MAX_TPR, kPartialRowsPerSm)
                   : plan_rows(rows, (int)H, 2, MaxVec<1>::N, MaxVec<1>::MAX_TPR, kPartialRowsPerSm);
   if (p.tpr < 0) return Q3_ERR_SHAPE;
+  if (p.grid > max_partial_rows) p.grid = max_partial_rows;
   if (ws == nullptr || ws_bytes < (int64_t)p.grid * H * 4) return Q3_ERR_WORKSPACE;
   const size_t smem = (32 + (size_t)p.rpb * H) * sizeof(float);
   if (vec) {
@@ -596,4 +598,53 @@ extern "C" int q3_rope_tables(const void* positions, int positions_are_int64, co
       rope_tables_kernel<T, int32_t><<<grid, 256, 0, st>>>((const int32_t*)positions, inv_freq, (T*)cos_t, (T*)sin_t, tokens, (int)D);
   });
   return launch_status();
+}
+
+// ------------------------------------------------------------------ RMSNorm backward without any allocation
+// Some callers may not allocate device memory at the point where they need this gradient: code that runs
+// inside a memory-pool callback or under an allocator lock, a host that pre-plans every byte of HBM and
+// forbids late cudaMalloc, or a real-time loop in which an allocation (and the implicit device
+// synchronisation cudaFree can cause) is not acceptable. For them the partial-row scratch of the weight
+// gradient lives in this fixed device array instead of a caller workspace. Every GPU that loads the
+// library carries the array (16 MiB) until the process exits.
+namespace q3 {
+constexpr int64_t kNoAllocMaxH = 4096;            // widest row the fixed scratch serves
+constexpr int kNoAllocPartialRows = 1024;         // partial weight-gradient rows that fit at that width
+static __device__ __align__(256) float g_rmsnorm_bwd_scratch[kNoAllocPartialRows * kNoAllocMaxH];
+
+// The array's name is only a host-side handle; kernels need its device address, which differs per
+// device. Resolve it once per device, with that device current.
+static int noalloc_scratch(float** out) {
+  static float* cached[64] = {nullptr};
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return Q3_ERR_CUDA - (int)e;
+  if (dev < 0 || dev >= 64) return Q3_ERR_SHAPE;
+  if (cached[dev] == nullptr) {
+    float* ptr = nullptr;
+    e = cudaGetSymbolAddress((void**)&ptr, g_rmsnorm_bwd_scratch);
+    if (e != cudaSuccess) return Q3_ERR_CUDA - (int)e;
+    cached[dev] = ptr;
+  }
+  *out = cached[dev];
+  return Q3_OK;
+}
+}  // namespace q3
+
+extern "C" int q3_rmsnorm_bwd_noalloc(const void* x, const void* weight, const void* dy, const float* inv_rms,
+                                      void* dx, void* dweight, int64_t rows, int64_t H, int dtype,
+                                      q3_stream_t stream) {
+  if (!x || !weight || !dy || !inv_rms || !dx || !dweight) return Q3_ERR_ARG;
+  if (rows < 1 || H < 1) return Q3_ERR_SHAPE;
+  if (H > kNoAllocMaxH) return Q3_ERR_LIMIT;   // beyond the fixed scratch: use q3_rmsnorm_bwd with a workspace
+  float* scratch = nullptr;
+  int rc = noalloc_scratch(&scratch);
+  if (rc != Q3_OK) return rc;
+  // The partial rows used by this call are fully overwritten before they are read, so nothing has to be
+  // cleared between calls.
+  const int max_rows = (int)((kNoAllocPartialRows * kNoAllocMaxH) / H);
+  Q3_DISPATCH_FLOAT(dtype, T, return (rmsnorm_bwd_launch<T, false>(x, weight, dy, nullptr, inv_rms, dx, dweight, scratch,
+                                                                   (int64_t)kNoAllocPartialRows * kNoAllocMaxH * 4, rows, H,
+                                                                   (cudaStream_t)stream, max_rows)));
+  return Q3_OK;
 }

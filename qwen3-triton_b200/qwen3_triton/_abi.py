@@ -36,6 +36,7 @@ SIGNATURES = {
     "q3_rmsnorm_fwd": (I, [P, P, P, P, L, L, D, I, P]),
     "q3_rmsnorm_bwd_workspace_bytes": (L, [L, L]),
     "q3_rmsnorm_bwd": (I, [P, P, P, P, P, P, P, L, L, L, I, P]),
+    "q3_rmsnorm_bwd_noalloc": (I, [P, P, P, P, P, P, L, L, I, P]),
     "q3_add_rmsnorm_fwd": (I, [P, P, P, P, P, P, L, L, D, I, P]),
     "q3_add_rmsnorm_bwd": (I, [P, P, P, P, P, P, P, P, L, L, L, I, P]),
     "q3_norm_rope_fwd": (I, [P, P, P, P, P, P, L, L, L, D, I, P]),
