@@ -1,0 +1,85 @@
+"""FSDP2 wrapping of the Qwen3 graph with a vocabulary-parallel loss head and per-layer recomputation.
+
+Behaviour of the reference's scripts/vocab_model_v12.py:17-56, training/fsdp/official.py:22-63 and
+training/fsdp/activation_checkpoint.py:4-19: every decoder layer, the embedding and the final norm are their
+own FSDP unit with bf16 parameters / fp32 reductions; the last `keep_full_layers` layers stay gathered after
+forward (no second all-gather in backward); every `checkpoint_every`-th layer is recomputed in backward
+(non-reentrant); the lm_head becomes a VocabParallelCE whose fp32 vocabulary shard is kept out of FSDP because
+its gradient is already averaged over data ranks. The wrapped model maps (input_ids, labels) to a loss only.
+"""
+from types import SimpleNamespace
+
+import torch
+from torch.distributed.fsdp import MixedPrecisionPolicy, fully_shard
+
+from ..model import PrecisionQwen3ForCausalLM
+from .vocab_parallel import VocabParallelCE
+
+
+def checkpoint_layer_indices(layer_count, *, all_layers=False, every=0):
+    if layer_count < 1 or type(every) is not int or every < 0:
+        raise ValueError('Positive layer count and nonnegative integer checkpoint interval required')
+    if all_layers and every:
+        raise ValueError('Choose all-layer or interval checkpoint, not both')
+    if all_layers:
+        return tuple(range(layer_count))
+    return tuple(range(0, layer_count, every)) if every else ()
+
+
+def canonical_parameter_name(name):
+    return name.replace('_checkpoint_wrapped_module.', '')
+
+
+def wrap_decoder_checkpoint(layer, *, mode='full'):
+    if mode != 'full':
+        raise ValueError('Only full recomputation is supported')
+    from torch.distributed.algorithms._checkpoint.checkpoint_wrapper import CheckpointImpl, checkpoint_wrapper
+    return checkpoint_wrapper(layer, preserve_rng_state=True, checkpoint_impl=CheckpointImpl.NO_REENTRANT)
+
+
+class VocabLossQwen3(PrecisionQwen3ForCausalLM):
+    """Loss-only graph: hidden states go straight into the vocabulary-parallel head."""
+
+    def forward(self, input_ids, labels=None, *, position_ids=None, use_cache=False, attention_mask=None,
+                past_key_values=None, output_attentions=False, output_hidden_states=False, return_dict=True,
+                logits_to_keep=0, diagnostic_logits=False):
+        if (labels is None or use_cache or attention_mask is not None or past_key_values is not None
+                or output_attentions or output_hidden_states or logits_to_keep):
+            raise ValueError('Vocabulary CE requires dense unpadded labeled loss-only training/evaluation')
+        hidden = self.model(input_ids, position_ids)
+        loss, logits = self.lm_head(hidden, labels, diagnostics=diagnostic_logits)
+        if not return_dict:
+            return (loss, logits)
+        return SimpleNamespace(loss=loss, logits=logits)
+
+
+def shard_vocab_loss_model(model, *, keep_full_layers, checkpoint_every, skip_embedding_backward_gather,
+                           fused_vocab_dw=False, communication=None, mesh=None):
+    if model.config.tie_word_embeddings:
+        raise ValueError('Untied head required')
+    if not 0 <= keep_full_layers <= len(model.model.layers):
+        raise ValueError('Invalid retention count')
+    if not isinstance(model, PrecisionQwen3ForCausalLM):
+        raise TypeError('Supported Qwen3 graph required')
+    model.__class__ = VocabLossQwen3
+    model.lm_head = VocabParallelCE(model.lm_head.weight.detach().cpu(), fused_dw=fused_vocab_dw,
+                                    communication=communication)
+    body = model.model
+    mp = MixedPrecisionPolicy(param_dtype=torch.bfloat16, reduce_dtype=torch.float32)
+    kw = dict(mp_policy=mp) if mesh is None else dict(mp_policy=mp, mesh=mesh)
+    fully_shard(body.embed_tokens.float(), reshard_after_forward=True, **kw)
+    if skip_embedding_backward_gather:
+        body.embed_tokens.set_unshard_in_backward(False)
+    checkpointed = checkpoint_layer_indices(len(body.layers), every=checkpoint_every)
+    for index, layer in enumerate(body.layers):
+        layer = layer.float()
+        if index in checkpointed:
+            layer = wrap_decoder_checkpoint(layer, mode='full')
+        body.layers[index] = layer
+        retain = index >= len(body.layers) - keep_full_layers
+        fully_shard(layer, reshard_after_forward=not retain, **kw)
+    fully_shard(body.norm.float(), reshard_after_forward=True, **kw)
+    body.rotary_emb.cuda()
+    fully_shard(model, reshard_after_forward=True, ignored_params={model.lm_head.weight}, **kw)
+    model.config.use_cache = False
+    return model

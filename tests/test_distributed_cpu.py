@@ -1,0 +1,104 @@
+"""Host-side logic of the multi-GPU path on CPU: the collective backend and the FSDP2 hook objects with two
+gloo ranks, the checkpoint / retention policy helpers, and the vocabulary-parallel statistics algebra."""
+import os
+import subprocess
+import sys
+import textwrap
+from pathlib import Path
+
+import pytest
+import torch
+
+ROOT = Path(__file__).resolve().parent.parent
+
+WORKER = textwrap.dedent('''
+    import sys, torch, torch.distributed as dist
+    sys.path.insert(0, r"%s")
+    from qwen3_triton.runtime.collectives import NcclCollectives, TritonCollectives
+    from qwen3_triton.runtime.fsdp import TritonAllGather, TritonReduceScatter
+    dist.init_process_group("gloo")
+    r, w = dist.get_rank(), dist.get_world_size()
+    comm = NcclCollectives()
+    assert TritonCollectives is NcclCollectives and comm.world == 2
+    # all-gather: every coordinate against the expected value, several sizes and dtypes
+    for dtype in (torch.bfloat16, torch.float32, torch.int64):
+        for n in (1, 7, 1031):
+            src = (torch.arange(n) + 1000 * r).to(dtype)
+            out = torch.empty(w * n, dtype=dtype)
+            comm.all_gather(out, src)
+            exp = torch.cat([(torch.arange(n) + 1000 * k).to(dtype) for k in range(w)])
+            assert torch.equal(out, exp), (dtype, n)
+    # reduce-scatter avg / sum in fp32
+    for op in ("avg", "sum"):
+        src = torch.arange(8, dtype=torch.float32) * (r + 1)
+        out = torch.empty(4)
+        comm.reduce_scatter(out, src, op)
+        full = torch.arange(8, dtype=torch.float32) * 3 / (2 if op == "avg" else 1)
+        assert torch.allclose(out, full.view(2, 4)[r]), op
+    t = torch.tensor([float(r), 5.0 - r]); comm.all_reduce(t, "max"); assert t.tolist() == [1.0, 5.0]
+    a = torch.arange(4.) + 10 * r; b = torch.empty(4); comm.all_to_all(b, a)
+    assert b.tolist() == [0. + 2 * r, 1. + 2 * r, 10. + 2 * r, 11. + 2 * r]
+    # FSDP2 hook protocol
+    ag, rs = TritonAllGather(comm), TritonReduceScatter(comm)
+    buf = ag.allocate((6,), dtype=torch.bfloat16, device=torch.device("cpu"))
+    ag(buf, torch.full((3,), float(r), dtype=torch.bfloat16), dist.group.WORLD)
+    assert buf.tolist() == [0, 0, 0, 1, 1, 1] and ag.calls == 1
+    out = torch.empty(2); rs(out, torch.ones(4) * (r + 1), dist.group.WORLD, dist.ReduceOp.AVG)
+    assert out.tolist() == [1.5, 1.5]
+    for bad in (lambda: ag(buf, buf[:3], dist.group.WORLD, async_op=True),
+                lambda: rs(out, torch.ones(4), dist.group.WORLD, dist.ReduceOp.MAX),
+                lambda: comm.all_gather(torch.empty(5), torch.ones(2)),
+                lambda: comm.reduce_scatter(torch.empty(2), torch.ones(4), "median")):
+        try:
+            bad(); raise SystemExit("expected ValueError")
+        except ValueError:
+            pass
+    rep = comm.report(); assert rep["calls"]["gather"] == 10 and rep["world"] == 2
+    comm.close()
+    try:
+        comm.barrier(); raise SystemExit("closed communicator must refuse")
+    except RuntimeError:
+        pass
+    dist.barrier(); dist.destroy_process_group(); print("rank", r, "ok")
+''') % str(ROOT / "qwen3-triton_b200")
+
+
+def test_collectives_and_fsdp_hooks_two_gloo_ranks(tmp_path):
+    script = tmp_path / "worker.py"
+    script.write_text(WORKER)
+    env = dict(os.environ, OMP_NUM_THREADS="1")
+    res = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2",
+                          "--master-addr", "127.0.0.1", "--master-port", "29611", str(script)], capture_output=True,
+                         text=True, timeout=240, env=env)
+    assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-3000:]
+    assert "rank 0 ok" in res.stdout and "rank 1 ok" in res.stdout
+
+
+def test_checkpoint_and_retention_policy_helpers():
+    from qwen3_triton.training.sharding import canonical_parameter_name, checkpoint_layer_indices
+    assert checkpoint_layer_indices(4, every=1) == (0, 1, 2, 3)
+    assert checkpoint_layer_indices(5, every=2) == (0, 2, 4)
+    assert checkpoint_layer_indices(3, all_layers=True) == (0, 1, 2)
+    assert checkpoint_layer_indices(3) == ()
+    with pytest.raises(ValueError):
+        checkpoint_layer_indices(3, all_layers=True, every=1)
+    with pytest.raises(ValueError):
+        checkpoint_layer_indices(0)
+    assert canonical_parameter_name('model.layers.0._checkpoint_wrapped_module.mlp.up_proj.weight') == 'model.layers.0.mlp.up_proj.weight'
+
+
+def test_vocab_parallel_statistics_algebra():
+    """The two-all-reduce scheme (MAX of shard LSEs, then SUM of exp(lse_local - max) and of the owned target
+    logit) reproduces the full cross-entropy: checked here with plain tensors standing in for the ranks."""
+    g = torch.Generator().manual_seed(0)
+    n, V, W = 9, 40, 4
+    logits, labels = torch.randn(n, V, generator=g) * 3, torch.randint(0, V, (n,), generator=g)
+    shards = logits.view(n, W, V // W)
+    lse_local = torch.logsumexp(shards, dim=2)                      # [n, W]
+    owner = labels // (V // W)
+    target = torch.stack([torch.where(owner == r, shards[torch.arange(n), r, labels % (V // W)], torch.zeros(n)) for r in range(W)], 1)
+    maximum = lse_local.max(dim=1).values                             # all-reduce MAX
+    packed = torch.stack([torch.exp(lse_local - maximum[:, None]).sum(1), target.sum(1)])   # all-reduce SUM
+    lse = maximum + torch.log(packed[0])
+    loss = (lse - packed[1]).mean()
+    torch.testing.assert_close(loss, torch.nn.functional.cross_entropy(logits, labels))
