@@ -45,6 +45,7 @@ struct GemmParams {
   int tiles_m, tiles_n, kblocks;
   uint32_t idesc;
   int a_mn, b_mn;   // operand is MN-major
+  int prefetch;     // issue L2 prefetches ahead of the smem ring
   int* status;
 };
 
@@ -155,9 +156,30 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         int mi, ni;
         tile_coords(tile, p.tiles_m, p.tiles_n, mi, ni);
         const int m0 = mi * BM, n0 = ni * (GATE_UP ? BN / 2 : BN);
+        // Operands that stream from HBM (weights of the vocabulary head, token-major operands of the weight
+        // gradient) see a longer latency than the smem ring covers: pull boxes into L2 kPrefetch k-blocks ahead.
+        auto prefetch = [&](int kb) {
+          const int k0 = kb * BK;
+          if (!p.a_mn) tma_prefetch_2d(&tmA, k0, m0);
+          else {
+#pragma unroll
+            for (int j = 0; j < BM / 64; ++j) tma_prefetch_2d(&tmA, m0 + 64 * j, k0);
+          }
+          if (GATE_UP) { tma_prefetch_2d(&tmB, k0, n0); tma_prefetch_2d(&tmB2, k0, n0); }
+          else if (!p.b_mn) tma_prefetch_2d(&tmB, k0, n0);
+          else {
+#pragma unroll
+            for (int j = 0; j < BN / 64; ++j) tma_prefetch_2d(&tmB, n0 + 64 * j, k0);
+          }
+        };
+        constexpr int kPrefetch = C::STAGES + 6;
+        if (p.prefetch) {
+          for (int kb = 0; kb < kPrefetch && kb < p.kblocks; ++kb) prefetch(kb);
+        }
         for (int kb = 0; kb < p.kblocks; ++kb, ++it) {
           const int s = it % C::STAGES;
           const uint32_t ph = (it / C::STAGES) & 1u;
+          if (p.prefetch && kb + kPrefetch < p.kblocks) prefetch(kb + kPrefetch);
           if (!mbar_wait(empty_bar(s), ph ^ 1u, abort_flag)) { ok = false; break; }
           const uint32_t a_dst = smem_base + s * C::STAGE_BYTES, b_dst = a_dst + C::A_BYTES;
           mbar_expect_tx(full_bar(s), C::STAGE_BYTES);
@@ -322,6 +344,10 @@ int launch_gemm(const Operand& A, const Operand& B, const void* b2, GemmParams& 
   p.a_mn = A.mn_major;
   p.b_mn = B.mn_major;
   p.idesc = make_idesc_f16(BM, BN, bf16, A.mn_major, B.mn_major);
+  {
+    const char* e = getenv("Q3_GEMM_PREFETCH");
+    p.prefetch = e ? atoi(e) : 0;   // measured slower on every shape tried; kept as an experiment switch
+  }
   const int64_t tiles = (int64_t)p.tiles_m * p.tiles_n;
   const int grid = (int)(tiles < sm_count() ? tiles : sm_count());
   auto kern = gemm_tc_kernel<BN, TO, GATE_UP>;
@@ -339,8 +365,9 @@ inline int pick_bn(int64_t M, int64_t N) {
   if (N <= 128) return 128;
   const int64_t sms = sm_count();
   const int64_t t256 = cdiv(M, BM) * cdiv(N, 256), t128 = cdiv(M, BM) * cdiv(N, 128);
-  // cost ~ waves * tile width
-  const int64_t c256 = cdiv(t256, sms) * 2, c128 = cdiv(t128, sms);
+  // cost ~ waves * time per tile. An N=128 tile does half the work but the tensor core is then limited by
+  // shared-memory operand bandwidth (A is re-read per 128 columns), so it costs ~0.62 of an N=256 tile.
+  const int64_t c256 = cdiv(t256, sms) * 100, c128 = cdiv(t128, sms) * 62;
   return c128 < c256 ? 128 : 256;
 }
 
