@@ -67,13 +67,27 @@ __global__ void __launch_bounds__(kEwThreads) cast_kernel(const S* __restrict__ 
     y[i] = from_f32<D>(to_f32<S>(x[i]));
 }
 
-__device__ __forceinline__ float sigmoidf_(float g) { return 1.f / (1.f + expf(-g)); }
+__device__ __forceinline__ float sigmoidf_(float g) { return __fdividef(1.f, 1.f + __expf(-g)); }
 
 template <typename T, int V>
 __global__ void __launch_bounds__(kEwThreads) swiglu_fwd_kernel(const T* __restrict__ g, const T* __restrict__ u,
                                                                 T* __restrict__ y, int64_t n) {
   const int64_t nvec = n / V;
-  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < nvec; i += (int64_t)gridDim.x * blockDim.x) {
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+  // two independent vectors per iteration: twice the bytes in flight per thread
+  for (; i + stride < nvec; i += 2 * stride) {
+    float a0[V], b0[V], a1[V], b1[V];
+    VecIO<T, V>::load(g + i * V, a0);
+    VecIO<T, V>::load(u + i * V, b0);
+    VecIO<T, V>::load(g + (i + stride) * V, a1);
+    VecIO<T, V>::load(u + (i + stride) * V, b1);
+#pragma unroll
+    for (int j = 0; j < V; ++j) { a0[j] = a0[j] * sigmoidf_(a0[j]) * b0[j]; a1[j] = a1[j] * sigmoidf_(a1[j]) * b1[j]; }
+    VecIO<T, V>::store(y + i * V, a0);
+    VecIO<T, V>::store(y + (i + stride) * V, a1);
+  }
+  for (; i < nvec; i += stride) {
     float a[V], b[V];
     VecIO<T, V>::load(g + i * V, a);
     VecIO<T, V>::load(u + i * V, b);

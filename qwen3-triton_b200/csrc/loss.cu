@@ -58,7 +58,27 @@ __global__ void __launch_bounds__(kCeThreads) ce_rows_kernel(const T* __restrict
     const int64_t physical = (row / (S - 1)) * S + row % (S - 1);
     const T* x = logits + physical * Vn;
     MaxSum acc; acc.m = -CUDART_INF_F; acc.s = 0.f;
-    for (int64_t i = threadIdx.x; i < nvec; i += blockDim.x) {
+    // four vectors per iteration: the loads are independent of the running (max, sum), so issuing them
+    // together keeps 64 B per thread in flight instead of 16 B
+    int64_t i = threadIdx.x;
+    for (; i + 3 * (int64_t)blockDim.x < nvec; i += 4 * (int64_t)blockDim.x) {
+      float v[4][V];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) VecIO<T, V>::load(x + (i + u * (int64_t)blockDim.x) * V, v[u]);
+      float vm = v[0][0];
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+#pragma unroll
+        for (int j = 0; j < V; ++j) vm = fmaxf(vm, v[u][j]);
+      const float nm = fmaxf(acc.m, vm);
+      float s = acc.s * __expf(acc.m - nm);
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+#pragma unroll
+        for (int j = 0; j < V; ++j) s += __expf(v[u][j] - nm);
+      acc.m = nm; acc.s = s;
+    }
+    for (; i < nvec; i += blockDim.x) {
       float v[V];
       VecIO<T, V>::load(x + i * V, v);
       float vm = v[0];

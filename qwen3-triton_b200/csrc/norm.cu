@@ -199,22 +199,40 @@ __global__ void __launch_bounds__(kRowThreads) norm_rope_fwd_kernel(
     const T* __restrict__ x, const T* __restrict__ w, const T* __restrict__ cs, const T* __restrict__ sn,
     T* __restrict__ y, float* __restrict__ inv, int64_t rows, int heads, int64_t seq, int D, float eps, int tpr,
     int layout) {
-  constexpr int MP = 4;
+  constexpr int MP = (V == 1) ? 4 : 1;   // vector paths: one pair per thread (D <= 512); scalar path: up to 4
   const int rpb = blockDim.x / tpr, rib = threadIdx.x / tpr, t = threadIdx.x % tpr, half = D / 2, npair = half / V;
-  for (int64_t base = (int64_t)blockIdx.x * rpb; base < rows; base += (int64_t)gridDim.x * rpb) {
+  const int64_t step = (int64_t)gridDim.x * rpb;
+  float a[MP][V], b[MP][V], na[MP][V], nb[MP][V];
+  auto load_row = [&](int64_t row, float (&a_)[MP][V], float (&b_)[MP][V]) {
+#pragma unroll
+    for (int i = 0; i < MP; ++i) {
+      const int p = t + i * tpr;
+      if (row < rows && p < npair) {
+        VecIO<T, V>::load(x + row * D + (int64_t)p * V, a_[i]);
+        VecIO<T, V>::load(x + row * D + half + (int64_t)p * V, b_[i]);
+      }
+    }
+  };
+  int64_t base = (int64_t)blockIdx.x * rpb;
+  if (base < rows) load_row(base + rib, a, b);
+  for (; base < rows; base += step) {
     const int64_t row = base + rib;
     const bool valid = row < rows;
+    if (base + step < rows) load_row(base + step + rib, na, nb);   // next row's data in flight during this row's math
     // layout 0: x is [tokens, heads, D]; layout 1: x is [batch, heads, seq, D]
     int64_t token = 0;
     if (valid) token = layout == 0 ? row / heads : (row / ((int64_t)heads * seq)) * seq + row % seq;
-    float a[MP][V], b[MP][V];
+    // table and weight loads do not depend on the row statistics: issue them before the reduction
+    float c1[MP][V], c2[MP][V], s1[MP][V], s2[MP][V];
     float ss = 0.f;
 #pragma unroll
     for (int i = 0; i < MP; ++i) {
       const int p = t + i * tpr;
       if (valid && p < npair) {
-        VecIO<T, V>::load(x + row * D + (int64_t)p * V, a[i]);
-        VecIO<T, V>::load(x + row * D + half + (int64_t)p * V, b[i]);
+        VecIO<T, V>::load(cs + token * D + (int64_t)p * V, c1[i]);
+        VecIO<T, V>::load(cs + token * D + half + (int64_t)p * V, c2[i]);
+        VecIO<T, V>::load(sn + token * D + (int64_t)p * V, s1[i]);
+        VecIO<T, V>::load(sn + token * D + half + (int64_t)p * V, s2[i]);
         if constexpr (NORM) {
 #pragma unroll
           for (int j = 0; j < V; ++j) ss += a[i][j] * a[i][j] + b[i][j] * b[i][j];
@@ -230,11 +248,7 @@ __global__ void __launch_bounds__(kRowThreads) norm_rope_fwd_kernel(
     for (int i = 0; i < MP; ++i) {
       const int p = t + i * tpr;
       if (valid && p < npair) {
-        float c1[V], c2[V], s1[V], s2[V], o1[V], o2[V];
-        VecIO<T, V>::load(cs + token * D + (int64_t)p * V, c1);
-        VecIO<T, V>::load(cs + token * D + half + (int64_t)p * V, c2);
-        VecIO<T, V>::load(sn + token * D + (int64_t)p * V, s1);
-        VecIO<T, V>::load(sn + token * D + half + (int64_t)p * V, s2);
+        float o1[V], o2[V];
         if constexpr (NORM) {
           float w1[V], w2[V];
           VecIO<T, V>::load(w + (int64_t)p * V, w1);
@@ -244,8 +258,8 @@ __global__ void __launch_bounds__(kRowThreads) norm_rope_fwd_kernel(
         }
 #pragma unroll
         for (int j = 0; j < V; ++j) {
-          o1[j] = a[i][j] * c1[j] - b[i][j] * s1[j];
-          o2[j] = b[i][j] * c2[j] + a[i][j] * s2[j];
+          o1[j] = a[i][j] * c1[i][j] - b[i][j] * s1[i][j];
+          o2[j] = b[i][j] * c2[i][j] + a[i][j] * s2[i][j];
         }
         VecIO<T, V>::store(y + row * D + (int64_t)p * V, o1);
         VecIO<T, V>::store(y + row * D + half + (int64_t)p * V, o2);
@@ -254,6 +268,10 @@ __global__ void __launch_bounds__(kRowThreads) norm_rope_fwd_kernel(
     if constexpr (NORM) {
       if (valid && t == 0) inv[row] = r;
     }
+#pragma unroll
+    for (int i = 0; i < MP; ++i)
+#pragma unroll
+      for (int j = 0; j < V; ++j) { a[i][j] = na[i][j]; b[i][j] = nb[i][j]; }
   }
 }
 
@@ -264,7 +282,7 @@ __global__ void __launch_bounds__(kRowThreads) norm_rope_bwd_kernel(
     const T* __restrict__ x, const T* __restrict__ w, const T* __restrict__ cs, const T* __restrict__ sn,
     const T* __restrict__ dy, const float* __restrict__ inv, T* __restrict__ dx, float* __restrict__ partial,
     int64_t rows, int heads, int64_t seq, int D, int tpr, int layout) {
-  constexpr int MP = 4;
+  constexpr int MP = (V == 1) ? 4 : 1;   // vector paths: one pair per thread (D <= 512); scalar path: up to 4
   extern __shared__ float comb[];  // [rpb][D]
   const int rpb = blockDim.x / tpr, rib = threadIdx.x / tpr, t = threadIdx.x % tpr, half = D / 2, npair = half / V;
   float acc1[MP][V], acc2[MP][V];
@@ -273,12 +291,31 @@ __global__ void __launch_bounds__(kRowThreads) norm_rope_bwd_kernel(
 #pragma unroll
     for (int j = 0; j < V; ++j) { acc1[i][j] = 0.f; acc2[i][j] = 0.f; }
 
-  for (int64_t base = (int64_t)blockIdx.x * rpb; base < rows; base += (int64_t)gridDim.x * rpb) {
+  const int64_t step = (int64_t)gridDim.x * rpb;
+  float g1[MP][V], g2[MP][V], x1[MP][V], x2[MP][V], ng1[MP][V], ng2[MP][V], nx1[MP][V], nx2[MP][V];
+  auto load_row = [&](int64_t row, float (&a1)[MP][V], float (&a2)[MP][V], float (&b1)[MP][V], float (&b2)[MP][V]) {
+#pragma unroll
+    for (int i = 0; i < MP; ++i) {
+      const int p = t + i * tpr;
+      if (row < rows && p < npair) {
+        VecIO<T, V>::load(dy + row * D + (int64_t)p * V, a1[i]);
+        VecIO<T, V>::load(dy + row * D + half + (int64_t)p * V, a2[i]);
+        if constexpr (NORM) {
+          VecIO<T, V>::load(x + row * D + (int64_t)p * V, b1[i]);
+          VecIO<T, V>::load(x + row * D + half + (int64_t)p * V, b2[i]);
+        }
+      }
+    }
+  };
+  int64_t base = (int64_t)blockIdx.x * rpb;
+  if (base < rows) load_row(base + rib, g1, g2, x1, x2);
+  for (; base < rows; base += step) {
     const int64_t row = base + rib;
     const bool valid = row < rows;
+    if (base + step < rows) load_row(base + step + rib, ng1, ng2, nx1, nx2);
     int64_t token = 0;
     if (valid) token = layout == 0 ? row / heads : (row / ((int64_t)heads * seq)) * seq + row % seq;
-    float d1[MP][V], d2[MP][V], x1[MP][V], x2[MP][V];
+    float d1[MP][V], d2[MP][V];
     float s = 0.f;
     float r = 1.f;
     if constexpr (NORM) r = valid ? inv[row] : 0.f;
@@ -286,22 +323,18 @@ __global__ void __launch_bounds__(kRowThreads) norm_rope_bwd_kernel(
     for (int i = 0; i < MP; ++i) {
       const int p = t + i * tpr;
       if (valid && p < npair) {
-        float g1[V], g2[V], c1[V], c2[V], s1[V], s2[V];
-        VecIO<T, V>::load(dy + row * D + (int64_t)p * V, g1);
-        VecIO<T, V>::load(dy + row * D + half + (int64_t)p * V, g2);
+        float c1[V], c2[V], s1[V], s2[V];
         VecIO<T, V>::load(cs + token * D + (int64_t)p * V, c1);
         VecIO<T, V>::load(cs + token * D + half + (int64_t)p * V, c2);
         VecIO<T, V>::load(sn + token * D + (int64_t)p * V, s1);
         VecIO<T, V>::load(sn + token * D + half + (int64_t)p * V, s2);
 #pragma unroll
         for (int j = 0; j < V; ++j) {
-          d1[i][j] = g1[j] * c1[j] + g2[j] * s2[j];
-          d2[i][j] = g2[j] * c2[j] - g1[j] * s1[j];
+          d1[i][j] = g1[i][j] * c1[j] + g2[i][j] * s2[j];
+          d2[i][j] = g2[i][j] * c2[j] - g1[i][j] * s1[j];
         }
         if constexpr (NORM) {
           float w1[V], w2[V];
-          VecIO<T, V>::load(x + row * D + (int64_t)p * V, x1[i]);
-          VecIO<T, V>::load(x + row * D + half + (int64_t)p * V, x2[i]);
           VecIO<T, V>::load(w + (int64_t)p * V, w1);
           VecIO<T, V>::load(w + half + (int64_t)p * V, w2);
 #pragma unroll
@@ -335,6 +368,13 @@ __global__ void __launch_bounds__(kRowThreads) norm_rope_bwd_kernel(
         VecIO<T, V>::store(dx + row * D + half + (int64_t)p * V, d2[i]);
       }
     }
+#pragma unroll
+    for (int i = 0; i < MP; ++i)
+#pragma unroll
+      for (int j = 0; j < V; ++j) {
+        g1[i][j] = ng1[i][j]; g2[i][j] = ng2[i][j];
+        if constexpr (NORM) { x1[i][j] = nx1[i][j]; x2[i][j] = nx2[i][j]; }
+      }
   }
   if constexpr (NORM) {
     __syncthreads();
@@ -447,7 +487,7 @@ int norm_rope_fwd_launch(const void* x, const void* w, const void* cs, const voi
   const int64_t rows = batch * seq * heads, half = D / 2;
   const bool vec = (half % VF == 0) && aligned16(x) && aligned16(cs) && aligned16(sn) && aligned16(y) && (!NORM || aligned16(w));
   if (vec) {
-    RowPlan p = plan_rows(rows, (int)(half / VF), 1, 4, 32, 16);
+    RowPlan p = plan_rows(rows, (int)(half / VF), 1, 1, 32, 16);
     if (p.tpr < 0 || p.tpr > 32) return Q3_ERR_SHAPE;
     norm_rope_fwd_kernel<T, VF, NORM><<<p.grid, p.block, 0, st>>>((const T*)x, (const T*)w, (const T*)cs, (const T*)sn,
                                                                   (T*)y, inv, rows, (int)heads, seq, (int)D, eps, p.tpr, layout);
@@ -468,7 +508,7 @@ int norm_rope_bwd_launch(const void* x, const void* w, const void* cs, const voi
   const int64_t rows = batch * seq * heads, half = D / 2;
   const bool vec = (half % VF == 0) && aligned16(cs) && aligned16(sn) && aligned16(dy) && aligned16(dx) &&
                    (!NORM || (aligned16(x) && aligned16(w)));
-  RowPlan p = vec ? plan_rows(rows, (int)(half / VF), 1, 4, 32, kPartialRowsPerSm * 2)
+  RowPlan p = vec ? plan_rows(rows, (int)(half / VF), 1, 1, 32, kPartialRowsPerSm * 2)
                   : plan_rows(rows, (int)half, 1, 4, 32, kPartialRowsPerSm * 2);
   if (p.tpr < 0 || p.tpr > 32) return Q3_ERR_SHAPE;
   if (NORM && (ws == nullptr || ws_bytes < (int64_t)p.grid * D * 4)) return Q3_ERR_WORKSPACE;
