@@ -178,9 +178,9 @@ def build_single_gpu(cfg, device):
     from qwen3_triton.runtime.mixed_precision import MasterWeights
     torch.manual_seed(20261114)
     with torch.device(device):
-        model = model_for_variant(cfg, "triton_optimized")
+        model = model_for_variant(cfg, os.environ.get("Q3_BENCH_VARIANT", "b200_fused"))
     model.to(device)   # buffers created on the CPU on purpose (rotary frequencies) move here
-    masters = MasterWeights(model)
+    masters = MasterWeights(model).fuse_into_optimizer()
     opt = TritonAdamW(masters.parameters(), lr=1e-4, betas=(0.9, 0.95), weight_decay=0.1)
     return model, masters, opt
 
@@ -315,7 +315,7 @@ def run_fsdp(args):
     cfg = slice_config(layers)
     torch.manual_seed(20261114)            # same weights on every rank
     with torch.device(device):
-        model = model_for_variant(cfg, "triton_optimized")
+        model = model_for_variant(cfg, os.environ.get("Q3_BENCH_VARIANT", "b200_fused"))
     comm = NcclCollectives()
     model = shard_vocab_loss_model(model, keep_full_layers=layers, checkpoint_every=1,
                                    skip_embedding_backward_gather=True, fused_vocab_dw=True, communication=None)

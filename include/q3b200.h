@@ -201,6 +201,15 @@ int q3_vce_accumulate(const void* partial, int partial_dtype, float* out, int64_
 int q3_adamw_multi(const int64_t* meta, float* coeff, int64_t n_tensors, int64_t total_blocks, int block_elems,
                    double lr, double beta1, double beta2, double weight_decay, double eps, q3_stream_t stream);
 
+/* Mixed-precision form of q3_adamw_multi for a single-GPU fp32-master / bf16-working setup: table int64 [n][9] =
+ * {param fp32, grad fp32 or 0, exp_avg, exp_avg_sq, step, numel, first_block, grad lowp or 0, working-copy lowp or 0}.
+ * When the low-precision gradient pointer is set it is read directly (no fp32 staging copy); when the working-copy
+ * pointer is set the updated parameter is also written there in `lowp_dtype` (bf16/fp16). Same update math.
+ * Fuses the reference's cast passes (qwen3_triton/runtime/ops.py:53-58,193-202) into runtime/adamw.py:34-61. */
+int q3_adamw_multi_mp(const int64_t* meta, float* coeff, int64_t n_tensors, int64_t total_blocks, int block_elems,
+                      int lowp_dtype, double lr, double beta1, double beta2, double weight_decay, double eps,
+                      q3_stream_t stream);
+
 /* ---- GEMM ----------------------------------------------------------------------------------- */
 
 /* C[M,N] (contiguous, out_dtype) = A * B with A(m,k) at a[m*a_sm + k*a_sk] and B(k,n) at b[k*b_sk + n*b_sn],
@@ -238,6 +247,16 @@ int64_t q3_attn_bwd_workspace_bytes(int64_t B, int64_t Hq, int64_t Hkv, int64_t 
 int q3_attn_bwd(const void* q, const void* k, const void* v, const void* out, const void* dout, const float* lse,
                 void* dq, void* dk, void* dv, void* workspace, int64_t workspace_bytes, int64_t B, int64_t Hq,
                 int64_t Hkv, int64_t S, int64_t D, double scale, int dtype, int* status, q3_stream_t stream);
+
+/* Token-major variants of the two calls above: q/out/dout/dq [B,S,Hq,128], k/v/dk/dv [B,S,Hkv,128] - what the
+ * q/k/v projections write and the output projection reads - so no transpose copies surround attention
+ * (the reference makes four per layer and direction: qwen3_triton/components.py:29,31). Tensor-core path only:
+ * Q3_ERR_SHAPE unless q3_attn_path() is 1. lse stays [B,Hq,S]. */
+int q3_attn_fwd_bshd(const void* q, const void* k, const void* v, void* out, float* lse, int64_t B, int64_t S,
+                     int64_t Hq, int64_t Hkv, int64_t D, double scale, int dtype, int* status, q3_stream_t stream);
+int q3_attn_bwd_bshd(const void* q, const void* k, const void* v, const void* out, const void* dout, const float* lse,
+                     void* dq, void* dk, void* dv, void* workspace, int64_t workspace_bytes, int64_t B, int64_t S,
+                     int64_t Hq, int64_t Hkv, int64_t D, double scale, int dtype, int* status, q3_stream_t stream);
 
 /* 1 if the tensor-core attention kernels run for these arguments, else 0. */
 int q3_attn_path(const void* q, const void* k, const void* v, const void* out, int64_t D, int dtype);

@@ -88,9 +88,112 @@ __global__ void __launch_bounds__(256) adamw_update_kernel(const int64_t* __rest
   }
 }
 
+// Mixed-precision variant: the gradient may arrive in bf16/fp16 (read directly, no fp32 staging copy) and the
+// updated parameter may also be written as a bf16/fp16 working copy, so a single-GPU mixed-precision step needs
+// neither a gradient-upcast pass nor a master->working cast pass. Table: int64[rows][9] =
+// {p, g_fp32 (or 0), m, v, step, numel, first_block, g_lowp (or 0), p_lowp (or 0)}.
+template <typename L>
+__global__ void __launch_bounds__(256, 4) adamw_update_mp_kernel(const int64_t* __restrict__ meta,
+                                                              const float* __restrict__ coeff, int64_t rows, double lr,
+                                                              double b1, double b2, double decay, double eps,
+                                                              int block_elems) {
+  const int64_t blk = blockIdx.x;
+  int64_t lo = 0, hi = rows;
+  while (lo + 1 < hi) {
+    const int64_t mid = (lo + hi) >> 1;
+    if (meta[mid * 9 + 6] <= blk) lo = mid; else hi = mid;
+  }
+  const int64_t r = lo;
+  float* __restrict__ p = reinterpret_cast<float*>(meta[r * 9 + 0]);
+  const float* __restrict__ g32 = reinterpret_cast<const float*>(meta[r * 9 + 1]);
+  float* __restrict__ m = reinterpret_cast<float*>(meta[r * 9 + 2]);
+  float* __restrict__ v = reinterpret_cast<float*>(meta[r * 9 + 3]);
+  const L* __restrict__ glo = reinterpret_cast<const L*>(meta[r * 9 + 7]);
+  L* __restrict__ plo = reinterpret_cast<L*>(meta[r * 9 + 8]);
+  const int64_t n = meta[r * 9 + 5];
+  const int64_t begin = (blk - meta[r * 9 + 6]) * (int64_t)block_elems;
+  const int64_t end = begin + block_elems < n ? begin + block_elems : n;
+  const float bc2 = coeff[r * 3 + 1], size = coeff[r * 3 + 2];
+  const uintptr_t bits = reinterpret_cast<uintptr_t>(p) | reinterpret_cast<uintptr_t>(m) | reinterpret_cast<uintptr_t>(v) |
+                         reinterpret_cast<uintptr_t>(g32) | reinterpret_cast<uintptr_t>(glo) |
+                         reinterpret_cast<uintptr_t>(plo);
+  if ((bits & 15u) == 0) {
+    // 8 elements per thread per iteration: 2 x 16-byte accesses on each fp32 array, one on each 16-bit array
+    const int64_t vend = begin + ((end - begin) & ~(int64_t)7);
+    for (int64_t i = begin + threadIdx.x * 8; i < vend; i += blockDim.x * 8) {
+      float pp[8], mm[8], vv[8], gg[8];
+      *reinterpret_cast<float4*>(pp) = *reinterpret_cast<const float4*>(p + i);
+      *reinterpret_cast<float4*>(pp + 4) = *reinterpret_cast<const float4*>(p + i + 4);
+      *reinterpret_cast<float4*>(mm) = *reinterpret_cast<const float4*>(m + i);
+      *reinterpret_cast<float4*>(mm + 4) = *reinterpret_cast<const float4*>(m + i + 4);
+      *reinterpret_cast<float4*>(vv) = *reinterpret_cast<const float4*>(v + i);
+      *reinterpret_cast<float4*>(vv + 4) = *reinterpret_cast<const float4*>(v + i + 4);
+      if (glo != nullptr) {
+        VecIO<L, 8>::load(glo + i, gg);
+      } else {
+        *reinterpret_cast<float4*>(gg) = *reinterpret_cast<const float4*>(g32 + i);
+        *reinterpret_cast<float4*>(gg + 4) = *reinterpret_cast<const float4*>(g32 + i + 4);
+      }
+#pragma unroll
+      for (int e = 0; e < 8; ++e) adamw_one(pp[e], gg[e], mm[e], vv[e], lr, b1, b2, decay, eps, bc2, size);
+      *reinterpret_cast<float4*>(p + i) = *reinterpret_cast<float4*>(pp);
+      *reinterpret_cast<float4*>(p + i + 4) = *reinterpret_cast<float4*>(pp + 4);
+      *reinterpret_cast<float4*>(m + i) = *reinterpret_cast<float4*>(mm);
+      *reinterpret_cast<float4*>(m + i + 4) = *reinterpret_cast<float4*>(mm + 4);
+      *reinterpret_cast<float4*>(v + i) = *reinterpret_cast<float4*>(vv);
+      *reinterpret_cast<float4*>(v + i + 4) = *reinterpret_cast<float4*>(vv + 4);
+      if (plo != nullptr) VecIO<L, 8>::store(plo + i, pp);
+    }
+    for (int64_t i = vend + threadIdx.x; i < end; i += blockDim.x) {
+      float pp = p[i], mm = m[i], vv = v[i];
+      adamw_one(pp, glo ? to_f32<L>(glo[i]) : g32[i], mm, vv, lr, b1, b2, decay, eps, bc2, size);
+      p[i] = pp; m[i] = mm; v[i] = vv;
+      if (plo) plo[i] = from_f32<L>(pp);
+    }
+  } else {
+    for (int64_t i = begin + threadIdx.x; i < end; i += blockDim.x) {
+      float pp = p[i], mm = m[i], vv = v[i];
+      adamw_one(pp, glo ? to_f32<L>(glo[i]) : g32[i], mm, vv, lr, b1, b2, decay, eps, bc2, size);
+      p[i] = pp; m[i] = mm; v[i] = vv;
+      if (plo) plo[i] = from_f32<L>(pp);
+    }
+  }
+}
+
+__global__ void adamw_prepare9_kernel(const int64_t* __restrict__ meta, float* __restrict__ coeff, int64_t rows,
+                                      double lr, double b1, double b2) {
+  const int64_t r = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+  if (r >= rows) return;
+  float* step_ptr = reinterpret_cast<float*>(meta[r * 9 + 4]);
+  const float step = *step_ptr + 1.f;
+  *step_ptr = step;
+  const float bc1 = (float)(1.0 - pow(b1, (double)step));
+  coeff[r * 3 + 0] = bc1;
+  coeff[r * 3 + 1] = (float)sqrt(1.0 - pow(b2, (double)step));
+  coeff[r * 3 + 2] = (float)(lr / (double)bc1);
+}
+
 }  // namespace q3
 
 using namespace q3;
+
+extern "C" int q3_adamw_multi_mp(const int64_t* meta, float* coeff, int64_t n_tensors, int64_t total_blocks,
+                                 int block_elems, int lowp_dtype, double lr, double beta1, double beta2,
+                                 double weight_decay, double eps, q3_stream_t stream) {
+  if (!meta || !coeff) return Q3_ERR_ARG;
+  if (n_tensors < 1 || total_blocks < 1 || total_blocks > 2147483647LL || block_elems < 256 || (block_elems & 7))
+    return Q3_ERR_SHAPE;
+  if (lowp_dtype != Q3_BF16 && lowp_dtype != Q3_F16) return Q3_ERR_DTYPE;
+  cudaStream_t st = (cudaStream_t)stream;
+  adamw_prepare9_kernel<<<(int)cdiv(n_tensors, 128), 128, 0, st>>>(meta, coeff, n_tensors, lr, beta1, beta2);
+  if (lowp_dtype == Q3_BF16)
+    adamw_update_mp_kernel<__nv_bfloat16><<<(unsigned)total_blocks, 256, 0, st>>>(meta, coeff, n_tensors, lr, beta1, beta2,
+                                                                                   weight_decay, eps, block_elems);
+  else
+    adamw_update_mp_kernel<__half><<<(unsigned)total_blocks, 256, 0, st>>>(meta, coeff, n_tensors, lr, beta1, beta2,
+                                                                            weight_decay, eps, block_elems);
+  return launch_status();
+}
 
 extern "C" int q3_adamw_multi(const int64_t* meta, float* coeff, int64_t n_tensors, int64_t total_blocks,
                               int block_elems, double lr, double beta1, double beta2, double weight_decay, double eps,

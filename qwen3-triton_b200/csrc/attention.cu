@@ -14,10 +14,12 @@ int attn_bwd_simt(const void* q, const void* k, const void* v, const void* dout,
                   void* dq, void* dk, void* dv, int64_t B, int64_t Hq, int64_t Hkv, int64_t S, int64_t D, float scale,
                   int dtype, cudaStream_t st);
 int attn_fwd_tc(const void* q, const void* k, const void* v, void* out, float* lse, int64_t B, int64_t Hq, int64_t Hkv,
-                int64_t S, float scale, int dtype, int* status, cudaStream_t st);
+                int64_t S, float scale, int dtype, int layout, int* status, cudaStream_t st);
 int attn_bwd_tc(const void* q, const void* k, const void* v, const void* dout, const float* lse, const float* delta,
                 void* dq, void* dk, void* dv, int64_t B, int64_t Hq, int64_t Hkv, int64_t S, float scale, int dtype,
-                int* status, cudaStream_t st);
+                int layout, int* status, cudaStream_t st);
+int attn_delta_layout(const void* out, const void* dout, float* delta, int64_t B, int64_t H, int64_t S, int64_t D,
+                      int layout, int dtype, cudaStream_t st);
 bool attn_tc_available();
 
 static int check_shape(int64_t B, int64_t Hq, int64_t Hkv, int64_t S, int64_t D) {
@@ -46,7 +48,7 @@ extern "C" int q3_attn_fwd(const void* q, const void* k, const void* v, void* ou
   if (rc != Q3_OK) return rc;
   if (dtype < Q3_F32 || dtype > Q3_F16) return Q3_ERR_DTYPE;
   cudaStream_t st = (cudaStream_t)stream;
-  if (tc_eligible(q, k, v, out, D, dtype)) return attn_fwd_tc(q, k, v, out, lse, B, Hq, Hkv, S, (float)scale, dtype, status, st);
+  if (tc_eligible(q, k, v, out, D, dtype)) return attn_fwd_tc(q, k, v, out, lse, B, Hq, Hkv, S, (float)scale, dtype, 0, status, st);
   return attn_fwd_simt(q, k, v, out, lse, B, Hq, Hkv, S, D, (float)scale, dtype, st);
 }
 
@@ -69,6 +71,35 @@ extern "C" int q3_attn_bwd(const void* q, const void* k, const void* v, const vo
   rc = attn_delta(out, dout, delta, B * Hq * S, D, dtype, st);
   if (rc != Q3_OK) return rc;
   if (tc_eligible(q, k, v, dout, D, dtype) && aligned16(dq) && aligned16(dk) && aligned16(dv))
-    return attn_bwd_tc(q, k, v, dout, lse, delta, dq, dk, dv, B, Hq, Hkv, S, (float)scale, dtype, status, st);
+    return attn_bwd_tc(q, k, v, dout, lse, delta, dq, dk, dv, B, Hq, Hkv, S, (float)scale, dtype, 0, status, st);
   return attn_bwd_simt(q, k, v, dout, lse, delta, dq, dk, dv, B, Hq, Hkv, S, D, (float)scale, dtype, st);
+}
+
+// Token-major variants: q/out/dout/dq are [B, S, Hq, 128] and k/v/dk/dv [B, S, Hkv, 128] - the layout the
+// q/k/v projections produce and the output projection consumes - so a decoder layer needs no transpose
+// copies around attention. Tensor-core path only (bf16/fp16, head_dim 128); lse stays [B, Hq, S].
+extern "C" int q3_attn_fwd_bshd(const void* q, const void* k, const void* v, void* out, float* lse, int64_t B,
+                                int64_t S, int64_t Hq, int64_t Hkv, int64_t D, double scale, int dtype, int* status,
+                                q3_stream_t stream) {
+  if (!q || !k || !v || !out || !lse) return Q3_ERR_ARG;
+  int rc = check_shape(B, Hq, Hkv, S, D);
+  if (rc != Q3_OK) return rc;
+  if (!tc_eligible(q, k, v, out, D, dtype)) return Q3_ERR_SHAPE;
+  return attn_fwd_tc(q, k, v, out, lse, B, Hq, Hkv, S, (float)scale, dtype, 1, status, (cudaStream_t)stream);
+}
+
+extern "C" int q3_attn_bwd_bshd(const void* q, const void* k, const void* v, const void* out, const void* dout,
+                                const float* lse, void* dq, void* dk, void* dv, void* workspace,
+                                int64_t workspace_bytes, int64_t B, int64_t S, int64_t Hq, int64_t Hkv, int64_t D,
+                                double scale, int dtype, int* status, q3_stream_t stream) {
+  if (!q || !k || !v || !out || !dout || !lse || !dq || !dk || !dv) return Q3_ERR_ARG;
+  int rc = check_shape(B, Hq, Hkv, S, D);
+  if (rc != Q3_OK) return rc;
+  if (!tc_eligible(q, k, v, dout, D, dtype) || !aligned16(dq) || !aligned16(dk) || !aligned16(dv)) return Q3_ERR_SHAPE;
+  if (!workspace || workspace_bytes < q3_attn_bwd_workspace_bytes(B, Hq, Hkv, S, D)) return Q3_ERR_WORKSPACE;
+  cudaStream_t st = (cudaStream_t)stream;
+  float* delta = (float*)workspace;
+  rc = attn_delta_layout(out, dout, delta, B, Hq, S, D, 1, dtype, st);
+  if (rc != Q3_OK) return rc;
+  return attn_bwd_tc(q, k, v, dout, lse, delta, dq, dk, dv, B, Hq, Hkv, S, (float)scale, dtype, 1, status, st);
 }

@@ -338,6 +338,33 @@ int attn_fwd_simt(const void* q, const void* k, const void* v, void* out, float*
   return launch_status();
 }
 
+// delta for token-major tensors [B, S, H, D]: input row (b, s, h) -> delta[(b*H + h)*S + s]
+template <typename T>
+__global__ void attn_delta_bshd_kernel(const T* __restrict__ o, const T* __restrict__ dout, float* __restrict__ delta,
+                                       int64_t rows, int H, int S, int D) {
+  const int lane = threadIdx.x & 31;
+  const int64_t row = blockIdx.x * (int64_t)(blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  float s = 0.f;
+  for (int c = lane; c < D; c += 32) s += to_f32<T>(o[row * D + c]) * to_f32<T>(dout[row * D + c]);
+  s = warp_sum(s);
+  if (lane == 0) {
+    const int64_t h = row % H, bs = row / H, sidx = bs % S, b = bs / S;
+    delta[(b * H + h) * S + sidx] = s;
+  }
+}
+
+int attn_delta_layout(const void* out, const void* dout, float* delta, int64_t B, int64_t H, int64_t S, int64_t D,
+                      int layout, int dtype, cudaStream_t st) {
+  const int64_t rows = B * H * S;
+  if (layout == 0) {
+    Q3_DISPATCH_FLOAT(dtype, T, (attn_delta_kernel<T><<<(unsigned)cdiv(rows, 8), 256, 0, st>>>((const T*)out, (const T*)dout, delta, rows, (int)D)));
+  } else {
+    Q3_DISPATCH_FLOAT(dtype, T, (attn_delta_bshd_kernel<T><<<(unsigned)cdiv(rows, 8), 256, 0, st>>>((const T*)out, (const T*)dout, delta, rows, (int)H, (int)S, (int)D)));
+  }
+  return launch_status();
+}
+
 int attn_delta(const void* out, const void* dout, float* delta, int64_t rows, int64_t D, int dtype, cudaStream_t st) {
   Q3_DISPATCH_FLOAT(dtype, T, (attn_delta_kernel<T><<<(unsigned)cdiv(rows, 8), 256, 0, st>>>((const T*)out, (const T*)dout, delta, rows, (int)D)));
   return launch_status();

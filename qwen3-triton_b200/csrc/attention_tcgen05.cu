@@ -42,6 +42,7 @@ struct AttnParams {
   void* out;
   float* lse;
   int Hq, Hkv, S;
+  int64_t q_ss, q_hs, q_bs;  // element strides of q/out over (sequence, head, batch)
   float scale_log2;  // softmax scale * log2(e)
   uint32_t idesc_qk; // A K-major, B K-major, N = 128
   uint32_t idesc_pv; // A K-major, B MN-major, N = 128
@@ -144,20 +145,20 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   if (warp == 0) {
     if (lane == 0) {
       mbar_expect_tx(q_full, TILE_BYTES);
-      tma_load_3d(q_s, &tmQ, 0, qt * TILE, bh, q_full);
-      tma_load_3d(q_s + HALF_BYTES, &tmQ, 64, qt * TILE, bh, q_full);
+      tma_load_4d(q_s, &tmQ, 0, qt * TILE, bh % p.Hq, bh / p.Hq, q_full);
+      tma_load_4d(q_s + HALF_BYTES, &tmQ, 64, qt * TILE, bh % p.Hq, bh / p.Hq, q_full);
       int issued = 0;
       for (int j = 0; j < ntiles; ++j) {
         const int s = j & 1;
         const uint32_t ph = (j >> 1) & 1u;
         if (!mbar_wait(k_empty(s), ph ^ 1u, abort_flag)) break;
         mbar_expect_tx(k_full(s), TILE_BYTES);
-        tma_load_3d(k_s + s * TILE_BYTES, &tmK, 0, j * TILE, bkv, k_full(s));
-        tma_load_3d(k_s + s * TILE_BYTES + HALF_BYTES, &tmK, 64, j * TILE, bkv, k_full(s));
+        tma_load_4d(k_s + s * TILE_BYTES, &tmK, 0, j * TILE, bkv % p.Hkv, bkv / p.Hkv, k_full(s));
+        tma_load_4d(k_s + s * TILE_BYTES + HALF_BYTES, &tmK, 64, j * TILE, bkv % p.Hkv, bkv / p.Hkv, k_full(s));
         if (!mbar_wait(v_empty(s), ph ^ 1u, abort_flag)) { mbar_wait_drain(k_full(s), ph); break; }
         mbar_expect_tx(v_full(s), TILE_BYTES);
-        tma_load_3d(v_s + s * TILE_BYTES, &tmV, 0, j * TILE, bkv, v_full(s));
-        tma_load_3d(v_s + s * TILE_BYTES + HALF_BYTES, &tmV, 64, j * TILE, bkv, v_full(s));
+        tma_load_4d(v_s + s * TILE_BYTES, &tmV, 0, j * TILE, bkv % p.Hkv, bkv / p.Hkv, v_full(s));
+        tma_load_4d(v_s + s * TILE_BYTES + HALF_BYTES, &tmV, 64, j * TILE, bkv % p.Hkv, bkv / p.Hkv, v_full(s));
         issued = j + 1;
       }
       // make sure nothing is still landing in shared memory when the CTA exits
@@ -270,7 +271,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       const uint32_t o_addr = lane_addr + 256 + ((ntiles - 1) & 1) * 128;
       const float inv = 1.f / l;
       const int qi = qt * TILE + row;
-      T* orow = reinterpret_cast<T*>(p.out) + ((int64_t)bh * p.S + qi) * AD;
+      T* orow = reinterpret_cast<T*>(p.out) + (int64_t)b * p.q_bs + (int64_t)h * p.q_hs + (int64_t)qi * p.q_ss;
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
         uint32_t r[32];
@@ -310,6 +311,7 @@ struct AttnBwdParams {
   void* dk;
   void* dv;
   int Hq, Hkv, S;
+  int64_t q_ss, q_hs, q_bs, k_ss, k_hs, k_bs;  // element strides over (sequence, head, batch)
   float scale, scale_log2;
   uint32_t idesc_kk128;  // A K-major, B K-major, N = 128
   uint32_t idesc_kk64;   // A K-major, B K-major, N = 64
@@ -383,22 +385,22 @@ attn_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
   if (warp == 0) {
     if (lane == 0) {
       mbar_expect_tx(q_full, 2 * TILE_BYTES);
-      tma_load_3d(q_s, &tmQ, 0, qt * TILE, bh, q_full);
-      tma_load_3d(q_s + HALF_BYTES, &tmQ, 64, qt * TILE, bh, q_full);
-      tma_load_3d(do_s, &tmDO, 0, qt * TILE, bh, q_full);
-      tma_load_3d(do_s + HALF_BYTES, &tmDO, 64, qt * TILE, bh, q_full);
+      tma_load_4d(q_s, &tmQ, 0, qt * TILE, bh % p.Hq, bh / p.Hq, q_full);
+      tma_load_4d(q_s + HALF_BYTES, &tmQ, 64, qt * TILE, bh % p.Hq, bh / p.Hq, q_full);
+      tma_load_4d(do_s, &tmDO, 0, qt * TILE, bh % p.Hq, bh / p.Hq, q_full);
+      tma_load_4d(do_s + HALF_BYTES, &tmDO, 64, qt * TILE, bh % p.Hq, bh / p.Hq, q_full);
       int issued = 0;
       for (int j = 0; j < ntiles; ++j) {
         const int s = j & 1;
         const uint32_t ph = (j >> 1) & 1u;
         if (!mbar_wait(k_empty(s), ph ^ 1u, abort_flag)) break;
         mbar_expect_tx(k_full(s), TILE_BYTES);
-        tma_load_3d(k_s + s * TILE_BYTES, &tmK, 0, j * TILE, bkv, k_full(s));
-        tma_load_3d(k_s + s * TILE_BYTES + HALF_BYTES, &tmK, 64, j * TILE, bkv, k_full(s));
+        tma_load_4d(k_s + s * TILE_BYTES, &tmK, 0, j * TILE, bkv % p.Hkv, bkv / p.Hkv, k_full(s));
+        tma_load_4d(k_s + s * TILE_BYTES + HALF_BYTES, &tmK, 64, j * TILE, bkv % p.Hkv, bkv / p.Hkv, k_full(s));
         if (!mbar_wait(v_empty(s), ph ^ 1u, abort_flag)) { mbar_wait_drain(k_full(s), ph); break; }
         mbar_expect_tx(v_full(s), TILE_BYTES);
-        tma_load_3d(v_s + s * TILE_BYTES, &tmV, 0, j * TILE, bkv, v_full(s));
-        tma_load_3d(v_s + s * TILE_BYTES + HALF_BYTES, &tmV, 64, j * TILE, bkv, v_full(s));
+        tma_load_4d(v_s + s * TILE_BYTES, &tmV, 0, j * TILE, bkv % p.Hkv, bkv / p.Hkv, v_full(s));
+        tma_load_4d(v_s + s * TILE_BYTES + HALF_BYTES, &tmV, 64, j * TILE, bkv % p.Hkv, bkv / p.Hkv, v_full(s));
         issued = j + 1;
       }
       mbar_wait_drain(q_full, 0);
@@ -460,7 +462,7 @@ attn_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     }
     if (ok && mbar_wait(dq_full, 0, abort_flag)) {
       tc_fence_after();
-      T* orow = reinterpret_cast<T*>(p.dq) + ((int64_t)bh * p.S + qi) * AD;
+      T* orow = reinterpret_cast<T*>(p.dq) + (int64_t)b * p.q_bs + (int64_t)h * p.q_hs + (int64_t)qi * p.q_ss;
 #pragma unroll 1
       for (int c = 0; c < 4; ++c) {
         uint32_t r[32];
@@ -542,10 +544,10 @@ attn_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   if (warp == 0) {
     if (lane == 0) {
       mbar_expect_tx(kv_full, 2 * TILE_BYTES);
-      tma_load_3d(k_s, &tmK, 0, kt * TILE, bk, kv_full);
-      tma_load_3d(k_s + HALF_BYTES, &tmK, 64, kt * TILE, bk, kv_full);
-      tma_load_3d(v_s, &tmV, 0, kt * TILE, bk, kv_full);
-      tma_load_3d(v_s + HALF_BYTES, &tmV, 64, kt * TILE, bk, kv_full);
+      tma_load_4d(k_s, &tmK, 0, kt * TILE, bk % p.Hkv, bk / p.Hkv, kv_full);
+      tma_load_4d(k_s + HALF_BYTES, &tmK, 64, kt * TILE, bk % p.Hkv, bk / p.Hkv, kv_full);
+      tma_load_4d(v_s, &tmV, 0, kt * TILE, bk % p.Hkv, bk / p.Hkv, kv_full);
+      tma_load_4d(v_s + HALF_BYTES, &tmV, 64, kt * TILE, bk % p.Hkv, bk / p.Hkv, kv_full);
       int issued = 0;
       for (int it = 0; it < total; ++it) {
         const int s = it % KV_STAGES;
@@ -555,10 +557,10 @@ attn_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         const int bh = (b * p.Hkv + kvh) * G + g;   // query head = kvh * G + g
         const uint32_t dst = st_s + s * 2 * SUB_BYTES;
         mbar_expect_tx(st_full(s), 2 * SUB_BYTES);
-        tma_load_3d(dst, &tmQ, 0, i * QSUB, bh, st_full(s));
-        tma_load_3d(dst + SUB_HALF, &tmQ, 64, i * QSUB, bh, st_full(s));
-        tma_load_3d(dst + SUB_BYTES, &tmDO, 0, i * QSUB, bh, st_full(s));
-        tma_load_3d(dst + SUB_BYTES + SUB_HALF, &tmDO, 64, i * QSUB, bh, st_full(s));
+        tma_load_4d(dst, &tmQ, 0, i * QSUB, bh % p.Hq, bh / p.Hq, st_full(s));
+        tma_load_4d(dst + SUB_HALF, &tmQ, 64, i * QSUB, bh % p.Hq, bh / p.Hq, st_full(s));
+        tma_load_4d(dst + SUB_BYTES, &tmDO, 0, i * QSUB, bh % p.Hq, bh / p.Hq, st_full(s));
+        tma_load_4d(dst + SUB_BYTES + SUB_HALF, &tmDO, 64, i * QSUB, bh % p.Hq, bh / p.Hq, st_full(s));
         issued = it + 1;
       }
       mbar_wait_drain(kv_full, 0);
@@ -646,8 +648,8 @@ attn_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     }
     if (ok && mbar_wait(acc_full, 0, abort_flag)) {
       tc_fence_after();
-      T* krow = reinterpret_cast<T*>(p.dk) + ((int64_t)bk * p.S + kj) * AD;
-      T* vrow = reinterpret_cast<T*>(p.dv) + ((int64_t)bk * p.S + kj) * AD;
+      T* krow = reinterpret_cast<T*>(p.dk) + (int64_t)b * p.k_bs + (int64_t)kvh * p.k_hs + (int64_t)kj * p.k_ss;
+      T* vrow = reinterpret_cast<T*>(p.dv) + (int64_t)b * p.k_bs + (int64_t)kvh * p.k_hs + (int64_t)kj * p.k_ss;
 #pragma unroll 1
       for (int c = 0; c < 4; ++c) {
         uint32_t rk[32], rv[32];
@@ -692,40 +694,42 @@ template <typename K> int configure_smem(K kern, int bytes, bool* done) {
 
 bool attn_tc_available() { return true; }
 
+namespace {
+// Element strides over (sequence, head, batch) for layout 0 = [B, H, S, 128] and layout 1 = [B, S, H, 128].
+struct Strides { int64_t ss, hs, bs; };
+inline Strides strides_for(int layout, int64_t H, int64_t S) {
+  if (layout == 0) return {tc::AD, S * tc::AD, H * S * tc::AD};
+  return {H * tc::AD, tc::AD, S * H * tc::AD};
+}
+}  // namespace
+
 int attn_fwd_tc(const void* q, const void* k, const void* v, void* out, float* lse, int64_t B, int64_t Hq, int64_t Hkv,
-                int64_t S, float scale, int dtype, int* status, cudaStream_t st) {
+                int64_t S, float scale, int dtype, int layout, int* status, cudaStream_t st) {
   using namespace tc;
   const bool bf16 = dtype == Q3_BF16;
+  const Strides sq = strides_for(layout, Hq, S), sk = strides_for(layout, Hkv, S);
   CUtensorMap tmQ, tmK, tmV;
-  int rc = make_tmap_3d(&tmQ, q, bf16, B * Hq, S, AD, AD, S * AD, 64, TILE);
+  int rc = make_tmap_4d(&tmQ, q, bf16, B, Hq, S, AD, sq.ss, sq.hs, sq.bs, 64, TILE);
   if (rc != Q3_OK) return rc;
-  rc = make_tmap_3d(&tmK, k, bf16, B * Hkv, S, AD, AD, S * AD, 64, TILE);
+  rc = make_tmap_4d(&tmK, k, bf16, B, Hkv, S, AD, sk.ss, sk.hs, sk.bs, 64, TILE);
   if (rc != Q3_OK) return rc;
-  rc = make_tmap_3d(&tmV, v, bf16, B * Hkv, S, AD, AD, S * AD, 64, TILE);
+  rc = make_tmap_4d(&tmV, v, bf16, B, Hkv, S, AD, sk.ss, sk.hs, sk.bs, 64, TILE);
   if (rc != Q3_OK) return rc;
   AttnParams p{};
   p.out = out; p.lse = lse; p.Hq = (int)Hq; p.Hkv = (int)Hkv; p.S = (int)S;
+  p.q_ss = sq.ss; p.q_hs = sq.hs; p.q_bs = sq.bs;
   p.scale_log2 = scale * kLog2e;
   p.idesc_qk = make_idesc_f16(128, 128, bf16, false, false);
   p.idesc_pv = make_idesc_f16(128, 128, bf16, false, true);
   p.status = status;
   dim3 grid((unsigned)cdiv(S, TILE), (unsigned)(B * Hq));
-  cudaError_t e;
   if (bf16) {
     static bool cfg = false;
-    if (!cfg) {
-      e = cudaFuncSetAttribute(attn_fwd_tc_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, kFwdSmem);
-      if (e != cudaSuccess) return Q3_ERR_CUDA - (int)e;
-      cfg = true;
-    }
+    if ((rc = configure_smem(attn_fwd_tc_kernel<__nv_bfloat16>, kFwdSmem, &cfg)) != Q3_OK) return rc;
     attn_fwd_tc_kernel<__nv_bfloat16><<<grid, kAttnThreads, kFwdSmem, st>>>(tmQ, tmK, tmV, p);
   } else {
     static bool cfg = false;
-    if (!cfg) {
-      e = cudaFuncSetAttribute(attn_fwd_tc_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, kFwdSmem);
-      if (e != cudaSuccess) return Q3_ERR_CUDA - (int)e;
-      cfg = true;
-    }
+    if ((rc = configure_smem(attn_fwd_tc_kernel<__half>, kFwdSmem, &cfg)) != Q3_OK) return rc;
     attn_fwd_tc_kernel<__half><<<grid, kAttnThreads, kFwdSmem, st>>>(tmQ, tmK, tmV, p);
   }
   return launch_status();
@@ -733,20 +737,22 @@ int attn_fwd_tc(const void* q, const void* k, const void* v, void* out, float* l
 
 int attn_bwd_tc(const void* q, const void* k, const void* v, const void* dout, const float* lse, const float* delta,
                 void* dq, void* dk, void* dv, int64_t B, int64_t Hq, int64_t Hkv, int64_t S, float scale, int dtype,
-                int* status, cudaStream_t st) {
+                int layout, int* status, cudaStream_t st) {
   using namespace tc;
   const bool bf16 = dtype == Q3_BF16;
+  const Strides sq = strides_for(layout, Hq, S), sk = strides_for(layout, Hkv, S);
   CUtensorMap tmQ, tmK, tmV, tmDO, tmQs, tmDOs;
   int rc;
-  if ((rc = make_tmap_3d(&tmQ, q, bf16, B * Hq, S, AD, AD, S * AD, 64, TILE)) != Q3_OK) return rc;
-  if ((rc = make_tmap_3d(&tmDO, dout, bf16, B * Hq, S, AD, AD, S * AD, 64, TILE)) != Q3_OK) return rc;
-  if ((rc = make_tmap_3d(&tmK, k, bf16, B * Hkv, S, AD, AD, S * AD, 64, TILE)) != Q3_OK) return rc;
-  if ((rc = make_tmap_3d(&tmV, v, bf16, B * Hkv, S, AD, AD, S * AD, 64, TILE)) != Q3_OK) return rc;
-  if ((rc = make_tmap_3d(&tmQs, q, bf16, B * Hq, S, AD, AD, S * AD, 64, QSUB)) != Q3_OK) return rc;
-  if ((rc = make_tmap_3d(&tmDOs, dout, bf16, B * Hq, S, AD, AD, S * AD, 64, QSUB)) != Q3_OK) return rc;
+  if ((rc = make_tmap_4d(&tmQ, q, bf16, B, Hq, S, AD, sq.ss, sq.hs, sq.bs, 64, TILE)) != Q3_OK) return rc;
+  if ((rc = make_tmap_4d(&tmDO, dout, bf16, B, Hq, S, AD, sq.ss, sq.hs, sq.bs, 64, TILE)) != Q3_OK) return rc;
+  if ((rc = make_tmap_4d(&tmK, k, bf16, B, Hkv, S, AD, sk.ss, sk.hs, sk.bs, 64, TILE)) != Q3_OK) return rc;
+  if ((rc = make_tmap_4d(&tmV, v, bf16, B, Hkv, S, AD, sk.ss, sk.hs, sk.bs, 64, TILE)) != Q3_OK) return rc;
+  if ((rc = make_tmap_4d(&tmQs, q, bf16, B, Hq, S, AD, sq.ss, sq.hs, sq.bs, 64, QSUB)) != Q3_OK) return rc;
+  if ((rc = make_tmap_4d(&tmDOs, dout, bf16, B, Hq, S, AD, sq.ss, sq.hs, sq.bs, 64, QSUB)) != Q3_OK) return rc;
   AttnBwdParams p{};
   p.lse = lse; p.delta = delta; p.dq = dq; p.dk = dk; p.dv = dv;
   p.Hq = (int)Hq; p.Hkv = (int)Hkv; p.S = (int)S; p.scale = scale; p.scale_log2 = scale * kLog2e;
+  p.q_ss = sq.ss; p.q_hs = sq.hs; p.q_bs = sq.bs; p.k_ss = sk.ss; p.k_hs = sk.hs; p.k_bs = sk.bs;
   p.idesc_kk128 = make_idesc_f16(128, 128, bf16, false, false);
   p.idesc_kk64 = make_idesc_f16(128, 64, bf16, false, false);
   p.idesc_kmn = make_idesc_f16(128, 128, bf16, false, true);

@@ -97,6 +97,12 @@ __device__ __forceinline__ void tma_prefetch_2d(const CUtensorMap* map, int x, i
                "r"(x), "r"(y)
                : "memory");
 }
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, int x, int y, int z, int w, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];" ::
+          "r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(z), "r"(w), "r"(bar)
+      : "memory");
+}
 __device__ __forceinline__ void prefetch_tmap(const CUtensorMap* map) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");
 }
@@ -258,6 +264,28 @@ inline int make_tmap_3d(CUtensorMap* map, const void* base, bool bf16, int64_t d
   CUresult r = fn(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3,
                   const_cast<void*>(base), gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? Q3_OK : Q3_ERR_TMAP;
+}
+
+// 4-D map over a [batch, head, seq, cols] tensor of 16-bit elements with arbitrary element strides for the
+// sequence, head and batch dimensions (cols contiguous); box = box_cols x box_rows x 1 x 1.
+inline int make_tmap_4d(CUtensorMap* map, const void* base, bool bf16, int64_t batch, int64_t heads, int64_t seq,
+                        int64_t cols, int64_t seq_stride, int64_t head_stride, int64_t batch_stride, int box_cols,
+                        int box_rows) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn) return Q3_ERR_DRIVER;
+  ensure_thread_context();
+  cuuint64_t gdim[4] = {(cuuint64_t)cols, (cuuint64_t)seq, (cuuint64_t)heads, (cuuint64_t)batch};
+  cuuint64_t gstride[3] = {(cuuint64_t)seq_stride * 2, (cuuint64_t)head_stride * 2, (cuuint64_t)batch_stride * 2};
+  cuuint32_t box[4] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows, 1, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = fn(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4,
+                  const_cast<void*>(base), gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS && getenv("Q3_DEBUG"))
+    fprintf(stderr, "q3: 4-d tensor map encode failed (%d): base=%p B=%lld H=%lld S=%lld strides=%lld,%lld,%lld\n", (int)r,
+            base, (long long)batch, (long long)heads, (long long)seq, (long long)seq_stride, (long long)head_stride,
+            (long long)batch_stride);
   return r == CUDA_SUCCESS ? Q3_OK : Q3_ERR_TMAP;
 }
 

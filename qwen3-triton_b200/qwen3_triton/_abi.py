@@ -53,6 +53,7 @@ SIGNATURES = {
     "q3_vce_finish": (I, [P, P, P, P, P, P, P, L, L, L, L, L, P, P]),
     "q3_vce_accumulate": (I, [P, I, P, L, L, I, P]),
     "q3_adamw_multi": (I, [P, P, L, L, I, D, D, D, D, D, P]),
+    "q3_adamw_multi_mp": (I, [P, P, L, L, I, I, D, D, D, D, D, P]),
     "q3_gemm": (I, [P, L, L, P, L, L, P, L, L, L, I, I, P, P]),
     "q3_gemm_path": (I, [P, L, L, P, L, L, P, L, L, L, I, I]),
     "q3_gate_up_swiglu_fwd": (I, [P, P, P, P, P, P, L, L, L, I, P, P]),
@@ -60,6 +61,8 @@ SIGNATURES = {
     "q3_attn_fwd": (I, [P, P, P, P, P, L, L, L, L, L, D, I, P, P]),
     "q3_attn_bwd_workspace_bytes": (L, [L, L, L, L, L]),
     "q3_attn_bwd": (I, [P, P, P, P, P, P, P, P, P, P, L, L, L, L, L, L, D, I, P, P]),
+    "q3_attn_fwd_bshd": (I, [P, P, P, P, P, L, L, L, L, L, D, I, P, P]),
+    "q3_attn_bwd_bshd": (I, [P, P, P, P, P, P, P, P, P, P, L, L, L, L, L, L, D, I, P, P]),
     "q3_attn_path": (I, [P, P, P, P, L, I]),
 }
 

@@ -27,5 +27,17 @@ class PrecisionQwen3ForCausalLM(TritonQwen3ForCausalLM):
         super().__init__(config, options)
 
 
+class FusedQwen3ForCausalLM(PrecisionQwen3ForCausalLM):
+    """Same parameters and state dict; every decoder layer is one fused autograd node (qwen3_triton/fused.py)."""
+
+    def __init__(self, config, options=None, *, precision_options=None):
+        from .fused import FusedBackbone
+        self.backbone_class = FusedBackbone
+        super().__init__(config, options, precision_options=precision_options)
+
+
 def model_for_variant(config, name, *, precision_options=None):
+    """The reference's variant names plus 'b200_fused' (fused decoder layers, token-major attention)."""
+    if name == 'b200_fused':
+        return FusedQwen3ForCausalLM(config, OptimizationOptions(), precision_options=precision_options)
     return PrecisionQwen3ForCausalLM(config, options_for_variant(name), precision_options=precision_options)

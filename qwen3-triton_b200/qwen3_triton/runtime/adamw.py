@@ -96,14 +96,26 @@ class TritonAdamW(torch.optim.Optimizer):
             blocks = 0
             device = None
             changed = []
+            mixed = False
             for parameter in group['params']:
-                if parameter.grad is None:
+                # single-GPU mixed precision (runtime/mixed_precision.py): a bf16 gradient to read directly and/or
+                # a bf16 working copy to refresh in the same pass
+                low_g = getattr(parameter, 'q3_lowp_grad', None)
+                low_p = getattr(parameter, 'q3_lowp_copy', None)
+                if parameter.grad is None and low_g is None:
                     continue
                 p = local(parameter)
-                g = local(parameter.grad)
-                if (p.dtype != torch.float32 or g.dtype != torch.float32 or not p.is_cuda or p.device != g.device
-                        or not p.is_contiguous() or not g.is_contiguous() or p.shape != g.shape or g.is_sparse):
+                g = local(parameter.grad) if low_g is None else None
+                if g is not None and (g.dtype != torch.float32 or p.device != g.device or not g.is_contiguous()
+                                      or p.shape != g.shape or g.is_sparse):
                     raise ValueError('Matching contiguous local CUDA FP32 parameter/gradient required')
+                if p.dtype != torch.float32 or not p.is_cuda or not p.is_contiguous():
+                    raise ValueError('Matching contiguous local CUDA FP32 parameter/gradient required')
+                for low in (low_g, low_p):
+                    if low is not None and (low.dtype not in (torch.bfloat16, torch.float16) or low.shape != p.shape
+                                            or low.device != p.device or not low.is_contiguous()):
+                        raise ValueError('Low-precision gradient / working copy must match the FP32 parameter')
+                mixed = mixed or low_g is not None or low_p is not None
                 if device is not None and device != p.device:
                     raise ValueError('One CUDA device per group')
                 device = p.device
@@ -119,7 +131,10 @@ class TritonAdamW(torch.optim.Optimizer):
                 if (m.shape != p.shape or v.shape != p.shape or m.dtype != torch.float32 or v.dtype != torch.float32
                         or step.dtype != torch.float32 or step.numel() != 1 or step.device != device):
                     raise ValueError('Invalid local FP32 AdamW state')
-                rows.append((p.data_ptr(), g.data_ptr(), m.data_ptr(), v.data_ptr(), step.data_ptr(), p.numel(), blocks))
+                rows.append((p.data_ptr(), g.data_ptr() if g is not None else 0, m.data_ptr(), v.data_ptr(), step.data_ptr(),
+                             p.numel(), blocks, low_g.data_ptr() if low_g is not None else 0,
+                             low_p.data_ptr() if low_p is not None else 0,
+                             _abi.dt((low_g if low_g is not None else low_p).dtype) if (low_g is not None or low_p is not None) else 0))
                 blocks += -(-p.numel() // self.block)
                 changed.extend([parameter, m, v, step])
                 if p is not parameter:
@@ -127,6 +142,10 @@ class TritonAdamW(torch.optim.Optimizer):
             if not rows:
                 continue
             # The pointer table only changes when gradients are re-allocated; cache the device copy.
+            lowp = {r[9] for r in rows if r[9]}
+            if len(lowp) > 1:
+                raise ValueError('One low-precision dtype per group')
+            rows = [r[:9] if mixed else r[:7] for r in rows]
             key = tuple(rows)
             cached = self._tables.get(index)
             if cached is None or cached[0] != key:
@@ -138,9 +157,14 @@ class TritonAdamW(torch.optim.Optimizer):
                 self._tables[index] = cached
             _, meta, coeff = cached
             b1, b2 = group['betas']
-            _abi.call('q3_adamw_multi', meta.data_ptr(), coeff.data_ptr(), len(rows), blocks, self.block,
-                      float(group['lr']), float(b1), float(b2), float(group['weight_decay']), float(group['eps']),
-                      _abi.stream())
+            if mixed:
+                _abi.call('q3_adamw_multi_mp', meta.data_ptr(), coeff.data_ptr(), len(rows), blocks, self.block,
+                          lowp.pop(), float(group['lr']), float(b1), float(b2), float(group['weight_decay']),
+                          float(group['eps']), _abi.stream())
+            else:
+                _abi.call('q3_adamw_multi', meta.data_ptr(), coeff.data_ptr(), len(rows), blocks, self.block,
+                          float(group['lr']), float(b1), float(b2), float(group['weight_decay']), float(group['eps']),
+                          _abi.stream())
             torch.autograd.graph.increment_version(changed)
         self.kernel_steps += 1
         return loss

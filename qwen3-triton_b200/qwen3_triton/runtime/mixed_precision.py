@@ -35,7 +35,16 @@ class MasterWeights:
                 seen[id(p)] = work
                 self.masters.append(master)
                 self.working.append(work)
+        self.fused = False
         self.sync_working()
+
+    def fuse_into_optimizer(self):
+        """Let TritonAdamW read the bf16 gradients directly and refresh the bf16 working copies in its own pass:
+        after this, `sync_working()` and `collect_grads()` launch nothing."""
+        self.fused = True
+        for m, w in zip(self.masters, self.working):
+            m.q3_lowp_copy = w.data
+        return self
 
     def parameters(self):
         return self.masters
@@ -43,6 +52,9 @@ class MasterWeights:
     @torch.no_grad()
     def sync_working(self):
         """master (fp32) -> working (bf16)."""
+        if self.fused and getattr(self, '_synced_once', False):
+            return
+        self._synced_once = True
         for m, w in zip(self.masters, self.working):
             _abi.call('q3_cast', m.data_ptr(), _abi.Q3_F32, w.data_ptr(), _abi.dt(self.compute_dtype), m.numel(),
                       _abi.stream())
@@ -50,6 +62,11 @@ class MasterWeights:
     @torch.no_grad()
     def collect_grads(self):
         """working.grad (bf16) -> master.grad (fp32); frees the bf16 gradient."""
+        if self.fused:
+            for m, w in zip(self.masters, self.working):
+                m.q3_lowp_grad = w.grad.contiguous() if w.grad is not None else None
+                w.grad = None
+            return
         for m, w in zip(self.masters, self.working):
             if w.grad is None:
                 m.grad = None

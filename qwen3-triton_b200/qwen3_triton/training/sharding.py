@@ -74,7 +74,10 @@ def shard_vocab_loss_model(model, *, keep_full_layers, checkpoint_every, skip_em
     for index, layer in enumerate(body.layers):
         layer = layer.float()
         if index in checkpointed:
-            layer = wrap_decoder_checkpoint(layer, mode='full')
+            if hasattr(layer, 'recompute'):
+                layer.recompute = True      # fused layers recompute inside their own backward
+            else:
+                layer = wrap_decoder_checkpoint(layer, mode='full')
         body.layers[index] = layer
         retain = index >= len(body.layers) - keep_full_layers
         fully_shard(layer, reshard_after_forward=not retain, **kw)

@@ -88,3 +88,33 @@ def test_version_counter_bumped():
     before = p._version
     TritonAdamW([p]).step()
     assert p._version > before
+
+
+def test_mixed_precision_fusion_is_bit_identical_to_separate_cast_passes():
+    """bf16 gradients read directly + bf16 working copy written by the optimizer kernel == upcast pass, fp32
+    AdamW, downcast pass."""
+    from qwen3_triton.runtime.adamw import TritonAdamW
+    from qwen3_triton.runtime.mixed_precision import MasterWeights
+
+    def build():
+        torch.manual_seed(7)
+        net = torch.nn.Sequential(torch.nn.Linear(130, 257, bias=False), torch.nn.Linear(257, 64, bias=False)).cuda()
+        mw = MasterWeights(net)
+        return net, mw, TritonAdamW(mw.parameters(), **HYPER)
+
+    net_a, mw_a, opt_a = build()
+    net_b, mw_b, opt_b = build()
+    mw_b.fuse_into_optimizer()
+    g = torch.Generator().manual_seed(8)
+    for _ in range(4):
+        grads = [torch.randn(w.shape, generator=g).to(torch.bfloat16).cuda() * 1e-2 for w in mw_a.working]
+        for mw, opt in ((mw_a, opt_a), (mw_b, opt_b)):
+            mw.sync_working()
+            for w, gr in zip(mw.working, grads):
+                w.grad = gr.clone()
+            mw.collect_grads()
+            opt.step()
+        mw_a.sync_working()
+    for ma, mb, wa, wb in zip(mw_a.masters, mw_b.masters, mw_a.working, mw_b.working):
+        assert torch.equal(ma, mb), float((ma - mb).abs().max())
+        assert torch.equal(wa, wb) and wb.dtype == torch.bfloat16, float((wa.float() - wb.float()).abs().max())

@@ -71,3 +71,28 @@ def test_candidate_entry_matches_causal_attention():
     a = candidate(q, k, v, fusion=False, lane_sum=True, round_kv=True, reciprocal=1, stages=2, xor_sum=True,
                   lse_fma=True, native_delta=True, native_dq=True, sum_fma=True)
     assert torch.equal(a, causal_attention(q, k, v))
+
+
+@pytest.mark.parametrize('B,Hq,Hkv,S', [(1, 4, 2, 128), (2, 8, 2, 300), (1, 4, 1, 513)])
+def test_token_major_layout_matches_head_major(B, Hq, Hkv, S):
+    """q3_attn_fwd_bshd / q3_attn_bwd_bshd read and write [B,S,H,128] directly; results must equal the
+    [B,H,S,128] entry points on transposed copies, bit for bit (same kernels, different TMA strides)."""
+    from qwen3_triton import _abi
+    from qwen3_triton.kernels.attention import attention_backward, attention_forward
+    dt = torch.bfloat16
+    q, k, v, do = (randn(s, i, dt).cuda() for i, s in enumerate([(B, S, Hq, 128), (B, S, Hkv, 128), (B, S, Hkv, 128), (B, S, Hq, 128)]))
+    out = torch.empty_like(q)
+    lse = torch.empty(B, Hq, S, device='cuda')
+    st = _abi.status_word('cuda').data_ptr()
+    _abi.call('q3_attn_fwd_bshd', q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lse.data_ptr(), B, S, Hq, Hkv,
+              128, 128 ** -0.5, _abi.Q3_BF16, st, _abi.stream())
+    qh, kh, vh, doh = (t.transpose(1, 2).contiguous() for t in (q, k, v, do))
+    out_h, lse_h = attention_forward(qh, kh, vh, 128 ** -0.5)
+    assert torch.equal(out.transpose(1, 2), out_h) and torch.equal(lse, lse_h)
+    dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+    ws = _abi.workspace(_abi.lib().q3_attn_bwd_workspace_bytes(B, Hq, Hkv, S, 128), 'cuda')
+    _abi.call('q3_attn_bwd_bshd', q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), do.data_ptr(), lse.data_ptr(),
+              dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), ws.data_ptr(), ws.numel(), B, S, Hq, Hkv, 128, 128 ** -0.5,
+              _abi.Q3_BF16, st, _abi.stream())
+    dqh, dkh, dvh = attention_backward(qh, kh, vh, out_h, doh, lse_h, 128 ** -0.5)
+    assert torch.equal(dq.transpose(1, 2), dqh) and torch.equal(dk.transpose(1, 2), dkh) and torch.equal(dv.transpose(1, 2), dvh)

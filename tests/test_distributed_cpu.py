@@ -59,7 +59,7 @@ WORKER = textwrap.dedent('''
         comm.barrier(); raise SystemExit("closed communicator must refuse")
     except RuntimeError:
         pass
-    dist.barrier(); dist.destroy_process_group(); print("rank", r, "ok")
+    dist.barrier(); dist.destroy_process_group(); sys.stdout.write("rank" + str(r) + "ok" + chr(10)); sys.stdout.flush()
 ''') % str(ROOT / "qwen3-triton_b200")
 
 
@@ -71,7 +71,7 @@ def test_collectives_and_fsdp_hooks_two_gloo_ranks(tmp_path):
                           "--master-addr", "127.0.0.1", "--master-port", "29611", str(script)], capture_output=True,
                          text=True, timeout=240, env=env)
     assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-3000:]
-    assert "rank 0 ok" in res.stdout and "rank 1 ok" in res.stdout
+    assert "rank0ok" in res.stdout and "rank1ok" in res.stdout
 
 
 def test_checkpoint_and_retention_policy_helpers():
