@@ -16,8 +16,9 @@ int attn_bwd_simt(const void* q, const void* k, const void* v, const void* dout,
 int attn_fwd_tc(const void* q, const void* k, const void* v, void* out, float* lse, int64_t B, int64_t Hq, int64_t Hkv,
                 int64_t S, float scale, int dtype, int layout, int* status, cudaStream_t st);
 int attn_bwd_tc(const void* q, const void* k, const void* v, const void* dout, const float* lse, const float* delta,
-                void* dq, void* dk, void* dv, int64_t B, int64_t Hq, int64_t Hkv, int64_t S, float scale, int dtype,
-                int layout, int* status, cudaStream_t st);
+                void* dq, void* dk, void* dv, float* partials, int64_t B, int64_t Hq, int64_t Hkv, int64_t S, float scale,
+                int dtype, int layout, int* status, cudaStream_t st);
+int attn_bwd_group_split(int64_t B, int64_t Hq, int64_t Hkv, int64_t S);
 int attn_delta_layout(const void* out, const void* dout, float* delta, int64_t B, int64_t H, int64_t S, int64_t D,
                       int layout, int dtype, cudaStream_t st);
 bool attn_tc_available();
@@ -52,9 +53,16 @@ extern "C" int q3_attn_fwd(const void* q, const void* k, const void* v, void* ou
   return attn_fwd_simt(q, k, v, out, lse, B, Hq, Hkv, S, D, (float)scale, dtype, st);
 }
 
+// delta = rowsum(dO * O) [B,Hq,S] fp32, then (small grids only) per-query-head fp32 partials of dK and dV
+static int64_t delta_bytes(int64_t B, int64_t Hq, int64_t S) { return ((B * Hq * S * 4 + 255) / 256) * 256; }
+
 extern "C" int64_t q3_attn_bwd_workspace_bytes(int64_t B, int64_t Hq, int64_t Hkv, int64_t S, int64_t D) {
-  (void)Hkv; (void)D;
-  return B * Hq * S * 4;  // delta = rowsum(dO * O), fp32
+  int64_t bytes = delta_bytes(B, Hq, S);
+  if (D == 128 && Hkv > 0 && Hq % Hkv == 0) {
+    const int split = attn_bwd_group_split(B, Hq, Hkv, S);
+    if (split > 1) bytes += (int64_t)split * 2 * B * Hkv * S * 128 * 4;
+  }
+  return bytes;
 }
 
 extern "C" int q3_attn_bwd(const void* q, const void* k, const void* v, const void* out, const void* dout,
@@ -71,7 +79,8 @@ extern "C" int q3_attn_bwd(const void* q, const void* k, const void* v, const vo
   rc = attn_delta(out, dout, delta, B * Hq * S, D, dtype, st);
   if (rc != Q3_OK) return rc;
   if (tc_eligible(q, k, v, dout, D, dtype) && aligned16(dq) && aligned16(dk) && aligned16(dv))
-    return attn_bwd_tc(q, k, v, dout, lse, delta, dq, dk, dv, B, Hq, Hkv, S, (float)scale, dtype, 0, status, st);
+    return attn_bwd_tc(q, k, v, dout, lse, delta, dq, dk, dv, (float*)((char*)workspace + delta_bytes(B, Hq, S)), B, Hq, Hkv,
+                       S, (float)scale, dtype, 0, status, st);
   return attn_bwd_simt(q, k, v, dout, lse, delta, dq, dk, dv, B, Hq, Hkv, S, D, (float)scale, dtype, st);
 }
 
@@ -101,5 +110,6 @@ extern "C" int q3_attn_bwd_bshd(const void* q, const void* k, const void* v, con
   float* delta = (float*)workspace;
   rc = attn_delta_layout(out, dout, delta, B, Hq, S, D, 1, dtype, st);
   if (rc != Q3_OK) return rc;
-  return attn_bwd_tc(q, k, v, dout, lse, delta, dq, dk, dv, B, Hq, Hkv, S, (float)scale, dtype, 1, status, st);
+  return attn_bwd_tc(q, k, v, dout, lse, delta, dq, dk, dv, (float*)((char*)workspace + delta_bytes(B, Hq, S)), B, Hq, Hkv, S,
+                     (float)scale, dtype, 1, status, st);
 }

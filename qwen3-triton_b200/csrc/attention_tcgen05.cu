@@ -26,6 +26,7 @@
 // graph uses) and kernels/attention_kernels.py:10-253. Math: ops/reference/attention.py:10-124.
 #include "tcgen05.cuh"
 #include <math_constants.h>
+#include <algorithm>
 
 namespace q3 {
 namespace tc {
@@ -34,7 +35,8 @@ constexpr int AD = 128;           // head dim
 constexpr int TILE = 128;         // query rows / keys per tile
 constexpr int HALF_BYTES = TILE * 128;       // one 64-column half of a 128-row tile (16 KB)
 constexpr int TILE_BYTES = 2 * HALF_BYTES;   // 32 KB
-constexpr int kAttnThreads = 192;
+constexpr int kAttnThreads = 320;   // warp 0 TMA, warp 1 MMA, warps 2..9 compute (two threads per tile row)
+constexpr int kComputeThreads = 256;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
 
@@ -48,6 +50,12 @@ struct AttnParams {
   uint32_t idesc_pv; // A K-major, B MN-major, N = 128
   int* status;
 };
+
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 
 template <typename T> __device__ __forceinline__ uint32_t pack2(float a, float b);
 template <> __device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float a, float b) {
@@ -120,6 +128,8 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   const uint32_t p_full = bar0 + 8u * 13, done_bar = bar0 + 8u * 14;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 15);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  const uint32_t x_bar = bar0 + 8u * 16;
+  float* xmax = reinterpret_cast<float*>(bars + 18);   // [2 tiles in flight + 1][2 column halves][128 rows]
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int nq = (p.S + TILE - 1) / TILE;
@@ -131,8 +141,9 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   if (threadIdx.x == 0) {
     *abort_flag = 0;
     for (int i = 0; i < 13; ++i) mbar_init(bar0 + 8u * i, 1);
-    mbar_init(p_full, 128);
+    mbar_init(p_full, kComputeThreads);
     mbar_init(done_bar, 1);
+    mbar_init(x_bar, kComputeThreads);
     fence_barrier_init();
     prefetch_tmap(&tmQ); prefetch_tmap(&tmK); prefetch_tmap(&tmV);
   }
@@ -199,64 +210,79 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     }
   } else {
     // ------------------------------------------------------------------ softmax / accumulate / epilogue
+    // Two threads per query row: warps 2-5 take score / output columns 0..63, warps 6-9 columns 64..127.
+    // The halves exchange their row maximum through shared memory once per key tile.
     const int qd = warp & 3;                 // TMEM lane quarter of this warp
+    const int ch = (warp - 2) >> 2;          // column half
     const int row = qd * 32 + lane;          // query row within the tile
     const uint32_t lane_addr = tmem + ((uint32_t)(qd * 32) << 16);
-    float o[AD];
+    float o[64];
 #pragma unroll
-    for (int i = 0; i < AD; ++i) o[i] = 0.f;
+    for (int i = 0; i < 64; ++i) o[i] = 0.f;
     float m = -CUDART_INF_F, l = 0.f, alpha_prev = 1.f;
     bool ok = true;
-    for (int j = 0; j < ntiles && ok; ++j) {
+    for (int j = 0; j < ntiles; ++j) {
       const int s = j & 1;
-      if (!mbar_wait(s_full(s), (j >> 1) & 1u, abort_flag)) { ok = false; break; }
+      if (!mbar_wait(s_full(s), (j >> 1) & 1u, abort_flag)) ok = false;
+      ok = __all_sync(0xffffffffu, ok);
       tc_fence_after();
-      const uint32_t s_addr = lane_addr + s * 128;
+      const uint32_t s_addr = lane_addr + s * 128 + ch * 64;
       const bool diag = (j == ntiles - 1);
-      // pass 1: row maximum of the raw scores
-      float mx = m;
+      // pass 1: maximum of this thread's 64 raw scores
+      float mx = -CUDART_INF_F;
+      if (ok) {
 #pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t r[32];
-        tmem_ld32(s_addr + c * 32, r);
-        tmem_ld_wait();
+        for (int c = 0; c < 2; ++c) {
+          uint32_t r[32];
+          tmem_ld32(s_addr + c * 32, r);
+          tmem_ld_wait();
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const float sv = __uint_as_float(r[i]);
-          if (!diag || c * 32 + i <= row) mx = fmaxf(mx, sv);
+          for (int i = 0; i < 32; ++i) {
+            const float sv = __uint_as_float(r[i]);
+            if (!diag || ch * 64 + c * 32 + i <= row) mx = fmaxf(mx, sv);
+          }
         }
       }
+      xmax[(j & 1) * 256 + ch * 128 + row] = mx;
+      mbar_arrive(x_bar);                      // release: the partner thread's maximum is visible after the wait
+      if (!mbar_wait(x_bar, j & 1u, abort_flag)) ok = false;
+      ok = __all_sync(0xffffffffu, ok);        // tcgen05.ld below is warp-collective: keep the decision uniform
+      if (!ok) break;
+      mx = fmaxf(m, fmaxf(mx, xmax[(j & 1) * 256 + (ch ^ 1) * 128 + row]));
       const float mc = mx * p.scale_log2;
-      const float alpha = exp2f(m * p.scale_log2 - mc);  // m = -inf on the first tile -> 0
+      const float alpha = fast_exp2(m * p.scale_log2 - mc);  // m = -inf on the first tile -> 0
       // the P buffer and O_{j-1} are free / ready once the previous PV product has completed
-      if (j > 0 && !mbar_wait(o_full((j - 1) & 1), ((j - 1) >> 1) & 1u, abort_flag)) { ok = false; break; }
+      if (j > 0 && !mbar_wait(o_full((j - 1) & 1), ((j - 1) >> 1) & 1u, abort_flag)) ok = false;
+      ok = __all_sync(0xffffffffu, ok);
       tc_fence_after();
-      // pass 2: probabilities -> shared memory (bf16), row sum
+      // pass 2: probabilities -> shared memory (bf16), partial row sum
       float sum = 0.f;
+      if (ok) {
 #pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t r[32];
-        float pv[32];
-        tmem_ld32(s_addr + c * 32, r);
-        tmem_ld_wait();
+        for (int c = 0; c < 2; ++c) {
+          uint32_t r[32];
+          float pv[32];
+          tmem_ld32(s_addr + c * 32, r);
+          tmem_ld_wait();
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const float e = exp2f(fmaf(__uint_as_float(r[i]), p.scale_log2, -mc));
-          pv[i] = (!diag || c * 32 + i <= row) ? e : 0.f;
-          sum += pv[i];
+          for (int i = 0; i < 32; ++i) {
+            const float e = fast_exp2(fmaf(__uint_as_float(r[i]), p.scale_log2, -mc));
+            pv[i] = (!diag || ch * 64 + c * 32 + i <= row) ? e : 0.f;
+            sum += pv[i];
+          }
+          store_swizzled32<T>(p_ptr, row, ch * 64 + c * 32, pv);
         }
-        store_swizzled32<T>(p_ptr, row, c * 32, pv);
       }
       l = l * alpha + sum;
       m = mx;
       tc_fence_before();
       fence_proxy_async_smem();   // generic-proxy writes of P must be visible to the tensor core
       mbar_arrive(p_full);
-      // fold O_{j-1} into the register accumulator while the tensor core computes S_{j+1} and P_j V_j
-      if (j > 0) {
-        const uint32_t o_addr = lane_addr + 256 + ((j - 1) & 1) * 128;
+      // fold this thread's half of O_{j-1} into registers while the tensor core computes S_{j+1} and P_j V_j
+      if (j > 0 && ok) {
+        const uint32_t o_addr = lane_addr + 256 + ((j - 1) & 1) * 128 + ch * 64;
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
+        for (int c = 0; c < 2; ++c) {
           uint32_t r[32];
           tmem_ld32(o_addr + c * 32, r);
           tmem_ld_wait();
@@ -266,14 +292,22 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       }
       alpha_prev = alpha;
     }
-    if (ok && mbar_wait(o_full((ntiles - 1) & 1), ((ntiles - 1) >> 1) & 1u, abort_flag)) {
+    // combine the two partial row sums (own slot of the exchange buffer, one more phase of the barrier)
+    xmax[512 + ch * 128 + row] = l;
+    mbar_arrive(x_bar);
+    if (ok && !mbar_wait(x_bar, ntiles & 1u, abort_flag)) ok = false;
+    ok = __all_sync(0xffffffffu, ok);
+    if (ok) l += xmax[512 + (ch ^ 1) * 128 + row];
+    bool fin = ok && mbar_wait(o_full((ntiles - 1) & 1), ((ntiles - 1) >> 1) & 1u, abort_flag);
+    fin = __all_sync(0xffffffffu, fin);
+    if (fin) {
       tc_fence_after();
-      const uint32_t o_addr = lane_addr + 256 + ((ntiles - 1) & 1) * 128;
+      const uint32_t o_addr = lane_addr + 256 + ((ntiles - 1) & 1) * 128 + ch * 64;
       const float inv = 1.f / l;
       const int qi = qt * TILE + row;
-      T* orow = reinterpret_cast<T*>(p.out) + (int64_t)b * p.q_bs + (int64_t)h * p.q_hs + (int64_t)qi * p.q_ss;
+      T* orow = reinterpret_cast<T*>(p.out) + (int64_t)b * p.q_bs + (int64_t)h * p.q_hs + (int64_t)qi * p.q_ss + ch * 64;
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
+      for (int c = 0; c < 2; ++c) {
         uint32_t r[32];
         tmem_ld32(o_addr + c * 32, r);
         tmem_ld_wait();
@@ -292,7 +326,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
           }
         }
       }
-      if (qi < p.S) p.lse[(int64_t)bh * p.S + qi] = (m * p.scale_log2 + log2f(l)) * kLn2;
+      if (qi < p.S && ch == 0) p.lse[(int64_t)bh * p.S + qi] = (m * p.scale_log2 + log2f(l)) * kLn2;
     }
   }
   tc_fence_before();
@@ -301,7 +335,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   if (threadIdx.x == 0 && *abort_flag) flag_status(p.status, Q3_STATUS_WAIT_TIMEOUT);
 }
 
-constexpr int kFwdSmem = 6 * TILE_BYTES + 1024 + 256;
+constexpr int kFwdSmem = 6 * TILE_BYTES + 1024 + 256 + 3 * 2 * 128 * 4;
 
 // ====================================================================================== backward
 struct AttnBwdParams {
@@ -310,6 +344,8 @@ struct AttnBwdParams {
   void* dq;
   void* dk;
   void* dv;
+  float* part;      // fp32 partial dK/dV [gsplit][2][B*Hkv*S][128] when gsplit > 1
+  int gsplit;       // 1: one CTA sums the whole query-head group; G: one CTA per query head + reduce kernel
   int Hq, Hkv, S;
   int64_t q_ss, q_hs, q_bs, k_ss, k_hs, k_bs;  // element strides over (sequence, head, batch)
   float scale, scale_log2;
@@ -371,7 +407,7 @@ attn_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
   if (threadIdx.x == 0) {
     *abort_flag = 0;
     for (int i = 0; i < 11; ++i) mbar_init(bar0 + 8u * i, 1);
-    mbar_init(ds_full, 128);
+    mbar_init(ds_full, kComputeThreads);
     mbar_init(done_bar, 1);
     fence_barrier_init();
     prefetch_tmap(&tmQ); prefetch_tmap(&tmK); prefetch_tmap(&tmV); prefetch_tmap(&tmDO);
@@ -431,18 +467,21 @@ attn_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
       mbar_wait_drain(done_bar, 0);
     }
   } else {
-    const int qd = warp & 3, row = qd * 32 + lane;
+    // two threads per query row: warps 2-5 take key columns 0..63 of each tile, warps 6-9 columns 64..127
+    const int qd = warp & 3, ch = (warp - 2) >> 2, row = qd * 32 + lane;
     const uint32_t lane_addr = tmem + ((uint32_t)(qd * 32) << 16);
     const int qi = qt * TILE + row;
     const float lse2 = (qi < p.S ? p.lse[(int64_t)bh * p.S + qi] : 0.f) * kLog2e;
     const float dl = qi < p.S ? p.delta[(int64_t)bh * p.S + qi] : 0.f;
     bool ok = true;
     for (int j = 0; j < ntiles && ok; ++j) {
-      if (!mbar_wait(sdp_full, j & 1u, abort_flag)) { ok = false; break; }
+      if (!mbar_wait(sdp_full, j & 1u, abort_flag)) ok = false;
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
       tc_fence_after();
       const bool diag = (j == ntiles - 1);
 #pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
+      for (int c = 2 * ch; c < 2 * ch + 2; ++c) {
         uint32_t rs[32], rp[32];
         float ds[32];
         tmem_ld32(lane_addr + c * 32, rs);
@@ -450,7 +489,7 @@ attn_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         tmem_ld_wait();
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
-          const float pr = exp2f(fmaf(__uint_as_float(rs[i]), p.scale_log2, -lse2));
+          const float pr = fast_exp2(fmaf(__uint_as_float(rs[i]), p.scale_log2, -lse2));
           const bool keep = (!diag || c * 32 + i <= row) && qi < p.S;
           ds[i] = keep ? pr * (__uint_as_float(rp[i]) - dl) : 0.f;
         }
@@ -460,11 +499,13 @@ attn_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
       fence_proxy_async_smem();
       mbar_arrive(ds_full);
     }
-    if (ok && mbar_wait(dq_full, 0, abort_flag)) {
+    bool fin = ok && mbar_wait(dq_full, 0, abort_flag);
+    fin = __all_sync(0xffffffffu, fin);
+    if (fin) {
       tc_fence_after();
       T* orow = reinterpret_cast<T*>(p.dq) + (int64_t)b * p.q_bs + (int64_t)h * p.q_hs + (int64_t)qi * p.q_ss;
 #pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
+      for (int c = 2 * ch; c < 2 * ch + 2; ++c) {
         uint32_t r[32];
         tmem_ld32(lane_addr + 256 + c * 32, r);
         tmem_ld_wait();
@@ -511,27 +552,29 @@ attn_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   const uint32_t pt_s = base + pt_off, dst_s = pt_s + SUB_BYTES;
   uint8_t* pt_ptr = smem + pt_off;
   uint8_t* dst_ptr = pt_ptr + SUB_BYTES;
-  float* stat = reinterpret_cast<float*>(dst_ptr + SUB_BYTES);   // [2][64]: lse*log2e, delta
-  uint64_t* bars = reinterpret_cast<uint64_t*>(stat + 2 * QSUB);
+  float* stat = reinterpret_cast<float*>(dst_ptr + SUB_BYTES);   // [2 items in flight][lse*log2e 64 | delta 64]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(stat + 4 * QSUB);
   const uint32_t bar0 = smem_u32(bars);
   const uint32_t kv_full = bar0;
   auto st_full = [&](int s) { return bar0 + 8u * (1 + s); };
   auto st_empty = [&](int s) { return bar0 + 8u * (4 + s); };
   auto sdp_full = [&](int s) { return bar0 + 8u * (7 + s); };
   const uint32_t pds_empty = bar0 + 8u * 9, acc_full = bar0 + 8u * 10, done_bar = bar0 + 8u * 11,
-                 pds_full = bar0 + 8u * 12;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 13);
+                 pds_full = bar0 + 8u * 12, stat_bar = bar0 + 8u * 13;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 14);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int kt = blockIdx.x, bk = blockIdx.y, b = bk / p.Hkv, kvh = bk % p.Hkv, G = p.Hq / p.Hkv;
   const int nsub = (p.S + QSUB - 1) / QSUB, first = kt * (TILE / QSUB);
-  const int per_head = nsub - first, total = G * per_head;
+  const int g0 = p.gsplit > 1 ? (int)blockIdx.z : 0, ng = p.gsplit > 1 ? 1 : G;
+  const int per_head = nsub - first, total = ng * per_head;
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
     for (int i = 0; i < 12; ++i) mbar_init(bar0 + 8u * i, 1);
-    mbar_init(pds_full, 128);
+    mbar_init(pds_full, kComputeThreads);
+    mbar_init(stat_bar, kComputeThreads);
     fence_barrier_init();
     prefetch_tmap(&tmQ); prefetch_tmap(&tmK); prefetch_tmap(&tmV); prefetch_tmap(&tmDO);
   }
@@ -553,7 +596,7 @@ attn_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         const int s = it % KV_STAGES;
         const uint32_t ph = (it / KV_STAGES) & 1u;
         if (!mbar_wait(st_empty(s), ph ^ 1u, abort_flag)) break;
-        const int g = it / per_head, i = first + it % per_head;
+        const int g = g0 + it / per_head, i = first + it % per_head;
         const int bh = (b * p.Hkv + kvh) * G + g;   // query head = kvh * G + g
         const uint32_t dst = st_s + s * 2 * SUB_BYTES;
         mbar_expect_tx(st_full(s), 2 * SUB_BYTES);
@@ -600,32 +643,38 @@ attn_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       mbar_wait_drain(done_bar, 0);
     }
   } else {
-    const int qd = warp & 3, row = qd * 32 + lane;   // key row within the tile
-    const int tid = threadIdx.x - 64;                // 0..127 among the compute threads
+    // two threads per key row: warps 2-5 take query columns 0..31 of each 64-query sub-tile, warps 6-9 32..63
+    const int qd = warp & 3, ch = (warp - 2) >> 2, row = qd * 32 + lane;   // key row within the tile
+    const int tid = threadIdx.x - 64;                                      // 0..255 among the compute threads
     const uint32_t lane_addr = tmem + ((uint32_t)(qd * 32) << 16);
     const int kj = kt * TILE + row;
+    // lse / delta of the 64 queries of an item: threads 0..63 fetch lse, 64..127 delta
+    auto load_stat = [&](int it) -> float {
+      const int g = g0 + it / per_head, i = first + it % per_head;
+      const int bh = (b * p.Hkv + kvh) * G + g;
+      const int qi = i * QSUB + (tid & 63);
+      if (qi >= p.S) return 0.f;
+      return tid < 64 ? p.lse[(int64_t)bh * p.S + qi] * kLog2e : p.delta[(int64_t)bh * p.S + qi];
+    };
+    float nxt = (tid < 128 && total > 0) ? load_stat(0) : 0.f;
     bool ok = true;
     for (int it = 0; it < total; ++it) {
-      const int g = it / per_head, i = first + it % per_head;
-      const int bh = (b * p.Hkv + kvh) * G + g;
-      // stage the 64 lse / delta values of this query sub-tile (previous readers are past their loop).
-      // A thread whose wait gave up keeps arriving at these barriers, so the group leaves together.
-      asm volatile("bar.sync 1, 128;" ::: "memory");
-      if (*abort_flag) { ok = false; break; }
-      {
-        const int qi = i * QSUB + (tid & 63);
-        float val = 0.f;
-        if (qi < p.S) val = tid < 64 ? p.lse[(int64_t)bh * p.S + qi] * kLog2e : p.delta[(int64_t)bh * p.S + qi];
-        stat[tid] = val;
-      }
-      asm volatile("bar.sync 1, 128;" ::: "memory");
-      if (!mbar_wait(sdp_full(it & 1), (it >> 1) & 1u, abort_flag)) { ok = false; continue; }
-      tc_fence_after();
+      const int i = first + it % per_head;
+      float* st = stat + (it & 1) * 2 * QSUB;
+      if (tid < 128) st[tid] = nxt;
+      mbar_arrive(stat_bar);
+      if (!mbar_wait(stat_bar, it & 1u, abort_flag)) ok = false;
+      // the next item's values travel from global memory while this item is processed
+      if (it + 1 < total && tid < 128) nxt = load_stat(it + 1);
+      if (ok && !mbar_wait(sdp_full(it & 1), (it >> 1) & 1u, abort_flag)) ok = false;
       // P^T / dS^T of the previous item must have been consumed before they are overwritten
-      if (!mbar_wait(pds_empty, (it & 1u) ^ 1u, abort_flag)) { ok = false; continue; }
+      if (ok && !mbar_wait(pds_empty, (it & 1u) ^ 1u, abort_flag)) ok = false;
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
       const bool diag = (i * QSUB < kt * TILE + TILE);   // sub-tile overlaps the diagonal block
-#pragma unroll 1
-      for (int c = 0; c < 2; ++c) {
+      {
+        const int c = ch;
         uint32_t rs[32], rp[32];
         float pv[32], dsv[32];
         tmem_ld32(lane_addr + (it & 1) * 64 + c * 32, rs);
@@ -634,10 +683,10 @@ attn_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
 #pragma unroll
         for (int e = 0; e < 32; ++e) {
           const int col = c * 32 + e, qi = i * QSUB + col;
-          const float pr = exp2f(fmaf(__uint_as_float(rs[e]), p.scale_log2, -stat[col]));
+          const float pr = fast_exp2(fmaf(__uint_as_float(rs[e]), p.scale_log2, -st[col]));
           const bool keep = qi < p.S && (!diag || kj <= qi);
           pv[e] = keep ? pr : 0.f;
-          dsv[e] = keep ? pr * (__uint_as_float(rp[e]) - stat[QSUB + col]) : 0.f;
+          dsv[e] = keep ? pr * (__uint_as_float(rp[e]) - st[QSUB + col]) : 0.f;
         }
         store_swizzled32<T>(pt_ptr, row, c * 32, pv);
         store_swizzled32<T>(dst_ptr, row, c * 32, dsv);
@@ -646,29 +695,52 @@ attn_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       fence_proxy_async_smem();
       mbar_arrive(pds_full);
     }
-    if (ok && mbar_wait(acc_full, 0, abort_flag)) {
+    bool fin = ok && mbar_wait(acc_full, 0, abort_flag);
+    fin = __all_sync(0xffffffffu, fin);
+    if (fin) {
       tc_fence_after();
-      T* krow = reinterpret_cast<T*>(p.dk) + (int64_t)b * p.k_bs + (int64_t)kvh * p.k_hs + (int64_t)kj * p.k_ss;
-      T* vrow = reinterpret_cast<T*>(p.dv) + (int64_t)b * p.k_bs + (int64_t)kvh * p.k_hs + (int64_t)kj * p.k_ss;
+      if (p.gsplit > 1) {
+        // fp32 partials of this query head; a second kernel sums the group in a fixed order
+        const int64_t rows = (int64_t)gridDim.y * p.S;
+        float* pk = p.part + (((int64_t)blockIdx.z * 2 + 0) * rows + (int64_t)bk * p.S + kj) * AD;
+        float* pvp = p.part + (((int64_t)blockIdx.z * 2 + 1) * rows + (int64_t)bk * p.S + kj) * AD;
 #pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t rk[32], rv[32];
-        tmem_ld32(lane_addr + 256 + c * 32, rk);
-        tmem_ld32(lane_addr + 384 + c * 32, rv);
-        tmem_ld_wait();
-        if (kj < p.S) {
+        for (int c = 2 * ch; c < 2 * ch + 2; ++c) {
+          uint32_t rk[32], rv[32];
+          tmem_ld32(lane_addr + 256 + c * 32, rk);
+          tmem_ld32(lane_addr + 384 + c * 32, rv);
+          tmem_ld_wait();
+          if (kj < p.S) {
 #pragma unroll
-          for (int g = 0; g < 4; ++g) {
-            uint4 wk, wv;
-            uint32_t* pk = reinterpret_cast<uint32_t*>(&wk);
-            uint32_t* pv2 = reinterpret_cast<uint32_t*>(&wv);
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              pk[e] = pack2<T>(__uint_as_float(rk[g * 8 + 2 * e]) * p.scale, __uint_as_float(rk[g * 8 + 2 * e + 1]) * p.scale);
-              pv2[e] = pack2<T>(__uint_as_float(rv[g * 8 + 2 * e]), __uint_as_float(rv[g * 8 + 2 * e + 1]));
+            for (int g = 0; g < 8; ++g) {
+              *reinterpret_cast<uint4*>(pk + c * 32 + g * 4) = make_uint4(rk[g * 4], rk[g * 4 + 1], rk[g * 4 + 2], rk[g * 4 + 3]);
+              *reinterpret_cast<uint4*>(pvp + c * 32 + g * 4) = make_uint4(rv[g * 4], rv[g * 4 + 1], rv[g * 4 + 2], rv[g * 4 + 3]);
             }
-            *reinterpret_cast<uint4*>(krow + c * 32 + g * 8) = wk;
-            *reinterpret_cast<uint4*>(vrow + c * 32 + g * 8) = wv;
+          }
+        }
+      } else {
+        T* krow = reinterpret_cast<T*>(p.dk) + (int64_t)b * p.k_bs + (int64_t)kvh * p.k_hs + (int64_t)kj * p.k_ss;
+        T* vrow = reinterpret_cast<T*>(p.dv) + (int64_t)b * p.k_bs + (int64_t)kvh * p.k_hs + (int64_t)kj * p.k_ss;
+#pragma unroll 1
+        for (int c = 2 * ch; c < 2 * ch + 2; ++c) {
+          uint32_t rk[32], rv[32];
+          tmem_ld32(lane_addr + 256 + c * 32, rk);
+          tmem_ld32(lane_addr + 384 + c * 32, rv);
+          tmem_ld_wait();
+          if (kj < p.S) {
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+              uint4 wk, wv;
+              uint32_t* pk = reinterpret_cast<uint32_t*>(&wk);
+              uint32_t* pv2 = reinterpret_cast<uint32_t*>(&wv);
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                pk[e] = pack2<T>(__uint_as_float(rk[g * 8 + 2 * e]) * p.scale, __uint_as_float(rk[g * 8 + 2 * e + 1]) * p.scale);
+                pv2[e] = pack2<T>(__uint_as_float(rv[g * 8 + 2 * e]), __uint_as_float(rv[g * 8 + 2 * e + 1]));
+              }
+              *reinterpret_cast<uint4*>(krow + c * 32 + g * 8) = wk;
+              *reinterpret_cast<uint4*>(vrow + c * 32 + g * 8) = wv;
+            }
           }
         }
       }
@@ -679,7 +751,33 @@ attn_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem, 512); }
   if (threadIdx.x == 0 && *abort_flag) flag_status(p.status, Q3_STATUS_WAIT_TIMEOUT);
 }
-constexpr int kDkdvSmem = 2 * TILE_BYTES + KV_STAGES * 2 * SUB_BYTES + 2 * SUB_BYTES + 2 * QSUB * 4 + 1024 + 256;
+constexpr int kDkdvSmem = 2 * TILE_BYTES + KV_STAGES * 2 * SUB_BYTES + 2 * SUB_BYTES + 4 * QSUB * 4 + 1024 + 256;
+
+// Sum the per-query-head fp32 partials of dK / dV in head order, scale dK, round once, store with strides.
+template <typename T>
+__global__ void attn_dkdv_reduce_kernel(const float* __restrict__ part, T* __restrict__ dk, T* __restrict__ dv, int G,
+                                        int64_t rows, int Hkv, int S, int64_t k_ss, int64_t k_hs, int64_t k_bs,
+                                        float scale) {
+  const int64_t total = rows * (AD / 4);
+  for (int64_t idx = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; idx < total; idx += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t row = idx / (AD / 4);
+    const int c = (int)(idx % (AD / 4)) * 4;
+    float4 ak = make_float4(0.f, 0.f, 0.f, 0.f), av = ak;
+    for (int z = 0; z < G; ++z) {
+      const float4 a = *reinterpret_cast<const float4*>(part + (((int64_t)z * 2 + 0) * rows + row) * AD + c);
+      const float4 bq = *reinterpret_cast<const float4*>(part + (((int64_t)z * 2 + 1) * rows + row) * AD + c);
+      ak.x += a.x; ak.y += a.y; ak.z += a.z; ak.w += a.w;
+      av.x += bq.x; av.y += bq.y; av.z += bq.z; av.w += bq.w;
+    }
+    const int64_t sidx = row % S, bkv = row / S, kvh = bkv % Hkv, b = bkv / Hkv;
+    const int64_t off = b * k_bs + kvh * k_hs + sidx * k_ss + c;
+    uint2 wk, wv;
+    wk.x = pack2<T>(ak.x * scale, ak.y * scale); wk.y = pack2<T>(ak.z * scale, ak.w * scale);
+    wv.x = pack2<T>(av.x, av.y); wv.y = pack2<T>(av.z, av.w);
+    *reinterpret_cast<uint2*>(dk + off) = wk;
+    *reinterpret_cast<uint2*>(dv + off) = wv;
+  }
+}
 
 template <typename K> int configure_smem(K kern, int bytes, bool* done) {
   if (!*done) {
@@ -693,6 +791,12 @@ template <typename K> int configure_smem(K kern, int bytes, bool* done) {
 }  // namespace tc
 
 bool attn_tc_available() { return true; }
+
+// One CTA per query head (plus a reduce kernel) when one CTA per key tile would leave SMs idle.
+int attn_bwd_group_split(int64_t B, int64_t Hq, int64_t Hkv, int64_t S) {
+  const int64_t G = Hq / Hkv, ctas = B * Hkv * cdiv(S, tc::TILE);
+  return (G > 1 && ctas < 2 * (int64_t)sm_count()) ? (int)G : 1;
+}
 
 namespace {
 // Element strides over (sequence, head, batch) for layout 0 = [B, H, S, 128] and layout 1 = [B, S, H, 128].
@@ -736,8 +840,8 @@ int attn_fwd_tc(const void* q, const void* k, const void* v, void* out, float* l
 }
 
 int attn_bwd_tc(const void* q, const void* k, const void* v, const void* dout, const float* lse, const float* delta,
-                void* dq, void* dk, void* dv, int64_t B, int64_t Hq, int64_t Hkv, int64_t S, float scale, int dtype,
-                int layout, int* status, cudaStream_t st) {
+                void* dq, void* dk, void* dv, float* partials, int64_t B, int64_t Hq, int64_t Hkv, int64_t S, float scale,
+                int dtype, int layout, int* status, cudaStream_t st) {
   using namespace tc;
   const bool bf16 = dtype == Q3_BF16;
   const Strides sq = strides_for(layout, Hq, S), sk = strides_for(layout, Hkv, S);
@@ -751,24 +855,35 @@ int attn_bwd_tc(const void* q, const void* k, const void* v, const void* dout, c
   if ((rc = make_tmap_4d(&tmDOs, dout, bf16, B, Hq, S, AD, sq.ss, sq.hs, sq.bs, 64, QSUB)) != Q3_OK) return rc;
   AttnBwdParams p{};
   p.lse = lse; p.delta = delta; p.dq = dq; p.dk = dk; p.dv = dv;
+  p.gsplit = attn_bwd_group_split(B, Hq, Hkv, S);
+  p.part = partials;
+  if (p.gsplit > 1 && partials == nullptr) return Q3_ERR_WORKSPACE;
   p.Hq = (int)Hq; p.Hkv = (int)Hkv; p.S = (int)S; p.scale = scale; p.scale_log2 = scale * kLog2e;
   p.q_ss = sq.ss; p.q_hs = sq.hs; p.q_bs = sq.bs; p.k_ss = sk.ss; p.k_hs = sk.hs; p.k_bs = sk.bs;
   p.idesc_kk128 = make_idesc_f16(128, 128, bf16, false, false);
   p.idesc_kk64 = make_idesc_f16(128, 64, bf16, false, false);
   p.idesc_kmn = make_idesc_f16(128, 128, bf16, false, true);
   p.status = status;
-  dim3 gq((unsigned)cdiv(S, TILE), (unsigned)(B * Hq)), gk((unsigned)cdiv(S, TILE), (unsigned)(B * Hkv));
+  dim3 gq((unsigned)cdiv(S, TILE), (unsigned)(B * Hq)), gk((unsigned)cdiv(S, TILE), (unsigned)(B * Hkv), (unsigned)p.gsplit);
+  const int64_t kv_rows = B * Hkv * S;
+  const int red_grid = (int)std::min<int64_t>(cdiv(kv_rows * (AD / 4), 256), (int64_t)sm_count() * 8);
   if (bf16) {
     static bool c1 = false, c2 = false;
     if ((rc = configure_smem(attn_dq_tc_kernel<__nv_bfloat16>, kDqSmem, &c1)) != Q3_OK) return rc;
     if ((rc = configure_smem(attn_dkdv_tc_kernel<__nv_bfloat16>, kDkdvSmem, &c2)) != Q3_OK) return rc;
     attn_dkdv_tc_kernel<__nv_bfloat16><<<gk, kAttnThreads, kDkdvSmem, st>>>(tmQs, tmK, tmV, tmDOs, p);
+    if (p.gsplit > 1)
+      attn_dkdv_reduce_kernel<__nv_bfloat16><<<red_grid, 256, 0, st>>>(partials, (__nv_bfloat16*)dk, (__nv_bfloat16*)dv, p.gsplit, kv_rows,
+                                                                     (int)Hkv, (int)S, sk.ss, sk.hs, sk.bs, scale);
     attn_dq_tc_kernel<__nv_bfloat16><<<gq, kAttnThreads, kDqSmem, st>>>(tmQ, tmK, tmV, tmDO, p);
   } else {
     static bool c1 = false, c2 = false;
     if ((rc = configure_smem(attn_dq_tc_kernel<__half>, kDqSmem, &c1)) != Q3_OK) return rc;
     if ((rc = configure_smem(attn_dkdv_tc_kernel<__half>, kDkdvSmem, &c2)) != Q3_OK) return rc;
     attn_dkdv_tc_kernel<__half><<<gk, kAttnThreads, kDkdvSmem, st>>>(tmQs, tmK, tmV, tmDOs, p);
+    if (p.gsplit > 1)
+      attn_dkdv_reduce_kernel<__half><<<red_grid, 256, 0, st>>>(partials, (__half*)dk, (__half*)dv, p.gsplit, kv_rows, (int)Hkv, (int)S,
+                                                              sk.ss, sk.hs, sk.bs, scale);
     attn_dq_tc_kernel<__half><<<gq, kAttnThreads, kDqSmem, st>>>(tmQ, tmK, tmV, tmDO, p);
   }
   return launch_status();

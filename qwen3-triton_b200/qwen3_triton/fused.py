@@ -219,12 +219,23 @@ class FusedDecoderLayer(TritonDecoderLayer):
         return FusedLayerFn.apply(resid, delta, cos, sin, meta, self.recompute, *self.weights())
 
 
+class AddNorm(HFOrderNorm):
+    """Final norm taking the (resid, delta) pair; called as a module so that FSDP's pre-forward hook has
+    gathered its weight."""
+
+    def forward(self, resid, delta=None):
+        from .kernels.norm import add_rms_norm, rms_norm
+        if delta is None:
+            return rms_norm(resid, self.weight, self.eps)
+        return add_rms_norm(delta, resid, self.weight, self.eps)[0]
+
+
 class FusedBackbone(TritonQwen3Model):
     decoder_class = FusedDecoderLayer
 
     def __init__(self, c, options):
         super().__init__(c, options)
-        self.norm = HFOrderNorm(c.hidden_size, c.rms_norm_eps)
+        self.norm = AddNorm(c.hidden_size, c.rms_norm_eps)
 
     def set_recompute(self, flag):
         for layer in self.layers:
@@ -232,7 +243,6 @@ class FusedBackbone(TritonQwen3Model):
 
     def forward(self, ids, position_ids=None):
         from ._model import position_ids_for
-        from .kernels.norm import add_rms_norm
         x = self.embed_tokens(ids)
         if position_ids is None:
             position_ids = position_ids_for(ids)
@@ -246,7 +256,4 @@ class FusedBackbone(TritonQwen3Model):
         resid, delta = x, None
         for layer in self.layers:
             resid, delta = layer(resid, delta, positions)
-        if delta is None:
-            return self.norm(resid)
-        y, _ = add_rms_norm(delta, resid, self.norm.weight, self.norm.eps)
-        return y
+        return self.norm(resid, delta)
