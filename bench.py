@@ -317,8 +317,10 @@ def run_fsdp(args):
     with torch.device(device):
         model = model_for_variant(cfg, os.environ.get("Q3_BENCH_VARIANT", "b200_fused"))
     comm = NcclCollectives()
+    ckpt = os.environ.get("Q3_BENCH_CHECKPOINT", "selective")     # 'selective' or 'full' per-layer recomputation
     model = shard_vocab_loss_model(model, keep_full_layers=layers, checkpoint_every=1,
-                                   skip_embedding_backward_gather=True, fused_vocab_dw=True, communication=None)
+                                   skip_embedding_backward_gather=True, fused_vocab_dw=True, communication=None,
+                                   checkpoint_mode=ckpt)
     hooks = configure(model, comm)
     decoder = [p for n, p in model.named_parameters() if not n.startswith("lm_head.")]
     opt = TritonAdamW([dict(params=decoder), dict(params=[model.lm_head.weight])], lr=1e-4, betas=(0.9, 0.95),
@@ -366,6 +368,14 @@ def run_fsdp(args):
     e2e_ms = float(t.item())
     clocks = sampler.stop() if sampler else None
 
+    if os.environ.get("Q3_BENCH_PROFILE") and rank == 0:
+        from torch.profiler import ProfilerActivity, profile
+        with profile(activities=[ProfilerActivity.CUDA, ProfilerActivity.CPU]) as prof:
+            step(dev_ids[0])
+            torch.cuda.synchronize()
+        sys.stderr.write(prof.key_averages().table(sort_by="cuda_time_total", row_limit=25, max_name_column_width=70) + "\n")
+    elif os.environ.get("Q3_BENCH_PROFILE"):
+        step(dev_ids[0])
     counter.profile = True
     step(dev_ids[0])
     torch.cuda.synchronize()
@@ -383,7 +393,7 @@ def run_fsdp(args):
             "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
             "data": "synthetic",
             "config": {"workload": "qwen3-8b %d layers under FSDP2, microbatch 1x2048 per GPU, vocab-parallel head, "
-                                   "per-layer recompute, AdamW (BASELINE config 5)" % layers,
+                                   "per-layer %s activation recompute, AdamW (BASELINE config 5)" % (layers, ckpt),
                        "global_batch": batch * world, "seq_len": seq, "parallelism": "fsdp%d" % world,
                        "l2": "weights and activations >> L2", "mfu_of_%s_peak_per_gpu" % peak_kind: mfu,
                        "tokens_per_s_per_gpu": value / world, "last_loss": last,

@@ -9,9 +9,12 @@ than Python can launch them. This module keeps the same math and the same parame
     write that layout through TMA, so no transpose copy exists;
   * carries the residual stream between layers as a pair (resid, delta) and folds `resid + delta` into the
     next RMSNorm (q3_add_rmsnorm_fwd/bwd), so no stand-alone residual-add kernel runs;
-  * optionally recomputes the layer's forward inside its own backward (`recompute=True`, the per-layer
-    activation checkpointing of the reference's training/fsdp/activation_checkpoint.py:15-19) without the
-    generic checkpoint wrapper.
+  * does per-layer activation checkpointing inside its own backward, without the generic checkpoint wrapper
+    (reference: training/fsdp/activation_checkpoint.py:15-19). `recompute` = 0 keeps every intermediate,
+    2 ("full") keeps only the layer input and re-runs the whole forward, 1 ("selective") keeps the outputs of
+    the GEMMs and of attention (x, q, k, v, o, lse, x1, gate, up: about 175 MB per layer at 2048 tokens) and
+    re-runs only the bandwidth-bound pieces (two RMSNorms, QK-norm+RoPE, SwiGLU) - all of the memory saving
+    that matters on a 180 GB GPU for 4 % instead of 33 % extra work.
 
 Requires bf16/fp16 tensors and head_dim 128 (the tensor-core attention path); other shapes use the
 operator-level modules.
@@ -126,6 +129,23 @@ def layer_forward(resid, delta, cos, sin, w, meta):
 
 
 _KEEP = ('h', 'x', 'inv1', 'q', 'k', 'v', 'qn', 'invq', 'kn', 'invk', 'o', 'lse', 'h2', 'x1', 'inv2', 'g', 'u', 'y')
+_KEEP_SELECTIVE = ('x', 'q', 'k', 'v', 'o', 'lse', 'x1', 'g', 'u')
+
+
+def recompute_cheap(r, cos, sin, w, meta):
+    """Rebuild the bandwidth-bound intermediates (h, qn, kn, h2, y and the saved inverse RMS values) from the
+    tensors kept by selective checkpointing."""
+    b, s, hq, hk, d, eps = meta
+    t = r['x'].shape[0]
+    w_in, wq, wk, wv, wo, wqn, wkn, w_post, wg, wu, wd = w
+    r['h'], _, r['inv1'] = _norm_fwd(r['x'], None, w_in, eps)
+    r['qn'], r['invq'] = _norm_rope_fwd(r['q'], wqn, cos, sin, t, hq, d, eps)
+    r['kn'], r['invk'] = _norm_rope_fwd(r['k'], wkn, cos, sin, t, hk, d, eps)
+    r['h2'], _, r['inv2'] = _norm_fwd(r['x1'], None, w_post, eps)
+    r['y'] = torch.empty_like(r['g'])
+    _abi.call('q3_swiglu_fwd', r['g'].data_ptr(), r['u'].data_ptr(), r['y'].data_ptr(), r['g'].numel(),
+              _abi.dt(r['g'].dtype), _abi.stream())
+    return r
 
 
 class FusedLayerFn(torch.autograd.Function):
@@ -136,9 +156,12 @@ class FusedLayerFn(torch.autograd.Function):
         r2 = resid.reshape(-1, shape[-1])
         d2 = delta.reshape(-1, shape[-1]) if delta is not None else None
         r = layer_forward(r2, d2, cos, sin, weights, meta)
+        recompute = int(recompute)
         ctx.meta, ctx.recompute, ctx.shape, ctx.has_delta = meta, recompute, shape, delta is not None
-        if recompute:
+        if recompute == 2:
             ctx.save_for_backward(r2, d2 if d2 is not None else r2, cos, sin, *weights)
+        elif recompute == 1:
+            ctx.save_for_backward(cos, sin, *weights, *[r[k] for k in _KEEP_SELECTIVE])
         else:
             ctx.save_for_backward(cos, sin, *weights, *[r[k] for k in _KEEP])
         return r['x1'].view(shape), r['m'].view(shape)
@@ -146,9 +169,14 @@ class FusedLayerFn(torch.autograd.Function):
     @staticmethod
     def backward(ctx, g_x1, g_m):
         b, s, hq, hk, d, eps = ctx.meta
-        if ctx.recompute:
+        if ctx.recompute == 2:
             r2, d2, cos, sin, *weights = ctx.saved_tensors
             r = layer_forward(r2, d2 if ctx.has_delta else None, cos, sin, weights, ctx.meta)
+        elif ctx.recompute == 1:
+            saved = ctx.saved_tensors
+            cos, sin = saved[0], saved[1]
+            weights = saved[2:13]
+            r = recompute_cheap(dict(zip(_KEEP_SELECTIVE, saved[13:])), cos, sin, weights, ctx.meta)
         else:
             saved = ctx.saved_tensors
             cos, sin = saved[0], saved[1]
@@ -203,7 +231,7 @@ class FusedDecoderLayer(TritonDecoderLayer):
         self.mlp = MLP(c, options)
         self.input_layernorm = HFOrderNorm(c.hidden_size, c.rms_norm_eps)
         self.post_attention_layernorm = HFOrderNorm(c.hidden_size, c.rms_norm_eps)
-        self.recompute = False
+        self.recompute = 0      # 0 none, 1 selective, 2 full (see module docstring)
 
     def weights(self):
         a, m = self.self_attn, self.mlp
@@ -237,9 +265,11 @@ class FusedBackbone(TritonQwen3Model):
         super().__init__(c, options)
         self.norm = AddNorm(c.hidden_size, c.rms_norm_eps)
 
-    def set_recompute(self, flag):
+    def set_recompute(self, level):
+        """0 / False: keep everything; 1 / 'selective'; 2 / True / 'full'."""
+        level = {'none': 0, 'selective': 1, 'full': 2, False: 0, True: 2}.get(level, level)
         for layer in self.layers:
-            layer.recompute = bool(flag)
+            layer.recompute = int(level)
 
     def forward(self, ids, position_ids=None):
         from ._model import position_ids_for

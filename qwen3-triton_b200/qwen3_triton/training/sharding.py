@@ -54,7 +54,7 @@ class VocabLossQwen3(PrecisionQwen3ForCausalLM):
 
 
 def shard_vocab_loss_model(model, *, keep_full_layers, checkpoint_every, skip_embedding_backward_gather,
-                           fused_vocab_dw=False, communication=None, mesh=None):
+                           fused_vocab_dw=False, communication=None, mesh=None, checkpoint_mode='full'):
     if model.config.tie_word_embeddings:
         raise ValueError('Untied head required')
     if not 0 <= keep_full_layers <= len(model.model.layers):
@@ -75,7 +75,8 @@ def shard_vocab_loss_model(model, *, keep_full_layers, checkpoint_every, skip_em
         layer = layer.float()
         if index in checkpointed:
             if hasattr(layer, 'recompute'):
-                layer.recompute = True      # fused layers recompute inside their own backward
+                # fused layers checkpoint inside their own backward ('full' or 'selective')
+                layer.recompute = {'full': 2, 'selective': 1}[checkpoint_mode]
             else:
                 layer = wrap_decoder_checkpoint(layer, mode='full')
         body.layers[index] = layer

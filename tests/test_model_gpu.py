@@ -112,7 +112,11 @@ def test_fused_decoder_layers_match_operator_graph_and_oracle(seq):
         return out, {n: p.grad.clone() for n, p in model.named_parameters()}
 
     out_f, g_f = run('b200_fused')
-    out_r, g_r = run('b200_fused', recompute=True)
+    out_r, g_r = run('b200_fused', recompute='full')
+    out_s, g_s = run('b200_fused', recompute='selective')
+    assert torch.equal(out_f.loss, out_s.loss)
+    for n in g_f:
+        assert torch.equal(g_f[n], g_s[n]), n
     out_o, g_o = run('triton_optimized')
     assert torch.equal(out_f.loss, out_r.loss)
     for n in g_f:
