@@ -284,8 +284,17 @@ def run_ours(args):
 
 def census(counter):
     by_name, gemm_flops = {}, 0.0
+    shapes = {}
     for name, a, s, e in counter.records:
         by_name[name] = by_name.get(name, 0.0) + s.elapsed_time(e)
+        if name == "q3_gemm":
+            key = (a[7], a[8], a[9], "A:%s B:%s" % ("K" if a[2] == 1 else "MN", "K" if a[4] == 1 else "MN"))
+            cnt, tot = shapes.get(key, (0, 0.0))
+            shapes[key] = (cnt + 1, tot + s.elapsed_time(e))
+    if os.environ.get("Q3_BENCH_PROFILE"):
+        for (m, n, k, lay), (cnt, tot) in sorted(shapes.items(), key=lambda kv: -kv[1][1]):
+            sys.stderr.write("gemm %6d x %6d x %6d %-10s n=%3d total %8.3f ms avg %8.1f us %7.1f TFLOP/s\n" % (
+                m, n, k, lay, cnt, tot, tot / cnt * 1e3, 2.0 * m * n * k * cnt / tot / 1e9))
         if name == "q3_gemm":
             gemm_flops += 2.0 * a[7] * a[8] * a[9]
         elif name == "q3_gate_up_swiglu_fwd":
@@ -320,7 +329,7 @@ def run_fsdp(args):
     ckpt = os.environ.get("Q3_BENCH_CHECKPOINT", "selective")     # 'selective' or 'full' per-layer recomputation
     model = shard_vocab_loss_model(model, keep_full_layers=layers, checkpoint_every=1,
                                    skip_embedding_backward_gather=True, fused_vocab_dw=True, communication=None,
-                                   checkpoint_mode=ckpt)
+                                   checkpoint_mode=ckpt, layers_per_unit=int(os.environ.get("Q3_BENCH_LAYERS_PER_UNIT", "4")))
     hooks = configure(model, comm)
     decoder = [p for n, p in model.named_parameters() if not n.startswith("lm_head.")]
     opt = TritonAdamW([dict(params=decoder), dict(params=[model.lm_head.weight])], lr=1e-4, betas=(0.9, 0.95),
@@ -374,6 +383,8 @@ def run_fsdp(args):
             step(dev_ids[0])
             torch.cuda.synchronize()
         sys.stderr.write(prof.key_averages().table(sort_by="cuda_time_total", row_limit=25, max_name_column_width=70) + "\n")
+        (ROOT / "gpurun_out").mkdir(exist_ok=True)
+        prof.export_chrome_trace(str(ROOT / "gpurun_out" / "trace_rank0.json"))
     elif os.environ.get("Q3_BENCH_PROFILE"):
         step(dev_ids[0])
     counter.profile = True
