@@ -180,6 +180,9 @@ def build_single_gpu(cfg, device):
     with torch.device(device):
         model = model_for_variant(cfg, os.environ.get("Q3_BENCH_VARIANT", "b200_fused"))
     model.to(device)   # buffers created on the CPU on purpose (rotary frequencies) move here
+    if hasattr(model, "fused_loss"):
+        # "1": hidden -> loss without logits in HBM (one extra logits GEMM in backward; measured 8 ms slower per step here)
+        model.fused_loss = os.environ.get("Q3_BENCH_FUSED_LOSS", "0") == "1"
     masters = MasterWeights(model).fuse_into_optimizer()
     opt = TritonAdamW(masters.parameters(), lr=1e-4, betas=(0.9, 0.95), weight_decay=0.1)
     return model, masters, opt
@@ -330,6 +333,7 @@ def run_fsdp(args):
     model = shard_vocab_loss_model(model, keep_full_layers=layers, checkpoint_every=1,
                                    skip_embedding_backward_gather=True, fused_vocab_dw=True, communication=None,
                                    checkpoint_mode=ckpt, layers_per_unit=int(os.environ.get("Q3_BENCH_LAYERS_PER_UNIT", "4")))
+    model.lm_head.fused = os.environ.get("Q3_BENCH_FUSED_LOSS", "0") == "1"
     hooks = configure(model, comm)
     decoder = [p for n, p in model.named_parameters() if not n.startswith("lm_head.")]
     opt = TritonAdamW([dict(params=decoder), dict(params=[model.lm_head.weight])], lr=1e-4, betas=(0.9, 0.95),

@@ -230,6 +230,39 @@ int q3_gate_up_swiglu_fwd(const void* x, const void* w_gate, const void* w_up, v
 int q3_gate_up_path(const void* x, const void* w_gate, const void* w_up, const void* gate, const void* up,
                     const void* y, int64_t M, int64_t N, int64_t K, int dtype);
 
+/* C (fp32, contiguous) += A * B; operands as q3_gemm, tensor-core path only (Q3_ERR_ALIGN otherwise). Used to
+ * accumulate the hidden-state gradient of the vocabulary head over vocabulary chunks in fp32, as the reference keeps
+ * partial_dx in fp32 (qwen3_triton/training/vocab_parallel.py:76). */
+int q3_gemm_acc_f32(const void* a, int64_t a_sm, int64_t a_sk, const void* b, int64_t b_sk, int64_t b_sn, float* c,
+                    int64_t M, int64_t N, int64_t K, int in_dtype, int* status, q3_stream_t stream);
+
+/* ---- fused lm_head + cross-entropy (no logits in memory) ---------------------------------------------------
+ * The reference materialises the logits [W*r, V/W] and their gradient (qwen3_triton/training/vocab_parallel.py:52,75;
+ * kernels/vocab_ce.py:78-112). Here the projection runs on the tensor cores and the softmax statistics / gradient are
+ * computed in the GEMM epilogue from tensor memory:
+ *   q3_shift_labels      labels_eff[b*S+s] = labels[b,s+1] (s < S-1) else ignore_index   (the shift of kernels/loss.py:9,20)
+ *   q3_linear_ce_stats   per (row, 256-column tile): max and sum-exp of the logits rounded to `dtype`; target logit
+ *                        where the vocabulary slice [vocab_start, vocab_start+V_local) owns the label
+ *   q3_linear_ce_combine lse_local[row] from the tile partials (tiles = q3_linear_ce_tiles(V_local))
+ *   q3_linear_ce_finish  optional lse = maximum + log(pack[0]) after the two all-reduces, then per data rank
+ *                        losses / counts / means (kernels/vocab_ce.py:34-53 on physical rows)
+ *   q3_linear_ce_grad    dZ [M, Vc] of one vocabulary chunk, recomputing that chunk of the logits */
+int64_t q3_linear_ce_tiles(int64_t V_local);
+int q3_shift_labels(const int64_t* labels, int64_t* labels_eff, int64_t rows, int64_t S, int64_t ignore_index,
+                    int64_t vocab_total, int* status, q3_stream_t stream);
+int q3_linear_ce_stats(const void* hidden, const void* weight, const int64_t* labels_eff, float* part_max,
+                       float* part_sum, float* target, int64_t M, int64_t V_local, int64_t K, int64_t vocab_start,
+                       int64_t ignore_index, int dtype, int* status, q3_stream_t stream);
+int q3_linear_ce_combine(const float* part_max, const float* part_sum, float* lse_local, int64_t rows, int64_t tiles,
+                         q3_stream_t stream);
+int q3_linear_ce_finish(const float* maximum, const float* pack, float* lse, const float* target,
+                        const int64_t* labels_eff, float* losses, int* counts, float* means, int64_t rows,
+                        int64_t rows_per_rank, int64_t ignore_index, int* status, q3_stream_t stream);
+int q3_linear_ce_grad(const void* hidden, const void* weight_chunk, const int64_t* labels_eff, const float* lse,
+                      const float* upstream, const int* counts, void* dz, int64_t M, int64_t Vc, int64_t K,
+                      int64_t vocab_start, int64_t rows_per_rank, int64_t ignore_index, int dtype, int* status,
+                      q3_stream_t stream);
+
 /* ---- attention ------------------------------------------------------------------------------ */
 
 /* Causal grouped-query attention. q/out [B,Hq,S,D], k/v [B,Hkv,S,D] contiguous, kv head = q head / (Hq/Hkv);

@@ -181,6 +181,20 @@ def main():
                 report("gemm_q_dgrad", timer(lambda: matmul(dy, Bm)), flops=2.0 * M * N * K)
                 report("gemm_q_wgrad", timer(lambda: matmul(dy.t(), A)), flops=2.0 * M * N * K)
             del A, Bm
+    if want("linear_ce"):
+        from qwen3_triton.kernels.fused_loss import fused_linear_cross_entropy
+        S = min(4096, T)
+        B = T // S
+        hid = torch.randn(B, S, H, device=dev).to(bf).requires_grad_(True)
+        wh = (torch.randn(V, H, device=dev) * 0.02).to(bf).requires_grad_(True)
+        lab = torch.randint(0, V, (B, S), device=dev)
+        report("linear_ce_fwd (no logits)", timer(lambda: fused_linear_cross_entropy(hid, wh, lab)), flops=2.0 * T * H * V)
+
+        def fb():
+            hid.grad = wh.grad = None
+            fused_linear_cross_entropy(hid, wh, lab).backward()
+        report("linear_ce_fwd+bwd (no logits)", timer(fb), flops=8.0 * T * H * V)
+        del hid, wh
     for (B, S) in [(4, 4096), (8, 2048), (2, 8192)]:
         name = f"attn_B{B}_S{S}"
         if want("attn") or want(name):

@@ -47,6 +47,15 @@ struct GemmParams {
   int a_mn, b_mn;   // operand is MN-major
   int prefetch;     // issue L2 prefetches ahead of the smem ring
   int* status;
+  // cross-entropy epilogues
+  const int64_t* labels;   // effective label per row (ignore_index where the row is not scored)
+  const float* lse;        // per row (EPI_CE_GRAD)
+  const float* ups;        // upstream gradient per data rank
+  const int* counts;       // valid-target count per data rank
+  int64_t rows_per_rank, vocab_start, ignore;
+  float* part_max;         // [M][tiles_n] (EPI_CE_STATS)
+  float* part_sum;
+  float* target;           // [M], must be zero-filled by the caller
 };
 
 template <int BN> struct Cfg {
@@ -104,11 +113,20 @@ __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, 
   ni = in / height;
 }
 
-// GATE_UP = false: C = A*B.  GATE_UP = true: BN must be 256; B tile = [W_gate rows | W_up rows].
-template <int BN, typename TO, bool GATE_UP>
+// Epilogues:
+//   EPI_STORE    C = A*B (TO = bf16 / fp16 / fp32)
+//   EPI_GATE_UP  BN must be 256; B tile = [W_gate rows | W_up rows]; stores G, U and silu(G)*U
+//   EPI_ACC_F32  C (fp32) += A*B
+//   EPI_CE_STATS A*B are logits that are never stored: per row and N-tile the (max, sum exp) of the logits rounded
+//                to TO, and the target logit where the tile owns the row's label
+//   EPI_CE_GRAD  stores dZ = (exp(z - lse[row]) - onehot) * upstream[source] / count[source] for the logits z
+enum { EPI_STORE = 0, EPI_GATE_UP = 1, EPI_ACC_F32 = 2, EPI_CE_STATS = 3, EPI_CE_GRAD = 4 };
+
+template <int BN, typename TO, int EPI>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                const __grid_constant__ CUtensorMap tmB2, const GemmParams p) {
+  constexpr bool GATE_UP = (EPI == EPI_GATE_UP);
   using C = Cfg<BN>;
   extern __shared__ uint8_t smem_raw[];
   // 1024-byte alignment keeps the 128-byte swizzle phase identical for TMA and UMMA.
@@ -257,7 +275,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       tc_fence_after();
       const int64_t row = (int64_t)mi * BM + q * 32 + lane;
       const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN;
-      if constexpr (!GATE_UP) {
+      if constexpr (EPI == EPI_STORE) {
         const int64_t n0 = (int64_t)ni * BN;
         TO* crow = reinterpret_cast<TO*>(p.c0) + row * p.N + n0;
 #pragma unroll 1
@@ -266,6 +284,84 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           tmem_ld32(t_row + c * 32, r);
           tmem_ld_wait();
           if (row < p.M && n0 + c * 32 < p.N) store_chunk32<TO>(crow + c * 32, r, n0 + c * 32, p.N);
+        }
+      } else if constexpr (EPI == EPI_ACC_F32) {
+        const int64_t n0 = (int64_t)ni * BN;
+        float* crow = reinterpret_cast<float*>(p.c0) + row * p.N + n0;
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld32(t_row + c * 32, r);
+          tmem_ld_wait();
+          if (row < p.M) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              if (n0 + c * 32 + 4 * j + 4 <= p.N) {
+                float4 o = *reinterpret_cast<const float4*>(crow + c * 32 + 4 * j);
+                o.x += __uint_as_float(r[4 * j]); o.y += __uint_as_float(r[4 * j + 1]);
+                o.z += __uint_as_float(r[4 * j + 2]); o.w += __uint_as_float(r[4 * j + 3]);
+                *reinterpret_cast<float4*>(crow + c * 32 + 4 * j) = o;
+              }
+            }
+          }
+        }
+      } else if constexpr (EPI == EPI_CE_STATS) {
+        const int64_t n0 = (int64_t)ni * BN;
+        const int64_t label = row < p.M ? p.labels[row] : p.ignore;
+        const int64_t hot = label - p.vocab_start - n0;   // column of the label inside this tile, if any
+        float mx = -3.0e38f, sum = 0.f;
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld32(t_row + c * 32, r);
+          tmem_ld_wait();
+          if (n0 + c * 32 < p.N) {
+            float z[32];
+            float cm = -3.0e38f;
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              z[j] = to_f32<TO>(from_f32<TO>(__uint_as_float(r[j])));   // the loss is defined on the rounded logits
+              if (n0 + c * 32 + j < p.N) cm = fmaxf(cm, z[j]);
+              if (c * 32 + j == hot && label != p.ignore && row < p.M) p.target[row] = z[j];
+            }
+            const float nm = fmaxf(mx, cm);
+            float acc_s = sum * __expf(mx - nm);
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (n0 + c * 32 + j < p.N) acc_s += __expf(z[j] - nm);
+            mx = nm; sum = acc_s;
+          }
+        }
+        if (row < p.M) {
+          p.part_max[row * p.tiles_n + ni] = mx;
+          p.part_sum[row * p.tiles_n + ni] = sum;
+        }
+      } else if constexpr (EPI == EPI_CE_GRAD) {
+        const int64_t n0 = (int64_t)ni * BN;
+        TO* crow = reinterpret_cast<TO*>(p.c0) + row * p.N + n0;
+        const int64_t label = row < p.M ? p.labels[row] : p.ignore;
+        const bool valid = label != p.ignore;
+        const int64_t hot = label - p.vocab_start - n0;
+        float l = 0.f, scale = 0.f;
+        if (valid) {
+          const int64_t source = row / p.rows_per_rank;
+          l = p.lse[row];
+          scale = p.ups[source] / (float)p.counts[source];
+        }
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld32(t_row + c * 32, r);
+          tmem_ld_wait();
+          if (row < p.M && n0 + c * 32 < p.N) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              const float z = to_f32<TO>(from_f32<TO>(__uint_as_float(r[j])));
+              const float g = valid ? (__expf(z - l) - (c * 32 + j == hot ? 1.f : 0.f)) * scale : 0.f;
+              r[j] = __float_as_uint(g);
+            }
+            store_chunk32<TO>(crow + c * 32, r, n0 + c * 32, p.N);
+          }
         }
       } else {
         const int64_t n0 = (int64_t)ni * (BN / 2);
@@ -321,8 +417,9 @@ inline bool classify(const void* ptr, int64_t s_outer, int64_t s_k, int64_t oute
   return false;
 }
 
-template <int BN, typename TO, bool GATE_UP>
+template <int BN, typename TO, int EPI>
 int launch_gemm(const Operand& A, const Operand& B, const void* b2, GemmParams& p, bool bf16, cudaStream_t st) {
+  constexpr bool GATE_UP = (EPI == EPI_GATE_UP);
   using C = Cfg<BN>;
   CUtensorMap tmA, tmB, tmB2;
   int rc;
@@ -350,7 +447,7 @@ int launch_gemm(const Operand& A, const Operand& B, const void* b2, GemmParams& 
   }
   const int64_t tiles = (int64_t)p.tiles_m * p.tiles_n;
   const int grid = (int)(tiles < sm_count() ? tiles : sm_count());
-  auto kern = gemm_tc_kernel<BN, TO, GATE_UP>;
+  auto kern = gemm_tc_kernel<BN, TO, EPI>;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
@@ -406,13 +503,13 @@ extern "C" int q3_gemm(const void* a, int64_t a_sm, int64_t a_sk, const void* b,
   const bool bf16 = in_dtype == Q3_BF16;
   const int bn = tc::pick_bn(M, N);
   if (out_dtype == Q3_F32)
-    return bn == 256 ? tc::launch_gemm<256, float, false>(A, B, nullptr, p, bf16, st)
-                     : tc::launch_gemm<128, float, false>(A, B, nullptr, p, bf16, st);
+    return bn == 256 ? tc::launch_gemm<256, float, tc::EPI_STORE>(A, B, nullptr, p, bf16, st)
+                     : tc::launch_gemm<128, float, tc::EPI_STORE>(A, B, nullptr, p, bf16, st);
   if (bf16)
-    return bn == 256 ? tc::launch_gemm<256, __nv_bfloat16, false>(A, B, nullptr, p, bf16, st)
-                     : tc::launch_gemm<128, __nv_bfloat16, false>(A, B, nullptr, p, bf16, st);
-  return bn == 256 ? tc::launch_gemm<256, __half, false>(A, B, nullptr, p, bf16, st)
-                   : tc::launch_gemm<128, __half, false>(A, B, nullptr, p, bf16, st);
+    return bn == 256 ? tc::launch_gemm<256, __nv_bfloat16, tc::EPI_STORE>(A, B, nullptr, p, bf16, st)
+                     : tc::launch_gemm<128, __nv_bfloat16, tc::EPI_STORE>(A, B, nullptr, p, bf16, st);
+  return bn == 256 ? tc::launch_gemm<256, __half, tc::EPI_STORE>(A, B, nullptr, p, bf16, st)
+                   : tc::launch_gemm<128, __half, tc::EPI_STORE>(A, B, nullptr, p, bf16, st);
 }
 
 // 1 if q3_gate_up_swiglu_fwd runs the fused tensor-core kernel for these arguments.
@@ -440,6 +537,65 @@ extern "C" int q3_gate_up_swiglu_fwd(const void* x, const void* w_gate, const vo
   tc::Operand A{x, false, K}, B{w_gate, false, K};
   tc::GemmParams p{};
   p.c0 = gate; p.c1 = up; p.c2 = y; p.M = M; p.N = N; p.K = K; p.status = status;
-  if (dtype == Q3_BF16) return tc::launch_gemm<256, __nv_bfloat16, true>(A, B, w_up, p, true, st);
-  return tc::launch_gemm<256, __half, true>(A, B, w_up, p, false, st);
+  if (dtype == Q3_BF16) return tc::launch_gemm<256, __nv_bfloat16, tc::EPI_GATE_UP>(A, B, w_up, p, true, st);
+  return tc::launch_gemm<256, __half, tc::EPI_GATE_UP>(A, B, w_up, p, false, st);
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// C (fp32, contiguous [M,N]) += A * B. Same operand rules as q3_gemm; tensor-core path only.
+extern "C" int q3_gemm_acc_f32(const void* a, int64_t a_sm, int64_t a_sk, const void* b, int64_t b_sk, int64_t b_sn,
+                               float* c, int64_t M, int64_t N, int64_t K, int in_dtype, int* status,
+                               q3_stream_t stream) {
+  if (!a || !b || !c) return Q3_ERR_ARG;
+  if (!q3_gemm_path(a, a_sm, a_sk, b, b_sk, b_sn, c, M, N, K, in_dtype, Q3_F32)) return Q3_ERR_ALIGN;
+  tc::Operand A, B;
+  tc::classify(a, a_sm, a_sk, M, K, &A);
+  tc::classify(b, b_sn, b_sk, N, K, &B);
+  tc::GemmParams p{};
+  p.c0 = c; p.M = M; p.N = N; p.K = K; p.status = status;
+  return tc::launch_gemm<256, float, tc::EPI_ACC_F32>(A, B, nullptr, p, in_dtype == Q3_BF16, (cudaStream_t)stream);
+}
+
+extern "C" int64_t q3_linear_ce_tiles(int64_t V_local) { return q3::cdiv(V_local, 256); }
+
+// Logits = hidden [M,K] * weight[V_local,K]^T are produced tile by tile in tensor memory and reduced to
+// per-(row, 256-column tile) softmax statistics in the epilogue; they are never written to memory.
+extern "C" int q3_linear_ce_stats(const void* hidden, const void* weight, const int64_t* labels_eff, float* part_max,
+                                  float* part_sum, float* target, int64_t M, int64_t V_local, int64_t K,
+                                  int64_t vocab_start, int64_t ignore_index, int dtype, int* status,
+                                  q3_stream_t stream) {
+  if (!hidden || !weight || !labels_eff || !part_max || !part_sum || !target) return Q3_ERR_ARG;
+  if (M < 1 || V_local < 1 || K < 1) return Q3_ERR_SHAPE;
+  if ((dtype != Q3_BF16 && dtype != Q3_F16) || (K % 8) || !aligned16(hidden) || !aligned16(weight)) return Q3_ERR_ALIGN;
+  cudaStream_t st = (cudaStream_t)stream;
+  cudaError_t e = cudaMemsetAsync(target, 0, (size_t)M * 4, st);
+  if (e != cudaSuccess) return Q3_ERR_CUDA - (int)e;
+  tc::Operand A{hidden, false, K}, B{weight, false, K};
+  tc::GemmParams p{};
+  p.M = M; p.N = V_local; p.K = K; p.status = status;
+  p.labels = labels_eff; p.vocab_start = vocab_start; p.ignore = ignore_index;
+  p.part_max = part_max; p.part_sum = part_sum; p.target = target;
+  if (dtype == Q3_BF16) return tc::launch_gemm<256, __nv_bfloat16, tc::EPI_CE_STATS>(A, B, nullptr, p, true, st);
+  return tc::launch_gemm<256, __half, tc::EPI_CE_STATS>(A, B, nullptr, p, false, st);
+}
+
+// dZ [M, Vc] for a slice of Vc vocabulary rows of `weight_chunk` starting at global index vocab_start:
+// recomputes that slice of the logits on the tensor cores and applies the softmax gradient in the epilogue.
+extern "C" int q3_linear_ce_grad(const void* hidden, const void* weight_chunk, const int64_t* labels_eff,
+                                 const float* lse, const float* upstream, const int* counts, void* dz, int64_t M,
+                                 int64_t Vc, int64_t K, int64_t vocab_start, int64_t rows_per_rank,
+                                 int64_t ignore_index, int dtype, int* status, q3_stream_t stream) {
+  if (!hidden || !weight_chunk || !labels_eff || !lse || !upstream || !counts || !dz) return Q3_ERR_ARG;
+  if (M < 1 || Vc < 1 || K < 1 || rows_per_rank < 1) return Q3_ERR_SHAPE;
+  if ((dtype != Q3_BF16 && dtype != Q3_F16) || (K % 8) || (Vc % 8) || !aligned16(hidden) || !aligned16(weight_chunk) ||
+      !aligned16(dz))
+    return Q3_ERR_ALIGN;
+  tc::Operand A{hidden, false, K}, B{weight_chunk, false, K};
+  tc::GemmParams p{};
+  p.c0 = dz; p.M = M; p.N = Vc; p.K = K; p.status = status;
+  p.labels = labels_eff; p.lse = lse; p.ups = upstream; p.counts = counts; p.rows_per_rank = rows_per_rank;
+  p.vocab_start = vocab_start; p.ignore = ignore_index;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (dtype == Q3_BF16) return tc::launch_gemm<256, __nv_bfloat16, tc::EPI_CE_GRAD>(A, B, nullptr, p, true, st);
+  return tc::launch_gemm<256, __half, tc::EPI_CE_GRAD>(A, B, nullptr, p, false, st);
 }

@@ -244,6 +244,71 @@ __global__ void vce_accum_kernel(const T* partial, float* out, int64_t n, float 
   }
 }
 
+// labels_eff[b*S+s] = labels[b, s+1] for s < S-1 (out-of-range values flagged and treated as ignored), else ignore
+__global__ void shift_labels_kernel(const int64_t* labels, int64_t* eff, int64_t n, int64_t S, int64_t ignore,
+                                    int64_t vocab_total, int* status) {
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+    int64_t l = ignore;
+    if (i % S < S - 1) {
+      l = labels[i + 1];
+      if (l != ignore && (l < 0 || l >= vocab_total)) { flag_status(status, Q3_STATUS_LABEL_RANGE); l = ignore; }
+    }
+    eff[i] = l;
+  }
+}
+
+// lse_local[row] from the per-tile (max, sum exp) partials, combined in tile order
+__global__ void lce_combine_kernel(const float* part_max, const float* part_sum, float* lse, int64_t rows, int tiles) {
+  for (int64_t r = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; r < rows; r += (int64_t)gridDim.x * blockDim.x) {
+    float m = part_max[r * tiles], s = part_sum[r * tiles];
+    for (int t = 1; t < tiles; ++t) {
+      const float pm = part_max[r * tiles + t], ps = part_sum[r * tiles + t];
+      const float nm = fmaxf(m, pm);
+      s = s * __expf(m - nm) + ps * __expf(pm - nm);
+      m = nm;
+    }
+    lse[r] = m + logf(s);
+  }
+}
+
+// One CTA per data rank over physical rows: losses, valid-target count, mean (fixed order).
+__global__ void __launch_bounds__(1024) lce_finish_kernel(const float* lse, const float* target, const int64_t* eff,
+                                                          float* losses, int* counts, float* means,
+                                                          int64_t rows_per_rank, int64_t ignore, int* status) {
+  __shared__ float sm[32];
+  __shared__ int smi[32];
+  const int64_t source = blockIdx.x;
+  float total = 0.f;
+  int cnt = 0;
+  for (int64_t i = threadIdx.x; i < rows_per_rank; i += blockDim.x) {
+    const int64_t r = source * rows_per_rank + i;
+    const bool valid = eff[r] != ignore;
+    const float l = valid ? lse[r] - target[r] : 0.f;
+    losses[r] = l;
+    total += l;
+    cnt += valid ? 1 : 0;
+  }
+  total = block_sum(total, sm);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) cnt += __shfl_xor_sync(0xffffffffu, cnt, o);
+  __syncthreads();
+  if (lane == 0) smi[warp] = cnt;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int c = 0;
+    for (int i = 0; i < nwarp; ++i) c += smi[i];
+    counts[source] = c;
+    means[source] = total / (float)c;
+    if (c == 0) flag_status(status, Q3_STATUS_EMPTY_TARGETS);
+  }
+}
+
+__global__ void lce_global_lse_kernel(const float* maximum, const float* pack, float* lse, int64_t n) {
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x)
+    lse[i] = maximum[i] + logf(pack[i]);
+}
+
 inline int small_grid(int64_t n, int threads) {
   int64_t g = cdiv(n, threads), cap = (int64_t)sm_count() * 8;
   return (int)(g < 1 ? 1 : (g > cap ? cap : g));
@@ -334,5 +399,39 @@ extern "C" int q3_vce_accumulate(const void* partial, int partial_dtype, float* 
   const float iw = 1.f / (float)world;
   Q3_DISPATCH_FLOAT(partial_dtype, T,
                     (vce_accum_kernel<T><<<small_grid(n, 256), 256, 0, st>>>((const T*)partial, out, n, iw, first)));
+  return launch_status();
+}
+
+extern "C" int q3_shift_labels(const int64_t* labels, int64_t* labels_eff, int64_t rows, int64_t S,
+                               int64_t ignore_index, int64_t vocab_total, int* status, q3_stream_t stream) {
+  if (!labels || !labels_eff) return Q3_ERR_ARG;
+  if (rows < 1 || S < 2 || rows % S) return Q3_ERR_SHAPE;
+  shift_labels_kernel<<<small_grid(rows, 256), 256, 0, (cudaStream_t)stream>>>(labels, labels_eff, rows, S, ignore_index,
+                                                                            vocab_total, status);
+  return launch_status();
+}
+
+extern "C" int q3_linear_ce_combine(const float* part_max, const float* part_sum, float* lse_local, int64_t rows,
+                                    int64_t tiles, q3_stream_t stream) {
+  if (!part_max || !part_sum || !lse_local) return Q3_ERR_ARG;
+  if (rows < 1 || tiles < 1) return Q3_ERR_SHAPE;
+  lce_combine_kernel<<<small_grid(rows, 128), 128, 0, (cudaStream_t)stream>>>(part_max, part_sum, lse_local, rows, (int)tiles);
+  return launch_status();
+}
+
+// lse = maximum + log(pack[0]) when the statistics were all-reduced (pass maximum = NULL to use lse_in as is);
+// then per data rank: losses, counts, means over physical rows.
+extern "C" int q3_linear_ce_finish(const float* maximum, const float* pack, float* lse, const float* target,
+                                   const int64_t* labels_eff, float* losses, int* counts, float* means, int64_t rows,
+                                   int64_t rows_per_rank, int64_t ignore_index, int* status, q3_stream_t stream) {
+  if (!lse || !target || !labels_eff || !losses || !counts || !means) return Q3_ERR_ARG;
+  if (rows < 1 || rows_per_rank < 1 || rows % rows_per_rank) return Q3_ERR_SHAPE;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (maximum != nullptr) {
+    if (!pack) return Q3_ERR_ARG;
+    lce_global_lse_kernel<<<small_grid(rows, 256), 256, 0, st>>>(maximum, pack, lse, rows);
+  }
+  lce_finish_kernel<<<(int)(rows / rows_per_rank), 1024, 0, st>>>(lse, target, labels_eff, losses, counts, means,
+                                                                 rows_per_rank, ignore_index, status);
   return launch_status();
 }

@@ -55,6 +55,13 @@ SIGNATURES = {
     "q3_adamw_multi": (I, [P, P, L, L, I, D, D, D, D, D, P]),
     "q3_adamw_multi_mp": (I, [P, P, L, L, I, I, D, D, D, D, D, P]),
     "q3_gemm": (I, [P, L, L, P, L, L, P, L, L, L, I, I, P, P]),
+    "q3_gemm_acc_f32": (I, [P, L, L, P, L, L, P, L, L, L, I, P, P]),
+    "q3_linear_ce_tiles": (L, [L]),
+    "q3_shift_labels": (I, [P, P, L, L, L, L, P, P]),
+    "q3_linear_ce_stats": (I, [P, P, P, P, P, P, L, L, L, L, L, I, P, P]),
+    "q3_linear_ce_combine": (I, [P, P, P, L, L, P]),
+    "q3_linear_ce_finish": (I, [P, P, P, P, P, P, P, P, L, L, L, P, P]),
+    "q3_linear_ce_grad": (I, [P, P, P, P, P, P, P, L, L, L, L, L, L, I, P, P]),
     "q3_gemm_path": (I, [P, L, L, P, L, L, P, L, L, L, I, I]),
     "q3_gate_up_swiglu_fwd": (I, [P, P, P, P, P, P, L, L, L, I, P, P]),
     "q3_gate_up_path": (I, [P, P, P, P, P, P, L, L, L, I]),

@@ -34,6 +34,19 @@ class FusedQwen3ForCausalLM(PrecisionQwen3ForCausalLM):
         from .fused import FusedBackbone
         self.backbone_class = FusedBackbone
         super().__init__(config, options, precision_options=precision_options)
+        self.fused_loss = False     # True: forward(ids, labels) returns the loss only; logits are never materialised
+
+    def forward(self, input_ids, labels=None, **kwargs):
+        if not self.fused_loss or labels is None:
+            return super().forward(input_ids, labels, **kwargs)
+        from types import SimpleNamespace
+        from .kernels.fused_loss import fused_linear_cross_entropy
+        if any(kwargs.get(k) for k in ('use_cache', 'past_key_values', 'attention_mask', 'output_attentions',
+                                       'output_hidden_states', 'logits_to_keep')):
+            raise ValueError('Only dense unpadded causal training without cache/extra outputs is implemented; no fallback')
+        hidden = self.model(input_ids, kwargs.get('position_ids'))
+        loss = fused_linear_cross_entropy(hidden, self.lm_head.weight, labels)
+        return SimpleNamespace(loss=loss, logits=None)
 
 
 def model_for_variant(config, name, *, precision_options=None):

@@ -44,6 +44,65 @@ def _reduce(owner, tensor, op):
         owner.communication.all_reduce(tensor, operation)
 
 
+class _FusedVocabCE(torch.autograd.Function):
+    """Same contract as _VocabCE, but neither the logits shard nor its gradient is ever materialised: the
+    projection GEMM reduces to softmax statistics in its epilogue, and backward walks the local vocabulary in
+    chunks (qwen3_triton/kernels/fused_loss.py)."""
+
+    @staticmethod
+    def forward(ctx, hidden, weight, labels, ignore, owner):
+        from ..kernels import fused_loss as F
+        world, rank = owner.world, owner.rank
+        b, s, k = hidden.shape
+        r = b * s
+        v = weight.shape[0]
+        if (hidden.dtype != torch.bfloat16 or weight.dtype != torch.float32 or labels.dtype != torch.int64
+                or labels.shape != (b, s) or s < 2 or not hidden.is_contiguous() or not labels.is_contiguous()
+                or hidden.device != weight.device or hidden.device != labels.device):
+            raise ValueError('Matching contiguous BF16 hidden, int64 labels and local FP32 weight required')
+        all_hidden = torch.empty((world * r, k), device=hidden.device, dtype=hidden.dtype)
+        all_labels = torch.empty(world * r, device=hidden.device, dtype=labels.dtype)
+        _gather(owner, all_hidden, hidden.view(r, k))
+        _gather(owner, all_labels, labels.view(-1))
+        w = cast_tensor(weight, torch.bfloat16)
+        eff = F.shifted_labels(all_labels.view(world * b, s), ignore, world * v)
+        local_lse, target = F.local_lse_and_target(all_hidden, w, eff, rank * v, ignore)
+        maximum = local_lse.clone()
+        _reduce(owner, maximum, dist.ReduceOp.MAX)
+        packed = packed_statistics(local_lse, maximum, target)
+        _reduce(owner, packed, dist.ReduceOp.SUM)
+        lse = torch.empty_like(local_lse)
+        _, counts, means = F.finish(lse, packed[1], eff, r, ignore, maximum, packed)
+        loss = means[rank].clone()
+        ctx.save_for_backward(all_hidden, w, eff, lse, counts)
+        ctx.rows, ctx.sequence, ctx.start, ctx.ignore, ctx.owner = r, s, rank * v, ignore, owner
+        owner.forward_calls += 1
+        return loss
+
+    @staticmethod
+    def backward(ctx, up):
+        from ..kernels import fused_loss as F
+        h, w, eff, lse, counts = ctx.saved_tensors
+        owner = ctx.owner
+        world, r, k = owner.world, ctx.rows, h.shape[1]
+        ups = torch.empty(world, device=h.device, dtype=up.dtype)
+        _gather(owner, ups, up.contiguous().view(1))
+        partial_dx, dw = F.head_backward(h, w, eff, lse, ups, counts, r, ctx.start, ctx.ignore, owner.chunk,
+                                         torch.float32)
+        if world == 1:
+            local_dx = partial_dx
+        else:
+            local_dx = torch.empty((r, k), device=h.device, dtype=torch.float32)
+            if owner.communication is None:
+                dist.reduce_scatter_tensor(local_dx, partial_dx, op=dist.ReduceOp.SUM)
+            else:
+                owner.communication.reduce_scatter(local_dx, partial_dx, 'sum')
+            accumulate_weight_gradient(dw, dw, world, True)     # mean over data ranks, in place
+        dx = cast_tensor(local_dx, torch.bfloat16)
+        owner.backward_calls += 1
+        return dx.view(-1, ctx.sequence, k), dw, None, None, None
+
+
 class _VocabCE(torch.autograd.Function):
     @staticmethod
     def forward(ctx, hidden, weight, labels, ignore, diagnostics, owner):
@@ -122,8 +181,12 @@ class _VocabCE(torch.autograd.Function):
 
 
 class VocabParallelCE(torch.nn.Module):
-    def __init__(self, full_weight_cpu, *, fused_dw=False, communication=None):
+    def __init__(self, full_weight_cpu, *, fused_dw=False, communication=None, fused=True, chunk=16384):
+        """`fused` (an addition to the reference signature): compute the loss without materialising the logits
+        shard; `diagnostics=True` in forward always takes the materialising path because it returns the logits."""
         super().__init__()
+        self.fused = bool(fused)
+        self.chunk = int(chunk)
         self.world, self.rank = _world()
         if full_weight_cpu.device.type != 'cpu' or full_weight_cpu.ndim != 2 or full_weight_cpu.shape[0] % self.world:
             raise ValueError('Equal CPU vocabulary shards required')
@@ -139,4 +202,6 @@ class VocabParallelCE(torch.nn.Module):
     def forward(self, hidden, labels, *, ignore_index=-100, diagnostics=False):
         if hidden.ndim != 3 or hidden.shape[-1] != self.in_features:
             raise ValueError('Expected [B,S,H] hidden states')
+        if self.fused and not diagnostics and self.in_features % 8 == 0 and self.weight.shape[0] % 8 == 0:
+            return _FusedVocabCE.apply(hidden, self.weight, labels, ignore_index, self), None
         return _VocabCE.apply(hidden, self.weight, labels, ignore_index, diagnostics, self)

@@ -57,6 +57,32 @@ def test_tiny_bf16_all_gradients_close_to_oracle():
         assert rel_l2(p.grad, oracle.p(name).grad) < 3e-2, name
 
 
+def test_vocab_parallel_head_fused_world1_matches_dense_loss():
+    """Default VocabParallelCE path: no logits shard in memory."""
+    from qwen3_triton.kernels.linear import linear
+    from qwen3_triton.kernels.loss import causal_cross_entropy
+    from qwen3_triton.training.vocab_parallel import VocabParallelCE
+    g = torch.Generator().manual_seed(12)
+    B, S, H, V = 2, 65, 256, 4104
+    hidden = torch.randn(B, S, H, generator=g).to(torch.bfloat16)
+    weight = torch.randn(V, H, generator=g) * 0.05
+    labels = torch.randint(0, V, (B, S), generator=g)
+    labels[1, 4] = -100
+    head = VocabParallelCE(weight, chunk=1024)
+    h1 = hidden.cuda().requires_grad_(True)
+    loss, dense = head(h1, labels.cuda())
+    assert dense is None
+    loss.backward()
+    h2 = hidden.cuda().requires_grad_(True)
+    w2 = weight.to(torch.bfloat16).cuda().requires_grad_(True)
+    ref = causal_cross_entropy(linear(h2, w2), labels.cuda())
+    ref.backward()
+    torch.testing.assert_close(loss, ref, rtol=1e-5, atol=1e-5)
+    close(h1.grad, h2.grad, what='dx')
+    close(head.weight.grad, w2.grad.float(), dtype=torch.bfloat16, what='dw')
+    assert head.weight.grad.dtype == torch.float32
+
+
 def test_vocab_parallel_head_world1_matches_dense_loss():
     from qwen3_triton.kernels.linear import linear
     from qwen3_triton.kernels.loss import causal_cross_entropy
@@ -67,7 +93,7 @@ def test_vocab_parallel_head_world1_matches_dense_loss():
     weight = (torch.randn(V, H, generator=g) * 0.05)
     labels = torch.randint(0, V, (B, S), generator=g)
     labels[1, 4] = -100
-    head = VocabParallelCE(weight)
+    head = VocabParallelCE(weight, fused=False)
     h1 = hidden.cuda().requires_grad_(True)
     loss, dense = head(h1, labels.cuda(), diagnostics=True)
     loss.backward()
@@ -132,3 +158,29 @@ def test_fused_decoder_layers_match_operator_graph_and_oracle(seq):
         # (the reference's own whole-model gate is 6e-2 per tensor)
         assert rel_l2(g_f[n], oracle.p(n).grad) < 4e-2, n
         assert rel_l2(g_f[n], g_o[n]) < 4e-2, n
+
+
+@pytest.mark.parametrize('B,S,H,V,chunk', [(2, 33, 256, 1000, 256), (1, 300, 512, 4104, 1024), (3, 17, 128, 520, 16384)])
+def test_fused_linear_cross_entropy_matches_materialised_path(B, S, H, V, chunk):
+    """hidden -> loss without logits in memory == causal_cross_entropy(linear(hidden, W)) and the fp32 oracle."""
+    from oracle import ops as O
+    from qwen3_triton.kernels.fused_loss import fused_linear_cross_entropy
+    from qwen3_triton.kernels.linear import linear
+    from qwen3_triton.kernels.loss import causal_cross_entropy
+    g = torch.Generator().manual_seed(21)
+    hidden = torch.randn(B, S, H, generator=g).to(torch.bfloat16)
+    weight = (torch.randn(V, H, generator=g) * 0.1).to(torch.bfloat16)
+    labels = torch.randint(0, V, (B, S), generator=g)
+    if S > 6:
+        labels[0, 5] = -100
+    h1, w1 = hidden.cuda().requires_grad_(True), weight.cuda().requires_grad_(True)
+    loss = fused_linear_cross_entropy(h1, w1, labels.cuda(), chunk=chunk)
+    (loss * 2.0).backward()
+    h2, w2 = hidden.cuda().requires_grad_(True), weight.cuda().requires_grad_(True)
+    ref = causal_cross_entropy(linear(h2, w2), labels.cuda())
+    (ref * 2.0).backward()
+    torch.testing.assert_close(loss, ref, rtol=1e-5, atol=1e-5)
+    close(h1.grad, h2.grad, what='dx vs materialised')
+    close(w1.grad, w2.grad, what='dw vs materialised')
+    logits = O.linear(hidden, weight).to(torch.bfloat16)
+    assert abs(float(loss) - float(O.causal_cross_entropy(logits.view(B, S, V), labels))) / float(ref) < 1e-3
