@@ -171,6 +171,27 @@ def main():
         total = sum(p.numel() for p in params)
         report(f"adamw ({total / 1e9:.2f}e9 params)", timer(opt.step), bytes_=28 * total)
         del params, opt
+    if want("pack"):
+        # one Qwen3-8B decoder layer as an FSDP unit over 8 ranks: shard copy-in, gathered split, gradient chunk-cat
+        from qwen3_triton.runtime import ops as pack
+        world = 8
+        shapes = [(4096, 4096), (1024, 4096), (1024, 4096), (4096, 4096), (12288, 4096), (12288, 4096), (4096, 12288), (4096,), (4096,), (128,), (128,)]
+        numels = [s[0] // world * (s[1] if len(s) > 1 else 1) for s in shapes]
+        total = sum(numels)
+        shards = [torch.randn(n, device=dev) for n in numels]
+        gathered = torch.empty(world * total, device=dev, dtype=bf)
+        report("pack copy_in (kernel)", timer(lambda: pack.all_gather_copy_in(shards, gathered, numels, total, 3)), bytes_=6 * total)
+        dsts = list(torch.split(gathered.narrow(0, 3 * total, total), numels))
+        report("pack copy_in (aten)", timer(lambda: torch._foreach_copy_(dsts, shards)), bytes_=6 * total)
+        outs = [torch.empty(world, n, device=dev, dtype=bf) for n in numels]
+        g2 = gathered.view(world, -1)
+        report("pack split (kernel)", timer(lambda: pack.split_with_sizes_copy(g2, numels, dim=1, out=outs)), bytes_=4 * world * total)
+        report("pack split (aten)", timer(lambda: torch.split_with_sizes_copy(g2, numels, dim=1, out=outs)), bytes_=4 * world * total)
+        grads = [torch.randn(s, device=dev).to(bf) for s in shapes]
+        rs_in = torch.empty(world, total, device=dev)
+        report("pack chunk_cat (kernel)", timer(lambda: pack.chunk_cat(grads, 0, world, rs_in)), bytes_=6 * world * total)
+        report("pack chunk_cat (aten)", timer(lambda: torch._chunk_cat(grads, 0, world, out=rs_in)), bytes_=6 * world * total)
+        del shards, gathered, outs, grads, rs_in
     for name, (M, N, K) in {"gemm_q_fwd": (T, 4096, 4096), "gemm_gate_fwd": (T, 12288, 4096), "gemm_down_fwd": (T, 4096, 12288),
                             "gemm_lm_head_fwd": (T, V, 4096)}.items():
         if want(name) or want("gemm"):

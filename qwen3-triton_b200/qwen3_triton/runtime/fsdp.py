@@ -56,7 +56,11 @@ class TritonReduceScatter(_Allocation, ReduceScatter):
         self.calls += 1
 
 
-def configure(model, communication):
+def configure(model, communication, *, pack_kernels=True):
+    """Install the comm hooks on every FSDP unit and (by default) the pack/unpack kernels of runtime/ops.py."""
+    if pack_kernels:
+        from .ops import install_fsdp_pack_kernels
+        install_fsdp_pack_kernels()
     ag = TritonAllGather(communication)
     rs = TritonReduceScatter(communication)
     count = 0

@@ -1,0 +1,142 @@
+"""FSDP2 pack / unpack data movement on the q3_multi_copy kernel.
+
+FSDP2 moves every parameter of a unit three times per step through `torch.ops.fsdp.*`: the cast-and-pack of the
+local fp32 shards into the bf16 all-gather input, the split of the all-gather output into per-parameter tensors,
+and the chunk-and-upcast of the bf16 gradients into the fp32 reduce-scatter input. The stock CUDA implementations
+run at 1-1.5 TB/s; `install_fsdp_pack_kernels()` replaces them (CUDA dispatch key only) with one q3_multi_copy
+launch per call. Same role as the reference's runtime/ops.py:53-58,193-202 behind runtime/dispatch.py:105-119,
+without a dispatch mode around the whole step.
+"""
+import math
+
+import torch
+
+from .. import _abi
+
+_SPAN = None
+_installed = False
+_table_cache = {}
+_lib = None
+
+
+def plan_copy_in(numels, out_ptr, out_itemsize, rank, input_ptrs):
+    """Table rows for all_gather_copy_in: shard i -> its slice of this rank's all-gather input."""
+    total = sum(numels)
+    rows, offset = [], 0
+    for n, p in zip(numels, input_ptrs):
+        rows.append((p, out_ptr + (total * rank + offset) * out_itemsize, 1, n, n, n, n))
+        offset += n
+    return rows
+
+
+def plan_split(src_ptr, itemsize, world, split_sizes, out_ptrs):
+    """Table rows for split_with_sizes_copy(dim=1) of a [world, total] buffer."""
+    total = sum(split_sizes)
+    rows, offset = [], 0
+    for n, p in zip(split_sizes, out_ptrs):
+        rows.append((src_ptr + offset * itemsize, p, world, n, total, n, (world - 1) * total + n))
+        offset += n
+    return rows
+
+
+def plan_chunk_cat(shapes, src_ptrs, out_ptr, out_itemsize, world):
+    """Table rows for chunk_cat(dim=0): tensor i is cut into `world` pieces of ceil(d0/world) leading rows
+    (the tail zero-padded); piece r goes to out[r, offset_i : offset_i + piece_numel]. Returns (rows, out_cols)."""
+    pieces = []
+    for shape in shapes:
+        d0 = shape[0] if len(shape) else 1
+        rest = math.prod(shape[1:]) if len(shape) > 1 else 1
+        pieces.append((-(-d0 // world)) * rest)
+    out_cols = sum(pieces)
+    rows, offset = [], 0
+    for shape, piece, p in zip(shapes, pieces, src_ptrs):
+        rows.append((p, out_ptr + offset * out_itemsize, world, piece, piece, out_cols, math.prod(shape) if len(shape) else 1))
+        offset += piece
+    return rows, out_cols
+
+
+def finalize(rows, span, src_itemsize, dst_itemsize):
+    """Append first_block and vec_ok to each row; returns (table, total_blocks). Empty pieces are dropped."""
+    table, blocks = [], 0
+    for src, dst, r, c, ss, ds, valid in rows:
+        if r * c == 0:
+            continue
+        vec = int(c % 8 == 0 and ss % 8 == 0 and ds % 8 == 0 and src % 16 == 0 and dst % 16 == 0)
+        table.append((src, dst, r, c, ss, ds, valid, blocks, vec))
+        blocks += -(-(r * c) // span)
+    return table, blocks
+
+
+def _launch(rows, src_dtype, dst_dtype, device):
+    global _SPAN
+    if _SPAN is None:
+        _SPAN = int(_abi.lib().q3_multi_copy_span())
+    table, blocks = finalize(rows, _SPAN, src_dtype.itemsize, dst_dtype.itemsize)
+    if not table:
+        return
+    key = tuple(table)
+    meta = _table_cache.get(key)
+    if meta is None:
+        if len(_table_cache) > 512:
+            _table_cache.clear()
+        cpu = torch.tensor(table, dtype=torch.int64)
+        meta = torch.empty(cpu.shape, device=device, dtype=torch.int64)
+        meta.copy_(cpu)
+        _table_cache[key] = meta
+    _abi.call('q3_multi_copy', meta.data_ptr(), len(table), blocks, _abi.dt(src_dtype), _abi.dt(dst_dtype), _abi.stream())
+
+
+_FLOATS = (torch.float32, torch.bfloat16, torch.float16)
+
+
+def all_gather_copy_in(all_gather_inputs, all_gather_output, inp_split_sizes, all_gather_input_numel, rank):
+    all_gather_input = all_gather_output.narrow(0, all_gather_input_numel * rank, all_gather_input_numel)
+    dtypes = {t.dtype for t in all_gather_inputs}
+    if (len(dtypes) != 1 or next(iter(dtypes)) not in _FLOATS or all_gather_output.dtype not in _FLOATS
+            or not all(t.is_contiguous() for t in all_gather_inputs)):
+        with torch.no_grad():
+            torch._foreach_copy_(torch.split(all_gather_input, inp_split_sizes), all_gather_inputs)
+        return all_gather_input, all_gather_output
+    rows = plan_copy_in([t.numel() for t in all_gather_inputs], all_gather_output.data_ptr(),
+                        all_gather_output.element_size(), rank, [t.data_ptr() for t in all_gather_inputs])
+    _launch(rows, next(iter(dtypes)), all_gather_output.dtype, all_gather_output.device)
+    return all_gather_input, all_gather_output
+
+
+def split_with_sizes_copy(all_gather_output, all_gather_input_split_sizes, dim=0, *, out):
+    ok = (dim == 1 and all_gather_output.ndim == 2 and all_gather_output.is_contiguous()
+          and all_gather_output.dtype in _FLOATS and len({o.dtype for o in out}) == 1 and out[0].dtype in _FLOATS
+          and all(o.is_contiguous() and o.ndim == 2 for o in out))
+    if not ok:
+        torch.split_with_sizes_copy(all_gather_output, all_gather_input_split_sizes, dim=dim, out=out)
+        return
+    rows = plan_split(all_gather_output.data_ptr(), all_gather_output.element_size(), all_gather_output.shape[0],
+                      list(all_gather_input_split_sizes), [o.data_ptr() for o in out])
+    _launch(rows, all_gather_output.dtype, out[0].dtype, all_gather_output.device)
+
+
+def chunk_cat(tensors, dim, num_chunks, out):
+    ok = (dim == 0 and out.ndim == 2 and out.is_contiguous() and out.dtype in _FLOATS and out.shape[0] == num_chunks
+          and len({t.dtype for t in tensors}) == 1 and tensors[0].dtype in _FLOATS
+          and all(t.is_contiguous() and t.ndim >= 1 for t in tensors))
+    if ok:
+        rows, cols = plan_chunk_cat([tuple(t.shape) for t in tensors], [t.data_ptr() for t in tensors], out.data_ptr(),
+                                    out.element_size(), num_chunks)
+        ok = cols == out.shape[1]
+    if not ok:
+        torch._chunk_cat(tensors, dim, num_chunks, out=out)
+        return
+    _launch(rows, tensors[0].dtype, out.dtype, out.device)
+
+
+def install_fsdp_pack_kernels():
+    """Route FSDP2's three pack/unpack ops to q3_multi_copy on CUDA tensors. Idempotent."""
+    global _installed, _lib
+    if _installed:
+        return
+    import torch.distributed.fsdp._fully_shard._fsdp_collectives  # noqa: F401  defines the fsdp:: ops
+    _lib = torch.library.Library("fsdp", "IMPL")
+    _lib.impl("all_gather_copy_in", all_gather_copy_in, "CUDA", allow_override=True)
+    _lib.impl("split_with_sizes_copy", split_with_sizes_copy, "CUDA", allow_override=True)
+    _lib.impl("chunk_cat", chunk_cat, "CUDA", allow_override=True)
+    _installed = True

@@ -102,3 +102,45 @@ def test_vocab_parallel_statistics_algebra():
     lse = maximum + torch.log(packed[0])
     loss = (lse - packed[1]).mean()
     torch.testing.assert_close(loss, torch.nn.functional.cross_entropy(logits, labels))
+
+
+def test_fsdp_pack_plans_against_reference_semantics():
+    """The table builders of runtime/ops.py, executed by a plain-Python interpreter of the table, reproduce
+    torch's own all_gather copy-in, split_with_sizes_copy and _chunk_cat on CPU tensors."""
+    import ctypes
+    from qwen3_triton.runtime import ops
+
+    def run(table, src_dtype, dst_dtype):
+        for src, dst, r, c, ss, ds, valid, _first, _vec in table:
+            s = torch.frombuffer((ctypes.c_char * (max(valid, 1) * src_dtype.itemsize)).from_address(src), dtype=src_dtype)
+            n_dst = (r - 1) * ds + c
+            d = torch.frombuffer((ctypes.c_char * (n_dst * dst_dtype.itemsize)).from_address(dst), dtype=dst_dtype)
+            for i in range(r):
+                for j in range(c):
+                    k = i * ss + j
+                    d[i * ds + j] = s[k].to(dst_dtype) if k < valid else 0
+
+    g = torch.Generator().manual_seed(0)
+    world, rank = 4, 2
+    shards = [torch.randn(n, generator=g) for n in (5, 12, 1)]
+    out = torch.zeros(world * 18, dtype=torch.bfloat16)
+    table, blocks = ops.finalize(ops.plan_copy_in([5, 12, 1], out.data_ptr(), 2, rank, [t.data_ptr() for t in shards]), 4096, 4, 2)
+    run(table, torch.float32, torch.bfloat16)
+    assert blocks == 3 and torch.equal(out[36:54], torch.cat(shards).to(torch.bfloat16)) and out[:36].abs().sum() == 0
+
+    gathered = torch.randn(world, 18, generator=g).to(torch.bfloat16)
+    outs = [torch.zeros(world, n, dtype=torch.bfloat16) for n in (5, 12, 1)]
+    table, _ = ops.finalize(ops.plan_split(gathered.data_ptr(), 2, world, [5, 12, 1], [o.data_ptr() for o in outs]), 4096, 2, 2)
+    run(table, torch.bfloat16, torch.bfloat16)
+    for o, ref in zip(outs, torch.split(gathered, [5, 12, 1], dim=1)):
+        assert torch.equal(o, ref)
+
+    grads = [torch.randn(s, generator=g).to(torch.bfloat16) for s in ((6, 3), (5, 2), (9,), (1, 4))]   # 5, 9, 1 need padding
+    rows, cols = ops.plan_chunk_cat([tuple(t.shape) for t in grads], [t.data_ptr() for t in grads], 0, 4, world)
+    ref = torch.zeros(world, cols)
+    torch._chunk_cat([t.float() for t in grads], 0, world, out=ref)
+    got = torch.full((world, cols), float('nan'))
+    rows, _ = ops.plan_chunk_cat([tuple(t.shape) for t in grads], [t.data_ptr() for t in grads], got.data_ptr(), 4, world)
+    table, _ = ops.finalize(rows, 4096, 2, 4)
+    run(table, torch.bfloat16, torch.float32)
+    assert torch.equal(got, ref)
