@@ -171,6 +171,20 @@ def main():
         total = sum(p.numel() for p in params)
         report(f"adamw ({total / 1e9:.2f}e9 params)", timer(opt.step), bytes_=28 * total)
         del params, opt
+    if want("adamw_mp"):
+        # same tensors, mixed-precision form: bf16 gradient in, fp32 master/moments updated, bf16 copy out
+        per_layer = [(4096, 4096), (1024, 4096), (1024, 4096), (4096, 4096), (12288, 4096), (12288, 4096), (4096, 12288), (4096,), (4096,), (128,), (128,)]
+        shapes = per_layer * max(1, int(36 * a.scale * 0.5))
+        from qwen3_triton.runtime.adamw import TritonAdamW
+        params = [torch.nn.Parameter(torch.randn(*s, device=dev) * 0.02) for s in shapes]
+        for p in params:
+            p.q3_lowp_grad = (torch.randn_like(p) * 1e-3).to(bf)
+            p.q3_lowp_copy = torch.empty_like(p, dtype=bf)
+        opt = TritonAdamW(params, lr=1e-4, betas=(0.9, 0.95), weight_decay=0.1)
+        opt.step()
+        total = sum(p.numel() for p in params)
+        report(f"adamw_mp ({total / 1e9:.2f}e9 params)", timer(opt.step), bytes_=30 * total)
+        del params, opt
     if want("pack"):
         # one Qwen3-8B decoder layer as an FSDP unit over 8 ranks: shard copy-in, gathered split, gradient chunk-cat
         from qwen3_triton.runtime import ops as pack

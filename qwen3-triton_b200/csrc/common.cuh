@@ -84,6 +84,17 @@ template <> struct VecIO<float, 4> {
   }
 };
 
+template <> struct VecIO<float, 8> {
+  static __device__ __forceinline__ void load(const float* p, float (&v)[8]) {
+    const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+  }
+  static __device__ __forceinline__ void store(float* p, const float (&v)[8]) {
+    *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+    *reinterpret_cast<float4*>(p + 4) = make_float4(v[4], v[5], v[6], v[7]);
+  }
+};
+
 template <> struct VecIO<__nv_bfloat16, 8> {
   static __device__ __forceinline__ void load(const __nv_bfloat16* p, float (&v)[8]) {
     uint4 t = *reinterpret_cast<const uint4*>(p);
@@ -97,6 +108,38 @@ template <> struct VecIO<__nv_bfloat16, 8> {
 #pragma unroll
     for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
     *reinterpret_cast<uint4*>(p) = t;
+  }
+};
+
+template <> struct VecIO<__nv_bfloat16, 4> {
+  static __device__ __forceinline__ void load(const __nv_bfloat16* p, float (&v)[4]) {
+    uint2 t = *reinterpret_cast<const uint2*>(p);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&t);
+#pragma unroll
+    for (int i = 0; i < 2; ++i) { float2 f = __bfloat1622float2(h[i]); v[2 * i] = f.x; v[2 * i + 1] = f.y; }
+  }
+  static __device__ __forceinline__ void store(__nv_bfloat16* p, const float (&v)[4]) {
+    uint2 t;
+    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&t);
+#pragma unroll
+    for (int i = 0; i < 2; ++i) h[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+    *reinterpret_cast<uint2*>(p) = t;
+  }
+};
+
+template <> struct VecIO<__half, 4> {
+  static __device__ __forceinline__ void load(const __half* p, float (&v)[4]) {
+    uint2 t = *reinterpret_cast<const uint2*>(p);
+    const __half2* h = reinterpret_cast<const __half2*>(&t);
+#pragma unroll
+    for (int i = 0; i < 2; ++i) { float2 f = __half22float2(h[i]); v[2 * i] = f.x; v[2 * i + 1] = f.y; }
+  }
+  static __device__ __forceinline__ void store(__half* p, const float (&v)[4]) {
+    uint2 t;
+    __half2* h = reinterpret_cast<__half2*>(&t);
+#pragma unroll
+    for (int i = 0; i < 2; ++i) h[i] = __floats2half2_rn(v[2 * i], v[2 * i + 1]);
+    *reinterpret_cast<uint2*>(p) = t;
   }
 };
 
@@ -161,4 +204,16 @@ __device__ __forceinline__ void flag_status(int* status, int bit) {
 }
 
 #endif  // __CUDACC__
+// Row of a multi-tensor table that owns block `blk`: the last row whose `first_block` column is <= blk (the column is
+// non-decreasing). Every thread walks the same few table entries, which stay in L1 after the first CTA of an SM.
+__device__ __forceinline__ int64_t find_owner(const int64_t* __restrict__ meta, int64_t rows, int stride, int col,
+                                              int64_t blk) {
+  int64_t lo = 0, hi = rows;
+  while (lo + 1 < hi) {
+    const int64_t mid = (lo + hi) >> 1;
+    if (meta[mid * stride + col] <= blk) lo = mid; else hi = mid;
+  }
+  return lo;
+}
+
 }  // namespace q3

@@ -16,44 +16,11 @@
 namespace q3 {
 
 constexpr int kPackSpan = 16384;
-constexpr int kPackVec = 8;
-constexpr int kPackBatch = 4;
-
-template <typename S>
-__device__ __forceinline__ void pack_load8(const S* __restrict__ p, float (&v)[8]) {
-  if constexpr (sizeof(S) == 4) {
-    const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
-    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
-  } else {
-    const uint4 t = *reinterpret_cast<const uint4*>(p);
-    const S* h = reinterpret_cast<const S*>(&t);
-#pragma unroll
-    for (int j = 0; j < 8; ++j) v[j] = to_f32<S>(h[j]);
-  }
-}
-
-template <typename D>
-__device__ __forceinline__ void pack_store8(D* __restrict__ p, const float (&v)[8]) {
-  if constexpr (sizeof(D) == 4) {
-    *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
-    *reinterpret_cast<float4*>(p + 4) = make_float4(v[4], v[5], v[6], v[7]);
-  } else {
-    uint4 t;
-    D* h = reinterpret_cast<D*>(&t);
-#pragma unroll
-    for (int j = 0; j < 8; ++j) h[j] = from_f32<D>(v[j]);
-    *reinterpret_cast<uint4*>(p) = t;
-  }
-}
 
 template <typename S, typename D>
 __global__ void __launch_bounds__(256) multi_copy_kernel(const int64_t* __restrict__ meta, int64_t n) {
   const int64_t blk = blockIdx.x;
-  int64_t lo = 0, hi = n;
-  while (lo + 1 < hi) {
-    const int64_t mid = (lo + hi) >> 1;
-    if (meta[mid * 9 + 7] <= blk) lo = mid; else hi = mid;
-  }
+  const int64_t lo = find_owner(meta, n, 9, 7, blk);
   const int64_t* e = meta + lo * 9;
   const S* __restrict__ src = reinterpret_cast<const S*>(e[0]);
   D* __restrict__ dst = reinterpret_cast<D*>(e[1]);
@@ -82,28 +49,32 @@ __global__ void __launch_bounds__(256) multi_copy_kernel(const int64_t* __restri
     di = r * ds + c;
   };
   if (e[8]) {
-    // cols and strides are multiples of 8 and both bases 16-byte aligned: 8 elements per access, 4 in flight
-    for (int base = threadIdx.x * kPackVec; base < span; base += 256 * kPackVec * kPackBatch) {
-      float v[kPackBatch][8];
-      int64_t di[kPackBatch];
+    // cols and strides are multiples of 8 and both bases 16-byte aligned: a lane moves 8 adjacent elements per
+    // access (one or two 16-byte words), four accesses in flight. Measured faster than 4-element lanes spread a
+    // CTA-width apart (chunk-cat 4.6 vs 3.9 TB/s).
+    constexpr int VEC = 8;
+    constexpr int BATCH = 4;
+    for (int base = threadIdx.x * VEC; base < span; base += 256 * VEC * BATCH) {
+      float v[BATCH][VEC];
+      int64_t di[BATCH];
 #pragma unroll
-      for (int b = 0; b < kPackBatch; ++b) {
-        const int off = base + b * 256 * kPackVec;
+      for (int b = 0; b < BATCH; ++b) {
+        const int off = base + b * 256 * VEC;
         di[b] = -1;
         if (off < span) {
           int64_t si;
           locate(off, si, di[b]);
-          if (si + 8 <= valid) {
-            pack_load8<S>(src + si, v[b]);
+          if (si + VEC <= valid) {
+            VecIO<S, VEC>::load(src + si, v[b]);
           } else {
 #pragma unroll
-            for (int j = 0; j < 8; ++j) v[b][j] = si + j < valid ? to_f32<S>(src[si + j]) : 0.f;
+            for (int j = 0; j < VEC; ++j) v[b][j] = si + j < valid ? to_f32<S>(src[si + j]) : 0.f;
           }
         }
       }
 #pragma unroll
-      for (int b = 0; b < kPackBatch; ++b)
-        if (di[b] >= 0) pack_store8<D>(dst + di[b], v[b]);
+      for (int b = 0; b < BATCH; ++b)
+        if (di[b] >= 0) VecIO<D, VEC>::store(dst + di[b], v[b]);
     }
   } else {
     for (int off = threadIdx.x; off < span; off += 256) {
