@@ -294,14 +294,13 @@ def census(counter):
             key = (a[7], a[8], a[9], "A:%s B:%s" % ("K" if a[2] == 1 else "MN", "K" if a[4] == 1 else "MN"))
             cnt, tot = shapes.get(key, (0, 0.0))
             shapes[key] = (cnt + 1, tot + s.elapsed_time(e))
+            gemm_flops += 2.0 * a[7] * a[8] * a[9]
+        elif name == "q3_gate_up_swiglu_fwd":
+            gemm_flops += 4.0 * a[6] * a[7] * a[8]
     if os.environ.get("Q3_BENCH_PROFILE"):
         for (m, n, k, lay), (cnt, tot) in sorted(shapes.items(), key=lambda kv: -kv[1][1]):
             sys.stderr.write("gemm %6d x %6d x %6d %-10s n=%3d total %8.3f ms avg %8.1f us %7.1f TFLOP/s\n" % (
                 m, n, k, lay, cnt, tot, tot / cnt * 1e3, 2.0 * m * n * k * cnt / tot / 1e9))
-        if name == "q3_gemm":
-            gemm_flops += 2.0 * a[7] * a[8] * a[9]
-        elif name == "q3_gate_up_swiglu_fwd":
-            gemm_flops += 4.0 * a[6] * a[7] * a[8]
     gemm_ms = by_name.get("q3_gemm", 0.0) + by_name.get("q3_gate_up_swiglu_fwd", 0.0)
     return by_name, gemm_flops, gemm_ms
 

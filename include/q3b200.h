@@ -212,15 +212,14 @@ int q3_adamw_multi_mp(const int64_t* meta, float* coeff, int64_t n_tensors, int6
 
 /* ---- FSDP pack / unpack -------------------------------------------------------------------------------------- */
 
-/* One launch copies (and converts) every 2-D piece listed in a device table int64 [n][9] =
- * {src, dst, rows, cols, src_row_stride, dst_row_stride, src_valid, first_block, vec_ok}: dst[r*dst_row_stride + c] =
+/* One launch copies (and converts) every 2-D piece listed in a device table int64 [n][8] =
+ * {src, dst, rows, cols, src_row_stride, dst_row_stride, src_valid, vec_ok}: dst[r*dst_row_stride + c] =
  * convert(src[r*src_row_stride + c]) or 0 where the source index is >= src_valid (padding of the last chunk).
- * first_block = running sum of ceil(rows*cols / q3_multi_copy_span()); vec_ok = 1 when cols and both strides are
- * multiples of 8 and both bases are 16-byte aligned. Covers FSDP2's all_gather_copy_in (fp32 shard -> bf16),
+ * vec_ok = 1 when cols and both strides are multiples of 8 and both bases are 16-byte aligned. total_elements
+ * (sum of rows*cols) only sizes the grid. Covers FSDP2's all_gather_copy_in (fp32 shard -> bf16),
  * split_with_sizes_copy and chunk_cat (bf16 grads -> fp32 reduce-scatter rows).
  * Reference: qwen3_triton/runtime/ops.py:70-93,116-127,186-202 behind runtime/dispatch.py:105-119. */
-int64_t q3_multi_copy_span(void);
-int q3_multi_copy(const int64_t* meta, int64_t n_entries, int64_t total_blocks, int src_dtype, int dst_dtype,
+int q3_multi_copy(const int64_t* meta, int64_t n_entries, int64_t total_elements, int src_dtype, int dst_dtype,
                   q3_stream_t stream);
 
 /* ---- GEMM ----------------------------------------------------------------------------------- */

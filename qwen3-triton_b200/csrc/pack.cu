@@ -3,10 +3,11 @@
 //   split-copy-out     : all-gather output [world, total] -> per-parameter [world, n_i] tensors          (strided rows)
 //   chunk-cat          : bf16 gradients, chunked along dim 0 into `world` pieces (zero-padded) and laid side by
 //                        side as fp32 rows of the reduce-scatter input                                   (upcast + pad)
-// One launch handles every tensor of an FSDP unit: a device table describes the 2-D pieces, a CTA takes a
-// 16384-element span of one piece (binary search on the table), 16-byte accesses when the piece allows.
+// One launch handles every tensor of an FSDP unit. The grid is persistent (one resident wave) and sweeps the pieces of
+// a device table one after another, grid-stride inside a piece, so that at any moment the whole grid reads one
+// contiguous window of DRAM; 8 adjacent elements per lane per access, four accesses in flight.
 //
-// Table: int64 [n][9] = {src, dst, rows, cols, src_row_stride, dst_row_stride, src_valid, first_block, vec_ok};
+// Table: int64 [n][8] = {src, dst, rows, cols, src_row_stride, dst_row_stride, src_valid, vec_ok};
 // element (r, c) is read from src[r*src_row_stride + c] if that index is < src_valid, else it is 0.
 //
 // Replaces, in the reference: qwen3_triton/runtime/ops.py:70-93,116-127,186-202 (_runtime_strided_copy,
@@ -15,72 +16,97 @@
 
 namespace q3 {
 
-constexpr int kPackSpan = 16384;
+constexpr int kPackCols = 8;        // table columns
+constexpr int kPackCtasPerSm = 2;   // measured best overall of 2..12 (chunk-cat 5.6 TB/s, split 5.5, copy-in 4.6)
+
+// One lane's share of one vectorised piece. A lane visits vectors first, first + stride, ...; its source and
+// destination offsets advance by constant steps with one conditional wrap to the next row, so the loop has no
+// division (index arithmetic, not DRAM, limited the divided form to 4.9 TB/s). IDX = unsigned when every offset of the
+// piece fits 32 bits; CHECK = false when no vector of the piece reaches past src_valid.
+template <typename S, typename D, typename IDX, bool CHECK>
+__device__ __forceinline__ void sweep_piece(const S* __restrict__ src, D* __restrict__ dst, int64_t cols64, int64_t ss64,
+                                            int64_t ds64, int64_t valid64, int64_t nvec, int64_t first, int64_t stride) {
+  const int64_t e0 = first << 3, hop = stride << 3;
+  int64_t r0, r_step;
+  if (((e0 | hop | cols64) >> 32) == 0) {   // the usual case: 32-bit divisions
+    r0 = (unsigned)e0 / (unsigned)cols64;
+    r_step = (unsigned)hop / (unsigned)cols64;
+  } else {
+    r0 = e0 / cols64;
+    r_step = hop / cols64;
+  }
+  const IDX cols = (IDX)cols64, valid = (IDX)valid64;
+  IDX c = (IDX)(e0 - r0 * cols64);
+  const IDX c_step = (IDX)(hop - r_step * cols64);
+  IDX si = (IDX)(r0 * ss64) + c, di = (IDX)(r0 * ds64) + c;
+  const IDX step_s = (IDX)(r_step * ss64) + c_step, step_d = (IDX)(r_step * ds64) + c_step;
+  const IDX wrap_s = (IDX)(ss64 - cols64), wrap_d = (IDX)(ds64 - cols64);
+  auto advance = [&]() {
+    c += c_step; si += step_s; di += step_d;
+    if (c >= cols) { c -= cols; si += wrap_s; di += wrap_d; }
+  };
+  auto load = [&](IDX at, float (&v)[8]) {
+    if (!CHECK || at + 8 <= valid) {
+      VecIO<S, 8>::load(src + at, v);
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[j] = at + j < valid ? to_f32<S>(src[at + j]) : 0.f;
+    }
+  };
+  constexpr int U = 4;   // independent accesses in flight per lane
+  int64_t left64 = (nvec - first + stride - 1) / stride;   // vectors this lane owns
+  int64_t left = left64;
+  for (; left >= U; left -= U) {
+    float v[U][8];
+    IDX d[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      d[u] = di;
+      load(si, v[u]);
+      advance();
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) VecIO<D, 8>::store(dst + d[u], v[u]);
+  }
+  // Tail one vector at a time: predicating the batch instead (tried both on loads and on stores) cost more
+  // registers or serialised the main loop and lost 5-30 % on whole-buffer copies.
+  for (; left > 0; --left) {
+    float v0[8];
+    load(si, v0);
+    VecIO<D, 8>::store(dst + di, v0);
+    advance();
+  }
+}
 
 template <typename S, typename D>
 __global__ void __launch_bounds__(256) multi_copy_kernel(const int64_t* __restrict__ meta, int64_t n) {
-  const int64_t blk = blockIdx.x;
-  const int64_t lo = find_owner(meta, n, 9, 7, blk);
-  const int64_t* e = meta + lo * 9;
-  const S* __restrict__ src = reinterpret_cast<const S*>(e[0]);
-  D* __restrict__ dst = reinterpret_cast<D*>(e[1]);
-  const int64_t rows = e[2], cols = e[3], ss = e[4], ds = e[5], valid = e[6];
-  const int64_t total = rows * cols;
-  const int64_t begin = (blk - e[7]) * kPackSpan;
-  const int64_t end = begin + kPackSpan < total ? begin + kPackSpan : total;
-  // the row of a span's first element by one 64-bit division; inside the span 32-bit arithmetic on the offset
-  const int64_t r0 = begin / cols, c0 = begin - r0 * cols;
-  const int span = (int)(end - begin);
-  const bool narrow = cols < (int64_t)1 << 31;
-  const unsigned ucols = (unsigned)cols;
-  auto locate = [&](int off, int64_t& si, int64_t& di) {
-    int64_t r, c;
-    if (narrow) {
-      const unsigned t = (unsigned)c0 + (unsigned)off;   // c0 < 2^31 and off <= 16384
-      const unsigned q = t / ucols;
-      r = r0 + q;
-      c = t - q * ucols;
-    } else {
-      const int64_t t = c0 + off;
-      r = r0 + (t >= cols);
-      c = t >= cols ? t - cols : t;
-    }
-    si = r * ss + c;
-    di = r * ds + c;
-  };
-  if (e[8]) {
-    // cols and strides are multiples of 8 and both bases 16-byte aligned: a lane moves 8 adjacent elements per
-    // access (one or two 16-byte words), four accesses in flight. Measured faster than 4-element lanes spread a
-    // CTA-width apart (chunk-cat 4.6 vs 3.9 TB/s).
-    constexpr int VEC = 8;
-    constexpr int BATCH = 4;
-    for (int base = threadIdx.x * VEC; base < span; base += 256 * VEC * BATCH) {
-      float v[BATCH][VEC];
-      int64_t di[BATCH];
-#pragma unroll
-      for (int b = 0; b < BATCH; ++b) {
-        const int off = base + b * 256 * VEC;
-        di[b] = -1;
-        if (off < span) {
-          int64_t si;
-          locate(off, si, di[b]);
-          if (si + VEC <= valid) {
-            VecIO<S, VEC>::load(src + si, v[b]);
-          } else {
-#pragma unroll
-            for (int j = 0; j < VEC; ++j) v[b][j] = si + j < valid ? to_f32<S>(src[si + j]) : 0.f;
-          }
-        }
+  const int64_t stride = (int64_t)gridDim.x * 256;
+  const int64_t first = blockIdx.x * (int64_t)256 + threadIdx.x;
+  for (int64_t ent = 0; ent < n; ++ent) {
+    const int64_t* e = meta + ent * kPackCols;
+    const S* __restrict__ src = reinterpret_cast<const S*>(e[0]);
+    D* __restrict__ dst = reinterpret_cast<D*>(e[1]);
+    const int64_t rows = e[2], cols = e[3], ss = e[4], ds = e[5], valid = e[6];
+    const int64_t total = rows * cols;
+    if (e[7]) {
+      // cols and both strides are multiples of 8, both bases 16-byte aligned
+      const int64_t nvec = total >> 3;
+      if (first >= nvec) continue;
+      const int64_t reach = (rows - 1) * (ss > ds ? ss : ds) + cols;       // largest offset + 1 on either side
+      const bool small = reach < ((int64_t)1 << 32) - 8 && valid < ((int64_t)1 << 32) - 8;   // unsigned offsets: the unused advance past the last vector may wrap
+      const bool check = (rows - 1) * ss + cols > valid;
+      if (small) {
+        if (check) sweep_piece<S, D, unsigned, true>(src, dst, cols, ss, ds, valid, nvec, first, stride);
+        else sweep_piece<S, D, unsigned, false>(src, dst, cols, ss, ds, valid, nvec, first, stride);
+      } else {
+        sweep_piece<S, D, int64_t, true>(src, dst, cols, ss, ds, valid, nvec, first, stride);
       }
-#pragma unroll
-      for (int b = 0; b < BATCH; ++b)
-        if (di[b] >= 0) VecIO<D, VEC>::store(dst + di[b], v[b]);
-    }
-  } else {
-    for (int off = threadIdx.x; off < span; off += 256) {
-      int64_t si, di;
-      locate(off, si, di);
-      dst[di] = from_f32<D>(si < valid ? to_f32<S>(src[si]) : 0.f);
+    } else {
+      for (int64_t i = first; i < total; i += stride) {
+        const int64_t r = i / cols, c = i - r * cols;
+        const int64_t si = r * ss + c;
+        dst[r * ds + c] = from_f32<D>(si < valid ? to_f32<S>(src[si]) : 0.f);
+      }
     }
   }
 }
@@ -89,14 +115,13 @@ __global__ void __launch_bounds__(256) multi_copy_kernel(const int64_t* __restri
 
 using namespace q3;
 
-extern "C" int64_t q3_multi_copy_span(void) { return kPackSpan; }
-
-extern "C" int q3_multi_copy(const int64_t* meta, int64_t n_entries, int64_t total_blocks, int src_dtype, int dst_dtype,
-                             q3_stream_t stream) {
+extern "C" int q3_multi_copy(const int64_t* meta, int64_t n_entries, int64_t total_elements, int src_dtype,
+                             int dst_dtype, q3_stream_t stream) {
   if (!meta) return Q3_ERR_ARG;
-  if (n_entries < 1 || total_blocks < 1 || total_blocks > 2147483647LL) return Q3_ERR_SHAPE;
+  if (n_entries < 1 || total_elements < 1) return Q3_ERR_SHAPE;
   cudaStream_t st = (cudaStream_t)stream;
-  const unsigned g = (unsigned)total_blocks;
+  const int64_t want = cdiv(cdiv(total_elements, 8), 256), cap = (int64_t)sm_count() * kPackCtasPerSm;
+  const unsigned g = (unsigned)(want < cap ? want : cap);
 #define Q3_MC(S, D) multi_copy_kernel<S, D><<<g, 256, 0, st>>>(meta, n_entries)
   if (src_dtype == Q3_F32 && dst_dtype == Q3_BF16) Q3_MC(float, __nv_bfloat16);
   else if (src_dtype == Q3_BF16 && dst_dtype == Q3_F32) Q3_MC(__nv_bfloat16, float);

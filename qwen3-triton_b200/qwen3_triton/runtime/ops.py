@@ -13,9 +13,9 @@ import torch
 
 from .. import _abi
 
-_SPAN = None
 _installed = False
 _table_cache = {}
+_seen_once = {}
 _lib = None
 
 
@@ -55,35 +55,75 @@ def plan_chunk_cat(shapes, src_ptrs, out_ptr, out_itemsize, world):
     return rows, out_cols
 
 
-def finalize(rows, span, src_itemsize, dst_itemsize):
-    """Append first_block and vec_ok to each row; returns (table, total_blocks). Empty pieces are dropped."""
-    table, blocks = [], 0
+def finalize(rows):
+    """Append vec_ok to each row; returns (table, total_elements). Empty pieces are dropped."""
+    table, total = [], 0
     for src, dst, r, c, ss, ds, valid in rows:
         if r * c == 0:
             continue
         vec = int(c % 8 == 0 and ss % 8 == 0 and ds % 8 == 0 and src % 16 == 0 and dst % 16 == 0)
-        table.append((src, dst, r, c, ss, ds, valid, blocks, vec))
-        blocks += -(-(r * c) // span)
-    return table, blocks
+        table.append((src, dst, r, c, ss, ds, valid, vec))
+        total += r * c
+    return table, total
+
+
+class _TableRing:
+    """Device copies of tables whose pointers change from step to step (gradient buffers): a ring of pinned host
+    slots and device slots, filled with an asynchronous copy on the launching stream, so that building a table
+    never blocks the host on that stream. A slot is reused only after the launch that read it has finished."""
+    SLOTS, ROWS = 64, 512
+
+    def __init__(self, device):
+        self.host = torch.empty((self.SLOTS, self.ROWS, 8), dtype=torch.int64, pin_memory=True)
+        self.dev = torch.empty((self.SLOTS, self.ROWS, 8), dtype=torch.int64, device=device)
+        self.events = [None] * self.SLOTS
+        self.next = 0
+
+    def put(self, table):
+        slot = self.next
+        self.next = (slot + 1) % self.SLOTS
+        if self.events[slot] is not None:
+            self.events[slot].synchronize()
+        n = len(table)
+        self.host[slot, :n] = torch.tensor(table, dtype=torch.int64)
+        self.dev[slot, :n].copy_(self.host[slot, :n], non_blocking=True)
+        return slot, self.dev[slot]
+
+    def launched(self, slot):
+        ev = self.events[slot] or torch.cuda.Event()
+        ev.record()
+        self.events[slot] = ev
+
+
+_rings = {}
 
 
 def _launch(rows, src_dtype, dst_dtype, device):
-    global _SPAN
-    if _SPAN is None:
-        _SPAN = int(_abi.lib().q3_multi_copy_span())
-    table, blocks = finalize(rows, _SPAN, src_dtype.itemsize, dst_dtype.itemsize)
+    table, total = finalize(rows)
     if not table:
         return
     key = tuple(table)
     meta = _table_cache.get(key)
+    slot = None
+    if meta is None and len(table) <= _TableRing.ROWS:
+        seen = _seen_once.pop(key, None)
+        if seen is None:
+            # first sight: stream it through the ring; a table that comes back unchanged gets a permanent copy
+            if len(_seen_once) > 4096:
+                _seen_once.clear()
+            _seen_once[key] = True
+            ring = _rings.get(device)
+            if ring is None:
+                ring = _rings[device] = _TableRing(device)
+            slot, meta = ring.put(table)
     if meta is None:
-        if len(_table_cache) > 512:
+        if len(_table_cache) > 1024:
             _table_cache.clear()
-        cpu = torch.tensor(table, dtype=torch.int64)
-        meta = torch.empty(cpu.shape, device=device, dtype=torch.int64)
-        meta.copy_(cpu)
+        meta = torch.tensor(table, dtype=torch.int64).to(device)
         _table_cache[key] = meta
-    _abi.call('q3_multi_copy', meta.data_ptr(), len(table), blocks, _abi.dt(src_dtype), _abi.dt(dst_dtype), _abi.stream())
+    _abi.call('q3_multi_copy', meta.data_ptr(), len(table), total, _abi.dt(src_dtype), _abi.dt(dst_dtype), _abi.stream())
+    if slot is not None:
+        _rings[device].launched(slot)
 
 
 _FLOATS = (torch.float32, torch.bfloat16, torch.float16)

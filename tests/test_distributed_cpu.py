@@ -111,7 +111,7 @@ def test_fsdp_pack_plans_against_reference_semantics():
     from qwen3_triton.runtime import ops
 
     def run(table, src_dtype, dst_dtype):
-        for src, dst, r, c, ss, ds, valid, _first, _vec in table:
+        for src, dst, r, c, ss, ds, valid, _vec in table:
             s = torch.frombuffer((ctypes.c_char * (max(valid, 1) * src_dtype.itemsize)).from_address(src), dtype=src_dtype)
             n_dst = (r - 1) * ds + c
             d = torch.frombuffer((ctypes.c_char * (n_dst * dst_dtype.itemsize)).from_address(dst), dtype=dst_dtype)
@@ -124,13 +124,13 @@ def test_fsdp_pack_plans_against_reference_semantics():
     world, rank = 4, 2
     shards = [torch.randn(n, generator=g) for n in (5, 12, 1)]
     out = torch.zeros(world * 18, dtype=torch.bfloat16)
-    table, blocks = ops.finalize(ops.plan_copy_in([5, 12, 1], out.data_ptr(), 2, rank, [t.data_ptr() for t in shards]), 4096, 4, 2)
+    table, total = ops.finalize(ops.plan_copy_in([5, 12, 1], out.data_ptr(), 2, rank, [t.data_ptr() for t in shards]))
     run(table, torch.float32, torch.bfloat16)
-    assert blocks == 3 and torch.equal(out[36:54], torch.cat(shards).to(torch.bfloat16)) and out[:36].abs().sum() == 0
+    assert total == 18 and torch.equal(out[36:54], torch.cat(shards).to(torch.bfloat16)) and out[:36].abs().sum() == 0
 
     gathered = torch.randn(world, 18, generator=g).to(torch.bfloat16)
     outs = [torch.zeros(world, n, dtype=torch.bfloat16) for n in (5, 12, 1)]
-    table, _ = ops.finalize(ops.plan_split(gathered.data_ptr(), 2, world, [5, 12, 1], [o.data_ptr() for o in outs]), 4096, 2, 2)
+    table, _ = ops.finalize(ops.plan_split(gathered.data_ptr(), 2, world, [5, 12, 1], [o.data_ptr() for o in outs]))
     run(table, torch.bfloat16, torch.bfloat16)
     for o, ref in zip(outs, torch.split(gathered, [5, 12, 1], dim=1)):
         assert torch.equal(o, ref)
@@ -141,6 +141,6 @@ def test_fsdp_pack_plans_against_reference_semantics():
     torch._chunk_cat([t.float() for t in grads], 0, world, out=ref)
     got = torch.full((world, cols), float('nan'))
     rows, _ = ops.plan_chunk_cat([tuple(t.shape) for t in grads], [t.data_ptr() for t in grads], got.data_ptr(), 4, world)
-    table, _ = ops.finalize(rows, 4096, 2, 4)
+    table, _ = ops.finalize(rows)
     run(table, torch.bfloat16, torch.float32)
     assert torch.equal(got, ref)
