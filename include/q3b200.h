@@ -58,6 +58,11 @@ int q3_abi_version(void);
 const char* q3_error_string(int code);
 int q3_device_sm_count(void);
 
+/* Device status word of the entry points that take no `status` argument (RMSNorm and norm+RoPE, whose wide-row
+ * kernels wait on bulk-copy barriers with a time limit): synchronising read of the Q3_STATUS_* bits flagged on the
+ * current device since the last clear. No counterpart in the reference. */
+int q3_async_status(int clear, int* value);
+
 /* ---- elementwise --------------------------------------------------------------------------- */
 
 /* out = a + b in fp32, rounded once. Reference: qwen3_triton/kernels/residual.py:7-11,29-30. */

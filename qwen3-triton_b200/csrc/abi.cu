@@ -21,3 +21,34 @@ extern "C" const char* q3_error_string(int code) {
 }
 
 extern "C" int q3_device_sm_count(void) { return q3::sm_count(); }
+
+// ---------------------------------------------------------------------------------------------------------
+// Status word for kernels whose entry points carry no status argument (the bulk-copy ring kernels of
+// norm_ring.cu): one int per device in global memory, flagged with the Q3_STATUS_* bits.
+static __device__ int g_async_status;
+
+namespace q3 {
+int* async_status() {
+  static int* ptr[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  if (ptr[dev] == nullptr) {
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_async_status) == cudaSuccess) ptr[dev] = static_cast<int*>(p);
+  }
+  return ptr[dev];
+}
+}  // namespace q3
+
+extern "C" int q3_async_status(int clear, int* value) {
+  if (!value) return Q3_ERR_ARG;
+  int* p = q3::async_status();
+  if (!p) return Q3_ERR_DRIVER;
+  cudaError_t e = cudaMemcpy(value, p, sizeof(int), cudaMemcpyDeviceToHost);
+  if (e != cudaSuccess) return Q3_ERR_CUDA - (int)e;
+  if (clear && *value) {
+    e = cudaMemset(p, 0, sizeof(int));
+    if (e != cudaSuccess) return Q3_ERR_CUDA - (int)e;
+  }
+  return Q3_OK;
+}

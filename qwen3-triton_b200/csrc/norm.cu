@@ -18,6 +18,18 @@
 
 namespace q3 {
 
+// Wide-row kernels that stage rows through shared memory with bulk copies (norm_ring.cu).
+bool rmsnorm_ring_applies(int64_t H, int dtype);
+int rmsnorm_bwd_ring_parts(int64_t rows);
+int rmsnorm_fwd_ring(const void* x, const void* res, const void* w, void* y, void* res_out, float* inv, int64_t rows,
+                     int64_t H, float eps, int dtype, cudaStream_t st);
+int rmsnorm_bwd_ring(const void* x, const void* w, const void* dy, const void* dres, const float* inv, void* dx,
+                     float* partial, int64_t rows, int64_t H, int dtype, cudaStream_t st);
+template <typename T> struct DtypeOf;
+template <> struct DtypeOf<float> { static constexpr int value = Q3_F32; };
+template <> struct DtypeOf<__nv_bfloat16> { static constexpr int value = Q3_BF16; };
+template <> struct DtypeOf<__half> { static constexpr int value = Q3_F16; };
+
 constexpr int kRowThreads = 256;
 constexpr int kPartialRowsPerSm = 4;  // partial dW rows written per SM (workspace bound)
 
@@ -438,6 +450,8 @@ int rmsnorm_fwd_launch(const void* x, const void* res, const void* w, void* y, v
                        int64_t rows, int64_t H, float eps, cudaStream_t st) {
   constexpr int VF = Vec16<T>::N;
   const bool vec = (H % VF == 0) && aligned16(x) && aligned16(w) && aligned16(y) && (!ADD || (aligned16(res) && aligned16(res_out)));
+  if (vec && rmsnorm_ring_applies(H, DtypeOf<T>::value))
+    return rmsnorm_fwd_ring(x, ADD ? res : nullptr, w, y, res_out, inv, rows, H, eps, DtypeOf<T>::value, st);
   if (vec) {
     RowPlan p = plan_rows(rows, (int)(H / VF), 2, MaxVec<VF>::N, MaxVec<VF>::MAX_TPR, 8);
     if (p.tpr < 0) return Q3_ERR_SHAPE;
@@ -459,6 +473,14 @@ int rmsnorm_bwd_launch(const void* x, const void* w, const void* dy, const void*
   constexpr int VF = Vec16<T>::N;
   const bool vec = (H % VF == 0) && aligned16(x) && aligned16(w) && aligned16(dy) && aligned16(dx) &&
                    (!ADD || dres == nullptr || aligned16(dres));
+  if (vec && rmsnorm_ring_applies(H, DtypeOf<T>::value) && rmsnorm_bwd_ring_parts(rows) <= max_partial_rows) {
+    const int parts = rmsnorm_bwd_ring_parts(rows);
+    if (ws == nullptr || ws_bytes < (int64_t)parts * H * 4) return Q3_ERR_WORKSPACE;
+    const int rc = rmsnorm_bwd_ring(x, w, dy, ADD ? dres : nullptr, inv, dx, ws, rows, H, DtypeOf<T>::value, st);
+    if (rc != Q3_OK) return rc;
+    reduce_partials_kernel<T><<<(int)cdiv(H, 32), dim3(32, 8), 0, st>>>(ws, (T*)dw, parts, (int)H);
+    return launch_status();
+  }
   RowPlan p = vec ? plan_rows(rows, (int)(H / VF), 2, MaxVec<VF>::N, MaxVec<VF>::MAX_TPR, kPartialRowsPerSm)
                   : plan_rows(rows, (int)H, 2, MaxVec<1>::N, MaxVec<1>::MAX_TPR, kPartialRowsPerSm);
   if (p.tpr < 0) return Q3_ERR_SHAPE;

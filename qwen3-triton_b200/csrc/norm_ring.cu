@@ -1,0 +1,356 @@
+// RMSNorm forward / backward for wide rows (2048 <= H <= 8192 elements of 16 bits) with the rows staged through a
+// shared-memory ring by bulk asynchronous copies.
+//
+// The register-resident kernels of norm.cu keep one row per CTA in flight and are limited by occupancy (the
+// backward one holds ~100 live floats per thread): 41-61 % of HBM peak at H = 4096. Here a CTA is 8 consumer warps
+// plus one producer warp. The producer thread streams whole rows (x, and dy / residual where needed) into a ring
+// of `stages` slots with cp.async.bulk, each completing on the slot's mbarrier; consumers wait for a slot, pull
+// their 16-byte vectors into registers, hand the slot back (one mbarrier arrival per warp) and then do the
+// arithmetic, so up to `stages` rows per CTA are in flight whatever the register count. One named barrier per
+// row carries the row reduction; it also votes on the wait results so that an expired wait ends the CTA uniformly
+// instead of leaving part of it parked on a barrier.
+//
+// Replaces, in the reference: qwen3_triton/kernels/norm.py:13-68 (_rms_forward, _rms_backward) and the add+norm
+// pair of kernels/residual.py.
+#include "tcgen05.cuh"
+
+namespace q3 {
+
+int* async_status();   // abi.cu: device status word for kernels whose entry points carry no status argument
+
+namespace ring {
+
+using namespace q3::tc;
+
+constexpr int kConsumers = 256;
+constexpr int kThreads = kConsumers + 32;
+constexpr int kMaxStages = 8;
+
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+               "l"(src), "r"(bytes), "r"(bar)
+               : "memory");
+}
+
+// Barrier over the consumer threads only (id 1) that also ANDs a predicate over them.
+__device__ __forceinline__ bool consumers_all(bool pred) {
+  int r;
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t"
+      "setp.ne.s32 q, %1, 0;\n\t"
+      "bar.red.and.pred p, 1, %2, q;\n\t"
+      "selp.s32 %0, 1, 0, p;\n\t}"
+      : "=r"(r)
+      : "r"((int)pred), "n"(kConsumers)
+      : "memory");
+  return r != 0;
+}
+
+struct Ring {
+  uint32_t full0, empty0;
+  volatile int* abort_flag;
+  float* red;          // [2][8]
+  uint8_t* slots;
+  __device__ __forceinline__ uint32_t full(int s) const { return full0 + 8u * s; }
+  __device__ __forceinline__ uint32_t empty(int s) const { return empty0 + 8u * s; }
+};
+
+// Shared memory: [stages][slot_bytes] | full[kMaxStages] | empty[kMaxStages] | abort | red[16]
+__device__ __forceinline__ Ring ring_setup(uint8_t* smem, int stages, size_t slot_bytes) {
+  Ring r;
+  r.slots = smem;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (size_t)stages * slot_bytes);
+  r.full0 = smem_u32(bars);
+  r.empty0 = r.full0 + 8u * kMaxStages;
+  int* tail = reinterpret_cast<int*>(bars + 2 * kMaxStages);
+  r.abort_flag = tail;
+  r.red = reinterpret_cast<float*>(tail + 4);
+  if (threadIdx.x == 0) {
+    *r.abort_flag = 0;
+    for (int s = 0; s < stages; ++s) { mbar_init(r.full(s), 1); mbar_init(r.empty(s), kConsumers / 32); }
+    fence_barrier_init();
+  }
+  __syncthreads();
+  return r;
+}
+
+inline size_t ring_smem_bytes(int stages, size_t slot_bytes) {
+  return (size_t)stages * slot_bytes + 2 * kMaxStages * 8 + 16 + 16 * 4;
+}
+
+// Producer: one thread. `n_in` row sources; row r of source i starts at src[i] + r * row_bytes.
+template <int NIN>
+__device__ __forceinline__ void produce(const Ring& rg, const uint8_t* const (&src)[NIN], int n_in, int64_t rows,
+                                        uint32_t row_bytes, int stages, size_t slot_bytes) {
+  uint32_t k = 0;
+  for (int64_t row = blockIdx.x; row < rows; row += gridDim.x, ++k) {
+    const int s = k % stages;
+    const uint32_t ph = (k / stages) & 1u;
+    if (!mbar_wait(rg.empty(s), ph ^ 1u, rg.abort_flag)) break;
+    mbar_expect_tx(rg.full(s), row_bytes * n_in);
+    const uint32_t dst = smem_u32(rg.slots + (size_t)s * slot_bytes);
+#pragma unroll
+    for (int i = 0; i < NIN; ++i)
+      if (i < n_in) bulk_load(dst + i * row_bytes, src[i] + (size_t)row * row_bytes, row_bytes, rg.full(s));
+  }
+  // Do not leave while copies may still be landing in this CTA's shared memory.
+  const uint32_t pending = k < (uint32_t)stages ? k : (uint32_t)stages;
+  for (uint32_t j = k - pending; j < k; ++j) mbar_wait_drain(rg.full(j % stages), (j / stages) & 1u);
+}
+
+// ------------------------------------------------------------------ forward
+// y = x * rsqrt(mean(x^2) + eps) * w; ADD: x := round(x + res) first, also stored to res_out.
+template <typename T, int MV, bool ADD>
+__global__ void __launch_bounds__(kThreads, MV <= 2 ? 2 : 1)
+rmsnorm_fwd_ring_kernel(const T* __restrict__ x, const T* __restrict__ res, const T* __restrict__ w, T* __restrict__ y,
+                        T* __restrict__ res_out, float* __restrict__ inv, int64_t rows, int H, float eps, int stages,
+                        int* status) {
+  extern __shared__ __align__(128) uint8_t smem[];
+  const uint32_t row_bytes = (uint32_t)H * sizeof(T);
+  const size_t slot_bytes = (size_t)row_bytes * (ADD ? 2 : 1);
+  const Ring rg = ring_setup(smem, stages, slot_bytes);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (warp == kConsumers / 32) {
+    if (lane == 0) {
+      const uint8_t* const src[2] = {reinterpret_cast<const uint8_t*>(x), reinterpret_cast<const uint8_t*>(res)};
+      produce<2>(rg, src, ADD ? 2 : 1, rows, row_bytes, stages, slot_bytes);
+    }
+  } else {
+    const int t = threadIdx.x, nvec = H / 8;
+    float ww[MV][8];
+#pragma unroll
+    for (int i = 0; i < MV; ++i)
+      if (t + i * kConsumers < nvec) VecIO<T, 8>::load(w + (size_t)(t + i * kConsumers) * 8, ww[i]);
+    uint32_t k = 0;
+    for (int64_t row = blockIdx.x; row < rows; row += gridDim.x, ++k) {
+      const int s = k % stages;
+      const bool ok = mbar_wait(rg.full(s), (k / stages) & 1u, rg.abort_flag);
+      const T* sx = reinterpret_cast<const T*>(rg.slots + (size_t)s * slot_bytes);
+      float c[MV][8];
+      float ss = 0.f;
+#pragma unroll
+      for (int i = 0; i < MV; ++i) {
+        const int v = t + i * kConsumers;
+        if (v < nvec) {
+          VecIO<T, 8>::load(sx + (size_t)v * 8, c[i]);
+          if constexpr (ADD) {
+            float r[8];
+            VecIO<T, 8>::load(sx + H + (size_t)v * 8, r);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) c[i][j] = to_f32<T>(from_f32<T>(c[i][j] + r[j]));   // the stored value is what is normalised
+          }
+#pragma unroll
+          for (int j = 0; j < 8; ++j) ss += c[i][j] * c[i][j];
+        }
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(rg.empty(s));
+      ss = warp_sum(ss);
+      float* red = rg.red + (k & 1u) * 8;
+      if (lane == 0) red[warp] = ss;
+      if (!consumers_all(ok)) break;
+      float tot = 0.f;
+#pragma unroll
+      for (int i = 0; i < kConsumers / 32; ++i) tot += red[i];
+      const float r = rsqrtf(tot / (float)H + eps);
+#pragma unroll
+      for (int i = 0; i < MV; ++i) {
+        const int v = t + i * kConsumers;
+        if (v < nvec) {
+          if constexpr (ADD) VecIO<T, 8>::store(res_out + (size_t)row * H + (size_t)v * 8, c[i]);
+          float o[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) o[j] = c[i][j] * r * ww[i][j];
+          VecIO<T, 8>::store(y + (size_t)row * H + (size_t)v * 8, o);
+        }
+      }
+      if (t == 0) inv[row] = r;
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0 && *rg.abort_flag) flag_status(status, Q3_STATUS_WAIT_TIMEOUT);
+}
+
+// ------------------------------------------------------------------ backward
+// dx = inv * (dy*w - x * inv^2 * mean(dy*w*x)) [+ dres];  partial[cta][c] = sum over the CTA's rows of dy * x * inv.
+template <typename T, int MV>
+__global__ void __launch_bounds__(kThreads, MV <= 2 ? 2 : 1)
+rmsnorm_bwd_ring_kernel(const T* __restrict__ x, const T* __restrict__ w, const T* __restrict__ dy,
+                        const T* __restrict__ dres, const float* __restrict__ inv, T* __restrict__ dx,
+                        float* __restrict__ partial, int64_t rows, int H, int stages, int* status) {
+  extern __shared__ __align__(128) uint8_t smem[];
+  const uint32_t row_bytes = (uint32_t)H * sizeof(T);
+  const int n_in = dres != nullptr ? 3 : 2;
+  const size_t slot_bytes = (size_t)row_bytes * n_in;
+  const Ring rg = ring_setup(smem, stages, slot_bytes);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (warp == kConsumers / 32) {
+    if (lane == 0) {
+      const uint8_t* const src[3] = {reinterpret_cast<const uint8_t*>(x), reinterpret_cast<const uint8_t*>(dy),
+                                     reinterpret_cast<const uint8_t*>(dres)};
+      produce<3>(rg, src, n_in, rows, row_bytes, stages, slot_bytes);
+    }
+  } else {
+    const int t = threadIdx.x, nvec = H / 8;
+    float ww[MV][8], acc[MV][8];
+#pragma unroll
+    for (int i = 0; i < MV; ++i) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) { acc[i][j] = 0.f; ww[i][j] = 0.f; }
+      if (t + i * kConsumers < nvec) VecIO<T, 8>::load(w + (size_t)(t + i * kConsumers) * 8, ww[i]);
+    }
+    uint32_t k = 0;
+    float r_next = blockIdx.x < rows ? inv[blockIdx.x] : 0.f;
+    for (int64_t row = blockIdx.x; row < rows; row += gridDim.x, ++k) {
+      const float r = r_next;
+      if (row + gridDim.x < rows) r_next = inv[row + gridDim.x];
+      const int s = k % stages;
+      const bool ok = mbar_wait(rg.full(s), (k / stages) & 1u, rg.abort_flag);
+      const T* sx = reinterpret_cast<const T*>(rg.slots + (size_t)s * slot_bytes);
+      float cx[MV][8], cg[MV][8];
+      float sum = 0.f;
+#pragma unroll
+      for (int i = 0; i < MV; ++i) {
+        const int v = t + i * kConsumers;
+        if (v < nvec) {
+          VecIO<T, 8>::load(sx + (size_t)v * 8, cx[i]);
+          VecIO<T, 8>::load(sx + H + (size_t)v * 8, cg[i]);
+        }
+      }
+#pragma unroll
+      for (int i = 0; i < MV; ++i) {
+        if (t + i * kConsumers < nvec) {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            acc[i][j] += cg[i][j] * cx[i][j] * r;
+            cg[i][j] *= ww[i][j];
+            sum += cg[i][j] * cx[i][j];
+          }
+        }
+      }
+      sum = warp_sum(sum);
+      float* red = rg.red + (k & 1u) * 8;
+      if (lane == 0) red[warp] = sum;
+      if (!consumers_all(ok)) break;
+      float tot = 0.f;
+#pragma unroll
+      for (int i = 0; i < kConsumers / 32; ++i) tot += red[i];
+      const float coef = tot * r * r / (float)H;
+#pragma unroll
+      for (int i = 0; i < MV; ++i) {
+        const int v = t + i * kConsumers;
+        if (v < nvec) {
+          float o[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) o[j] = (cg[i][j] - cx[i][j] * coef) * r;
+          if (n_in == 3) {   // the upstream residual gradient is still in the slot
+            float d[8];
+            VecIO<T, 8>::load(sx + 2 * (size_t)H + (size_t)v * 8, d);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) o[j] += d[j];
+          }
+          VecIO<T, 8>::store(dx + (size_t)row * H + (size_t)v * 8, o);
+        }
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(rg.empty(s));
+    }
+    // every consumer writes its columns of this CTA's partial row (zeros if the CTA had no rows)
+#pragma unroll
+    for (int i = 0; i < MV; ++i) {
+      const int v = t + i * kConsumers;
+      if (v < nvec) {
+        float* dst = partial + (size_t)blockIdx.x * H + (size_t)v * 8;
+        *reinterpret_cast<float4*>(dst) = make_float4(acc[i][0], acc[i][1], acc[i][2], acc[i][3]);
+        *reinterpret_cast<float4*>(dst + 4) = make_float4(acc[i][4], acc[i][5], acc[i][6], acc[i][7]);
+      }
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0 && *rg.abort_flag) flag_status(status, Q3_STATUS_WAIT_TIMEOUT);
+}
+
+inline int pick_stages(size_t slot_bytes) {
+  // two CTAs per SM, ~100 KB of ring each; at least 2 slots
+  int s = (int)((100 * 1024) / slot_bytes);
+  return s < 2 ? 2 : (s > kMaxStages ? kMaxStages : s);
+}
+
+template <typename K> inline int allow_smem(K kern, size_t bytes) {
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+  return e == cudaSuccess ? Q3_OK : Q3_ERR_CUDA - (int)e;
+}
+
+}  // namespace ring
+
+// True if the ring kernels serve this row width and element type.
+bool rmsnorm_ring_applies(int64_t H, int dtype) {
+  return (dtype == Q3_BF16 || dtype == Q3_F16) && H >= 2048 && H <= 8192 && H % 8 == 0;
+}
+
+// Number of partial weight-gradient rows the backward ring kernel writes (its grid size).
+int rmsnorm_bwd_ring_parts(int64_t rows) {
+  const int64_t cap = (int64_t)sm_count() * 2;
+  return (int)(rows < cap ? rows : cap);
+}
+
+template <typename T>
+static int fwd_ring_t(const void* x, const void* res, const void* w, void* y, void* res_out, float* inv, int64_t rows,
+                      int64_t H, float eps, cudaStream_t st) {
+  using namespace ring;
+  const bool add = res != nullptr;
+  const size_t slot = (size_t)H * sizeof(T) * (add ? 2 : 1);
+  const int stages = pick_stages(slot);
+  const size_t smem = ring_smem_bytes(stages, slot);
+  const int64_t cap = (int64_t)sm_count() * 2;
+  const int grid = (int)(rows < cap ? rows : cap);
+  int* status = async_status();
+  int rc;
+#define Q3_FWD(MV, ADD)                                                                                          \
+  do {                                                                                                           \
+    auto kern = rmsnorm_fwd_ring_kernel<T, MV, ADD>;                                                             \
+    if ((rc = allow_smem(kern, smem)) != Q3_OK) return rc;                                                       \
+    kern<<<grid, kThreads, smem, st>>>((const T*)x, (const T*)res, (const T*)w, (T*)y, (T*)res_out, inv, rows,   \
+                                       (int)H, eps, stages, status);                                             \
+  } while (0)
+  if (H <= 4096) { if (add) Q3_FWD(2, true); else Q3_FWD(2, false); }
+  else { if (add) Q3_FWD(4, true); else Q3_FWD(4, false); }
+#undef Q3_FWD
+  return launch_status();
+}
+
+int rmsnorm_fwd_ring(const void* x, const void* res, const void* w, void* y, void* res_out, float* inv, int64_t rows,
+                     int64_t H, float eps, int dtype, cudaStream_t st) {
+  return dtype == Q3_BF16 ? fwd_ring_t<__nv_bfloat16>(x, res, w, y, res_out, inv, rows, H, eps, st)
+                          : fwd_ring_t<__half>(x, res, w, y, res_out, inv, rows, H, eps, st);
+}
+
+template <typename T>
+static int bwd_ring_t(const void* x, const void* w, const void* dy, const void* dres, const float* inv, void* dx,
+                      float* partial, int64_t rows, int64_t H, cudaStream_t st) {
+  using namespace ring;
+  const size_t slot = (size_t)H * sizeof(T) * (dres ? 3 : 2);
+  const int stages = pick_stages(slot);
+  const size_t smem = ring_smem_bytes(stages, slot);
+  const int grid = rmsnorm_bwd_ring_parts(rows);
+  int* status = async_status();
+  int rc;
+#define Q3_BWD(MV)                                                                                               \
+  do {                                                                                                           \
+    auto kern = rmsnorm_bwd_ring_kernel<T, MV>;                                                                  \
+    if ((rc = allow_smem(kern, smem)) != Q3_OK) return rc;                                                       \
+    kern<<<grid, kThreads, smem, st>>>((const T*)x, (const T*)w, (const T*)dy, (const T*)dres, inv, (T*)dx,      \
+                                       partial, rows, (int)H, stages, status);                                   \
+  } while (0)
+  if (H <= 4096) Q3_BWD(2); else Q3_BWD(4);
+#undef Q3_BWD
+  return launch_status();
+}
+
+int rmsnorm_bwd_ring(const void* x, const void* w, const void* dy, const void* dres, const float* inv, void* dx,
+                     float* partial, int64_t rows, int64_t H, int dtype, cudaStream_t st) {
+  return dtype == Q3_BF16 ? bwd_ring_t<__nv_bfloat16>(x, w, dy, dres, inv, dx, partial, rows, H, st)
+                          : bwd_ring_t<__half>(x, w, dy, dres, inv, dx, partial, rows, H, st);
+}
+
+}  // namespace q3

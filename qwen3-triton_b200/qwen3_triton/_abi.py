@@ -28,6 +28,7 @@ SIGNATURES = {
     "q3_abi_version": (I, []),
     "q3_error_string": (c_char_p, [I]),
     "q3_device_sm_count": (I, []),
+    "q3_async_status": (I, [I, P]),
     "q3_residual_add": (I, [P, P, P, L, I, P]),
     "q3_cast": (I, [P, I, P, I, L, P]),
     "q3_swiglu_fwd": (I, [P, P, P, L, I, P]),
@@ -140,11 +141,16 @@ def status_word(device) -> torch.Tensor:
 
 def read_status(device=None, *, clear=True) -> int:
     """Synchronising read of the device status word."""
-    word = status_word(device if device is not None else torch.cuda.current_device())
+    index = device if device is not None else torch.cuda.current_device()
+    word = status_word(index)
     value = int(word.item())
     if clear and value:
         word.zero_()
-    return value
+    # the library's own word, flagged by entry points that take no status argument
+    own = ctypes.c_int(0)
+    with torch.cuda.device(word.device):
+        check(lib().q3_async_status(1 if clear else 0, ctypes.byref(own)), "q3_async_status")
+    return value | own.value
 
 
 def raise_on_status(device=None) -> None:

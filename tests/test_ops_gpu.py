@@ -59,6 +59,38 @@ def test_rms_norm_dweight_is_deterministic():
     assert torch.equal(grads[0], grads[1]) and torch.equal(grads[0], grads[2])
 
 
+@pytest.mark.parametrize('dtype', [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize('H', [2048, 4096, 5120, 8192])
+@pytest.mark.parametrize('rows', [1, 300, 3001])
+def test_wide_rows_through_the_shared_memory_ring(dtype, H, rows):
+    """Rows of 2048..8192 elements go through the bulk-copy ring kernels: fewer rows than CTAs, and enough rows that
+    every CTA wraps its ring several times (3001 rows over 296 CTAs = 10-11 rows each, 2-8 slots). Plain and
+    add+norm forms, backward with and without an incoming residual gradient; no wait may time out."""
+    from qwen3_triton import _abi
+    from qwen3_triton.kernels.norm import add_rms_norm, rms_norm
+    shape = (rows, H)
+    x, r = randn(shape, 21, dtype), randn(shape, 22, dtype)
+    w = (1 + 0.1 * randn((H,), 23)).to(dtype)
+    dy, dr = randn(shape, 24, dtype), randn(shape, 25, dtype)
+    xg, wg = dev(x).requires_grad_(True), dev(w).requires_grad_(True)
+    y = rms_norm(xg, wg, 1e-6)
+    y.backward(dev(dy))
+    close(y, O.rms_norm(x, w).to(dtype), what='y')
+    dx, dw = O.rms_norm_backward(x, w, dy)
+    close(xg.grad, dx.to(dtype), what='dx')
+    close(wg.grad, dw.to(dtype), scale=float(dw.abs().mean()), what='dw')
+    xg, rg, wg = dev(x).requires_grad_(True), dev(r).requires_grad_(True), dev(w).requires_grad_(True)
+    y, res = add_rms_norm(xg, rg, wg, 1e-6)
+    torch.autograd.backward([y, res], [dev(dy), dev(dr)])
+    y_ref, res_ref = O.add_rms_norm(x, r, w, 1e-6, round_dtype=dtype)
+    close(res, res_ref.to(dtype), what='residual_out')
+    close(y, y_ref.to(dtype), what='add y')
+    dx_ref, dw_ref = O.rms_norm_backward(res_ref, w, dy)
+    close(xg.grad, (dx_ref + dr.float()).to(dtype), what='add dx')
+    close(wg.grad, dw_ref.to(dtype), scale=float(dw_ref.abs().mean()), what='add dw')
+    assert _abi.read_status() == 0
+
+
 @pytest.mark.parametrize('dtype', [torch.bfloat16, torch.float32])
 @pytest.mark.parametrize('shape', [(2, 17, 256), (1, 64, 4096), (3, 3, 50)])
 def test_add_rms_norm(dtype, shape):
