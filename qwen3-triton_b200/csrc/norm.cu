@@ -25,6 +25,12 @@ int rmsnorm_fwd_ring(const void* x, const void* res, const void* w, void* y, voi
                      int64_t H, float eps, int dtype, cudaStream_t st);
 int rmsnorm_bwd_ring(const void* x, const void* w, const void* dy, const void* dres, const float* inv, void* dx,
                      float* partial, int64_t rows, int64_t H, int dtype, cudaStream_t st);
+bool norm_rope_ring_applies(int64_t heads, int64_t D, int dtype);
+int norm_rope_bwd_ring_parts(int64_t tokens, int64_t heads, int64_t D, int dtype);
+int norm_rope_fwd_ring(const void* x, const void* w, const void* cs, const void* sn, void* y, float* inv,
+                       int64_t tokens, int64_t heads, int64_t D, float eps, int dtype, cudaStream_t st);
+int norm_rope_bwd_ring(const void* x, const void* w, const void* cs, const void* sn, const void* dy, const float* inv,
+                       void* dx, float* partial, int64_t tokens, int64_t heads, int64_t D, int dtype, cudaStream_t st);
 template <typename T> struct DtypeOf;
 template <> struct DtypeOf<float> { static constexpr int value = Q3_F32; };
 template <> struct DtypeOf<__nv_bfloat16> { static constexpr int value = Q3_BF16; };
@@ -508,6 +514,8 @@ int norm_rope_fwd_launch(const void* x, const void* w, const void* cs, const voi
   constexpr int VF = Vec16<T>::N;
   const int64_t rows = batch * seq * heads, half = D / 2;
   const bool vec = (half % VF == 0) && aligned16(x) && aligned16(cs) && aligned16(sn) && aligned16(y) && (!NORM || aligned16(w));
+  if (NORM && vec && layout == 0 && norm_rope_ring_applies(heads, D, DtypeOf<T>::value))
+    return norm_rope_fwd_ring(x, w, cs, sn, y, inv, batch * seq, heads, D, eps, DtypeOf<T>::value, st);
   if (vec) {
     RowPlan p = plan_rows(rows, (int)(half / VF), 1, 1, 32, 16);
     if (p.tpr < 0 || p.tpr > 32) return Q3_ERR_SHAPE;
@@ -530,6 +538,14 @@ int norm_rope_bwd_launch(const void* x, const void* w, const void* cs, const voi
   const int64_t rows = batch * seq * heads, half = D / 2;
   const bool vec = (half % VF == 0) && aligned16(cs) && aligned16(sn) && aligned16(dy) && aligned16(dx) &&
                    (!NORM || (aligned16(x) && aligned16(w)));
+  if (NORM && vec && layout == 0 && norm_rope_ring_applies(heads, D, DtypeOf<T>::value)) {
+    const int parts = norm_rope_bwd_ring_parts(batch * seq, heads, D, DtypeOf<T>::value);
+    if (ws == nullptr || ws_bytes < (int64_t)parts * D * 4) return Q3_ERR_WORKSPACE;
+    const int rc = norm_rope_bwd_ring(x, w, cs, sn, dy, inv, dx, ws, batch * seq, heads, D, DtypeOf<T>::value, st);
+    if (rc != Q3_OK) return rc;
+    reduce_partials_kernel<T><<<(int)cdiv(D, 32), dim3(32, 8), 0, st>>>(ws, (T*)dw, parts, (int)D);
+    return launch_status();
+  }
   RowPlan p = vec ? plan_rows(rows, (int)(half / VF), 1, 1, 32, kPartialRowsPerSm * 2)
                   : plan_rows(rows, (int)half, 1, 4, 32, kPartialRowsPerSm * 2);
   if (p.tpr < 0 || p.tpr > 32) return Q3_ERR_SHAPE;

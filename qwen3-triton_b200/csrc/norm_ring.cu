@@ -1,5 +1,5 @@
-// RMSNorm forward / backward for wide rows (2048 <= H <= 8192 elements of 16 bits) with the rows staged through a
-// shared-memory ring by bulk asynchronous copies.
+// RMSNorm forward / backward for wide rows (2048 <= H <= 8192 elements of 16 bits), and per-head RMSNorm + RoPE on
+// token-major tensors, with the rows staged through a shared-memory ring by bulk asynchronous copies.
 //
 // The register-resident kernels of norm.cu keep one row per CTA in flight and are limited by occupancy (the
 // backward one holds ~100 live floats per thread): 41-61 % of HBM peak at H = 4096. Here a CTA is 8 consumer warps
@@ -74,7 +74,7 @@ __device__ __forceinline__ Ring ring_setup(uint8_t* smem, int stages, size_t slo
   return r;
 }
 
-inline size_t ring_smem_bytes(int stages, size_t slot_bytes) {
+__host__ __device__ inline size_t ring_smem_bytes(int stages, size_t slot_bytes) {
   return (size_t)stages * slot_bytes + 2 * kMaxStages * 8 + 16 + 16 * 4;
 }
 
@@ -270,6 +270,219 @@ rmsnorm_bwd_ring_kernel(const T* __restrict__ x, const T* __restrict__ w, const 
   if (threadIdx.x == 0 && *rg.abort_flag) flag_status(status, Q3_STATUS_WAIT_TIMEOUT);
 }
 
+// ------------------------------------------------------------------ per-head RMSNorm + RoPE, token-major rows
+// x is [tokens, heads, D]; cos/sin are [tokens, D]. A slot holds `tps` consecutive tokens: their heads*D input
+// elements (one contiguous copy), for backward the same span of dy, and their cos and sin rows. The 256 consumers
+// form 256/tpr groups of tpr = D/16 lanes; group g owns row g of the slot (token g / heads, head g % heads) and
+// each lane the vector pair (p, p + D/2). Reductions stay inside a group (shuffles), so consumers need no
+// CTA-wide barrier; warps leave the loop on their own if a wait expires.
+struct RopeGeom {
+  int tpr;        // lanes per (token, head) row = D / 16
+  int tps;        // tokens per slot
+  uint32_t x_bytes, t_bytes;   // bytes of one token's heads*D elements, of one token's D table elements
+};
+
+template <typename T, bool BWD>
+__device__ __forceinline__ void rope_produce(const Ring& rg, const RopeGeom& g, const T* x, const T* dy, const T* cs,
+                                             const T* sn, int64_t tokens, int stages, size_t slot_bytes) {
+  uint32_t k = 0;
+  const int64_t groups = (tokens + g.tps - 1) / g.tps;
+  const uint32_t x_slot = g.x_bytes * g.tps, t_slot = g.t_bytes * g.tps;
+  for (int64_t tg = blockIdx.x; tg < groups; tg += gridDim.x, ++k) {
+    const int s = k % stages;
+    if (!mbar_wait(rg.empty(s), ((k / stages) & 1u) ^ 1u, rg.abort_flag)) break;
+    const int64_t tok0 = tg * g.tps;
+    const uint32_t n = (uint32_t)((tokens - tok0) < g.tps ? (tokens - tok0) : g.tps);
+    const uint32_t xb = g.x_bytes * n, tb = g.t_bytes * n;
+    mbar_expect_tx(rg.full(s), (BWD ? 2 : 1) * xb + 2 * tb);
+    const uint32_t dst = smem_u32(rg.slots + (size_t)s * slot_bytes);
+    const uint8_t* xs = reinterpret_cast<const uint8_t*>(x) + (size_t)tok0 * g.x_bytes;
+    bulk_load(dst, xs, xb, rg.full(s));
+    uint32_t off = x_slot;
+    if (BWD) {
+      bulk_load(dst + off, reinterpret_cast<const uint8_t*>(dy) + (size_t)tok0 * g.x_bytes, xb, rg.full(s));
+      off += x_slot;
+    }
+    bulk_load(dst + off, reinterpret_cast<const uint8_t*>(cs) + (size_t)tok0 * g.t_bytes, tb, rg.full(s));
+    bulk_load(dst + off + t_slot, reinterpret_cast<const uint8_t*>(sn) + (size_t)tok0 * g.t_bytes, tb, rg.full(s));
+  }
+  const uint32_t pending = k < (uint32_t)stages ? k : (uint32_t)stages;
+  for (uint32_t j = k - pending; j < k; ++j) mbar_wait_drain(rg.full(j % stages), (j / stages) & 1u);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kThreads, 2)
+norm_rope_fwd_ring_kernel(const T* __restrict__ x, const T* __restrict__ w, const T* __restrict__ cs,
+                          const T* __restrict__ sn, T* __restrict__ y, float* __restrict__ inv, int64_t tokens,
+                          int heads, int D, float eps, RopeGeom g, int stages, int* status) {
+  extern __shared__ __align__(128) uint8_t smem[];
+  const size_t slot_bytes = (size_t)g.tps * (g.x_bytes + 2 * g.t_bytes);
+  const Ring rg = ring_setup(smem, stages, slot_bytes);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (warp == kConsumers / 32) {
+    if (lane == 0) rope_produce<T, false>(rg, g, x, nullptr, cs, sn, tokens, stages, slot_bytes);
+  } else {
+    const int half = D / 2, grp = threadIdx.x / g.tpr, p = threadIdx.x % g.tpr;
+    const int ltok = grp / heads, head = grp - ltok * heads;     // this lane's row inside a slot
+    float w1[8], w2[8];
+    VecIO<T, 8>::load(w + p * 8, w1);
+    VecIO<T, 8>::load(w + half + p * 8, w2);
+    const int64_t groups = (tokens + g.tps - 1) / g.tps;
+    uint32_t k = 0;
+    for (int64_t tg = blockIdx.x; tg < groups; tg += gridDim.x, ++k) {
+      const int s = k % stages;
+      bool ok = mbar_wait(rg.full(s), (k / stages) & 1u, rg.abort_flag);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      const int64_t token = tg * g.tps + ltok;
+      const bool valid = token < tokens;
+      const T* sx = reinterpret_cast<const T*>(rg.slots + (size_t)s * slot_bytes);
+      const T* row = sx + (size_t)grp * D;
+      const T* scs = sx + (size_t)g.tps * heads * D + (size_t)ltok * D;
+      const T* ssn = scs + (size_t)g.tps * D;
+      float a[8], b[8], c1[8], c2[8], s1[8], s2[8];
+      if (valid) {
+        VecIO<T, 8>::load(row + p * 8, a);
+        VecIO<T, 8>::load(row + half + p * 8, b);
+        VecIO<T, 8>::load(scs + p * 8, c1);
+        VecIO<T, 8>::load(scs + half + p * 8, c2);
+        VecIO<T, 8>::load(ssn + p * 8, s1);
+        VecIO<T, 8>::load(ssn + half + p * 8, s2);
+      } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) a[j] = b[j] = c1[j] = c2[j] = s1[j] = s2[j] = 0.f;
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(rg.empty(s));
+      float ss = 0.f;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) ss += a[j] * a[j] + b[j] * b[j];
+      for (int o = g.tpr >> 1; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+      const float r = rsqrtf(ss / (float)D + eps);
+      if (valid) {
+        float o1[8], o2[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const float na = a[j] * r * w1[j], nb = b[j] * r * w2[j];
+          o1[j] = na * c1[j] - nb * s1[j];
+          o2[j] = nb * c2[j] + na * s2[j];
+        }
+        T* out = y + ((size_t)token * heads + head) * D;
+        VecIO<T, 8>::store(out + p * 8, o1);
+        VecIO<T, 8>::store(out + half + p * 8, o2);
+        if (p == 0) inv[(size_t)token * heads + head] = r;
+      }
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0 && *rg.abort_flag) flag_status(status, Q3_STATUS_WAIT_TIMEOUT);
+}
+
+// Backward: dn1 = g1*cos1 + g2*sin2 ; dn2 = g2*cos2 - g1*sin1, then the RMSNorm backward of dn on x.
+// partial[cta][c] = sum over the CTA's rows of dn[c] * x[c] * inv, combined over the CTA's groups in a fixed order.
+template <typename T>
+__global__ void __launch_bounds__(kThreads, 2)
+norm_rope_bwd_ring_kernel(const T* __restrict__ x, const T* __restrict__ w, const T* __restrict__ cs,
+                          const T* __restrict__ sn, const T* __restrict__ dy, const float* __restrict__ inv,
+                          T* __restrict__ dx, float* __restrict__ partial, int64_t tokens, int heads, int D,
+                          RopeGeom g, int stages, int* status) {
+  extern __shared__ __align__(128) uint8_t smem[];
+  const size_t slot_bytes = (size_t)g.tps * (2 * g.x_bytes + 2 * g.t_bytes);
+  const Ring rg = ring_setup(smem, stages, slot_bytes);
+  float* comb = reinterpret_cast<float*>(smem + ring_smem_bytes(stages, slot_bytes));   // [groups][D], 16-byte aligned
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (warp == kConsumers / 32) {
+    if (lane == 0) rope_produce<T, true>(rg, g, x, dy, cs, sn, tokens, stages, slot_bytes);
+  } else {
+    const int half = D / 2, grp = threadIdx.x / g.tpr, p = threadIdx.x % g.tpr;
+    const int ltok = grp / heads, head = grp - ltok * heads;
+    float w1[8], w2[8], acc1[8], acc2[8];
+    VecIO<T, 8>::load(w + p * 8, w1);
+    VecIO<T, 8>::load(w + half + p * 8, w2);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc1[j] = acc2[j] = 0.f;
+    const int64_t groups = (tokens + g.tps - 1) / g.tps;
+    uint32_t k = 0;
+    auto inv_of = [&](int64_t tg) {
+      const int64_t token = tg * g.tps + ltok;
+      return (tg < groups && token < tokens) ? inv[(size_t)token * heads + head] : 0.f;
+    };
+    float r_next = inv_of(blockIdx.x);
+    for (int64_t tg = blockIdx.x; tg < groups; tg += gridDim.x, ++k) {
+      const float r = r_next;
+      r_next = inv_of(tg + gridDim.x);
+      const int s = k % stages;
+      bool ok = mbar_wait(rg.full(s), (k / stages) & 1u, rg.abort_flag);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      const int64_t token = tg * g.tps + ltok;
+      const bool valid = token < tokens;
+      const T* sx = reinterpret_cast<const T*>(rg.slots + (size_t)s * slot_bytes);
+      const size_t span = (size_t)g.tps * heads * D;
+      const T* xrow = sx + (size_t)grp * D;
+      const T* grow = sx + span + (size_t)grp * D;
+      const T* scs = sx + 2 * span + (size_t)ltok * D;
+      const T* ssn = scs + (size_t)g.tps * D;
+      // rotate the gradient first so that the tables and dy are dead before x is read: fewer live registers
+      float x1[8], x2[8], d1[8], d2[8];
+      if (valid) {
+        float g1[8], g2[8], c[8], sv[8];
+        VecIO<T, 8>::load(grow + p * 8, g1);
+        VecIO<T, 8>::load(grow + half + p * 8, g2);
+        VecIO<T, 8>::load(scs + p * 8, c);
+        VecIO<T, 8>::load(ssn + half + p * 8, sv);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) d1[j] = g1[j] * c[j] + g2[j] * sv[j];
+        VecIO<T, 8>::load(scs + half + p * 8, c);
+        VecIO<T, 8>::load(ssn + p * 8, sv);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) d2[j] = g2[j] * c[j] - g1[j] * sv[j];
+        VecIO<T, 8>::load(xrow + p * 8, x1);
+        VecIO<T, 8>::load(xrow + half + p * 8, x2);
+      } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) x1[j] = x2[j] = d1[j] = d2[j] = 0.f;
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(rg.empty(s));
+      float sum = 0.f;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        acc1[j] += d1[j] * x1[j] * r;
+        acc2[j] += d2[j] * x2[j] * r;
+        d1[j] *= w1[j];
+        d2[j] *= w2[j];
+        sum += d1[j] * x1[j] + d2[j] * x2[j];
+      }
+      for (int o = g.tpr >> 1; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+      const float coef = sum * r * r / (float)D;
+      if (valid) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          d1[j] = (d1[j] - x1[j] * coef) * r;
+          d2[j] = (d2[j] - x2[j] * coef) * r;
+        }
+        T* out = dx + ((size_t)token * heads + head) * D;
+        VecIO<T, 8>::store(out + p * 8, d1);
+        VecIO<T, 8>::store(out + half + p * 8, d2);
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      comb[(size_t)grp * D + p * 8 + j] = acc1[j];
+      comb[(size_t)grp * D + half + p * 8 + j] = acc2[j];
+    }
+  }
+  __syncthreads();
+  const int ngroups = kConsumers / g.tpr;
+  for (int c = threadIdx.x; c < D; c += blockDim.x) {
+    float tsum = 0.f;
+    for (int r2 = 0; r2 < ngroups; ++r2) tsum += comb[(size_t)r2 * D + c];
+    partial[(size_t)blockIdx.x * D + c] = tsum;
+  }
+  if (threadIdx.x == 0 && *rg.abort_flag) flag_status(status, Q3_STATUS_WAIT_TIMEOUT);
+}
+
 inline int pick_stages(size_t slot_bytes) {
   // two CTAs per SM, ~100 KB of ring each; at least 2 slots
   int s = (int)((100 * 1024) / slot_bytes);
@@ -351,6 +564,83 @@ int rmsnorm_bwd_ring(const void* x, const void* w, const void* dy, const void* d
                      float* partial, int64_t rows, int64_t H, int dtype, cudaStream_t st) {
   return dtype == Q3_BF16 ? bwd_ring_t<__nv_bfloat16>(x, w, dy, dres, inv, dx, partial, rows, H, st)
                           : bwd_ring_t<__half>(x, w, dy, dres, inv, dx, partial, rows, H, st);
+}
+
+
+// Geometry of the token-major norm+RoPE ring kernels, or tpr = 0 if they do not serve this shape: D a multiple of 16
+// up to 512 (16, 32, 64 ... lanes per row must divide a warp), and heads dividing the 256 / (D/16) rows of a slot.
+static ring::RopeGeom rope_geom(int64_t heads, int64_t D, int dtype) {
+  ring::RopeGeom g{0, 0, 0, 0};
+  if (dtype != Q3_BF16 && dtype != Q3_F16) return g;
+  if (D % 16 != 0 || D > 512) return g;
+  const int tpr = (int)(D / 16);
+  if (tpr & (tpr - 1)) return g;
+  const int rows = ring::kConsumers / tpr;
+  if (heads > rows || rows % heads != 0) return g;
+  g.tpr = tpr;
+  g.tps = (int)(rows / heads);
+  g.x_bytes = (uint32_t)(heads * D * 2);
+  g.t_bytes = (uint32_t)(D * 2);
+  return g;
+}
+
+bool norm_rope_ring_applies(int64_t heads, int64_t D, int dtype) { return rope_geom(heads, D, dtype).tpr != 0; }
+
+int norm_rope_bwd_ring_parts(int64_t tokens, int64_t heads, int64_t D, int dtype) {
+  const ring::RopeGeom g = rope_geom(heads, D, dtype);
+  const int64_t groups = (tokens + g.tps - 1) / g.tps, cap = (int64_t)sm_count() * 2;
+  return (int)(groups < cap ? groups : cap);
+}
+
+template <typename T>
+static int rope_fwd_ring_t(const void* x, const void* w, const void* cs, const void* sn, void* y, float* inv,
+                           int64_t tokens, int64_t heads, int64_t D, float eps, int dtype, cudaStream_t st) {
+  using namespace ring;
+  const RopeGeom g = rope_geom(heads, D, dtype);
+  const size_t slot = (size_t)g.tps * (g.x_bytes + 2 * g.t_bytes);
+  const int stages = pick_stages(slot);
+  const size_t smem = ring_smem_bytes(stages, slot);
+  const int64_t groups = (tokens + g.tps - 1) / g.tps, cap = (int64_t)sm_count() * 2;
+  const int grid = (int)(groups < cap ? groups : cap);
+  auto kern = norm_rope_fwd_ring_kernel<T>;
+  int rc = allow_smem(kern, smem);
+  if (rc != Q3_OK) return rc;
+  kern<<<grid, kThreads, smem, st>>>((const T*)x, (const T*)w, (const T*)cs, (const T*)sn, (T*)y, inv, tokens,
+                                     (int)heads, (int)D, eps, g, stages, async_status());
+  return launch_status();
+}
+
+int norm_rope_fwd_ring(const void* x, const void* w, const void* cs, const void* sn, void* y, float* inv,
+                       int64_t tokens, int64_t heads, int64_t D, float eps, int dtype, cudaStream_t st) {
+  return dtype == Q3_BF16 ? rope_fwd_ring_t<__nv_bfloat16>(x, w, cs, sn, y, inv, tokens, heads, D, eps, dtype, st)
+                          : rope_fwd_ring_t<__half>(x, w, cs, sn, y, inv, tokens, heads, D, eps, dtype, st);
+}
+
+template <typename T>
+static int rope_bwd_ring_t(const void* x, const void* w, const void* cs, const void* sn, const void* dy,
+                           const float* inv, void* dx, float* partial, int64_t tokens, int64_t heads, int64_t D,
+                           int dtype, cudaStream_t st) {
+  using namespace ring;
+  const RopeGeom g = rope_geom(heads, D, dtype);
+  const size_t slot = (size_t)g.tps * (2 * g.x_bytes + 2 * g.t_bytes);
+  const size_t comb = (size_t)(kConsumers / g.tpr) * D * sizeof(float);
+  int stages = (int)((100 * 1024 - comb) / slot);
+  stages = stages < 2 ? 2 : (stages > kMaxStages ? kMaxStages : stages);
+  const size_t smem = ring_smem_bytes(stages, slot) + comb;
+  const int grid = norm_rope_bwd_ring_parts(tokens, heads, D, dtype);
+  auto kern = norm_rope_bwd_ring_kernel<T>;
+  int rc = allow_smem(kern, smem);
+  if (rc != Q3_OK) return rc;
+  kern<<<grid, kThreads, smem, st>>>((const T*)x, (const T*)w, (const T*)cs, (const T*)sn, (const T*)dy, inv, (T*)dx,
+                                     partial, tokens, (int)heads, (int)D, g, stages, async_status());
+  return launch_status();
+}
+
+int norm_rope_bwd_ring(const void* x, const void* w, const void* cs, const void* sn, const void* dy, const float* inv,
+                       void* dx, float* partial, int64_t tokens, int64_t heads, int64_t D, int dtype,
+                       cudaStream_t st) {
+  return dtype == Q3_BF16 ? rope_bwd_ring_t<__nv_bfloat16>(x, w, cs, sn, dy, inv, dx, partial, tokens, heads, D, dtype, st)
+                          : rope_bwd_ring_t<__half>(x, w, cs, sn, dy, inv, dx, partial, tokens, heads, D, dtype, st);
 }
 
 }  // namespace q3

@@ -217,6 +217,26 @@ def test_norm_rope(dtype, B, S, H, D):
     close(wg.grad, dw.to(dtype), scale=float(dw.abs().mean()), what='dw')
 
 
+@pytest.mark.parametrize('dtype', [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize('B,S,H,D', [(1, 5000, 32, 128), (1, 5001, 8, 128), (3, 1667, 16, 64), (2, 301, 1, 256)])
+def test_norm_rope_through_the_shared_memory_ring(dtype, B, S, H, D):
+    """Token-major norm+RoPE at sizes where every CTA wraps its ring many times, with a ragged last slot
+    (5001 tokens in slots of 4) and one to several tokens per slot; no wait may time out."""
+    from qwen3_triton import _abi
+    from qwen3_triton.kernels.norm_rope import norm_rope
+    x, dy = randn((B, S, H, D), 61, dtype), randn((B, S, H, D), 62, dtype)
+    w = (1 + 0.1 * randn((D,), 63)).to(dtype)
+    cos, sin = randn((B, S, D), 64, dtype), randn((B, S, D), 65, dtype)
+    xg, wg = dev(x).requires_grad_(True), dev(w).requires_grad_(True)
+    y = norm_rope(xg, wg, dev(cos), dev(sin), 1e-6)
+    y.backward(dev(dy))
+    close(y, O.norm_rope(x, w, cos, sin).to(dtype), what='y')
+    dx, dw = O.norm_rope_backward(x, w, cos, sin, dy)
+    close(xg.grad, dx.to(dtype), what='dx')
+    close(wg.grad, dw.to(dtype), scale=float(dw.abs().mean()), what='dw')
+    assert _abi.read_status() == 0
+
+
 def test_fused_qk_norm_rope_golden(golden_ops):
     from ops.triton.fused_qk_norm_rope import fused_qk_norm_rope_triton
     d = recipe.op_inputs()
