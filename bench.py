@@ -34,7 +34,7 @@ UNIT = "tokens/s"
 
 # kernels launched by one call of each C-ABI entry (for the gpu_launches claim)
 LAUNCHES = {"q3_rmsnorm_bwd": 2, "q3_add_rmsnorm_bwd": 2, "q3_norm_rope_bwd": 2, "q3_adamw_multi": 2, "q3_ce_fwd": 2,
-            "q3_attn_bwd": 3, "q3_vce_finish": 2, "q3_embedding_bwd": 1}
+            "q3_attn_bwd": 3, "q3_vce_finish": 2, "q3_embedding_bwd": 2, "q3_embedding_shard_bwd": 2}
 
 
 def slice_config(layers):
@@ -305,6 +305,25 @@ def census(counter):
     return by_name, gemm_flops, gemm_ms
 
 
+def unit_sizes(layers):
+    """FSDP unit sizes for the decoder layers. Default: units of 4 layers, but the first four layers as 1+1+2, so that
+    the all-gather that cannot hide (the first) and the reduce-scatter that cannot hide (the last) are small.
+    Q3_BENCH_LAYERS_PER_UNIT = an integer (uniform) or a comma-separated list that sums to the layer count."""
+    spec = os.environ.get("Q3_BENCH_LAYERS_PER_UNIT", "")
+    if "," in spec:
+        return [int(v) for v in spec.split(",")]
+    if spec:
+        return int(spec)
+    if layers < 8:
+        return 1
+    sizes = [1, 1, 2]
+    rest = layers - 4
+    sizes += [4] * (rest // 4)
+    if rest % 4:
+        sizes.append(rest % 4)
+    return sizes
+
+
 def run_fsdp(args):
     """N > 1: BASELINE config 5 - the full 36-layer model under FSDP2 (one process per GPU, NCCL), bf16 parameter
     all-gather, fp32 gradient reduce-scatter, vocabulary-parallel lm_head + cross-entropy, per-layer activation
@@ -331,7 +350,8 @@ def run_fsdp(args):
     ckpt = os.environ.get("Q3_BENCH_CHECKPOINT", "selective")     # 'selective' or 'full' per-layer recomputation
     model = shard_vocab_loss_model(model, keep_full_layers=layers, checkpoint_every=1,
                                    skip_embedding_backward_gather=True, fused_vocab_dw=True, communication=None,
-                                   checkpoint_mode=ckpt, layers_per_unit=int(os.environ.get("Q3_BENCH_LAYERS_PER_UNIT", "4")))
+                                   checkpoint_mode=ckpt, layers_per_unit=unit_sizes(layers),
+                                   vocab_parallel_embedding=os.environ.get("Q3_BENCH_VP_EMBEDDING", "1") == "1")
     model.lm_head.fused = os.environ.get("Q3_BENCH_FUSED_LOSS", "0") == "1"
     hooks = configure(model, comm)
     decoder = [p for n, p in model.named_parameters() if not n.startswith("lm_head.")]
@@ -406,8 +426,9 @@ def run_fsdp(args):
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
             "data": "synthetic",
-            "config": {"workload": "qwen3-8b %d layers under FSDP2, microbatch 1x2048 per GPU, vocab-parallel head, "
-                                   "per-layer %s activation recompute, AdamW (BASELINE config 5)" % (layers, ckpt),
+            "config": {"workload": "qwen3-8b %d layers under FSDP2, microbatch 1x2048 per GPU, vocab-parallel head%s, "
+                                   "per-layer %s activation recompute, AdamW (BASELINE config 5)" % (
+                                       layers, " and embedding" if os.environ.get("Q3_BENCH_VP_EMBEDDING", "1") == "1" else "", ckpt),
                        "global_batch": batch * world, "seq_len": seq, "parallelism": "fsdp%d" % world,
                        "l2": "weights and activations >> L2", "mfu_of_%s_peak_per_gpu" % peak_kind: mfu,
                        "tokens_per_s_per_gpu": value / world, "last_loss": last,

@@ -155,9 +155,24 @@ int q3_embedding_fwd(const void* ids, int ids_are_int64, const void* weight, voi
                      int64_t vocab, int dtype, int* status, q3_stream_t stream);
 
 /* Dense dweight [vocab, H]: zero-filled, then one writer per token id sums its dy rows in position order
- * (deterministic, no float atomics). Reference: qwen3_triton/kernels/embedding.py:24-46,68-77. */
-int q3_embedding_bwd(const void* ids, int ids_are_int64, const void* dy, void* dweight, int64_t tokens, int64_t H,
-                     int64_t vocab, int dtype, q3_stream_t stream);
+ * (deterministic, no float atomics). workspace: q3_embedding_bwd_workspace_bytes(tokens) bytes (two int32 per
+ * position: next position with the same id, "has a predecessor").
+ * Reference: qwen3_triton/kernels/embedding.py:24-46,68-77. */
+int64_t q3_embedding_bwd_workspace_bytes(int64_t tokens);
+int q3_embedding_bwd(const void* ids, int ids_are_int64, const void* dy, void* dweight, void* workspace,
+                     int64_t workspace_bytes, int64_t tokens, int64_t H, int64_t vocab, int dtype, q3_stream_t stream);
+
+/* One contiguous shard of the table, rows [row_lo, row_lo + rows), stored in w_dtype (fp32 master or the compute type):
+ * y[t, :] (y_dtype) = the row of ids[t] if this shard owns it, else zeros, so that the sum over shards is the full
+ * lookup; H % 8 == 0. An id outside [0, vocab) sets Q3_STATUS_ID_RANGE. The backward form writes the shard's fp32
+ * gradient scale * sum of dy rows over owned positions, zero elsewhere, deterministically.
+ * No counterpart in the reference (its embedding is sharded by FSDP and gathered whole). */
+int q3_embedding_shard_fwd(const void* ids, int ids_are_int64, const void* weight_shard, int w_dtype, void* y, int y_dtype,
+                           int64_t tokens, int64_t H, int64_t vocab, int64_t row_lo, int64_t rows, int* status,
+                           q3_stream_t stream);
+int q3_embedding_shard_bwd(const void* ids, int ids_are_int64, const void* dy, int dtype, float* dweight_shard,
+                           void* workspace, int64_t workspace_bytes, int64_t tokens, int64_t H, int64_t row_lo,
+                           int64_t rows, double scale, q3_stream_t stream);
 
 /* ---- cross-entropy over materialised logits ------------------------------------------------- */
 

@@ -46,7 +46,10 @@ SIGNATURES = {
     "q3_rope_apply": (I, [P, P, P, P, L, L, L, L, I, I, I, P]),
     "q3_rope_tables": (I, [P, I, P, P, P, L, L, I, P]),
     "q3_embedding_fwd": (I, [P, I, P, P, L, L, L, I, P, P]),
-    "q3_embedding_bwd": (I, [P, I, P, P, L, L, L, I, P]),
+    "q3_embedding_bwd_workspace_bytes": (L, [L]),
+    "q3_embedding_bwd": (I, [P, I, P, P, P, L, L, L, L, I, P]),
+    "q3_embedding_shard_fwd": (I, [P, I, P, I, P, I, L, L, L, L, L, P, P]),
+    "q3_embedding_shard_bwd": (I, [P, I, P, I, P, P, L, L, L, L, L, D, P]),
     "q3_ce_fwd": (I, [P, P, P, P, P, P, P, L, L, L, L, I, P, P]),
     "q3_ce_local_rows": (I, [P, P, P, P, L, L, L, L, L, L, I, P, P]),
     "q3_ce_grad": (I, [P, P, P, P, P, P, L, L, L, L, L, L, L, I, P]),

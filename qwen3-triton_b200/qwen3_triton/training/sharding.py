@@ -55,7 +55,10 @@ class VocabLossQwen3(PrecisionQwen3ForCausalLM):
 
 def shard_vocab_loss_model(model, *, keep_full_layers, checkpoint_every, skip_embedding_backward_gather,
                            fused_vocab_dw=False, communication=None, mesh=None, checkpoint_mode='full',
-                           layers_per_unit=1):
+                           layers_per_unit=1, vocab_parallel_embedding=False):
+    """Reference surface (scripts/vocab_model_v12.py:35-56) plus three knobs: `checkpoint_mode`, `layers_per_unit`
+    (an int, or a sequence of unit sizes that sums to the layer count) and `vocab_parallel_embedding` (the token
+    table stays row-sharded outside FSDP instead of being gathered and its dense gradient reduce-scattered)."""
     if model.config.tie_word_embeddings:
         raise ValueError('Untied head required')
     if not 0 <= keep_full_layers <= len(model.model.layers):
@@ -68,12 +71,24 @@ def shard_vocab_loss_model(model, *, keep_full_layers, checkpoint_every, skip_em
     body = model.model
     mp = MixedPrecisionPolicy(param_dtype=torch.bfloat16, reduce_dtype=torch.float32)
     kw = dict(mp_policy=mp) if mesh is None else dict(mp_policy=mp, mesh=mesh)
-    fully_shard(body.embed_tokens.float(), reshard_after_forward=True, **kw)
-    if skip_embedding_backward_gather:
-        body.embed_tokens.set_unshard_in_backward(False)
+    ignored = {model.lm_head.weight}
+    if vocab_parallel_embedding:
+        from .vocab_parallel import VocabParallelEmbedding
+        body.embed_tokens = VocabParallelEmbedding(body.embed_tokens.weight.detach().cpu(), communication=communication)
+        ignored.add(body.embed_tokens.weight)
+    else:
+        fully_shard(body.embed_tokens.float(), reshard_after_forward=True, **kw)
+        if skip_embedding_backward_gather:
+            body.embed_tokens.set_unshard_in_backward(False)
     checkpointed = checkpoint_layer_indices(len(body.layers), every=checkpoint_every)
-    if layers_per_unit < 1:
-        raise ValueError('layers_per_unit must be positive')
+    if isinstance(layers_per_unit, int):
+        if layers_per_unit < 1:
+            raise ValueError('layers_per_unit must be positive')
+        sizes = [min(layers_per_unit, len(body.layers) - first) for first in range(0, len(body.layers), layers_per_unit)]
+    else:
+        sizes = [int(n) for n in layers_per_unit]
+        if not sizes or min(sizes) < 1 or sum(sizes) != len(body.layers):
+            raise ValueError('layers_per_unit sizes must be positive and sum to the number of layers')
     for index, layer in enumerate(body.layers):
         layer = layer.float()
         if index in checkpointed:
@@ -87,12 +102,14 @@ def shard_vocab_loss_model(model, *, keep_full_layers, checkpoint_every, skip_em
     # hooks cost about a millisecond per unit and direction; at 2048 tokens per GPU a B200 finishes a
     # layer's forward in about that time, so larger units keep the GPU fed. Collective payloads grow by
     # the same factor (4 layers: 1.5 GB gathered, 3 GB reduced), still far below the memory budget.
-    for first in range(0, len(body.layers), layers_per_unit):
-        group = [body.layers[i] for i in range(first, min(first + layers_per_unit, len(body.layers)))]
+    first = 0
+    for size in sizes:
+        group = [body.layers[i] for i in range(first, first + size)]
         retain = first + len(group) - 1 >= len(body.layers) - keep_full_layers
         fully_shard(group if len(group) > 1 else group[0], reshard_after_forward=not retain, **kw)
+        first += size
     fully_shard(body.norm.float(), reshard_after_forward=True, **kw)
     body.rotary_emb.cuda()
-    fully_shard(model, reshard_after_forward=True, ignored_params={model.lm_head.weight}, **kw)
+    fully_shard(model, reshard_after_forward=True, ignored_params=ignored, **kw)
     model.config.use_cache = False
     return model

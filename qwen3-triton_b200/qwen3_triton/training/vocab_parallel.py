@@ -205,3 +205,76 @@ class VocabParallelCE(torch.nn.Module):
         if self.fused and not diagnostics and self.in_features % 8 == 0 and self.weight.shape[0] % 8 == 0:
             return _FusedVocabCE.apply(hidden, self.weight, labels, ignore_index, self), None
         return _VocabCE.apply(hidden, self.weight, labels, ignore_index, diagnostics, self)
+
+
+class _VocabEmbedding(torch.autograd.Function):
+    """Lookup in a row-sharded table. Forward: all-gather the token ids (a few KB), every rank looks up the rows it
+    owns for the tokens of all ranks (zeros elsewhere), a reduce-scatter SUM hands each rank its own tokens' rows
+    (each row has exactly one non-zero contribution, so the sum is exact). Backward: all-gather the hidden
+    gradients, accumulate the owned rows locally in FP32 in a fixed order, divide by the number of data ranks
+    (the mean FSDP's reduce-scatter AVG would give). Traffic per step: [W*T, H] BF16 each way instead of the
+    whole table (BF16 gather + FP32 gradient reduce-scatter)."""
+
+    @staticmethod
+    def forward(ctx, ids, weight, owner):
+        from ..kernels.embedding import shard_lookup
+        world, rank = owner.world, owner.rank
+        if ids.dtype != torch.int64 or not ids.is_contiguous() or weight.dtype != torch.float32 or ids.device != weight.device:
+            raise ValueError('Contiguous int64 IDs and a local FP32 table shard on one device required')
+        n = ids.numel()
+        rows, h = weight.shape
+        all_ids = torch.empty(world * n, device=ids.device, dtype=ids.dtype)
+        _gather(owner, all_ids, ids.view(-1))
+        partial = shard_lookup(all_ids, weight, rank * rows, world * rows, torch.bfloat16)
+        if world == 1:
+            out = partial
+        else:
+            out = torch.empty((n, h), device=ids.device, dtype=torch.bfloat16)
+            if owner.communication is None:
+                dist.reduce_scatter_tensor(out, partial, op=dist.ReduceOp.SUM)
+            else:
+                owner.communication.reduce_scatter(out, partial, 'sum')
+        ctx.save_for_backward(all_ids)
+        ctx.owner, ctx.rows = owner, rows
+        owner.forward_calls += 1
+        return out.view(*ids.shape, h)
+
+    @staticmethod
+    def backward(ctx, dy):
+        from ..kernels.embedding import shard_weight_gradient
+        all_ids, = ctx.saved_tensors
+        owner = ctx.owner
+        world, rank = owner.world, owner.rank
+        h = dy.shape[-1]
+        dy = dy.contiguous().view(-1, h)
+        all_dy = torch.empty((world * dy.shape[0], h), device=dy.device, dtype=dy.dtype)
+        _gather(owner, all_dy, dy)
+        dw = shard_weight_gradient(all_ids, all_dy, rank * ctx.rows, ctx.rows, 1.0 / world)
+        owner.backward_calls += 1
+        return None, dw, None
+
+
+class VocabParallelEmbedding(torch.nn.Module):
+    """Token embedding whose table is split by rows over the data ranks and never gathered; the counterpart of
+    VocabParallelCE for the input side. `weight` is this rank's contiguous FP32 master shard and must be kept out
+    of FSDP; its gradient arrives already averaged over data ranks. No counterpart in the reference, which lets
+    FSDP gather the whole table every step (qwen3_triton/_model.py:110-118 under scripts/vocab_model_v12.py:43-44)."""
+
+    def __init__(self, full_weight_cpu, *, communication=None):
+        super().__init__()
+        self.world, self.rank = _world()
+        if full_weight_cpu.device.type != 'cpu' or full_weight_cpu.ndim != 2 or full_weight_cpu.shape[0] % self.world:
+            raise ValueError('Equal CPU vocabulary shards required')
+        if full_weight_cpu.shape[1] % 8:
+            raise ValueError('Hidden size must be a multiple of 8')
+        self.num_embeddings, self.embedding_dim = full_weight_cpu.shape
+        v = self.num_embeddings // self.world
+        self.weight = torch.nn.Parameter(full_weight_cpu[self.rank * v:(self.rank + 1) * v].float().cuda().clone())
+        self.communication = communication
+        self.forward_calls = 0
+        self.backward_calls = 0
+
+    def forward(self, ids):
+        if ids.dtype != torch.int64:
+            raise TypeError('int64 token ids required')
+        return _VocabEmbedding.apply(ids.contiguous(), self.weight, self)

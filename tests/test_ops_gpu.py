@@ -280,6 +280,53 @@ def test_embedding_gather_bit_exact_and_dense_gradient(dtype, idtype):
     assert torch.equal(g1, wg.grad)                                        # deterministic
 
 
+@pytest.mark.parametrize('world', [1, 4])
+def test_embedding_vocabulary_shards_sum_to_the_full_lookup_and_gradient(world):
+    """Each of `world` row shards (fp32 master) looks up the tokens it owns and zeros elsewhere: the sum over
+    shards is the bf16-cast full lookup bit for bit; the shard gradients, stacked, are the full fp32 gradient
+    times the scale; long chains of one repeated token and ids at the shard edges included."""
+    from qwen3_triton.kernels.embedding import shard_lookup, shard_weight_gradient
+    V, H, T = 1024, 264, 5000
+    w = randn((V, H), 66, torch.float32)
+    g = torch.Generator().manual_seed(67)
+    ids = torch.randint(0, V, (T,), generator=g)
+    ids[100:1300] = 255                 # one chain of 1200 positions, on a shard edge for world 4
+    ids[0], ids[1], ids[-1] = 0, V - 1, 256
+    dy = randn((T, H), 68, torch.bfloat16)
+    rows = V // world
+    total = torch.zeros(T, H)
+    grads = []
+    for r in range(world):
+        shard = w[r * rows:(r + 1) * rows].cuda().contiguous()
+        part = shard_lookup(ids.cuda(), shard, r * rows, V, torch.bfloat16)
+        own = (ids >= r * rows) & (ids < (r + 1) * rows)
+        assert part[~own.cuda()].abs().sum() == 0
+        total += part.float().cpu()
+        grads.append(shard_weight_gradient(ids.cuda(), dev(dy), r * rows, rows, 0.25).cpu())
+        assert torch.equal(grads[-1], shard_weight_gradient(ids.cuda(), dev(dy), r * rows, rows, 0.25).cpu())
+    assert torch.equal(total, w.to(torch.bfloat16)[ids].float())
+    ref = torch.zeros(V, H, dtype=torch.float64).index_add_(0, ids, dy.double()) * 0.25
+    torch.testing.assert_close(torch.cat(grads).double(), ref, rtol=1e-5, atol=1e-5)
+
+
+def test_vocab_parallel_embedding_module_world_1():
+    from qwen3_triton.training.vocab_parallel import VocabParallelEmbedding
+    V, H = 512, 128
+    w = randn((V, H), 69, torch.float32)
+    emb = VocabParallelEmbedding(w)
+    g = torch.Generator().manual_seed(70)
+    ids = torch.randint(0, V, (2, 300), generator=g)
+    y = emb(ids.cuda())
+    assert y.dtype == torch.bfloat16 and torch.equal(y.cpu(), w.to(torch.bfloat16)[ids])
+    dy = randn((2, 300, H), 71, torch.bfloat16)
+    y.backward(dev(dy))
+    ref = torch.zeros(V, H).index_add_(0, ids.view(-1), dy.float().view(-1, H))
+    torch.testing.assert_close(emb.weight.grad.cpu(), ref, rtol=1e-5, atol=1e-5)
+    assert emb.forward_calls == 1 and emb.backward_calls == 1
+    with pytest.raises(TypeError):
+        emb(ids.int().cuda())
+
+
 def test_embedding_out_of_range_id_sets_status_not_trap():
     from qwen3_triton import _abi
     from qwen3_triton.kernels.embedding import embedding
