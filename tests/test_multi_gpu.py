@@ -1,0 +1,93 @@
+"""Two ranks on two GPUs (skipped on a single-GPU box): the vocabulary-parallel embedding against the full lookup
+and the averaged full gradient, and one training step of a small fused-layer model under FSDP2 with the embedding
+gathered by FSDP versus kept vocabulary-parallel (same loss, same embedding-gradient shard, same loss after AdamW)."""
+import os
+import subprocess
+import sys
+import textwrap
+from pathlib import Path
+
+import pytest
+import torch
+
+ROOT = Path(__file__).resolve().parent.parent
+pytestmark = pytest.mark.gpu
+
+WORKER = textwrap.dedent('''
+    import os, sys, types, torch, torch.distributed as dist
+    sys.path.insert(0, r"%s")
+    from qwen3_triton import _abi, model_for_variant
+    from qwen3_triton.runtime.adamw import TritonAdamW
+    from qwen3_triton.runtime.collectives import NcclCollectives
+    from qwen3_triton.runtime.fsdp import configure
+    from qwen3_triton.training.sharding import shard_vocab_loss_model
+    from qwen3_triton.training.vocab_parallel import VocabParallelEmbedding
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    dev = torch.device("cuda", int(os.environ["LOCAL_RANK"]))
+    torch.cuda.set_device(dev)
+    dist.init_process_group("nccl", device_id=dev)
+
+    # 1. vocabulary-parallel embedding
+    V, H, T = 1024, 256, 700
+    g = torch.Generator().manual_seed(5)
+    full = torch.randn(V, H, generator=g)
+    ids_all = torch.randint(0, V, (world, 2, T // 2), generator=g)
+    ids_all[:, 0, :50] = 511                                  # repeated token on a shard edge
+    dy_all = torch.randn(world, 2, T // 2, H, generator=g).to(torch.bfloat16)
+    emb = VocabParallelEmbedding(full)
+    y = emb(ids_all[rank].to(dev))
+    assert torch.equal(y.cpu(), full.to(torch.bfloat16)[ids_all[rank]])
+    y.backward(dy_all[rank].to(dev))
+    ref = torch.zeros(V, H, dtype=torch.float64).index_add_(0, ids_all.view(-1), dy_all.double().view(-1, H)) / world
+    rows = V // world
+    torch.testing.assert_close(emb.weight.grad.double().cpu(), ref[rank * rows:(rank + 1) * rows], rtol=1e-5, atol=1e-5)
+
+    # 2. one FSDP2 step, embedding gathered by FSDP vs vocabulary-parallel
+    cfg = types.SimpleNamespace(model_type="qwen3", hidden_act="silu", attention_dropout=0.0, attention_bias=False,
+                                use_sliding_window=False, rope_scaling=None, vocab_size=1024, hidden_size=256,
+                                intermediate_size=512, num_hidden_layers=4, num_attention_heads=2, num_key_value_heads=1,
+                                head_dim=128, max_position_embeddings=512, rms_norm_eps=1e-6, rope_theta=1e6,
+                                initializer_range=0.02, tie_word_embeddings=False, use_cache=False)
+    gen = torch.Generator().manual_seed(100 + rank)
+    ids = torch.randint(0, cfg.vocab_size, (2, 256), generator=gen).to(dev)
+    results = []
+    for vp in (False, True):
+        torch.manual_seed(1234)
+        with torch.device(dev):
+            model = model_for_variant(cfg, "b200_fused")
+        comm = NcclCollectives()
+        model = shard_vocab_loss_model(model, keep_full_layers=4, checkpoint_every=1, skip_embedding_backward_gather=True,
+                                       fused_vocab_dw=True, communication=None, checkpoint_mode="selective",
+                                       layers_per_unit=[1, 1, 2], vocab_parallel_embedding=vp)
+        configure(model, comm)
+        opt = TritonAdamW([p for p in model.parameters()], lr=1e-3, betas=(0.9, 0.95), weight_decay=0.1)
+        out = model(ids, labels=ids)
+        out.loss.backward()
+        w = model.model.embed_tokens.weight
+        grad = w.grad.to_local() if hasattr(w.grad, "to_local") else w.grad
+        opt.step()
+        opt.zero_grad(set_to_none=True)
+        loss2 = model(ids, labels=ids).loss
+        results.append((float(out.loss), grad.float().cpu().clone(), float(loss2)))
+        assert _abi.read_status() == 0
+    (l0, g0, s0), (l1, g1, s1) = results
+    assert abs(l0 - l1) / abs(l0) < 1e-3, (l0, l1)
+    assert abs(s0 - s1) / abs(s0) < 2e-3, (s0, s1)
+    assert s0 < l0
+    rel = float((g0 - g1).norm() / g0.norm())
+    assert rel < 2e-2, rel
+    dist.barrier(); dist.destroy_process_group()
+    sys.stdout.write("rank" + str(rank) + "ok" + chr(10)); sys.stdout.flush()
+''') % str(ROOT / "qwen3-triton_b200")
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_two_gpu_vocab_parallel_embedding_and_fsdp_step(tmp_path):
+    script = tmp_path / "worker.py"
+    script.write_text(WORKER)
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", OMP_NUM_THREADS="1")
+    res = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2",
+                          "--master-addr", "127.0.0.1", "--master-port", "29621", str(script)], capture_output=True,
+                         text=True, timeout=600, env=env)
+    assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-5000:]
+    assert "rank0ok" in res.stdout and "rank1ok" in res.stdout
