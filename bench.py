@@ -34,7 +34,23 @@ UNIT = "tokens/s"
 
 # kernels launched by one call of each C-ABI entry (for the gpu_launches claim)
 LAUNCHES = {"q3_rmsnorm_bwd": 2, "q3_add_rmsnorm_bwd": 2, "q3_norm_rope_bwd": 2, "q3_adamw_multi": 2, "q3_ce_fwd": 2,
-            "q3_attn_bwd": 3, "q3_vce_finish": 2, "q3_embedding_bwd": 2, "q3_embedding_shard_bwd": 2}
+            "q3_attn_bwd": 3, "q3_vce_finish": 2, "q3_embedding_bwd": 2, "q3_embedding_shard_bwd": 2,
+            "q3_qk_norm_rope_bwd": 3}
+
+
+GEMM_ENTRIES = ("q3_gemm", "q3_gemm_acc", "q3_gate_up_swiglu_fwd", "q3_linear_fwd_grouped", "q3_linear_dgrad_grouped",
+                "q3_linear_wgrad_grouped")
+
+
+def gemm_flops_of(name, a):
+    """FLOPs of one call of a GEMM entry point from its recorded arguments (0 for anything else)."""
+    if name in ("q3_gemm", "q3_gemm_acc"):
+        return 2.0 * a[7] * a[8] * a[9]
+    if name == "q3_gate_up_swiglu_fwd":
+        return 4.0 * a[6] * a[7] * a[8]
+    if name in ("q3_linear_fwd_grouped", "q3_linear_dgrad_grouped", "q3_linear_wgrad_grouped"):
+        return 2.0 * a[5] * a[6] * sum(a[3][i] for i in range(a[4]))
+    return 0.0
 
 
 def slice_config(layers):
@@ -248,11 +264,8 @@ def run_ours(args):
     for name, a, s, e in counter.records:
         t = s.elapsed_time(e)
         by_name[name] = by_name.get(name, 0.0) + t
-        if name == "q3_gemm":
-            gemm_flops += 2.0 * a[7] * a[8] * a[9]
-        elif name == "q3_gate_up_swiglu_fwd":
-            gemm_flops += 4.0 * a[6] * a[7] * a[8]
-    gemm_ms = by_name.get("q3_gemm", 0.0) + by_name.get("q3_gate_up_swiglu_fwd", 0.0)
+        gemm_flops += gemm_flops_of(name, a)
+    gemm_ms = sum(by_name.get(n, 0.0) for n in GEMM_ENTRIES)
     peak_tf, _, peak_kind = measured_peaks()
     achieved = gemm_flops / (gemm_ms * 1e-3) / 1e12 if gemm_ms > 0 else 0.0
     total_ms = sum(by_name.values())
@@ -275,7 +288,7 @@ def run_ours(args):
                 "d2h_bytes_per_step": 4},
         "gpu_launches": launches,
         "clocks": clocks,
-        "roofline": {"bound": "tensor", "kernel": "gemm_tc_kernel (all q3_gemm + q3_gate_up_swiglu_fwd launches of a step)",
+        "roofline": {"bound": "tensor", "kernel": "gemm_tc_kernel (all GEMM entry points of a step: q3_gemm, q3_linear_*_grouped, q3_gate_up_swiglu_fwd)",
                      "achieved": achieved, "peak": peak_tf, "unit": "TFLOP/s", "frac": achieved / peak_tf,
                      "peak_kind": peak_kind + " bf16_tflops_sustained", "traffic": None,
                      "gemm_ms_per_step": gemm_ms, "all_kernels_ms_per_step": total_ms, "census_ms": census},
@@ -290,18 +303,16 @@ def census(counter):
     shapes = {}
     for name, a, s, e in counter.records:
         by_name[name] = by_name.get(name, 0.0) + s.elapsed_time(e)
-        if name == "q3_gemm":
+        if name in ("q3_gemm", "q3_gemm_acc"):
             key = (a[7], a[8], a[9], "A:%s B:%s" % ("K" if a[2] == 1 else "MN", "K" if a[4] == 1 else "MN"))
             cnt, tot = shapes.get(key, (0, 0.0))
             shapes[key] = (cnt + 1, tot + s.elapsed_time(e))
-            gemm_flops += 2.0 * a[7] * a[8] * a[9]
-        elif name == "q3_gate_up_swiglu_fwd":
-            gemm_flops += 4.0 * a[6] * a[7] * a[8]
+        gemm_flops += gemm_flops_of(name, a)
     if os.environ.get("Q3_BENCH_PROFILE"):
         for (m, n, k, lay), (cnt, tot) in sorted(shapes.items(), key=lambda kv: -kv[1][1]):
             sys.stderr.write("gemm %6d x %6d x %6d %-10s n=%3d total %8.3f ms avg %8.1f us %7.1f TFLOP/s\n" % (
                 m, n, k, lay, cnt, tot, tot / cnt * 1e3, 2.0 * m * n * k * cnt / tot / 1e9))
-    gemm_ms = by_name.get("q3_gemm", 0.0) + by_name.get("q3_gate_up_swiglu_fwd", 0.0)
+    gemm_ms = sum(by_name.get(n, 0.0) for n in GEMM_ENTRIES)
     return by_name, gemm_flops, gemm_ms
 
 
@@ -436,7 +447,7 @@ def run_fsdp(args):
             "e2e": {"value": tokens / (e2e_ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": batch * seq * 8 * world,
                     "d2h_bytes_per_step": 4 * world},
             "gpu_launches": launches, "clocks": clocks,
-            "roofline": {"bound": "tensor", "kernel": "gemm_tc_kernel (all q3_gemm + q3_gate_up_swiglu_fwd launches of a step, rank 0)",
+            "roofline": {"bound": "tensor", "kernel": "gemm_tc_kernel (all GEMM entry points of a step, rank 0: q3_gemm, q3_linear_*_grouped, q3_gate_up_swiglu_fwd)",
                          "achieved": achieved, "peak": peak_tf, "unit": "TFLOP/s", "frac": achieved / peak_tf,
                          "peak_kind": peak_kind + " bf16_tflops_sustained", "traffic": None, "gemm_ms_per_step": gemm_ms,
                          "all_kernels_ms_per_step": sum(by_name.values()),

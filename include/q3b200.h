@@ -136,6 +136,20 @@ int q3_norm_rope_bwd(const void* x, const void* weight, const void* cos_t, const
                      const float* inv_rms, void* dx, void* dweight, void* workspace, int64_t workspace_bytes,
                      int64_t tokens, int64_t heads, int64_t D, int dtype, q3_stream_t stream);
 
+/* q [tokens, hq, D] and k [tokens, hk, D] of one layer through per-head RMSNorm + RoPE in ONE launch (one grid shared
+ * out between the two tensors by size); same arithmetic as two q3_norm_rope_* calls, which is also the fallback where
+ * the wide-row kernels do not apply. workspace: q3_qk_norm_rope_bwd_workspace_bytes.
+ * Reference: ops/triton/fused_qk_norm_rope.py (`_FusedQKNormRoPEFunction`, one kernel for q and k) and the pair of
+ * `_norm_rope_forward` / `_norm_rope_backward` launches of qwen3_triton/kernels/norm_rope.py. */
+int q3_qk_norm_rope_fwd(const void* q, const void* k, const void* q_weight, const void* k_weight, const void* cos_t,
+                        const void* sin_t, void* yq, void* yk, float* inv_q, float* inv_k, int64_t tokens, int64_t hq,
+                        int64_t hk, int64_t D, double eps, int dtype, q3_stream_t stream);
+int64_t q3_qk_norm_rope_bwd_workspace_bytes(int64_t tokens, int64_t hq, int64_t hk, int64_t D);
+int q3_qk_norm_rope_bwd(const void* q, const void* k, const void* q_weight, const void* k_weight, const void* cos_t,
+                        const void* sin_t, const void* dyq, const void* dyk, const float* inv_q, const float* inv_k,
+                        void* dq, void* dk, void* dq_weight, void* dk_weight, void* workspace, int64_t workspace_bytes,
+                        int64_t tokens, int64_t hq, int64_t hk, int64_t D, int dtype, q3_stream_t stream);
+
 /* RoPE (backward != 0: its transpose). layout 0: x [batch, seq, heads, D]; layout 1: x [batch, heads, seq, D];
  * cos/sin [batch, seq, D]. Reference: qwen3_triton/kernels/rotary.py:20-34,47-66; ops/triton/rope.py:164-170;
  * ops/reference/rope.py:13-55. */
@@ -267,6 +281,27 @@ int q3_gate_up_path(const void* x, const void* w_gate, const void* w_up, const v
  * partial_dx in fp32 (qwen3_triton/training/vocab_parallel.py:76). */
 int q3_gemm_acc_f32(const void* a, int64_t a_sm, int64_t a_sk, const void* b, int64_t b_sk, int64_t b_sn, float* c,
                     int64_t M, int64_t N, int64_t K, int in_dtype, int* status, q3_stream_t stream);
+
+/* C += A * B with C contiguous [M,N] in out_dtype (fp32, or the input type: read, add in fp32, round once). Same
+ * operand rules as q3_gemm, tensor-core path only (Q3_ERR_ALIGN otherwise). Used to sum the input gradients of
+ * projections that share an input (q/k/v, gate/up) without add kernels; the reference does those sums with its
+ * `_add` kernel (qwen3_triton/kernels/residual.py:13-27) after separate `_gemm` launches. */
+int q3_gemm_acc(const void* a, int64_t a_sm, int64_t a_sk, const void* b, int64_t b_sk, int64_t b_sn, void* c,
+                int64_t M, int64_t N, int64_t K, int in_dtype, int out_dtype, int* status, q3_stream_t stream);
+
+/* Linear layers that share their input (q/k/v, gate/up), `count` = 2 or 3 weights W_i [N_i, K], row-major contiguous
+ * 16-bit tensors, one persistent launch each instead of `count` GEMMs (+ adds):
+ *   fwd   y_i [M, N_i] = x [M, K] * W_i^T
+ *   dgrad dx [M, K]    = sum_i dy_i [M, N_i] * W_i          (every N_i a multiple of 64)
+ *   wgrad dW_i [N_i,K] = dy_i^T * x
+ * `weights`, `ys`, `dys`, `dws` and `n` are HOST arrays of `count` device pointers / sizes, read at launch.
+ * Reference: the same `_gemm` launches of qwen3_triton/kernels/linear.py:45-77, one per projection, and `_add`. */
+int q3_linear_fwd_grouped(const void* x, const void* const* weights, void* const* ys, const int64_t* n, int count,
+                          int64_t M, int64_t K, int dtype, int* status, q3_stream_t stream);
+int q3_linear_dgrad_grouped(const void* const* dys, const void* const* weights, void* dx, const int64_t* n, int count,
+                            int64_t M, int64_t K, int dtype, int* status, q3_stream_t stream);
+int q3_linear_wgrad_grouped(const void* const* dys, const void* x, void* const* dws, const int64_t* n, int count,
+                            int64_t M, int64_t K, int dtype, int* status, q3_stream_t stream);
 
 /* ---- fused lm_head + cross-entropy (no logits in memory) ---------------------------------------------------
  * The reference materialises the logits [W*r, V/W] and their gradient (qwen3_triton/training/vocab_parallel.py:52,75;

@@ -47,6 +47,15 @@ struct GemmParams {
   int a_mn, b_mn;   // operand is MN-major
   int prefetch;     // issue L2 prefetches ahead of the smem ring
   int* status;
+  // grouped products that share one operand (seg_mode 0 = plain GEMM):
+  //   1: segments along N  - B_i and C_i differ, A shared            (q/k/v projections of one input)
+  //   2: segments along K  - A_i and B_i differ, one C               (sum of their input gradients)
+  //   3: segments along M  - A_i and C_i differ, B shared            (their weight gradients)
+  // seg_end[i] = cumulative count of N tiles / k-blocks / M tiles up to and including segment i.
+  int seg_mode;
+  int seg_end[3];
+  void* seg_c[3];
+  int64_t seg_dim[3];   // N_i (mode 1) or M_i (mode 3)
   // cross-entropy epilogues
   const int64_t* labels;   // effective label per row (ignore_index where the row is not scored)
   const float* lse;        // per row (EPI_CE_GRAD)
@@ -57,6 +66,17 @@ struct GemmParams {
   float* part_sum;
   float* target;           // [M], must be zero-filled by the caller
 };
+
+struct alignas(64) GemmMaps {
+  CUtensorMap a[3];
+  CUtensorMap b[3];   // gate/up: b[0] = W_gate, b[1] = W_up
+};
+
+__device__ __forceinline__ int seg_of(const GemmParams& p, int idx, int& start) {
+  const int seg = (idx >= p.seg_end[0]) + (idx >= p.seg_end[1]);
+  start = seg == 0 ? 0 : p.seg_end[seg - 1];
+  return seg;
+}
 
 template <int BN> struct Cfg {
   static constexpr int A_BYTES = BM * BK * 2;
@@ -116,7 +136,7 @@ __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, 
 // Epilogues:
 //   EPI_STORE    C = A*B (TO = bf16 / fp16 / fp32)
 //   EPI_GATE_UP  BN must be 256; B tile = [W_gate rows | W_up rows]; stores G, U and silu(G)*U
-//   EPI_ACC_F32  C (fp32) += A*B
+//   EPI_ACC_F32  C += A*B, C in fp32 or (read-add-round) in a 16-bit type
 //   EPI_CE_STATS A*B are logits that are never stored: per row and N-tile the (max, sum exp) of the logits rounded
 //                to TO, and the target logit where the tile owns the row's label
 //   EPI_CE_GRAD  stores dZ = (exp(z - lse[row]) - onehot) * upstream[source] / count[source] for the logits z
@@ -124,8 +144,7 @@ enum { EPI_STORE = 0, EPI_GATE_UP = 1, EPI_ACC_F32 = 2, EPI_CE_STATS = 3, EPI_CE
 
 template <int BN, typename TO, int EPI>
 __global__ void __launch_bounds__(kGemmThreads, 1)
-gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-               const __grid_constant__ CUtensorMap tmB2, const GemmParams p) {
+gemm_tc_kernel(const __grid_constant__ GemmMaps maps, const GemmParams p) {
   constexpr bool GATE_UP = (EPI == EPI_GATE_UP);
   using C = Cfg<BN>;
   extern __shared__ uint8_t smem_raw[];
@@ -152,9 +171,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     for (int a = 0; a < 2; ++a) { mbar_init(tfull_bar(a), 1); mbar_init(tempty_bar(a), 4); }
     mbar_init(done_bar, 1);
     fence_barrier_init();
-    prefetch_tmap(&tmA);
-    prefetch_tmap(&tmB);
-    if (GATE_UP) prefetch_tmap(&tmB2);
+    prefetch_tmap(&maps.a[0]);
+    prefetch_tmap(&maps.b[0]);
+    if (GATE_UP) prefetch_tmap(&maps.b[1]);
   }
   if (warp == 1) {
     tmem_alloc(smem_u32(tmem_slot), C::TMEM_COLS);
@@ -173,21 +192,35 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
         int mi, ni;
         tile_coords(tile, p.tiles_m, p.tiles_n, mi, ni);
-        const int m0 = mi * BM, n0 = ni * (GATE_UP ? BN / 2 : BN);
+        int m0 = mi * BM, n0 = ni * (GATE_UP ? BN / 2 : BN);
+        const CUtensorMap* tmA = &maps.a[0];
+        const CUtensorMap* tmB = &maps.b[0];
+        const CUtensorMap* tmB2 = &maps.b[1];
+        if (p.seg_mode == 1) {
+          int start;
+          const int seg = seg_of(p, ni, start);
+          tmB = &maps.b[seg];
+          n0 = (ni - start) * BN;
+        } else if (p.seg_mode == 3) {
+          int start;
+          const int seg = seg_of(p, mi, start);
+          tmA = &maps.a[seg];
+          m0 = (mi - start) * BM;
+        }
         // Operands that stream from HBM (weights of the vocabulary head, token-major operands of the weight
         // gradient) see a longer latency than the smem ring covers: pull boxes into L2 kPrefetch k-blocks ahead.
         auto prefetch = [&](int kb) {
           const int k0 = kb * BK;
-          if (!p.a_mn) tma_prefetch_2d(&tmA, k0, m0);
+          if (!p.a_mn) tma_prefetch_2d(tmA, k0, m0);
           else {
 #pragma unroll
-            for (int j = 0; j < BM / 64; ++j) tma_prefetch_2d(&tmA, m0 + 64 * j, k0);
+            for (int j = 0; j < BM / 64; ++j) tma_prefetch_2d(tmA, m0 + 64 * j, k0);
           }
-          if (GATE_UP) { tma_prefetch_2d(&tmB, k0, n0); tma_prefetch_2d(&tmB2, k0, n0); }
-          else if (!p.b_mn) tma_prefetch_2d(&tmB, k0, n0);
+          if (GATE_UP) { tma_prefetch_2d(tmB, k0, n0); tma_prefetch_2d(tmB2, k0, n0); }
+          else if (!p.b_mn) tma_prefetch_2d(tmB, k0, n0);
           else {
 #pragma unroll
-            for (int j = 0; j < BN / 64; ++j) tma_prefetch_2d(&tmB, n0 + 64 * j, k0);
+            for (int j = 0; j < BN / 64; ++j) tma_prefetch_2d(tmB, n0 + 64 * j, k0);
           }
         };
         constexpr int kPrefetch = C::STAGES + 6;
@@ -201,21 +234,28 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           if (!mbar_wait(empty_bar(s), ph ^ 1u, abort_flag)) { ok = false; break; }
           const uint32_t a_dst = smem_base + s * C::STAGE_BYTES, b_dst = a_dst + C::A_BYTES;
           mbar_expect_tx(full_bar(s), C::STAGE_BYTES);
-          const int k0 = kb * BK;
+          int k0 = kb * BK;
+          if (p.seg_mode == 2) {   // this k-block belongs to one (A_i, B_i) pair
+            int start;
+            const int seg = seg_of(p, kb, start);
+            tmA = &maps.a[seg];
+            tmB = &maps.b[seg];
+            k0 = (kb - start) * BK;
+          }
           if (!p.a_mn) {
-            tma_load_2d(a_dst, &tmA, k0, m0, full_bar(s));
+            tma_load_2d(a_dst, tmA, k0, m0, full_bar(s));
           } else {
 #pragma unroll
-            for (int j = 0; j < BM / 64; ++j) tma_load_2d(a_dst + j * (BK * 128), &tmA, m0 + 64 * j, k0, full_bar(s));
+            for (int j = 0; j < BM / 64; ++j) tma_load_2d(a_dst + j * (BK * 128), tmA, m0 + 64 * j, k0, full_bar(s));
           }
           if (GATE_UP) {
-            tma_load_2d(b_dst, &tmB, k0, n0, full_bar(s));
-            tma_load_2d(b_dst + (BN / 2) * 128, &tmB2, k0, n0, full_bar(s));
+            tma_load_2d(b_dst, tmB, k0, n0, full_bar(s));
+            tma_load_2d(b_dst + (BN / 2) * 128, tmB2, k0, n0, full_bar(s));
           } else if (!p.b_mn) {
-            tma_load_2d(b_dst, &tmB, k0, n0, full_bar(s));
+            tma_load_2d(b_dst, tmB, k0, n0, full_bar(s));
           } else {
 #pragma unroll
-            for (int j = 0; j < BN / 64; ++j) tma_load_2d(b_dst + j * (BK * 128), &tmB, n0 + 64 * j, k0, full_bar(s));
+            for (int j = 0; j < BN / 64; ++j) tma_load_2d(b_dst + j * (BK * 128), tmB, n0 + 64 * j, k0, full_bar(s));
           }
         }
       }
@@ -276,6 +316,31 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       const int64_t row = (int64_t)mi * BM + q * 32 + lane;
       const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN;
       if constexpr (EPI == EPI_STORE) {
+        int64_t n0 = (int64_t)ni * BN, ncols = p.N, mrows = p.M, crow_idx = row;
+        TO* cbase = reinterpret_cast<TO*>(p.c0);
+        if (p.seg_mode == 1) {
+          int start;
+          const int seg = seg_of(p, ni, start);
+          cbase = reinterpret_cast<TO*>(p.seg_c[seg]);
+          ncols = p.seg_dim[seg];
+          n0 = (int64_t)(ni - start) * BN;
+        } else if (p.seg_mode == 3) {
+          int start;
+          const int seg = seg_of(p, mi, start);
+          cbase = reinterpret_cast<TO*>(p.seg_c[seg]);
+          mrows = p.seg_dim[seg];
+          crow_idx = (int64_t)(mi - start) * BM + q * 32 + lane;
+        }
+        TO* crow = cbase + crow_idx * ncols + n0;
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld32(t_row + c * 32, r);
+          tmem_ld_wait();
+          if (crow_idx < mrows && n0 + c * 32 < ncols) store_chunk32<TO>(crow + c * 32, r, n0 + c * 32, ncols);
+        }
+      } else if constexpr (EPI == EPI_ACC_F32) {
+        // C += A*B with C in TO (fp32, or a 16-bit type: read, add in fp32, round once)
         const int64_t n0 = (int64_t)ni * BN;
         TO* crow = reinterpret_cast<TO*>(p.c0) + row * p.N + n0;
 #pragma unroll 1
@@ -283,26 +348,18 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           uint32_t r[32];
           tmem_ld32(t_row + c * 32, r);
           tmem_ld_wait();
-          if (row < p.M && n0 + c * 32 < p.N) store_chunk32<TO>(crow + c * 32, r, n0 + c * 32, p.N);
-        }
-      } else if constexpr (EPI == EPI_ACC_F32) {
-        const int64_t n0 = (int64_t)ni * BN;
-        float* crow = reinterpret_cast<float*>(p.c0) + row * p.N + n0;
-#pragma unroll 1
-        for (int c = 0; c < BN / 32; ++c) {
-          uint32_t r[32];
-          tmem_ld32(t_row + c * 32, r);
-          tmem_ld_wait();
-          if (row < p.M) {
+          if (row < p.M && n0 + c * 32 < p.N) {
+            constexpr int W = 16 / (int)sizeof(TO);   // elements per 16-byte access
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-              if (n0 + c * 32 + 4 * j + 4 <= p.N) {
-                float4 o = *reinterpret_cast<const float4*>(crow + c * 32 + 4 * j);
-                o.x += __uint_as_float(r[4 * j]); o.y += __uint_as_float(r[4 * j + 1]);
-                o.z += __uint_as_float(r[4 * j + 2]); o.w += __uint_as_float(r[4 * j + 3]);
-                *reinterpret_cast<float4*>(crow + c * 32 + 4 * j) = o;
+            for (int j = 0; j < 32 / W; ++j) {
+              if (n0 + c * 32 + W * j + W <= p.N) {
+                float old[W];
+                VecIO<TO, W>::load(crow + c * 32 + W * j, old);
+#pragma unroll
+                for (int e = 0; e < W; ++e) r[W * j + e] = __float_as_uint(__uint_as_float(r[W * j + e]) + old[e]);
               }
             }
+            store_chunk32<TO>(crow + c * 32, r, n0 + c * 32, p.N);
           }
         }
       } else if constexpr (EPI == EPI_CE_STATS) {
@@ -421,19 +478,21 @@ template <int BN, typename TO, int EPI>
 int launch_gemm(const Operand& A, const Operand& B, const void* b2, GemmParams& p, bool bf16, cudaStream_t st) {
   constexpr bool GATE_UP = (EPI == EPI_GATE_UP);
   using C = Cfg<BN>;
-  CUtensorMap tmA, tmB, tmB2;
+  GemmMaps maps;
   int rc;
-  if (!A.mn_major) rc = make_tmap_2d(&tmA, A.ptr, bf16, p.M, p.K, A.ld, BK, BM);
-  else rc = make_tmap_2d(&tmA, A.ptr, bf16, p.K, p.M, A.ld, 64, BK);
+  if (!A.mn_major) rc = make_tmap_2d(&maps.a[0], A.ptr, bf16, p.M, p.K, A.ld, BK, BM);
+  else rc = make_tmap_2d(&maps.a[0], A.ptr, bf16, p.K, p.M, A.ld, 64, BK);
   if (rc != Q3_OK) return rc;
-  if (!B.mn_major) rc = make_tmap_2d(&tmB, B.ptr, bf16, p.N, p.K, B.ld, BK, GATE_UP ? BN / 2 : BN);
-  else rc = make_tmap_2d(&tmB, B.ptr, bf16, p.K, p.N, B.ld, 64, BK);
+  if (!B.mn_major) rc = make_tmap_2d(&maps.b[0], B.ptr, bf16, p.N, p.K, B.ld, BK, GATE_UP ? BN / 2 : BN);
+  else rc = make_tmap_2d(&maps.b[0], B.ptr, bf16, p.K, p.N, B.ld, 64, BK);
   if (rc != Q3_OK) return rc;
-  tmB2 = tmB;
+  maps.a[1] = maps.a[2] = maps.a[0];
+  maps.b[1] = maps.b[2] = maps.b[0];
   if (GATE_UP) {
-    rc = make_tmap_2d(&tmB2, b2, bf16, p.N, p.K, B.ld, BK, BN / 2);
+    rc = make_tmap_2d(&maps.b[1], b2, bf16, p.N, p.K, B.ld, BK, BN / 2);
     if (rc != Q3_OK) return rc;
   }
+  p.seg_mode = 0;
   const int n_per_tile = GATE_UP ? BN / 2 : BN;
   p.tiles_m = (int)cdiv(p.M, BM);
   p.tiles_n = (int)cdiv(p.N, n_per_tile);
@@ -454,7 +513,69 @@ int launch_gemm(const Operand& A, const Operand& B, const void* b2, GemmParams& 
     if (e != cudaSuccess) return Q3_ERR_CUDA - (int)e;
     configured = true;
   }
-  kern<<<grid, kGemmThreads, C::SMEM_BYTES, st>>>(tmA, tmB, tmB2, p);
+  kern<<<grid, kGemmThreads, C::SMEM_BYTES, st>>>(maps, p);
+  return launch_status();
+}
+
+// Up to three products that share an operand in one persistent launch (BN = 256, plain store epilogue):
+//   mode 1: C_i[M,N_i] = A[M,K] * B_i[N_i,K]^T          tiles along N walk the segments
+//   mode 2: C[M,N]     = sum_i A_i[M,K_i] * B_i[K_i,N]    k-blocks walk the segments (K_i % 64 == 0)
+//   mode 3: C_i[M_i,N] = A_i[T,M_i]^T * B[T,N]            tiles along M walk the segments
+// All matrices row-major and contiguous. One launch fills the SMs where the small members of a group (the k / v
+// projections: 64 tiles on 148 SMs) would leave most of them idle.
+template <typename TO>
+int launch_grouped(int mode, int count, const void* const* a, const void* const* b, void* const* c, const int64_t* sizes,
+                   int64_t M, int64_t N, int64_t K, bool bf16, int* status, cudaStream_t st) {
+  constexpr int BN = 256;
+  using C = Cfg<BN>;
+  GemmMaps maps;
+  GemmParams p{};
+  p.status = status;
+  p.seg_mode = mode;
+  int rc = Q3_OK;
+  int64_t total = 0;
+  for (int i = 0; i < 3; ++i) {
+    const int j = i < count ? i : count - 1;    // unused slots repeat the last segment
+    const int64_t sz = sizes[j];
+    if (mode == 1) {
+      if (i == 0) rc = make_tmap_2d(&maps.a[0], a[0], bf16, M, K, K, BK, BM);
+      if (rc == Q3_OK) rc = make_tmap_2d(&maps.b[i], b[j], bf16, sz, K, K, BK, BN);
+      if (i > 0) maps.a[i] = maps.a[0];
+      if (i < count) total += cdiv(sz, BN);
+    } else if (mode == 2) {
+      rc = make_tmap_2d(&maps.a[i], a[j], bf16, M, sz, sz, BK, BM);
+      if (rc == Q3_OK) rc = make_tmap_2d(&maps.b[i], b[j], bf16, sz, N, N, 64, BK);
+      if (i < count) total += sz / BK;
+    } else {
+      rc = make_tmap_2d(&maps.a[i], a[j], bf16, K, sz, sz, 64, BK);
+      if (i == 0 && rc == Q3_OK) rc = make_tmap_2d(&maps.b[0], b[0], bf16, K, N, N, 64, BK);
+      if (i > 0) maps.b[i] = maps.b[0];
+      if (i < count) total += cdiv(sz, BM);
+    }
+    if (rc != Q3_OK) return rc;
+    p.seg_end[i] = (int)total;
+    p.seg_c[i] = c[mode == 2 ? 0 : j];
+    p.seg_dim[i] = sz;
+  }
+  p.c0 = c[0];
+  p.M = M; p.N = N; p.K = K;
+  p.tiles_m = mode == 3 ? (int)total : (int)cdiv(M, BM);
+  p.tiles_n = mode == 1 ? (int)total : (int)cdiv(N, BN);
+  p.kblocks = mode == 2 ? (int)total : (int)cdiv(K, BK);
+  p.a_mn = mode == 3;
+  p.b_mn = mode != 1;
+  p.idesc = make_idesc_f16(BM, BN, bf16, p.a_mn != 0, p.b_mn != 0);
+  p.prefetch = 0;
+  const int64_t tiles = (int64_t)p.tiles_m * p.tiles_n;
+  const int grid = (int)(tiles < sm_count() ? tiles : sm_count());
+  auto kern = gemm_tc_kernel<BN, TO, EPI_STORE>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
+    if (e != cudaSuccess) return Q3_ERR_CUDA - (int)e;
+    configured = true;
+  }
+  kern<<<grid, kGemmThreads, C::SMEM_BYTES, st>>>(maps, p);
   return launch_status();
 }
 
@@ -554,6 +675,88 @@ extern "C" int q3_gemm_acc_f32(const void* a, int64_t a_sm, int64_t a_sk, const 
   tc::GemmParams p{};
   p.c0 = c; p.M = M; p.N = N; p.K = K; p.status = status;
   return tc::launch_gemm<256, float, tc::EPI_ACC_F32>(A, B, nullptr, p, in_dtype == Q3_BF16, (cudaStream_t)stream);
+}
+
+// C (contiguous [M,N], out_dtype = fp32 or the input type) += A * B: the sum of several products (the input gradient
+// of projections that share an input) without separate add kernels. Tensor-core path only.
+extern "C" int q3_gemm_acc(const void* a, int64_t a_sm, int64_t a_sk, const void* b, int64_t b_sk, int64_t b_sn, void* c,
+                           int64_t M, int64_t N, int64_t K, int in_dtype, int out_dtype, int* status,
+                           q3_stream_t stream) {
+  if (!a || !b || !c) return Q3_ERR_ARG;
+  if (!q3_gemm_path(a, a_sm, a_sk, b, b_sk, b_sn, c, M, N, K, in_dtype, out_dtype)) return Q3_ERR_ALIGN;
+  tc::Operand A, B;
+  tc::classify(a, a_sm, a_sk, M, K, &A);
+  tc::classify(b, b_sn, b_sk, N, K, &B);
+  tc::GemmParams p{};
+  p.c0 = c; p.M = M; p.N = N; p.K = K; p.status = status;
+  const bool bf16 = in_dtype == Q3_BF16;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (out_dtype == Q3_F32) return tc::launch_gemm<256, float, tc::EPI_ACC_F32>(A, B, nullptr, p, bf16, st);
+  if (bf16) return tc::launch_gemm<256, __nv_bfloat16, tc::EPI_ACC_F32>(A, B, nullptr, p, bf16, st);
+  return tc::launch_gemm<256, __half, tc::EPI_ACC_F32>(A, B, nullptr, p, bf16, st);
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// Grouped linear layers that share their input (q/k/v, or gate/up): `count` = 2 or 3 weight matrices W_i [N_i, K].
+static int grouped_check(int count, const int64_t* n, int64_t M, int64_t K, int dtype) {
+  if (count < 2 || count > 3 || !n) return Q3_ERR_ARG;
+  if (dtype != Q3_BF16 && dtype != Q3_F16) return Q3_ERR_DTYPE;
+  if (M < 1 || K < 1 || (K % 8)) return Q3_ERR_SHAPE;
+  for (int i = 0; i < count; ++i)
+    if (n[i] < 1 || (n[i] % 8)) return Q3_ERR_SHAPE;
+  return Q3_OK;
+}
+static bool all_aligned(const void* const* ptrs, int count) {
+  for (int i = 0; i < count; ++i)
+    if (!ptrs[i] || !aligned16(ptrs[i])) return false;
+  return true;
+}
+
+// y_i [M, N_i] = x [M, K] * W_i^T, one launch.
+extern "C" int q3_linear_fwd_grouped(const void* x, const void* const* weights, void* const* ys, const int64_t* n,
+                                     int count, int64_t M, int64_t K, int dtype, int* status, q3_stream_t stream) {
+  if (!x || !weights || !ys) return Q3_ERR_ARG;
+  int rc = grouped_check(count, n, M, K, dtype);
+  if (rc != Q3_OK) return rc;
+  if (!aligned16(x) || !all_aligned(weights, count) || !all_aligned((const void* const*)ys, count)) return Q3_ERR_ALIGN;
+  const void* a[1] = {x};
+  int64_t total = 0;
+  for (int i = 0; i < count; ++i) total += n[i];
+  cudaStream_t st = (cudaStream_t)stream;
+  if (dtype == Q3_BF16) return tc::launch_grouped<__nv_bfloat16>(1, count, a, weights, ys, n, M, total, K, true, status, st);
+  return tc::launch_grouped<__half>(1, count, a, weights, ys, n, M, total, K, false, status, st);
+}
+
+// dx [M, K] = sum_i dy_i [M, N_i] * W_i [N_i, K], one launch (every N_i a multiple of 64).
+extern "C" int q3_linear_dgrad_grouped(const void* const* dys, const void* const* weights, void* dx, const int64_t* n,
+                                       int count, int64_t M, int64_t K, int dtype, int* status, q3_stream_t stream) {
+  if (!dys || !weights || !dx) return Q3_ERR_ARG;
+  int rc = grouped_check(count, n, M, K, dtype);
+  if (rc != Q3_OK) return rc;
+  for (int i = 0; i < count; ++i)
+    if (n[i] % 64) return Q3_ERR_SHAPE;
+  if (!aligned16(dx) || !all_aligned(dys, count) || !all_aligned(weights, count)) return Q3_ERR_ALIGN;
+  void* c[1] = {dx};
+  int64_t total = 0;
+  for (int i = 0; i < count; ++i) total += n[i];
+  cudaStream_t st = (cudaStream_t)stream;
+  if (dtype == Q3_BF16) return tc::launch_grouped<__nv_bfloat16>(2, count, dys, weights, c, n, M, K, total, true, status, st);
+  return tc::launch_grouped<__half>(2, count, dys, weights, c, n, M, K, total, false, status, st);
+}
+
+// dW_i [N_i, K] = dy_i [M, N_i]^T * x [M, K], one launch.
+extern "C" int q3_linear_wgrad_grouped(const void* const* dys, const void* x, void* const* dws, const int64_t* n,
+                                       int count, int64_t M, int64_t K, int dtype, int* status, q3_stream_t stream) {
+  if (!dys || !x || !dws) return Q3_ERR_ARG;
+  int rc = grouped_check(count, n, M, K, dtype);
+  if (rc != Q3_OK) return rc;
+  if (!aligned16(x) || !all_aligned(dys, count) || !all_aligned((const void* const*)dws, count)) return Q3_ERR_ALIGN;
+  const void* b[1] = {x};
+  int64_t total = 0;
+  for (int i = 0; i < count; ++i) total += n[i];
+  cudaStream_t st = (cudaStream_t)stream;
+  if (dtype == Q3_BF16) return tc::launch_grouped<__nv_bfloat16>(3, count, dys, b, dws, n, total, K, M, true, status, st);
+  return tc::launch_grouped<__half>(3, count, dys, b, dws, n, total, K, M, false, status, st);
 }
 
 extern "C" int64_t q3_linear_ce_tiles(int64_t V_local) { return q3::cdiv(V_local, 256); }

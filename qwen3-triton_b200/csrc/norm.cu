@@ -31,6 +31,15 @@ int norm_rope_fwd_ring(const void* x, const void* w, const void* cs, const void*
                        int64_t tokens, int64_t heads, int64_t D, float eps, int dtype, cudaStream_t st);
 int norm_rope_bwd_ring(const void* x, const void* w, const void* cs, const void* sn, const void* dy, const float* inv,
                        void* dx, float* partial, int64_t tokens, int64_t heads, int64_t D, int dtype, cudaStream_t st);
+void qk_norm_rope_bwd_ring_parts(int64_t tokens, int64_t hq, int64_t hk, int64_t D, int dtype, int* parts_q,
+                                 int* parts_k);
+int qk_norm_rope_fwd_ring(const void* q, const void* wq, void* yq, float* invq, int64_t hq, const void* k,
+                          const void* wk, void* yk, float* invk, int64_t hk, const void* cs, const void* sn,
+                          int64_t tokens, int64_t D, float eps, int dtype, cudaStream_t st);
+int qk_norm_rope_bwd_ring(const void* q, const void* wq, const void* dyq, void* dq, const float* invq, float* pq,
+                          int64_t hq, const void* k, const void* wk, const void* dyk, void* dk, const float* invk,
+                          float* pk, int64_t hk, const void* cs, const void* sn, int64_t tokens, int64_t D, int dtype,
+                          cudaStream_t st);
 template <typename T> struct DtypeOf;
 template <> struct DtypeOf<float> { static constexpr int value = Q3_F32; };
 template <> struct DtypeOf<__nv_bfloat16> { static constexpr int value = Q3_BF16; };
@@ -643,6 +652,65 @@ extern "C" int q3_norm_rope_bwd(const void* x, const void* weight, const void* c
                                                                     (float*)workspace, workspace_bytes, 1, tokens,
                                                                     heads, D, 0, (cudaStream_t)stream)));
   return Q3_OK;
+}
+
+// q [tokens, hq, D] and k [tokens, hk, D] of one layer in one launch (token-major only). Falls back to two launches
+// of the single-tensor form where the wide-row kernels do not apply.
+extern "C" int q3_qk_norm_rope_fwd(const void* q, const void* k, const void* q_weight, const void* k_weight,
+                                   const void* cos_t, const void* sin_t, void* yq, void* yk, float* inv_q, float* inv_k,
+                                   int64_t tokens, int64_t hq, int64_t hk, int64_t D, double eps, int dtype,
+                                   q3_stream_t stream) {
+  if (!q || !k || !q_weight || !k_weight || !cos_t || !sin_t || !yq || !yk || !inv_q || !inv_k) return Q3_ERR_ARG;
+  if (tokens < 1 || hq < 1 || hk < 1 || D < 2 || (D & 1) || !(eps > 0)) return Q3_ERR_SHAPE;
+  const bool al = aligned16(q) && aligned16(k) && aligned16(q_weight) && aligned16(k_weight) && aligned16(cos_t) &&
+                  aligned16(sin_t) && aligned16(yq) && aligned16(yk);
+  if (al && norm_rope_ring_applies(hq, D, dtype) && norm_rope_ring_applies(hk, D, dtype))
+    return qk_norm_rope_fwd_ring(q, q_weight, yq, inv_q, hq, k, k_weight, yk, inv_k, hk, cos_t, sin_t, tokens, D,
+                                 (float)eps, dtype, (cudaStream_t)stream);
+  int rc = q3_norm_rope_fwd(q, q_weight, cos_t, sin_t, yq, inv_q, tokens, hq, D, eps, dtype, stream);
+  if (rc != Q3_OK) return rc;
+  return q3_norm_rope_fwd(k, k_weight, cos_t, sin_t, yk, inv_k, tokens, hk, D, eps, dtype, stream);
+}
+
+extern "C" int64_t q3_qk_norm_rope_bwd_workspace_bytes(int64_t tokens, int64_t hq, int64_t hk, int64_t D) {
+  return q3_norm_rope_bwd_workspace_bytes(tokens, hq, D) + q3_norm_rope_bwd_workspace_bytes(tokens, hk, D);
+}
+
+extern "C" int q3_qk_norm_rope_bwd(const void* q, const void* k, const void* q_weight, const void* k_weight,
+                                   const void* cos_t, const void* sin_t, const void* dyq, const void* dyk,
+                                   const float* inv_q, const float* inv_k, void* dq, void* dk, void* dq_weight,
+                                   void* dk_weight, void* workspace, int64_t workspace_bytes, int64_t tokens,
+                                   int64_t hq, int64_t hk, int64_t D, int dtype, q3_stream_t stream) {
+  if (!q || !k || !q_weight || !k_weight || !cos_t || !sin_t || !dyq || !dyk || !inv_q || !inv_k || !dq || !dk ||
+      !dq_weight || !dk_weight)
+    return Q3_ERR_ARG;
+  if (tokens < 1 || hq < 1 || hk < 1 || D < 2 || (D & 1)) return Q3_ERR_SHAPE;
+  const int64_t wq_bytes = q3_norm_rope_bwd_workspace_bytes(tokens, hq, D);
+  if (!workspace || workspace_bytes < q3_qk_norm_rope_bwd_workspace_bytes(tokens, hq, hk, D)) return Q3_ERR_WORKSPACE;
+  float* pq = static_cast<float*>(workspace);
+  float* pk = reinterpret_cast<float*>(static_cast<char*>(workspace) + wq_bytes);
+  cudaStream_t st = (cudaStream_t)stream;
+  const bool al = aligned16(q) && aligned16(k) && aligned16(q_weight) && aligned16(k_weight) && aligned16(cos_t) &&
+                  aligned16(sin_t) && aligned16(dyq) && aligned16(dyk) && aligned16(dq) && aligned16(dk);
+  if (al && norm_rope_ring_applies(hq, D, dtype) && norm_rope_ring_applies(hk, D, dtype)) {
+    int cq = 0, ck = 0;
+    qk_norm_rope_bwd_ring_parts(tokens, hq, hk, D, dtype, &cq, &ck);
+    int rc = qk_norm_rope_bwd_ring(q, q_weight, dyq, dq, inv_q, pq, hq, k, k_weight, dyk, dk, inv_k, pk, hk, cos_t,
+                                   sin_t, tokens, D, dtype, st);
+    if (rc != Q3_OK) return rc;
+    if (dtype == Q3_BF16) {
+      reduce_partials_kernel<__nv_bfloat16><<<(int)cdiv(D, 32), dim3(32, 8), 0, st>>>(pq, (__nv_bfloat16*)dq_weight, cq, (int)D);
+      reduce_partials_kernel<__nv_bfloat16><<<(int)cdiv(D, 32), dim3(32, 8), 0, st>>>(pk, (__nv_bfloat16*)dk_weight, ck, (int)D);
+    } else {
+      reduce_partials_kernel<__half><<<(int)cdiv(D, 32), dim3(32, 8), 0, st>>>(pq, (__half*)dq_weight, cq, (int)D);
+      reduce_partials_kernel<__half><<<(int)cdiv(D, 32), dim3(32, 8), 0, st>>>(pk, (__half*)dk_weight, ck, (int)D);
+    }
+    return launch_status();
+  }
+  int rc = q3_norm_rope_bwd(q, q_weight, cos_t, sin_t, dyq, inv_q, dq, dq_weight, pq, wq_bytes, tokens, hq, D, dtype, stream);
+  if (rc != Q3_OK) return rc;
+  return q3_norm_rope_bwd(k, k_weight, cos_t, sin_t, dyk, inv_k, dk, dk_weight, pk, workspace_bytes - wq_bytes, tokens,
+                          hk, D, dtype, stream);
 }
 
 extern "C" int q3_rope_apply(const void* x, const void* cos_t, const void* sin_t, void* y, int64_t batch, int64_t seq,

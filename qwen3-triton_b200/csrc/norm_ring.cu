@@ -284,11 +284,12 @@ struct RopeGeom {
 
 template <typename T, bool BWD>
 __device__ __forceinline__ void rope_produce(const Ring& rg, const RopeGeom& g, const T* x, const T* dy, const T* cs,
-                                             const T* sn, int64_t tokens, int stages, size_t slot_bytes) {
+                                             const T* sn, int64_t tokens, int stages, size_t slot_bytes, int cta,
+                                             int ncta) {
   uint32_t k = 0;
   const int64_t groups = (tokens + g.tps - 1) / g.tps;
   const uint32_t x_slot = g.x_bytes * g.tps, t_slot = g.t_bytes * g.tps;
-  for (int64_t tg = blockIdx.x; tg < groups; tg += gridDim.x, ++k) {
+  for (int64_t tg = cta; tg < groups; tg += ncta, ++k) {
     const int s = k % stages;
     if (!mbar_wait(rg.empty(s), ((k / stages) & 1u) ^ 1u, rg.abort_flag)) break;
     const int64_t tok0 = tg * g.tps;
@@ -310,17 +311,38 @@ __device__ __forceinline__ void rope_produce(const Ring& rg, const RopeGeom& g, 
   for (uint32_t j = k - pending; j < k; ++j) mbar_wait_drain(rg.full(j % stages), (j / stages) & 1u);
 }
 
+// One tensor's share of a launch: q and k of a layer go through one grid, CTAs [0, ncta) of the first job and
+// [ncta_a, ncta_a + ncta_b) of the second (ncta = 0: no second tensor).
+template <typename T> struct RopeJob {
+  const T* x;        // [tokens, heads, D]
+  const T* w;        // [D]
+  const T* dy;       // backward only
+  T* y;              // forward: output; backward: dx
+  float* inv;        // [tokens * heads]; forward writes, backward reads
+  float* partial;    // backward: [ncta][D]
+  int heads, stages, ncta;
+  RopeGeom g;
+};
+
 template <typename T>
 __global__ void __launch_bounds__(kThreads, 2)
-norm_rope_fwd_ring_kernel(const T* __restrict__ x, const T* __restrict__ w, const T* __restrict__ cs,
-                          const T* __restrict__ sn, T* __restrict__ y, float* __restrict__ inv, int64_t tokens,
-                          int heads, int D, float eps, RopeGeom g, int stages, int* status) {
+norm_rope_fwd_ring_kernel(const RopeJob<T> ja, const RopeJob<T> jb, const T* __restrict__ cs, const T* __restrict__ sn,
+                          int64_t tokens, int D, float eps, int* status) {
   extern __shared__ __align__(128) uint8_t smem[];
+  const bool second = (int)blockIdx.x >= ja.ncta;
+  const RopeJob<T>& job = second ? jb : ja;
+  const int cta = second ? (int)blockIdx.x - ja.ncta : (int)blockIdx.x, ncta = job.ncta;
+  const RopeGeom g = job.g;
+  const int heads = job.heads, stages = job.stages;
+  const T* __restrict__ x = job.x;
+  const T* __restrict__ w = job.w;
+  T* __restrict__ y = job.y;
+  float* __restrict__ inv = job.inv;
   const size_t slot_bytes = (size_t)g.tps * (g.x_bytes + 2 * g.t_bytes);
   const Ring rg = ring_setup(smem, stages, slot_bytes);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (warp == kConsumers / 32) {
-    if (lane == 0) rope_produce<T, false>(rg, g, x, nullptr, cs, sn, tokens, stages, slot_bytes);
+    if (lane == 0) rope_produce<T, false>(rg, g, x, nullptr, cs, sn, tokens, stages, slot_bytes, cta, ncta);
   } else {
     const int half = D / 2, grp = threadIdx.x / g.tpr, p = threadIdx.x % g.tpr;
     const int ltok = grp / heads, head = grp - ltok * heads;     // this lane's row inside a slot
@@ -329,7 +351,7 @@ norm_rope_fwd_ring_kernel(const T* __restrict__ x, const T* __restrict__ w, cons
     VecIO<T, 8>::load(w + half + p * 8, w2);
     const int64_t groups = (tokens + g.tps - 1) / g.tps;
     uint32_t k = 0;
-    for (int64_t tg = blockIdx.x; tg < groups; tg += gridDim.x, ++k) {
+    for (int64_t tg = cta; tg < groups; tg += ncta, ++k) {
       const int s = k % stages;
       bool ok = mbar_wait(rg.full(s), (k / stages) & 1u, rg.abort_flag);
       ok = __all_sync(0xffffffffu, ok);
@@ -382,17 +404,26 @@ norm_rope_fwd_ring_kernel(const T* __restrict__ x, const T* __restrict__ w, cons
 // partial[cta][c] = sum over the CTA's rows of dn[c] * x[c] * inv, combined over the CTA's groups in a fixed order.
 template <typename T>
 __global__ void __launch_bounds__(kThreads, 2)
-norm_rope_bwd_ring_kernel(const T* __restrict__ x, const T* __restrict__ w, const T* __restrict__ cs,
-                          const T* __restrict__ sn, const T* __restrict__ dy, const float* __restrict__ inv,
-                          T* __restrict__ dx, float* __restrict__ partial, int64_t tokens, int heads, int D,
-                          RopeGeom g, int stages, int* status) {
+norm_rope_bwd_ring_kernel(const RopeJob<T> ja, const RopeJob<T> jb, const T* __restrict__ cs, const T* __restrict__ sn,
+                          int64_t tokens, int D, int* status) {
   extern __shared__ __align__(128) uint8_t smem[];
+  const bool second = (int)blockIdx.x >= ja.ncta;
+  const RopeJob<T>& job = second ? jb : ja;
+  const int cta = second ? (int)blockIdx.x - ja.ncta : (int)blockIdx.x, ncta = job.ncta;
+  const RopeGeom g = job.g;
+  const int heads = job.heads, stages = job.stages;
+  const T* __restrict__ x = job.x;
+  const T* __restrict__ w = job.w;
+  const T* __restrict__ dy = job.dy;
+  T* __restrict__ dx = job.y;
+  const float* __restrict__ inv = job.inv;
+  float* __restrict__ partial = job.partial;
   const size_t slot_bytes = (size_t)g.tps * (2 * g.x_bytes + 2 * g.t_bytes);
   const Ring rg = ring_setup(smem, stages, slot_bytes);
   float* comb = reinterpret_cast<float*>(smem + ring_smem_bytes(stages, slot_bytes));   // [groups][D], 16-byte aligned
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (warp == kConsumers / 32) {
-    if (lane == 0) rope_produce<T, true>(rg, g, x, dy, cs, sn, tokens, stages, slot_bytes);
+    if (lane == 0) rope_produce<T, true>(rg, g, x, dy, cs, sn, tokens, stages, slot_bytes, cta, ncta);
   } else {
     const int half = D / 2, grp = threadIdx.x / g.tpr, p = threadIdx.x % g.tpr;
     const int ltok = grp / heads, head = grp - ltok * heads;
@@ -407,10 +438,10 @@ norm_rope_bwd_ring_kernel(const T* __restrict__ x, const T* __restrict__ w, cons
       const int64_t token = tg * g.tps + ltok;
       return (tg < groups && token < tokens) ? inv[(size_t)token * heads + head] : 0.f;
     };
-    float r_next = inv_of(blockIdx.x);
-    for (int64_t tg = blockIdx.x; tg < groups; tg += gridDim.x, ++k) {
+    float r_next = inv_of(cta);
+    for (int64_t tg = cta; tg < groups; tg += ncta, ++k) {
       const float r = r_next;
-      r_next = inv_of(tg + gridDim.x);
+      r_next = inv_of(tg + ncta);
       const int s = k % stages;
       bool ok = mbar_wait(rg.full(s), (k / stages) & 1u, rg.abort_flag);
       ok = __all_sync(0xffffffffu, ok);
@@ -478,7 +509,7 @@ norm_rope_bwd_ring_kernel(const T* __restrict__ x, const T* __restrict__ w, cons
   for (int c = threadIdx.x; c < D; c += blockDim.x) {
     float tsum = 0.f;
     for (int r2 = 0; r2 < ngroups; ++r2) tsum += comb[(size_t)r2 * D + c];
-    partial[(size_t)blockIdx.x * D + c] = tsum;
+    partial[(size_t)cta * D + c] = tsum;
   }
   if (threadIdx.x == 0 && *rg.abort_flag) flag_status(status, Q3_STATUS_WAIT_TIMEOUT);
 }
@@ -586,61 +617,115 @@ static ring::RopeGeom rope_geom(int64_t heads, int64_t D, int dtype) {
 
 bool norm_rope_ring_applies(int64_t heads, int64_t D, int dtype) { return rope_geom(heads, D, dtype).tpr != 0; }
 
+// CTAs given to a tensor: all two-per-SM slots when it is alone, its share by bytes when q and k go together.
+static int rope_ctas(int64_t tokens, const ring::RopeGeom& g, int64_t cap) {
+  const int64_t groups = (tokens + g.tps - 1) / g.tps;
+  return (int)(groups < cap ? groups : (cap < 1 ? 1 : cap));
+}
+
 int norm_rope_bwd_ring_parts(int64_t tokens, int64_t heads, int64_t D, int dtype) {
-  const ring::RopeGeom g = rope_geom(heads, D, dtype);
-  const int64_t groups = (tokens + g.tps - 1) / g.tps, cap = (int64_t)sm_count() * 2;
-  return (int)(groups < cap ? groups : cap);
+  return rope_ctas(tokens, rope_geom(heads, D, dtype), (int64_t)sm_count() * 2);
+}
+
+// Number of partial rows each tensor of a fused q+k backward writes: q first, then k.
+void qk_norm_rope_bwd_ring_parts(int64_t tokens, int64_t hq, int64_t hk, int64_t D, int dtype, int* parts_q,
+                                 int* parts_k) {
+  const int64_t cap = (int64_t)sm_count() * 2;
+  int64_t cq = cap * hq / (hq + hk);
+  if (cq < 1) cq = 1;
+  if (cq > cap - 1) cq = cap - 1;
+  *parts_q = rope_ctas(tokens, rope_geom(hq, D, dtype), cq);
+  *parts_k = rope_ctas(tokens, rope_geom(hk, D, dtype), cap - cq);
 }
 
 template <typename T>
-static int rope_fwd_ring_t(const void* x, const void* w, const void* cs, const void* sn, void* y, float* inv,
-                           int64_t tokens, int64_t heads, int64_t D, float eps, int dtype, cudaStream_t st) {
+static ring::RopeJob<T> make_job(const void* x, const void* w, const void* dy, void* y, float* inv, float* partial,
+                                 int64_t heads, int64_t D, int dtype, int ncta, bool bwd, size_t* smem) {
   using namespace ring;
-  const RopeGeom g = rope_geom(heads, D, dtype);
-  const size_t slot = (size_t)g.tps * (g.x_bytes + 2 * g.t_bytes);
-  const int stages = pick_stages(slot);
-  const size_t smem = ring_smem_bytes(stages, slot);
-  const int64_t groups = (tokens + g.tps - 1) / g.tps, cap = (int64_t)sm_count() * 2;
-  const int grid = (int)(groups < cap ? groups : cap);
+  RopeJob<T> j{};
+  j.x = (const T*)x; j.w = (const T*)w; j.dy = (const T*)dy; j.y = (T*)y; j.inv = inv; j.partial = partial;
+  j.heads = (int)heads; j.ncta = ncta;
+  *smem = 0;
+  if (ncta == 0) return j;
+  j.g = rope_geom(heads, D, dtype);
+  const size_t slot = (size_t)j.g.tps * ((bwd ? 2 : 1) * j.g.x_bytes + 2 * j.g.t_bytes);
+  const size_t comb = bwd ? (size_t)(kConsumers / j.g.tpr) * D * sizeof(float) : 0;
+  int stages = (int)((100 * 1024 - comb) / slot);
+  j.stages = stages < 2 ? 2 : (stages > kMaxStages ? kMaxStages : stages);
+  *smem = ring_smem_bytes(j.stages, slot) + comb;
+  return j;
+}
+
+template <typename T>
+static int rope_fwd_launch(const void* xa, const void* wa, void* ya, float* inva, int64_t ha, int ca, const void* xb,
+                           const void* wb, void* yb, float* invb, int64_t hb, int cb, const void* cs, const void* sn,
+                           int64_t tokens, int64_t D, float eps, int dtype, cudaStream_t st) {
+  using namespace ring;
+  size_t sa, sb;
+  const RopeJob<T> ja = make_job<T>(xa, wa, nullptr, ya, inva, nullptr, ha, D, dtype, ca, false, &sa);
+  const RopeJob<T> jb = make_job<T>(xb, wb, nullptr, yb, invb, nullptr, hb, D, dtype, cb, false, &sb);
+  const size_t smem = sa > sb ? sa : sb;
   auto kern = norm_rope_fwd_ring_kernel<T>;
   int rc = allow_smem(kern, smem);
   if (rc != Q3_OK) return rc;
-  kern<<<grid, kThreads, smem, st>>>((const T*)x, (const T*)w, (const T*)cs, (const T*)sn, (T*)y, inv, tokens,
-                                     (int)heads, (int)D, eps, g, stages, async_status());
+  kern<<<ca + cb, kThreads, smem, st>>>(ja, jb, (const T*)cs, (const T*)sn, tokens, (int)D, eps, async_status());
+  return launch_status();
+}
+
+template <typename T>
+static int rope_bwd_launch(const void* xa, const void* wa, const void* dya, void* dxa, const float* inva, float* pa,
+                           int64_t ha, int ca, const void* xb, const void* wb, const void* dyb, void* dxb,
+                           const float* invb, float* pb, int64_t hb, int cb, const void* cs, const void* sn,
+                           int64_t tokens, int64_t D, int dtype, cudaStream_t st) {
+  using namespace ring;
+  size_t sa, sb;
+  const RopeJob<T> ja = make_job<T>(xa, wa, dya, dxa, const_cast<float*>(inva), pa, ha, D, dtype, ca, true, &sa);
+  const RopeJob<T> jb = make_job<T>(xb, wb, dyb, dxb, const_cast<float*>(invb), pb, hb, D, dtype, cb, true, &sb);
+  const size_t smem = sa > sb ? sa : sb;
+  auto kern = norm_rope_bwd_ring_kernel<T>;
+  int rc = allow_smem(kern, smem);
+  if (rc != Q3_OK) return rc;
+  kern<<<ca + cb, kThreads, smem, st>>>(ja, jb, (const T*)cs, (const T*)sn, tokens, (int)D, async_status());
   return launch_status();
 }
 
 int norm_rope_fwd_ring(const void* x, const void* w, const void* cs, const void* sn, void* y, float* inv,
                        int64_t tokens, int64_t heads, int64_t D, float eps, int dtype, cudaStream_t st) {
-  return dtype == Q3_BF16 ? rope_fwd_ring_t<__nv_bfloat16>(x, w, cs, sn, y, inv, tokens, heads, D, eps, dtype, st)
-                          : rope_fwd_ring_t<__half>(x, w, cs, sn, y, inv, tokens, heads, D, eps, dtype, st);
-}
-
-template <typename T>
-static int rope_bwd_ring_t(const void* x, const void* w, const void* cs, const void* sn, const void* dy,
-                           const float* inv, void* dx, float* partial, int64_t tokens, int64_t heads, int64_t D,
-                           int dtype, cudaStream_t st) {
-  using namespace ring;
-  const RopeGeom g = rope_geom(heads, D, dtype);
-  const size_t slot = (size_t)g.tps * (2 * g.x_bytes + 2 * g.t_bytes);
-  const size_t comb = (size_t)(kConsumers / g.tpr) * D * sizeof(float);
-  int stages = (int)((100 * 1024 - comb) / slot);
-  stages = stages < 2 ? 2 : (stages > kMaxStages ? kMaxStages : stages);
-  const size_t smem = ring_smem_bytes(stages, slot) + comb;
-  const int grid = norm_rope_bwd_ring_parts(tokens, heads, D, dtype);
-  auto kern = norm_rope_bwd_ring_kernel<T>;
-  int rc = allow_smem(kern, smem);
-  if (rc != Q3_OK) return rc;
-  kern<<<grid, kThreads, smem, st>>>((const T*)x, (const T*)w, (const T*)cs, (const T*)sn, (const T*)dy, inv, (T*)dx,
-                                     partial, tokens, (int)heads, (int)D, g, stages, async_status());
-  return launch_status();
+  const int c = rope_ctas(tokens, rope_geom(heads, D, dtype), (int64_t)sm_count() * 2);
+  return dtype == Q3_BF16
+             ? rope_fwd_launch<__nv_bfloat16>(x, w, y, inv, heads, c, nullptr, nullptr, nullptr, nullptr, 0, 0, cs, sn, tokens, D, eps, dtype, st)
+             : rope_fwd_launch<__half>(x, w, y, inv, heads, c, nullptr, nullptr, nullptr, nullptr, 0, 0, cs, sn, tokens, D, eps, dtype, st);
 }
 
 int norm_rope_bwd_ring(const void* x, const void* w, const void* cs, const void* sn, const void* dy, const float* inv,
                        void* dx, float* partial, int64_t tokens, int64_t heads, int64_t D, int dtype,
                        cudaStream_t st) {
-  return dtype == Q3_BF16 ? rope_bwd_ring_t<__nv_bfloat16>(x, w, cs, sn, dy, inv, dx, partial, tokens, heads, D, dtype, st)
-                          : rope_bwd_ring_t<__half>(x, w, cs, sn, dy, inv, dx, partial, tokens, heads, D, dtype, st);
+  const int c = norm_rope_bwd_ring_parts(tokens, heads, D, dtype);
+  return dtype == Q3_BF16
+             ? rope_bwd_launch<__nv_bfloat16>(x, w, dy, dx, inv, partial, heads, c, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, 0, 0, cs, sn, tokens, D, dtype, st)
+             : rope_bwd_launch<__half>(x, w, dy, dx, inv, partial, heads, c, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, 0, 0, cs, sn, tokens, D, dtype, st);
+}
+
+// q and k of one layer in one launch.
+int qk_norm_rope_fwd_ring(const void* q, const void* wq, void* yq, float* invq, int64_t hq, const void* k,
+                          const void* wk, void* yk, float* invk, int64_t hk, const void* cs, const void* sn,
+                          int64_t tokens, int64_t D, float eps, int dtype, cudaStream_t st) {
+  int cq, ck;
+  qk_norm_rope_bwd_ring_parts(tokens, hq, hk, D, dtype, &cq, &ck);
+  return dtype == Q3_BF16
+             ? rope_fwd_launch<__nv_bfloat16>(q, wq, yq, invq, hq, cq, k, wk, yk, invk, hk, ck, cs, sn, tokens, D, eps, dtype, st)
+             : rope_fwd_launch<__half>(q, wq, yq, invq, hq, cq, k, wk, yk, invk, hk, ck, cs, sn, tokens, D, eps, dtype, st);
+}
+
+int qk_norm_rope_bwd_ring(const void* q, const void* wq, const void* dyq, void* dq, const float* invq, float* pq,
+                          int64_t hq, const void* k, const void* wk, const void* dyk, void* dk, const float* invk,
+                          float* pk, int64_t hk, const void* cs, const void* sn, int64_t tokens, int64_t D, int dtype,
+                          cudaStream_t st) {
+  int cq, ck;
+  qk_norm_rope_bwd_ring_parts(tokens, hq, hk, D, dtype, &cq, &ck);
+  return dtype == Q3_BF16
+             ? rope_bwd_launch<__nv_bfloat16>(q, wq, dyq, dq, invq, pq, hq, cq, k, wk, dyk, dk, invk, pk, hk, ck, cs, sn, tokens, D, dtype, st)
+             : rope_bwd_launch<__half>(q, wq, dyq, dq, invq, pq, hq, cq, k, wk, dyk, dk, invk, pk, hk, ck, cs, sn, tokens, D, dtype, st);
 }
 
 }  // namespace q3

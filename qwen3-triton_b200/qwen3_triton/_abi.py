@@ -43,6 +43,9 @@ SIGNATURES = {
     "q3_norm_rope_fwd": (I, [P, P, P, P, P, P, L, L, L, D, I, P]),
     "q3_norm_rope_bwd_workspace_bytes": (L, [L, L, L]),
     "q3_norm_rope_bwd": (I, [P, P, P, P, P, P, P, P, P, L, L, L, L, I, P]),
+    "q3_qk_norm_rope_fwd": (I, [P, P, P, P, P, P, P, P, P, P, L, L, L, L, D, I, P]),
+    "q3_qk_norm_rope_bwd_workspace_bytes": (L, [L, L, L, L]),
+    "q3_qk_norm_rope_bwd": (I, [P] * 15 + [L, L, L, L, L, I, P]),
     "q3_rope_apply": (I, [P, P, P, P, L, L, L, L, I, I, I, P]),
     "q3_rope_tables": (I, [P, I, P, P, P, L, L, I, P]),
     "q3_embedding_fwd": (I, [P, I, P, P, L, L, L, I, P, P]),
@@ -61,6 +64,10 @@ SIGNATURES = {
     "q3_multi_copy": (I, [P, L, L, I, I, P]),
     "q3_gemm": (I, [P, L, L, P, L, L, P, L, L, L, I, I, P, P]),
     "q3_gemm_acc_f32": (I, [P, L, L, P, L, L, P, L, L, L, I, P, P]),
+    "q3_gemm_acc": (I, [P, L, L, P, L, L, P, L, L, L, I, I, P, P]),
+    "q3_linear_fwd_grouped": (I, [P, P, P, P, I, L, L, I, P, P]),
+    "q3_linear_dgrad_grouped": (I, [P, P, P, P, I, L, L, I, P, P]),
+    "q3_linear_wgrad_grouped": (I, [P, P, P, P, I, L, L, I, P, P]),
     "q3_linear_ce_tiles": (L, [L]),
     "q3_shift_labels": (I, [P, P, L, L, L, L, P, P]),
     "q3_linear_ce_stats": (I, [P, P, P, P, P, P, L, L, L, L, L, I, P, P]),
@@ -119,6 +126,15 @@ def check(code: int, what: str) -> None:
     if code != 0:
         msg = lib().q3_error_string(code).decode()
         raise Q3Error(f"{what}: {msg} (code {code})")
+
+
+def pointer_array(tensors):
+    """Host array of device pointers for the grouped entry points (keep it alive until the call returns)."""
+    return (c_void_p * len(tensors))(*[t.data_ptr() for t in tensors])
+
+
+def size_array(sizes):
+    return (c_int64 * len(sizes))(*[int(v) for v in sizes])
 
 
 def call(name: str, *args) -> None:

@@ -52,6 +52,54 @@ def mm_tn(dy, x):
     return _gemm(dy.data_ptr(), 1, dy.shape[1], x.data_ptr(), x.shape[1], 1, dy.shape[1], x.shape[1], dy.shape[0], dy)
 
 
+def _grouped_ok(x, weights):
+    return all(w.shape[0] % 64 == 0 for w in weights) and x.shape[1] % 8 == 0
+
+
+def linear_group_fwd(x, weights):
+    """[x @ w.T for w in weights] in one launch."""
+    if not _grouped_ok(x, weights):
+        return [mm_nt(x, w) for w in weights]
+    ys = [_empty((x.shape[0], w.shape[0]), x) for w in weights]
+    wp, yp, n = _abi.pointer_array(weights), _abi.pointer_array(ys), _abi.size_array([w.shape[0] for w in weights])
+    _abi.call('q3_linear_fwd_grouped', x.data_ptr(), wp, yp, n, len(weights), x.shape[0], x.shape[1], _abi.dt(x.dtype),
+              _abi.status_word(x.device).data_ptr(), _abi.stream())
+    return ys
+
+
+def linear_group_dgrad(dys, weights):
+    """sum(dy @ w for dy, w in zip(dys, weights)) in one launch (one accumulator, no add kernels)."""
+    if not _grouped_ok(dys[0], weights):
+        out = mm_nn(dys[0], weights[0])
+        for dy, w in zip(dys[1:], weights[1:]):
+            mm_nn_acc(out, dy, w)
+        return out
+    dx = _empty((dys[0].shape[0], weights[0].shape[1]), dys[0])
+    dp, wp, n = _abi.pointer_array(dys), _abi.pointer_array(weights), _abi.size_array([w.shape[0] for w in weights])
+    _abi.call('q3_linear_dgrad_grouped', dp, wp, dx.data_ptr(), n, len(weights), dx.shape[0], dx.shape[1],
+              _abi.dt(dx.dtype), _abi.status_word(dx.device).data_ptr(), _abi.stream())
+    return dx
+
+
+def linear_group_wgrad(dys, x):
+    """[dy.T @ x for dy in dys] in one launch."""
+    if not all(dy.shape[1] % 8 == 0 for dy in dys) or x.shape[1] % 8:
+        return [mm_tn(dy, x) for dy in dys]
+    dws = [_empty((dy.shape[1], x.shape[1]), x) for dy in dys]
+    dp, gp, n = _abi.pointer_array(dys), _abi.pointer_array(dws), _abi.size_array([dy.shape[1] for dy in dys])
+    _abi.call('q3_linear_wgrad_grouped', dp, x.data_ptr(), gp, n, len(dys), x.shape[0], x.shape[1], _abi.dt(x.dtype),
+              _abi.status_word(x.device).data_ptr(), _abi.stream())
+    return dws
+
+
+def mm_nn_acc(out, dy, w):
+    """out [M,K] += dy [M,N] @ w[N,K] (read-add-round in the GEMM epilogue; no separate add pass)"""
+    _abi.call('q3_gemm_acc', dy.data_ptr(), dy.shape[1], 1, w.data_ptr(), w.shape[1], 1, out.data_ptr(), dy.shape[0],
+              w.shape[1], dy.shape[1], _abi.dt(dy.dtype), _abi.dt(out.dtype), _abi.status_word(dy.device).data_ptr(),
+              _abi.stream())
+    return out
+
+
 def _add(a, b):
     out = torch.empty_like(a)
     _abi.call('q3_residual_add', a.data_ptr(), b.data_ptr(), out.data_ptr(), a.numel(), _abi.dt(a.dtype), _abi.stream())
@@ -102,6 +150,26 @@ def _norm_rope_bwd(x, w, cos, sin, dy, inv, tokens, heads, d):
     return dx, dw
 
 
+def _qk_norm_rope_fwd(q, k, wq, wk, cos, sin, tokens, hq, hk, d, eps):
+    """q and k through per-head RMSNorm + RoPE in one launch: (qn, invq, kn, invk)."""
+    yq, yk = torch.empty_like(q), torch.empty_like(k)
+    invq, invk = _empty((tokens * hq,), q, torch.float32), _empty((tokens * hk,), k, torch.float32)
+    _abi.call('q3_qk_norm_rope_fwd', q.data_ptr(), k.data_ptr(), wq.data_ptr(), wk.data_ptr(), cos.data_ptr(),
+              sin.data_ptr(), yq.data_ptr(), yk.data_ptr(), invq.data_ptr(), invk.data_ptr(), tokens, hq, hk, d, eps,
+              _abi.dt(q.dtype), _abi.stream())
+    return yq, invq, yk, invk
+
+
+def _qk_norm_rope_bwd(q, k, wq, wk, cos, sin, dyq, dyk, invq, invk, tokens, hq, hk, d):
+    dq, dk, dwq, dwk = torch.empty_like(q), torch.empty_like(k), torch.empty_like(wq), torch.empty_like(wk)
+    ws = _abi.workspace(_abi.lib().q3_qk_norm_rope_bwd_workspace_bytes(tokens, hq, hk, d), q.device)
+    _abi.call('q3_qk_norm_rope_bwd', q.data_ptr(), k.data_ptr(), wq.data_ptr(), wk.data_ptr(), cos.data_ptr(),
+              sin.data_ptr(), dyq.data_ptr(), dyk.data_ptr(), invq.data_ptr(), invk.data_ptr(), dq.data_ptr(),
+              dk.data_ptr(), dwq.data_ptr(), dwk.data_ptr(), ws.data_ptr(), ws.numel(), tokens, hq, hk, d,
+              _abi.dt(q.dtype), _abi.stream())
+    return dq, dwq, dk, dwk
+
+
 def layer_forward(resid, delta, cos, sin, w, meta):
     """All intermediates of one decoder layer. resid/delta [T, H]; returns a dict."""
     b, s, hq, hk, d, eps = meta
@@ -109,9 +177,8 @@ def layer_forward(resid, delta, cos, sin, w, meta):
     w_in, wq, wk, wv, wo, wqn, wkn, w_post, wg, wu, wd = w
     r = {}
     r['h'], r['x'], r['inv1'] = _norm_fwd(resid, delta, w_in, eps)
-    r['q'], r['k'], r['v'] = mm_nt(r['h'], wq), mm_nt(r['h'], wk), mm_nt(r['h'], wv)
-    r['qn'], r['invq'] = _norm_rope_fwd(r['q'], wqn, cos, sin, t, hq, d, eps)
-    r['kn'], r['invk'] = _norm_rope_fwd(r['k'], wkn, cos, sin, t, hk, d, eps)
+    r['q'], r['k'], r['v'] = linear_group_fwd(r['h'], [wq, wk, wv])
+    r['qn'], r['invq'], r['kn'], r['invk'] = _qk_norm_rope_fwd(r['q'], r['k'], wqn, wkn, cos, sin, t, hq, hk, d, eps)
     r['o'] = torch.empty_like(r['q'])
     r['lse'] = _empty((b, hq, s), resid, torch.float32)
     _abi.call('q3_attn_fwd_bshd', r['qn'].data_ptr(), r['kn'].data_ptr(), r['v'].data_ptr(), r['o'].data_ptr(),
@@ -139,8 +206,7 @@ def recompute_cheap(r, cos, sin, w, meta):
     t = r['x'].shape[0]
     w_in, wq, wk, wv, wo, wqn, wkn, w_post, wg, wu, wd = w
     r['h'], _, r['inv1'] = _norm_fwd(r['x'], None, w_in, eps)
-    r['qn'], r['invq'] = _norm_rope_fwd(r['q'], wqn, cos, sin, t, hq, d, eps)
-    r['kn'], r['invk'] = _norm_rope_fwd(r['k'], wkn, cos, sin, t, hk, d, eps)
+    r['qn'], r['invq'], r['kn'], r['invk'] = _qk_norm_rope_fwd(r['q'], r['k'], wqn, wkn, cos, sin, t, hq, hk, d, eps)
     r['h2'], _, r['inv2'] = _norm_fwd(r['x1'], None, w_post, eps)
     r['y'] = torch.empty_like(r['g'])
     _abi.call('q3_swiglu_fwd', r['g'].data_ptr(), r['u'].data_ptr(), r['y'].data_ptr(), r['g'].numel(),
@@ -194,8 +260,8 @@ class FusedLayerFn(torch.autograd.Function):
         _abi.call('q3_swiglu_bwd', r['g'].data_ptr(), r['u'].data_ptr(), dy.data_ptr(), dg.data_ptr(), du.data_ptr(),
                   dg.numel(), _abi.dt(dg.dtype), _abi.stream())
         del dy
-        dh2 = _add(mm_nn(dg, wg), mm_nn(du, wu))
-        dwg, dwu = mm_tn(dg, r['h2']), mm_tn(du, r['h2'])
+        dh2 = linear_group_dgrad([dg, du], [wg, wu])
+        dwg, dwu = linear_group_wgrad([dg, du], r['h2'])
         del dg, du
         dx1, dw_post = _norm_bwd(r['x1'], w_post, dh2, dres, r['inv2'])
         # attention block
@@ -207,10 +273,10 @@ class FusedLayerFn(torch.autograd.Function):
                   do.data_ptr(), r['lse'].data_ptr(), dqn.data_ptr(), dkn.data_ptr(), dv.data_ptr(), ws.data_ptr(),
                   ws.numel(), b, s, hq, hk, d, d ** -0.5, _abi.dt(dx1.dtype), _abi.status_word(dx1.device).data_ptr(),
                   _abi.stream())
-        dq, dwqn = _norm_rope_bwd(r['q'], wqn, cos, sin, dqn, r['invq'], t, hq, d)
-        dk, dwkn = _norm_rope_bwd(r['k'], wkn, cos, sin, dkn, r['invk'], t, hk, d)
-        dh = _add(_add(mm_nn(dq, wq), mm_nn(dk, wk)), mm_nn(dv, wv))
-        dwq, dwk, dwv = mm_tn(dq, r['h']), mm_tn(dk, r['h']), mm_tn(dv, r['h'])
+        dq, dwqn, dk, dwkn = _qk_norm_rope_bwd(r['q'], r['k'], wqn, wkn, cos, sin, dqn, dkn, r['invq'], r['invk'],
+                                               t, hq, hk, d)
+        dh = linear_group_dgrad([dq, dk, dv], [wq, wk, wv])
+        dwq, dwk, dwv = linear_group_wgrad([dq, dk, dv], r['h'])
         dx, dw_in = _norm_bwd(r['x'], w_in, dh, dx1, r['inv1'])
         dx = dx.view(ctx.shape)
         return (dx, dx if ctx.has_delta else None, None, None, None, None,

@@ -54,6 +54,50 @@ def test_fp32_output_and_determinism():
     assert torch.equal(c, matmul(a, b, output_dtype=torch.float32))
 
 
+@pytest.mark.parametrize('dtype', [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize('M,K,sizes', [(2048, 4096, (4096, 1024, 1024)), (300, 520, (192, 64, 320)), (129, 136, (448, 64)),
+                                       (2048, 1024, (3072, 3072))])
+def test_grouped_linear_layers_equal_separate_gemms(dtype, M, K, sizes):
+    """q/k/v- and gate/up-style groups in one launch: forward outputs and weight gradients bit-identical to the
+    single GEMMs (same tiles, same k order), the summed input gradient equal to fp32 math on the same operands."""
+    from qwen3_triton import _abi
+    from qwen3_triton.fused import linear_group_dgrad, linear_group_fwd, linear_group_wgrad, mm_nn, mm_nt, mm_tn
+    x = randn((M, K), 41, dtype).cuda()
+    ws = [randn((n, K), 42 + i, dtype, scale=0.05).cuda() for i, n in enumerate(sizes)]
+    dys = [randn((M, n), 52 + i, dtype).cuda() for i, n in enumerate(sizes)]
+    ys = linear_group_fwd(x, ws)
+    for y, w in zip(ys, ws):
+        assert torch.equal(y, mm_nt(x, w))
+        close(y, ref_mm(x, w.t()).to(dtype), scale=K ** 0.5 * 0.05, what='grouped fwd')
+    dws = linear_group_wgrad(dys, x)
+    for dw, dy in zip(dws, dys):
+        assert torch.equal(dw, mm_tn(dy, x))
+    dx = linear_group_dgrad(dys, ws)
+    ref = sum(ref_mm(dy, w) for dy, w in zip(dys, ws))
+    close(dx, ref.to(dtype), scale=float(ref.abs().mean()) / 2, what='grouped dgrad')
+    assert torch.equal(dx, linear_group_dgrad(dys, ws))
+    assert _abi.read_status() == 0
+
+
+@pytest.mark.parametrize('out', [torch.bfloat16, torch.float16, torch.float32])
+@pytest.mark.parametrize('M,N,K', [(256, 512, 128), (200, 264, 72), (2048, 4096, 1024)])
+def test_accumulating_epilogue(out, M, N, K):
+    """C += A*B with C in the input type (read, add in fp32, round once) or in fp32: against fp32 math on the same
+    operands, in the input-gradient layout it is used for."""
+    from qwen3_triton import _abi
+    dtype = torch.float16 if out == torch.float16 else torch.bfloat16
+    dy, w = randn((M, K), 31, dtype).cuda(), randn((K, N), 32, dtype).cuda()
+    c0 = randn((M, N), 33, out, scale=K ** 0.5)
+    c = c0.cuda().clone()
+    _abi.call('q3_gemm_acc', dy.data_ptr(), K, 1, w.data_ptr(), N, 1, c.data_ptr(), M, N, K, _abi.dt(dtype), _abi.dt(out),
+              _abi.status_word(c.device).data_ptr(), _abi.stream())
+    ref = c0.float() + ref_mm(dy, w)
+    if out == torch.float32:
+        torch.testing.assert_close(c.cpu(), ref, rtol=1e-4, atol=2e-2)
+    else:
+        close(c, ref.to(out), scale=K ** 0.5, what='C += A*B')
+
+
 @pytest.mark.parametrize('dtype', [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize('M,N,K', [(1, 1, 1), (17, 129, 33), (65, 7, 257)])
 def test_fallback_path_odd_shapes_and_fp32(dtype, M, N, K):

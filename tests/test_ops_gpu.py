@@ -237,6 +237,31 @@ def test_norm_rope_through_the_shared_memory_ring(dtype, B, S, H, D):
     assert _abi.read_status() == 0
 
 
+@pytest.mark.parametrize('T,hq,hk,D', [(4100, 32, 8, 128), (333, 4, 4, 64), (50, 3, 1, 10)])
+def test_q_and_k_in_one_launch_equal_two_launches(T, hq, hk, D):
+    """q3_qk_norm_rope_* share one grid between q and k (or fall back to two launches for shapes the wide-row kernels
+    do not take): outputs, input gradients and inverse norms bit-identical to the single-tensor entry points, weight
+    gradients equal up to the fp32 order of the per-CTA partial sums."""
+    from qwen3_triton import _abi
+    from qwen3_triton.fused import _norm_rope_bwd, _norm_rope_fwd, _qk_norm_rope_bwd, _qk_norm_rope_fwd
+    bf = torch.bfloat16
+    q, k = randn((T, hq, D), 81, bf).cuda(), randn((T, hk, D), 82, bf).cuda()
+    wq, wk = (1 + 0.1 * randn((D,), 83)).to(bf).cuda(), (1 + 0.1 * randn((D,), 84)).to(bf).cuda()
+    cos, sin = randn((T, D), 85, bf).cuda(), randn((T, D), 86, bf).cuda()
+    dq, dk = randn((T, hq, D), 87, bf).cuda(), randn((T, hk, D), 88, bf).cuda()
+    yq, iq, yk, ik = _qk_norm_rope_fwd(q, k, wq, wk, cos, sin, T, hq, hk, D, 1e-6)
+    yq1, iq1 = _norm_rope_fwd(q, wq, cos, sin, T, hq, D, 1e-6)
+    yk1, ik1 = _norm_rope_fwd(k, wk, cos, sin, T, hk, D, 1e-6)
+    assert torch.equal(yq, yq1) and torch.equal(yk, yk1) and torch.equal(iq, iq1) and torch.equal(ik, ik1)
+    gq, gwq, gk, gwk = _qk_norm_rope_bwd(q, k, wq, wk, cos, sin, dq, dk, iq, ik, T, hq, hk, D)
+    gq1, gwq1 = _norm_rope_bwd(q, wq, cos, sin, dq, iq, T, hq, D)
+    gk1, gwk1 = _norm_rope_bwd(k, wk, cos, sin, dk, ik, T, hk, D)
+    assert torch.equal(gq, gq1) and torch.equal(gk, gk1)
+    close(gwq, gwq1, scale=float(gwq1.float().abs().mean()), what='dwq')
+    close(gwk, gwk1, scale=float(gwk1.float().abs().mean()), what='dwk')
+    assert _abi.read_status() == 0
+
+
 def test_fused_qk_norm_rope_golden(golden_ops):
     from ops.triton.fused_qk_norm_rope import fused_qk_norm_rope_triton
     d = recipe.op_inputs()
