@@ -230,7 +230,7 @@ def main():
             fused_linear_cross_entropy(hid, wh, lab).backward()
         report("linear_ce_fwd+bwd (no logits)", timer(fb), flops=8.0 * T * H * V)
         del hid, wh
-    for (B, S) in [(4, 4096), (8, 2048), (2, 8192)]:
+    for (B, S) in [(4, 4096), (8, 2048), (2, 8192), (1, 2048)]:
         name = f"attn_B{B}_S{S}"
         if want("attn") or want(name):
             S2 = max(256, int(S * min(1.0, a.scale * 4)) // 128 * 128) if a.scale < 0.25 else S

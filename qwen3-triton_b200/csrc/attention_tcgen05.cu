@@ -106,6 +106,21 @@ __device__ __forceinline__ void mma_kmn(uint32_t d_tmem, uint32_t a_smem, uint32
   }
 }
 
+// Barrier over the two compute warps that share a TMEM lane quarter (64 threads, hardware barrier 1 + quarter),
+// ANDing a predicate over them. Both warps must reach every call: no early exit between two calls.
+__device__ __forceinline__ bool pair_all(int quarter, bool pred) {
+  int r;
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t"
+      "setp.ne.s32 q, %1, 0;\n\t"
+      "bar.red.and.pred p, %2, 64, q;\n\t"
+      "selp.s32 %0, 1, 0, p;\n\t}"
+      : "=r"(r)
+      : "r"((int)pred), "r"(quarter + 1)
+      : "memory");
+  return r != 0;
+}
+
 template <typename T>
 __global__ void __launch_bounds__(kAttnThreads, 1)
 attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
@@ -128,7 +143,6 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   const uint32_t p_full = bar0 + 8u * 13, done_bar = bar0 + 8u * 14;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 15);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  const uint32_t x_bar = bar0 + 8u * 16;
   float* xmax = reinterpret_cast<float*>(bars + 18);   // [2 tiles in flight + 1][2 column halves][128 rows]
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -143,7 +157,6 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     for (int i = 0; i < 13; ++i) mbar_init(bar0 + 8u * i, 1);
     mbar_init(p_full, kComputeThreads);
     mbar_init(done_bar, 1);
-    mbar_init(x_bar, kComputeThreads);
     fence_barrier_init();
     prefetch_tmap(&tmQ); prefetch_tmap(&tmK); prefetch_tmap(&tmV);
   }
@@ -244,9 +257,9 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         }
       }
       xmax[(j & 1) * 256 + ch * 128 + row] = mx;
-      mbar_arrive(x_bar);                      // release: the partner thread's maximum is visible after the wait
-      if (!mbar_wait(x_bar, j & 1u, abort_flag)) ok = false;
-      ok = __all_sync(0xffffffffu, ok);        // tcgen05.ld below is warp-collective: keep the decision uniform
+      // the partner thread (same row, other column half) sits in the warp four above / below: a 64-thread hardware
+      // barrier publishes both maxima and makes the keep-going decision uniform over the pair
+      ok = pair_all(qd, ok);
       if (!ok) break;
       mx = fmaxf(m, fmaxf(mx, xmax[(j & 1) * 256 + (ch ^ 1) * 128 + row]));
       const float mc = mx * p.scale_log2;
@@ -294,9 +307,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     }
     // combine the two partial row sums (own slot of the exchange buffer, one more phase of the barrier)
     xmax[512 + ch * 128 + row] = l;
-    mbar_arrive(x_bar);
-    if (ok && !mbar_wait(x_bar, ntiles & 1u, abort_flag)) ok = false;
-    ok = __all_sync(0xffffffffu, ok);
+    ok = pair_all(qd, ok);
     if (ok) l += xmax[512 + (ch ^ 1) * 128 + row];
     bool fin = ok && mbar_wait(o_full((ntiles - 1) & 1), ((ntiles - 1) >> 1) & 1u, abort_flag);
     fin = __all_sync(0xffffffffu, fin);
@@ -374,7 +385,9 @@ __device__ __forceinline__ void mma_kmn2(uint32_t d_tmem, uint32_t a_smem, uint3
 }
 
 // ------------------------------------------------------------------ dQ: one CTA per 128-query tile
-// smem: [Q][dO][K0][K1][V0][V1][dS] 32 KB each. TMEM columns: S 0..127, dP 128..255, dQ 256..383.
+// smem: [Q][dO][K0][K1][V0][V1][dS] 32 KB each. TMEM columns: S double-buffered 0..127 / 128..255, dP 256..383,
+// dQ 384..511. The score product of the next key tile is issued before the tensor core waits for dS of the current
+// one, so it runs under the exponentials; dP and dQ stay in order behind it.
 template <typename T>
 __global__ void __launch_bounds__(kAttnThreads, 1)
 attn_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
@@ -393,8 +406,9 @@ attn_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
   auto k_empty = [&](int s) { return bar0 + 8u * (3 + s); };
   auto v_full = [&](int s) { return bar0 + 8u * (5 + s); };
   auto v_empty = [&](int s) { return bar0 + 8u * (7 + s); };
-  const uint32_t sdp_full = bar0 + 8u * 9, dq_full = bar0 + 8u * 10, ds_full = bar0 + 8u * 11, done_bar = bar0 + 8u * 12;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 13);
+  const uint32_t dp_full = bar0 + 8u * 9, dq_full = bar0 + 8u * 10, ds_full = bar0 + 8u * 11, done_bar = bar0 + 8u * 12;
+  auto s_full = [&](int s) { return bar0 + 8u * (13 + s); };
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 15);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -409,6 +423,8 @@ attn_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     for (int i = 0; i < 11; ++i) mbar_init(bar0 + 8u * i, 1);
     mbar_init(ds_full, kComputeThreads);
     mbar_init(done_bar, 1);
+    mbar_init(s_full(0), 1);
+    mbar_init(s_full(1), 1);
     fence_barrier_init();
     prefetch_tmap(&tmQ); prefetch_tmap(&tmK); prefetch_tmap(&tmV); prefetch_tmap(&tmDO);
   }
@@ -447,19 +463,32 @@ attn_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      bool ok = mbar_wait(q_full, 0, abort_flag);
+      bool ok = mbar_wait(q_full, 0, abort_flag) && mbar_wait(k_full(0), 0, abort_flag);
+      if (ok) {
+        tc_fence_after();
+        mma_kk(tmem + 0, q_s, HALF_BYTES, k_s, HALF_BYTES, p.idesc_kk128, 8, false);                       // S_0
+        mma_commit(s_full(0));
+      }
       for (int j = 0; j < ntiles && ok; ++j) {
         const int s = j & 1;
         const uint32_t ph = (j >> 1) & 1u;
-        if (!mbar_wait(k_full(s), ph, abort_flag) || !mbar_wait(v_full(s), ph, abort_flag)) { ok = false; break; }
+        // dP_j: its buffer is free, the compute warps finished tile j-1 before ds_full(j-1) completed
+        if (!mbar_wait(v_full(s), ph, abort_flag)) { ok = false; break; }
         tc_fence_after();
-        mma_kk(tmem + 0, q_s, HALF_BYTES, k_s + s * TILE_BYTES, HALF_BYTES, p.idesc_kk128, 8, false);     // S
-        mma_kk(tmem + 128, do_s, HALF_BYTES, v_s + s * TILE_BYTES, HALF_BYTES, p.idesc_kk128, 8, false);  // dP
-        mma_commit(sdp_full);
+        mma_kk(tmem + 256, do_s, HALF_BYTES, v_s + s * TILE_BYTES, HALF_BYTES, p.idesc_kk128, 8, false);  // dP_j
+        mma_commit(dp_full);
         mma_commit(v_empty(s));
+        // S_{j+1} into the other score buffer (last read for tile j-1): runs while the compute warps work on tile j
+        if (j + 1 < ntiles) {
+          const int s1 = (j + 1) & 1;
+          if (!mbar_wait(k_full(s1), ((j + 1) >> 1) & 1u, abort_flag)) { ok = false; break; }
+          tc_fence_after();
+          mma_kk(tmem + s1 * 128, q_s, HALF_BYTES, k_s + s1 * TILE_BYTES, HALF_BYTES, p.idesc_kk128, 8, false);
+          mma_commit(s_full(s1));
+        }
         if (!mbar_wait(ds_full, j & 1u, abort_flag)) { ok = false; break; }
         tc_fence_after();
-        mma_kmn2(tmem + 256, ds_s, HALF_BYTES, k_s + s * TILE_BYTES, HALF_BYTES, p.idesc_kmn, 8, j > 0);   // dQ += dS K
+        mma_kmn2(tmem + 384, ds_s, HALF_BYTES, k_s + s * TILE_BYTES, HALF_BYTES, p.idesc_kmn, 8, j > 0);   // dQ += dS K
         mma_commit(k_empty(s));
       }
       if (ok) mma_commit(dq_full);
@@ -475,17 +504,18 @@ attn_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     const float dl = qi < p.S ? p.delta[(int64_t)bh * p.S + qi] : 0.f;
     bool ok = true;
     for (int j = 0; j < ntiles && ok; ++j) {
-      if (!mbar_wait(sdp_full, j & 1u, abort_flag)) ok = false;
+      if (!mbar_wait(s_full(j & 1), (j >> 1) & 1u, abort_flag) || !mbar_wait(dp_full, j & 1u, abort_flag)) ok = false;
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
       const bool diag = (j == ntiles - 1);
+      const uint32_t s_addr = lane_addr + (j & 1) * 128;
 #pragma unroll 1
       for (int c = 2 * ch; c < 2 * ch + 2; ++c) {
         uint32_t rs[32], rp[32];
         float ds[32];
-        tmem_ld32(lane_addr + c * 32, rs);
-        tmem_ld32(lane_addr + 128 + c * 32, rp);
+        tmem_ld32(s_addr + c * 32, rs);
+        tmem_ld32(lane_addr + 256 + c * 32, rp);
         tmem_ld_wait();
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
@@ -507,7 +537,7 @@ attn_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
 #pragma unroll 1
       for (int c = 2 * ch; c < 2 * ch + 2; ++c) {
         uint32_t r[32];
-        tmem_ld32(lane_addr + 256 + c * 32, r);
+        tmem_ld32(lane_addr + 384 + c * 32, r);
         tmem_ld_wait();
         if (qi < p.S) {
 #pragma unroll
