@@ -147,8 +147,10 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int nq = (p.S + TILE - 1) / TILE;
-  const int qt = nq - 1 - (int)blockIdx.x;  // heaviest tiles first
-  const int bh = blockIdx.y, b = bh / p.Hq, h = bh % p.Hq, kvh = h / (p.Hq / p.Hkv);
+  // grid = (batch * heads, query tiles): blocks start in x-major order, so every head's heaviest (last) query tile
+  // starts before any lighter one - longest work first over the whole grid, not per head
+  const int qt = nq - 1 - (int)blockIdx.y;
+  const int bh = blockIdx.x, b = bh / p.Hq, h = bh % p.Hq, kvh = h / (p.Hq / p.Hkv);
   const int bkv = b * p.Hkv + kvh;
   const int ntiles = qt + 1;
 
@@ -249,10 +251,14 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
           uint32_t r[32];
           tmem_ld32(s_addr + c * 32, r);
           tmem_ld_wait();
+          if (!diag) {   // all but the last key tile of a query tile: no causal mask, no per-element compare
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            const float sv = __uint_as_float(r[i]);
-            if (!diag || ch * 64 + c * 32 + i <= row) mx = fmaxf(mx, sv);
+            for (int i = 0; i < 32; i += 2)
+              mx = fmaxf(mx, fmaxf(__uint_as_float(r[i]), __uint_as_float(r[i + 1])));
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              if (ch * 64 + c * 32 + i <= row) mx = fmaxf(mx, __uint_as_float(r[i]));
           }
         }
       }
@@ -277,11 +283,19 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
           float pv[32];
           tmem_ld32(s_addr + c * 32, r);
           tmem_ld_wait();
+          if (!diag) {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            const float e = fast_exp2(fmaf(__uint_as_float(r[i]), p.scale_log2, -mc));
-            pv[i] = (!diag || ch * 64 + c * 32 + i <= row) ? e : 0.f;
-            sum += pv[i];
+            for (int i = 0; i < 32; ++i) {
+              pv[i] = fast_exp2(fmaf(__uint_as_float(r[i]), p.scale_log2, -mc));
+              sum += pv[i];
+            }
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              const float e = fast_exp2(fmaf(__uint_as_float(r[i]), p.scale_log2, -mc));
+              pv[i] = (ch * 64 + c * 32 + i <= row) ? e : 0.f;
+              sum += pv[i];
+            }
           }
           store_swizzled32<T>(p_ptr, row, ch * 64 + c * 32, pv);
         }
@@ -413,8 +427,8 @@ attn_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int nq = (p.S + TILE - 1) / TILE;
-  const int qt = nq - 1 - (int)blockIdx.x;
-  const int bh = blockIdx.y, b = bh / p.Hq, h = bh % p.Hq, kvh = h / (p.Hq / p.Hkv);
+  const int qt = nq - 1 - (int)blockIdx.y;   // heaviest query tiles of all heads first
+  const int bh = blockIdx.x, b = bh / p.Hq, h = bh % p.Hq, kvh = h / (p.Hq / p.Hkv);
   const int bkv = b * p.Hkv + kvh;
   const int ntiles = qt + 1;
 
@@ -517,11 +531,17 @@ attn_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         tmem_ld32(s_addr + c * 32, rs);
         tmem_ld32(lane_addr + 256 + c * 32, rp);
         tmem_ld_wait();
+        if (!diag && qi < p.S) {
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const float pr = fast_exp2(fmaf(__uint_as_float(rs[i]), p.scale_log2, -lse2));
-          const bool keep = (!diag || c * 32 + i <= row) && qi < p.S;
-          ds[i] = keep ? pr * (__uint_as_float(rp[i]) - dl) : 0.f;
+          for (int i = 0; i < 32; ++i)
+            ds[i] = fast_exp2(fmaf(__uint_as_float(rs[i]), p.scale_log2, -lse2)) * (__uint_as_float(rp[i]) - dl);
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const float pr = fast_exp2(fmaf(__uint_as_float(rs[i]), p.scale_log2, -lse2));
+            const bool keep = (!diag || c * 32 + i <= row) && qi < p.S;
+            ds[i] = keep ? pr * (__uint_as_float(rp[i]) - dl) : 0.f;
+          }
         }
         store_swizzled32<T>(ds_ptr, row, c * 32, ds);
       }
@@ -595,9 +615,12 @@ attn_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int kt = blockIdx.x, bk = blockIdx.y, b = bk / p.Hkv, kvh = bk % p.Hkv, G = p.Hq / p.Hkv;
+  // grid = (batch * kv heads * group split, key tiles): key tile 0 sees every query and goes first for all heads
+  const int gs = p.gsplit > 1 ? p.gsplit : 1;
+  const int kt = blockIdx.y, bk = (int)blockIdx.x / gs, zsplit = (int)blockIdx.x % gs;
+  const int b = bk / p.Hkv, kvh = bk % p.Hkv, G = p.Hq / p.Hkv;
   const int nsub = (p.S + QSUB - 1) / QSUB, first = kt * (TILE / QSUB);
-  const int g0 = p.gsplit > 1 ? (int)blockIdx.z : 0, ng = p.gsplit > 1 ? 1 : G;
+  const int g0 = p.gsplit > 1 ? zsplit : 0, ng = p.gsplit > 1 ? 1 : G;
   const int per_head = nsub - first, total = ng * per_head;
 
   if (threadIdx.x == 0) {
@@ -710,13 +733,22 @@ attn_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         tmem_ld32(lane_addr + (it & 1) * 64 + c * 32, rs);
         tmem_ld32(lane_addr + 128 + (it & 1) * 64 + c * 32, rp);
         tmem_ld_wait();
+        if (!diag && (i + 1) * QSUB <= p.S) {   // sub-tile strictly below the diagonal block and inside the sequence
 #pragma unroll
-        for (int e = 0; e < 32; ++e) {
-          const int col = c * 32 + e, qi = i * QSUB + col;
-          const float pr = fast_exp2(fmaf(__uint_as_float(rs[e]), p.scale_log2, -st[col]));
-          const bool keep = qi < p.S && (!diag || kj <= qi);
-          pv[e] = keep ? pr : 0.f;
-          dsv[e] = keep ? pr * (__uint_as_float(rp[e]) - st[QSUB + col]) : 0.f;
+          for (int e = 0; e < 32; ++e) {
+            const int col = c * 32 + e;
+            pv[e] = fast_exp2(fmaf(__uint_as_float(rs[e]), p.scale_log2, -st[col]));
+            dsv[e] = pv[e] * (__uint_as_float(rp[e]) - st[QSUB + col]);
+          }
+        } else {
+#pragma unroll
+          for (int e = 0; e < 32; ++e) {
+            const int col = c * 32 + e, qi = i * QSUB + col;
+            const float pr = fast_exp2(fmaf(__uint_as_float(rs[e]), p.scale_log2, -st[col]));
+            const bool keep = qi < p.S && (!diag || kj <= qi);
+            pv[e] = keep ? pr : 0.f;
+            dsv[e] = keep ? pr * (__uint_as_float(rp[e]) - st[QSUB + col]) : 0.f;
+          }
         }
         store_swizzled32<T>(pt_ptr, row, c * 32, pv);
         store_swizzled32<T>(dst_ptr, row, c * 32, dsv);
@@ -731,9 +763,9 @@ attn_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       tc_fence_after();
       if (p.gsplit > 1) {
         // fp32 partials of this query head; a second kernel sums the group in a fixed order
-        const int64_t rows = (int64_t)gridDim.y * p.S;
-        float* pk = p.part + (((int64_t)blockIdx.z * 2 + 0) * rows + (int64_t)bk * p.S + kj) * AD;
-        float* pvp = p.part + (((int64_t)blockIdx.z * 2 + 1) * rows + (int64_t)bk * p.S + kj) * AD;
+        const int64_t rows = (int64_t)(gridDim.x / gs) * p.S;
+        float* pk = p.part + (((int64_t)zsplit * 2 + 0) * rows + (int64_t)bk * p.S + kj) * AD;
+        float* pvp = p.part + (((int64_t)zsplit * 2 + 1) * rows + (int64_t)bk * p.S + kj) * AD;
 #pragma unroll 1
         for (int c = 2 * ch; c < 2 * ch + 2; ++c) {
           uint32_t rk[32], rv[32];
@@ -856,7 +888,7 @@ int attn_fwd_tc(const void* q, const void* k, const void* v, void* out, float* l
   p.idesc_qk = make_idesc_f16(128, 128, bf16, false, false);
   p.idesc_pv = make_idesc_f16(128, 128, bf16, false, true);
   p.status = status;
-  dim3 grid((unsigned)cdiv(S, TILE), (unsigned)(B * Hq));
+  dim3 grid((unsigned)(B * Hq), (unsigned)cdiv(S, TILE));
   if (bf16) {
     static bool cfg = false;
     if ((rc = configure_smem(attn_fwd_tc_kernel<__nv_bfloat16>, kFwdSmem, &cfg)) != Q3_OK) return rc;
@@ -894,7 +926,7 @@ int attn_bwd_tc(const void* q, const void* k, const void* v, const void* dout, c
   p.idesc_kk64 = make_idesc_f16(128, 64, bf16, false, false);
   p.idesc_kmn = make_idesc_f16(128, 128, bf16, false, true);
   p.status = status;
-  dim3 gq((unsigned)cdiv(S, TILE), (unsigned)(B * Hq)), gk((unsigned)cdiv(S, TILE), (unsigned)(B * Hkv), (unsigned)p.gsplit);
+  dim3 gq((unsigned)(B * Hq), (unsigned)cdiv(S, TILE)), gk((unsigned)(B * Hkv * p.gsplit), (unsigned)cdiv(S, TILE));
   const int64_t kv_rows = B * Hkv * S;
   const int red_grid = (int)std::min<int64_t>(cdiv(kv_rows * (AD / 4), 256), (int64_t)sm_count() * 8);
   if (bf16) {
