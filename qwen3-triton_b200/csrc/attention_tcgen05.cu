@@ -37,6 +37,10 @@ constexpr int HALF_BYTES = TILE * 128;       // one 64-column half of a 128-row 
 constexpr int TILE_BYTES = 2 * HALF_BYTES;   // 32 KB
 constexpr int kAttnThreads = 320;   // warp 0 TMA, warp 1 MMA, warps 2..9 compute (two threads per tile row)
 constexpr int kComputeThreads = 256;
+// The dQ kernel has no reduction along a row, so its rows are cut four ways (16 compute warps, one 32-column chunk of
+// the score tile per thread): twice the warps to hide tensor-memory load latency, half the registers per thread.
+constexpr int kDqComputeThreads = 512;
+constexpr int kDqThreads = 64 + kDqComputeThreads;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
 
@@ -157,7 +161,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   if (threadIdx.x == 0) {
     *abort_flag = 0;
     for (int i = 0; i < 13; ++i) mbar_init(bar0 + 8u * i, 1);
-    mbar_init(p_full, kComputeThreads);
+    mbar_init(p_full, kComputeThreads / 32);      // one arrival per compute warp
     mbar_init(done_bar, 1);
     fence_barrier_init();
     prefetch_tmap(&tmQ); prefetch_tmap(&tmK); prefetch_tmap(&tmV);
@@ -304,7 +308,8 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       m = mx;
       tc_fence_before();
       fence_proxy_async_smem();   // generic-proxy writes of P must be visible to the tensor core
-      mbar_arrive(p_full);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(p_full);   // the warp's writes are ordered before lane 0's arrival
       // fold this thread's half of O_{j-1} into registers while the tensor core computes S_{j+1} and P_j V_j
       if (j > 0 && ok) {
         const uint32_t o_addr = lane_addr + 256 + ((j - 1) & 1) * 128 + ch * 64;
@@ -403,7 +408,7 @@ __device__ __forceinline__ void mma_kmn2(uint32_t d_tmem, uint32_t a_smem, uint3
 // dQ 384..511. The score product of the next key tile is issued before the tensor core waits for dS of the current
 // one, so it runs under the exponentials; dP and dQ stay in order behind it.
 template <typename T>
-__global__ void __launch_bounds__(kAttnThreads, 1)
+__global__ void __launch_bounds__(kDqThreads, 1)
 attn_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                   const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
                   const AttnBwdParams p) {
@@ -435,7 +440,7 @@ attn_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
   if (threadIdx.x == 0) {
     *abort_flag = 0;
     for (int i = 0; i < 11; ++i) mbar_init(bar0 + 8u * i, 1);
-    mbar_init(ds_full, kComputeThreads);
+    mbar_init(ds_full, kDqComputeThreads / 32);   // one arrival per compute warp
     mbar_init(done_bar, 1);
     mbar_init(s_full(0), 1);
     mbar_init(s_full(1), 1);
@@ -510,7 +515,7 @@ attn_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
       mbar_wait_drain(done_bar, 0);
     }
   } else {
-    // two threads per query row: warps 2-5 take key columns 0..63 of each tile, warps 6-9 columns 64..127
+    // four threads per query row: warps 2-5 take key columns 0..31 of each tile, 6-9 columns 32..63, and so on
     const int qd = warp & 3, ch = (warp - 2) >> 2, row = qd * 32 + lane;
     const uint32_t lane_addr = tmem + ((uint32_t)(qd * 32) << 16);
     const int qi = qt * TILE + row;
@@ -524,8 +529,8 @@ attn_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
       tc_fence_after();
       const bool diag = (j == ntiles - 1);
       const uint32_t s_addr = lane_addr + (j & 1) * 128;
-#pragma unroll 1
-      for (int c = 2 * ch; c < 2 * ch + 2; ++c) {
+      {
+        const int c = ch;
         uint32_t rs[32], rp[32];
         float ds[32];
         tmem_ld32(s_addr + c * 32, rs);
@@ -547,15 +552,16 @@ attn_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
       }
       tc_fence_before();
       fence_proxy_async_smem();
-      mbar_arrive(ds_full);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(ds_full);   // the warp's writes are ordered before lane 0's arrival
     }
     bool fin = ok && mbar_wait(dq_full, 0, abort_flag);
     fin = __all_sync(0xffffffffu, fin);
     if (fin) {
       tc_fence_after();
       T* orow = reinterpret_cast<T*>(p.dq) + (int64_t)b * p.q_bs + (int64_t)h * p.q_hs + (int64_t)qi * p.q_ss;
-#pragma unroll 1
-      for (int c = 2 * ch; c < 2 * ch + 2; ++c) {
+      {
+        const int c = ch;
         uint32_t r[32];
         tmem_ld32(lane_addr + 384 + c * 32, r);
         tmem_ld_wait();
@@ -626,8 +632,8 @@ attn_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   if (threadIdx.x == 0) {
     *abort_flag = 0;
     for (int i = 0; i < 12; ++i) mbar_init(bar0 + 8u * i, 1);
-    mbar_init(pds_full, kComputeThreads);
-    mbar_init(stat_bar, kComputeThreads);
+    mbar_init(pds_full, kComputeThreads / 32);    // one arrival per compute warp
+    mbar_init(stat_bar, kComputeThreads / 32);
     fence_barrier_init();
     prefetch_tmap(&tmQ); prefetch_tmap(&tmK); prefetch_tmap(&tmV); prefetch_tmap(&tmDO);
   }
@@ -715,13 +721,12 @@ attn_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       const int i = first + it % per_head;
       float* st = stat + (it & 1) * 2 * QSUB;
       if (tid < 128) st[tid] = nxt;
-      mbar_arrive(stat_bar);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(stat_bar);   // the warp's writes are ordered before lane 0's arrival
       if (!mbar_wait(stat_bar, it & 1u, abort_flag)) ok = false;
       // the next item's values travel from global memory while this item is processed
       if (it + 1 < total && tid < 128) nxt = load_stat(it + 1);
       if (ok && !mbar_wait(sdp_full(it & 1), (it >> 1) & 1u, abort_flag)) ok = false;
-      // P^T / dS^T of the previous item must have been consumed before they are overwritten
-      if (ok && !mbar_wait(pds_empty, (it & 1u) ^ 1u, abort_flag)) ok = false;
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
@@ -750,12 +755,19 @@ attn_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             dsv[e] = keep ? pr * (__uint_as_float(rp[e]) - st[QSUB + col]) : 0.f;
           }
         }
-        store_swizzled32<T>(pt_ptr, row, c * 32, pv);
-        store_swizzled32<T>(dst_ptr, row, c * 32, dsv);
+        // P^T / dS^T of the previous item must have been consumed before they are overwritten; waiting only here
+        // lets this item's exponentials run under the previous item's dV / dK products
+        if (!mbar_wait(pds_empty, (it & 1u) ^ 1u, abort_flag)) ok = false;
+        ok = __all_sync(0xffffffffu, ok);
+        if (ok) {
+          store_swizzled32<T>(pt_ptr, row, c * 32, pv);
+          store_swizzled32<T>(dst_ptr, row, c * 32, dsv);
+        }
       }
       tc_fence_before();
       fence_proxy_async_smem();
-      mbar_arrive(pds_full);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(pds_full);   // the warp's writes are ordered before lane 0's arrival
     }
     bool fin = ok && mbar_wait(acc_full, 0, abort_flag);
     fin = __all_sync(0xffffffffu, fin);
@@ -937,7 +949,7 @@ int attn_bwd_tc(const void* q, const void* k, const void* v, const void* dout, c
     if (p.gsplit > 1)
       attn_dkdv_reduce_kernel<__nv_bfloat16><<<red_grid, 256, 0, st>>>(partials, (__nv_bfloat16*)dk, (__nv_bfloat16*)dv, p.gsplit, kv_rows,
                                                                      (int)Hkv, (int)S, sk.ss, sk.hs, sk.bs, scale);
-    attn_dq_tc_kernel<__nv_bfloat16><<<gq, kAttnThreads, kDqSmem, st>>>(tmQ, tmK, tmV, tmDO, p);
+    attn_dq_tc_kernel<__nv_bfloat16><<<gq, kDqThreads, kDqSmem, st>>>(tmQ, tmK, tmV, tmDO, p);
   } else {
     static bool c1 = false, c2 = false;
     if ((rc = configure_smem(attn_dq_tc_kernel<__half>, kDqSmem, &c1)) != Q3_OK) return rc;
@@ -946,7 +958,7 @@ int attn_bwd_tc(const void* q, const void* k, const void* v, const void* dout, c
     if (p.gsplit > 1)
       attn_dkdv_reduce_kernel<__half><<<red_grid, 256, 0, st>>>(partials, (__half*)dk, (__half*)dv, p.gsplit, kv_rows, (int)Hkv, (int)S,
                                                               sk.ss, sk.hs, sk.bs, scale);
-    attn_dq_tc_kernel<__half><<<gq, kAttnThreads, kDqSmem, st>>>(tmQ, tmK, tmV, tmDO, p);
+    attn_dq_tc_kernel<__half><<<gq, kDqThreads, kDqSmem, st>>>(tmQ, tmK, tmV, tmDO, p);
   }
   return launch_status();
 }
