@@ -41,6 +41,13 @@ constexpr int kComputeThreads = 256;
 // the score tile per thread): twice the warps to hide tensor-memory load latency, half the registers per thread.
 constexpr int kDqComputeThreads = 512;
 constexpr int kDqThreads = 64 + kDqComputeThreads;
+// The forward kernel also runs four threads per row (32 score and 32 output columns each); the row maximum and the
+// row sum cross the four through shared memory and a 128-thread hardware barrier.
+constexpr int kFwdComputeThreads = 512;
+constexpr int kFwdThreads = 64 + kFwdComputeThreads;
+// Same for the dK/dV kernel: four threads per key row, 16 of the 64 query columns of an item each.
+constexpr int kDkdvComputeThreads = 512;
+constexpr int kDkdvThreads = 64 + kDkdvComputeThreads;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
 
@@ -88,6 +95,22 @@ __device__ __forceinline__ void store_swizzled32(uint8_t* tile, int row, int c0,
   }
 }
 
+// Same for 16 consecutive columns (two 16-byte chunks).
+template <typename T>
+__device__ __forceinline__ void store_swizzled16(uint8_t* tile, int row, int c0, const float (&v)[16]) {
+  uint8_t* half = tile + (c0 >> 6) * HALF_BYTES + row * 128;
+  const int chunk0 = (c0 & 63) >> 3;
+#pragma unroll
+  for (int j = 0; j < 2; ++j) {
+    uint4 w;
+    w.x = pack2<T>(v[8 * j + 0], v[8 * j + 1]);
+    w.y = pack2<T>(v[8 * j + 2], v[8 * j + 3]);
+    w.z = pack2<T>(v[8 * j + 4], v[8 * j + 5]);
+    w.w = pack2<T>(v[8 * j + 6], v[8 * j + 7]);
+    *reinterpret_cast<uint4*>(half + (((chunk0 + j) ^ (row & 7)) << 4)) = w;
+  }
+}
+
 // 8 MMAs (k = 16 each) covering a contraction of 128 over two 64-wide halves, both operands K-major.
 __device__ __forceinline__ void mma_kk_128(uint32_t d_tmem, uint32_t a_smem, uint32_t b_smem, uint32_t idesc,
                                            bool accumulate_first) {
@@ -110,14 +133,14 @@ __device__ __forceinline__ void mma_kmn(uint32_t d_tmem, uint32_t a_smem, uint32
   }
 }
 
-// Barrier over the two compute warps that share a TMEM lane quarter (64 threads, hardware barrier 1 + quarter),
-// ANDing a predicate over them. Both warps must reach every call: no early exit between two calls.
-__device__ __forceinline__ bool pair_all(int quarter, bool pred) {
+// Barrier over the four compute warps that share a TMEM lane quarter (128 threads, hardware barrier 1 + quarter),
+// ANDing a predicate over them. All four warps must reach every call: no early exit between two calls.
+__device__ __forceinline__ bool row_group_all(int quarter, bool pred) {
   int r;
   asm volatile(
       "{\n\t.reg .pred p, q;\n\t"
       "setp.ne.s32 q, %1, 0;\n\t"
-      "bar.red.and.pred p, %2, 64, q;\n\t"
+      "bar.red.and.pred p, %2, 128, q;\n\t"
       "selp.s32 %0, 1, 0, p;\n\t}"
       : "=r"(r)
       : "r"((int)pred), "r"(quarter + 1)
@@ -126,7 +149,7 @@ __device__ __forceinline__ bool pair_all(int quarter, bool pred) {
 }
 
 template <typename T>
-__global__ void __launch_bounds__(kAttnThreads, 1)
+__global__ void __maxnreg__(112)   // 576 threads x 112 registers = one CTA per SM (shared memory allows no more)
 attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                    const __grid_constant__ CUtensorMap tmV, const AttnParams p) {
   extern __shared__ uint8_t smem_raw[];
@@ -147,7 +170,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   const uint32_t p_full = bar0 + 8u * 13, done_bar = bar0 + 8u * 14;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 15);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  float* xmax = reinterpret_cast<float*>(bars + 18);   // [2 tiles in flight + 1][2 column halves][128 rows]
+  float* xmax = reinterpret_cast<float*>(bars + 18);   // [2 tiles in flight + 1][4 column quarters][128 rows]
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int nq = (p.S + TILE - 1) / TILE;
@@ -161,7 +184,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   if (threadIdx.x == 0) {
     *abort_flag = 0;
     for (int i = 0; i < 13; ++i) mbar_init(bar0 + 8u * i, 1);
-    mbar_init(p_full, kComputeThreads / 32);      // one arrival per compute warp
+    mbar_init(p_full, kFwdComputeThreads / 32);   // one arrival per compute warp
     mbar_init(done_bar, 1);
     fence_barrier_init();
     prefetch_tmap(&tmQ); prefetch_tmap(&tmK); prefetch_tmap(&tmV);
@@ -229,15 +252,15 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     }
   } else {
     // ------------------------------------------------------------------ softmax / accumulate / epilogue
-    // Two threads per query row: warps 2-5 take score / output columns 0..63, warps 6-9 columns 64..127.
-    // The halves exchange their row maximum through shared memory once per key tile.
+    // Four threads per query row: warps 2-5 take score / output columns 0..31, warps 6-9 columns 32..63, and so
+    // on. The quarters exchange their row maximum through shared memory once per key tile.
     const int qd = warp & 3;                 // TMEM lane quarter of this warp
-    const int ch = (warp - 2) >> 2;          // column half
+    const int ch = (warp - 2) >> 2;          // column quarter
     const int row = qd * 32 + lane;          // query row within the tile
     const uint32_t lane_addr = tmem + ((uint32_t)(qd * 32) << 16);
-    float o[64];
+    float o[32];
 #pragma unroll
-    for (int i = 0; i < 64; ++i) o[i] = 0.f;
+    for (int i = 0; i < 32; ++i) o[i] = 0.f;
     float m = -CUDART_INF_F, l = 0.f, alpha_prev = 1.f;
     bool ok = true;
     for (int j = 0; j < ntiles; ++j) {
@@ -245,115 +268,96 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       if (!mbar_wait(s_full(s), (j >> 1) & 1u, abort_flag)) ok = false;
       ok = __all_sync(0xffffffffu, ok);
       tc_fence_after();
-      const uint32_t s_addr = lane_addr + s * 128 + ch * 64;
+      const uint32_t s_addr = lane_addr + s * 128 + ch * 32;
       const bool diag = (j == ntiles - 1);
-      // pass 1: maximum of this thread's 64 raw scores
+      // pass 1: maximum of this thread's 32 raw scores (kept in registers for pass 2)
+      uint32_t r[32];
       float mx = -CUDART_INF_F;
       if (ok) {
-#pragma unroll 1
-        for (int c = 0; c < 2; ++c) {
-          uint32_t r[32];
-          tmem_ld32(s_addr + c * 32, r);
-          tmem_ld_wait();
-          if (!diag) {   // all but the last key tile of a query tile: no causal mask, no per-element compare
+        tmem_ld32(s_addr, r);
+        tmem_ld_wait();
+        if (!diag) {   // all but the last key tile of a query tile: no causal mask, no per-element compare
 #pragma unroll
-            for (int i = 0; i < 32; i += 2)
-              mx = fmaxf(mx, fmaxf(__uint_as_float(r[i]), __uint_as_float(r[i + 1])));
-          } else {
+          for (int i = 0; i < 32; i += 2) mx = fmaxf(mx, fmaxf(__uint_as_float(r[i]), __uint_as_float(r[i + 1])));
+        } else {
 #pragma unroll
-            for (int i = 0; i < 32; ++i)
-              if (ch * 64 + c * 32 + i <= row) mx = fmaxf(mx, __uint_as_float(r[i]));
-          }
+          for (int i = 0; i < 32; ++i)
+            if (ch * 32 + i <= row) mx = fmaxf(mx, __uint_as_float(r[i]));
         }
       }
-      xmax[(j & 1) * 256 + ch * 128 + row] = mx;
-      // the partner thread (same row, other column half) sits in the warp four above / below: a 64-thread hardware
-      // barrier publishes both maxima and makes the keep-going decision uniform over the pair
-      ok = pair_all(qd, ok);
+      float* xm = xmax + (j & 1) * 512;
+      xm[ch * 128 + row] = mx;
+      // the partner threads (same row, other column quarters) sit in the warps 4, 8 and 12 away: a 128-thread hardware
+      // barrier publishes the four maxima and makes the keep-going decision uniform over them
+      ok = row_group_all(qd, ok);
       if (!ok) break;
-      mx = fmaxf(m, fmaxf(mx, xmax[(j & 1) * 256 + (ch ^ 1) * 128 + row]));
+      mx = fmaxf(fmaxf(m, xm[row]), fmaxf(fmaxf(xm[128 + row], xm[256 + row]), xm[384 + row]));
       const float mc = mx * p.scale_log2;
       const float alpha = fast_exp2(m * p.scale_log2 - mc);  // m = -inf on the first tile -> 0
+      // pass 2: probabilities from the scores still in registers, partial row sum
+      float pv[32];
+      float sum = 0.f;
+      if (!diag) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          pv[i] = fast_exp2(fmaf(__uint_as_float(r[i]), p.scale_log2, -mc));
+          sum += pv[i];
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const float e = fast_exp2(fmaf(__uint_as_float(r[i]), p.scale_log2, -mc));
+          pv[i] = (ch * 32 + i <= row) ? e : 0.f;
+          sum += pv[i];
+        }
+      }
       // the P buffer and O_{j-1} are free / ready once the previous PV product has completed
       if (j > 0 && !mbar_wait(o_full((j - 1) & 1), ((j - 1) >> 1) & 1u, abort_flag)) ok = false;
       ok = __all_sync(0xffffffffu, ok);
       tc_fence_after();
-      // pass 2: probabilities -> shared memory (bf16), partial row sum
-      float sum = 0.f;
-      if (ok) {
-#pragma unroll 1
-        for (int c = 0; c < 2; ++c) {
-          uint32_t r[32];
-          float pv[32];
-          tmem_ld32(s_addr + c * 32, r);
-          tmem_ld_wait();
-          if (!diag) {
-#pragma unroll
-            for (int i = 0; i < 32; ++i) {
-              pv[i] = fast_exp2(fmaf(__uint_as_float(r[i]), p.scale_log2, -mc));
-              sum += pv[i];
-            }
-          } else {
-#pragma unroll
-            for (int i = 0; i < 32; ++i) {
-              const float e = fast_exp2(fmaf(__uint_as_float(r[i]), p.scale_log2, -mc));
-              pv[i] = (ch * 64 + c * 32 + i <= row) ? e : 0.f;
-              sum += pv[i];
-            }
-          }
-          store_swizzled32<T>(p_ptr, row, ch * 64 + c * 32, pv);
-        }
-      }
+      if (ok) store_swizzled32<T>(p_ptr, row, ch * 32, pv);
       l = l * alpha + sum;
       m = mx;
       tc_fence_before();
       fence_proxy_async_smem();   // generic-proxy writes of P must be visible to the tensor core
       __syncwarp();
       if (lane == 0) mbar_arrive(p_full);   // the warp's writes are ordered before lane 0's arrival
-      // fold this thread's half of O_{j-1} into registers while the tensor core computes S_{j+1} and P_j V_j
+      // fold this thread's quarter of O_{j-1} into registers while the tensor core computes S_{j+1} and P_j V_j
       if (j > 0 && ok) {
-        const uint32_t o_addr = lane_addr + 256 + ((j - 1) & 1) * 128 + ch * 64;
+        uint32_t ro[32];
+        tmem_ld32(lane_addr + 256 + ((j - 1) & 1) * 128 + ch * 32, ro);
+        tmem_ld_wait();
 #pragma unroll
-        for (int c = 0; c < 2; ++c) {
-          uint32_t r[32];
-          tmem_ld32(o_addr + c * 32, r);
-          tmem_ld_wait();
-#pragma unroll
-          for (int i = 0; i < 32; ++i) o[c * 32 + i] = fmaf(o[c * 32 + i], alpha_prev, __uint_as_float(r[i]));
-        }
+        for (int i = 0; i < 32; ++i) o[i] = fmaf(o[i], alpha_prev, __uint_as_float(ro[i]));
       }
       alpha_prev = alpha;
     }
-    // combine the two partial row sums (own slot of the exchange buffer, one more phase of the barrier)
-    xmax[512 + ch * 128 + row] = l;
-    ok = pair_all(qd, ok);
-    if (ok) l += xmax[512 + (ch ^ 1) * 128 + row];
+    // combine the four partial row sums (own slot of the exchange buffer, one more round of the barrier)
+    xmax[1024 + ch * 128 + row] = l;
+    ok = row_group_all(qd, ok);
+    if (ok) l = (xmax[1024 + row] + xmax[1024 + 128 + row]) + (xmax[1024 + 256 + row] + xmax[1024 + 384 + row]);
     bool fin = ok && mbar_wait(o_full((ntiles - 1) & 1), ((ntiles - 1) >> 1) & 1u, abort_flag);
     fin = __all_sync(0xffffffffu, fin);
     if (fin) {
       tc_fence_after();
-      const uint32_t o_addr = lane_addr + 256 + ((ntiles - 1) & 1) * 128 + ch * 64;
       const float inv = 1.f / l;
       const int qi = qt * TILE + row;
-      T* orow = reinterpret_cast<T*>(p.out) + (int64_t)b * p.q_bs + (int64_t)h * p.q_hs + (int64_t)qi * p.q_ss + ch * 64;
+      T* orow = reinterpret_cast<T*>(p.out) + (int64_t)b * p.q_bs + (int64_t)h * p.q_hs + (int64_t)qi * p.q_ss + ch * 32;
+      uint32_t ro[32];
+      tmem_ld32(lane_addr + 256 + ((ntiles - 1) & 1) * 128 + ch * 32, ro);
+      tmem_ld_wait();
+      if (qi < p.S) {
 #pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        uint32_t r[32];
-        tmem_ld32(o_addr + c * 32, r);
-        tmem_ld_wait();
-        if (qi < p.S) {
+        for (int g = 0; g < 4; ++g) {
+          uint4 w;
+          uint32_t* wp = reinterpret_cast<uint32_t*>(&w);
 #pragma unroll
-          for (int g = 0; g < 4; ++g) {
-            uint4 w;
-            uint32_t* wp = reinterpret_cast<uint32_t*>(&w);
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              const int i = g * 8 + e * 2;
-              wp[e] = pack2<T>(fmaf(o[c * 32 + i], alpha_prev, __uint_as_float(r[i])) * inv,
-                               fmaf(o[c * 32 + i + 1], alpha_prev, __uint_as_float(r[i + 1])) * inv);
-            }
-            *reinterpret_cast<uint4*>(orow + c * 32 + g * 8) = w;
+          for (int e = 0; e < 4; ++e) {
+            const int i = g * 8 + e * 2;
+            wp[e] = pack2<T>(fmaf(o[i], alpha_prev, __uint_as_float(ro[i])) * inv,
+                             fmaf(o[i + 1], alpha_prev, __uint_as_float(ro[i + 1])) * inv);
           }
+          *reinterpret_cast<uint4*>(orow + g * 8) = w;
         }
       }
       if (qi < p.S && ch == 0) p.lse[(int64_t)bh * p.S + qi] = (m * p.scale_log2 + log2f(l)) * kLn2;
@@ -365,7 +369,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   if (threadIdx.x == 0 && *abort_flag) flag_status(p.status, Q3_STATUS_WAIT_TIMEOUT);
 }
 
-constexpr int kFwdSmem = 6 * TILE_BYTES + 1024 + 256 + 3 * 2 * 128 * 4;
+constexpr int kFwdSmem = 6 * TILE_BYTES + 1024 + 256 + 3 * 4 * 128 * 4;
 
 // ====================================================================================== backward
 struct AttnBwdParams {
@@ -588,7 +592,7 @@ constexpr int kDqSmem = 7 * TILE_BYTES + 1024 + 256;
 
 // ------------------------------------------------------------------ dK/dV: one CTA per 128-key tile of (b, kv head)
 // Work items: (query head g of the group) x (64-query sub-tile i >= 2*kt). Shared memory:
-//   [K 32K][V 32K] resident, 3 stages of {Q_i 16K, dO_i 16K}, [P^T 16K][dS^T 16K], lse/delta 2 x 64 floats.
+//   [K 32K][V 32K] resident, 3 stages of {Q_i 16K, dO_i 16K}, 2 x {[P^T 16K][dS^T 16K]}, lse/delta 2 x 2 x 64 floats.
 // TMEM columns: S^T buffers 0..63 / 64..127, dP^T buffers 128..191 / 192..255, dK 256..383, dV 384..511.
 constexpr int QSUB = 64;
 constexpr int SUB_HALF = QSUB * 128;        // 8 KB: one 64-column half of a 64-row tile
@@ -596,7 +600,7 @@ constexpr int SUB_BYTES = 2 * SUB_HALF;     // 16 KB
 constexpr int KV_STAGES = 3;
 
 template <typename T>
-__global__ void __launch_bounds__(kAttnThreads, 1)
+__global__ void __launch_bounds__(kDkdvThreads, 1)
 attn_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                     const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
                     const AttnBwdParams p) {
@@ -604,20 +608,22 @@ attn_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem = smem_raw + (base - smem_u32(smem_raw));
   const uint32_t k_s = base, v_s = base + TILE_BYTES, st_s = base + 2 * TILE_BYTES;
+  // two {P^T, dS^T} buffers: item it uses buffer it & 1, so the exponentials and stores of one item run while the
+  // tensor core still reads the previous item's buffer
   const uint32_t pt_off = 2 * TILE_BYTES + KV_STAGES * 2 * SUB_BYTES;
-  const uint32_t pt_s = base + pt_off, dst_s = pt_s + SUB_BYTES;
-  uint8_t* pt_ptr = smem + pt_off;
-  uint8_t* dst_ptr = pt_ptr + SUB_BYTES;
-  float* stat = reinterpret_cast<float*>(dst_ptr + SUB_BYTES);   // [2 items in flight][lse*log2e 64 | delta 64]
+  const uint32_t pds_s = base + pt_off;
+  uint8_t* pds_ptr = smem + pt_off;
+  float* stat = reinterpret_cast<float*>(pds_ptr + 4 * SUB_BYTES);   // [2 items in flight][lse*log2e 64 | delta 64]
   uint64_t* bars = reinterpret_cast<uint64_t*>(stat + 4 * QSUB);
   const uint32_t bar0 = smem_u32(bars);
   const uint32_t kv_full = bar0;
   auto st_full = [&](int s) { return bar0 + 8u * (1 + s); };
   auto st_empty = [&](int s) { return bar0 + 8u * (4 + s); };
   auto sdp_full = [&](int s) { return bar0 + 8u * (7 + s); };
-  const uint32_t pds_empty = bar0 + 8u * 9, acc_full = bar0 + 8u * 10, done_bar = bar0 + 8u * 11,
-                 pds_full = bar0 + 8u * 12, stat_bar = bar0 + 8u * 13;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 14);
+  const uint32_t acc_full = bar0 + 8u * 10, done_bar = bar0 + 8u * 11, stat_bar = bar0 + 8u * 13;
+  auto pds_empty = [&](int b2) { return bar0 + 8u * (b2 ? 14 : 9); };    // count 1 (tcgen05.commit)
+  auto pds_full = [&](int b2) { return bar0 + 8u * (b2 ? 15 : 12); };    // count = compute warps
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -632,8 +638,10 @@ attn_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   if (threadIdx.x == 0) {
     *abort_flag = 0;
     for (int i = 0; i < 12; ++i) mbar_init(bar0 + 8u * i, 1);
-    mbar_init(pds_full, kComputeThreads / 32);    // one arrival per compute warp
-    mbar_init(stat_bar, kComputeThreads / 32);
+    mbar_init(pds_full(0), kDkdvComputeThreads / 32);    // one arrival per compute warp
+    mbar_init(pds_full(1), kDkdvComputeThreads / 32);
+    mbar_init(pds_empty(1), 1);
+    mbar_init(stat_bar, kDkdvComputeThreads / 32);
     fence_barrier_init();
     prefetch_tmap(&tmQ); prefetch_tmap(&tmK); prefetch_tmap(&tmV); prefetch_tmap(&tmDO);
   }
@@ -689,22 +697,23 @@ attn_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           mma_kk(tmem + 128 + buf * 64, v_s, HALF_BYTES, st1 + SUB_BYTES, SUB_HALF, p.idesc_kk64, 8, false);
           mma_commit(sdp_full(buf));
         }
-        if (!mbar_wait(pds_full, it & 1u, abort_flag)) { ok = false; break; }
+        if (!mbar_wait(pds_full(it & 1), (it >> 1) & 1u, abort_flag)) { ok = false; break; }
         tc_fence_after();
         const uint32_t st0 = st_s + s * 2 * SUB_BYTES;
+        const uint32_t pt_s = pds_s + (it & 1) * 2 * SUB_BYTES, dst_s = pt_s + SUB_BYTES;
         mma_kmn2(tmem + 384, pt_s, 0, st0 + SUB_BYTES, SUB_HALF, p.idesc_kmn, 4, it > 0);   // dV += P^T dO
         mma_kmn2(tmem + 256, dst_s, 0, st0, SUB_HALF, p.idesc_kmn, 4, it > 0);             // dK += dS^T Q
         mma_commit(st_empty(s));
-        mma_commit(pds_empty);
+        mma_commit(pds_empty(it & 1));
       }
       if (ok) mma_commit(acc_full);
       mma_commit(done_bar);
       mbar_wait_drain(done_bar, 0);
     }
   } else {
-    // two threads per key row: warps 2-5 take query columns 0..31 of each 64-query sub-tile, warps 6-9 32..63
+    // four threads per key row: warps 2-5 take query columns 0..15 of each 64-query sub-tile, 6-9 16..31, and so on
     const int qd = warp & 3, ch = (warp - 2) >> 2, row = qd * 32 + lane;   // key row within the tile
-    const int tid = threadIdx.x - 64;                                      // 0..255 among the compute threads
+    const int tid = threadIdx.x - 64;                                      // 0..511 among the compute threads
     const uint32_t lane_addr = tmem + ((uint32_t)(qd * 32) << 16);
     const int kj = kt * TILE + row;
     // lse / delta of the 64 queries of an item: threads 0..63 fetch lse, 64..127 delta
@@ -732,42 +741,43 @@ attn_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       tc_fence_after();
       const bool diag = (i * QSUB < kt * TILE + TILE);   // sub-tile overlaps the diagonal block
       {
-        const int c = ch;
-        uint32_t rs[32], rp[32];
-        float pv[32], dsv[32];
-        tmem_ld32(lane_addr + (it & 1) * 64 + c * 32, rs);
-        tmem_ld32(lane_addr + 128 + (it & 1) * 64 + c * 32, rp);
+        const int c0 = ch * 16;   // this thread's 16 query columns of the item
+        uint32_t rs[16], rp[16];
+        float pv[16], dsv[16];
+        tmem_ld16(lane_addr + (it & 1) * 64 + c0, rs);
+        tmem_ld16(lane_addr + 128 + (it & 1) * 64 + c0, rp);
         tmem_ld_wait();
         if (!diag && (i + 1) * QSUB <= p.S) {   // sub-tile strictly below the diagonal block and inside the sequence
 #pragma unroll
-          for (int e = 0; e < 32; ++e) {
-            const int col = c * 32 + e;
+          for (int e = 0; e < 16; ++e) {
+            const int col = c0 + e;
             pv[e] = fast_exp2(fmaf(__uint_as_float(rs[e]), p.scale_log2, -st[col]));
             dsv[e] = pv[e] * (__uint_as_float(rp[e]) - st[QSUB + col]);
           }
         } else {
 #pragma unroll
-          for (int e = 0; e < 32; ++e) {
-            const int col = c * 32 + e, qi = i * QSUB + col;
+          for (int e = 0; e < 16; ++e) {
+            const int col = c0 + e, qi = i * QSUB + col;
             const float pr = fast_exp2(fmaf(__uint_as_float(rs[e]), p.scale_log2, -st[col]));
             const bool keep = qi < p.S && (!diag || kj <= qi);
             pv[e] = keep ? pr : 0.f;
             dsv[e] = keep ? pr * (__uint_as_float(rp[e]) - st[QSUB + col]) : 0.f;
           }
         }
-        // P^T / dS^T of the previous item must have been consumed before they are overwritten; waiting only here
-        // lets this item's exponentials run under the previous item's dV / dK products
-        if (!mbar_wait(pds_empty, (it & 1u) ^ 1u, abort_flag)) ok = false;
+        // P^T / dS^T of the item before last must have been consumed before its buffer is overwritten; waiting
+        // only here lets this item's exponentials run under the previous items' dV / dK products
+        if (!mbar_wait(pds_empty(it & 1), ((it >> 1) & 1u) ^ 1u, abort_flag)) ok = false;
         ok = __all_sync(0xffffffffu, ok);
         if (ok) {
-          store_swizzled32<T>(pt_ptr, row, c * 32, pv);
-          store_swizzled32<T>(dst_ptr, row, c * 32, dsv);
+          uint8_t* pt_ptr = pds_ptr + (it & 1) * 2 * SUB_BYTES;
+          store_swizzled16<T>(pt_ptr, row, c0, pv);
+          store_swizzled16<T>(pt_ptr + SUB_BYTES, row, c0, dsv);
         }
       }
       tc_fence_before();
       fence_proxy_async_smem();
       __syncwarp();
-      if (lane == 0) mbar_arrive(pds_full);   // the warp's writes are ordered before lane 0's arrival
+      if (lane == 0) mbar_arrive(pds_full(it & 1));   // the warp's writes are ordered before lane 0's arrival
     }
     bool fin = ok && mbar_wait(acc_full, 0, abort_flag);
     fin = __all_sync(0xffffffffu, fin);
@@ -778,8 +788,8 @@ attn_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         const int64_t rows = (int64_t)(gridDim.x / gs) * p.S;
         float* pk = p.part + (((int64_t)zsplit * 2 + 0) * rows + (int64_t)bk * p.S + kj) * AD;
         float* pvp = p.part + (((int64_t)zsplit * 2 + 1) * rows + (int64_t)bk * p.S + kj) * AD;
-#pragma unroll 1
-        for (int c = 2 * ch; c < 2 * ch + 2; ++c) {
+        {
+          const int c = ch;
           uint32_t rk[32], rv[32];
           tmem_ld32(lane_addr + 256 + c * 32, rk);
           tmem_ld32(lane_addr + 384 + c * 32, rv);
@@ -795,8 +805,8 @@ attn_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       } else {
         T* krow = reinterpret_cast<T*>(p.dk) + (int64_t)b * p.k_bs + (int64_t)kvh * p.k_hs + (int64_t)kj * p.k_ss;
         T* vrow = reinterpret_cast<T*>(p.dv) + (int64_t)b * p.k_bs + (int64_t)kvh * p.k_hs + (int64_t)kj * p.k_ss;
-#pragma unroll 1
-        for (int c = 2 * ch; c < 2 * ch + 2; ++c) {
+        {
+          const int c = ch;
           uint32_t rk[32], rv[32];
           tmem_ld32(lane_addr + 256 + c * 32, rk);
           tmem_ld32(lane_addr + 384 + c * 32, rv);
@@ -825,7 +835,8 @@ attn_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem, 512); }
   if (threadIdx.x == 0 && *abort_flag) flag_status(p.status, Q3_STATUS_WAIT_TIMEOUT);
 }
-constexpr int kDkdvSmem = 2 * TILE_BYTES + KV_STAGES * 2 * SUB_BYTES + 2 * SUB_BYTES + 4 * QSUB * 4 + 1024 + 256;
+constexpr int kDkdvSmem = 2 * TILE_BYTES + KV_STAGES * 2 * SUB_BYTES + 4 * SUB_BYTES + 4 * QSUB * 4 + 1024 + 256;
+static_assert(kDkdvSmem <= 227 * 1024, "dK/dV kernel shared memory exceeds the per-CTA limit");
 
 // Sum the per-query-head fp32 partials of dK / dV in head order, scale dK, round once, store with strides.
 template <typename T>
@@ -904,11 +915,11 @@ int attn_fwd_tc(const void* q, const void* k, const void* v, void* out, float* l
   if (bf16) {
     static bool cfg = false;
     if ((rc = configure_smem(attn_fwd_tc_kernel<__nv_bfloat16>, kFwdSmem, &cfg)) != Q3_OK) return rc;
-    attn_fwd_tc_kernel<__nv_bfloat16><<<grid, kAttnThreads, kFwdSmem, st>>>(tmQ, tmK, tmV, p);
+    attn_fwd_tc_kernel<__nv_bfloat16><<<grid, kFwdThreads, kFwdSmem, st>>>(tmQ, tmK, tmV, p);
   } else {
     static bool cfg = false;
     if ((rc = configure_smem(attn_fwd_tc_kernel<__half>, kFwdSmem, &cfg)) != Q3_OK) return rc;
-    attn_fwd_tc_kernel<__half><<<grid, kAttnThreads, kFwdSmem, st>>>(tmQ, tmK, tmV, p);
+    attn_fwd_tc_kernel<__half><<<grid, kFwdThreads, kFwdSmem, st>>>(tmQ, tmK, tmV, p);
   }
   return launch_status();
 }
@@ -945,7 +956,7 @@ int attn_bwd_tc(const void* q, const void* k, const void* v, const void* dout, c
     static bool c1 = false, c2 = false;
     if ((rc = configure_smem(attn_dq_tc_kernel<__nv_bfloat16>, kDqSmem, &c1)) != Q3_OK) return rc;
     if ((rc = configure_smem(attn_dkdv_tc_kernel<__nv_bfloat16>, kDkdvSmem, &c2)) != Q3_OK) return rc;
-    attn_dkdv_tc_kernel<__nv_bfloat16><<<gk, kAttnThreads, kDkdvSmem, st>>>(tmQs, tmK, tmV, tmDOs, p);
+    attn_dkdv_tc_kernel<__nv_bfloat16><<<gk, kDkdvThreads, kDkdvSmem, st>>>(tmQs, tmK, tmV, tmDOs, p);
     if (p.gsplit > 1)
       attn_dkdv_reduce_kernel<__nv_bfloat16><<<red_grid, 256, 0, st>>>(partials, (__nv_bfloat16*)dk, (__nv_bfloat16*)dv, p.gsplit, kv_rows,
                                                                      (int)Hkv, (int)S, sk.ss, sk.hs, sk.bs, scale);
@@ -954,7 +965,7 @@ int attn_bwd_tc(const void* q, const void* k, const void* v, const void* dout, c
     static bool c1 = false, c2 = false;
     if ((rc = configure_smem(attn_dq_tc_kernel<__half>, kDqSmem, &c1)) != Q3_OK) return rc;
     if ((rc = configure_smem(attn_dkdv_tc_kernel<__half>, kDkdvSmem, &c2)) != Q3_OK) return rc;
-    attn_dkdv_tc_kernel<__half><<<gk, kAttnThreads, kDkdvSmem, st>>>(tmQs, tmK, tmV, tmDOs, p);
+    attn_dkdv_tc_kernel<__half><<<gk, kDkdvThreads, kDkdvSmem, st>>>(tmQs, tmK, tmV, tmDOs, p);
     if (p.gsplit > 1)
       attn_dkdv_reduce_kernel<__half><<<red_grid, 256, 0, st>>>(partials, (__half*)dk, (__half*)dv, p.gsplit, kv_rows, (int)Hkv, (int)S,
                                                               sk.ss, sk.hs, sk.bs, scale);
