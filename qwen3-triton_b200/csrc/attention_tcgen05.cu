@@ -35,8 +35,8 @@ constexpr int AD = 128;           // head dim
 constexpr int TILE = 128;         // query rows / keys per tile
 constexpr int HALF_BYTES = TILE * 128;       // one 64-column half of a 128-row tile (16 KB)
 constexpr int TILE_BYTES = 2 * HALF_BYTES;   // 32 KB
-constexpr int kAttnThreads = 320;   // warp 0 TMA, warp 1 MMA, warps 2..9 compute (two threads per tile row)
-constexpr int kComputeThreads = 256;
+constexpr int kAttnThreads = 320;   // dK/dV kernel: warp 0 TMA, warp 1 MMA, warps 2..9 compute (two threads per tile row)
+constexpr int kComputeThreads = 256;   // of the dK/dV kernel
 // The dQ kernel has no reduction along a row, so its rows are cut four ways (16 compute warps, one 32-column chunk of
 // the score tile per thread): twice the warps to hide tensor-memory load latency, half the registers per thread.
 constexpr int kDqComputeThreads = 512;
@@ -45,9 +45,6 @@ constexpr int kDqThreads = 64 + kDqComputeThreads;
 // row sum cross the four through shared memory and a 128-thread hardware barrier.
 constexpr int kFwdComputeThreads = 512;
 constexpr int kFwdThreads = 64 + kFwdComputeThreads;
-// Same for the dK/dV kernel: four threads per key row, 16 of the 64 query columns of an item each.
-constexpr int kDkdvComputeThreads = 512;
-constexpr int kDkdvThreads = 64 + kDkdvComputeThreads;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
 
@@ -95,22 +92,6 @@ __device__ __forceinline__ void store_swizzled32(uint8_t* tile, int row, int c0,
   }
 }
 
-// Same for 16 consecutive columns (two 16-byte chunks).
-template <typename T>
-__device__ __forceinline__ void store_swizzled16(uint8_t* tile, int row, int c0, const float (&v)[16]) {
-  uint8_t* half = tile + (c0 >> 6) * HALF_BYTES + row * 128;
-  const int chunk0 = (c0 & 63) >> 3;
-#pragma unroll
-  for (int j = 0; j < 2; ++j) {
-    uint4 w;
-    w.x = pack2<T>(v[8 * j + 0], v[8 * j + 1]);
-    w.y = pack2<T>(v[8 * j + 2], v[8 * j + 3]);
-    w.z = pack2<T>(v[8 * j + 4], v[8 * j + 5]);
-    w.w = pack2<T>(v[8 * j + 6], v[8 * j + 7]);
-    *reinterpret_cast<uint4*>(half + (((chunk0 + j) ^ (row & 7)) << 4)) = w;
-  }
-}
-
 // 8 MMAs (k = 16 each) covering a contraction of 128 over two 64-wide halves, both operands K-major.
 __device__ __forceinline__ void mma_kk_128(uint32_t d_tmem, uint32_t a_smem, uint32_t b_smem, uint32_t idesc,
                                            bool accumulate_first) {
@@ -149,7 +130,7 @@ __device__ __forceinline__ bool row_group_all(int quarter, bool pred) {
 }
 
 template <typename T>
-__global__ void __maxnreg__(112)   // 576 threads x 112 registers = one CTA per SM (shared memory allows no more)
+__global__ void __launch_bounds__(kFwdThreads, 1)   // 18 warps: 5 on one scheduler, whose 16 K registers cap a thread at 96
 attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                    const __grid_constant__ CUtensorMap tmV, const AttnParams p) {
   extern __shared__ uint8_t smem_raw[];
@@ -270,10 +251,11 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       tc_fence_after();
       const uint32_t s_addr = lane_addr + s * 128 + ch * 32;
       const bool diag = (j == ntiles - 1);
-      // pass 1: maximum of this thread's 32 raw scores (kept in registers for pass 2)
-      uint32_t r[32];
+      // pass 1: maximum of this thread's 32 raw scores (re-read from tensor memory for pass 2: keeping them across
+      // the barrier does not fit the 96 registers a thread can have here)
       float mx = -CUDART_INF_F;
       if (ok) {
+        uint32_t r[32];
         tmem_ld32(s_addr, r);
         tmem_ld_wait();
         if (!diag) {   // all but the last key tile of a query tile: no causal mask, no per-element compare
@@ -294,9 +276,12 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       mx = fmaxf(fmaxf(m, xm[row]), fmaxf(fmaxf(xm[128 + row], xm[256 + row]), xm[384 + row]));
       const float mc = mx * p.scale_log2;
       const float alpha = fast_exp2(m * p.scale_log2 - mc);  // m = -inf on the first tile -> 0
-      // pass 2: probabilities from the scores still in registers, partial row sum
+      // pass 2: probabilities, partial row sum
       float pv[32];
       float sum = 0.f;
+      uint32_t r[32];
+      tmem_ld32(s_addr, r);
+      tmem_ld_wait();
       if (!diag) {
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
@@ -592,7 +577,7 @@ constexpr int kDqSmem = 7 * TILE_BYTES + 1024 + 256;
 
 // ------------------------------------------------------------------ dK/dV: one CTA per 128-key tile of (b, kv head)
 // Work items: (query head g of the group) x (64-query sub-tile i >= 2*kt). Shared memory:
-//   [K 32K][V 32K] resident, 3 stages of {Q_i 16K, dO_i 16K}, 2 x {[P^T 16K][dS^T 16K]}, lse/delta 2 x 2 x 64 floats.
+//   [K 32K][V 32K] resident, 3 stages of {Q_i 16K, dO_i 16K}, [P^T 16K][dS^T 16K], lse/delta 2 x 64 floats.
 // TMEM columns: S^T buffers 0..63 / 64..127, dP^T buffers 128..191 / 192..255, dK 256..383, dV 384..511.
 constexpr int QSUB = 64;
 constexpr int SUB_HALF = QSUB * 128;        // 8 KB: one 64-column half of a 64-row tile
@@ -600,7 +585,7 @@ constexpr int SUB_BYTES = 2 * SUB_HALF;     // 16 KB
 constexpr int KV_STAGES = 3;
 
 template <typename T>
-__global__ void __launch_bounds__(kDkdvThreads, 1)
+__global__ void __launch_bounds__(kAttnThreads, 1)
 attn_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                     const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
                     const AttnBwdParams p) {
@@ -608,22 +593,20 @@ attn_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem = smem_raw + (base - smem_u32(smem_raw));
   const uint32_t k_s = base, v_s = base + TILE_BYTES, st_s = base + 2 * TILE_BYTES;
-  // two {P^T, dS^T} buffers: item it uses buffer it & 1, so the exponentials and stores of one item run while the
-  // tensor core still reads the previous item's buffer
   const uint32_t pt_off = 2 * TILE_BYTES + KV_STAGES * 2 * SUB_BYTES;
-  const uint32_t pds_s = base + pt_off;
-  uint8_t* pds_ptr = smem + pt_off;
-  float* stat = reinterpret_cast<float*>(pds_ptr + 4 * SUB_BYTES);   // [2 items in flight][lse*log2e 64 | delta 64]
+  const uint32_t pt_s = base + pt_off, dst_s = pt_s + SUB_BYTES;
+  uint8_t* pt_ptr = smem + pt_off;
+  uint8_t* dst_ptr = pt_ptr + SUB_BYTES;
+  float* stat = reinterpret_cast<float*>(dst_ptr + SUB_BYTES);   // [2 items in flight][lse*log2e 64 | delta 64]
   uint64_t* bars = reinterpret_cast<uint64_t*>(stat + 4 * QSUB);
   const uint32_t bar0 = smem_u32(bars);
   const uint32_t kv_full = bar0;
   auto st_full = [&](int s) { return bar0 + 8u * (1 + s); };
   auto st_empty = [&](int s) { return bar0 + 8u * (4 + s); };
   auto sdp_full = [&](int s) { return bar0 + 8u * (7 + s); };
-  const uint32_t acc_full = bar0 + 8u * 10, done_bar = bar0 + 8u * 11, stat_bar = bar0 + 8u * 13;
-  auto pds_empty = [&](int b2) { return bar0 + 8u * (b2 ? 14 : 9); };    // count 1 (tcgen05.commit)
-  auto pds_full = [&](int b2) { return bar0 + 8u * (b2 ? 15 : 12); };    // count = compute warps
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
+  const uint32_t pds_empty = bar0 + 8u * 9, acc_full = bar0 + 8u * 10, done_bar = bar0 + 8u * 11,
+                 pds_full = bar0 + 8u * 12, stat_bar = bar0 + 8u * 13;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 14);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -638,10 +621,8 @@ attn_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   if (threadIdx.x == 0) {
     *abort_flag = 0;
     for (int i = 0; i < 12; ++i) mbar_init(bar0 + 8u * i, 1);
-    mbar_init(pds_full(0), kDkdvComputeThreads / 32);    // one arrival per compute warp
-    mbar_init(pds_full(1), kDkdvComputeThreads / 32);
-    mbar_init(pds_empty(1), 1);
-    mbar_init(stat_bar, kDkdvComputeThreads / 32);
+    mbar_init(pds_full, kComputeThreads / 32);    // one arrival per compute warp
+    mbar_init(stat_bar, kComputeThreads / 32);
     fence_barrier_init();
     prefetch_tmap(&tmQ); prefetch_tmap(&tmK); prefetch_tmap(&tmV); prefetch_tmap(&tmDO);
   }
@@ -697,23 +678,22 @@ attn_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           mma_kk(tmem + 128 + buf * 64, v_s, HALF_BYTES, st1 + SUB_BYTES, SUB_HALF, p.idesc_kk64, 8, false);
           mma_commit(sdp_full(buf));
         }
-        if (!mbar_wait(pds_full(it & 1), (it >> 1) & 1u, abort_flag)) { ok = false; break; }
+        if (!mbar_wait(pds_full, it & 1u, abort_flag)) { ok = false; break; }
         tc_fence_after();
         const uint32_t st0 = st_s + s * 2 * SUB_BYTES;
-        const uint32_t pt_s = pds_s + (it & 1) * 2 * SUB_BYTES, dst_s = pt_s + SUB_BYTES;
         mma_kmn2(tmem + 384, pt_s, 0, st0 + SUB_BYTES, SUB_HALF, p.idesc_kmn, 4, it > 0);   // dV += P^T dO
         mma_kmn2(tmem + 256, dst_s, 0, st0, SUB_HALF, p.idesc_kmn, 4, it > 0);             // dK += dS^T Q
         mma_commit(st_empty(s));
-        mma_commit(pds_empty(it & 1));
+        mma_commit(pds_empty);
       }
       if (ok) mma_commit(acc_full);
       mma_commit(done_bar);
       mbar_wait_drain(done_bar, 0);
     }
   } else {
-    // four threads per key row: warps 2-5 take query columns 0..15 of each 64-query sub-tile, 6-9 16..31, and so on
+    // two threads per key row: warps 2-5 take query columns 0..31 of each 64-query sub-tile, warps 6-9 32..63
     const int qd = warp & 3, ch = (warp - 2) >> 2, row = qd * 32 + lane;   // key row within the tile
-    const int tid = threadIdx.x - 64;                                      // 0..511 among the compute threads
+    const int tid = threadIdx.x - 64;                                      // 0..255 among the compute threads
     const uint32_t lane_addr = tmem + ((uint32_t)(qd * 32) << 16);
     const int kj = kt * TILE + row;
     // lse / delta of the 64 queries of an item: threads 0..63 fetch lse, 64..127 delta
@@ -741,43 +721,42 @@ attn_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       tc_fence_after();
       const bool diag = (i * QSUB < kt * TILE + TILE);   // sub-tile overlaps the diagonal block
       {
-        const int c0 = ch * 16;   // this thread's 16 query columns of the item
-        uint32_t rs[16], rp[16];
-        float pv[16], dsv[16];
-        tmem_ld16(lane_addr + (it & 1) * 64 + c0, rs);
-        tmem_ld16(lane_addr + 128 + (it & 1) * 64 + c0, rp);
+        const int c = ch;
+        uint32_t rs[32], rp[32];
+        float pv[32], dsv[32];
+        tmem_ld32(lane_addr + (it & 1) * 64 + c * 32, rs);
+        tmem_ld32(lane_addr + 128 + (it & 1) * 64 + c * 32, rp);
         tmem_ld_wait();
         if (!diag && (i + 1) * QSUB <= p.S) {   // sub-tile strictly below the diagonal block and inside the sequence
 #pragma unroll
-          for (int e = 0; e < 16; ++e) {
-            const int col = c0 + e;
+          for (int e = 0; e < 32; ++e) {
+            const int col = c * 32 + e;
             pv[e] = fast_exp2(fmaf(__uint_as_float(rs[e]), p.scale_log2, -st[col]));
             dsv[e] = pv[e] * (__uint_as_float(rp[e]) - st[QSUB + col]);
           }
         } else {
 #pragma unroll
-          for (int e = 0; e < 16; ++e) {
-            const int col = c0 + e, qi = i * QSUB + col;
+          for (int e = 0; e < 32; ++e) {
+            const int col = c * 32 + e, qi = i * QSUB + col;
             const float pr = fast_exp2(fmaf(__uint_as_float(rs[e]), p.scale_log2, -st[col]));
             const bool keep = qi < p.S && (!diag || kj <= qi);
             pv[e] = keep ? pr : 0.f;
             dsv[e] = keep ? pr * (__uint_as_float(rp[e]) - st[QSUB + col]) : 0.f;
           }
         }
-        // P^T / dS^T of the item before last must have been consumed before its buffer is overwritten; waiting
-        // only here lets this item's exponentials run under the previous items' dV / dK products
-        if (!mbar_wait(pds_empty(it & 1), ((it >> 1) & 1u) ^ 1u, abort_flag)) ok = false;
+        // P^T / dS^T of the previous item must have been consumed before they are overwritten; waiting only here
+        // lets this item's exponentials run under the previous item's dV / dK products
+        if (!mbar_wait(pds_empty, (it & 1u) ^ 1u, abort_flag)) ok = false;
         ok = __all_sync(0xffffffffu, ok);
         if (ok) {
-          uint8_t* pt_ptr = pds_ptr + (it & 1) * 2 * SUB_BYTES;
-          store_swizzled16<T>(pt_ptr, row, c0, pv);
-          store_swizzled16<T>(pt_ptr + SUB_BYTES, row, c0, dsv);
+          store_swizzled32<T>(pt_ptr, row, c * 32, pv);
+          store_swizzled32<T>(dst_ptr, row, c * 32, dsv);
         }
       }
       tc_fence_before();
       fence_proxy_async_smem();
       __syncwarp();
-      if (lane == 0) mbar_arrive(pds_full(it & 1));   // the warp's writes are ordered before lane 0's arrival
+      if (lane == 0) mbar_arrive(pds_full);   // the warp's writes are ordered before lane 0's arrival
     }
     bool fin = ok && mbar_wait(acc_full, 0, abort_flag);
     fin = __all_sync(0xffffffffu, fin);
@@ -788,8 +767,8 @@ attn_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         const int64_t rows = (int64_t)(gridDim.x / gs) * p.S;
         float* pk = p.part + (((int64_t)zsplit * 2 + 0) * rows + (int64_t)bk * p.S + kj) * AD;
         float* pvp = p.part + (((int64_t)zsplit * 2 + 1) * rows + (int64_t)bk * p.S + kj) * AD;
-        {
-          const int c = ch;
+#pragma unroll 1
+        for (int c = 2 * ch; c < 2 * ch + 2; ++c) {
           uint32_t rk[32], rv[32];
           tmem_ld32(lane_addr + 256 + c * 32, rk);
           tmem_ld32(lane_addr + 384 + c * 32, rv);
@@ -805,8 +784,8 @@ attn_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       } else {
         T* krow = reinterpret_cast<T*>(p.dk) + (int64_t)b * p.k_bs + (int64_t)kvh * p.k_hs + (int64_t)kj * p.k_ss;
         T* vrow = reinterpret_cast<T*>(p.dv) + (int64_t)b * p.k_bs + (int64_t)kvh * p.k_hs + (int64_t)kj * p.k_ss;
-        {
-          const int c = ch;
+#pragma unroll 1
+        for (int c = 2 * ch; c < 2 * ch + 2; ++c) {
           uint32_t rk[32], rv[32];
           tmem_ld32(lane_addr + 256 + c * 32, rk);
           tmem_ld32(lane_addr + 384 + c * 32, rv);
@@ -835,8 +814,7 @@ attn_dkdv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem, 512); }
   if (threadIdx.x == 0 && *abort_flag) flag_status(p.status, Q3_STATUS_WAIT_TIMEOUT);
 }
-constexpr int kDkdvSmem = 2 * TILE_BYTES + KV_STAGES * 2 * SUB_BYTES + 4 * SUB_BYTES + 4 * QSUB * 4 + 1024 + 256;
-static_assert(kDkdvSmem <= 227 * 1024, "dK/dV kernel shared memory exceeds the per-CTA limit");
+constexpr int kDkdvSmem = 2 * TILE_BYTES + KV_STAGES * 2 * SUB_BYTES + 2 * SUB_BYTES + 4 * QSUB * 4 + 1024 + 256;
 
 // Sum the per-query-head fp32 partials of dK / dV in head order, scale dK, round once, store with strides.
 template <typename T>
@@ -956,7 +934,7 @@ int attn_bwd_tc(const void* q, const void* k, const void* v, const void* dout, c
     static bool c1 = false, c2 = false;
     if ((rc = configure_smem(attn_dq_tc_kernel<__nv_bfloat16>, kDqSmem, &c1)) != Q3_OK) return rc;
     if ((rc = configure_smem(attn_dkdv_tc_kernel<__nv_bfloat16>, kDkdvSmem, &c2)) != Q3_OK) return rc;
-    attn_dkdv_tc_kernel<__nv_bfloat16><<<gk, kDkdvThreads, kDkdvSmem, st>>>(tmQs, tmK, tmV, tmDOs, p);
+    attn_dkdv_tc_kernel<__nv_bfloat16><<<gk, kAttnThreads, kDkdvSmem, st>>>(tmQs, tmK, tmV, tmDOs, p);
     if (p.gsplit > 1)
       attn_dkdv_reduce_kernel<__nv_bfloat16><<<red_grid, 256, 0, st>>>(partials, (__nv_bfloat16*)dk, (__nv_bfloat16*)dv, p.gsplit, kv_rows,
                                                                      (int)Hkv, (int)S, sk.ss, sk.hs, sk.bs, scale);
@@ -965,7 +943,7 @@ int attn_bwd_tc(const void* q, const void* k, const void* v, const void* dout, c
     static bool c1 = false, c2 = false;
     if ((rc = configure_smem(attn_dq_tc_kernel<__half>, kDqSmem, &c1)) != Q3_OK) return rc;
     if ((rc = configure_smem(attn_dkdv_tc_kernel<__half>, kDkdvSmem, &c2)) != Q3_OK) return rc;
-    attn_dkdv_tc_kernel<__half><<<gk, kDkdvThreads, kDkdvSmem, st>>>(tmQs, tmK, tmV, tmDOs, p);
+    attn_dkdv_tc_kernel<__half><<<gk, kAttnThreads, kDkdvSmem, st>>>(tmQs, tmK, tmV, tmDOs, p);
     if (p.gsplit > 1)
       attn_dkdv_reduce_kernel<__half><<<red_grid, 256, 0, st>>>(partials, (__half*)dk, (__half*)dv, p.gsplit, kv_rows, (int)Hkv, (int)S,
                                                               sk.ss, sk.hs, sk.bs, scale);
