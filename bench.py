@@ -358,9 +358,14 @@ def run_fsdp(args):
     with torch.device(device):
         model = model_for_variant(cfg, os.environ.get("Q3_BENCH_VARIANT", "b200_fused"))
     comm = NcclCollectives()
-    ckpt = os.environ.get("Q3_BENCH_CHECKPOINT", "selective")     # 'selective' or 'full' per-layer recomputation
+    # the vocabulary-parallel head and embedding talk over their own communicator, so that their small collectives on
+    # the compute stream do not queue behind FSDP's reduce-scatters on the same NCCL communicator
+    vocab_comm = NcclCollectives(group=dist.new_group()) if os.environ.get("Q3_BENCH_VP_GROUP", "1") == "1" else None
+    # activation recomputation: 'none' keeps every layer's activations (about 5 GB at 2048 tokens per GPU, nothing on
+    # a 180 GB part); 'selective' / 'full' are the memory-saving modes
+    ckpt = os.environ.get("Q3_BENCH_CHECKPOINT", "none")
     model = shard_vocab_loss_model(model, keep_full_layers=layers, checkpoint_every=1,
-                                   skip_embedding_backward_gather=True, fused_vocab_dw=True, communication=None,
+                                   skip_embedding_backward_gather=True, fused_vocab_dw=True, communication=vocab_comm,
                                    checkpoint_mode=ckpt, layers_per_unit=unit_sizes(layers),
                                    vocab_parallel_embedding=os.environ.get("Q3_BENCH_VP_EMBEDDING", "1") == "1")
     model.lm_head.fused = os.environ.get("Q3_BENCH_FUSED_LOSS", "0") == "1"
@@ -438,11 +443,12 @@ def run_fsdp(args):
             "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
             "data": "synthetic",
             "config": {"workload": "qwen3-8b %d layers under FSDP2, microbatch 1x2048 per GPU, vocab-parallel head%s, "
-                                   "per-layer %s activation recompute, AdamW (BASELINE config 5)" % (
+                                   "%s activation recompute, AdamW (BASELINE config 5)" % (
                                        layers, " and embedding" if os.environ.get("Q3_BENCH_VP_EMBEDDING", "1") == "1" else "", ckpt),
                        "global_batch": batch * world, "seq_len": seq, "parallelism": "fsdp%d" % world,
                        "l2": "weights and activations >> L2", "mfu_of_%s_peak_per_gpu" % peak_kind: mfu,
                        "tokens_per_s_per_gpu": value / world, "last_loss": last,
+                       "peak_memory_gb_rank0": round(torch.cuda.max_memory_allocated() / 2 ** 30, 1),
                        "fsdp_units": hooks["units"], "collectives": comm.report()},
             "e2e": {"value": tokens / (e2e_ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": batch * seq * 8 * world,
                     "d2h_bytes_per_step": 4 * world},

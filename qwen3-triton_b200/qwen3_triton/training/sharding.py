@@ -56,7 +56,8 @@ class VocabLossQwen3(PrecisionQwen3ForCausalLM):
 def shard_vocab_loss_model(model, *, keep_full_layers, checkpoint_every, skip_embedding_backward_gather,
                            fused_vocab_dw=False, communication=None, mesh=None, checkpoint_mode='full',
                            layers_per_unit=1, vocab_parallel_embedding=False):
-    """Reference surface (scripts/vocab_model_v12.py:35-56) plus three knobs: `checkpoint_mode`, `layers_per_unit`
+    """Reference surface (scripts/vocab_model_v12.py:35-56) plus three knobs: `checkpoint_mode` ('full' as the
+    reference, 'selective', or 'none' where memory allows: 36 layers at 2048 tokens keep about 5 GB), `layers_per_unit`
     (an int, or a sequence of unit sizes that sums to the layer count) and `vocab_parallel_embedding` (the token
     table stays row-sharded outside FSDP instead of being gathered and its dense gradient reduce-scattered)."""
     if model.config.tie_word_embeddings:
@@ -94,9 +95,10 @@ def shard_vocab_loss_model(model, *, keep_full_layers, checkpoint_every, skip_em
         if index in checkpointed:
             if hasattr(layer, 'recompute'):
                 # fused layers checkpoint inside their own backward ('full' or 'selective')
-                layer.recompute = {'full': 2, 'selective': 1}[checkpoint_mode]
+                layer.recompute = {'full': 2, 'selective': 1, 'none': 0}[checkpoint_mode]
             else:
-                layer = wrap_decoder_checkpoint(layer, mode='full')
+                if checkpoint_mode != 'none':
+                    layer = wrap_decoder_checkpoint(layer, mode='full')
         body.layers[index] = layer
     # One FSDP unit per `layers_per_unit` consecutive layers (1 = the reference's policy). FSDP2's Python
     # hooks cost about a millisecond per unit and direction; at 2048 tokens per GPU a B200 finishes a
