@@ -367,9 +367,10 @@ def run_fsdp(args):
     model = shard_vocab_loss_model(model, keep_full_layers=layers, checkpoint_every=1,
                                    skip_embedding_backward_gather=True, fused_vocab_dw=True, communication=vocab_comm,
                                    checkpoint_mode=ckpt, layers_per_unit=unit_sizes(layers),
-                                   vocab_parallel_embedding=os.environ.get("Q3_BENCH_VP_EMBEDDING", "1") == "1")
+                                   vocab_parallel_embedding=os.environ.get("Q3_BENCH_VP_EMBEDDING", "1") == "1",
+                                   forward_prefetch=int(os.environ.get("Q3_BENCH_FORWARD_PREFETCH", "2")))
     model.lm_head.fused = os.environ.get("Q3_BENCH_FUSED_LOSS", "0") == "1"
-    hooks = configure(model, comm)
+    hooks = configure(model, comm, pack_gradients_off_compute_stream=os.environ.get("Q3_BENCH_PACK_SIDE", "1") == "1")
     decoder = [p for n, p in model.named_parameters() if not n.startswith("lm_head.")]
     opt = TritonAdamW([dict(params=decoder), dict(params=[model.lm_head.weight])], lr=1e-4, betas=(0.9, 0.95),
                       weight_decay=0.1)

@@ -56,11 +56,13 @@ class TritonReduceScatter(_Allocation, ReduceScatter):
         self.calls += 1
 
 
-def configure(model, communication, *, pack_kernels=True):
-    """Install the comm hooks on every FSDP unit and (by default) the pack/unpack kernels of runtime/ops.py."""
+def configure(model, communication, *, pack_kernels=True, pack_gradients_off_compute_stream=False):
+    """Install the comm hooks on every FSDP unit and (by default) the pack/unpack kernels of runtime/ops.py.
+    `pack_gradients_off_compute_stream`: run the reduce-scatter copy-in on FSDP's reduce-scatter stream."""
     if pack_kernels:
-        from .ops import install_fsdp_pack_kernels
+        from .ops import install_fsdp_pack_kernels, pack_gradients_on_reduce_scatter_stream
         install_fsdp_pack_kernels()
+        pack_gradients_on_reduce_scatter_stream(model if pack_gradients_off_compute_stream else None)
     ag = TritonAllGather(communication)
     rs = TritonReduceScatter(communication)
     count = 0

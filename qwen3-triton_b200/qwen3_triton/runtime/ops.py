@@ -155,6 +155,30 @@ def split_with_sizes_copy(all_gather_output, all_gather_input_split_sizes, dim=0
     _launch(rows, all_gather_output.dtype, out[0].dtype, all_gather_output.device)
 
 
+_rs_root = None        # weak reference to the root FSDP module whose reduce-scatter stream takes the gradient pack
+
+
+def pack_gradients_on_reduce_scatter_stream(root_module):
+    """torch 2.11 issues the reduce-scatter copy-in (`fsdp::chunk_cat`) on the compute stream, where it costs about
+    8 ms per step of Qwen3-8B. After this call the override runs it on FSDP's reduce-scatter stream instead, ordered
+    after the compute stream's work so far; FSDP then queues the collective behind it on that same stream. The
+    gradients are marked as used by that stream, so the allocator does not hand their memory out early."""
+    global _rs_root
+    import weakref
+    _rs_root = weakref.ref(root_module) if root_module is not None else None
+
+
+def _reduce_scatter_stream():
+    root = _rs_root() if _rs_root is not None else None
+    if root is None:
+        return None
+    try:
+        ctx = root._get_fsdp_state()._comm_ctx
+        return getattr(ctx, 'reduce_scatter_stream', None)
+    except Exception:
+        return None
+
+
 def chunk_cat(tensors, dim, num_chunks, out):
     ok = (dim == 0 and out.ndim == 2 and out.is_contiguous() and out.dtype in _FLOATS and out.shape[0] == num_chunks
           and len({t.dtype for t in tensors}) == 1 and tensors[0].dtype in _FLOATS
@@ -166,7 +190,16 @@ def chunk_cat(tensors, dim, num_chunks, out):
     if not ok:
         torch._chunk_cat(tensors, dim, num_chunks, out=out)
         return
-    _launch(rows, tensors[0].dtype, out.dtype, out.device)
+    side = _reduce_scatter_stream()
+    if side is None:
+        _launch(rows, tensors[0].dtype, out.dtype, out.device)
+        return
+    side.wait_stream(torch.cuda.current_stream(out.device))
+    for t in tensors:
+        t.record_stream(side)
+    out.record_stream(side)
+    with torch.cuda.stream(side):
+        _launch(rows, tensors[0].dtype, out.dtype, out.device)
 
 
 def install_fsdp_pack_kernels():

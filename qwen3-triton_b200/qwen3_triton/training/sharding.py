@@ -55,10 +55,11 @@ class VocabLossQwen3(PrecisionQwen3ForCausalLM):
 
 def shard_vocab_loss_model(model, *, keep_full_layers, checkpoint_every, skip_embedding_backward_gather,
                            fused_vocab_dw=False, communication=None, mesh=None, checkpoint_mode='full',
-                           layers_per_unit=1, vocab_parallel_embedding=False):
+                           layers_per_unit=1, vocab_parallel_embedding=False, forward_prefetch=1):
     """Reference surface (scripts/vocab_model_v12.py:35-56) plus three knobs: `checkpoint_mode` ('full' as the
     reference, 'selective', or 'none' where memory allows: 36 layers at 2048 tokens keep about 5 GB), `layers_per_unit`
-    (an int, or a sequence of unit sizes that sums to the layer count) and `vocab_parallel_embedding` (the token
+    (an int, or a sequence of unit sizes that sums to the layer count), `forward_prefetch` (all-gathers issued that
+    many units ahead in forward) and `vocab_parallel_embedding` (the token
     table stays row-sharded outside FSDP instead of being gathered and its dense gradient reduce-scattered)."""
     if model.config.tie_word_embeddings:
         raise ValueError('Untied head required')
@@ -105,13 +106,25 @@ def shard_vocab_loss_model(model, *, keep_full_layers, checkpoint_every, skip_em
     # layer's forward in about that time, so larger units keep the GPU fed. Collective payloads grow by
     # the same factor (4 layers: 1.5 GB gathered, 3 GB reduced), still far below the memory budget.
     first = 0
+    heads = []
     for size in sizes:
         group = [body.layers[i] for i in range(first, first + size)]
         retain = first + len(group) - 1 >= len(body.layers) - keep_full_layers
         fully_shard(group if len(group) > 1 else group[0], reshard_after_forward=not retain, **kw)
+        heads.append(group[0])
         first += size
+    # `forward_prefetch` units ahead: FSDP2's default issues the next unit's all-gather when the current unit starts,
+    # which does not cover the ~1 ms all-gather latency when the first units are single layers
+    if forward_prefetch > 1:
+        for index, head in enumerate(heads):
+            ahead = heads[index + 1:index + 1 + forward_prefetch]
+            if ahead:
+                head.set_modules_to_forward_prefetch(ahead)
     fully_shard(body.norm.float(), reshard_after_forward=True, **kw)
     body.rotary_emb.cuda()
     fully_shard(model, reshard_after_forward=True, ignored_params=ignored, **kw)
+    if forward_prefetch > 1 and heads:
+        # the root unit runs first: let it start the first decoder units' all-gathers before the embedding lookup
+        model.set_modules_to_forward_prefetch(heads[:forward_prefetch])
     model.config.use_cache = False
     return model
