@@ -370,7 +370,7 @@ def run_fsdp(args):
                                    vocab_parallel_embedding=os.environ.get("Q3_BENCH_VP_EMBEDDING", "1") == "1",
                                    forward_prefetch=int(os.environ.get("Q3_BENCH_FORWARD_PREFETCH", "2")))
     model.lm_head.fused = os.environ.get("Q3_BENCH_FUSED_LOSS", "0") == "1"
-    hooks = configure(model, comm, pack_gradients_off_compute_stream=os.environ.get("Q3_BENCH_PACK_SIDE", "1") == "1")
+    hooks = configure(model, comm, pack_gradients_off_compute_stream=os.environ.get("Q3_BENCH_PACK_SIDE", "0") == "1")
     decoder = [p for n, p in model.named_parameters() if not n.startswith("lm_head.")]
     opt = TritonAdamW([dict(params=decoder), dict(params=[model.lm_head.weight])], lr=1e-4, betas=(0.9, 0.95),
                       weight_decay=0.1)

@@ -4,8 +4,8 @@
 //
 // Table layout (device, int64[rows][7]): {p, g, m, v, step pointers, numel, first_block}.
 // Math order: decoupled decay, moments, bias corrections bc1 = 1-b1^t, sqrt(bc2) = sqrt(1-b2^t),
-// step_size = lr/bc1, denom = sqrt(v)/sqrt(bc2) + eps; the coefficient arithmetic is fp64 and each
-// stored quantity is rounded to fp32 once.
+// step_size = lr/bc1, denom = sqrt(v)/sqrt(bc2) + eps; the per-tensor coefficients are computed in fp64, the
+// per-element arithmetic in fp32.
 //
 // Replaces, in the reference: qwen3_triton/runtime/adamw.py:20-30 (_adamw_prepare) and
 // runtime/adamw.py:34-61 (_adamw_update).
@@ -27,13 +27,19 @@ __global__ void adamw_prepare_kernel(const int64_t* __restrict__ meta, float* __
   coeff[r * 3 + 2] = (float)(lr / (double)bc1);
 }
 
+// One element. The hyper-parameters arrive as doubles (the host's values) and are rounded to fp32 once per thread; the
+// per-element arithmetic is fp32 with fused multiply-adds and IEEE sqrt / division. (An earlier form did the
+// per-element arithmetic in fp64: ten fp64 conversions and operations per element made the kernel compute-bound
+// at the 1.36 GHz the chip holds under its power cap inside a training step.) Against the fp64 oracle the result
+// differs by a few 1e-7 relative, inside the 1e-5 gate.
 __device__ __forceinline__ void adamw_one(float& p, float g, float& m, float& v, double lr, double b1, double b2,
                                           double decay, double eps, float bc2, float size) {
-  p = (float)((double)p - lr * decay * (double)p);
-  m = (float)fma(b1, (double)m, (1.0 - b1) * (double)g);
-  v = (float)(b2 * (double)v + (1.0 - b2) * (double)g * (double)g);
-  const float root = __fsqrt_rn(v);
-  const float denom = (float)((double)__fdiv_rn(root, bc2) + eps);
+  const float lr_decay = (float)(lr * decay), b1f = (float)b1, omb1 = (float)(1.0 - b1), b2f = (float)b2,
+              omb2 = (float)(1.0 - b2), epsf = (float)eps;
+  p = fmaf(-lr_decay, p, p);
+  m = fmaf(b1f, m, omb1 * g);
+  v = fmaf(b2f, v, (omb2 * g) * g);
+  const float denom = __fdiv_rn(__fsqrt_rn(v), bc2) + epsf;
   p = p - __fdiv_rn(size * m, denom);
 }
 
