@@ -183,7 +183,7 @@ def main():
         opt = TritonAdamW(params, lr=1e-4, betas=(0.9, 0.95), weight_decay=0.1)
         opt.step()
         total = sum(p.numel() for p in params)
-        report(f"adamw_mp ({total / 1e9:.2f}e9 params)", timer(opt.step), bytes_=30 * total)
+        report(f"adamw_mp ({total / 1e9:.2f}e9 params)", timer(opt.step), bytes_=28 * total)
         del params, opt
     if want("pack"):
         # one Qwen3-8B decoder layer as an FSDP unit over 8 ranks: shard copy-in, gathered split, gradient chunk-cat

@@ -99,7 +99,7 @@ __global__ void __launch_bounds__(256) adamw_update_kernel(const int64_t* __rest
 // neither a gradient-upcast pass nor a master->working cast pass. Table: int64[rows][9] =
 // {p, g_fp32 (or 0), m, v, step, numel, first_block, g_lowp (or 0), p_lowp (or 0)}.
 template <typename L>
-__global__ void __launch_bounds__(256, 4) adamw_update_mp_kernel(const int64_t* __restrict__ meta,
+__global__ void __launch_bounds__(256) adamw_update_mp_kernel(const int64_t* __restrict__ meta,
                                                               const float* __restrict__ coeff, int64_t rows, double lr,
                                                               double b1, double b2, double decay, double eps,
                                                               int block_elems) {
@@ -124,31 +124,22 @@ __global__ void __launch_bounds__(256, 4) adamw_update_mp_kernel(const int64_t* 
                          reinterpret_cast<uintptr_t>(g32) | reinterpret_cast<uintptr_t>(glo) |
                          reinterpret_cast<uintptr_t>(plo);
   if ((bits & 15u) == 0) {
-    // 8 elements per thread per iteration: 2 x 16-byte accesses on each fp32 array, one on each 16-bit array
-    const int64_t vend = begin + ((end - begin) & ~(int64_t)7);
-    for (int64_t i = begin + threadIdx.x * 8; i < vend; i += blockDim.x * 8) {
-      float pp[8], mm[8], vv[8], gg[8];
+    // same shape as the fp32-gradient kernel: 4 elements per thread per iteration, one 16-byte access on each fp32
+    // array and one 8-byte access on each 16-bit array
+    const int64_t vend = begin + ((end - begin) & ~(int64_t)3);
+    for (int64_t i = begin + threadIdx.x * 4; i < vend; i += blockDim.x * 4) {
+      float pp[4], mm[4], vv[4], gg[4];
       *reinterpret_cast<float4*>(pp) = *reinterpret_cast<const float4*>(p + i);
-      *reinterpret_cast<float4*>(pp + 4) = *reinterpret_cast<const float4*>(p + i + 4);
       *reinterpret_cast<float4*>(mm) = *reinterpret_cast<const float4*>(m + i);
-      *reinterpret_cast<float4*>(mm + 4) = *reinterpret_cast<const float4*>(m + i + 4);
       *reinterpret_cast<float4*>(vv) = *reinterpret_cast<const float4*>(v + i);
-      *reinterpret_cast<float4*>(vv + 4) = *reinterpret_cast<const float4*>(v + i + 4);
-      if (glo != nullptr) {
-        VecIO<L, 8>::load(glo + i, gg);
-      } else {
-        *reinterpret_cast<float4*>(gg) = *reinterpret_cast<const float4*>(g32 + i);
-        *reinterpret_cast<float4*>(gg + 4) = *reinterpret_cast<const float4*>(g32 + i + 4);
-      }
+      if (glo != nullptr) VecIO<L, 4>::load(glo + i, gg);
+      else *reinterpret_cast<float4*>(gg) = *reinterpret_cast<const float4*>(g32 + i);
 #pragma unroll
-      for (int e = 0; e < 8; ++e) adamw_one(pp[e], gg[e], mm[e], vv[e], lr, b1, b2, decay, eps, bc2, size);
+      for (int e = 0; e < 4; ++e) adamw_one(pp[e], gg[e], mm[e], vv[e], lr, b1, b2, decay, eps, bc2, size);
       *reinterpret_cast<float4*>(p + i) = *reinterpret_cast<float4*>(pp);
-      *reinterpret_cast<float4*>(p + i + 4) = *reinterpret_cast<float4*>(pp + 4);
       *reinterpret_cast<float4*>(m + i) = *reinterpret_cast<float4*>(mm);
-      *reinterpret_cast<float4*>(m + i + 4) = *reinterpret_cast<float4*>(mm + 4);
       *reinterpret_cast<float4*>(v + i) = *reinterpret_cast<float4*>(vv);
-      *reinterpret_cast<float4*>(v + i + 4) = *reinterpret_cast<float4*>(vv + 4);
-      if (plo != nullptr) VecIO<L, 8>::store(plo + i, pp);
+      if (plo != nullptr) VecIO<L, 4>::store(plo + i, pp);
     }
     for (int64_t i = vend + threadIdx.x; i < end; i += blockDim.x) {
       float pp = p[i], mm = m[i], vv = v[i];
