@@ -39,7 +39,7 @@ LAUNCHES = {"q3_rmsnorm_bwd": 2, "q3_add_rmsnorm_bwd": 2, "q3_norm_rope_bwd": 2,
 
 
 GEMM_ENTRIES = ("q3_gemm", "q3_gemm_acc", "q3_gate_up_swiglu_fwd", "q3_linear_fwd_grouped", "q3_linear_dgrad_grouped",
-                "q3_linear_wgrad_grouped")
+                "q3_linear_wgrad_grouped", "q3_down_dgrad_swiglu_bwd")
 
 
 def gemm_flops_of(name, a):
@@ -48,6 +48,8 @@ def gemm_flops_of(name, a):
         return 2.0 * a[7] * a[8] * a[9]
     if name == "q3_gate_up_swiglu_fwd":
         return 4.0 * a[6] * a[7] * a[8]
+    if name == "q3_down_dgrad_swiglu_bwd":
+        return 2.0 * a[6] * a[7] * a[8]
     if name in ("q3_linear_fwd_grouped", "q3_linear_dgrad_grouped", "q3_linear_wgrad_grouped"):
         return 2.0 * a[5] * a[6] * sum(a[3][i] for i in range(a[4]))
     return 0.0

@@ -303,6 +303,13 @@ int q3_linear_dgrad_grouped(const void* const* dys, const void* const* weights, 
 int q3_linear_wgrad_grouped(const void* const* dys, const void* x, void* const* dws, const int64_t* n, int count,
                             int64_t M, int64_t K, int dtype, int* status, q3_stream_t stream);
 
+/* Input gradient of down_proj fused with the SwiGLU backward: dY = dM [M,H] * W_down [H,I] is formed tile by tile in
+ * tensor memory and turned into dG, dU (from the saved G, U [M,I]) in the epilogue; dY itself is never written.
+ * Bit-identical to q3_gemm (dgrad) followed by q3_swiglu_bwd. Reference: `_gemm` (kernels/linear.py:45-77) then
+ * `_backward` (kernels/activation.py:22-34). */
+int q3_down_dgrad_swiglu_bwd(const void* dm, const void* w_down, const void* gate, const void* up, void* dgate, void* dup,
+                             int64_t M, int64_t I, int64_t H, int dtype, int* status, q3_stream_t stream);
+
 /* ---- fused lm_head + cross-entropy (no logits in memory) ---------------------------------------------------
  * The reference materialises the logits [W*r, V/W] and their gradient (qwen3_triton/training/vocab_parallel.py:52,75;
  * kernels/vocab_ce.py:78-112). Here the projection runs on the tensor cores and the softmax statistics / gradient are

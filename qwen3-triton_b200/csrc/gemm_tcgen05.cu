@@ -38,9 +38,11 @@ constexpr int kGemmThreads = 192;
 constexpr int kGroupM = 8;
 
 struct GemmParams {
-  void* c0;   // C, or G for the gate/up variant
-  void* c1;   // U
+  void* c0;   // C, or G for the gate/up variant, or dG for the SwiGLU-backward variant
+  void* c1;   // U, or dU
   void* c2;   // Y
+  const void* aux0;   // saved G (SwiGLU backward)
+  const void* aux1;   // saved U
   int64_t M, N, K;  // N = output columns (per matrix for gate/up)
   int tiles_m, tiles_n, kblocks;
   uint32_t idesc;
@@ -140,7 +142,8 @@ __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, 
 //   EPI_CE_STATS A*B are logits that are never stored: per row and N-tile the (max, sum exp) of the logits rounded
 //                to TO, and the target logit where the tile owns the row's label
 //   EPI_CE_GRAD  stores dZ = (exp(z - lse[row]) - onehot) * upstream[source] / count[source] for the logits z
-enum { EPI_STORE = 0, EPI_GATE_UP = 1, EPI_ACC_F32 = 2, EPI_CE_STATS = 3, EPI_CE_GRAD = 4 };
+//   EPI_SWIGLU_BWD  A*B is dY of y = silu(G)*U, rounded to TO as the stored dY would be; stores dG and dU, never dY
+enum { EPI_STORE = 0, EPI_GATE_UP = 1, EPI_ACC_F32 = 2, EPI_CE_STATS = 3, EPI_CE_GRAD = 4, EPI_SWIGLU_BWD = 5 };
 
 template <int BN, typename TO, int EPI>
 __global__ void __launch_bounds__(kGemmThreads, 1)
@@ -360,6 +363,37 @@ gemm_tc_kernel(const __grid_constant__ GemmMaps maps, const GemmParams p) {
               }
             }
             store_chunk32<TO>(crow + c * 32, r, n0 + c * 32, p.N);
+          }
+        }
+      } else if constexpr (EPI == EPI_SWIGLU_BWD) {
+        const int64_t n0 = (int64_t)ni * BN;
+        const TO* grow = reinterpret_cast<const TO*>(p.aux0) + row * p.N + n0;
+        const TO* urow = reinterpret_cast<const TO*>(p.aux1) + row * p.N + n0;
+        TO* dgrow = reinterpret_cast<TO*>(p.c0) + row * p.N + n0;
+        TO* durow = reinterpret_cast<TO*>(p.c1) + row * p.N + n0;
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          uint32_t r[32], du[32];
+          tmem_ld32(t_row + c * 32, r);
+          tmem_ld_wait();
+          if (row < p.M && n0 + c * 32 < p.N) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              if (n0 + c * 32 + 8 * j + 8 <= p.N) {
+                float g8[8], u8[8];
+                VecIO<TO, 8>::load(grow + c * 32 + 8 * j, g8);
+                VecIO<TO, 8>::load(urow + c * 32 + 8 * j, u8);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                  const float dy = to_f32<TO>(from_f32<TO>(__uint_as_float(r[8 * j + e])));   // the dY a separate GEMM would store
+                  const float sg = __fdividef(1.f, 1.f + __expf(-g8[e]));
+                  r[8 * j + e] = __float_as_uint(dy * u8[e] * sg * (1.f + g8[e] * (1.f - sg)));
+                  du[8 * j + e] = __float_as_uint(dy * g8[e] * sg);
+                }
+              }
+            }
+            store_chunk32<TO>(dgrow + c * 32, r, n0 + c * 32, p.N);
+            store_chunk32<TO>(durow + c * 32, du, n0 + c * 32, p.N);
           }
         }
       } else if constexpr (EPI == EPI_CE_STATS) {
@@ -757,6 +791,26 @@ extern "C" int q3_linear_wgrad_grouped(const void* const* dys, const void* x, vo
   cudaStream_t st = (cudaStream_t)stream;
   if (dtype == Q3_BF16) return tc::launch_grouped<__nv_bfloat16>(3, count, dys, b, dws, n, total, K, M, true, status, st);
   return tc::launch_grouped<__half>(3, count, dys, b, dws, n, total, K, M, false, status, st);
+}
+
+// dY = dM [M,H] * W_down [H,I] is the gradient of y = silu(G)*U; this forms dG and dU in the GEMM epilogue from the
+// saved G and U and never writes dY (one launch instead of q3_gemm + q3_swiglu_bwd, 2 x M x I x 2 bytes less
+// traffic). dY is rounded to the storage type before use, so dG / dU equal the two-kernel path bit for bit.
+extern "C" int q3_down_dgrad_swiglu_bwd(const void* dm, const void* w_down, const void* gate, const void* up, void* dgate,
+                                        void* dup, int64_t M, int64_t I, int64_t H, int dtype, int* status,
+                                        q3_stream_t stream) {
+  if (!dm || !w_down || !gate || !up || !dgate || !dup) return Q3_ERR_ARG;
+  if (M < 1 || I < 1 || H < 1) return Q3_ERR_SHAPE;
+  if (dtype != Q3_BF16 && dtype != Q3_F16) return Q3_ERR_DTYPE;
+  if ((I % 8) || (H % 8) || !aligned16(dm) || !aligned16(w_down) || !aligned16(gate) || !aligned16(up) ||
+      !aligned16(dgate) || !aligned16(dup))
+    return Q3_ERR_ALIGN;
+  tc::Operand A{dm, false, H}, B{w_down, true, I};
+  tc::GemmParams p{};
+  p.c0 = dgate; p.c1 = dup; p.aux0 = gate; p.aux1 = up; p.M = M; p.N = I; p.K = H; p.status = status;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (dtype == Q3_BF16) return tc::launch_gemm<256, __nv_bfloat16, tc::EPI_SWIGLU_BWD>(A, B, nullptr, p, true, st);
+  return tc::launch_gemm<256, __half, tc::EPI_SWIGLU_BWD>(A, B, nullptr, p, false, st);
 }
 
 extern "C" int64_t q3_linear_ce_tiles(int64_t V_local) { return q3::cdiv(V_local, 256); }

@@ -68,6 +68,7 @@ SIGNATURES = {
     "q3_linear_fwd_grouped": (I, [P, P, P, P, I, L, L, I, P, P]),
     "q3_linear_dgrad_grouped": (I, [P, P, P, P, I, L, L, I, P, P]),
     "q3_linear_wgrad_grouped": (I, [P, P, P, P, I, L, L, I, P, P]),
+    "q3_down_dgrad_swiglu_bwd": (I, [P, P, P, P, P, P, L, L, L, I, P, P]),
     "q3_linear_ce_tiles": (L, [L]),
     "q3_shift_labels": (I, [P, P, L, L, L, L, P, P]),
     "q3_linear_ce_stats": (I, [P, P, P, P, P, P, L, L, L, L, L, I, P, P]),

@@ -254,12 +254,18 @@ class FusedLayerFn(torch.autograd.Function):
         dm = g_m.reshape(t, hdim).contiguous()
         dres = g_x1.reshape(t, hdim).contiguous() if g_x1 is not None else None
         # MLP
-        dy = mm_nn(dm, wd)
         dwd = mm_tn(dm, r['y'])
         dg, du = torch.empty_like(r['g']), torch.empty_like(r['u'])
-        _abi.call('q3_swiglu_bwd', r['g'].data_ptr(), r['u'].data_ptr(), dy.data_ptr(), dg.data_ptr(), du.data_ptr(),
-                  dg.numel(), _abi.dt(dg.dtype), _abi.stream())
-        del dy
+        if wd.shape[0] % 8 == 0 and wd.shape[1] % 8 == 0:
+            # dY = dM @ W_down never leaves tensor memory: the GEMM epilogue turns it into dG, dU
+            _abi.call('q3_down_dgrad_swiglu_bwd', dm.data_ptr(), wd.data_ptr(), r['g'].data_ptr(), r['u'].data_ptr(),
+                      dg.data_ptr(), du.data_ptr(), t, wd.shape[1], wd.shape[0], _abi.dt(dg.dtype),
+                      _abi.status_word(dm.device).data_ptr(), _abi.stream())
+        else:
+            dy = mm_nn(dm, wd)
+            _abi.call('q3_swiglu_bwd', r['g'].data_ptr(), r['u'].data_ptr(), dy.data_ptr(), dg.data_ptr(), du.data_ptr(),
+                      dg.numel(), _abi.dt(dg.dtype), _abi.stream())
+            del dy
         dh2 = linear_group_dgrad([dg, du], [wg, wu])
         dwg, dwu = linear_group_wgrad([dg, du], r['h2'])
         del dg, du

@@ -79,6 +79,36 @@ def test_grouped_linear_layers_equal_separate_gemms(dtype, M, K, sizes):
     assert _abi.read_status() == 0
 
 
+@pytest.mark.parametrize('dtype', [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize('M,I,H', [(256, 512, 128), (200, 264, 72), (2048, 3072, 1024)])
+def test_down_proj_input_gradient_fused_with_swiglu_backward(dtype, M, I, H):
+    """dG, dU from the GEMM epilogue (dY never stored) against q3_gemm followed by q3_swiglu_bwd on the same
+    operands: the epilogue rounds dY to the storage type first, so the two agree to the last bit or, where the
+    compiler fuses the multiplies differently, to one unit in the last place; and against fp32 math."""
+    from qwen3_triton import _abi
+    from qwen3_triton.fused import mm_nn
+    dm = randn((M, H), 91, dtype).cuda()
+    wd = randn((H, I), 92, dtype, scale=0.05).cuda()
+    g, u = randn((M, I), 93, dtype).cuda(), randn((M, I), 94, dtype).cuda()
+    dg, du = torch.full_like(g, float('nan')), torch.full_like(u, float('nan'))
+    _abi.call('q3_down_dgrad_swiglu_bwd', dm.data_ptr(), wd.data_ptr(), g.data_ptr(), u.data_ptr(), dg.data_ptr(),
+              du.data_ptr(), M, I, H, _abi.dt(dtype), _abi.status_word(dm.device).data_ptr(), _abi.stream())
+    dy = mm_nn(dm, wd)
+    dg2, du2 = torch.empty_like(g), torch.empty_like(u)
+    _abi.call('q3_swiglu_bwd', g.data_ptr(), u.data_ptr(), dy.data_ptr(), dg2.data_ptr(), du2.data_ptr(), g.numel(),
+              _abi.dt(dtype), _abi.stream())
+    ulp = 2 ** -7 if dtype == torch.bfloat16 else 2 ** -10
+    for a, b in ((dg, dg2), (du, du2)):
+        assert torch.isfinite(a).all()
+        assert float(((a.float() - b.float()).abs() / (b.float().abs() + 1e-6)).max()) <= 2 * ulp
+    dy32 = ref_mm(dm, wd).to(dtype).float()
+    gf, uf = g.float().cpu(), u.float().cpu()
+    sg = torch.sigmoid(gf)
+    close(dg, (dy32 * uf * sg * (1 + gf * (1 - sg))).to(dtype), scale=H ** 0.5 * 0.05, what='dG')
+    close(du, (dy32 * gf * sg).to(dtype), scale=H ** 0.5 * 0.05, what='dU')
+    assert _abi.read_status() == 0
+
+
 @pytest.mark.parametrize('out', [torch.bfloat16, torch.float16, torch.float32])
 @pytest.mark.parametrize('M,N,K', [(256, 512, 128), (200, 264, 72), (2048, 4096, 1024)])
 def test_accumulating_epilogue(out, M, N, K):
