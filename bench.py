@@ -157,7 +157,10 @@ def run_reference(args):
     line = {"impl": "reference", "metric": METRIC, "value": tps, "unit": UNIT, "n_gpus": args.gpus, "steps": steps,
             "warmup": warmup, "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "f32", "data": "synthetic",
-            "config": {"workload": "qwen3-8b 4-layer slice fwd+bwd+AdamW (CPU sample 1x%d tokens)" % sample},
+            "config": {"workload": "qwen3-8b 4-layer slice fwd+bwd+AdamW (CPU sample 1x%d tokens)" % sample,
+                       "note": "the CPU arm always times the 4-layer slice (BASELINE config 4); the full 36-layer model "
+                               "of config 5 needs ~130 GB of host memory for fp32 weights, gradients and moments and "
+                               "would run about 9x fewer tokens/s, so at N>1 this line is an upper bound for the CPU"},
             "cpu_baseline": {"value": tps, "unit": UNIT, "cores": cores, "kind": "port",
                              "sample": f"oracle model, 4 layers, 1 x {sample} tokens per step, median of {steps}"},
             "e2e": {"value": tps, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
