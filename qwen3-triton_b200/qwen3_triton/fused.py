@@ -100,12 +100,6 @@ def mm_nn_acc(out, dy, w):
     return out
 
 
-def _add(a, b):
-    out = torch.empty_like(a)
-    _abi.call('q3_residual_add', a.data_ptr(), b.data_ptr(), out.data_ptr(), a.numel(), _abi.dt(a.dtype), _abi.stream())
-    return out
-
-
 def _norm_fwd(x, delta, w, eps):
     """(h, x_sum, inv): h = RMSNorm(x + delta) * w; x_sum = x + delta (x itself when delta is None)."""
     rows, hdim = x.shape
