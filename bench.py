@@ -216,9 +216,27 @@ def run_ours(args):
     device = torch.device("cuda", 0)
     torch.cuda.set_device(device)
     counter = Counter()
-    layers, batch, seq = 4, 4, 2048
-    cfg = slice_config(layers)
-    model, masters, opt = build_single_gpu(cfg, device)
+    # N=1 workload: the full 36-layer Qwen3-8B at the per-GPU microbatch of config 5 (1 x 2048) when it fits this GPU
+    # (fp32 masters + moments 98 GB, bf16 working copies and gradients 33 GB, activations 6 GB), else the 4-layer
+    # slice of config 4 (4 x 2048). Q3_BENCH_N1 = "full" | "slice" forces one.
+    choice = os.environ.get("Q3_BENCH_N1", "auto")
+    free_gib = torch.cuda.mem_get_info(device)[0] / 2 ** 30
+    want_full = choice == "full" or (choice == "auto" and free_gib >= 160)
+    model = masters = opt = None
+    if want_full:
+        layers, batch, seq = 36, 1, 2048
+        try:
+            cfg = slice_config(layers)
+            model, masters, opt = build_single_gpu(cfg, device)
+        except torch.cuda.OutOfMemoryError:
+            model = masters = opt = None
+            import gc
+            gc.collect()
+            torch.cuda.empty_cache()
+    if model is None:
+        layers, batch, seq = 4, 4, 2048
+        cfg = slice_config(layers)
+        model, masters, opt = build_single_gpu(cfg, device)
     gen = torch.Generator().manual_seed(3)
     nbatches = args.warmup + args.steps
     host_ids = [torch.randint(0, cfg.vocab_size, (batch, seq), generator=gen).pin_memory() for _ in range(min(nbatches, 8))]
@@ -230,6 +248,7 @@ def run_ours(args):
         out.loss.backward()
         masters.collect_grads()
         opt.step()
+        masters.release_grads()
         return out.loss
 
     for i in range(args.warmup):
@@ -286,9 +305,13 @@ def run_ours(args):
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic",
-        "config": {"workload": "qwen3-8b 4-layer slice fwd+bwd+AdamW, microbatch 4x2048 (BASELINE config 4)",
-                   "global_batch": batch, "seq_len": seq, "parallelism": "single", "l2": "inputs+weights >> L2 (4 GB bf16 weights)",
-                   "attention_path": "see kernel census", "mfu_of_%s_peak" % peak_kind: mfu, "last_loss": last},
+        "config": {"workload": ("qwen3-8b full 36-layer model on one GPU, fwd+bwd+AdamW, microbatch 1x2048 (the per-GPU "
+                                "workload of BASELINE config 5, no sharding)" if layers == 36 else
+                                "qwen3-8b 4-layer slice fwd+bwd+AdamW, microbatch 4x2048 (BASELINE config 4)"),
+                   "global_batch": batch, "seq_len": seq, "parallelism": "single",
+                   "l2": "inputs+weights >> L2 (%d GB bf16 weights)" % (16 if layers == 36 else 4),
+                   "attention_path": "see kernel census", "mfu_of_%s_peak" % peak_kind: mfu, "last_loss": last,
+                   "peak_memory_gb": round(torch.cuda.max_memory_allocated() / 2 ** 30, 1)},
         "e2e": {"value": tokens / (e2e_ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": batch * seq * 8,
                 "d2h_bytes_per_step": 4},
         "gpu_launches": launches,

@@ -239,10 +239,11 @@ int q3_adamw_multi(const int64_t* meta, float* coeff, int64_t n_tensors, int64_t
  * {param fp32, grad fp32 or 0, exp_avg, exp_avg_sq, step, numel, first_block, grad lowp or 0, working-copy lowp or 0}.
  * When the low-precision gradient pointer is set it is read directly (no fp32 staging copy); when the working-copy
  * pointer is set the updated parameter is also written there in `lowp_dtype` (bf16/fp16). Same update math.
+ * all_rows_lowp = 1 promises that every row has both low-precision pointers (selects a leaner kernel).
  * Fuses the reference's cast passes (qwen3_triton/runtime/ops.py:53-58,193-202) into runtime/adamw.py:34-61. */
 int q3_adamw_multi_mp(const int64_t* meta, float* coeff, int64_t n_tensors, int64_t total_blocks, int block_elems,
-                      int lowp_dtype, double lr, double beta1, double beta2, double weight_decay, double eps,
-                      q3_stream_t stream);
+                      int lowp_dtype, int all_rows_lowp, double lr, double beta1, double beta2, double weight_decay,
+                      double eps, q3_stream_t stream);
 
 /* ---- FSDP pack / unpack -------------------------------------------------------------------------------------- */
 

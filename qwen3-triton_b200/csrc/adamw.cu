@@ -98,8 +98,10 @@ __global__ void __launch_bounds__(256) adamw_update_kernel(const int64_t* __rest
 // updated parameter may also be written as a bf16/fp16 working copy, so a single-GPU mixed-precision step needs
 // neither a gradient-upcast pass nor a master->working cast pass. Table: int64[rows][9] =
 // {p, g_fp32 (or 0), m, v, step, numel, first_block, g_lowp (or 0), p_lowp (or 0)}.
-template <typename L>
-__global__ void __launch_bounds__(256) adamw_update_mp_kernel(const int64_t* __restrict__ meta,
+// BOTH: every row has a low-precision gradient and a low-precision copy (the single-GPU mixed-precision step): no
+// fp32 gradient pointer, no per-row branches, 48 registers and five CTAs per SM.
+template <typename L, bool BOTH>
+__global__ void __launch_bounds__(256, BOTH ? 5 : 4) adamw_update_mp_kernel(const int64_t* __restrict__ meta,
                                                               const float* __restrict__ coeff, int64_t rows, double lr,
                                                               double b1, double b2, double decay, double eps,
                                                               int block_elems) {
@@ -111,7 +113,7 @@ __global__ void __launch_bounds__(256) adamw_update_mp_kernel(const int64_t* __r
   }
   const int64_t r = lo;
   float* __restrict__ p = reinterpret_cast<float*>(meta[r * 9 + 0]);
-  const float* __restrict__ g32 = reinterpret_cast<const float*>(meta[r * 9 + 1]);
+  const float* __restrict__ g32 = BOTH ? nullptr : reinterpret_cast<const float*>(meta[r * 9 + 1]);
   float* __restrict__ m = reinterpret_cast<float*>(meta[r * 9 + 2]);
   float* __restrict__ v = reinterpret_cast<float*>(meta[r * 9 + 3]);
   const L* __restrict__ glo = reinterpret_cast<const L*>(meta[r * 9 + 7]);
@@ -126,20 +128,27 @@ __global__ void __launch_bounds__(256) adamw_update_mp_kernel(const int64_t* __r
   if ((bits & 15u) == 0) {
     // same shape as the fp32-gradient kernel: 4 elements per thread per iteration, one 16-byte access on each fp32
     // array and one 8-byte access on each 16-bit array
-    const int64_t vend = begin + ((end - begin) & ~(int64_t)3);
-    for (int64_t i = begin + threadIdx.x * 4; i < vend; i += blockDim.x * 4) {
+    // 32-bit offsets from the chunk's base pointers keep the loop at 48 registers
+    const int vspan = (int)(end - begin) & ~3;
+    const int64_t vend = begin + vspan;
+    float* __restrict__ pb = p + begin;
+    float* __restrict__ mb = m + begin;
+    float* __restrict__ vb = v + begin;
+    const L* __restrict__ gb = glo + begin;
+    L* __restrict__ lb = plo + begin;
+    for (int i = threadIdx.x * 4; i < vspan; i += 256 * 4) {
       float pp[4], mm[4], vv[4], gg[4];
-      *reinterpret_cast<float4*>(pp) = *reinterpret_cast<const float4*>(p + i);
-      *reinterpret_cast<float4*>(mm) = *reinterpret_cast<const float4*>(m + i);
-      *reinterpret_cast<float4*>(vv) = *reinterpret_cast<const float4*>(v + i);
-      if (glo != nullptr) VecIO<L, 4>::load(glo + i, gg);
-      else *reinterpret_cast<float4*>(gg) = *reinterpret_cast<const float4*>(g32 + i);
+      *reinterpret_cast<float4*>(pp) = *reinterpret_cast<const float4*>(pb + i);
+      *reinterpret_cast<float4*>(mm) = *reinterpret_cast<const float4*>(mb + i);
+      *reinterpret_cast<float4*>(vv) = *reinterpret_cast<const float4*>(vb + i);
+      if (BOTH || glo != nullptr) VecIO<L, 4>::load(gb + i, gg);
+      else *reinterpret_cast<float4*>(gg) = *reinterpret_cast<const float4*>(g32 + begin + i);
 #pragma unroll
       for (int e = 0; e < 4; ++e) adamw_one(pp[e], gg[e], mm[e], vv[e], lr, b1, b2, decay, eps, bc2, size);
-      *reinterpret_cast<float4*>(p + i) = *reinterpret_cast<float4*>(pp);
-      *reinterpret_cast<float4*>(m + i) = *reinterpret_cast<float4*>(mm);
-      *reinterpret_cast<float4*>(v + i) = *reinterpret_cast<float4*>(vv);
-      if (plo != nullptr) VecIO<L, 4>::store(plo + i, pp);
+      *reinterpret_cast<float4*>(pb + i) = *reinterpret_cast<float4*>(pp);
+      *reinterpret_cast<float4*>(mb + i) = *reinterpret_cast<float4*>(mm);
+      *reinterpret_cast<float4*>(vb + i) = *reinterpret_cast<float4*>(vv);
+      if (BOTH || plo != nullptr) VecIO<L, 4>::store(lb + i, pp);
     }
     for (int64_t i = vend + threadIdx.x; i < end; i += blockDim.x) {
       float pp = p[i], mm = m[i], vv = v[i];
@@ -175,20 +184,20 @@ __global__ void adamw_prepare9_kernel(const int64_t* __restrict__ meta, float* _
 using namespace q3;
 
 extern "C" int q3_adamw_multi_mp(const int64_t* meta, float* coeff, int64_t n_tensors, int64_t total_blocks,
-                                 int block_elems, int lowp_dtype, double lr, double beta1, double beta2,
-                                 double weight_decay, double eps, q3_stream_t stream) {
+                                 int block_elems, int lowp_dtype, int all_rows_lowp, double lr, double beta1,
+                                 double beta2, double weight_decay, double eps, q3_stream_t stream) {
   if (!meta || !coeff) return Q3_ERR_ARG;
   if (n_tensors < 1 || total_blocks < 1 || total_blocks > 2147483647LL || block_elems < 256 || (block_elems & 7))
     return Q3_ERR_SHAPE;
   if (lowp_dtype != Q3_BF16 && lowp_dtype != Q3_F16) return Q3_ERR_DTYPE;
   cudaStream_t st = (cudaStream_t)stream;
   adamw_prepare9_kernel<<<(int)cdiv(n_tensors, 128), 128, 0, st>>>(meta, coeff, n_tensors, lr, beta1, beta2);
-  if (lowp_dtype == Q3_BF16)
-    adamw_update_mp_kernel<__nv_bfloat16><<<(unsigned)total_blocks, 256, 0, st>>>(meta, coeff, n_tensors, lr, beta1, beta2,
-                                                                                   weight_decay, eps, block_elems);
-  else
-    adamw_update_mp_kernel<__half><<<(unsigned)total_blocks, 256, 0, st>>>(meta, coeff, n_tensors, lr, beta1, beta2,
-                                                                            weight_decay, eps, block_elems);
+#define Q3_MP(L, BOTH)                                                                                              \
+  adamw_update_mp_kernel<L, BOTH><<<(unsigned)total_blocks, 256, 0, st>>>(meta, coeff, n_tensors, lr, beta1, beta2, \
+                                                                           weight_decay, eps, block_elems)
+  if (lowp_dtype == Q3_BF16) { if (all_rows_lowp) Q3_MP(__nv_bfloat16, true); else Q3_MP(__nv_bfloat16, false); }
+  else { if (all_rows_lowp) Q3_MP(__half, true); else Q3_MP(__half, false); }
+#undef Q3_MP
   return launch_status();
 }
 

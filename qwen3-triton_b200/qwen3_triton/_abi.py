@@ -60,7 +60,7 @@ SIGNATURES = {
     "q3_vce_finish": (I, [P, P, P, P, P, P, P, L, L, L, L, L, P, P]),
     "q3_vce_accumulate": (I, [P, I, P, L, L, I, P]),
     "q3_adamw_multi": (I, [P, P, L, L, I, D, D, D, D, D, P]),
-    "q3_adamw_multi_mp": (I, [P, P, L, L, I, I, D, D, D, D, D, P]),
+    "q3_adamw_multi_mp": (I, [P, P, L, L, I, I, I, D, D, D, D, D, P]),
     "q3_multi_copy": (I, [P, L, L, I, I, P]),
     "q3_gemm": (I, [P, L, L, P, L, L, P, L, L, L, I, I, P, P]),
     "q3_gemm_acc_f32": (I, [P, L, L, P, L, L, P, L, L, L, I, P, P]),

@@ -159,8 +159,8 @@ class TritonAdamW(torch.optim.Optimizer):
             b1, b2 = group['betas']
             if mixed:
                 _abi.call('q3_adamw_multi_mp', meta.data_ptr(), coeff.data_ptr(), len(rows), blocks, self.block,
-                          lowp.pop(), float(group['lr']), float(b1), float(b2), float(group['weight_decay']),
-                          float(group['eps']), _abi.stream())
+                          lowp.pop(), int(all(row[7] and row[8] for row in rows)), float(group['lr']), float(b1),
+                          float(b2), float(group['weight_decay']), float(group['eps']), _abi.stream())
             else:
                 _abi.call('q3_adamw_multi', meta.data_ptr(), coeff.data_ptr(), len(rows), blocks, self.block,
                           float(group['lr']), float(b1), float(b2), float(group['weight_decay']), float(group['eps']),

@@ -49,6 +49,12 @@ class MasterWeights:
     def parameters(self):
         return self.masters
 
+    def release_grads(self):
+        """Drop the low-precision gradients handed to the optimizer (call after optimizer.step()): otherwise they stay
+        alive through the next backward, next to the new ones."""
+        for m in self.masters:
+            m.q3_lowp_grad = None
+
     @torch.no_grad()
     def sync_working(self):
         """master (fp32) -> working (bf16)."""
