@@ -205,7 +205,7 @@ def build_single_gpu(cfg, device):
         # "1": hidden -> loss without logits in HBM (one extra logits GEMM in backward; measured 8 ms slower per step here)
         model.fused_loss = os.environ.get("Q3_BENCH_FUSED_LOSS", "0") == "1"
     masters = MasterWeights(model).fuse_into_optimizer()
-    opt = TritonAdamW(masters.parameters(), lr=1e-4, betas=(0.9, 0.95), weight_decay=0.1)
+    opt = TritonAdamW(masters.parameters(), lr=1e-4, betas=(0.9, 0.95), weight_decay=0.1, block=16384)
     return model, masters, opt
 
 
@@ -401,7 +401,7 @@ def run_fsdp(args):
     hooks = configure(model, comm, pack_gradients_off_compute_stream=os.environ.get("Q3_BENCH_PACK_SIDE", "0") == "1")
     decoder = [p for n, p in model.named_parameters() if not n.startswith("lm_head.")]
     opt = TritonAdamW([dict(params=decoder), dict(params=[model.lm_head.weight])], lr=1e-4, betas=(0.9, 0.95),
-                      weight_decay=0.1)
+                      weight_decay=0.1, block=16384)
     gen = torch.Generator().manual_seed(100 + rank)
     host_ids = [torch.randint(0, cfg.vocab_size, (batch, seq), generator=gen).pin_memory() for _ in range(8)]
     dev_ids = [h.to(device) for h in host_ids]
