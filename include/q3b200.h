@@ -101,8 +101,9 @@ int q3_rmsnorm_bwd(const void* x, const void* weight, const void* dy, const floa
  * memory-pool callback, in a host that fixes its whole HBM plan up front, in a latency-critical loop that must
  * not risk cudaMalloc/cudaFree): the partial-row scratch is a fixed 16 MiB device array inside the library
  * instead of a caller workspace, and the call allocates nothing. Limit: H <= 4096 (Q3_ERR_LIMIT beyond that).
- * The first call on each device resolves the array's device address; make that call before starting any
- * stream capture. All calls on a device share the array, so calls that overlap on the GPU (different streams)
+ * The first call on each device resolves the array's device address and may make the driver load the module
+ * that holds the array: make that call during set-up, before the region in which nothing may be allocated
+ * and before starting any stream capture. All calls on a device share the array, so calls that overlap on the GPU (different streams)
  * race: serialise them. Same results as q3_rmsnorm_bwd.
  * This entry point has no counterpart in the reference. */
 int q3_rmsnorm_bwd_noalloc(const void* x, const void* weight, const void* dy, const float* inv_rms, void* dx,
@@ -368,6 +369,25 @@ int q3_attn_bwd_bshd(const void* q, const void* k, const void* v, const void* ou
 
 /* 1 if the tensor-core attention kernels run for these arguments, else 0. */
 int q3_attn_path(const void* q, const void* k, const void* v, const void* out, int64_t D, int dtype);
+
+/* The dK/dV pass of q3_attn_bwd at head_dim 128 has two schedules: one CTA per key tile that accumulates the gradients
+ * of the whole query-head group in tensor memory (returns 1), or, on grids too small to fill the GPU, one CTA per
+ * query head followed by a fixed-order reduction (returns G = Hq/Hkv; the reference always does the latter:
+ * qwen3_triton/kernels/attention_precision.py:84-143). q3_attn_bwd_group_split tells which one runs for a shape;
+ * q3_attn_bwd_group_policy(0 | 1 | 2) selects by grid size (default) / always the first / always the second,
+ * process-wide, and returns the previous setting (any other argument only queries). Both give the same result
+ * up to fp32 summation order; the workspace query follows the setting. */
+int q3_attn_bwd_group_split(int64_t B, int64_t Hq, int64_t Hkv, int64_t S);
+int q3_attn_bwd_group_policy(int policy);
+
+/* ---- self-test ------------------------------------------------------------------------------ */
+
+/* Makes a bounded wait run out on purpose, the harmless way: one CTA waits on a barrier nothing arrives at, with a
+ * limit of limit_ns (1 us .. 100 ms). The kernel must come back by itself with Q3_STATUS_WAIT_TIMEOUT OR-ed into
+ * *status and outcome[0] = outcome[1] = 0 (both warps gave up: the first by its time limit, the second through the
+ * CTA-wide abort flag). The same mbar_wait guards every barrier in the tensor-core and bulk-copy kernels. Stands in
+ * for the reference's timed-out barrier check, scripts/check_triton_collectives_v14.py:127-133. */
+int q3_selftest_wait_timeout(int64_t limit_ns, int* status, int* outcome, q3_stream_t stream);
 
 #ifdef __cplusplus
 }

@@ -19,6 +19,7 @@ int attn_bwd_tc(const void* q, const void* k, const void* v, const void* dout, c
                 void* dq, void* dk, void* dv, float* partials, int64_t B, int64_t Hq, int64_t Hkv, int64_t S, float scale,
                 int dtype, int layout, int* status, cudaStream_t st);
 int attn_bwd_group_split(int64_t B, int64_t Hq, int64_t Hkv, int64_t S);
+int attn_bwd_set_group_policy(int policy);
 int attn_delta_layout(const void* out, const void* dout, float* delta, int64_t B, int64_t H, int64_t S, int64_t D,
                       int layout, int dtype, cudaStream_t st);
 bool attn_tc_available();
@@ -52,6 +53,18 @@ extern "C" int q3_attn_fwd(const void* q, const void* k, const void* v, void* ou
   if (tc_eligible(q, k, v, out, D, dtype)) return attn_fwd_tc(q, k, v, out, lse, B, Hq, Hkv, S, (float)scale, dtype, 0, status, st);
   return attn_fwd_simt(q, k, v, out, lse, B, Hq, Hkv, S, D, (float)scale, dtype, st);
 }
+
+// Which of the two dK/dV schedules q3_attn_bwd runs at head_dim 128 for this shape: 1 = one CTA per key tile sums the
+// whole query-head group in tensor memory; G = Hq/Hkv = one CTA per query head and a fixed-order reduction.
+extern "C" int q3_attn_bwd_group_split(int64_t B, int64_t Hq, int64_t Hkv, int64_t S) {
+  if (B < 1 || Hq < 1 || Hkv < 1 || S < 1 || Hq % Hkv) return Q3_ERR_SHAPE;
+  return attn_bwd_group_split(B, Hq, Hkv, S);
+}
+
+// Tuning / test switch for that choice (process-wide): 0 by grid size (default), 1 always group-accumulate, 2 always
+// per-head split. Returns the previous value; other values only query. Change it only while no backward is in flight
+// between its workspace query and its launch.
+extern "C" int q3_attn_bwd_group_policy(int policy) { return attn_bwd_set_group_policy(policy); }
 
 // delta = rowsum(dO * O) [B,Hq,S] fp32, then (small grids only) per-query-head fp32 partials of dK and dV
 static int64_t delta_bytes(int64_t B, int64_t Hq, int64_t S) { return ((B * Hq * S * 4 + 255) / 256) * 256; }

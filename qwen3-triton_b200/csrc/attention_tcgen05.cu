@@ -842,23 +842,29 @@ __global__ void attn_dkdv_reduce_kernel(const float* __restrict__ part, T* __res
   }
 }
 
-template <typename K> int configure_smem(K kern, int bytes, bool* done) {
-  if (!*done) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
-    if (e != cudaSuccess) return Q3_ERR_CUDA - (int)e;
-    *done = true;
-  }
-  return Q3_OK;
+template <typename K> int configure_smem(K kern, int bytes, DeviceFlags* done) {
+  return ensure_dynamic_smem(kern, bytes, done);
 }
 
 }  // namespace tc
 
 bool attn_tc_available() { return true; }
 
+// How the dK/dV kernel covers a query-head group: 0 = by grid size (below), 1 = always one CTA per key tile that
+// accumulates the whole group in tensor memory, 2 = always one CTA per query head plus the reduce kernel.
+static int g_group_policy = 0;
+int attn_bwd_set_group_policy(int policy) {
+  const int old = g_group_policy;
+  if (policy >= 0 && policy <= 2) g_group_policy = policy;
+  return old;
+}
+
 // One CTA per query head (plus a reduce kernel) when one CTA per key tile would leave SMs idle.
 int attn_bwd_group_split(int64_t B, int64_t Hq, int64_t Hkv, int64_t S) {
   const int64_t G = Hq / Hkv, ctas = B * Hkv * cdiv(S, tc::TILE);
-  return (G > 1 && ctas < 2 * (int64_t)sm_count()) ? (int)G : 1;
+  if (G <= 1 || g_group_policy == 1) return 1;
+  if (g_group_policy == 2) return (int)G;
+  return ctas < 2 * (int64_t)sm_count() ? (int)G : 1;
 }
 
 namespace {
@@ -891,11 +897,11 @@ int attn_fwd_tc(const void* q, const void* k, const void* v, void* out, float* l
   p.status = status;
   dim3 grid((unsigned)(B * Hq), (unsigned)cdiv(S, TILE));
   if (bf16) {
-    static bool cfg = false;
+    static DeviceFlags cfg = {};
     if ((rc = configure_smem(attn_fwd_tc_kernel<__nv_bfloat16>, kFwdSmem, &cfg)) != Q3_OK) return rc;
     attn_fwd_tc_kernel<__nv_bfloat16><<<grid, kFwdThreads, kFwdSmem, st>>>(tmQ, tmK, tmV, p);
   } else {
-    static bool cfg = false;
+    static DeviceFlags cfg = {};
     if ((rc = configure_smem(attn_fwd_tc_kernel<__half>, kFwdSmem, &cfg)) != Q3_OK) return rc;
     attn_fwd_tc_kernel<__half><<<grid, kFwdThreads, kFwdSmem, st>>>(tmQ, tmK, tmV, p);
   }
@@ -931,7 +937,7 @@ int attn_bwd_tc(const void* q, const void* k, const void* v, const void* dout, c
   const int64_t kv_rows = B * Hkv * S;
   const int red_grid = (int)std::min<int64_t>(cdiv(kv_rows * (AD / 4), 256), (int64_t)sm_count() * 8);
   if (bf16) {
-    static bool c1 = false, c2 = false;
+    static DeviceFlags c1 = {}, c2 = {};
     if ((rc = configure_smem(attn_dq_tc_kernel<__nv_bfloat16>, kDqSmem, &c1)) != Q3_OK) return rc;
     if ((rc = configure_smem(attn_dkdv_tc_kernel<__nv_bfloat16>, kDkdvSmem, &c2)) != Q3_OK) return rc;
     attn_dkdv_tc_kernel<__nv_bfloat16><<<gk, kAttnThreads, kDkdvSmem, st>>>(tmQs, tmK, tmV, tmDOs, p);
@@ -940,7 +946,7 @@ int attn_bwd_tc(const void* q, const void* k, const void* v, const void* dout, c
                                                                      (int)Hkv, (int)S, sk.ss, sk.hs, sk.bs, scale);
     attn_dq_tc_kernel<__nv_bfloat16><<<gq, kDqThreads, kDqSmem, st>>>(tmQ, tmK, tmV, tmDO, p);
   } else {
-    static bool c1 = false, c2 = false;
+    static DeviceFlags c1 = {}, c2 = {};
     if ((rc = configure_smem(attn_dq_tc_kernel<__half>, kDqSmem, &c1)) != Q3_OK) return rc;
     if ((rc = configure_smem(attn_dkdv_tc_kernel<__half>, kDkdvSmem, &c2)) != Q3_OK) return rc;
     attn_dkdv_tc_kernel<__half><<<gk, kAttnThreads, kDkdvSmem, st>>>(tmQs, tmK, tmV, tmDOs, p);

@@ -31,6 +31,20 @@ inline int sm_count() {
   return cached[dev];
 }
 
+// cudaFuncSetAttribute(MaxDynamicSharedMemorySize) applies to the current device only, so a kernel's "already
+// configured" note is kept per device. One DeviceFlags object (a function-local static) per kernel instantiation.
+struct DeviceFlags { bool done[64]; };
+
+template <typename K> inline int ensure_dynamic_smem(K kern, int bytes, DeviceFlags* flags) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) dev = -1;
+  if (dev >= 0 && flags->done[dev]) return Q3_OK;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+  if (e != cudaSuccess) return Q3_ERR_CUDA - (int)e;
+  if (dev >= 0) flags->done[dev] = true;
+  return Q3_OK;
+}
+
 inline int launch_status() {
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? Q3_OK : Q3_ERR_CUDA - (int)e;

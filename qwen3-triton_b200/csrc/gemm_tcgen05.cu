@@ -541,12 +541,8 @@ int launch_gemm(const Operand& A, const Operand& B, const void* b2, GemmParams& 
   const int64_t tiles = (int64_t)p.tiles_m * p.tiles_n;
   const int grid = (int)(tiles < sm_count() ? tiles : sm_count());
   auto kern = gemm_tc_kernel<BN, TO, EPI>;
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
-    if (e != cudaSuccess) return Q3_ERR_CUDA - (int)e;
-    configured = true;
-  }
+  static DeviceFlags configured = {};
+  if (int rc2 = ensure_dynamic_smem(kern, C::SMEM_BYTES, &configured); rc2 != Q3_OK) return rc2;
   kern<<<grid, kGemmThreads, C::SMEM_BYTES, st>>>(maps, p);
   return launch_status();
 }
@@ -603,12 +599,8 @@ int launch_grouped(int mode, int count, const void* const* a, const void* const*
   const int64_t tiles = (int64_t)p.tiles_m * p.tiles_n;
   const int grid = (int)(tiles < sm_count() ? tiles : sm_count());
   auto kern = gemm_tc_kernel<BN, TO, EPI_STORE>;
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
-    if (e != cudaSuccess) return Q3_ERR_CUDA - (int)e;
-    configured = true;
-  }
+  static DeviceFlags configured = {};
+  if (int rc2 = ensure_dynamic_smem(kern, C::SMEM_BYTES, &configured); rc2 != Q3_OK) return rc2;
   kern<<<grid, kGemmThreads, C::SMEM_BYTES, st>>>(maps, p);
   return launch_status();
 }

@@ -49,7 +49,8 @@ __device__ __forceinline__ uint64_t global_ns() {
 constexpr uint64_t kWaitLimitNs = 2000000000ull;  // 2 s: far beyond any legitimate wait in these kernels
 
 // Bounded wait. Returns false if it gave up (own time limit reached, or another thread of the CTA did).
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                          uint64_t limit_ns = kWaitLimitNs) {
   uint64_t t0 = 0;
   for (uint32_t it = 0;; ++it) {
     if (mbar_try_wait(bar, parity)) return true;
@@ -58,7 +59,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
       if (*abort_flag) return false;
       const uint64_t now = global_ns();
       if (t0 == 0) t0 = now;
-      else if (now - t0 > kWaitLimitNs) { *abort_flag = 1; return false; }
+      else if (now - t0 > limit_ns) { *abort_flag = 1; return false; }
     }
   }
 }

@@ -84,6 +84,9 @@ SIGNATURES = {
     "q3_attn_fwd_bshd": (I, [P, P, P, P, P, L, L, L, L, L, D, I, P, P]),
     "q3_attn_bwd_bshd": (I, [P, P, P, P, P, P, P, P, P, P, L, L, L, L, L, L, D, I, P, P]),
     "q3_attn_path": (I, [P, P, P, P, L, I]),
+    "q3_attn_bwd_group_split": (I, [L, L, L, L]),
+    "q3_attn_bwd_group_policy": (I, [I]),
+    "q3_selftest_wait_timeout": (I, [L, P, P, P]),
 }
 
 _lib = None

@@ -39,6 +39,20 @@ def golden_tiny():
 
 
 @pytest.fixture(autouse=True)
+def _l2_log(request):
+    """With Q3_TEST_L2_LOG=<file>, append the largest relative L2 distance each test measured through helpers.close."""
+    import helpers
+    helpers.l2_seen.clear()
+    yield
+    path = helpers.l2_log_path()
+    if path and helpers.l2_seen:
+        what, worst = max(helpers.l2_seen, key=lambda t: t[1])
+        over = [w for w, _ in helpers.l2_seen if " OVER " in w]
+        with open(path, "a") as fh:
+            fh.write(f"{worst:.3e}\t{request.node.nodeid}\t{what}\t{';'.join(over)}\n")
+
+
+@pytest.fixture(autouse=True)
 def _status_clean():
     """After every GPU test the device status word must be clean (no out-of-range id, no timed-out wait)."""
     yield

@@ -4,7 +4,7 @@ import pytest
 import torch
 
 import recipe
-from helpers import close, randn
+from helpers import L2, L2_ATTENTION_GRAD, close, randn
 from oracle import ops as O
 
 pytestmark = pytest.mark.gpu
@@ -30,9 +30,9 @@ def test_attention_forward_backward(B, Hq, Hkv, S, D, dtype):
     # The saved output is rounded to `dtype`, so delta = rowsum(dO*O) carries that rounding into dS; a handful
     # of near-zero gradient elements then sit a few percent of the tensor scale away (the reference's own
     # attention-gradient tolerance is 8e-2 absolute). Relative term stays at the stated 2e-2.
-    close(qg.grad, dq.to(dtype), what='dq', atol_mult=5.0)
-    close(kg.grad, dk.to(dtype), what='dk', atol_mult=5.0)
-    close(vg.grad, dv.to(dtype), what='dv', atol_mult=5.0)
+    close(qg.grad, dq.to(dtype), what='dq', atol_mult=5.0, l2=L2_ATTENTION_GRAD[dtype])
+    close(kg.grad, dk.to(dtype), what='dk', atol_mult=5.0, l2=L2_ATTENTION_GRAD[dtype])
+    close(vg.grad, dv.to(dtype), what='dv', atol_mult=5.0, l2=L2_ATTENTION_GRAD[dtype])
 
 
 def test_attention_golden_and_lse(golden_ops):
@@ -45,12 +45,12 @@ def test_attention_golden_and_lse(golden_ops):
     _, lse_ref = O.attention(d['q'], d['k'], d['v'])
     torch.testing.assert_close(lse.cpu(), lse_ref, rtol=1e-4, atol=1e-4)
     dq, dk, dv = attention_backward_triton(q, k, v, do, lse=lse)
-    close(dq, golden_ops['attn_dq'])
-    close(dk, golden_ops['attn_dk'])
-    close(dv, golden_ops['attn_dv'])
+    close(dq, golden_ops['attn_dq'], l2=L2_ATTENTION_GRAD[dq.dtype])
+    close(dk, golden_ops['attn_dk'], l2=L2_ATTENTION_GRAD[dk.dtype])
+    close(dv, golden_ops['attn_dv'], l2=L2_ATTENTION_GRAD[dv.dtype])
     qg = q.clone().requires_grad_(True)
     attention_triton_autograd(qg, k, v).backward(do)
-    close(qg.grad, golden_ops['attn_dq'])
+    close(qg.grad, golden_ops['attn_dq'], l2=L2_ATTENTION_GRAD[qg.grad.dtype])
 
 
 def test_gqa_head_mapping_is_exact():
@@ -96,3 +96,97 @@ def test_token_major_layout_matches_head_major(B, Hq, Hkv, S):
               _abi.Q3_BF16, st, _abi.stream())
     dqh, dkh, dvh = attention_backward(qh, kh, vh, out_h, doh, lse_h, 128 ** -0.5)
     assert torch.equal(dq.transpose(1, 2), dqh) and torch.equal(dk.transpose(1, 2), dkh) and torch.equal(dv.transpose(1, 2), dvh)
+
+
+# ------------------------------------------------------------------------------------------------------------------
+# The two dK/dV schedules at head_dim 128. Small grids (fewer than two CTAs per SM) run one CTA per query head and a
+# fixed-order reduction; the shapes the training step and the attention benchmark use (batch x kv heads x key tiles
+# >= 296) run one CTA per key tile that accumulates the whole query-head group in tensor memory. Both are compared
+# with the oracle here, on long sequences (16 - 64 key tiles), and the test asserts which schedule ran.
+def _oracle_by_group(q, k, v, do):
+    """Oracle forward/backward one (batch, kv head) at a time: same math, [1, G, S, S] fp32 scores at once."""
+    B, Hq, S, D = q.shape
+    Hkv = k.shape[1]
+    G = Hq // Hkv
+    out, dq = torch.empty(B, Hq, S, D), torch.empty(B, Hq, S, D)
+    dk, dv = torch.empty(B, Hkv, S, D), torch.empty(B, Hkv, S, D)
+    for b in range(B):
+        for h in range(Hkv):
+            qs, ks, vs = q[b:b + 1, h * G:(h + 1) * G], k[b:b + 1, h:h + 1], v[b:b + 1, h:h + 1]
+            dos = do[b:b + 1, h * G:(h + 1) * G]
+            out[b, h * G:(h + 1) * G] = O.attention(qs, ks, vs)[0][0]
+            a, c, e = O.attention_backward(qs, ks, vs, dos)
+            dq[b, h * G:(h + 1) * G], dk[b, h], dv[b, h] = a[0], c[0, 0], e[0, 0]
+    return out, dq, dk, dv
+
+
+class _GroupPolicy:
+    def __init__(self, policy):
+        self.policy = policy
+
+    def __enter__(self):
+        from qwen3_triton import _abi
+        self.old = _abi.lib().q3_attn_bwd_group_policy(self.policy)
+
+    def __exit__(self, *exc):
+        from qwen3_triton import _abi
+        _abi.lib().q3_attn_bwd_group_policy(self.old)
+
+
+def _check_against_oracle(B, Hq, Hkv, S, dtype, expect_split):
+    from qwen3_triton import _abi
+    from qwen3_triton.kernels.attention import causal_attention
+    D = 128
+    assert _abi.lib().q3_attn_bwd_group_split(B, Hq, Hkv, S) == expect_split
+    q, k, v = randn((B, Hq, S, D), 31, dtype), randn((B, Hkv, S, D), 32, dtype), randn((B, Hkv, S, D), 33, dtype)
+    do = randn((B, Hq, S, D), 34, dtype)
+    qg, kg, vg = (t.cuda().requires_grad_(True) for t in (q, k, v))
+    out = causal_attention(qg, kg, vg)
+    out.backward(do.cuda())
+    assert _abi.read_status() == 0
+    ref, dq, dk, dv = _oracle_by_group(q, k, v, do)
+    close(out, ref.to(dtype), what='out')
+    close(qg.grad, dq.to(dtype), what='dq', atol_mult=5.0, l2=L2_ATTENTION_GRAD[dtype])
+    close(kg.grad, dk.to(dtype), what='dk', atol_mult=5.0, l2=L2_ATTENTION_GRAD[dtype])
+    close(vg.grad, dv.to(dtype), what='dv', atol_mult=5.0, l2=L2_ATTENTION_GRAD[dtype])
+    return qg.grad, kg.grad, vg.grad
+
+
+@pytest.mark.parametrize('B,Hq,Hkv,S', [(4, 32, 8, 1280), (3, 32, 8, 2048)])
+def test_backward_group_accumulating_schedule_at_training_shapes(B, Hq, Hkv, S):
+    """Grids of 320 and 384 key-tile CTAs: the schedule picked by size is the group-accumulating one."""
+    _check_against_oracle(B, Hq, Hkv, S, torch.bfloat16, expect_split=1)
+
+
+@pytest.mark.parametrize('S', [2048, 4096, 8192])
+@pytest.mark.parametrize('dtype', [torch.bfloat16, torch.float16])
+def test_backward_schedules_on_long_sequences(S, dtype):
+    """One query-head group (4 query heads on 1 kv head) of each sequence length the attention benchmark uses
+    (2048, 4096, 8192 = 16, 32, 64 key tiles), both schedules forced in turn; each against the oracle, and against
+    each other (they differ only in fp32 summation order)."""
+    if dtype == torch.float16 and S != 4096:
+        pytest.skip('fp16 covered at one length')
+    with _GroupPolicy(1):
+        a = _check_against_oracle(1, 4, 1, S, dtype, expect_split=1)
+    with _GroupPolicy(2):
+        b = _check_against_oracle(1, 4, 1, S, dtype, expect_split=4)
+    for x, y, name in zip(a, b, ('dq', 'dk', 'dv')):
+        close(x, y.float().cpu().to(dtype), what=name + ' schedules agree', l2=L2[dtype])
+
+
+@pytest.mark.parametrize('B,Hq,Hkv,S', [(1, 2, 2, 257), (2, 4, 4, 1024)])
+def test_backward_without_grouping_at_head_dim_128(B, Hq, Hkv, S):
+    """Hq == Hkv: a group is one head, so there is nothing to split."""
+    _check_against_oracle(B, Hq, Hkv, S, torch.bfloat16, expect_split=1)
+
+
+def test_group_policy_switch_round_trip():
+    from qwen3_triton import _abi
+    lib = _abi.lib()
+    assert lib.q3_attn_bwd_group_policy(-1) == 0            # query only
+    assert lib.q3_attn_bwd_group_split(1, 32, 8, 2048) == 4  # 128 CTAs on 148 SMs: per-head split
+    with _GroupPolicy(1):
+        assert lib.q3_attn_bwd_group_split(1, 32, 8, 2048) == 1
+        ws1 = lib.q3_attn_bwd_workspace_bytes(1, 32, 8, 2048, 128)
+    assert lib.q3_attn_bwd_workspace_bytes(1, 32, 8, 2048, 128) > ws1   # the split schedule needs fp32 partials
+    assert lib.q3_attn_bwd_group_policy(-1) == 0

@@ -4,7 +4,7 @@ CUDA-core fallback; all against fp32 torch.mm on the same bf16-quantised inputs.
 import pytest
 import torch
 
-from helpers import close, randn
+from helpers import close, randn, rel_l2
 from oracle import ops as O
 
 pytestmark = pytest.mark.gpu
@@ -56,7 +56,8 @@ def test_fp32_output_and_determinism():
 
 @pytest.mark.parametrize('dtype', [torch.bfloat16, torch.float16])
 @pytest.mark.parametrize('M,K,sizes', [(2048, 4096, (4096, 1024, 1024)), (300, 520, (192, 64, 320)), (129, 136, (448, 64)),
-                                       (2048, 1024, (3072, 3072))])
+                                       (2048, 1024, (3072, 3072)), (2048, 4096, (12288, 12288)),
+                                       (8192, 4096, (4096, 1024, 1024))])
 def test_grouped_linear_layers_equal_separate_gemms(dtype, M, K, sizes):
     """q/k/v- and gate/up-style groups in one launch: forward outputs and weight gradients bit-identical to the
     single GEMMs (same tiles, same k order), the summed input gradient equal to fp32 math on the same operands."""
@@ -80,7 +81,7 @@ def test_grouped_linear_layers_equal_separate_gemms(dtype, M, K, sizes):
 
 
 @pytest.mark.parametrize('dtype', [torch.bfloat16, torch.float16])
-@pytest.mark.parametrize('M,I,H', [(256, 512, 128), (200, 264, 72), (2048, 3072, 1024)])
+@pytest.mark.parametrize('M,I,H', [(256, 512, 128), (200, 264, 72), (2048, 3072, 1024), (2048, 12288, 4096)])
 def test_down_proj_input_gradient_fused_with_swiglu_backward(dtype, M, I, H):
     """dG, dU from the GEMM epilogue (dY never stored) against q3_gemm followed by q3_swiglu_bwd on the same
     operands: the epilogue rounds dY to the storage type first, so the two agree to the last bit or, where the
@@ -163,7 +164,7 @@ def test_linear_autograd(shape):
         linear(xg.transpose(0, 1), wg)
 
 
-@pytest.mark.parametrize('M,N,K', [(128, 128, 64), (200, 344, 256), (512, 1536, 1024), (64, 688, 256)])
+@pytest.mark.parametrize('M,N,K', [(128, 128, 64), (200, 344, 256), (512, 1536, 1024), (64, 688, 256), (2048, 12288, 4096)])
 def test_fused_gate_up_swiglu(M, N, K):
     from qwen3_triton import _abi
     from qwen3_triton.kernels.mlp import gate_up_swiglu
@@ -183,3 +184,71 @@ def test_fused_gate_up_swiglu(M, N, K):
     close(g_.grad, gr.grad.to(dt), what='dWg')
     close(u_.grad, ur.grad.to(dt), what='dWu')
     close(gate_up_swiglu_triton(x.cuda(), wg.cuda(), wu.cuda()), y, what='ops.triton')
+
+
+# ------------------------------------------------------------------------------------------------------------------
+# The GEMM shapes of the Qwen3-8B training step (tokens M = 2048 per GPU, or 8192 for the 4-layer slice):
+# attention projections 4096 x 4096, gate/up 12288 x 4096, down 4096 x 12288 and the vocabulary head 151936 x 4096
+# (593.5 tiles of 256 columns: the half-full last tile; 2374 k-blocks as a contraction). The GPU computes the whole
+# product; the fp32 CPU reference is taken on every 37th output row (three or more rows of every 128-row tile, all
+# columns, so every output tile is touched) plus the last row.
+LAYER_SHAPES = [(2048, 4096, 4096), (2048, 12288, 4096), (2048, 4096, 12288), (2048, 151936, 4096),
+                (8192, 4096, 4096), (8192, 12288, 4096), (8192, 4096, 12288), (8192, 151936, 4096)]
+_operands = {}
+
+
+def _operand(shape, seed, scale=1.0):
+    """bf16 operand, generated once per (shape, seed) on the CPU and kept on both sides."""
+    key = (shape, seed)
+    if key not in _operands:
+        if len(_operands) > 6:
+            _operands.clear()
+        host = randn(shape, seed, torch.bfloat16, scale)
+        _operands[key] = (host, host.cuda())
+    return _operands[key]
+
+
+def _rows(n):
+    idx = torch.arange(0, n, 37)
+    return torch.cat([idx, torch.tensor([n - 1])]) if idx[-1] != n - 1 else idx
+
+
+@pytest.mark.parametrize('M,N,K', LAYER_SHAPES)
+def test_layer_shapes_forward(M, N, K):
+    from qwen3_triton.kernels.linear import gemm_path, matmul
+    (x, xd), (w, wd) = _operand((M, K), 61), _operand((N, K), 62, 0.02)
+    assert gemm_path(xd, wd.t()) == 'tcgen05'
+    y = matmul(xd, wd.t())
+    r = _rows(M)
+    close(y[r.cuda()], (x[r].float() @ w.float().t()).to(torch.bfloat16), what='X*W^T')
+
+
+@pytest.mark.parametrize('M,N,K', LAYER_SHAPES)
+def test_layer_shapes_input_gradient(M, N, K):
+    """dX [M,K] = dY [M,N] * W [N,K]: the contraction runs over the layer's output width N."""
+    from qwen3_triton.kernels.linear import gemm_path, matmul
+    (dy, dyd), (w, wd) = _operand((M, N), 63), _operand((N, K), 62, 0.02)
+    assert gemm_path(dyd, wd) == 'tcgen05'
+    dx = matmul(dyd, wd)
+    r = _rows(M)
+    close(dx[r.cuda()], (dy[r].float() @ w.float()).to(torch.bfloat16), what='dY*W')
+
+
+@pytest.mark.parametrize('M,N,K', LAYER_SHAPES)
+@pytest.mark.parametrize('out', [torch.bfloat16, torch.float32])
+def test_layer_shapes_weight_gradient(M, N, K, out):
+    """dW [N,K] = dY [M,N]^T * X [M,K]: both operands token-major, contraction over the tokens; bf16 result as the
+    training step stores it and fp32 result as the vocabulary head accumulates it."""
+    from qwen3_triton.kernels.linear import gemm_path, matmul
+    if out == torch.float32 and N != 151936:
+        pytest.skip('fp32 weight gradients are used for the vocabulary head only')
+    (dy, dyd), (x, xd) = _operand((M, N), 63), _operand((M, K), 61)
+    assert gemm_path(dyd.t(), xd) == 'tcgen05'
+    dw = matmul(dyd.t(), xd, output_dtype=out)
+    r = _rows(N)
+    ref = dy[:, r].float().t() @ x.float()
+    if out == torch.float32:
+        torch.testing.assert_close(dw[r.cuda()].cpu(), ref, rtol=1e-3, atol=1e-3 * float(ref.abs().mean()))
+        assert rel_l2(dw[r.cuda()], ref) < 1e-4
+    else:
+        close(dw[r.cuda()], ref.to(torch.bfloat16), what='dY^T*X')
