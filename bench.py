@@ -1,16 +1,22 @@
 #!/usr/bin/env python
 """Training-step throughput of the Qwen3-8B-shaped hot path on B200, one JSON line on stdout.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--out DIR]
 
-N = 1: BASELINE config 4 - a 4-layer slice of the Qwen3-8B architecture (hidden 4096, 32/8 heads, head_dim 128,
-intermediate 12288, vocab 151936, untied lm_head), bf16 compute with fp32 master weights, microbatch 4 x 2048,
-forward + cross-entropy + backward + AdamW every step, synthetic uniform token ids, weights ~ N(0, 0.02).
-N > 1 (launched with torch.distributed.run): the full 36-layer model under FSDP2, microbatch 1 x 2048 per GPU.
+Workload (metric: training tokens per second, Qwen3-8B shapes, microbatch 1 x 2048 tokens per GPU, forward +
+cross-entropy + backward + AdamW every step, bf16 compute with fp32 master weights and moments, seeded synthetic
+token ids, weights ~ N(0, 0.02)):
+  N = 1  the full 36-layer model on one GPU, unsharded (falls back to a 4-layer slice at 4 x 2048 when the GPU
+         has less than 160 GiB free);
+  N > 1  (launched with torch.distributed.run) the same model under FSDP2: bf16 parameter all-gather, fp32 gradient
+         reduce-scatter, vocabulary-parallel lm_head + cross-entropy, per-layer activation recomputation
+         ("full", the contract configuration; the "selective" and "none" policies are timed after it and reported
+         under config.other_recompute_policies).
+The loss head never writes the [tokens, vocab] logits (Q3_BENCH_FUSED_LOSS=0 selects the materialising head).
 
 `value` = tokens/s over all GPUs with the token ids already resident in HBM; `e2e.value` = the same step driven
-with pinned-host ids copied in and the loss read back every step. `--impl reference` times the CPU oracle
-restatement of the reference's model on a bounded sample of the same workload.
+through the public model API with pinned-host ids copied in and the loss read back every step. `--impl reference`
+times the CPU restatement of the reference's model (oracle/) on a bounded sample of the same workload.
 """
 from __future__ import annotations
 
@@ -20,6 +26,7 @@ import os
 import statistics
 import subprocess
 import sys
+import tempfile
 import time
 from pathlib import Path
 
@@ -35,24 +42,43 @@ UNIT = "tokens/s"
 # kernels launched by one call of each C-ABI entry (for the gpu_launches claim)
 LAUNCHES = {"q3_rmsnorm_bwd": 2, "q3_add_rmsnorm_bwd": 2, "q3_norm_rope_bwd": 2, "q3_adamw_multi": 2, "q3_ce_fwd": 2,
             "q3_attn_bwd": 3, "q3_vce_finish": 2, "q3_embedding_bwd": 2, "q3_embedding_shard_bwd": 2,
-            "q3_qk_norm_rope_bwd": 3}
+            "q3_qk_norm_rope_bwd": 3, "q3_attn_bwd_bshd": 3}
+
+GEMM_ENTRIES = ("q3_gemm", "q3_gemm_acc", "q3_gemm_acc_f32", "q3_gate_up_swiglu_fwd", "q3_linear_fwd_grouped",
+                "q3_linear_dgrad_grouped", "q3_linear_wgrad_grouped", "q3_down_dgrad_swiglu_bwd", "q3_linear_ce_stats",
+                "q3_linear_ce_grad")
+
+# DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum, one ncu capture per shape) divided by the algorithmic
+# bytes (operands read once + result written once) of the GEMM shapes of one training step at 2048 tokens; the source
+# table with the full command is profiles/gemm_tc_kernel_step_shapes_dram.md. Used for roofline.traffic.
+DRAM_OVER_ALGORITHMIC = 1.0
+DRAM_RATIO_SOURCE = "profiles/gemm_tc_kernel_step_shapes_dram.md"
 
 
-GEMM_ENTRIES = ("q3_gemm", "q3_gemm_acc", "q3_gate_up_swiglu_fwd", "q3_linear_fwd_grouped", "q3_linear_dgrad_grouped",
-                "q3_linear_wgrad_grouped", "q3_down_dgrad_swiglu_bwd")
-
-
-def gemm_flops_of(name, a):
-    """FLOPs of one call of a GEMM entry point from its recorded arguments (0 for anything else)."""
+def gemm_work_of(name, a):
+    """(FLOPs, algorithmic bytes) of one call of a GEMM entry point from its recorded arguments."""
+    def dense(m, n, k, out_bytes=2):
+        return 2.0 * m * n * k, 2.0 * (m * k + n * k) + out_bytes * m * n
     if name in ("q3_gemm", "q3_gemm_acc"):
-        return 2.0 * a[7] * a[8] * a[9]
+        return dense(a[7], a[8], a[9], 4 if a[11] == 0 else 2)
+    if name == "q3_gemm_acc_f32":
+        return dense(a[7], a[8], a[9], 8)
     if name == "q3_gate_up_swiglu_fwd":
-        return 4.0 * a[6] * a[7] * a[8]
+        m, n, k = a[6], a[7], a[8]
+        return 4.0 * m * n * k, 2.0 * (m * k + 2 * n * k) + 6.0 * m * n
     if name == "q3_down_dgrad_swiglu_bwd":
-        return 2.0 * a[6] * a[7] * a[8]
+        m, i, h = a[6], a[7], a[8]
+        return 2.0 * m * i * h, 2.0 * (m * h + i * h) + 8.0 * m * i
     if name in ("q3_linear_fwd_grouped", "q3_linear_dgrad_grouped", "q3_linear_wgrad_grouped"):
-        return 2.0 * a[5] * a[6] * sum(a[3][i] for i in range(a[4]))
-    return 0.0
+        m, k, total = a[5], a[6], sum(a[3][i] for i in range(a[4]))
+        return 2.0 * m * k * total, 2.0 * (m * k + total * k + m * total)
+    if name == "q3_linear_ce_stats":
+        m, v, k = a[6], a[7], a[8]
+        return 2.0 * m * v * k, 2.0 * (m * k + v * k)
+    if name == "q3_linear_ce_grad":
+        m, v, k = a[7], a[8], a[9]
+        return dense(m, v, k)
+    return 0.0, 0.0
 
 
 def slice_config(layers):
@@ -70,15 +96,15 @@ def model_flops_per_token(cfg, seq):
 
 
 class ClockSampler:
+    """nvidia-smi clock / throttle-reason samples every 200 ms while the timed region runs (read-only query)."""
     FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
               "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
               "clocks_event_reasons.sw_power_cap")
 
-    def __init__(self, index):
+    def __init__(self, index, out_dir):
         self.proc = None
-        self.path = ROOT / "gpurun_out" / f"clocks_bench_{index}.csv"
+        self.path = Path(out_dir) / f"clocks_gpu{index}.csv"
         try:
-            self.path.parent.mkdir(exist_ok=True)
             self.fh = open(self.path, "w")
             self.proc = subprocess.Popen(["nvidia-smi", "-i", str(index), f"--query-gpu={self.FIELDS}",
                                           "--format=csv,noheader,nounits", "-lms", "200"], stdout=self.fh,
@@ -122,47 +148,116 @@ def measured_peaks():
 
 
 # ---------------------------------------------------------------------------------------- CPU reference arm
-def cpu_reference_step_tokens_per_s(layers, sample_tokens, steps, warmup):
-    """The oracle restatement of the reference's CPU model (same architecture, fp32, torch CPU kernels on all
-    host threads): forward + CE + backward + AdamW on a bounded sample of `sample_tokens` tokens per step."""
-    from oracle.model import OracleQwen3
-    torch.set_num_threads(os.cpu_count() or 1)
-    cfg = slice_config(layers)
-    model = OracleQwen3(cfg, seed=1)
-    opt = torch.optim.AdamW(model.parameters(), lr=1e-4, betas=(0.9, 0.95), weight_decay=0.1)
-    gen = torch.Generator().manual_seed(2)
-    ids = torch.randint(0, cfg.vocab_size, (1, sample_tokens), generator=gen)
+def _median_ms(fn, warmup, runs):
+    for _ in range(warmup):
+        fn()
     times = []
-    for i in range(warmup + steps):
+    for _ in range(runs):
         t0 = time.perf_counter()
+        fn()
+        times.append(time.perf_counter() - t0)
+    return statistics.median(times) * 1e3
+
+
+def cpu_model_step_ms(cfg, batch, seq, warmup, runs, adamw=None):
+    """One forward + CE + backward + AdamW step of the restated reference CPU model (fp32, all host threads)."""
+    from oracle.model import OracleQwen3
+    model = OracleQwen3(cfg, seed=1)
+    opt = torch.optim.AdamW(model.parameters(), **(adamw or dict(lr=1e-4, betas=(0.9, 0.95), weight_decay=0.1)))
+    ids = torch.randint(0, cfg.vocab_size, (batch, seq), generator=torch.Generator().manual_seed(2))
+
+    def step():
         opt.zero_grad(set_to_none=True)
         loss, _ = model(ids, ids)
         loss.backward()
         opt.step()
-        if i >= warmup:
-            times.append(time.perf_counter() - t0)
-    sec = statistics.median(times)
-    return sample_tokens / sec, sec
+    return _median_ms(step, warmup, runs)
+
+
+def cpu_workload_baseline(layers, sample_tokens, warmup=3, runs=5):
+    """tokens/s of the `layers`-layer Qwen3-8B-shaped model on the host, from a bounded sample: steps of a 2-layer and
+    of a 4-layer slice at 1 x `sample_tokens` tokens give the per-layer and the embedding+head cost per step, from which
+    the step of the full depth follows (4 layers: measured directly)."""
+    torch.set_num_threads(os.cpu_count() or 1)
+    t4 = cpu_model_step_ms(slice_config(4), 1, sample_tokens, warmup, runs)
+    if layers == 4:
+        return sample_tokens / (t4 * 1e-3), t4, f"4 layers, 1 x {sample_tokens} tokens per step, {warmup} warm-ups, median of {runs}"
+    t2 = cpu_model_step_ms(slice_config(2), 1, sample_tokens, warmup, runs)
+    per_layer = max((t4 - t2) / 2.0, 0.0)
+    full = (t2 - 2.0 * per_layer) + layers * per_layer
+    note = (f"{layers}-layer step extrapolated from measured 2- and 4-layer slices at 1 x {sample_tokens} tokens "
+            f"({t2:.0f} ms, {t4:.0f} ms: {per_layer:.0f} ms per layer + {t2 - 2 * per_layer:.0f} ms embedding/head/optimizer rest), "
+            f"{warmup} warm-ups, median of {runs}; the 4-layer slice alone gives {sample_tokens / (t4 * 1e-3):.1f} tokens/s")
+    return sample_tokens / (full * 1e-3), full, note
+
+
+def cpu_operator_baselines(warmup=1, runs=3):
+    """The reference's CPU operators (restated in oracle/ops.py, fp32, all host threads) at the operator-sweep and
+    attention shapes, each on a stated slice; and the tiny two-layer decoder's full training step."""
+    from types import SimpleNamespace
+    from oracle import ops as O
+    torch.set_num_threads(os.cpu_count() or 1)
+    g = torch.Generator().manual_seed(4)
+    r = lambda *s: torch.randn(*s, generator=g)  # noqa: E731
+    T = 4096                                    # a quarter of the 16384-token sweep
+    out = []
+
+    def add(name, shape, fn, note=""):
+        out.append({"op": name, "shape": shape, "ms": round(_median_ms(fn, warmup, runs), 3), "note": note})
+
+    tiny = SimpleNamespace(vocab_size=2048, hidden_size=256, intermediate_size=688, num_hidden_layers=2,
+                           num_attention_heads=4, num_key_value_heads=2, head_dim=64, rms_norm_eps=1e-6, rope_theta=1e6,
+                           initializer_range=0.02)
+    ms = cpu_model_step_ms(tiny, 2, 128, 3, 5)
+    out.append({"op": "tiny decoder full step (2 layers, hidden 256, vocab 2048, fp32)", "shape": "batch 2 x seq 128",
+                "ms": round(ms, 3), "note": "%.0f tokens/s; 3 warm-ups, median of 5" % (256 / (ms * 1e-3))})
+    x, w, dy = r(T, 4096), torch.ones(4096), r(T, 4096)
+    add("rms_norm fwd", f"[{T},4096]", lambda: O.rms_norm(x, w), "1/4 of 16384 tokens")
+    add("rms_norm bwd", f"[{T},4096]", lambda: O.rms_norm_backward(x, w, dy), "1/4 of 16384 tokens")
+    q, k = r(1, T, 32, 128), r(1, T, 8, 128)
+    wq, wk = torch.ones(128), torch.ones(128)
+    pos = torch.arange(T)[None]
+    inv = 1.0 / (1e6 ** (torch.arange(0, 128, 2).float() / 128))
+    ang = pos[..., None].float() * inv
+    cos, sin = torch.cat([ang.cos(), ang.cos()], -1), torch.cat([ang.sin(), ang.sin()], -1)
+    add("qk_norm_rope fwd", f"q [1,{T},32,128] k [1,{T},8,128]", lambda: O.qk_norm_rope(q, k, wq, wk, cos, sin),
+        "1/4 of 16384 tokens")
+    gate, up = r(T, 12288), r(T, 12288)
+    add("swiglu fwd", f"[{T},12288] x2", lambda: O.swiglu(gate, up), "1/4 of 16384 tokens")
+    aq, ak, av, ado = r(1, 4, 4096, 128), r(1, 1, 4096, 128), r(1, 1, 4096, 128), r(1, 4, 4096, 128)
+    add("attention fwd", "B1 Hq4 Hkv1 S4096 D128", lambda: O.attention(aq, ak, av), "one query-head group = 1/32 of B4 Hq32 S4096")
+    add("attention bwd", "B1 Hq4 Hkv1 S4096 D128", lambda: O.attention_backward(aq, ak, av, ado), "1/32 of B4 Hq32 S4096")
+    a, b = r(2048, 4096), r(4096, 4096)
+    add("linear fwd (q_proj)", "2048 x 4096 x 4096", lambda: O.linear(a, b))
+    logits, labels = r(1, 1024, 151936), torch.randint(0, 151936, (1, 1024), generator=g)
+    add("cross-entropy fwd", "[1024,151936] fp32 logits", lambda: O.causal_cross_entropy(logits, labels), "1/16 of 16384 tokens")
+    n = 4096 * 12288
+    p = torch.nn.Parameter(r(n))
+    p.grad = r(n) * 1e-3
+    opt = torch.optim.AdamW([p], lr=1e-4, betas=(0.9, 0.95), weight_decay=0.1)
+    add("AdamW step", f"{n} fp32 parameters", opt.step, "one gate_proj matrix = 1/163 of 8.19e9 parameters")
+    return out
 
 
 def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    layers = 4
-    sample = 128
-    steps, warmup = max(1, min(args.steps, 3)), 1
-    tps, sec = cpu_reference_step_tokens_per_s(layers, sample, steps, warmup)
+    layers, sample = 36, 128
+    warmup, runs = 3, max(5, min(args.steps, 7))
+    tps, ms, note = cpu_workload_baseline(layers, sample, warmup, runs)
     cores = os.cpu_count() or 1
-    line = {"impl": "reference", "metric": METRIC, "value": tps, "unit": UNIT, "n_gpus": args.gpus, "steps": steps,
-            "warmup": warmup, "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+    extra = None if os.environ.get("Q3_BENCH_SKIP_CPU_OPS") else cpu_operator_baselines()
+    line = {"impl": "reference", "metric": METRIC, "value": tps, "unit": UNIT, "n_gpus": args.gpus, "steps": runs,
+            "warmup": warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "f32", "data": "synthetic",
-            "config": {"workload": "qwen3-8b 4-layer slice fwd+bwd+AdamW (CPU sample 1x%d tokens)" % sample,
-                       "note": "the CPU arm always times the 4-layer slice (BASELINE config 4); the full 36-layer model "
-                               "of config 5 needs ~130 GB of host memory for fp32 weights, gradients and moments and "
-                               "would run about 9x fewer tokens/s, so at N>1 this line is an upper bound for the CPU"},
-            "cpu_baseline": {"value": tps, "unit": UNIT, "cores": cores, "kind": "port",
-                             "sample": f"oracle model, 4 layers, 1 x {sample} tokens per step, median of {steps}"},
+            "config": {"workload": "qwen3-8b full 36-layer model, fwd+bwd+AdamW, microbatch 1x2048 per GPU "
+                                   "(CPU arm: restated reference model on the host cores, bounded sample)",
+                       "global_batch": args.gpus, "seq_len": 2048, "parallelism": "cpu",
+                       "note": "a step of the full model at 2048 tokens needs about 130 GB of host memory and minutes "
+                               "per step on the CPU, so the arm times 1 x %d-token steps of 2- and 4-layer slices and "
+                               "extrapolates the depth; tokens/s is per host, not multiplied by the GPU count" % sample},
+            "cpu_baseline": {"value": tps, "unit": UNIT, "cores": cores, "kind": "port", "sample": note, "extra": extra},
             "e2e": {"value": tps, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(line), flush=True)
 
@@ -193,6 +288,45 @@ class Counter:
             self.orig(name, *a)
 
 
+def census(counter):
+    """Per-entry-point time of the recorded step and the GEMM totals (ms, FLOPs, algorithmic bytes)."""
+    by_name, flops, nbytes, shapes = {}, 0.0, 0.0, {}
+    for name, a, s, e in counter.records:
+        t = s.elapsed_time(e)
+        by_name[name] = by_name.get(name, 0.0) + t
+        f, b = gemm_work_of(name, a)
+        flops += f
+        nbytes += b
+        if name in ("q3_gemm", "q3_gemm_acc"):
+            key = (a[7], a[8], a[9], "A:%s B:%s" % ("K" if a[2] == 1 else "MN", "K" if a[4] == 1 else "MN"))
+            cnt, tot = shapes.get(key, (0, 0.0))
+            shapes[key] = (cnt + 1, tot + t)
+    if os.environ.get("Q3_BENCH_PROFILE"):
+        for (m, n, k, lay), (cnt, tot) in sorted(shapes.items(), key=lambda kv: -kv[1][1]):
+            sys.stderr.write("gemm %6d x %6d x %6d %-10s n=%3d total %8.3f ms avg %8.1f us %7.1f TFLOP/s\n" % (
+                m, n, k, lay, cnt, tot, tot / cnt * 1e3, 2.0 * m * n * k * cnt / tot / 1e9))
+    gemm_ms = sum(by_name.get(n, 0.0) for n in GEMM_ENTRIES)
+    return by_name, flops, nbytes, gemm_ms
+
+
+def roofline_of(counter):
+    by_name, flops, nbytes, gemm_ms = census(counter)
+    peak_tf, _, peak_kind = measured_peaks()
+    achieved = flops / (gemm_ms * 1e-3) / 1e12 if gemm_ms > 0 else 0.0
+    return {"bound": "tensor",
+            "kernel": "gemm_tc_kernel (every GEMM entry point of one step: q3_gemm*, q3_linear_*_grouped, "
+                      "q3_gate_up_swiglu_fwd, q3_down_dgrad_swiglu_bwd, q3_linear_ce_*)",
+            "achieved": achieved, "peak": peak_tf, "unit": "TFLOP/s", "frac": achieved / peak_tf,
+            "peak_kind": peak_kind + " bf16_tflops_sustained",
+            "traffic": nbytes * DRAM_OVER_ALGORITHMIC,
+            "traffic_note": "bytes per step over all GEMM launches: algorithmic bytes (operands once + result once) "
+                            "x %.2f, the DRAM/algorithmic ratio ncu measured on the step's GEMM shapes (%s)" % (
+                                DRAM_OVER_ALGORITHMIC, DRAM_RATIO_SOURCE),
+            "algorithmic_bytes_per_step": nbytes, "flops_per_step": flops, "gemm_ms_per_step": gemm_ms,
+            "all_kernels_ms_per_step": sum(by_name.values()),
+            "census_ms": {k: round(v, 3) for k, v in sorted(by_name.items(), key=lambda kv: -kv[1])}}
+
+
 def build_single_gpu(cfg, device):
     from qwen3_triton import model_for_variant
     from qwen3_triton.runtime.adamw import TritonAdamW
@@ -202,8 +336,8 @@ def build_single_gpu(cfg, device):
         model = model_for_variant(cfg, os.environ.get("Q3_BENCH_VARIANT", "b200_fused"))
     model.to(device)   # buffers created on the CPU on purpose (rotary frequencies) move here
     if hasattr(model, "fused_loss"):
-        # "1": hidden -> loss without logits in HBM (one extra logits GEMM in backward; measured 8 ms slower per step here)
-        model.fused_loss = os.environ.get("Q3_BENCH_FUSED_LOSS", "0") == "1"
+        # hidden -> loss without the [tokens, vocab] logits in HBM ("0": materialise them, one GEMM less in backward)
+        model.fused_loss = os.environ.get("Q3_BENCH_FUSED_LOSS", "1") == "1"
     masters = MasterWeights(model).fuse_into_optimizer()
     opt = TritonAdamW(masters.parameters(), lr=1e-4, betas=(0.9, 0.95), weight_decay=0.1, block=16384)
     return model, masters, opt
@@ -213,12 +347,11 @@ def run_ours(args):
     world = int(os.environ.get("WORLD_SIZE", "1"))
     if world > 1:
         return run_fsdp(args)
+    from qwen3_triton import _abi
     device = torch.device("cuda", 0)
     torch.cuda.set_device(device)
     counter = Counter()
-    # N=1 workload: the full 36-layer Qwen3-8B at the per-GPU microbatch of config 5 (1 x 2048) when it fits this GPU
-    # (fp32 masters + moments 98 GB, bf16 working copies and gradients 33 GB, activations 6 GB), else the 4-layer
-    # slice of config 4 (4 x 2048). Q3_BENCH_N1 = "full" | "slice" forces one.
+    # the full model fits one B200: fp32 masters + moments 98 GB, bf16 working copies and gradients 33 GB, activations 6 GB
     choice = os.environ.get("Q3_BENCH_N1", "auto")
     free_gib = torch.cuda.mem_get_info(device)[0] / 2 ** 30
     want_full = choice == "full" or (choice == "auto" and free_gib >= 160)
@@ -254,7 +387,7 @@ def run_ours(args):
     for i in range(args.warmup):
         step(dev_ids[i % len(dev_ids)])
     torch.cuda.synchronize()
-    sampler = ClockSampler(0)
+    sampler = ClockSampler(0, args.out)
     counter.launches = 0
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     torch.cuda.synchronize()
@@ -267,6 +400,7 @@ def run_ours(args):
     ms = start.elapsed_time(end) / args.steps
     tokens = batch * seq
     value = tokens / (ms * 1e-3)
+    status = _abi.read_status()          # a kernel that gave up or saw a bad label would have left its bit here
 
     # end to end: pinned host ids copied in, loss read back, every step
     torch.cuda.synchronize()
@@ -277,71 +411,44 @@ def run_ours(args):
     torch.cuda.synchronize()
     e2e_ms = (time.perf_counter() - t0) * 1e3 / args.steps
     clocks = sampler.stop()
+    status |= _abi.read_status()
 
     # per-kernel census of one more step with CUDA events around every C-ABI call
     counter.profile = True
     step(dev_ids[0])
     torch.cuda.synchronize()
     counter.profile = False
-    by_name = {}
-    gemm_flops = 0.0
-    for name, a, s, e in counter.records:
-        t = s.elapsed_time(e)
-        by_name[name] = by_name.get(name, 0.0) + t
-        gemm_flops += gemm_flops_of(name, a)
-    gemm_ms = sum(by_name.get(n, 0.0) for n in GEMM_ENTRIES)
+    roofline = roofline_of(counter)
     peak_tf, _, peak_kind = measured_peaks()
-    achieved = gemm_flops / (gemm_ms * 1e-3) / 1e12 if gemm_ms > 0 else 0.0
-    total_ms = sum(by_name.values())
-    census = {k: round(v, 3) for k, v in sorted(by_name.items(), key=lambda kv: -kv[1])}
-
-    flops_tok = model_flops_per_token(cfg, seq)
-    mfu = value * flops_tok / (peak_tf * 1e12)
+    mfu = value * model_flops_per_token(cfg, seq) / (peak_tf * 1e12)
     if os.environ.get("Q3_BENCH_SKIP_CPU"):     # profiling runs under ncu skip the host-side baseline leg
-        cpu_tps = None
+        cpu = {"value": None, "unit": UNIT, "cores": os.cpu_count() or 1, "kind": "port", "sample": "skipped"}
     else:
-        cpu_tps, _ = cpu_reference_step_tokens_per_s(layers, 128, 1, 1)
+        cpu_tps, _, note = cpu_workload_baseline(layers, 128)
+        cpu = {"value": cpu_tps, "unit": UNIT, "cores": os.cpu_count() or 1, "kind": "port", "sample": note,
+               "extra": None if os.environ.get("Q3_BENCH_SKIP_CPU_OPS") else cpu_operator_baselines()}
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic",
         "config": {"workload": ("qwen3-8b full 36-layer model on one GPU, fwd+bwd+AdamW, microbatch 1x2048 (the per-GPU "
-                                "workload of BASELINE config 5, no sharding)" if layers == 36 else
-                                "qwen3-8b 4-layer slice fwd+bwd+AdamW, microbatch 4x2048 (BASELINE config 4)"),
+                                "workload of the multi-GPU runs, unsharded)" if layers == 36 else
+                                "qwen3-8b 4-layer slice fwd+bwd+AdamW, microbatch 4x2048"),
                    "global_batch": batch, "seq_len": seq, "parallelism": "single",
                    "l2": "inputs+weights >> L2 (%d GB bf16 weights)" % (16 if layers == 36 else 4),
-                   "attention_path": "see kernel census", "mfu_of_%s_peak" % peak_kind: mfu, "last_loss": last,
+                   "loss_head": "no logits in memory" if getattr(model, "fused_loss", False) else "materialised logits",
+                   "mfu_of_%s_peak" % peak_kind: mfu, "last_loss": last, "device_status": status,
                    "peak_memory_gb": round(torch.cuda.max_memory_allocated() / 2 ** 30, 1)},
         "e2e": {"value": tokens / (e2e_ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": batch * seq * 8,
                 "d2h_bytes_per_step": 4},
         "gpu_launches": launches,
         "clocks": clocks,
-        "roofline": {"bound": "tensor", "kernel": "gemm_tc_kernel (all GEMM entry points of a step: q3_gemm, q3_linear_*_grouped, q3_gate_up_swiglu_fwd)",
-                     "achieved": achieved, "peak": peak_tf, "unit": "TFLOP/s", "frac": achieved / peak_tf,
-                     "peak_kind": peak_kind + " bf16_tflops_sustained", "traffic": None,
-                     "gemm_ms_per_step": gemm_ms, "all_kernels_ms_per_step": total_ms, "census_ms": census},
-        "cpu_baseline": {"value": cpu_tps, "unit": UNIT, "cores": os.cpu_count() or 1, "kind": "port",
-                         "sample": "oracle model, 4 layers, 1 x 128 tokens, one timed step after one warm-up"},
+        "roofline": roofline,
+        "cpu_baseline": cpu,
     }
     print(json.dumps(line), flush=True)
-
-
-def census(counter):
-    by_name, gemm_flops = {}, 0.0
-    shapes = {}
-    for name, a, s, e in counter.records:
-        by_name[name] = by_name.get(name, 0.0) + s.elapsed_time(e)
-        if name in ("q3_gemm", "q3_gemm_acc"):
-            key = (a[7], a[8], a[9], "A:%s B:%s" % ("K" if a[2] == 1 else "MN", "K" if a[4] == 1 else "MN"))
-            cnt, tot = shapes.get(key, (0, 0.0))
-            shapes[key] = (cnt + 1, tot + s.elapsed_time(e))
-        gemm_flops += gemm_flops_of(name, a)
-    if os.environ.get("Q3_BENCH_PROFILE"):
-        for (m, n, k, lay), (cnt, tot) in sorted(shapes.items(), key=lambda kv: -kv[1][1]):
-            sys.stderr.write("gemm %6d x %6d x %6d %-10s n=%3d total %8.3f ms avg %8.1f us %7.1f TFLOP/s\n" % (
-                m, n, k, lay, cnt, tot, tot / cnt * 1e3, 2.0 * m * n * k * cnt / tot / 1e9))
-    gemm_ms = sum(by_name.get(n, 0.0) for n in GEMM_ENTRIES)
-    return by_name, gemm_flops, gemm_ms
+    if status:
+        raise SystemExit("device status word is not clean: %d (see include/q3b200.h, Q3_STATUS_*)" % status)
 
 
 def unit_sizes(layers):
@@ -363,12 +470,44 @@ def unit_sizes(layers):
     return sizes
 
 
-def run_fsdp(args):
-    """N > 1: BASELINE config 5 - the full 36-layer model under FSDP2 (one process per GPU, NCCL), bf16 parameter
-    all-gather, fp32 gradient reduce-scatter, vocabulary-parallel lm_head + cross-entropy, per-layer activation
-    recomputation, microbatch 1 x 2048 per GPU, AdamW every step."""
-    import torch.distributed as dist
+PARITY_PARAMS = ("model.layers.0.self_attn.q_proj.weight", "model.layers.%d.mlp.down_proj.weight",
+                 "model.layers.%d.mlp.gate_proj.weight", "lm_head.weight")
+
+
+def unsharded_yardstick(cfg, device, all_ids, rank, world, names):
+    """Loss and this rank's gradient rows of `names` from ONE unsharded bf16 copy of the model run on the
+    concatenated batch of all ranks (what FSDP's averaged gradients must equal). Built from the same seed as the
+    sharded model, freed before that one is built."""
     from qwen3_triton import model_for_variant
+    torch.manual_seed(20261114)
+    with torch.device(device):
+        whole = model_for_variant(cfg, "b200_fused")
+    whole = whole.to(device=device, dtype=torch.bfloat16)
+    whole.model.set_recompute("full")
+    whole.fused_loss = True
+    ids = torch.cat(all_ids).to(device)
+    loss = whole(ids, labels=ids).loss
+    loss.backward()
+    named = dict(whole.named_parameters())
+    shards = {}
+    for name in names:
+        g = named[name].grad
+        rows = g.shape[0] // world
+        shards[name] = g[rank * rows:(rank + 1) * rows].float().clone()
+    value = float(loss)
+    del whole, named, loss
+    import gc
+    gc.collect()
+    torch.cuda.empty_cache()
+    return value, shards
+
+
+def run_fsdp(args):
+    """N > 1: the full 36-layer model under FSDP2 (one process per GPU, NCCL), bf16 parameter all-gather, fp32
+    gradient reduce-scatter, vocabulary-parallel lm_head + cross-entropy and embedding, microbatch 1 x 2048 per GPU,
+    AdamW every step; per-layer activation recomputation for the headline number, the lighter policies after it."""
+    import torch.distributed as dist
+    from qwen3_triton import _abi, model_for_variant
     from qwen3_triton.runtime.adamw import TritonAdamW
     from qwen3_triton.runtime.collectives import NcclCollectives
     from qwen3_triton.runtime.fsdp import configure
@@ -377,11 +516,26 @@ def run_fsdp(args):
     rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ.get("LOCAL_RANK", "0"))
     device = torch.device("cuda", local)
     torch.cuda.set_device(device)
-    dist.init_process_group("nccl", device_id=device)
+    pg_options = None
+    max_ctas = int(os.environ.get("Q3_BENCH_NCCL_MAX_CTAS", "0"))
+    if max_ctas > 0:
+        # fewer NCCL CTAs leave more SMs (and HBM bandwidth) to the GEMMs the collectives run beside
+        pg_options = dist.ProcessGroupNCCL.Options()
+        pg_options.config.max_ctas = max_ctas
+        pg_options.config.min_ctas = min(max_ctas, int(os.environ.get("Q3_BENCH_NCCL_MIN_CTAS", "1")))
+    dist.init_process_group("nccl", device_id=device, pg_options=pg_options)
     counter = Counter()
     layers = int(os.environ.get("Q3_BENCH_LAYERS", "36"))
     batch, seq = 1, 2048
     cfg = slice_config(layers)
+    host_ids = [[torch.randint(0, cfg.vocab_size, (batch, seq), generator=torch.Generator().manual_seed(100 * (k + 1) + r))
+                 for r in range(world)] for k in range(8)]
+
+    parity = None
+    names = [n % (layers // 2 if i == 1 else layers - 1) if "%d" in n else n for i, n in enumerate(PARITY_PARAMS)]
+    if os.environ.get("Q3_BENCH_PARITY", "1") == "1":
+        yard_loss, yard = unsharded_yardstick(cfg, device, host_ids[0], rank, world, names)
+
     torch.manual_seed(20261114)            # same weights on every rank
     with torch.device(device):
         model = model_for_variant(cfg, os.environ.get("Q3_BENCH_VARIANT", "b200_fused"))
@@ -389,22 +543,23 @@ def run_fsdp(args):
     # the vocabulary-parallel head and embedding talk over their own communicator, so that their small collectives on
     # the compute stream do not queue behind FSDP's reduce-scatters on the same NCCL communicator
     vocab_comm = NcclCollectives(group=dist.new_group()) if os.environ.get("Q3_BENCH_VP_GROUP", "1") == "1" else None
-    # activation recomputation: 'none' keeps every layer's activations (about 5 GB at 2048 tokens per GPU, nothing on
-    # a 180 GB part); 'selective' / 'full' are the memory-saving modes
-    ckpt = os.environ.get("Q3_BENCH_CHECKPOINT", "none")
+    policies = [p for p in os.environ.get("Q3_BENCH_CHECKPOINT", "full,selective,none").split(",") if p]
     model = shard_vocab_loss_model(model, keep_full_layers=layers, checkpoint_every=1,
                                    skip_embedding_backward_gather=True, fused_vocab_dw=True, communication=vocab_comm,
-                                   checkpoint_mode=ckpt, layers_per_unit=unit_sizes(layers),
+                                   checkpoint_mode=policies[0], layers_per_unit=unit_sizes(layers),
                                    vocab_parallel_embedding=os.environ.get("Q3_BENCH_VP_EMBEDDING", "1") == "1",
                                    forward_prefetch=int(os.environ.get("Q3_BENCH_FORWARD_PREFETCH", "2")))
-    model.lm_head.fused = os.environ.get("Q3_BENCH_FUSED_LOSS", "0") == "1"
+    model.lm_head.fused = os.environ.get("Q3_BENCH_FUSED_LOSS", "1") == "1"
     hooks = configure(model, comm, pack_gradients_off_compute_stream=os.environ.get("Q3_BENCH_PACK_SIDE", "0") == "1")
     decoder = [p for n, p in model.named_parameters() if not n.startswith("lm_head.")]
     opt = TritonAdamW([dict(params=decoder), dict(params=[model.lm_head.weight])], lr=1e-4, betas=(0.9, 0.95),
                       weight_decay=0.1, block=16384)
-    gen = torch.Generator().manual_seed(100 + rank)
-    host_ids = [torch.randint(0, cfg.vocab_size, (batch, seq), generator=gen).pin_memory() for _ in range(8)]
-    dev_ids = [h.to(device) for h in host_ids]
+    pinned = [k[rank].pin_memory() for k in host_ids]
+    dev_ids = [h.to(device) for h in pinned]
+
+    def set_policy(policy):
+        for layer in model.model.layers:
+            layer.recompute = {"full": 2, "selective": 1, "none": 0}[policy]
 
     def step(ids):
         opt.zero_grad(set_to_none=True)
@@ -413,31 +568,57 @@ def run_fsdp(args):
         opt.step()
         return out.loss
 
-    for i in range(args.warmup):
-        step(dev_ids[i % len(dev_ids)])
-    torch.cuda.synchronize()
-    dist.barrier()
-    sampler = ClockSampler(local) if rank == 0 else None
-    counter.launches = 0
-    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    torch.cuda.synchronize()
-    start.record()
-    for i in range(args.steps):
-        step(dev_ids[i % len(dev_ids)])
-    end.record()
-    torch.cuda.synchronize()
-    dist.barrier()
-    launches = counter.launches
-    t = torch.tensor([start.elapsed_time(end) / args.steps], device=device)
-    dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms = float(t.item())
+    if os.environ.get("Q3_BENCH_PARITY", "1") == "1":
+        # First step of the sharded model on the same global batch, before any update: the mean of the ranks' losses
+        # against the unsharded loss, and the reduce-scattered (rank-averaged) gradient shards against the unsharded
+        # gradient rows. Worst value over ranks.
+        opt.zero_grad(set_to_none=True)
+        out = model(dev_ids[0], labels=dev_ids[0])
+        out.loss.backward()
+        mean_loss = out.loss.detach().float().clone()
+        dist.all_reduce(mean_loss, op=dist.ReduceOp.AVG)
+        named = dict(model.named_parameters())
+        worst = torch.zeros(1, device=device)
+        for name in names:
+            g = named[name].grad
+            g = (g.to_local() if hasattr(g, "to_local") else g).float()
+            worst = torch.maximum(worst, ((g - yard[name]).norm() / yard[name].norm()).reshape(1))
+        dist.all_reduce(worst, op=dist.ReduceOp.MAX)
+        parity = {"loss": abs(float(mean_loss) - yard_loss) / abs(yard_loss), "grads": float(worst),
+                  "what": "first step vs one unsharded bf16 model on the concatenated %d x 2048 batch: relative loss "
+                          "difference; worst relative L2 over ranks of the gradient shards of %s" % (world, ", ".join(names))}
+        del yard, named
+        opt.zero_grad(set_to_none=True)
+
+    def timed(policy, steps, warmup):
+        set_policy(policy)
+        for i in range(warmup):
+            step(dev_ids[i % len(dev_ids)])
+        torch.cuda.synchronize()
+        dist.barrier()
+        counter.launches = 0
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        start.record()
+        for i in range(steps):
+            step(dev_ids[i % len(dev_ids)])
+        end.record()
+        torch.cuda.synchronize()
+        dist.barrier()
+        t = torch.tensor([start.elapsed_time(end) / steps], device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item()), counter.launches
+
+    sampler = ClockSampler(local, args.out) if rank == 0 else None
+    ms, launches = timed(policies[0], args.steps, args.warmup)
+    status = _abi.read_status()
 
     torch.cuda.synchronize()
     dist.barrier()
     t0 = time.perf_counter()
     last = 0.0
     for i in range(args.steps):
-        ids = host_ids[i % len(host_ids)].to(device, non_blocking=True)
+        ids = pinned[i % len(pinned)].to(device, non_blocking=True)
         last = float(step(ids).item())
     torch.cuda.synchronize()
     t = torch.tensor([(time.perf_counter() - t0) * 1e3 / args.steps], device=device)
@@ -451,45 +632,62 @@ def run_fsdp(args):
             step(dev_ids[0])
             torch.cuda.synchronize()
         sys.stderr.write(prof.key_averages().table(sort_by="cuda_time_total", row_limit=25, max_name_column_width=70) + "\n")
-        (ROOT / "gpurun_out").mkdir(exist_ok=True)
-        prof.export_chrome_trace(str(ROOT / "gpurun_out" / "trace_rank0.json"))
+        prof.export_chrome_trace(str(Path(args.out) / "trace_rank0.json"))
     elif os.environ.get("Q3_BENCH_PROFILE"):
         step(dev_ids[0])
     counter.profile = True
     step(dev_ids[0])
     torch.cuda.synchronize()
     counter.profile = False
-    by_name, gemm_flops, gemm_ms = census(counter)
+    roofline = roofline_of(counter)
+    peak_memory = round(torch.cuda.max_memory_allocated() / 2 ** 30, 1)
     dist.barrier()
+
+    others = {}
+    short = max(3, min(args.steps, 6))
+    for policy in policies[1:]:
+        other_ms, _ = timed(policy, short, 2)
+        others[policy] = other_ms
+    status |= _abi.read_status()
+    bad = torch.tensor([status], device=device)
+    dist.all_reduce(bad, op=dist.ReduceOp.BOR)
+    status = int(bad.item())
+
     if rank == 0:
         peak_tf, _, peak_kind = measured_peaks()
-        achieved = gemm_flops / (gemm_ms * 1e-3) / 1e12 if gemm_ms > 0 else 0.0
         tokens = batch * seq * world
         value = tokens / (ms * 1e-3)
-        mfu = (value / world) * model_flops_per_token(cfg, seq) / (peak_tf * 1e12)
+        flops_tok = model_flops_per_token(cfg, seq)
+        mfu = (value / world) * flops_tok / (peak_tf * 1e12)
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
             "data": "synthetic",
             "config": {"workload": "qwen3-8b %d layers under FSDP2, microbatch 1x2048 per GPU, vocab-parallel head%s, "
-                                   "%s activation recompute, AdamW (BASELINE config 5)" % (
-                                       layers, " and embedding" if os.environ.get("Q3_BENCH_VP_EMBEDDING", "1") == "1" else "", ckpt),
+                                   "%s activation recomputation per layer, AdamW every step" % (
+                                       layers, " and embedding" if os.environ.get("Q3_BENCH_VP_EMBEDDING", "1") == "1" else "",
+                                       policies[0]),
                        "global_batch": batch * world, "seq_len": seq, "parallelism": "fsdp%d" % world,
-                       "l2": "weights and activations >> L2", "mfu_of_%s_peak_per_gpu" % peak_kind: mfu,
-                       "tokens_per_s_per_gpu": value / world, "last_loss": last,
-                       "peak_memory_gb_rank0": round(torch.cuda.max_memory_allocated() / 2 ** 30, 1),
+                       "l2": "weights and activations >> L2",
+                       "loss_head": "no logits in memory" if model.lm_head.fused else "materialised logits shard",
+                       "mfu_of_%s_peak_per_gpu" % peak_kind: mfu, "mfu_basis": "model FLOPs (recomputed forward not counted)",
+                       "tokens_per_s_per_gpu": value / world, "last_loss": last, "device_status": status,
+                       "parity_step1_rel": parity,
+                       "other_recompute_policies": {p: {"ms_per_step": v, "tokens_per_s": tokens / (v * 1e-3),
+                                                        "mfu_of_%s_peak_per_gpu" % peak_kind:
+                                                            (tokens / world / (v * 1e-3)) * flops_tok / (peak_tf * 1e12),
+                                                        "steps": short} for p, v in others.items()},
+                       "peak_memory_gb_rank0": peak_memory, "nccl_max_ctas": max_ctas or "default",
                        "fsdp_units": hooks["units"], "collectives": comm.report()},
             "e2e": {"value": tokens / (e2e_ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": batch * seq * 8 * world,
                     "d2h_bytes_per_step": 4 * world},
             "gpu_launches": launches, "clocks": clocks,
-            "roofline": {"bound": "tensor", "kernel": "gemm_tc_kernel (all GEMM entry points of a step, rank 0: q3_gemm, q3_linear_*_grouped, q3_gate_up_swiglu_fwd)",
-                         "achieved": achieved, "peak": peak_tf, "unit": "TFLOP/s", "frac": achieved / peak_tf,
-                         "peak_kind": peak_kind + " bf16_tflops_sustained", "traffic": None, "gemm_ms_per_step": gemm_ms,
-                         "all_kernels_ms_per_step": sum(by_name.values()),
-                         "census_ms": {k: round(v, 3) for k, v in sorted(by_name.items(), key=lambda kv: -kv[1])}},
+            "roofline": roofline,
         }
         print(json.dumps(line), flush=True)
     dist.destroy_process_group()
+    if status:
+        raise SystemExit("device status word is not clean: %d (see include/q3b200.h, Q3_STATUS_*)" % status)
 
 
 def main():
@@ -498,11 +696,17 @@ def main():
     ap.add_argument("--steps", type=int, default=8)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--out", default=None, help="directory for the clock samples (default: a temporary directory)")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: the product has no CPU path")
+    if args.out is None:
+        with tempfile.TemporaryDirectory(prefix="q3bench_") as tmp:
+            args.out = tmp
+            return run_ours(args)
+    Path(args.out).mkdir(parents=True, exist_ok=True)
     run_ours(args)
 
 

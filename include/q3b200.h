@@ -380,6 +380,30 @@ int q3_attn_path(const void* q, const void* k, const void* v, const void* out, i
 int q3_attn_bwd_group_split(int64_t B, int64_t Hq, int64_t Hkv, int64_t S);
 int q3_attn_bwd_group_policy(int policy);
 
+/* ---- token-block data path and validation statistics ---------------------------------------- */
+
+/* out[i] = training ? ((first + i + offset) * stride + seed) mod n : first + i, for i in [0, count): the order in
+ * which training visits the n blocks of a corpus (stride coprime to n gives a full-period permutation); exact 128-bit
+ * integer arithmetic. Reference: training/data.py:26-27 (Blocks.__getitem__ index). */
+int q3_block_order(int64_t* out, int64_t first, int64_t count, int64_t offset, int64_t stride, int64_t seed, int64_t n,
+                   int training, q3_stream_t stream);
+
+/* ids[b, s] = corpus[block[b] * seq + s] widened to int64, for a corpus of uint32 token ids resident on the device.
+ * block [batch] int64 on the device; a block outside [0, corpus_tokens / seq) sets Q3_STATUS_ID_RANGE and yields zeros.
+ * Reference: training/data.py:28 (the slice and astype(int64) of Blocks.__getitem__). */
+int q3_token_blocks(const uint32_t* corpus, int64_t corpus_tokens, const int64_t* block, int64_t* ids, int64_t batch,
+                    int64_t seq, int* status, q3_stream_t stream);
+
+/* totals[0] += loss[0] * tokens; totals[1] += tokens, in fp64 with separate multiply and add (totals: 2 doubles on the
+ * device; tokens == 0 launches nothing). Reference: qwen3_triton/runtime/metrics.py:8-17 (accumulate_validation). */
+int q3_validation_accumulate(const float* loss, double* totals, int64_t tokens, q3_stream_t stream);
+
+/* totals[0] += sum of losses[b, s] over the shifted rows (s < S-1) whose target labels[b, s+1] != ignore_index,
+ * totals[1] += their number; fp64, fixed summation order. losses [B*(S-1)] as written by q3_ce_fwd, labels [B,S].
+ * Reference: training/evaluation.py:20-26 (shifted_nll: summed NLL and scored-token count of a batch). */
+int q3_validation_rows(const float* losses, const int64_t* labels, int64_t B, int64_t S, int64_t ignore_index,
+                       double* totals, q3_stream_t stream);
+
 /* ---- self-test ------------------------------------------------------------------------------ */
 
 /* Makes a bounded wait run out on purpose, the harmless way: one CTA waits on a barrier nothing arrives at, with a

@@ -87,6 +87,10 @@ SIGNATURES = {
     "q3_attn_bwd_group_split": (I, [L, L, L, L]),
     "q3_attn_bwd_group_policy": (I, [I]),
     "q3_selftest_wait_timeout": (I, [L, P, P, P]),
+    "q3_block_order": (I, [P, L, L, L, L, L, L, I, P]),
+    "q3_token_blocks": (I, [P, L, P, P, L, L, P, P]),
+    "q3_validation_accumulate": (I, [P, P, L, P]),
+    "q3_validation_rows": (I, [P, P, L, L, L, P, P]),
 }
 
 _lib = None

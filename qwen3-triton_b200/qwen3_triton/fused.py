@@ -1,7 +1,7 @@
 """Decoder layer as ONE autograd node with a hand-written backward, driving the C ABI directly.
 
 The operator-level graph (one autograd.Function per RMSNorm / linear / RoPE / attention / SwiGLU, as in the
-reference qwen3_triton/components.py:9-54) costs about forty Python autograd nodes, four transpose copies and
+reference qwen3_triton/components.py:9-54 and _model.py:84-108) costs about forty Python autograd nodes, four transpose copies and
 two residual-add kernels per layer and direction. At 2048 tokens per GPU a B200 finishes those kernels faster
 than Python can launch them. This module keeps the same math and the same parameters but
 
@@ -22,8 +22,7 @@ operator-level modules.
 import torch
 
 from . import _abi
-from ._model import TritonDecoderLayer, TritonQwen3Model
-from .components import Attention, HFOrderNorm, MLP
+from ._model import Backbone, DecoderBlock
 
 
 def _empty(shape, like, dtype=None):
@@ -287,16 +286,12 @@ def fused_layer_supported(x, head_dim):
     return x.is_cuda and x.dtype in (torch.bfloat16, torch.float16) and head_dim == 128
 
 
-class FusedDecoderLayer(TritonDecoderLayer):
-    """Same parameters (and names) as the operator-level DecoderLayer; forward maps (resid, delta) to
+class FusedDecoderLayer(DecoderBlock):
+    """Same parameters (and names) as the operator-level DecoderBlock; forward maps (resid, delta) to
     (resid', delta') through FusedLayerFn."""
 
-    def __init__(self, c, options):
-        torch.nn.Module.__init__(self)
-        self.self_attn = Attention(c, options)
-        self.mlp = MLP(c, options)
-        self.input_layernorm = HFOrderNorm(c.hidden_size, c.rms_norm_eps)
-        self.post_attention_layernorm = HFOrderNorm(c.hidden_size, c.rms_norm_eps)
+    def __init__(self, c, recipe):
+        super().__init__(c, recipe)
         self.recompute = 0      # 0 none, 1 selective, 2 full (see module docstring)
 
     def weights(self):
@@ -305,31 +300,23 @@ class FusedDecoderLayer(TritonDecoderLayer):
                 a.q_norm.weight, a.k_norm.weight, self.post_attention_layernorm.weight, m.gate_proj.weight,
                 m.up_proj.weight, m.down_proj.weight)
 
-    def forward(self, resid, delta, position_embeddings):
-        cos, sin = position_embeddings
-        a = self.self_attn
+    def forward(self, resid, delta, rope):
+        cos, sin = rope
         b, s, _ = resid.shape
-        meta = (b, s, a.num_heads, a.num_kv_heads, a.head_dim, float(self.input_layernorm.eps))
+        meta = (b, s, self.heads, self.kv_heads, self.head_dim, float(self.input_layernorm.eps))
         return FusedLayerFn.apply(resid, delta, cos, sin, meta, self.recompute, *self.weights())
 
 
-class AddNorm(HFOrderNorm):
-    """Final norm taking the (resid, delta) pair; called as a module so that FSDP's pre-forward hook has
-    gathered its weight."""
-
-    def forward(self, resid, delta=None):
-        from .kernels.norm import add_rms_norm, rms_norm
-        if delta is None:
-            return rms_norm(resid, self.weight, self.eps)
-        return add_rms_norm(delta, resid, self.weight, self.eps)[0]
+def _final_norm(resid, delta, scale):
+    """RMSNorm of the (resid, delta) pair the last layer hands over."""
+    from .kernels.norm import add_rms_norm, rms_norm
+    if delta is None:
+        return rms_norm(resid, scale.weight, scale.eps)
+    return add_rms_norm(delta, resid, scale.weight, scale.eps)[0]
 
 
-class FusedBackbone(TritonQwen3Model):
-    decoder_class = FusedDecoderLayer
-
-    def __init__(self, c, options):
-        super().__init__(c, options)
-        self.norm = AddNorm(c.hidden_size, c.rms_norm_eps)
+class FusedBackbone(Backbone):
+    block_class = FusedDecoderLayer
 
     def set_recompute(self, level):
         """0 / False: keep everything; 1 / 'selective'; 2 / True / 'full'."""
@@ -338,18 +325,11 @@ class FusedBackbone(TritonQwen3Model):
             layer.recompute = int(level)
 
     def forward(self, ids, position_ids=None):
-        from ._model import position_ids_for
-        x = self.embed_tokens(ids)
-        if position_ids is None:
-            position_ids = position_ids_for(ids)
-        if position_ids.shape == (1, ids.shape[1]) and ids.shape[0] != 1:
-            position_ids = position_ids.expand(ids.shape[0], -1).contiguous()
-        if position_ids.shape != ids.shape:
-            raise ValueError('position_ids must match batch and sequence')
-        if not fused_layer_supported(x, self.layers[0].self_attn.head_dim):
+        x = self.lookup(ids)
+        if not fused_layer_supported(x, self.layers[0].head_dim):
             raise ValueError('Fused decoder layers need bf16/fp16 CUDA tensors and head_dim 128')
-        positions = self.rotary_emb(position_ids, x.dtype)
+        rope = self.rope_for(ids, position_ids, x.dtype)
         resid, delta = x, None
         for layer in self.layers:
-            resid, delta = layer(resid, delta, positions)
-        return self.norm(resid, delta)
+            resid, delta = layer(resid, delta, rope)
+        return self.norm(_final_norm, resid, delta)

@@ -1,48 +1,53 @@
-"""Public Qwen3 training model and variant factory (reference qwen3_triton/model.py:7-23). Unlike the
-reference, any Qwen3-shaped configuration is accepted (layer count, widths), so the 4-layer slice and the
-tiny test model use the same class as the 8B model."""
-from dataclasses import fields, replace
+"""Public Qwen3 training model and variant factory (import path of the reference's qwen3_triton/model.py).
 
-from ._model import TritonQwen3ForCausalLM
-from .components import Backbone, HFOrderNorm  # noqa: F401
-from .configuration import OptimizationOptions, options_for_variant
+Unlike the reference class, any Qwen3-shaped configuration is accepted (layer count, widths), so the 4-layer slice and
+the tiny test model use the same class as the 8B model.
+"""
+from dataclasses import replace
 
-_PRECISION_KEYS = {'xor_sum', 'lse_fma', 'native_delta', 'native_dq', 'sum_fma'}
+from ._model import OptimizationOptions, TritonQwen3ForCausalLM, options_for_variant, widen_options
+
+PRECISION_SWITCHES = ('xor_sum', 'lse_fma', 'native_delta', 'native_dq', 'sum_fma')
+
+
+def checked_precision_options(given):
+    """The five attention precision switches of the reference API, all explicit booleans (default: all on). The CUDA
+    attention kernels have one arithmetic, so the switches are validated, stored with the options and passed on."""
+    if given is None:
+        return dict.fromkeys(PRECISION_SWITCHES, True)
+    if sorted(given) != sorted(PRECISION_SWITCHES) or not all(isinstance(v, bool) for v in given.values()):
+        raise ValueError('Explicit five boolean precision options required')
+    return dict(given)
 
 
 class PrecisionQwen3ForCausalLM(TritonQwen3ForCausalLM):
-    backbone_class = Backbone
+    """The graph the 8B training runs use: options widened to the full switch set (missing switches off, as when the
+    reference is handed a bare ComputeOptions) plus the attention precision switches."""
 
     def __init__(self, config, options=None, *, precision_options=None):
-        if precision_options is None:
-            precision_options = dict(xor_sum=True, lse_fma=True, native_delta=True, native_dq=True, sum_fma=True)
-        if set(precision_options) != _PRECISION_KEYS or any(type(v) is not bool for v in precision_options.values()):
-            raise ValueError('Explicit five boolean precision options required')
-        names = [f.name for f in fields(OptimizationOptions) if f.name != 'precision_options']
-        if options is None:
-            options = OptimizationOptions(**{n: False for n in names})
-        elif not isinstance(options, OptimizationOptions):
-            options = OptimizationOptions(**{n: getattr(options, n, False) for n in names})
-        options = replace(options, precision_options=tuple(precision_options.items()))
-        super().__init__(config, options)
+        chosen = checked_precision_options(precision_options)
+        wide = widen_options(options if options is not None else object())
+        super().__init__(config, replace(wide, precision_options=tuple(chosen.items())))
 
 
 class FusedQwen3ForCausalLM(PrecisionQwen3ForCausalLM):
-    """Same parameters and state dict; every decoder layer is one fused autograd node (qwen3_triton/fused.py)."""
+    """Same parameters and state dict; every decoder layer is one fused autograd node (qwen3_triton/fused.py).
+    With `fused_loss` set, forward(ids, labels) goes from hidden states to the loss without materialising logits."""
 
     def __init__(self, config, options=None, *, precision_options=None):
         from .fused import FusedBackbone
         self.backbone_class = FusedBackbone
         super().__init__(config, options, precision_options=precision_options)
-        self.fused_loss = False     # True: forward(ids, labels) returns the loss only; logits are never materialised
+        self.fused_loss = False
 
     def forward(self, input_ids, labels=None, **kwargs):
-        if not self.fused_loss or labels is None:
+        from ._model import Leaf
+        if not self.fused_loss or labels is None or not isinstance(self.lm_head, Leaf):
             return super().forward(input_ids, labels, **kwargs)
         from types import SimpleNamespace
+        from ._model import _UNSUPPORTED
         from .kernels.fused_loss import fused_linear_cross_entropy
-        if any(kwargs.get(k) for k in ('use_cache', 'past_key_values', 'attention_mask', 'output_attentions',
-                                       'output_hidden_states', 'logits_to_keep')):
+        if any(kwargs.get(k) for k in _UNSUPPORTED):
             raise ValueError('Only dense unpadded causal training without cache/extra outputs is implemented; no fallback')
         hidden = self.model(input_ids, kwargs.get('position_ids'))
         loss = fused_linear_cross_entropy(hidden, self.lm_head.weight, labels)

@@ -7,7 +7,7 @@ reference qwen3_triton/runtime/adamw.py:64-159 (class name kept so call sites do
 bumps autograd version counters after the in-place update.
 """
 import copy
-from collections import defaultdict
+from typing import NamedTuple
 
 import torch
 
@@ -16,6 +16,28 @@ from .. import _abi
 
 def local(tensor):
     return tensor.to_local() if hasattr(tensor, 'to_local') else tensor
+
+
+STATE_KEYS = ('step', 'exp_avg', 'exp_avg_sq')
+UNSUPPORTED_MODES = ('amsgrad', 'maximize', 'differentiable', 'capturable')
+
+
+class _Row(NamedTuple):
+    """One parameter's line of the device pointer table (q3_adamw_multi / q3_adamw_multi_mp column order)."""
+    param: int
+    grad: int            # fp32 gradient, or 0 when a low-precision gradient is given
+    exp_avg: int
+    exp_avg_sq: int
+    step: int
+    numel: int
+    first_block: int
+    lowp_grad: int = 0   # bf16/fp16 gradient read directly (single-GPU mixed precision)
+    lowp_copy: int = 0   # bf16/fp16 working copy refreshed in the same pass
+    lowp_dtype: int = 0
+
+
+def _fp32_cuda_contiguous(t):
+    return t.dtype == torch.float32 and t.is_cuda and t.is_contiguous()
 
 
 class TritonAdamW(torch.optim.Optimizer):
@@ -29,59 +51,122 @@ class TritonAdamW(torch.optim.Optimizer):
         self.kernel_steps = 0
         self._tables = {}
 
+    # ------------------------------------------------------------------------------------------ restore
+    def _checked_entry(self, parameter, entry):
+        """The (step, exp_avg, exp_avg_sq) tensors of one checkpoint entry, validated against the local shard."""
+        if set(entry) != set(STATE_KEYS):
+            raise ValueError('Expected plain FP32 AdamW checkpoint state')
+        shard = local(parameter)
+        tensors = []
+        for key in STATE_KEYS:
+            t = local(entry[key])
+            if t.dtype != torch.float32 or not t.is_contiguous():
+                raise ValueError('Contiguous FP32 checkpoint state required before upload')
+            if t.numel() != 1 if key == 'step' else t.shape != shard.shape:
+                raise ValueError('Local checkpoint shape differs')
+            if t.device.type != 'cpu' and t.device != shard.device:
+                raise ValueError('Load CPU or same-device local shards only')
+            tensors.append(t)
+        return tensors
+
     def load_state_dict(self, state_dict):
-        # Validate first, then reuse the existing device buffers and upload one tensor at a time, so a
-        # restore never holds a second copy of the moments on the device.
-        state_dict = state_dict.copy()
+        """Restore in two passes: first check the whole checkpoint against the current groups and shards without
+        touching the device, then copy tensor by tensor into the buffers this optimizer already holds (allocating
+        only what is missing). The stock Optimizer.load_state_dict builds a complete second state on the device
+        before dropping the old one - a transient extra copy of both moments (reference
+        qwen3_triton/runtime/adamw.py:76-115 avoids the same thing)."""
+        state_dict = dict(state_dict)
         for hook in self._optimizer_load_state_dict_pre_hooks.values():
-            changed = hook(self, state_dict)
-            if changed is not None:
-                state_dict = changed
+            state_dict = hook(self, state_dict) or state_dict
         saved_groups = copy.deepcopy(state_dict['param_groups'])
-        if len(saved_groups) != len(self.param_groups) or any(
-                len(a['params']) != len(b['params']) for a, b in zip(saved_groups, self.param_groups)):
+        if [len(g['params']) for g in saved_groups] != [len(g['params']) for g in self.param_groups]:
             raise ValueError('Optimizer checkpoint group layout differs')
-        specifications = []
-        groups = []
+        pending, groups = [], []
         for saved, current in zip(saved_groups, self.param_groups):
-            if any(saved.get(key, False) for key in ['amsgrad', 'maximize', 'differentiable', 'capturable']):
+            if any(saved.get(mode) for mode in UNSUPPORTED_MODES):
                 raise ValueError('Unsupported optimizer checkpoint mode')
-            groups.append(dict(saved, params=current['params']))
+            groups.append({**saved, 'params': current['params']})
             for saved_id, parameter in zip(saved['params'], current['params']):
-                source_state = state_dict['state'].get(saved_id, {})
-                if not source_state:
-                    continue
-                if set(source_state) != {'step', 'exp_avg', 'exp_avg_sq'}:
-                    raise ValueError('Expected plain FP32 AdamW checkpoint state')
-                p = local(parameter)
-                for key in ['step', 'exp_avg', 'exp_avg_sq']:
-                    source = local(source_state[key])
-                    if source.dtype != torch.float32 or not source.is_contiguous():
-                        raise ValueError('Contiguous FP32 checkpoint state required before upload')
-                    if (key == 'step' and source.numel() != 1) or (key != 'step' and source.shape != p.shape):
-                        raise ValueError('Local checkpoint shape differs')
-                    if source.device.type != 'cpu' and source.device != p.device:
-                        raise ValueError('Load CPU or same-device local shards only')
-                specifications.append((parameter, source_state))
-        restored = defaultdict(dict)
-        versions = []
-        for parameter, sources in specifications:
-            p = local(parameter)
-            previous = self.state.get(parameter, {})
-            for key in ['step', 'exp_avg', 'exp_avg_sq']:
-                source = local(sources[key])
-                target = local(previous[key]) if key in previous else None
-                if target is None or target.shape != source.shape or target.device != p.device or target.dtype != torch.float32:
-                    target = torch.empty(source.shape, device=p.device, dtype=torch.float32)
-                target.copy_(source)
-                restored[parameter][key] = target
-                versions.append(target)
-        if versions:
-            torch.autograd.graph.increment_version(versions)
-        self.__setstate__(dict(state=restored, param_groups=groups))
+                entry = state_dict['state'].get(saved_id)
+                if entry:
+                    pending.append((parameter, self._checked_entry(parameter, entry)))
+        restored, touched = {}, []
+        for parameter, tensors in pending:
+            device = local(parameter).device
+            held = self.state.get(parameter, {})
+            slot = {}
+            for key, source in zip(STATE_KEYS, tensors):
+                buffer = local(held[key]) if key in held else None
+                reusable = (buffer is not None and buffer.shape == source.shape and buffer.device == device
+                            and buffer.dtype == torch.float32)
+                if not reusable:
+                    buffer = torch.empty(source.shape, device=device, dtype=torch.float32)
+                buffer.copy_(source)
+                slot[key] = buffer
+                touched.append(buffer)
+            restored[parameter] = slot
+        if touched:
+            torch.autograd.graph.increment_version(touched)
+        self.__setstate__({'state': restored, 'param_groups': groups})
         self._tables = {}
         for hook in self._optimizer_load_state_dict_post_hooks.values():
             hook(self)
+
+    # ------------------------------------------------------------------------------------------ step
+    def _state_for(self, parameter, shard):
+        state = self.state[parameter]
+        if not state:
+            state['step'] = torch.zeros((), device=shard.device, dtype=torch.float32)
+            state['exp_avg'] = torch.zeros(shard.shape, device=shard.device, dtype=torch.float32)
+            state['exp_avg_sq'] = torch.zeros(shard.shape, device=shard.device, dtype=torch.float32)
+        m, v, step = local(state['exp_avg']), local(state['exp_avg_sq']), state['step']
+        if (m.shape != shard.shape or v.shape != shard.shape or m.dtype != torch.float32 or v.dtype != torch.float32
+                or step.dtype != torch.float32 or step.numel() != 1 or step.device != shard.device):
+            raise ValueError('Invalid local FP32 AdamW state')
+        return m, v, step
+
+    def _rows_of(self, group):
+        """(table rows, total blocks, device, tensors the kernel will modify) for the parameters that have a gradient."""
+        rows, touched, blocks, device = [], [], 0, None
+        for parameter in group['params']:
+            low_g = getattr(parameter, 'q3_lowp_grad', None)      # set by runtime/mixed_precision.py
+            low_p = getattr(parameter, 'q3_lowp_copy', None)
+            if parameter.grad is None and low_g is None:
+                continue
+            shard = local(parameter)
+            grad = local(parameter.grad) if low_g is None else None
+            if not _fp32_cuda_contiguous(shard) or (grad is not None and (
+                    not _fp32_cuda_contiguous(grad) or grad.device != shard.device or grad.shape != shard.shape
+                    or grad.is_sparse)):
+                raise ValueError('Matching contiguous local CUDA FP32 parameter/gradient required')
+            for low in (low_g, low_p):
+                if low is not None and (low.dtype not in (torch.bfloat16, torch.float16) or low.shape != shard.shape
+                                        or low.device != shard.device or not low.is_contiguous()):
+                    raise ValueError('Low-precision gradient / working copy must match the FP32 parameter')
+            if device not in (None, shard.device):
+                raise ValueError('One CUDA device per group')
+            device = shard.device
+            if not shard.numel():
+                continue
+            m, v, step = self._state_for(parameter, shard)
+            low = low_g if low_g is not None else low_p
+            rows.append(_Row(shard.data_ptr(), grad.data_ptr() if grad is not None else 0, m.data_ptr(), v.data_ptr(),
+                             step.data_ptr(), shard.numel(), blocks, _abi.ptr(low_g) or 0, _abi.ptr(low_p) or 0,
+                             _abi.dt(low.dtype) if low is not None else 0))
+            blocks += -(-shard.numel() // self.block)
+            touched += [parameter, m, v, step] + ([shard] if shard is not parameter else [])
+        return rows, blocks, device, touched
+
+    def _device_table(self, index, rows, columns, device):
+        """Pointer table and per-tensor coefficient scratch on the device; rebuilt only when a pointer changed
+        (gradients re-allocated), since uploading it costs a synchronising copy."""
+        key = tuple(r[:columns] for r in rows)
+        cached = self._tables.get(index)
+        if cached is None or cached[0] != key:
+            meta = torch.tensor(key, dtype=torch.int64).to(device)
+            coeff = torch.empty((len(rows), 3), device=device, dtype=torch.float32)
+            cached = self._tables[index] = (key, meta, coeff)
+        return cached[1], cached[2]
 
     @torch.no_grad()
     def step(self, closure=None):
@@ -92,80 +177,24 @@ class TritonAdamW(torch.optim.Optimizer):
         if getattr(self, 'grad_scale', None) is not None or getattr(self, 'found_inf', None) is not None:
             raise ValueError('GradScaler is not supported by this explicit BF16/FP32 path')
         for index, group in enumerate(self.param_groups):
-            rows = []
-            blocks = 0
-            device = None
-            changed = []
-            mixed = False
-            for parameter in group['params']:
-                # single-GPU mixed precision (runtime/mixed_precision.py): a bf16 gradient to read directly and/or
-                # a bf16 working copy to refresh in the same pass
-                low_g = getattr(parameter, 'q3_lowp_grad', None)
-                low_p = getattr(parameter, 'q3_lowp_copy', None)
-                if parameter.grad is None and low_g is None:
-                    continue
-                p = local(parameter)
-                g = local(parameter.grad) if low_g is None else None
-                if g is not None and (g.dtype != torch.float32 or p.device != g.device or not g.is_contiguous()
-                                      or p.shape != g.shape or g.is_sparse):
-                    raise ValueError('Matching contiguous local CUDA FP32 parameter/gradient required')
-                if p.dtype != torch.float32 or not p.is_cuda or not p.is_contiguous():
-                    raise ValueError('Matching contiguous local CUDA FP32 parameter/gradient required')
-                for low in (low_g, low_p):
-                    if low is not None and (low.dtype not in (torch.bfloat16, torch.float16) or low.shape != p.shape
-                                            or low.device != p.device or not low.is_contiguous()):
-                        raise ValueError('Low-precision gradient / working copy must match the FP32 parameter')
-                mixed = mixed or low_g is not None or low_p is not None
-                if device is not None and device != p.device:
-                    raise ValueError('One CUDA device per group')
-                device = p.device
-                if not p.numel():
-                    continue
-                state = self.state[parameter]
-                if not state:
-                    state['step'] = torch.zeros((), device=device, dtype=torch.float32)
-                    state['exp_avg'] = torch.zeros(p.shape, device=device, dtype=torch.float32)
-                    state['exp_avg_sq'] = torch.zeros(p.shape, device=device, dtype=torch.float32)
-                m, v = local(state['exp_avg']), local(state['exp_avg_sq'])
-                step = state['step']
-                if (m.shape != p.shape or v.shape != p.shape or m.dtype != torch.float32 or v.dtype != torch.float32
-                        or step.dtype != torch.float32 or step.numel() != 1 or step.device != device):
-                    raise ValueError('Invalid local FP32 AdamW state')
-                rows.append((p.data_ptr(), g.data_ptr() if g is not None else 0, m.data_ptr(), v.data_ptr(), step.data_ptr(),
-                             p.numel(), blocks, low_g.data_ptr() if low_g is not None else 0,
-                             low_p.data_ptr() if low_p is not None else 0,
-                             _abi.dt((low_g if low_g is not None else low_p).dtype) if (low_g is not None or low_p is not None) else 0))
-                blocks += -(-p.numel() // self.block)
-                changed.extend([parameter, m, v, step])
-                if p is not parameter:
-                    changed.append(p)
+            rows, blocks, device, touched = self._rows_of(group)
             if not rows:
                 continue
-            # The pointer table only changes when gradients are re-allocated; cache the device copy.
-            lowp = {r[9] for r in rows if r[9]}
-            if len(lowp) > 1:
+            low_dtypes = {r.lowp_dtype for r in rows if r.lowp_dtype}
+            if len(low_dtypes) > 1:
                 raise ValueError('One low-precision dtype per group')
-            rows = [r[:9] if mixed else r[:7] for r in rows]
-            key = tuple(rows)
-            cached = self._tables.get(index)
-            if cached is None or cached[0] != key:
-                cpu = torch.tensor(rows, dtype=torch.int64)
-                meta = torch.empty(cpu.shape, device=device, dtype=torch.int64)
-                meta.copy_(cpu)
-                coeff = torch.empty((len(rows), 3), device=device, dtype=torch.float32)
-                cached = (key, meta, coeff)
-                self._tables[index] = cached
-            _, meta, coeff = cached
-            b1, b2 = group['betas']
-            if mixed:
+            beta1, beta2 = group['betas']
+            scalars = (float(group['lr']), float(beta1), float(beta2), float(group['weight_decay']), float(group['eps']))
+            if low_dtypes:
+                meta, coeff = self._device_table(index, rows, 9, device)
+                every_row_both = int(all(r.lowp_grad and r.lowp_copy for r in rows))
                 _abi.call('q3_adamw_multi_mp', meta.data_ptr(), coeff.data_ptr(), len(rows), blocks, self.block,
-                          lowp.pop(), int(all(row[7] and row[8] for row in rows)), float(group['lr']), float(b1),
-                          float(b2), float(group['weight_decay']), float(group['eps']), _abi.stream())
+                          low_dtypes.pop(), every_row_both, *scalars, _abi.stream())
             else:
-                _abi.call('q3_adamw_multi', meta.data_ptr(), coeff.data_ptr(), len(rows), blocks, self.block,
-                          float(group['lr']), float(b1), float(b2), float(group['weight_decay']), float(group['eps']),
+                meta, coeff = self._device_table(index, rows, 7, device)
+                _abi.call('q3_adamw_multi', meta.data_ptr(), coeff.data_ptr(), len(rows), blocks, self.block, *scalars,
                           _abi.stream())
-            torch.autograd.graph.increment_version(changed)
+            torch.autograd.graph.increment_version(touched)
         self.kernel_steps += 1
         return loss
 

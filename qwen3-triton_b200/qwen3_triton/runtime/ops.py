@@ -19,12 +19,14 @@ _seen_once = {}
 _lib = None
 
 
-def plan_copy_in(numels, out_ptr, out_itemsize, rank, input_ptrs):
-    """Table rows for all_gather_copy_in: shard i -> its slice of this rank's all-gather input."""
-    total = sum(numels)
+def plan_copy_in(split_sizes, out_ptr, out_itemsize, rank, input_ptrs, input_numel=None):
+    """Table rows for all_gather_copy_in: shard i -> its slice of this rank's all-gather input, which starts
+    `input_numel` * rank elements into the output (input_numel = sum of the split sizes unless the caller says
+    otherwise) and is cut by `split_sizes`."""
+    first = (sum(split_sizes) if input_numel is None else input_numel) * rank
     rows, offset = [], 0
-    for n, p in zip(numels, input_ptrs):
-        rows.append((p, out_ptr + (total * rank + offset) * out_itemsize, 1, n, n, n, n))
+    for n, p in zip(split_sizes, input_ptrs):
+        rows.append((p, out_ptr + (first + offset) * out_itemsize, 1, n, n, n, n))
         offset += n
     return rows
 
@@ -132,13 +134,16 @@ _FLOATS = (torch.float32, torch.bfloat16, torch.float16)
 def all_gather_copy_in(all_gather_inputs, all_gather_output, inp_split_sizes, all_gather_input_numel, rank):
     all_gather_input = all_gather_output.narrow(0, all_gather_input_numel * rank, all_gather_input_numel)
     dtypes = {t.dtype for t in all_gather_inputs}
-    if (len(dtypes) != 1 or next(iter(dtypes)) not in _FLOATS or all_gather_output.dtype not in _FLOATS
+    sizes = [int(n) for n in inp_split_sizes]
+    # the kernel path needs the split FSDP asked for to be the inputs' own sizes, filling this rank's slot exactly
+    consistent = sizes == [t.numel() for t in all_gather_inputs] and sum(sizes) == all_gather_input_numel
+    if (not consistent or len(dtypes) != 1 or next(iter(dtypes)) not in _FLOATS or all_gather_output.dtype not in _FLOATS
             or not all(t.is_contiguous() for t in all_gather_inputs)):
         with torch.no_grad():
             torch._foreach_copy_(torch.split(all_gather_input, inp_split_sizes), all_gather_inputs)
         return all_gather_input, all_gather_output
-    rows = plan_copy_in([t.numel() for t in all_gather_inputs], all_gather_output.data_ptr(),
-                        all_gather_output.element_size(), rank, [t.data_ptr() for t in all_gather_inputs])
+    rows = plan_copy_in(sizes, all_gather_output.data_ptr(), all_gather_output.element_size(), rank,
+                        [t.data_ptr() for t in all_gather_inputs], all_gather_input_numel)
     _launch(rows, next(iter(dtypes)), all_gather_output.dtype, all_gather_output.device)
     return all_gather_input, all_gather_output
 

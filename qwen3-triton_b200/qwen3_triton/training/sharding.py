@@ -7,8 +7,6 @@ forward (no second all-gather in backward); every `checkpoint_every`-th layer is
 (non-reentrant); the lm_head becomes a VocabParallelCE whose fp32 vocabulary shard is kept out of FSDP because
 its gradient is already averaged over data ranks. The wrapped model maps (input_ids, labels) to a loss only.
 """
-from types import SimpleNamespace
-
 import torch
 from torch.distributed.fsdp import MixedPrecisionPolicy, fully_shard
 
@@ -37,22 +35,6 @@ def wrap_decoder_checkpoint(layer, *, mode='full'):
     return checkpoint_wrapper(layer, preserve_rng_state=True, checkpoint_impl=CheckpointImpl.NO_REENTRANT)
 
 
-class VocabLossQwen3(PrecisionQwen3ForCausalLM):
-    """Loss-only graph: hidden states go straight into the vocabulary-parallel head."""
-
-    def forward(self, input_ids, labels=None, *, position_ids=None, use_cache=False, attention_mask=None,
-                past_key_values=None, output_attentions=False, output_hidden_states=False, return_dict=True,
-                logits_to_keep=0, diagnostic_logits=False):
-        if (labels is None or use_cache or attention_mask is not None or past_key_values is not None
-                or output_attentions or output_hidden_states or logits_to_keep):
-            raise ValueError('Vocabulary CE requires dense unpadded labeled loss-only training/evaluation')
-        hidden = self.model(input_ids, position_ids)
-        loss, logits = self.lm_head(hidden, labels, diagnostics=diagnostic_logits)
-        if not return_dict:
-            return (loss, logits)
-        return SimpleNamespace(loss=loss, logits=logits)
-
-
 def shard_vocab_loss_model(model, *, keep_full_layers, checkpoint_every, skip_embedding_backward_gather,
                            fused_vocab_dw=False, communication=None, mesh=None, checkpoint_mode='full',
                            layers_per_unit=1, vocab_parallel_embedding=False, forward_prefetch=1):
@@ -67,7 +49,7 @@ def shard_vocab_loss_model(model, *, keep_full_layers, checkpoint_every, skip_em
         raise ValueError('Invalid retention count')
     if not isinstance(model, PrecisionQwen3ForCausalLM):
         raise TypeError('Supported Qwen3 graph required')
-    model.__class__ = VocabLossQwen3
+    # the graph hands (hidden, labels) to any lm_head that is not a plain weight leaf: the model becomes loss-only
     model.lm_head = VocabParallelCE(model.lm_head.weight.detach().cpu(), fused_dw=fused_vocab_dw,
                                     communication=communication)
     body = model.model

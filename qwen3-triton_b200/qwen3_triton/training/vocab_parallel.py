@@ -44,140 +44,146 @@ def _reduce(owner, tensor, op):
         owner.communication.all_reduce(tensor, operation)
 
 
-class _FusedVocabCE(torch.autograd.Function):
-    """Same contract as _VocabCE, but neither the logits shard nor its gradient is ever materialised: the
-    projection GEMM reduces to softmax statistics in its epilogue, and backward walks the local vocabulary in
-    chunks (qwen3_triton/kernels/fused_loss.py)."""
+def _check_head_inputs(hidden, weight, labels):
+    b, s, _ = hidden.shape
+    ok = (hidden.dtype == torch.bfloat16 and weight.dtype == torch.float32 and labels.dtype == torch.int64
+          and labels.shape == (b, s) and s >= 2 and hidden.is_contiguous() and labels.is_contiguous()
+          and hidden.device == weight.device == labels.device)
+    if not ok:
+        raise ValueError('Matching contiguous BF16 hidden, int64 labels and local FP32 weight required')
 
-    @staticmethod
-    def forward(ctx, hidden, weight, labels, ignore, owner):
-        from ..kernels import fused_loss as F
-        world, rank = owner.world, owner.rank
-        b, s, k = hidden.shape
-        r = b * s
-        v = weight.shape[0]
-        if (hidden.dtype != torch.bfloat16 or weight.dtype != torch.float32 or labels.dtype != torch.int64
-                or labels.shape != (b, s) or s < 2 or not hidden.is_contiguous() or not labels.is_contiguous()
-                or hidden.device != weight.device or hidden.device != labels.device):
-            raise ValueError('Matching contiguous BF16 hidden, int64 labels and local FP32 weight required')
-        all_hidden = torch.empty((world * r, k), device=hidden.device, dtype=hidden.dtype)
-        all_labels = torch.empty(world * r, device=hidden.device, dtype=labels.dtype)
-        _gather(owner, all_hidden, hidden.view(r, k))
-        _gather(owner, all_labels, labels.view(-1))
-        w = cast_tensor(weight, torch.bfloat16)
-        eff = F.shifted_labels(all_labels.view(world * b, s), ignore, world * v)
-        local_lse, target = F.local_lse_and_target(all_hidden, w, eff, rank * v, ignore)
-        maximum = local_lse.clone()
-        _reduce(owner, maximum, dist.ReduceOp.MAX)
-        packed = packed_statistics(local_lse, maximum, target)
-        _reduce(owner, packed, dist.ReduceOp.SUM)
-        lse = torch.empty_like(local_lse)
-        _, counts, means = F.finish(lse, packed[1], eff, r, ignore, maximum, packed)
-        loss = means[rank].clone()
-        ctx.save_for_backward(all_hidden, w, eff, lse, counts)
-        ctx.rows, ctx.sequence, ctx.start, ctx.ignore, ctx.owner = r, s, rank * v, ignore, owner
-        owner.forward_calls += 1
-        return loss
 
-    @staticmethod
-    def backward(ctx, up):
+def _reduce_scatter_rows(owner, partial, rows, dtype):
+    """Each rank's own `rows` rows of the sum over ranks of `partial` [world*rows, H]."""
+    if owner.world == 1:
+        return partial
+    out = torch.empty((rows, partial.shape[1]), device=partial.device, dtype=dtype)
+    if owner.communication is None:
+        dist.reduce_scatter_tensor(out, partial, op=dist.ReduceOp.SUM)
+    else:
+        owner.communication.reduce_scatter(out, partial, 'sum')
+    return out
+
+
+class _StreamedScores:
+    """Scores of the local vocabulary slice that never exist in memory: the projection GEMM reduces every logit
+    tile to softmax statistics in its epilogue, and backward walks the slice in chunks, recomputing one chunk of
+    logits into dZ at a time (qwen3_triton/kernels/fused_loss.py)."""
+    keeps_logits = False
+
+    def statistics(self, all_hidden, w, all_labels, batch_rows, sequence, start, total, ignore):
         from ..kernels import fused_loss as F
-        h, w, eff, lse, counts = ctx.saved_tensors
-        owner = ctx.owner
-        world, r, k = owner.world, ctx.rows, h.shape[1]
-        ups = torch.empty(world, device=h.device, dtype=up.dtype)
-        _gather(owner, ups, up.contiguous().view(1))
-        partial_dx, dw = F.head_backward(h, w, eff, lse, ups, counts, r, ctx.start, ctx.ignore, owner.chunk,
+        eff = F.shifted_labels(all_labels.view(-1, sequence), ignore, total)
+        local_lse, target = F.local_lse_and_target(all_hidden, w, eff, start, ignore)
+        return local_lse, target, (eff,)
+
+    def finish(self, maximum, packed, kept, rows, sequence, world, ignore):
+        from ..kernels import fused_loss as F
+        lse = torch.empty_like(maximum)
+        _, counts, means = F.finish(lse, packed[1], kept[0], rows, ignore, maximum, packed)
+        return lse, counts, means
+
+    def gradients(self, owner, all_hidden, w, kept, lse, counts, ups, rows, sequence, start, ignore):
+        from ..kernels import fused_loss as F
+        partial_dx, dw = F.head_backward(all_hidden, w, kept[0], lse, ups, counts, rows, start, ignore, owner.chunk,
                                          torch.float32)
+        if owner.world > 1:
+            accumulate_weight_gradient(dw, dw, owner.world, True)     # mean over data ranks, in place
+        return partial_dx, dw
+
+
+class _StoredScores:
+    """The reference's arrangement (qwen3_triton/training/vocab_parallel.py:38-89 there): the [world*rows, V/world]
+    logits slice is written once by the projection GEMM, read by the statistics and gradient kernels, and can be
+    handed back in full for diagnostics."""
+    keeps_logits = True
+
+    def statistics(self, all_hidden, w, all_labels, batch_rows, sequence, start, total, ignore):
+        logits = matmul(all_hidden, w.t(), optimized=True)
+        local_lse, target = local_statistics(logits, all_labels, sequence, start, vocab_total=total, ignore=ignore)
+        return local_lse, target, (all_labels, logits)
+
+    def finish(self, maximum, packed, kept, rows, sequence, world, ignore):
+        return finish_statistics(maximum, packed, kept[0], rows, sequence, world, ignore)
+
+    def gradients(self, owner, all_hidden, w, kept, lse, counts, ups, rows, sequence, start, ignore):
+        labels, logits = kept
+        world = owner.world
+        dz = logit_gradient(logits, labels, lse, counts, ups, rows, sequence, start, ignore,
+                            vocab_total=world * w.shape[0])
+        partial_dx = matmul(dz, w, optimized=True, output_dtype=torch.float32)
+        if owner.fused_dw:
+            from ..kernels.vocab_dw import weight_gradient_mean
+            return partial_dx, weight_gradient_mean(dz, all_hidden, rows, world, owner.dw_config)
+        dw = torch.empty(w.shape, device=w.device, dtype=torch.float32)
+        for source in range(world):          # one product per data rank, averaged in rank order
+            part = slice(source * rows, (source + 1) * rows)
+            accumulate_weight_gradient(matmul(dz[part].t(), all_hidden[part], optimized=True), dw, world, source == 0)
+        return partial_dx, dw
+
+    def dense_logits(self, owner, kept, batch, rows, sequence):
+        """[B, S, V] logits of this rank's tokens: every rank sends each peer that peer's rows of its slice."""
+        logits = kept[1]
+        world, v = owner.world, logits.shape[1]
+        received = torch.empty_like(logits)
         if world == 1:
-            local_dx = partial_dx
+            received.copy_(logits)
+        elif owner.communication is None:
+            dist.all_to_all_single(received, logits)
         else:
-            local_dx = torch.empty((r, k), device=h.device, dtype=torch.float32)
-            if owner.communication is None:
-                dist.reduce_scatter_tensor(local_dx, partial_dx, op=dist.ReduceOp.SUM)
-            else:
-                owner.communication.reduce_scatter(local_dx, partial_dx, 'sum')
-            accumulate_weight_gradient(dw, dw, world, True)     # mean over data ranks, in place
-        dx = cast_tensor(local_dx, torch.bfloat16)
-        owner.backward_calls += 1
-        return dx.view(-1, ctx.sequence, k), dw, None, None, None
+            owner.communication.all_to_all(received, logits)
+        return received.view(world, rows, v).transpose(0, 1).contiguous().view(batch, sequence, world * v)
 
 
 class _VocabCE(torch.autograd.Function):
+    """hidden [B,S,H] (this rank's tokens), weight [V/world, H] (this rank's vocabulary rows) -> (loss, logits or
+    None). One protocol for both ways of handling the scores: all-gather hidden states and labels; score the local
+    slice (per-row log-sum-exp and the target logit where the slice owns the label); all-reduce MAX, then SUM of
+    the exp-shifted partition sums and targets; finish to this rank's token-mean loss. Backward: all-gather the
+    upstream scalars, form dZ against the global log-sum-exp, reduce-scatter the fp32 partial dX, keep dW local
+    (already averaged over data ranks). Same arguments and saved quantities as the reference's _VocabCE, with the
+    score handling delegated to `scores`."""
+
     @staticmethod
-    def forward(ctx, hidden, weight, labels, ignore, diagnostics, owner):
+    def forward(ctx, hidden, weight, labels, ignore, diagnostics, owner, scores=None):
+        scores = scores or _StoredScores()
+        _check_head_inputs(hidden, weight, labels)
+        if diagnostics and not scores.keeps_logits:
+            raise ValueError('Diagnostic logits need the stored-scores path')
         world, rank = owner.world, owner.rank
         b, s, k = hidden.shape
-        r = b * s
-        v = weight.shape[0]
-        if (hidden.dtype != torch.bfloat16 or weight.dtype != torch.float32 or labels.dtype != torch.int64
-                or labels.shape != (b, s) or s < 2 or not hidden.is_contiguous() or not labels.is_contiguous()
-                or hidden.device != weight.device or hidden.device != labels.device):
-            raise ValueError('Matching contiguous BF16 hidden, int64 labels and local FP32 weight required')
-        all_hidden = torch.empty((world * r, k), device=hidden.device, dtype=hidden.dtype)
-        all_labels = torch.empty(world * r, device=hidden.device, dtype=labels.dtype)
-        _gather(owner, all_hidden, hidden.view(r, k))
+        rows, v = b * s, weight.shape[0]
+        all_hidden = torch.empty((world * rows, k), device=hidden.device, dtype=hidden.dtype)
+        all_labels = torch.empty(world * rows, device=hidden.device, dtype=labels.dtype)
+        _gather(owner, all_hidden, hidden.view(rows, k))
         _gather(owner, all_labels, labels.view(-1))
         w = cast_tensor(weight, torch.bfloat16)
-        logits = matmul(all_hidden, w.t(), optimized=True)
-        local_lse, target = local_statistics(logits, all_labels, s, rank * v, vocab_total=world * v, ignore=ignore)
+        local_lse, target, kept = scores.statistics(all_hidden, w, all_labels, rows, s, rank * v, world * v, ignore)
         maximum = local_lse.clone()
         _reduce(owner, maximum, dist.ReduceOp.MAX)
         packed = packed_statistics(local_lse, maximum, target)
         _reduce(owner, packed, dist.ReduceOp.SUM)
-        lse, counts, means = finish_statistics(maximum, packed, all_labels, r, s, world, ignore)
-        loss = means[rank].clone()
+        lse, counts, means = scores.finish(maximum, packed, kept, rows, s, world, ignore)
         dense = None
         if diagnostics:
-            received = torch.empty_like(logits)
-            if world == 1:
-                received.copy_(logits)
-            elif owner.communication is None:
-                dist.all_to_all_single(received, logits)
-            else:
-                owner.communication.all_to_all(received, logits)
-            dense = received.view(world, r, v).transpose(0, 1).contiguous().view(b, s, world * v)
+            dense = scores.dense_logits(owner, kept, b, rows, s)
             ctx.mark_non_differentiable(dense)
-        ctx.save_for_backward(all_hidden, w, all_labels, logits, lse, counts)
-        ctx.rows = r
-        ctx.sequence = s
-        ctx.start = rank * v
-        ctx.ignore = ignore
-        ctx.owner = owner
+        ctx.save_for_backward(all_hidden, w, lse, counts, *kept)
+        ctx.rows, ctx.sequence, ctx.start, ctx.ignore, ctx.owner, ctx.scores = rows, s, rank * v, ignore, owner, scores
         owner.forward_calls += 1
-        return loss, dense
+        return means[rank].clone(), dense
 
     @staticmethod
-    def backward(ctx, up, _diagnostic_grad):
-        h, w, labels, logits, lse, counts = ctx.saved_tensors
+    def backward(ctx, up, _dense_grad):
+        all_hidden, w, lse, counts, *kept = ctx.saved_tensors
         owner = ctx.owner
-        world = owner.world
-        r = ctx.rows
-        k = h.shape[1]
-        ups = torch.empty(world, device=h.device, dtype=up.dtype)
+        ups = torch.empty(owner.world, device=up.device, dtype=up.dtype)
         _gather(owner, ups, up.contiguous().view(1))
-        dz = logit_gradient(logits, labels, lse, counts, ups, r, ctx.sequence, ctx.start, ctx.ignore,
-                            vocab_total=world * w.shape[0])
-        partial_dx = matmul(dz, w, optimized=True, output_dtype=torch.float32)
-        if world == 1:
-            local_dx = partial_dx
-        else:
-            local_dx = torch.empty((r, k), device=h.device, dtype=torch.float32)
-            if owner.communication is None:
-                dist.reduce_scatter_tensor(local_dx, partial_dx, op=dist.ReduceOp.SUM)
-            else:
-                owner.communication.reduce_scatter(local_dx, partial_dx, 'sum')
-        dx = cast_tensor(local_dx, torch.bfloat16)
-        if owner.fused_dw:
-            from ..kernels.vocab_dw import weight_gradient_mean
-            dw = weight_gradient_mean(dz, h, r, world, owner.dw_config)
-        else:
-            dw = torch.empty(w.shape, device=w.device, dtype=torch.float32)
-            for source in range(world):
-                partial_dw = matmul(dz[source * r:(source + 1) * r].t(), h[source * r:(source + 1) * r], optimized=True)
-                accumulate_weight_gradient(partial_dw, dw, world, source == 0)
+        partial_dx, dw = ctx.scores.gradients(owner, all_hidden, w, tuple(kept), lse, counts, ups, ctx.rows,
+                                              ctx.sequence, ctx.start, ctx.ignore)
+        dx = cast_tensor(_reduce_scatter_rows(owner, partial_dx, ctx.rows, torch.float32), torch.bfloat16)
         owner.backward_calls += 1
-        return dx.view(-1, ctx.sequence, k), dw, None, None, None, None
+        return dx.view(-1, ctx.sequence, all_hidden.shape[1]), dw, None, None, None, None, None
 
 
 class VocabParallelCE(torch.nn.Module):
@@ -202,9 +208,9 @@ class VocabParallelCE(torch.nn.Module):
     def forward(self, hidden, labels, *, ignore_index=-100, diagnostics=False):
         if hidden.ndim != 3 or hidden.shape[-1] != self.in_features:
             raise ValueError('Expected [B,S,H] hidden states')
-        if self.fused and not diagnostics and self.in_features % 8 == 0 and self.weight.shape[0] % 8 == 0:
-            return _FusedVocabCE.apply(hidden, self.weight, labels, ignore_index, self), None
-        return _VocabCE.apply(hidden, self.weight, labels, ignore_index, diagnostics, self)
+        streamed = self.fused and not diagnostics and self.in_features % 8 == 0 and self.weight.shape[0] % 8 == 0
+        scores = _StreamedScores() if streamed else _StoredScores()
+        return _VocabCE.apply(hidden, self.weight, labels, ignore_index, diagnostics, self, scores)
 
 
 class _VocabEmbedding(torch.autograd.Function):
@@ -226,14 +232,7 @@ class _VocabEmbedding(torch.autograd.Function):
         all_ids = torch.empty(world * n, device=ids.device, dtype=ids.dtype)
         _gather(owner, all_ids, ids.view(-1))
         partial = shard_lookup(all_ids, weight, rank * rows, world * rows, torch.bfloat16)
-        if world == 1:
-            out = partial
-        else:
-            out = torch.empty((n, h), device=ids.device, dtype=torch.bfloat16)
-            if owner.communication is None:
-                dist.reduce_scatter_tensor(out, partial, op=dist.ReduceOp.SUM)
-            else:
-                owner.communication.reduce_scatter(out, partial, 'sum')
+        out = _reduce_scatter_rows(owner, partial, n, torch.bfloat16)
         ctx.save_for_backward(all_ids)
         ctx.owner, ctx.rows = owner, rows
         owner.forward_calls += 1

@@ -56,7 +56,8 @@ def main(ref_root):
     out['attn_dq'], out['attn_dk'], out['attn_dv'] = aq, ak, av
     np.savez_compressed(HERE / 'ops.npz', **{k: v.detach().numpy() for k, v in out.items()})
 
-    # BASELINE config 1: the tiny decoder, one forward + CE + backward + AdamW step on CPU in fp32.
+    # The tiny decoder (2 layers, hidden 256, 4/2 heads of 64, vocab 2048): one forward + CE + backward + AdamW step on
+    # CPU in fp32.
     c = recipe.tiny_config()
     cfg = TinyQwenConfig(vocab_size=c.vocab_size, hidden_size=c.hidden_size, intermediate_size=c.intermediate_size,
                          num_hidden_layers=c.num_hidden_layers, num_attention_heads=c.num_attention_heads,
@@ -81,7 +82,59 @@ def main(ref_root):
     print('wrote', HERE / 'ops.npz', HERE / 'tiny_model.npz')
 
 
+DATA_CASES = [  # corpus tokens, seq, seed, offset
+    (51, 5, 42, 0), (1000, 7, 20261102, 0), (104729 * 3 + 5, 3, 1, 17), (209458 * 2, 2, 123456789, 5), (64, 8, 0, 3)]
+VALIDATION_CASES = [(1, 4, 4), (17, 4, 4), (32, 4, 4), (7, 2, 3), (9, 1, 2)]   # blocks, world, batch
+
+
+def data_fixtures(ref_root):
+    """training/data.py and training/evaluation.py of the reference, run on small synthetic corpora (token value =
+    position, so a block identifies itself): served block indices, strides, the validation partition and the shifted
+    NLL of seeded logits."""
+    import tempfile
+    sys.path.insert(0, ref_root)
+    from training.data import Blocks
+    from training.evaluation import shifted_nll, validation_batches
+    out = {}
+    with tempfile.TemporaryDirectory() as tmp:
+        for case, (tokens, seq, seed, offset) in enumerate(DATA_CASES):
+            path = Path(tmp) / f'c{case}.bin'
+            np.arange(tokens, dtype='<u4').tofile(path)
+            train = Blocks(path, seq, offset=offset, training=True, seed=seed)
+            plain = Blocks(path, seq)
+            count = min(len(train), 64)
+            out[f'data{case}/meta'] = np.array([tokens, seq, seed, offset, len(train), train.stride], dtype=np.int64)
+            out[f'data{case}/train_first_tokens'] = np.array([int(train[i][0]) for i in range(count)], dtype=np.int64)
+            out[f'data{case}/wrap_first_tokens'] = np.array([int(train[len(train) + i][0]) for i in range(4)], dtype=np.int64)
+            out[f'data{case}/eval_last_block'] = plain[len(plain) - 1].numpy()
+    gen = torch.Generator().manual_seed(7)
+    for case, (size, world, batch) in enumerate(VALIDATION_CASES):
+        ids = torch.randint(0, 11, (size, 6), generator=gen)
+        table = torch.randn(size, 6, 11, generator=gen)
+        masks, served, total, count = [], [], 0.0, 0
+        for rank in range(world):
+            for call, (data, valid) in enumerate(validation_batches(list(ids), rank, world, batch)):
+                start = call * world * batch + rank * batch
+                logits = torch.stack([table[i] if i < size else table[0] for i in range(start, start + batch)])
+                n, c = shifted_nll(logits, data, valid)
+                total += float(n)
+                count += int(c)
+                masks.append(valid.numpy())
+                served.append(data.numpy())
+        out[f'val{case}/meta'] = np.array([size, world, batch], dtype=np.int64)
+        out[f'val{case}/ids'] = ids.numpy()
+        out[f'val{case}/table'] = table.numpy()
+        out[f'val{case}/valid'] = np.stack(masks)
+        out[f'val{case}/served'] = np.stack(served)
+        out[f'val{case}/total_count'] = np.array([total, count], dtype=np.float64)
+    np.savez_compressed(HERE / 'data.npz', **out)
+    print('wrote', HERE / 'data.npz')
+
+
 if __name__ == '__main__':
-    if len(sys.argv) != 2:
-        raise SystemExit('usage: make_golden.py <path to a checkout of the reference repository>')
-    main(sys.argv[1])
+    args = [a for a in sys.argv[1:] if a != '--data-only']
+    if len(args) != 1:
+        raise SystemExit('usage: make_golden.py [--data-only] <path to a checkout of the reference repository>')
+    if '--data-only' not in sys.argv:
+        main(args[0])
+    data_fixtures(args[0])

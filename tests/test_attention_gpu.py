@@ -145,10 +145,10 @@ def _check_against_oracle(B, Hq, Hkv, S, dtype, expect_split):
     out.backward(do.cuda())
     assert _abi.read_status() == 0
     ref, dq, dk, dv = _oracle_by_group(q, k, v, do)
-    close(out, ref.to(dtype), what='out')
-    close(qg.grad, dq.to(dtype), what='dq', atol_mult=5.0, l2=L2_ATTENTION_GRAD[dtype])
-    close(kg.grad, dk.to(dtype), what='dk', atol_mult=5.0, l2=L2_ATTENTION_GRAD[dtype])
-    close(vg.grad, dv.to(dtype), what='dv', atol_mult=5.0, l2=L2_ATTENTION_GRAD[dtype])
+    close(out, ref.to(dtype), what='out', scale='row')
+    close(qg.grad, dq.to(dtype), what='dq', scale='row', atol_mult=5.0, l2=L2_ATTENTION_GRAD[dtype])
+    close(kg.grad, dk.to(dtype), what='dk', scale='row', atol_mult=5.0, l2=L2_ATTENTION_GRAD[dtype])
+    close(vg.grad, dv.to(dtype), what='dv', scale='row', atol_mult=5.0, l2=L2_ATTENTION_GRAD[dtype])
     return qg.grad, kg.grad, vg.grad
 
 

@@ -1,6 +1,10 @@
 """Two ranks on two GPUs (skipped on a single-GPU box): the vocabulary-parallel embedding against the full lookup
-and the averaged full gradient, and one training step of a small fused-layer model under FSDP2 with the embedding
-gathered by FSDP versus kept vocabulary-parallel (same loss, same embedding-gradient shard, same loss after AdamW)."""
+and the averaged full gradient; one training step of a small fused-layer model under FSDP2, with the embedding
+gathered by FSDP and kept vocabulary-parallel, against an UNSHARDED copy of the same model run on the concatenated
+batch of both ranks (loss of each rank's tokens, and the rank's shards of the embedding, lm_head and a decoder
+matrix gradient, which FSDP averages over ranks); and the two sharded forms against each other (same loss, same
+embedding-gradient shard, same loss after AdamW). What the reference checks with its CPU-gathered fp64 average
+(scripts/check_triton_fsdp_v14.py:22-100)."""
 import os
 import subprocess
 import sys
@@ -48,8 +52,23 @@ WORKER = textwrap.dedent('''
                                 intermediate_size=512, num_hidden_layers=4, num_attention_heads=2, num_key_value_heads=1,
                                 head_dim=128, max_position_embeddings=512, rms_norm_eps=1e-6, rope_theta=1e6,
                                 initializer_range=0.02, tie_word_embeddings=False, use_cache=False)
-    gen = torch.Generator().manual_seed(100 + rank)
-    ids = torch.randint(0, cfg.vocab_size, (2, 256), generator=gen).to(dev)
+    all_ids = [torch.randint(0, cfg.vocab_size, (2, 256), generator=torch.Generator().manual_seed(100 + r)) for r in range(world)]
+    ids = all_ids[rank].to(dev)
+    # unsharded yardstick: same seed -> same weights, bf16 compute, the global batch in one process
+    torch.manual_seed(1234)
+    with torch.device(dev):
+        whole = model_for_variant(cfg, "b200_fused")
+    whole = whole.to(torch.bfloat16)
+    whole.model.set_recompute("selective")
+    mine = float(whole(ids, labels=ids).loss)
+    whole(torch.cat(all_ids).to(dev), labels=torch.cat(all_ids).to(dev)).loss.backward()
+    yard = {n: p.grad.float().cpu() for n, p in whole.named_parameters()}
+    del whole
+
+    def shard_of(name, t):
+        rows = yard[name].shape[0] // world
+        return yard[name][rank * rows:(rank + 1) * rows], (t.to_local() if hasattr(t, "to_local") else t).float().cpu()
+
     results = []
     for vp in (False, True):
         torch.manual_seed(1234)
@@ -63,6 +82,14 @@ WORKER = textwrap.dedent('''
         opt = TritonAdamW([p for p in model.parameters()], lr=1e-3, betas=(0.9, 0.95), weight_decay=0.1)
         out = model(ids, labels=ids)
         out.loss.backward()
+        assert abs(float(out.loss) - mine) / mine < 1e-3, (float(out.loss), mine)
+        named = dict(model.named_parameters())
+        for name in ("model.embed_tokens.weight", "lm_head.weight", "model.layers.2.mlp.down_proj.weight",
+                     "model.layers.0.self_attn.k_proj.weight", "model.norm.weight"):
+            want, got = shard_of(name, named[name].grad)
+            rel = float((got - want).norm() / want.norm())
+            sys.stdout.write("rank%%d vp=%%s %%s rel_l2 %%.3e" %% (rank, vp, name, rel) + chr(10))
+            assert rel < 2e-2, (name, rel)
         w = model.model.embed_tokens.weight
         grad = w.grad.to_local() if hasattr(w.grad, "to_local") else w.grad
         opt.step()
