@@ -220,8 +220,8 @@ def cpu_operator_baselines(warmup=1, runs=3):
     inv = 1.0 / (1e6 ** (torch.arange(0, 128, 2).float() / 128))
     ang = pos[..., None].float() * inv
     cos, sin = torch.cat([ang.cos(), ang.cos()], -1), torch.cat([ang.sin(), ang.sin()], -1)
-    add("qk_norm_rope fwd", f"q [1,{T},32,128] k [1,{T},8,128]", lambda: O.qk_norm_rope(q, k, wq, wk, cos, sin),
-        "1/4 of 16384 tokens")
+    add("qk_norm_rope fwd", f"q [1,{T},32,128] k [1,{T},8,128]",
+        lambda: (O.norm_rope(q, wq, cos, sin), O.norm_rope(k, wk, cos, sin)), "1/4 of 16384 tokens")
     gate, up = r(T, 12288), r(T, 12288)
     add("swiglu fwd", f"[{T},12288] x2", lambda: O.swiglu(gate, up), "1/4 of 16384 tokens")
     aq, ak, av, ado = r(1, 4, 4096, 128), r(1, 1, 4096, 128), r(1, 1, 4096, 128), r(1, 4, 4096, 128)

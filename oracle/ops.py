@@ -124,9 +124,14 @@ def attention(q, k, v, scale=None):
     return torch.matmul(torch.softmax(s, dim=-1), v), lse
 
 
-def attention_backward(q, k, v, dout, scale=None):
+def attention_backward(q, k, v, dout, scale=None, saved_out=None):
     """ops/reference/attention.py:57-124: dV = P^T dO, dP = dO V^T, dS = P*(dP - sum(dP*P)),
-    dQ = scale*dS K, dK = scale*dS^T Q, expanded K/V grads summed back per kv head."""
+    dQ = scale*dS K, dK = scale*dS^T Q, expanded K/V grads summed back per kv head.
+
+    With `saved_out` (the forward output as it was stored, e.g. rounded to bf16) the row term sum(dP*P) is replaced
+    by rowsum(dO * saved_out): algebraically the same number, and the form every flash-attention backward uses
+    because P is not kept (the reference's kernels do: qwen3_triton/kernels/attention_precision.py:69-76,100 `delta`). The
+    rounding of the stored output then enters dS exactly as it does in the kernels."""
     q, k, v, dout = _f(q), _f(k), _f(v), _f(dout)
     b, hq, n, d = q.shape
     hk = k.shape[1]
@@ -138,7 +143,8 @@ def attention_backward(q, k, v, dout, scale=None):
     p = torch.softmax(s.masked_fill(~mask, float('-inf')), dim=-1)
     dv = torch.matmul(p.transpose(-2, -1), dout)
     dp = torch.matmul(dout, ve.transpose(-2, -1))
-    ds = p * (dp - (dp * p).sum(-1, keepdim=True))
+    row = (dp * p).sum(-1, keepdim=True) if saved_out is None else (dout * _f(saved_out)).sum(-1, keepdim=True)
+    ds = p * (dp - row)
     dq = torch.matmul(ds, ke) * scale
     dk = torch.matmul(ds.transpose(-2, -1), q) * scale
     dk = dk.view(b, hk, g, n, d).sum(2)

@@ -4,7 +4,7 @@ import pytest
 import torch
 
 import recipe
-from helpers import L2, L2_ATTENTION_GRAD, close, randn
+from helpers import L2, L2_ATTENTION_GRAD, close, randn, rel_l2
 from oracle import ops as O
 
 pytestmark = pytest.mark.gpu
@@ -103,21 +103,26 @@ def test_token_major_layout_matches_head_major(B, Hq, Hkv, S):
 # fixed-order reduction; the shapes the training step and the attention benchmark use (batch x kv heads x key tiles
 # >= 296) run one CTA per key tile that accumulates the whole query-head group in tensor memory. Both are compared
 # with the oracle here, on long sequences (16 - 64 key tiles), and the test asserts which schedule ran.
-def _oracle_by_group(q, k, v, do):
-    """Oracle forward/backward one (batch, kv head) at a time: same math, [1, G, S, S] fp32 scores at once."""
+def _oracle_by_group(q, k, v, do, saved_out=None):
+    """Oracle forward/backward one (batch, kv head) at a time: same math, [1, G, S, S] fp32 scores at once. Returns the
+    output, the exact gradients and, with `saved_out`, the gradients computed with the stored output in the row term."""
     B, Hq, S, D = q.shape
     Hkv = k.shape[1]
     G = Hq // Hkv
-    out, dq = torch.empty(B, Hq, S, D), torch.empty(B, Hq, S, D)
-    dk, dv = torch.empty(B, Hkv, S, D), torch.empty(B, Hkv, S, D)
+    out = torch.empty(B, Hq, S, D)
+    exact = [torch.empty(B, Hq, S, D), torch.empty(B, Hkv, S, D), torch.empty(B, Hkv, S, D)]
+    stored = [torch.empty_like(t) for t in exact]
     for b in range(B):
         for h in range(Hkv):
-            qs, ks, vs = q[b:b + 1, h * G:(h + 1) * G], k[b:b + 1, h:h + 1], v[b:b + 1, h:h + 1]
-            dos = do[b:b + 1, h * G:(h + 1) * G]
-            out[b, h * G:(h + 1) * G] = O.attention(qs, ks, vs)[0][0]
-            a, c, e = O.attention_backward(qs, ks, vs, dos)
-            dq[b, h * G:(h + 1) * G], dk[b, h], dv[b, h] = a[0], c[0, 0], e[0, 0]
-    return out, dq, dk, dv
+            heads = slice(h * G, (h + 1) * G)
+            qs, ks, vs, dos = q[b:b + 1, heads], k[b:b + 1, h:h + 1], v[b:b + 1, h:h + 1], do[b:b + 1, heads]
+            out[b, heads] = O.attention(qs, ks, vs)[0][0]
+            for grads, so in ((exact, None), (stored, saved_out)):
+                if grads is stored and saved_out is None:
+                    continue
+                a, c, e = O.attention_backward(qs, ks, vs, dos, saved_out=None if so is None else so[b:b + 1, heads])
+                grads[0][b, heads], grads[1][b, h], grads[2][b, h] = a[0], c[0, 0], e[0, 0]
+    return out, exact, stored
 
 
 class _GroupPolicy:
@@ -144,11 +149,15 @@ def _check_against_oracle(B, Hq, Hkv, S, dtype, expect_split):
     out = causal_attention(qg, kg, vg)
     out.backward(do.cuda())
     assert _abi.read_status() == 0
-    ref, dq, dk, dv = _oracle_by_group(q, k, v, do)
+    ref, exact, stored = _oracle_by_group(q, k, v, do, saved_out=out.detach().float().cpu())
     close(out, ref.to(dtype), what='out', scale='row')
-    close(qg.grad, dq.to(dtype), what='dq', scale='row', atol_mult=5.0, l2=L2_ATTENTION_GRAD[dtype])
-    close(kg.grad, dk.to(dtype), what='dk', scale='row', atol_mult=5.0, l2=L2_ATTENTION_GRAD[dtype])
-    close(vg.grad, dv.to(dtype), what='dv', scale='row', atol_mult=5.0, l2=L2_ATTENTION_GRAD[dtype])
+    for name, got, e, s in zip(('dq', 'dk', 'dv'), (qg.grad, kg.grad, vg.grad), exact, stored):
+        # against the exact math: per-tensor distance (the rounding of the stored output shifts the row term of dS by
+        # about 2^-9 |dO||O|, which is a visible fraction of the few rows whose gradient nearly cancels)
+        assert rel_l2(got, e) <= L2_ATTENTION_GRAD[dtype], (name, rel_l2(got, e))
+        # against the same math with the stored output in the row term, as flash-attention backward defines it:
+        # element by element, floor relative to each row
+        close(got, s.to(dtype), what=name, scale='row', atol_mult=5.0, l2=L2_ATTENTION_GRAD[dtype])
     return qg.grad, kg.grad, vg.grad
 
 
