@@ -404,6 +404,39 @@ int q3_validation_accumulate(const float* loss, double* totals, int64_t tokens, 
 int q3_validation_rows(const float* losses, const int64_t* labels, int64_t B, int64_t S, int64_t ignore_index,
                        double* totals, q3_stream_t stream);
 
+/* ---- decode-time kernels -------------------------------------------------------------------- */
+
+/* pos[b, s] = start + s (int64 [batch, seq]). Reference: qwen3_triton/inference/kernels.py:12-22 (positions). */
+int q3_inf_positions(int64_t* pos, int64_t batch, int64_t seq, int64_t start, q3_stream_t stream);
+
+/* Append the new keys / values k, v [B,S,H,D] (token-major) to the caches [B,H,C,D] at tokens start .. start+S-1.
+ * D * element size must be a multiple of 16 bytes. Reference: inference/kernels.py:25-36 (append). */
+int q3_kv_append(const void* k, const void* v, void* cache_k, void* cache_v, int64_t B, int64_t S, int64_t H, int64_t D,
+                 int64_t C, int64_t start, int dtype, q3_stream_t stream);
+
+/* Causal attention of S new query tokens q [B,S,Hq,D] over the cached keys / values [B,Hkv,C,D], which already hold
+ * tokens 0 .. start+S-1: query s sees keys t <= start + s. out [B,S,Hq,D]. D in {64,128,256}; Hq/Hkv in {1,2,4,8}.
+ * One pass over each 256-key chunk of the cache serves all query heads of a kv head; chunks are merged by their
+ * log-sum-exp (fp32 partials in the workspace). Reference: inference/kernels.py:39-115 (cached attention and the
+ * split decode path, which this replaces for every S). */
+int64_t q3_cache_attention_workspace_bytes(int64_t B, int64_t S, int64_t Hq, int64_t D, int64_t start);
+int q3_cache_attention(const void* q, const void* cache_k, const void* cache_v, void* out, void* workspace,
+                       int64_t workspace_bytes, int64_t B, int64_t S, int64_t Hq, int64_t Hkv, int64_t D, int64_t C,
+                       int64_t start, double scale, int dtype, q3_stream_t stream);
+
+/* y [M,N] = x [M,K] * weight[N,K]^T for M <= 8 (decode): the weight matrix is streamed once. fp32 accumulation, or
+ * fp64 with accurate != 0. K * element size must be a multiple of 16 bytes.
+ * Reference: inference/kernels.py:117-148 (_inference_gemv behind linear(gemv=True)). */
+int q3_gemv(const void* x, const void* weight, void* y, int64_t M, int64_t N, int64_t K, int dtype, int accurate,
+            q3_stream_t stream);
+
+/* Greedy decode step over logits [B,V]: token = argmax (lowest index among equal maxima), or `pad` for a row that is
+ * already done; ids[row, position] = next_token[row] = token; done[row] |= token in eos_ids (n_eos int64 on the
+ * device). done is one byte per row. Reference: inference/kernels.py:150-173 (argmax parts + select). */
+int q3_select_tokens(const void* logits, int64_t B, int64_t V, int64_t* ids, int64_t ids_stride, int64_t position,
+                     int64_t* next_token, uint8_t* done, const int64_t* eos_ids, int n_eos, int64_t pad, int dtype,
+                     q3_stream_t stream);
+
 /* ---- self-test ------------------------------------------------------------------------------ */
 
 /* Makes a bounded wait run out on purpose, the harmless way: one CTA waits on a barrier nothing arrives at, with a
