@@ -578,15 +578,20 @@ def run_fsdp(args):
         mean_loss = out.loss.detach().float().clone()
         dist.all_reduce(mean_loss, op=dist.ReduceOp.AVG)
         named = dict(model.named_parameters())
-        worst = torch.zeros(1, device=device)
-        for name in names:
+        rel = torch.zeros(len(names), device=device)
+        ratio = torch.zeros(len(names), device=device)
+        for i, name in enumerate(names):
             g = named[name].grad
             g = (g.to_local() if hasattr(g, "to_local") else g).float()
-            worst = torch.maximum(worst, ((g - yard[name]).norm() / yard[name].norm()).reshape(1))
-        dist.all_reduce(worst, op=dist.ReduceOp.MAX)
-        parity = {"loss": abs(float(mean_loss) - yard_loss) / abs(yard_loss), "grads": float(worst),
+            rel[i] = (g - yard[name]).norm() / yard[name].norm()
+            ratio[i] = g.norm() / yard[name].norm()
+        dist.all_reduce(rel, op=dist.ReduceOp.MAX)
+        dist.all_reduce(ratio, op=dist.ReduceOp.MAX)
+        parity = {"loss": abs(float(mean_loss) - yard_loss) / abs(yard_loss), "grads": float(rel.max()),
+                  "grads_by_tensor": {n: round(float(v), 5) for n, v in zip(names, rel)},
+                  "grad_norm_ratio_by_tensor": {n: round(float(v), 4) for n, v in zip(names, ratio)},
                   "what": "first step vs one unsharded bf16 model on the concatenated %d x 2048 batch: relative loss "
-                          "difference; worst relative L2 over ranks of the gradient shards of %s" % (world, ", ".join(names))}
+                          "difference; relative L2 (worst over ranks) of this rank's gradient shard of each tensor" % world}
         del yard, named
         opt.zero_grad(set_to_none=True)
 
@@ -650,7 +655,7 @@ def run_fsdp(args):
         others[policy] = other_ms
     status |= _abi.read_status()
     bad = torch.tensor([status], device=device)
-    dist.all_reduce(bad, op=dist.ReduceOp.BOR)
+    dist.all_reduce(bad, op=dist.ReduceOp.MAX)     # any non-zero word on any rank fails the run
     status = int(bad.item())
 
     if rank == 0:

@@ -1,5 +1,5 @@
 #!/usr/bin/env python
-"""Per-operator timing against the B200 rooflines (BASELINE configs 2 and 3).
+"""Per-operator timing against the B200 rooflines (the 16384-token operator sweep and the attention shapes).
 
     python qwen3-triton_b200/benchmarks/op_bench.py [--ops a,b,...] [--scale 1.0] [--iters 10] [--json out.json]
 
@@ -116,18 +116,23 @@ def main():
         wd, dwd = torch.ones(D, device=dev, dtype=bf), torch.empty(D, device=dev, dtype=bf)
         ws2 = _abi.workspace(lib.q3_norm_rope_bwd_workspace_bytes(T, HQ, D), dev)
 
-        def fwd():
-            _abi.call("q3_norm_rope_fwd", q.data_ptr(), wd.data_ptr(), cos.data_ptr(), sin.data_ptr(), qo.data_ptr(), qi.data_ptr(), T, HQ, D, 1e-6, 1, st())
-            _abi.call("q3_norm_rope_fwd", k.data_ptr(), wd.data_ptr(), cos.data_ptr(), sin.data_ptr(), ko.data_ptr(), ki.data_ptr(), T, HK, D, 1e-6, 1, st())
+        dwq, dwk = torch.empty(D, device=dev, dtype=bf), torch.empty(D, device=dev, dtype=bf)
+        dq, dk = torch.empty_like(q), torch.empty_like(k)
+        ws3 = _abi.workspace(lib.q3_qk_norm_rope_bwd_workspace_bytes(T, HQ, HK, D), dev)
+
+        def fwd():     # q and k in one launch, as the decoder layer calls it
+            _abi.call("q3_qk_norm_rope_fwd", q.data_ptr(), k.data_ptr(), wd.data_ptr(), wd.data_ptr(), cos.data_ptr(), sin.data_ptr(),
+                      qo.data_ptr(), ko.data_ptr(), qi.data_ptr(), ki.data_ptr(), T, HQ, HK, D, 1e-6, 1, st())
 
         def bwd():
-            _abi.call("q3_norm_rope_bwd", q.data_ptr(), wd.data_ptr(), cos.data_ptr(), sin.data_ptr(), qo.data_ptr(), qi.data_ptr(), qo.data_ptr(), dwd.data_ptr(), ws2.data_ptr(), ws2.numel(), T, HQ, D, 1, st())
-            _abi.call("q3_norm_rope_bwd", k.data_ptr(), wd.data_ptr(), cos.data_ptr(), sin.data_ptr(), ko.data_ptr(), ki.data_ptr(), ko.data_ptr(), dwd.data_ptr(), ws2.data_ptr(), ws2.numel(), T, HK, D, 1, st())
+            _abi.call("q3_qk_norm_rope_bwd", q.data_ptr(), k.data_ptr(), wd.data_ptr(), wd.data_ptr(), cos.data_ptr(), sin.data_ptr(),
+                      qo.data_ptr(), ko.data_ptr(), qi.data_ptr(), ki.data_ptr(), dq.data_ptr(), dk.data_ptr(), dwq.data_ptr(),
+                      dwk.data_ptr(), ws3.data_ptr(), ws3.numel(), T, HQ, HK, D, 1, st())
         if want("norm_rope_fwd"):
             report("norm_rope_fwd (q+k)", timer(fwd), bytes_=2 * T * (HQ + HK) * D * 2 + 2 * T * D * 2)
         if want("norm_rope_bwd"):
             report("norm_rope_bwd (q+k)", timer(bwd), bytes_=3 * T * (HQ + HK) * D * 2 + 2 * T * D * 2)
-        del q, k, qo, ko
+        del q, k, qo, ko, dq, dk
     if want("swiglu_fwd") or want("swiglu_bwd"):
         g, u = torch.randn(T, I, device=dev).to(bf), torch.randn(T, I, device=dev).to(bf)
         o1, o2 = torch.empty_like(g), torch.empty_like(g)
@@ -242,6 +247,24 @@ def main():
             report(name + "_fwd", timer(lambda: attention_forward(q, k, v, D ** -0.5)), flops=fl)
             report(name + "_bwd", timer(lambda: attention_backward(q, k, v, out, do, lse, D ** -0.5)), flops=2.5 * fl)
             del q, k, v, do, out
+    if want("decode"):
+        # decode-time operators at batch 8, 8192 cached tokens: all bound by the bytes they must read once
+        from qwen3_triton.inference import kernels as IK
+        Bd, Td = 8, 8192
+        ck, cv = torch.randn(Bd, HK, Td, D, device=dev).to(bf), torch.randn(Bd, HK, Td, D, device=dev).to(bf)
+        qd = torch.randn(Bd, 1, HQ, D, device=dev).to(bf)
+        report("decode attention (B8, 8192 keys)", timer(lambda: IK.attention(qd, ck, cv, Td - 1)), bytes_=2 * Bd * HK * Td * D * 2)
+        kn, vn = torch.randn(Bd, 1, HK, D, device=dev).to(bf), torch.randn(Bd, 1, HK, D, device=dev).to(bf)
+        report("decode cache append", timer(lambda: IK.append(kn, vn, ck, cv, Td - 1)), bytes_=4 * Bd * HK * D * 2)
+        xw, wg_ = torch.randn(Bd, H, device=dev).to(bf), (torch.randn(I, H, device=dev) * 0.02).to(bf)
+        report("decode gemv 8 x 12288 x 4096", timer(lambda: IK.linear(xw, wg_)), bytes_=I * H * 2)
+        wv_ = (torch.randn(V, H, device=dev) * 0.02).to(bf)
+        report("decode gemv 8 x 151936 x 4096", timer(lambda: IK.linear(xw, wv_)), bytes_=V * H * 2)
+        lg = torch.randn(Bd, V, device=dev).to(bf)
+        ids_ = torch.zeros(Bd, 4, dtype=torch.int64, device=dev)
+        nx, dn = torch.zeros(Bd, 1, dtype=torch.int64, device=dev), torch.zeros(Bd, dtype=torch.bool, device=dev)
+        report("decode select (8 x 151936)", timer(lambda: IK.select(lg, ids_, nx, dn, 1, (151645,), 0)), bytes_=Bd * V * 2)
+        del ck, cv, wg_, wv_, lg
     assert _abi.read_status() == 0
     if a.json:
         Path(a.json).write_text(json.dumps({"peaks": {"hbm_gbs": hbm, "bf16_tflops": tf, "kind": kind}, "T": T, "results": results}, indent=1))

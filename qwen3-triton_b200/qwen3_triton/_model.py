@@ -166,21 +166,33 @@ def position_ids_for(ids):
 
 
 class RotaryTables(nn.Module):
-    """inv_freq = theta^(-2i/D), built on the CPU whatever the default device is (a meta-device build keeps real
-    values), turned into cos/sin tables of the activation dtype per call."""
+    """inv_freq = theta^(-2i/D) in fp32, turned into cos/sin tables of the activation dtype per call.
+
+    The frequencies are deliberately NOT a registered buffer: `model.to(torch.bfloat16)` would round them to 8 bits
+    of mantissa, and a rotation angle is position * frequency - at position 2048 that rounding is an error of
+    several radians in the fast components. (The reference keeps them as a buffer and casts back to fp32 at use,
+    qwen3_triton/_model.py:49-59 there, which restores the dtype but not the lost bits.) They are built on the CPU
+    whatever the default device is, so a meta-device build keeps real values, and copied once per device."""
 
     def __init__(self, c):
         super().__init__()
         exponent = torch.arange(0, c.head_dim, 2, device='cpu', dtype=torch.float32) / c.head_dim
-        self.register_buffer('inv_freq', 1.0 / (c.rope_theta ** exponent), persistent=False)
+        self._inv_freq = 1.0 / (c.rope_theta ** exponent)
+        self._per_device = {}
+
+    @property
+    def inv_freq(self):
+        return self._inv_freq
+
+    def frequencies(self, device):
+        key = (device.type, device.index)
+        if key not in self._per_device:
+            self._per_device[key] = self._inv_freq.to(device)
+        return self._per_device[key]
 
     def forward(self, positions, dtype):
-        from .kernels.attention import cast_tensor
         from .kernels.rotary import rotary_tables
-        freq = self.inv_freq
-        if freq.dtype != torch.float32:     # a blanket .to(bf16) on the model must not degrade the angles
-            freq = cast_tensor(freq, torch.float32)
-        return rotary_tables(positions, freq, dtype)
+        return rotary_tables(positions, self.frequencies(positions.device), dtype)
 
 
 # ------------------------------------------------------------------------------------------------ graph

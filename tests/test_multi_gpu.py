@@ -58,7 +58,7 @@ WORKER = textwrap.dedent('''
     torch.manual_seed(1234)
     with torch.device(dev):
         whole = model_for_variant(cfg, "b200_fused")
-    whole = whole.to(torch.bfloat16)
+    whole = whole.to(dev, torch.bfloat16)     # also moves the rotary frequencies, which are built on the CPU
     whole.model.set_recompute("selective")
     mine = float(whole(ids, labels=ids).loss)
     whole(torch.cat(all_ids).to(dev), labels=torch.cat(all_ids).to(dev)).loss.backward()
