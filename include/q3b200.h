@@ -416,10 +416,10 @@ int q3_kv_append(const void* k, const void* v, void* cache_k, void* cache_v, int
 
 /* Causal attention of S new query tokens q [B,S,Hq,D] over the cached keys / values [B,Hkv,C,D], which already hold
  * tokens 0 .. start+S-1: query s sees keys t <= start + s. out [B,S,Hq,D]. D in {64,128,256}; Hq/Hkv in {1,2,4,8}.
- * One pass over each 256-key chunk of the cache serves all query heads of a kv head; chunks are merged by their
- * log-sum-exp (fp32 partials in the workspace). Reference: inference/kernels.py:39-115 (cached attention and the
+ * One pass over each chunk of the cache (32 KB of keys: 128 at head_dim 128 in bf16) serves all query heads of a kv
+ * head; chunks are merged by their log-sum-exp (fp32 partials in the workspace). Reference: inference/kernels.py:39-115 (cached attention and the
  * split decode path, which this replaces for every S). */
-int64_t q3_cache_attention_workspace_bytes(int64_t B, int64_t S, int64_t Hq, int64_t D, int64_t start);
+int64_t q3_cache_attention_workspace_bytes(int64_t B, int64_t S, int64_t Hq, int64_t D, int64_t start, int dtype);
 int q3_cache_attention(const void* q, const void* cache_k, const void* cache_v, void* out, void* workspace,
                        int64_t workspace_bytes, int64_t B, int64_t S, int64_t Hq, int64_t Hkv, int64_t D, int64_t C,
                        int64_t start, double scale, int dtype, q3_stream_t stream);
@@ -432,10 +432,12 @@ int q3_gemv(const void* x, const void* weight, void* y, int64_t M, int64_t N, in
 
 /* Greedy decode step over logits [B,V]: token = argmax (lowest index among equal maxima), or `pad` for a row that is
  * already done; ids[row, position] = next_token[row] = token; done[row] |= token in eos_ids (n_eos int64 on the
- * device). done is one byte per row. Reference: inference/kernels.py:150-173 (argmax parts + select). */
+ * device). done is one byte per row; the workspace (8-byte aligned) holds the per-slice maxima of the first stage.
+ * Reference: inference/kernels.py:150-173 (argmax parts + select). */
+int64_t q3_select_tokens_workspace_bytes(int64_t B, int64_t V);
 int q3_select_tokens(const void* logits, int64_t B, int64_t V, int64_t* ids, int64_t ids_stride, int64_t position,
-                     int64_t* next_token, uint8_t* done, const int64_t* eos_ids, int n_eos, int64_t pad, int dtype,
-                     q3_stream_t stream);
+                     int64_t* next_token, uint8_t* done, const int64_t* eos_ids, int n_eos, int64_t pad, void* workspace,
+                     int64_t workspace_bytes, int dtype, q3_stream_t stream);
 
 /* ---- self-test ------------------------------------------------------------------------------ */
 

@@ -1,10 +1,11 @@
 // Decode-time kernels: positions, KV-cache append, attention over the cache, small-M linear (GEMV) and greedy token
 // selection. All of them are bound by HBM traffic (the cache, the weight matrix, the logits), so the work is laid out
-// to read each byte once with 16-byte accesses:
-//   * attention over the cache runs one CTA per (batch, kv head, chunk of 256 keys) and serves ALL query heads of the
+// to read each byte once, with 16-byte accesses and enough of them in flight:
+//   * attention over the cache runs one CTA per (batch, kv head, chunk of keys) and serves ALL query heads of the
 //     group from one pass over that K/V chunk (grouped-query attention: 4 query heads share a kv head in Qwen3, so
-//     the cache is read once instead of four times), then a small merge kernel combines the chunks;
-//   * the GEMV gives every warp one weight row and streams it once for up to 8 input rows;
+//     the cache is read once instead of four times); the chunk is staged in shared memory with asynchronous copies,
+//     and a small merge kernel combines the chunks by their log-sum-exp;
+//   * the GEMV gives every warp a few weight rows and streams them once for up to 8 input rows;
 //   * the argmax reads the logits once, ties resolved to the lowest index.
 //
 // Replaces, in the reference: qwen3_triton/inference/kernels.py:12-22 (positions), :25-36 (append), :39-115
@@ -36,32 +37,55 @@ __global__ void kv_append_kernel(const T* __restrict__ k, const T* __restrict__ 
   }
 }
 
-constexpr int kChunk = 256;        // keys per CTA
 constexpr int kAttnThreads = 256;  // 8 warps; a warp covers two keys per step (16 lanes per key row)
-constexpr int kMaxGroup = 8;       // query heads per kv head served by one CTA
+constexpr int kTileBytes = 32768;  // one K (or V) chunk in shared memory
+// keys per CTA: as many rows of D elements as fit 32 KB (128 keys at head_dim 128 in bf16)
+__host__ __device__ constexpr int chunk_keys(int D, int elem_bytes) { return kTileBytes / (D * elem_bytes); }
+
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(smem)), "l"(gmem)
+               : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() {
+  asm volatile("cp.async.commit_group;\n\tcp.async.wait_group 0;" ::: "memory");
+}
 
 // Partial attention of one query token against one chunk of cached keys, for the G query heads of a kv head.
 //   q      [B, S, Hq, D]       cache_k / cache_v [B, Hkv, C, D]
 //   part   [B, S, Hq, splits, D] fp32 (normalised within the chunk)   lse [B, S, Hq, splits] fp32 (natural log)
-// Key t is visible to query token s iff t <= start + s and t < T = start + S. EPL = D / 16 elements per lane.
+// Key t is visible to query token s iff t <= start + s. EPL = D / 16 elements per lane.
+// The CTA first brings the live part of its K and V chunk into shared memory with 16-byte asynchronous copies (up to
+// 64 KB in flight per CTA, two CTAs per SM: enough outstanding bytes to keep HBM busy), then its warps walk the keys
+// from there.
 template <typename T, int EPL, int G>
-__global__ void __launch_bounds__(kAttnThreads)
+__global__ void __launch_bounds__(kAttnThreads, 2)
 cache_attention_partial_kernel(const T* __restrict__ q, const T* __restrict__ ck, const T* __restrict__ cv,
                                float* __restrict__ part, float* __restrict__ lse, int64_t S, int64_t Hq, int64_t Hkv,
                                int64_t C, int64_t start, int splits, float scale) {
   constexpr int D = EPL * 16;
+  constexpr int CHUNK = chunk_keys(D, (int)sizeof(T));
+  extern __shared__ __align__(16) uint8_t smem[];
+  const T* ks = reinterpret_cast<const T*>(smem);
+  const T* vs = reinterpret_cast<const T*>(smem + kTileBytes);
   const int split = blockIdx.x, s = blockIdx.y;
   const int64_t bk = blockIdx.z, b = bk / Hkv, kvh = bk % Hkv;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, sub = lane & 15, half = lane >> 4;
   const int64_t visible = start + s + 1;                      // keys 0 .. visible-1
-  const int64_t first = (int64_t)split * kChunk;
-  int64_t last = first + kChunk;
+  const int64_t first = (int64_t)split * CHUNK;
+  int64_t last = first + CHUNK;
   if (last > visible) last = visible;
+  const int live_keys = last > first ? (int)(last - first) : 0;
 
-  __shared__ float s_max[8][G], s_sum[8][G];
-  __shared__ float s_acc[8][G][D];
-
-  // this lane's slice of the G query vectors, pre-scaled
+  {   // the live part of the chunk is one contiguous range of the cache
+    const uint8_t* kg = reinterpret_cast<const uint8_t*>(ck + (bk * C + first) * D);
+    const uint8_t* vg = reinterpret_cast<const uint8_t*>(cv + (bk * C + first) * D);
+    const int nbytes = live_keys * D * (int)sizeof(T);
+    for (int off = threadIdx.x * 16; off < nbytes; off += kAttnThreads * 16) {
+      cp_async16(smem + off, kg + off);
+      cp_async16(smem + kTileBytes + off, vg + off);
+    }
+  }
+  // this lane's slice of the G query vectors, pre-scaled (overlaps the copies)
   float qv[G][EPL];
 #pragma unroll
   for (int g = 0; g < G; ++g) {
@@ -76,22 +100,22 @@ cache_attention_partial_kernel(const T* __restrict__ q, const T* __restrict__ ck
 #pragma unroll
     for (int e = 0; e < EPL; ++e) acc[g][e] = 0.f;
   }
-  const T* kbase = ck + (bk * C) * D;
-  const T* vbase = cv + (bk * C) * D;
-  // warp w takes keys first + 2*w + half, stepping by 16 (8 warps x 2 keys)
-  for (int64_t t0 = first + 2 * warp; t0 < last; t0 += 16) {
-    const int64_t t = t0 + half;
-    const bool live = t < last;
+  cp_async_wait_all();
+  __syncthreads();
+  // warp w takes keys 2*w + half, stepping by 16 (8 warps x 2 keys)
+  for (int t0 = 2 * warp; t0 < live_keys; t0 += 16) {
+    const int t = t0 + half;
+    const bool live = t < live_keys;
     float kk[EPL], vv[EPL];
     if (live) {
       constexpr int W = (16 / (int)sizeof(T)) < EPL ? (16 / (int)sizeof(T)) : EPL;   // 8- or 16-byte accesses
 #pragma unroll
       for (int c = 0; c < EPL / W; ++c) {
         float tmp[W];
-        VecIO<T, W>::load(kbase + t * D + sub * EPL + c * W, tmp);
+        VecIO<T, W>::load(ks + t * D + sub * EPL + c * W, tmp);
 #pragma unroll
         for (int e = 0; e < W; ++e) kk[c * W + e] = tmp[e];
-        VecIO<T, W>::load(vbase + t * D + sub * EPL + c * W, tmp);
+        VecIO<T, W>::load(vs + t * D + sub * EPL + c * W, tmp);
 #pragma unroll
         for (int e = 0; e < W; ++e) vv[c * W + e] = tmp[e];
       }
@@ -117,6 +141,10 @@ cache_attention_partial_kernel(const T* __restrict__ q, const T* __restrict__ ck
       }
     }
   }
+  __syncthreads();                                             // every warp is done with the tiles: reuse them
+  float* s_acc = reinterpret_cast<float*>(smem);               // [8 warps][G][D], at most 32 KB
+  float* s_max = reinterpret_cast<float*>(smem + kTileBytes);  // [8][G]
+  float* s_sum = s_max + 8 * G;
   // fold the two half-warps (different keys, same columns), then the 8 warps through shared memory
 #pragma unroll
   for (int g = 0; g < G; ++g) {
@@ -130,10 +158,10 @@ cache_attention_partial_kernel(const T* __restrict__ q, const T* __restrict__ ck
       acc[g][e] = acc[g][e] * a + oa * bsc;
     }
     m[g] = nm;
-    if (lane == 0) { s_max[warp][g] = m[g]; s_sum[warp][g] = l[g]; }
+    if (lane == 0) { s_max[warp * G + g] = m[g]; s_sum[warp * G + g] = l[g]; }
     if (half == 0) {
 #pragma unroll
-      for (int e = 0; e < EPL; ++e) s_acc[warp][g][sub * EPL + e] = acc[g][e];
+      for (int e = 0; e < EPL; ++e) s_acc[(warp * G + g) * D + sub * EPL + e] = acc[g][e];
     }
   }
   __syncthreads();
@@ -142,14 +170,14 @@ cache_attention_partial_kernel(const T* __restrict__ q, const T* __restrict__ ck
     const int g = idx / D, d = idx % D;
     float nm = -CUDART_INF_F;
 #pragma unroll
-    for (int w = 0; w < 8; ++w) nm = fmaxf(nm, s_max[w][g]);
+    for (int w = 0; w < 8; ++w) nm = fmaxf(nm, s_max[w * G + g]);
     float tot = 0.f, val = 0.f;
     if (nm > -CUDART_INF_F) {
 #pragma unroll
       for (int w = 0; w < 8; ++w) {
-        const float f = __expf(s_max[w][g] - nm);
-        tot += s_sum[w][g] * f;
-        val += s_acc[w][g][d] * f;
+        const float f = __expf(s_max[w * G + g] - nm);
+        tot += s_sum[w * G + g] * f;
+        val += s_acc[(w * G + g) * D + d] * f;
       }
     }
     const int64_t row = ((b * S + s) * Hq + kvh * G + g) * splits + split;
@@ -158,92 +186,169 @@ cache_attention_partial_kernel(const T* __restrict__ q, const T* __restrict__ ck
   }
 }
 
-// out[row, :] = sum_i part[row, i, :] * exp(lse[row, i] - max) / sum_i exp(lse[row, i] - max); one warp per row.
-template <typename T>
-__global__ void cache_attention_merge_kernel(const float* __restrict__ part, const float* __restrict__ lse,
-                                             T* __restrict__ out, int64_t rows, int splits, int D) {
+// out[row, :] = sum_i part[row, i, :] * w_i, w_i = exp(lse[row, i] - max) / sum_j exp(lse[row, j] - max); one warp per
+// row. The lanes first share out the chunks to find the maximum and the weights (kept in registers, 32 chunks per
+// round), then every lane owns CPL = D / 32 consecutive columns and adds the chunks up in order - independent,
+// unrolled vector loads rather than one dependent load after another.
+template <typename T, int CPL>
+__global__ void __launch_bounds__(128)
+cache_attention_merge_kernel(const float* __restrict__ part, const float* __restrict__ lse, T* __restrict__ out,
+                             int64_t rows, int splits) {
+  constexpr int D = CPL * 32;
   const int64_t row = blockIdx.x * (int64_t)(blockDim.x >> 5) + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
   if (row >= rows) return;
+  const float* l = lse + row * splits;
   float mx = -CUDART_INF_F;
-  for (int i = 0; i < splits; ++i) mx = fmaxf(mx, lse[row * splits + i]);
+  for (int i = lane; i < splits; i += 32) mx = fmaxf(mx, l[i]);
+  mx = warp_max(mx);
   float denom = 0.f;
-  for (int i = 0; i < splits; ++i) denom += __expf(lse[row * splits + i] - mx);   // same order in every lane
-  for (int d = lane; d < D; d += 32) {
-    float val = 0.f;
-    for (int i = 0; i < splits; ++i) val += part[(row * splits + i) * D + d] * __expf(lse[row * splits + i] - mx);
-    out[row * D + d] = from_f32<T>(val / denom);
-  }
-}
-
-// y[m, n] = sum_k x[m, k] * w[n, k], M <= 8: a warp owns one n and streams its weight row once, 16 bytes per lane and
-// step, against all M input rows (those stay in L1/L2). ACC = float, or double for the `accurate` mode.
-template <typename T, typename ACC, int M>
-__global__ void __launch_bounds__(256)
-gemv_kernel(const T* __restrict__ x, const T* __restrict__ w, T* __restrict__ y, int64_t N, int64_t K) {
-  constexpr int W = 16 / (int)sizeof(T);
-  const int64_t n = blockIdx.x * (int64_t)(blockDim.x >> 5) + (threadIdx.x >> 5);
-  const int lane = threadIdx.x & 31;
-  if (n >= N) return;
-  ACC acc[M];
+  for (int i = lane; i < splits; i += 32) denom += __expf(l[i] - mx);
+  denom = warp_sum(denom);                       // xor-butterfly: the same value, bit for bit, in every lane
+  const float inv = 1.f / denom;
+  float acc[CPL];
 #pragma unroll
-  for (int m = 0; m < M; ++m) acc[m] = (ACC)0;
-  const T* wr = w + n * K;
-  const int64_t kvec = K / W * W;
-  for (int64_t k = (int64_t)lane * W; k < kvec; k += 32 * W) {
-    float wv[W];
-    VecIO<T, W>::load(wr + k, wv);
+  for (int c = 0; c < CPL; ++c) acc[c] = 0.f;
+  const float* p = part + row * splits * D + lane * CPL;
+  for (int base = 0; base < splits; base += 32) {
+    const float mine = base + lane < splits ? __expf(l[base + lane] - mx) * inv : 0.f;
+    const int n = splits - base < 32 ? splits - base : 32;
+#pragma unroll 8
+    for (int i = 0; i < n; ++i) {
+      const float w = __shfl_sync(0xffffffffu, mine, i);
+      float v[CPL];
+      if constexpr (CPL >= 4) {
 #pragma unroll
-    for (int m = 0; m < M; ++m) {
-      float xv[W];
-      VecIO<T, W>::load(x + m * K + k, xv);
+        for (int c = 0; c < CPL; c += 4) {
+          const float4 t = *reinterpret_cast<const float4*>(p + (int64_t)(base + i) * D + c);
+          v[c] = t.x; v[c + 1] = t.y; v[c + 2] = t.z; v[c + 3] = t.w;
+        }
+      } else {
+        const float2 t = *reinterpret_cast<const float2*>(p + (int64_t)(base + i) * D);
+        v[0] = t.x; v[1] = t.y;
+      }
 #pragma unroll
-      for (int e = 0; e < W; ++e) acc[m] += (ACC)(wv[e] * xv[e]);
+      for (int c = 0; c < CPL; ++c) acc[c] = fmaf(v[c], w, acc[c]);
     }
   }
-  for (int64_t k = kvec + lane; k < K; k += 32) {
-    const float wv = to_f32<T>(wr[k]);
+  T* o = out + row * D + lane * CPL;
 #pragma unroll
-    for (int m = 0; m < M; ++m) acc[m] += (ACC)(wv * to_f32<T>(x[m * K + k]));
-  }
-#pragma unroll
-  for (int m = 0; m < M; ++m) {
-    ACC v = acc[m];
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-    if (lane == 0) y[m * N + n] = from_f32<T>((float)v);
-  }
+  for (int c = 0; c < CPL; ++c) o[c] = from_f32<T>(acc[c]);
 }
 
-// Row-wise argmax (lowest index among equal maxima), then the decode bookkeeping of one step: a finished row emits
-// `pad`; the token goes to ids[row, position] and next[row]; a row that emits an end-of-sequence id becomes finished.
+// 16 bytes of T as floats through a streaming load: weight rows are read exactly once and must not evict the
+// input rows from L1.
+template <typename T> __device__ __forceinline__ void load_stream16(const T* p, float (&v)[16 / sizeof(T)]);
+template <> __device__ __forceinline__ void load_stream16<float>(const float* p, float (&v)[4]) {
+  const float4 t = __ldcs(reinterpret_cast<const float4*>(p));
+  v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+}
+template <> __device__ __forceinline__ void load_stream16<__nv_bfloat16>(const __nv_bfloat16* p, float (&v)[8]) {
+  const uint4 t = __ldcs(reinterpret_cast<const uint4*>(p));
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&t);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) { const float2 f = __bfloat1622float2(h[i]); v[2 * i] = f.x; v[2 * i + 1] = f.y; }
+}
+template <> __device__ __forceinline__ void load_stream16<__half>(const __half* p, float (&v)[8]) {
+  const uint4 t = __ldcs(reinterpret_cast<const uint4*>(p));
+  const __half2* h = reinterpret_cast<const __half2*>(&t);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) { const float2 f = __half22float2(h[i]); v[2 * i] = f.x; v[2 * i + 1] = f.y; }
+}
+
+// y[m, n] = sum_k x[m, k] * w[n, k], M <= 8. A warp owns R consecutive weight rows and walks K in chunks of 32
+// 16-byte vectors. Per chunk it issues, before any arithmetic, R streaming loads of weights (R independent 512-byte
+// requests in flight per warp; the matrix is read exactly once and bypasses L1) and the M loads of its slice of the
+// input rows (which stay in L1). ACC = float, or double for the `accurate` mode (products in fp32, as the
+// reference accumulates them).
+template <typename T, typename ACC, int M, int R>
+__global__ void __launch_bounds__(128)
+gemv_kernel(const T* __restrict__ x, const T* __restrict__ w, T* __restrict__ y, int64_t N, int64_t K) {
+  constexpr int W = 16 / (int)sizeof(T);
+  const int lane = threadIdx.x & 31;
+  const int64_t n0 = (blockIdx.x * (int64_t)(blockDim.x >> 5) + (threadIdx.x >> 5)) * R;
+  if (n0 >= N) return;
+  ACC acc[R][M];
+#pragma unroll
+  for (int r = 0; r < R; ++r)
+#pragma unroll
+    for (int m = 0; m < M; ++m) acc[r][m] = (ACC)0;
+  for (int64_t k = (int64_t)lane * W; k < K; k += 32 * W) {       // K is a multiple of W: a vector is all in or all out
+    float wv[R][W], xv[M][W];
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      if (n0 + r < N) load_stream16<T>(w + (n0 + r) * K + k, wv[r]);
+      else {
+#pragma unroll
+        for (int e = 0; e < W; ++e) wv[r][e] = 0.f;
+      }
+    }
+#pragma unroll
+    for (int m = 0; m < M; ++m) VecIO<T, W>::load(x + m * K + k, xv[m]);
+#pragma unroll
+    for (int m = 0; m < M; ++m)
+#pragma unroll
+      for (int r = 0; r < R; ++r)
+#pragma unroll
+        for (int e = 0; e < W; ++e) acc[r][m] += (ACC)(wv[r][e] * xv[m][e]);
+  }
+#pragma unroll
+  for (int r = 0; r < R; ++r)
+#pragma unroll
+    for (int m = 0; m < M; ++m) {
+      ACC v = acc[r][m];
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+      if (lane == 0 && n0 + r < N) y[m * N + n0 + r] = from_f32<T>((float)v);
+    }
+}
+
+// Greedy selection in two stages. Stage 1: every row is cut into `parts` slices, one CTA each, which reduce their
+// slice to (maximum, lowest index holding it). Stage 2: one warp per row reduces the slices the same way and does
+// the bookkeeping of a decode step: a finished row emits `pad`; the token goes to ids[row, position] and next[row];
+// a row that emits an end-of-sequence id becomes finished.
+__device__ __forceinline__ void better(float& best, int64_t& where, float v, int64_t i) {
+  if (v > best || (v == best && i < where)) { best = v; where = i; }
+}
+
 template <typename T>
-__global__ void __launch_bounds__(1024)
-select_kernel(const T* __restrict__ logits, int64_t V, int64_t* __restrict__ ids, int64_t ids_stride, int64_t position,
-              int64_t* __restrict__ next, uint8_t* __restrict__ done, const int64_t* __restrict__ eos, int n_eos,
-              int64_t pad) {
-  __shared__ float s_val[32];
-  __shared__ int64_t s_idx[32];
-  const int64_t row = blockIdx.x;
+__global__ void __launch_bounds__(256)
+argmax_parts_kernel(const T* __restrict__ logits, int64_t V, int parts, float* __restrict__ pval, int64_t* __restrict__ pidx) {
+  __shared__ float s_val[8];
+  __shared__ int64_t s_idx[8];
+  const int64_t row = blockIdx.y;
+  const int part = blockIdx.x;
+  const int64_t per = (V + parts - 1) / parts, lo = part * per, hi = lo + per < V ? lo + per : V;
   const T* x = logits + row * V;
   float best = -CUDART_INF_F;
   int64_t where = INT64_MAX;
-  for (int64_t i = threadIdx.x; i < V; i += blockDim.x) {
-    const float v = to_f32<T>(x[i]);
-    if (v > best || (v == best && i < where)) { best = v; where = i; }
-  }
+  for (int64_t i = lo + threadIdx.x; i < hi; i += blockDim.x) better(best, where, to_f32<T>(x[i]), i);
 #pragma unroll
-  for (int o = 16; o > 0; o >>= 1) {
-    const float ov = __shfl_xor_sync(0xffffffffu, best, o);
-    const int64_t oi = __shfl_xor_sync(0xffffffffu, where, o);
-    if (ov > best || (ov == best && oi < where)) { best = ov; where = oi; }
-  }
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  if (lane == 0) { s_val[warp] = best; s_idx[warp] = where; }
+  for (int o = 16; o > 0; o >>= 1)
+    better(best, where, __shfl_xor_sync(0xffffffffu, best, o), __shfl_xor_sync(0xffffffffu, where, o));
+  if ((threadIdx.x & 31) == 0) { s_val[threadIdx.x >> 5] = best; s_idx[threadIdx.x >> 5] = where; }
   __syncthreads();
   if (threadIdx.x == 0) {
-    for (int w = 1; w < (int)(blockDim.x >> 5); ++w)
-      if (s_val[w] > best || (s_val[w] == best && s_idx[w] < where)) { best = s_val[w]; where = s_idx[w]; }
+    for (int w = 1; w < 8; ++w) better(best, where, s_val[w], s_idx[w]);
+    pval[row * parts + part] = best;
+    pidx[row * parts + part] = where;
+  }
+}
+
+__global__ void select_kernel(const float* __restrict__ pval, const int64_t* __restrict__ pidx, int parts,
+                              int64_t* __restrict__ ids, int64_t ids_stride, int64_t position, int64_t* __restrict__ next,
+                              uint8_t* __restrict__ done, const int64_t* __restrict__ eos, int n_eos, int64_t pad,
+                              int64_t rows) {
+  const int64_t row = blockIdx.x * (int64_t)(blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (row >= rows) return;
+  float best = -CUDART_INF_F;
+  int64_t where = INT64_MAX;
+  for (int i = lane; i < parts; i += 32) better(best, where, pval[row * parts + i], pidx[row * parts + i]);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1)
+    better(best, where, __shfl_xor_sync(0xffffffffu, best, o), __shfl_xor_sync(0xffffffffu, where, o));
+  if (lane == 0) {
     const bool was_done = done[row] != 0;
     const int64_t token = was_done ? pad : (where == INT64_MAX ? 0 : where);
     bool end = false;
@@ -283,40 +388,46 @@ extern "C" int q3_kv_append(const void* k, const void* v, void* cache_k, void* c
   return launch_status();
 }
 
-extern "C" int64_t q3_cache_attention_workspace_bytes(int64_t B, int64_t S, int64_t Hq, int64_t D, int64_t start) {
-  if (B < 1 || S < 1 || Hq < 1 || D < 1 || start < 0) return 0;
-  const int64_t splits = cdiv(start + S, inf::kChunk);
-  return B * S * Hq * splits * (D + 1) * 4;
+static int64_t cache_attention_splits(int64_t total, int64_t D, int dtype) {
+  return cdiv(total, inf::chunk_keys((int)D, dtype_size(dtype)));
+}
+
+extern "C" int64_t q3_cache_attention_workspace_bytes(int64_t B, int64_t S, int64_t Hq, int64_t D, int64_t start,
+                                                      int dtype) {
+  if (B < 1 || S < 1 || Hq < 1 || D < 1 || start < 0 || dtype < Q3_F32 || dtype > Q3_F16) return 0;
+  return B * S * Hq * cache_attention_splits(start + S, D, dtype) * (D + 1) * 4;
 }
 
 namespace {
+template <typename T, int EPL, int G>
+int launch_partial(dim3 grid, const void* q, const void* ck, const void* cv, float* part, float* lse, int64_t S, int64_t Hq,
+                   int64_t Hkv, int64_t C, int64_t start, int splits, float scale, cudaStream_t st) {
+  auto kern = inf::cache_attention_partial_kernel<T, EPL, G>;
+  static DeviceFlags configured = {};
+  const int smem = 2 * inf::kTileBytes;
+  if (int rc = ensure_dynamic_smem(kern, smem, &configured); rc != Q3_OK) return rc;
+  kern<<<grid, inf::kAttnThreads, smem, st>>>((const T*)q, (const T*)ck, (const T*)cv, part, lse, S, Hq, Hkv, C, start,
+                                              splits, scale);
+  return launch_status();
+}
+
 template <typename T, int EPL>
 int launch_cache_attention(const void* q, const void* ck, const void* cv, void* out, float* part, float* lse, int64_t B,
                            int64_t S, int64_t Hq, int64_t Hkv, int64_t C, int64_t start, float scale, cudaStream_t st) {
   const int G = (int)(Hq / Hkv);
-  const int splits = (int)cdiv(start + S, inf::kChunk);
+  const int splits = (int)cdiv(start + S, inf::chunk_keys(EPL * 16, (int)sizeof(T)));
   dim3 grid((unsigned)splits, (unsigned)S, (unsigned)(B * Hkv));
-#define Q3_CASE(GG)                                                                                             \
-  case GG:                                                                                                      \
-    inf::cache_attention_partial_kernel<T, EPL, GG><<<grid, inf::kAttnThreads, 0, st>>>(                        \
-        (const T*)q, (const T*)ck, (const T*)cv, part, lse, S, Hq, Hkv, C, start, splits, scale);               \
-    break;
-  switch (G) {
-    Q3_CASE(1) Q3_CASE(2) Q3_CASE(4)
-    case 8:
-      if constexpr (EPL <= 8) {     // 8 warps x 8 heads x D fp32 of combine space must fit 48 KB
-        inf::cache_attention_partial_kernel<T, EPL, 8><<<grid, inf::kAttnThreads, 0, st>>>(
-            (const T*)q, (const T*)ck, (const T*)cv, part, lse, S, Hq, Hkv, C, start, splits, scale);
-        break;
-      }
-      return Q3_ERR_SHAPE;
-    default: return Q3_ERR_SHAPE;
+  int rc = Q3_ERR_SHAPE;
+  if (G == 1) rc = launch_partial<T, EPL, 1>(grid, q, ck, cv, part, lse, S, Hq, Hkv, C, start, splits, scale, st);
+  else if (G == 2) rc = launch_partial<T, EPL, 2>(grid, q, ck, cv, part, lse, S, Hq, Hkv, C, start, splits, scale, st);
+  else if (G == 4) rc = launch_partial<T, EPL, 4>(grid, q, ck, cv, part, lse, S, Hq, Hkv, C, start, splits, scale, st);
+  else if (G == 8) {
+    // 8 warps x 8 heads x D fp32 of combine space must fit the 32 KB tile it reuses
+    if constexpr (EPL <= 8) rc = launch_partial<T, EPL, 8>(grid, q, ck, cv, part, lse, S, Hq, Hkv, C, start, splits, scale, st);
   }
-#undef Q3_CASE
-  int rc = launch_status();
   if (rc != Q3_OK) return rc;
   const int64_t rows = B * S * Hq;
-  inf::cache_attention_merge_kernel<T><<<(unsigned)cdiv(rows, 8), 256, 0, st>>>(part, lse, (T*)out, rows, splits, EPL * 16);
+  inf::cache_attention_merge_kernel<T, EPL / 2><<<(unsigned)cdiv(rows, 4), 128, 0, st>>>(part, lse, (T*)out, rows, splits);
   return launch_status();
 }
 }  // namespace
@@ -330,8 +441,8 @@ extern "C" int q3_cache_attention(const void* q, const void* cache_k, const void
   if (D != 64 && D != 128 && D != 256) return Q3_ERR_SHAPE;
   if (dtype < Q3_F32 || dtype > Q3_F16) return Q3_ERR_DTYPE;
   if (!aligned16(q) || !aligned16(cache_k) || !aligned16(cache_v) || !aligned16(out)) return Q3_ERR_ALIGN;
-  if (!workspace || workspace_bytes < q3_cache_attention_workspace_bytes(B, S, Hq, D, start)) return Q3_ERR_WORKSPACE;
-  const int64_t splits = cdiv(start + S, inf::kChunk);
+  if (!workspace || workspace_bytes < q3_cache_attention_workspace_bytes(B, S, Hq, D, start, dtype)) return Q3_ERR_WORKSPACE;
+  const int64_t splits = cache_attention_splits(start + S, D, dtype);
   float* part = (float*)workspace;
   float* lse = part + B * S * Hq * splits * D;
   cudaStream_t st = (cudaStream_t)stream;
@@ -350,13 +461,16 @@ extern "C" int q3_gemv(const void* x, const void* weight, void* y, int64_t M, in
   if (M < 1 || M > 8 || N < 1 || K < 1) return Q3_ERR_SHAPE;
   if (dtype < Q3_F32 || dtype > Q3_F16) return Q3_ERR_DTYPE;
   if ((K * dtype_size(dtype)) % 16 || !aligned16(x) || !aligned16(weight)) return Q3_ERR_ALIGN;
-  const unsigned grid = (unsigned)cdiv(N, 8);
   cudaStream_t st = (cudaStream_t)stream;
-#define Q3_GEMV(MM)                                                                                                   \
-  case MM:                                                                                                            \
-    if (accurate) inf::gemv_kernel<T, double, MM><<<grid, 256, 0, st>>>((const T*)x, (const T*)weight, (T*)y, N, K);   \
-    else inf::gemv_kernel<T, float, MM><<<grid, 256, 0, st>>>((const T*)x, (const T*)weight, (T*)y, N, K);             \
-    break;
+  // 4 warps per CTA; 8 weight rows per warp for up to two input rows, 4 beyond (register budget: R x M accumulators)
+#define Q3_GEMV(MM)                                                                                                     \
+  case MM: {                                                                                                            \
+    constexpr int R = MM <= 2 ? 8 : 4;                                                                                  \
+    const unsigned grid = (unsigned)cdiv(N, 4 * R);                                                                     \
+    if (accurate) inf::gemv_kernel<T, double, MM, R><<<grid, 128, 0, st>>>((const T*)x, (const T*)weight, (T*)y, N, K); \
+    else inf::gemv_kernel<T, float, MM, R><<<grid, 128, 0, st>>>((const T*)x, (const T*)weight, (T*)y, N, K);           \
+    break;                                                                                                              \
+  }
   Q3_DISPATCH_FLOAT(dtype, T, {
     switch ((int)M) { Q3_GEMV(1) Q3_GEMV(2) Q3_GEMV(3) Q3_GEMV(4) Q3_GEMV(5) Q3_GEMV(6) Q3_GEMV(7) Q3_GEMV(8) }
   });
@@ -364,14 +478,31 @@ extern "C" int q3_gemv(const void* x, const void* weight, void* y, int64_t M, in
   return launch_status();
 }
 
+static int select_parts(int64_t V) { return (int)(cdiv(V, 4096) < 64 ? cdiv(V, 4096) : 64); }
+
+extern "C" int64_t q3_select_tokens_workspace_bytes(int64_t B, int64_t V) {
+  if (B < 1 || V < 1) return 0;
+  return B * select_parts(V) * 12;
+}
+
 extern "C" int q3_select_tokens(const void* logits, int64_t B, int64_t V, int64_t* ids, int64_t ids_stride,
                                 int64_t position, int64_t* next_token, uint8_t* done, const int64_t* eos_ids, int n_eos,
-                                int64_t pad, int dtype, q3_stream_t stream) {
+                                int64_t pad, void* workspace, int64_t workspace_bytes, int dtype, q3_stream_t stream) {
   if (!logits || !ids || !next_token || !done || (n_eos > 0 && !eos_ids)) return Q3_ERR_ARG;
-  if (B < 1 || V < 1 || position < 0 || position >= ids_stride || n_eos < 0) return Q3_ERR_SHAPE;
+  if (B < 1 || B > 65535 || V < 1 || position < 0 || position >= ids_stride || n_eos < 0) return Q3_ERR_SHAPE;
   if (dtype < Q3_F32 || dtype > Q3_F16) return Q3_ERR_DTYPE;
+  if (!workspace || workspace_bytes < q3_select_tokens_workspace_bytes(B, V) ||
+      (reinterpret_cast<uintptr_t>(workspace) & 7u))
+    return Q3_ERR_WORKSPACE;
+  const int parts = select_parts(V);
+  int64_t* pidx = (int64_t*)workspace;                       // 8-byte entries first: keeps them aligned
+  float* pval = (float*)(pidx + B * parts);
   cudaStream_t st = (cudaStream_t)stream;
-  Q3_DISPATCH_FLOAT(dtype, T, (inf::select_kernel<T><<<(unsigned)B, 1024, 0, st>>>(
-                                  (const T*)logits, V, ids, ids_stride, position, next_token, done, eos_ids, n_eos, pad)));
+  dim3 grid((unsigned)parts, (unsigned)B);
+  Q3_DISPATCH_FLOAT(dtype, T, (inf::argmax_parts_kernel<T><<<grid, 256, 0, st>>>((const T*)logits, V, parts, pval, pidx)));
+  int rc = launch_status();
+  if (rc != Q3_OK) return rc;
+  inf::select_kernel<<<(unsigned)cdiv(B, 4), 128, 0, st>>>(pval, pidx, parts, ids, ids_stride, position, next_token, done,
+                                                            eos_ids, n_eos, pad, B);
   return launch_status();
 }

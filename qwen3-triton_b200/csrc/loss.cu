@@ -15,6 +15,9 @@
 namespace q3 {
 
 constexpr int kCeThreads = 512;
+// The row-statistics kernel ends every row with a block-wide combine during which its CTA has no loads in flight.
+// CTAs of 256 threads, four or more resident per SM, reach that point at different times and cover for each other.
+constexpr int kCeRowThreads = 256;
 
 struct MaxSum { float m, s; };
 
@@ -47,7 +50,7 @@ __device__ __forceinline__ MaxSum block_maxsum(MaxSum v, float* smm, float* sms)
 // One CTA per shifted row (grid-stride): lse over the local vocabulary slice and the target logit
 // if this slice owns the label (else 0).
 template <typename T, int V>
-__global__ void __launch_bounds__(kCeThreads) ce_rows_kernel(const T* __restrict__ logits,
+__global__ void __launch_bounds__(kCeRowThreads, 4) ce_rows_kernel(const T* __restrict__ logits,
                                                              const int64_t* __restrict__ labels,
                                                              float* __restrict__ lse, float* __restrict__ target,
                                                              int64_t nrows, int64_t S, int64_t Vn, int64_t start,
@@ -326,14 +329,14 @@ extern "C" int q3_ce_local_rows(const void* logits, const int64_t* labels, float
   if (physical_rows < 1 || S < 2 || physical_rows % S || V_local < 1) return Q3_ERR_SHAPE;
   cudaStream_t st = (cudaStream_t)stream;
   const int64_t nrows = physical_rows / S * (S - 1);
-  const int grid = (int)(nrows < (int64_t)sm_count() * 4 ? nrows : (int64_t)sm_count() * 4);
+  const int grid = (int)(nrows < (int64_t)sm_count() * 8 ? nrows : (int64_t)sm_count() * 8);
   Q3_DISPATCH_FLOAT(dtype, T, {
     constexpr int VF = Vec16<T>::N;
     // every row start must be 16-byte aligned for the vector path
     const bool vec = aligned16(logits) && (V_local % VF == 0);
-    if (vec) ce_rows_kernel<T, VF><<<grid, kCeThreads, 0, st>>>((const T*)logits, labels, lse_local, target, nrows, S,
+    if (vec) ce_rows_kernel<T, VF><<<grid, kCeRowThreads, 0, st>>>((const T*)logits, labels, lse_local, target, nrows, S,
                                                                V_local, vocab_start, ignore_index, vocab_total, status);
-    else ce_rows_kernel<T, 1><<<grid, kCeThreads, 0, st>>>((const T*)logits, labels, lse_local, target, nrows, S,
+    else ce_rows_kernel<T, 1><<<grid, kCeRowThreads, 0, st>>>((const T*)logits, labels, lse_local, target, nrows, S,
                                                           V_local, vocab_start, ignore_index, vocab_total, status);
   });
   return launch_status();

@@ -89,10 +89,11 @@ SIGNATURES = {
     "q3_selftest_wait_timeout": (I, [L, P, P, P]),
     "q3_inf_positions": (I, [P, L, L, L, P]),
     "q3_kv_append": (I, [P, P, P, P, L, L, L, L, L, L, I, P]),
-    "q3_cache_attention_workspace_bytes": (L, [L, L, L, L, L]),
+    "q3_cache_attention_workspace_bytes": (L, [L, L, L, L, L, I]),
     "q3_cache_attention": (I, [P, P, P, P, P, L, L, L, L, L, L, L, L, D, I, P]),
     "q3_gemv": (I, [P, P, P, L, L, L, I, I, P]),
-    "q3_select_tokens": (I, [P, L, L, P, L, L, P, P, P, I, L, I, P]),
+    "q3_select_tokens_workspace_bytes": (L, [L, L]),
+    "q3_select_tokens": (I, [P, L, L, P, L, L, P, P, P, I, L, P, L, I, P]),
     "q3_block_order": (I, [P, L, L, L, L, L, L, I, P]),
     "q3_token_blocks": (I, [P, L, P, P, L, L, P, P]),
     "q3_validation_accumulate": (I, [P, P, L, P]),

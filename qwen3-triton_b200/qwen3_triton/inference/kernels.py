@@ -51,7 +51,7 @@ def attention(q, cache_k, cache_v, start, *, split_decode=False):
     if not all(t.is_cuda and t.is_contiguous() and t.dtype == q.dtype and t.device == q.device for t in tensors):
         raise ValueError('Matching contiguous CUDA tensors required; no fallback')
     out = torch.empty_like(q)
-    ws = _abi.workspace(_abi.lib().q3_cache_attention_workspace_bytes(b, s, hq, d, start), q.device)
+    ws = _abi.workspace(_abi.lib().q3_cache_attention_workspace_bytes(b, s, hq, d, start, _abi.dt(q.dtype)), q.device)
     _abi.call('q3_cache_attention', q.data_ptr(), cache_k.data_ptr(), cache_v.data_ptr(), out.data_ptr(), ws.data_ptr(),
               ws.numel(), b, s, hq, hk, d, capacity, start, d ** -0.5, _abi.dt(q.dtype), _abi.stream())
     return out
@@ -89,9 +89,10 @@ def select(logits, ids, next_token, done, position, eos, pad):
     if not all(t.is_cuda and t.is_contiguous() and t.device == logits.device for t in tensors):
         raise ValueError('Contiguous same-device CUDA tensors required; no fallback')
     stops = torch.tensor(list(eos), device=logits.device, dtype=torch.int64) if len(eos) else None
+    ws = _abi.workspace(_abi.lib().q3_select_tokens_workspace_bytes(logits.shape[0], logits.shape[1]), logits.device)
     _abi.call('q3_select_tokens', logits.data_ptr(), logits.shape[0], logits.shape[1], ids.data_ptr(), ids.shape[1],
-              position, next_token.data_ptr(), done.data_ptr(), _abi.ptr(stops), len(eos), pad, _abi.dt(logits.dtype),
-              _abi.stream())
+              position, next_token.data_ptr(), done.data_ptr(), _abi.ptr(stops), len(eos), pad, ws.data_ptr(), ws.numel(),
+              _abi.dt(logits.dtype), _abi.stream())
 
 
 def rms_norm(x, weight, eps, *, reference_accumulation=False):
