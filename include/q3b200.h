@@ -420,6 +420,10 @@ int q3_kv_append(const void* k, const void* v, void* cache_k, void* cache_v, int
  * head; chunks are merged by their log-sum-exp (fp32 partials in the workspace). Reference: inference/kernels.py:39-115 (cached attention and the
  * split decode path, which this replaces for every S). */
 int64_t q3_cache_attention_workspace_bytes(int64_t B, int64_t S, int64_t Hq, int64_t D, int64_t start, int dtype);
+/* 16-bit caches at head_dim 128 run the chunk products on the tensor cores (the G query heads of a group are rows of
+ * one MMA tile); everything else, or everything after q3_cache_attention_path(1), runs the CUDA-core kernel. The
+ * switch is process-wide, returns the previous setting, and only queries for arguments other than 0 / 1. */
+int q3_cache_attention_path(int path);
 int q3_cache_attention(const void* q, const void* cache_k, const void* cache_v, void* out, void* workspace,
                        int64_t workspace_bytes, int64_t B, int64_t S, int64_t Hq, int64_t Hkv, int64_t D, int64_t C,
                        int64_t start, double scale, int dtype, q3_stream_t stream);

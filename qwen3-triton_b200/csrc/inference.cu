@@ -64,7 +64,7 @@ cache_attention_partial_kernel(const T* __restrict__ q, const T* __restrict__ ck
                                int64_t C, int64_t start, int splits, float scale) {
   constexpr int D = EPL * 16;
   constexpr int CHUNK = chunk_keys(D, (int)sizeof(T));
-  extern __shared__ __align__(16) uint8_t smem[];
+  extern __shared__ __align__(128) uint8_t smem[];
   const T* ks = reinterpret_cast<const T*>(smem);
   const T* vs = reinterpret_cast<const T*>(smem + kTileBytes);
   const int split = blockIdx.x, s = blockIdx.y;
@@ -184,6 +184,259 @@ cache_attention_partial_kernel(const T* __restrict__ q, const T* __restrict__ ck
     part[row * D + d] = tot > 0.f ? val / tot : 0.f;
     if (d == 0) lse[row] = tot > 0.f ? nm + __logf(tot) : -CUDART_INF_F;
   }
+}
+
+// ---- the same partial attention on the tensor cores (16-bit types, head_dim 128) ------------------------------------
+// The CUDA-core kernel above spends ~90 instructions per key on a 4-head group and is issue-bound at a quarter of the
+// HBM rate. Here the G query heads of a group are the rows of a 16-row MMA tile (rows G..15 are zero), so one
+// mma.sync m16n8k16 per 8 keys and 16 head-dim values does the score work of all heads at once, and a second one per
+// 8 output columns the value work: about 150 instructions per warp for its 16 keys. Each of the 8 warps takes 16 of
+// the chunk's 128 keys, so there is no running rescale inside a warp; the warps are merged as in the kernel above.
+// K and V rows (256 bytes) are stored with their 16-byte pieces XOR-swizzled by (key & 7), which makes the
+// ldmatrix reads - eight rows 256 bytes apart - conflict-free.
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+template <typename T> __device__ __forceinline__ void mma_16816(float (&d)[4], uint32_t a0, uint32_t a2, uint32_t b0, uint32_t b1);
+template <> __device__ __forceinline__ void mma_16816<__nv_bfloat16>(float (&d)[4], uint32_t a0, uint32_t a2, uint32_t b0, uint32_t b1) {
+  const uint32_t z = 0;   // rows 8..15 of the A tile are zero
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3]) : "r"(a0), "r"(z), "r"(a2), "r"(z), "r"(b0), "r"(b1));
+}
+template <> __device__ __forceinline__ void mma_16816<__half>(float (&d)[4], uint32_t a0, uint32_t a2, uint32_t b0, uint32_t b1) {
+  const uint32_t z = 0;
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3]) : "r"(a0), "r"(z), "r"(a2), "r"(z), "r"(b0), "r"(b1));
+}
+// all 16 rows of the A tile in use
+template <typename T> __device__ __forceinline__ void mma_16816_full(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1);
+template <> __device__ __forceinline__ void mma_16816_full<__nv_bfloat16>(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+template <> __device__ __forceinline__ void mma_16816_full<__half>(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+template <typename T> __device__ __forceinline__ uint32_t pack_pair(float a, float b);
+template <> __device__ __forceinline__ uint32_t pack_pair<__nv_bfloat16>(float a, float b) {
+  const __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<const uint32_t*>(&h);
+}
+template <> __device__ __forceinline__ uint32_t pack_pair<__half>(float a, float b) {
+  const __half2 h = __floats2half2_rn(a, b);
+  return *reinterpret_cast<const uint32_t*>(&h);
+}
+
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+// One CTA walks `chunks_per_cta` consecutive 128-key chunks through two shared-memory stages: the copies of the next
+// chunk are in flight while the tensor cores work on the current one. Every warp keeps a running (max, sum, output)
+// for its 16 keys of each chunk and rescales when the maximum moves.
+template <typename T, int G>
+__global__ void __launch_bounds__(kAttnThreads, 1)
+cache_attention_partial_mma_kernel(const T* __restrict__ q, const T* __restrict__ ck, const T* __restrict__ cv,
+                                   float* __restrict__ part, float* __restrict__ lse, int64_t S, int64_t Hq, int64_t Hkv,
+                                   int64_t C, int64_t start, int splits, int chunks_per_cta, float scale) {
+  constexpr int D = 128, CHUNK = 128, ROW = 256;               // ROW: bytes per key row
+  constexpr int STAGE = 2 * kTileBytes;                        // K tile + V tile
+  extern __shared__ __align__(128) uint8_t smem[];
+  const uint32_t smem_u = (uint32_t)__cvta_generic_to_shared(smem);
+  const int split = blockIdx.x, s = blockIdx.y;
+  const int64_t bk = blockIdx.z, b = bk / Hkv, kvh = bk % Hkv;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t visible = start + s + 1;
+  const int64_t cta_first = (int64_t)split * chunks_per_cta * CHUNK;
+  int nchunks = 0;
+  if (cta_first < visible) {
+    const int64_t span = visible - cta_first;
+    nchunks = (int)((span + CHUNK - 1) / CHUNK);
+    if (nchunks > chunks_per_cta) nchunks = chunks_per_cta;
+  }
+  const uint8_t* kg = reinterpret_cast<const uint8_t*>(ck + (bk * C + cta_first) * D);
+  const uint8_t* vg = reinterpret_cast<const uint8_t*>(cv + (bk * C + cta_first) * D);
+
+  // 16-byte pieces of the live rows, swizzled; V rows past the live range are zeroed (0 * garbage must stay 0)
+  auto load_chunk = [&](int i) {
+    uint8_t* stage = smem + (i & 1) * STAGE;
+    const int64_t left = visible - (cta_first + (int64_t)i * CHUNK);
+    const int live = left < CHUNK ? (int)left : CHUNK;
+    const uint8_t* ksrc = kg + (int64_t)i * kTileBytes;
+    const uint8_t* vsrc = vg + (int64_t)i * kTileBytes;
+    for (int piece = threadIdx.x; piece < CHUNK * 16; piece += kAttnThreads) {
+      const int key = piece >> 4, c = piece & 15;
+      const int dst = key * ROW + ((c ^ (key & 7)) << 4);
+      if (key < live) {
+        cp_async16(stage + dst, ksrc + piece * 16);
+        cp_async16(stage + kTileBytes + dst, vsrc + piece * 16);
+      } else {
+        *reinterpret_cast<uint4*>(stage + kTileBytes + dst) = make_uint4(0u, 0u, 0u, 0u);
+      }
+    }
+    cp_async_commit();
+  };
+  if (nchunks > 0) load_chunk(0);
+
+  // A fragments of Q: row g = lane / 4 (zero for g >= G), two head-dim values at 16*k + 2*(lane % 4) (+8)
+  const int g = lane >> 2, pair = (lane & 3) * 2;
+  uint32_t qa[8][2];
+  {
+    const T* qp = q + (((b * S + s) * Hq) + kvh * G + (g < G ? g : 0)) * D;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      qa[k][0] = g < G ? *reinterpret_cast<const uint32_t*>(qp + 16 * k + pair) : 0u;
+      qa[k][1] = g < G ? *reinterpret_cast<const uint32_t*>(qp + 16 * k + 8 + pair) : 0u;
+    }
+  }
+  const int kbase = warp * 16;                                  // this warp's keys within every chunk
+  float m_w = -CUDART_INF_F, l_w = 0.f;
+  float o[16][4];
+#pragma unroll
+  for (int j = 0; j < 16; ++j) { o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f; }
+
+  for (int i = 0; i < nchunks; ++i) {
+    if (i + 1 < nchunks) { load_chunk(i + 1); cp_async_wait<1>(); } else { cp_async_wait<0>(); }
+    __syncthreads();
+    const uint32_t ks = smem_u + (i & 1) * STAGE, vs = ks + kTileBytes;
+    const int64_t left = visible - (cta_first + (int64_t)i * CHUNK);
+    const int live_keys = left < CHUNK ? (int)left : CHUNK;
+    if (kbase < live_keys) {
+      // S[16 x 16 keys] = Q K^T: per 16 head-dim values one ldmatrix.x4 (keys 0-7 / 8-15 x two 8-value pieces), two MMAs
+      float sc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+      {
+        const int key = kbase + (lane & 7) + ((lane >> 4) << 3), sub = (lane >> 3) & 1;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          uint32_t r[4];
+          ldmatrix_x4(r, ks + key * ROW + (((2 * k + sub) ^ (key & 7)) << 4));
+          mma_16816<T>(sc[0], qa[k][0], qa[k][1], r[0], r[1]);
+          mma_16816<T>(sc[1], qa[k][0], qa[k][1], r[2], r[3]);
+        }
+      }
+      // this thread: row g, keys kbase + 8*nt + pair + {0, 1}
+      float p[2][2];
+      float mx = -CUDART_INF_F;
+#pragma unroll
+      for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const bool live = kbase + 8 * nt + pair + e < live_keys;
+          p[nt][e] = live ? sc[nt][e] * scale : -CUDART_INF_F;
+          mx = fmaxf(mx, p[nt][e]);
+        }
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));       // the four lanes of a row; finite: key kbase is live
+      const float nm = fmaxf(m_w, mx);
+      const float alpha = __expf(m_w - nm);                      // 0 on the first chunk (m_w = -inf)
+      float sum = 0.f;
+#pragma unroll
+      for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          p[nt][e] = __expf(p[nt][e] - nm);
+          sum += p[nt][e];
+        }
+      sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+      sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+      l_w = l_w * alpha + sum;
+      m_w = nm;
+      if (i > 0) {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) { o[j][0] *= alpha; o[j][1] *= alpha; }
+      }
+      // O[16 x 128] += P V: P's accumulator layout is the A-fragment layout of the next product
+      const uint32_t pa0 = pack_pair<T>(p[0][0], p[0][1]), pa2 = pack_pair<T>(p[1][0], p[1][1]);
+      {
+        const int key = kbase + (lane & 7) + (((lane >> 3) & 1) << 3), sub = lane >> 4;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {                            // two 8-column output tiles per ldmatrix
+          uint32_t r[4];
+          ldmatrix_x4_trans(r, vs + key * ROW + (((2 * j + sub) ^ (key & 7)) << 4));
+          mma_16816<T>(o[2 * j], pa0, pa2, r[0], r[1]);
+          mma_16816<T>(o[2 * j + 1], pa0, pa2, r[2], r[3]);
+        }
+      }
+    }
+    __syncthreads();                                             // this stage may be overwritten two chunks later
+  }
+  float* s_acc = reinterpret_cast<float*>(smem);               // [8 warps][G][128]: at most 32 KB of stage 0
+  float* s_max = reinterpret_cast<float*>(smem + kTileBytes);  // [8][G]
+  float* s_sum = s_max + 8 * G;
+  if (g < G) {
+    if ((lane & 3) == 0) { s_max[warp * G + g] = m_w; s_sum[warp * G + g] = l_w; }
+#pragma unroll
+    for (int j = 0; j < 16; ++j)
+      *reinterpret_cast<float2*>(s_acc + (warp * G + g) * D + 8 * j + pair) = make_float2(o[j][0], o[j][1]);
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < G * D; idx += kAttnThreads) {
+    const int gg = idx / D, d = idx % D;
+    float nm = -CUDART_INF_F;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) nm = fmaxf(nm, s_max[w * G + gg]);
+    float tot = 0.f, val = 0.f;
+    if (nm > -CUDART_INF_F) {
+#pragma unroll
+      for (int w = 0; w < 8; ++w) {
+        const float f = __expf(s_max[w * G + gg] - nm);         // exp(-inf) = 0 for a warp without live keys
+        tot += s_sum[w * G + gg] * f;
+        val += s_acc[(w * G + gg) * D + d] * f;
+      }
+    }
+    const int64_t row = ((b * S + s) * Hq + kvh * G + gg) * splits + split;
+    part[row * D + d] = tot > 0.f ? val / tot : 0.f;
+    if (d == 0) lse[row] = tot > 0.f ? nm + __logf(tot) : -CUDART_INF_F;
+  }
+}
+
+// ---- small-M linear on the tensor cores (16-bit types) ------------------------------------------------------------
+// y[m, n] = sum_k x[m, k] w[n, k], M <= 8: 16 weight rows are the rows of an MMA tile and the M input rows its 8
+// columns, so the arithmetic costs two instructions per 16 x 32 block of weights and the kernel is a pure stream.
+// The contraction index may be permuted freely as long as both operands agree: lane (g, t) loads 16 contiguous bytes
+// w[n0 + g][k0 + 8t .. 8t+7] (and the same for row g + 8) and x[g][k0 + 8t .. 8t+7]; the four register pairs of each
+// load feed the (2t, 2t+1) and (2t+8, 2t+9) slots of two MMAs. The 4 warps of a CTA split K and add up in shared
+// memory (fixed order), which quadruples the bytes in flight per weight row.
+template <typename T, int UNROLL>
+__global__ void __launch_bounds__(128)
+gemv_mma_kernel(const T* __restrict__ x, const T* __restrict__ w, T* __restrict__ y, int64_t M, int64_t N, int64_t K) {
+  __shared__ float red[4][16][8];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+  const int64_t n0 = (int64_t)blockIdx.x * 16;
+  const int64_t ra = n0 + g < N ? n0 + g : N - 1, rb = n0 + g + 8 < N ? n0 + g + 8 : N - 1;   // clamped: rows past N are not stored
+  const T* wa = w + ra * K + 8 * t;
+  const T* wb = w + rb * K + 8 * t;
+  const T* xr = x + (int64_t)(g < M ? g : 0) * K + 8 * t;
+  float acc[4] = {0.f, 0.f, 0.f, 0.f};
+  const int64_t steps = K / 32;                                  // K % 32 == 0
+  for (int64_t st = warp * UNROLL; st < steps; st += 4 * UNROLL) {
+    uint4 a[UNROLL], c[UNROLL], xv[UNROLL];
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+      const bool in = st + u < steps;
+      const int64_t k0 = (st + u) * 32;
+      a[u] = in ? __ldcs(reinterpret_cast<const uint4*>(wa + k0)) : make_uint4(0u, 0u, 0u, 0u);
+      c[u] = in ? __ldcs(reinterpret_cast<const uint4*>(wb + k0)) : make_uint4(0u, 0u, 0u, 0u);
+      xv[u] = (in && g < M) ? *reinterpret_cast<const uint4*>(xr + k0) : make_uint4(0u, 0u, 0u, 0u);
+    }
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+      mma_16816_full<T>(acc, a[u].x, c[u].x, a[u].y, c[u].y, xv[u].x, xv[u].y);
+      mma_16816_full<T>(acc, a[u].z, c[u].z, a[u].w, c[u].w, xv[u].z, xv[u].w);
+    }
+  }
+  // accumulator: (row g, cols 2t, 2t+1), (row g + 8, same cols); columns are the input rows m
+  red[warp][g][2 * t] = acc[0]; red[warp][g][2 * t + 1] = acc[1];
+  red[warp][g + 8][2 * t] = acc[2]; red[warp][g + 8][2 * t + 1] = acc[3];
+  __syncthreads();
+  const int r = threadIdx.x >> 3, m = threadIdx.x & 7;         // 128 threads = 16 rows x 8 columns
+  if (n0 + r < N && m < M)
+    y[(int64_t)m * N + n0 + r] = from_f32<T>((red[0][r][m] + red[1][r][m]) + (red[2][r][m] + red[3][r][m]));
 }
 
 // out[row, :] = sum_i part[row, i, :] * w_i, w_i = exp(lse[row, i] - max) / sum_j exp(lse[row, j] - max); one warp per
@@ -411,6 +664,22 @@ int launch_partial(dim3 grid, const void* q, const void* ck, const void* cv, flo
   return launch_status();
 }
 
+template <typename T, int G>
+int launch_partial_mma(dim3 grid, const void* q, const void* ck, const void* cv, float* part, float* lse, int64_t S,
+                       int64_t Hq, int64_t Hkv, int64_t C, int64_t start, int splits, int chunks_per_cta, float scale,
+                       cudaStream_t st) {
+  auto kern = inf::cache_attention_partial_mma_kernel<T, G>;
+  static DeviceFlags configured = {};
+  const int smem = 4 * inf::kTileBytes;                        // two stages of (K tile, V tile)
+  if (int rc = ensure_dynamic_smem(kern, smem, &configured); rc != Q3_OK) return rc;
+  kern<<<grid, inf::kAttnThreads, smem, st>>>((const T*)q, (const T*)ck, (const T*)cv, part, lse, S, Hq, Hkv, C, start,
+                                              splits, chunks_per_cta, scale);
+  return launch_status();
+}
+
+// Process-wide switch for tests and tuning: 0 = tensor cores where they apply (default), 1 = CUDA cores always.
+int g_cache_attention_path = 0;
+
 template <typename T, int EPL>
 int launch_cache_attention(const void* q, const void* ck, const void* cv, void* out, float* part, float* lse, int64_t B,
                            int64_t S, int64_t Hq, int64_t Hkv, int64_t C, int64_t start, float scale, cudaStream_t st) {
@@ -418,6 +687,25 @@ int launch_cache_attention(const void* q, const void* ck, const void* cv, void* 
   const int splits = (int)cdiv(start + S, inf::chunk_keys(EPL * 16, (int)sizeof(T)));
   dim3 grid((unsigned)splits, (unsigned)S, (unsigned)(B * Hkv));
   int rc = Q3_ERR_SHAPE;
+  if constexpr (EPL == 8 && sizeof(T) == 2) {
+    if (g_cache_attention_path == 0) {
+      // chunks per CTA: as many as keep at least four CTAs per SM in the grid (fewer, larger partial results to merge
+      // and copies that overlap the arithmetic inside a CTA); the workspace is sized for one chunk per CTA
+      const int64_t chunks = cdiv(start + S, 128), base = B * Hkv * S;
+      int cpc = 8;
+      while (cpc > 1 && base * cdiv(chunks, cpc) < 4 * (int64_t)sm_count()) cpc >>= 1;
+      const int nsplit = (int)cdiv(chunks, cpc);
+      dim3 grid2((unsigned)nsplit, (unsigned)S, (unsigned)(B * Hkv));
+      if (G == 1) rc = launch_partial_mma<T, 1>(grid2, q, ck, cv, part, lse, S, Hq, Hkv, C, start, nsplit, cpc, scale, st);
+      else if (G == 2) rc = launch_partial_mma<T, 2>(grid2, q, ck, cv, part, lse, S, Hq, Hkv, C, start, nsplit, cpc, scale, st);
+      else if (G == 4) rc = launch_partial_mma<T, 4>(grid2, q, ck, cv, part, lse, S, Hq, Hkv, C, start, nsplit, cpc, scale, st);
+      else if (G == 8) rc = launch_partial_mma<T, 8>(grid2, q, ck, cv, part, lse, S, Hq, Hkv, C, start, nsplit, cpc, scale, st);
+      if (rc != Q3_OK) return rc;
+      const int64_t rows2 = B * S * Hq;
+      inf::cache_attention_merge_kernel<T, EPL / 2><<<(unsigned)cdiv(rows2, 4), 128, 0, st>>>(part, lse, (T*)out, rows2, nsplit);
+      return launch_status();
+    }
+  }
   if (G == 1) rc = launch_partial<T, EPL, 1>(grid, q, ck, cv, part, lse, S, Hq, Hkv, C, start, splits, scale, st);
   else if (G == 2) rc = launch_partial<T, EPL, 2>(grid, q, ck, cv, part, lse, S, Hq, Hkv, C, start, splits, scale, st);
   else if (G == 4) rc = launch_partial<T, EPL, 4>(grid, q, ck, cv, part, lse, S, Hq, Hkv, C, start, splits, scale, st);
@@ -431,6 +719,14 @@ int launch_cache_attention(const void* q, const void* ck, const void* cv, void* 
   return launch_status();
 }
 }  // namespace
+
+// 0: tensor-core kernel for 16-bit caches at head_dim 128 (default); 1: CUDA-core kernel for everything. Returns the
+// previous setting; any other argument only queries.
+extern "C" int q3_cache_attention_path(int path) {
+  const int old = g_cache_attention_path;
+  if (path == 0 || path == 1) g_cache_attention_path = path;
+  return old;
+}
 
 extern "C" int q3_cache_attention(const void* q, const void* cache_k, const void* cache_v, void* out, void* workspace,
                                   int64_t workspace_bytes, int64_t B, int64_t S, int64_t Hq, int64_t Hkv, int64_t D,
@@ -462,6 +758,12 @@ extern "C" int q3_gemv(const void* x, const void* weight, void* y, int64_t M, in
   if (dtype < Q3_F32 || dtype > Q3_F16) return Q3_ERR_DTYPE;
   if ((K * dtype_size(dtype)) % 16 || !aligned16(x) || !aligned16(weight)) return Q3_ERR_ALIGN;
   cudaStream_t st = (cudaStream_t)stream;
+  if (!accurate && dtype != Q3_F32 && K % 32 == 0 && aligned16(x) && aligned16(weight)) {
+    const unsigned grid = (unsigned)cdiv(N, 16);
+    if (dtype == Q3_BF16) inf::gemv_mma_kernel<__nv_bfloat16, 4><<<grid, 128, 0, st>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)weight, (__nv_bfloat16*)y, M, N, K);
+    else inf::gemv_mma_kernel<__half, 4><<<grid, 128, 0, st>>>((const __half*)x, (const __half*)weight, (__half*)y, M, N, K);
+    return launch_status();
+  }
   // 4 warps per CTA; 8 weight rows per warp for up to two input rows, 4 beyond (register budget: R x M accumulators)
 #define Q3_GEMV(MM)                                                                                                     \
   case MM: {                                                                                                            \

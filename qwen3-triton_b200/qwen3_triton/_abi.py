@@ -91,6 +91,7 @@ SIGNATURES = {
     "q3_kv_append": (I, [P, P, P, P, L, L, L, L, L, L, I, P]),
     "q3_cache_attention_workspace_bytes": (L, [L, L, L, L, L, I]),
     "q3_cache_attention": (I, [P, P, P, P, P, L, L, L, L, L, L, L, L, D, I, P]),
+    "q3_cache_attention_path": (I, [I]),
     "q3_gemv": (I, [P, P, P, L, L, L, I, I, P]),
     "q3_select_tokens_workspace_bytes": (L, [L, L]),
     "q3_select_tokens": (I, [P, L, L, P, L, L, P, P, P, I, L, P, L, I, P]),

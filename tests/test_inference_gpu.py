@@ -51,6 +51,28 @@ def test_attention_over_the_cache(B, S, Hq, Hkv, D, start, dtype):
     assert torch.equal(out, K.attention(q.cuda(), ck.cuda(), cv.cuda(), start))        # deterministic
 
 
+@pytest.mark.parametrize('B,S,Hq,Hkv,start', [(2, 1, 32, 8, 1000), (1, 5, 8, 8, 130), (1, 1, 16, 2, 127), (3, 2, 4, 2, 0)])
+def test_tensor_core_and_cuda_core_cache_attention_agree(B, S, Hq, Hkv, start):
+    """bf16 caches at head_dim 128 take the MMA kernel; the CUDA-core kernel must give the same result up to the bf16
+    rounding of the probabilities (the MMA kernel feeds them to the second product in bf16)."""
+    from qwen3_triton import _abi
+    from qwen3_triton.inference import kernels as K
+    dtype, D = torch.bfloat16, 128
+    C = start + S
+    q = randn((B, S, Hq, D), 41, dtype).cuda()
+    ck, cv = randn((B, Hkv, C, D), 42, dtype).cuda(), randn((B, Hkv, C, D), 43, dtype).cuda()
+    lib = _abi.lib()
+    assert lib.q3_cache_attention_path(-1) == 0
+    fast = K.attention(q, ck, cv, start)
+    old = lib.q3_cache_attention_path(1)
+    try:
+        slow = K.attention(q, ck, cv, start)
+    finally:
+        lib.q3_cache_attention_path(old)
+    close(fast, slow.float().cpu().to(dtype), what='mma vs cuda cores', scale='row')
+    close(fast, OI.attention(q.cpu(), ck.cpu(), cv.cpu(), start).to(dtype), what='mma vs oracle', scale='row')
+
+
 def test_grouped_query_heads_read_their_own_kv_head():
     from qwen3_triton.inference import kernels as K
     B, S, Hq, Hkv, D, T = 1, 1, 8, 2, 64, 40
