@@ -51,7 +51,7 @@ GEMM_ENTRIES = ("q3_gemm", "q3_gemm_acc", "q3_gemm_acc_f32", "q3_gate_up_swiglu_
 # DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum, one ncu capture per shape) divided by the algorithmic
 # bytes (operands read once + result written once) of the GEMM shapes of one training step at 2048 tokens; the source
 # table with the full command is profiles/gemm_tc_kernel_step_shapes_dram.md. Used for roofline.traffic.
-DRAM_OVER_ALGORITHMIC = 1.0
+DRAM_OVER_ALGORITHMIC = 1.214
 DRAM_RATIO_SOURCE = "profiles/gemm_tc_kernel_step_shapes_dram.md"
 
 
@@ -550,7 +550,10 @@ def run_fsdp(args):
                                    vocab_parallel_embedding=os.environ.get("Q3_BENCH_VP_EMBEDDING", "1") == "1",
                                    forward_prefetch=int(os.environ.get("Q3_BENCH_FORWARD_PREFETCH", "2")))
     model.lm_head.fused = os.environ.get("Q3_BENCH_FUSED_LOSS", "1") == "1"
-    hooks = configure(model, comm, pack_gradients_off_compute_stream=os.environ.get("Q3_BENCH_PACK_SIDE", "0") == "1")
+    # gradients reduced by the pull kernel over peer memory (bf16 on the links, fp32 sums) unless Q3_BENCH_PEER_REDUCE=0
+    peer_reduce = os.environ.get("Q3_BENCH_PEER_REDUCE", "1") == "1" and world in (2, 4, 8)
+    hooks = configure(model, comm, pack_gradients_off_compute_stream=os.environ.get("Q3_BENCH_PACK_SIDE", "0") == "1",
+                      peer_memory_reduce=peer_reduce)
     decoder = [p for n, p in model.named_parameters() if not n.startswith("lm_head.")]
     opt = TritonAdamW([dict(params=decoder), dict(params=[model.lm_head.weight])], lr=1e-4, betas=(0.9, 0.95),
                       weight_decay=0.1, block=16384)
@@ -683,6 +686,10 @@ def run_fsdp(args):
                                                             (tokens / world / (v * 1e-3)) * flops_tok / (peak_tf * 1e12),
                                                         "steps": short} for p, v in others.items()},
                        "peak_memory_gb_rank0": peak_memory, "nccl_max_ctas": max_ctas or "default",
+                       "gradient_reduce": ("pull kernel over peer memory, bf16 on the links, fp32 sums in rank order "
+                                           "(%d of %d reduce-scatter calls)" % (hooks["reduce_scatter"].peer_calls,
+                                                                                hooks["reduce_scatter"].calls)
+                                           if peer_reduce else "NCCL fp32 reduce-scatter"),
                        "fsdp_units": hooks["units"], "collectives": comm.report()},
             "e2e": {"value": tokens / (e2e_ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": batch * seq * 8 * world,
                     "d2h_bytes_per_step": 4 * world},
@@ -690,6 +697,8 @@ def run_fsdp(args):
             "roofline": roofline,
         }
         print(json.dumps(line), flush=True)
+    if hooks["peer_reducer"] is not None:
+        hooks["peer_reducer"].close()
     dist.destroy_process_group()
     if status:
         raise SystemExit("device status word is not clean: %d (see include/q3b200.h, Q3_STATUS_*)" % status)

@@ -404,6 +404,25 @@ int q3_validation_accumulate(const float* loss, double* totals, int64_t tokens, 
 int q3_validation_rows(const float* losses, const int64_t* labels, int64_t B, int64_t S, int64_t ignore_index,
                        double* totals, q3_stream_t stream);
 
+/* ---- gradient reduce-scatter over peer memory ------------------------------------------------ */
+
+/* A device buffer that other processes on the node can map (plain cudaMalloc + its 64-byte IPC handle), the mapping
+ * of a peer's buffer from its handle, and their release. The staging buffers of q3_reduce_scatter_pull are made this
+ * way once, at set-up; no counterpart in the reference's Python (its symmetric-memory experiments live in scripts/). */
+int q3_peer_alloc(int64_t bytes, void** ptr, void* handle64);
+int q3_peer_open(const void* handle64, void** ptr);
+int q3_peer_close(void* ptr);
+int q3_peer_free(void* ptr);
+
+/* out[i] = scale * sum_r widen(peers[r][first + i]), i in [0, count): this rank's rows of every rank's 16-bit staging
+ * buffer, pulled with plain peer loads, added in fp32 in rank order. `peers` is a HOST array of `world` (2, 4 or 8)
+ * device pointers; first % 8 == 0. One kernel replaces the chunk-cat upcast and the fp32 ring reduce-scatter of a
+ * gradient bucket; the result equals an fp32 reduce-scatter of the upcast values. Ordering across ranks (staging
+ * complete before the pull, not overwritten before every rank has pulled) is the caller's job.
+ * Reference: qwen3_triton/runtime/collectives.py:139-203 (reduce_scatter, lossless_bf16) + runtime/ops.py:193-202. */
+int q3_reduce_scatter_pull(const void* const* peers, int world, float* out, int64_t first, int64_t count, double scale,
+                           int dtype, q3_stream_t stream);
+
 /* ---- decode-time kernels -------------------------------------------------------------------- */
 
 /* pos[b, s] = start + s (int64 [batch, seq]). Reference: qwen3_triton/inference/kernels.py:12-22 (positions). */

@@ -87,6 +87,11 @@ SIGNATURES = {
     "q3_attn_bwd_group_split": (I, [L, L, L, L]),
     "q3_attn_bwd_group_policy": (I, [I]),
     "q3_selftest_wait_timeout": (I, [L, P, P, P]),
+    "q3_peer_alloc": (I, [L, P, P]),
+    "q3_peer_open": (I, [P, P]),
+    "q3_peer_close": (I, [P]),
+    "q3_peer_free": (I, [P]),
+    "q3_reduce_scatter_pull": (I, [P, I, P, L, L, D, I, P]),
     "q3_inf_positions": (I, [P, L, L, L, P]),
     "q3_kv_append": (I, [P, P, P, P, L, L, L, L, L, L, I, P]),
     "q3_cache_attention_workspace_bytes": (L, [L, L, L, L, L, I]),

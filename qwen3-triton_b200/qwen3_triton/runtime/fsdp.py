@@ -37,9 +37,11 @@ class TritonAllGather(_Allocation, AllGather):
 
 
 class TritonReduceScatter(_Allocation, ReduceScatter):
-    def __init__(self, communication):
+    def __init__(self, communication, peer_reducer=None):
         self.communication = communication
+        self.peer_reducer = peer_reducer       # runtime/peer_reduce.py: gradients staged as bf16, pulled over NVLink
         self.calls = 0
+        self.peer_calls = 0
 
     def __call__(self, output_tensor, input_tensor, group, op, async_op=False):
         if async_op:
@@ -52,19 +54,61 @@ class TritonReduceScatter(_Allocation, ReduceScatter):
             operation = 'sum'
         else:
             raise ValueError('FSDP SUM/AVG only')
-        self.communication.reduce_scatter(output_tensor, input_tensor, operation, lossless_bf16=True)
         self.calls += 1
+        if self.peer_reducer is not None and self.peer_reducer.staged(input_tensor):
+            if operation != 'avg':
+                # with a gradient divide factor FSDP scales its fp32 buffer before a SUM; that buffer was never filled
+                raise ValueError('peer_memory_reduce supports the AVG gradient reduction only')
+            self.peer_reducer.reduce(input_tensor, output_tensor, 1.0 / self.communication.world)
+            self.peer_calls += 1
+            return
+        self.communication.reduce_scatter(output_tensor, input_tensor, operation, lossless_bf16=True)
 
 
-def configure(model, communication, *, pack_kernels=True, pack_gradients_off_compute_stream=False):
+def largest_unit_elements(model, world):
+    """Upper bound of the padded gradient elements one FSDP unit reduces: per unit, the parameters it manages, each
+    padded to a multiple of the world size along its first dimension."""
+    largest = 0
+    for module in model.modules():
+        if not isinstance(module, FSDPModule):
+            continue
+        group = module._get_fsdp_state()._fsdp_param_group
+        if group is None:
+            continue
+        total = 0
+        for fsdp_param in group.fsdp_params:
+            shape = tuple(fsdp_param._orig_size)
+            first = shape[0] if shape else 1
+            rest = 1
+            for d in shape[1:]:
+                rest *= d
+            total += -(-first // world) * world * rest
+        largest = max(largest, total)
+    return largest
+
+
+def configure(model, communication, *, pack_kernels=True, pack_gradients_off_compute_stream=False,
+              peer_memory_reduce=False):
     """Install the comm hooks on every FSDP unit and (by default) the pack/unpack kernels of runtime/ops.py.
-    `pack_gradients_off_compute_stream`: run the reduce-scatter copy-in on FSDP's reduce-scatter stream."""
+    `pack_gradients_off_compute_stream`: run the reduce-scatter copy-in on FSDP's reduce-scatter stream.
+    `peer_memory_reduce`: reduce gradients with the pull kernel over peer memory (runtime/peer_reduce.py; one node,
+    2 / 4 / 8 ranks, implies the copy-in on the reduce-scatter stream); the returned dict holds the reducer under
+    'peer_reducer' - call its close() before the process group is destroyed."""
+    reducer = None
+    if peer_memory_reduce:
+        if not pack_kernels:
+            raise ValueError('peer_memory_reduce needs the pack kernels')
+        from .peer_reduce import PeerGradientReducer
+        device = torch.device('cuda', torch.cuda.current_device())
+        reducer = PeerGradientReducer(communication.group, device, largest_unit_elements(model, communication.world))
     if pack_kernels:
-        from .ops import install_fsdp_pack_kernels, pack_gradients_on_reduce_scatter_stream
+        from .ops import (install_fsdp_pack_kernels, pack_gradients_on_reduce_scatter_stream,
+                          reduce_gradients_over_peer_memory)
         install_fsdp_pack_kernels()
-        pack_gradients_on_reduce_scatter_stream(model if pack_gradients_off_compute_stream else None)
+        pack_gradients_on_reduce_scatter_stream(model if (pack_gradients_off_compute_stream or reducer) else None)
+        reduce_gradients_over_peer_memory(reducer)
     ag = TritonAllGather(communication)
-    rs = TritonReduceScatter(communication)
+    rs = TritonReduceScatter(communication, reducer)
     count = 0
     for module in model.modules():
         if isinstance(module, FSDPModule):
@@ -73,4 +117,4 @@ def configure(model, communication, *, pack_kernels=True, pack_gradients_off_com
             count += 1
     if not count:
         raise ValueError('No FSDP units to configure')
-    return dict(all_gather=ag, reduce_scatter=rs, units=count)
+    return dict(all_gather=ag, reduce_scatter=rs, units=count, peer_reducer=reducer)

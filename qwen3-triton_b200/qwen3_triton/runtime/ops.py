@@ -161,6 +161,14 @@ def split_with_sizes_copy(all_gather_output, all_gather_input_split_sizes, dim=0
 
 
 _rs_root = None        # weak reference to the root FSDP module whose reduce-scatter stream takes the gradient pack
+_peer_reducer = None   # runtime/peer_reduce.py:PeerGradientReducer when gradients are reduced over peer memory
+
+
+def reduce_gradients_over_peer_memory(reducer):
+    """With a PeerGradientReducer installed, `fsdp::chunk_cat` packs 16-bit gradients into its staging buffer (on the
+    reduce-scatter stream) instead of upcasting them into FSDP's fp32 buffer; the reduce-scatter hook then pulls."""
+    global _peer_reducer
+    _peer_reducer = reducer
 
 
 def pack_gradients_on_reduce_scatter_stream(root_module):
@@ -196,6 +204,10 @@ def chunk_cat(tensors, dim, num_chunks, out):
         torch._chunk_cat(tensors, dim, num_chunks, out=out)
         return
     side = _reduce_scatter_stream()
+    peer = _peer_reducer
+    if peer is not None and (side is None or tensors[0].dtype not in (torch.bfloat16, torch.float16)
+                             or out.dtype != torch.float32 or out.device != peer.device):
+        peer = None
     if side is None:
         _launch(rows, tensors[0].dtype, out.dtype, out.device)
         return
@@ -204,6 +216,8 @@ def chunk_cat(tensors, dim, num_chunks, out):
         t.record_stream(side)
     out.record_stream(side)
     with torch.cuda.stream(side):
+        if peer is not None and peer.stage(tensors, out, _launch, plan_chunk_cat):
+            return          # the gradients wait, still 16-bit, in the peer-visible staging buffer; `out` stays unwritten
         _launch(rows, tensors[0].dtype, out.dtype, out.device)
 
 

@@ -3,7 +3,8 @@ and the averaged full gradient; one training step of a small fused-layer model u
 gathered by FSDP and kept vocabulary-parallel, against an UNSHARDED copy of the same model run on the concatenated
 batch of both ranks (loss of each rank's tokens, and the rank's shards of the embedding, lm_head and a decoder
 matrix gradient, which FSDP averages over ranks); and the two sharded forms against each other (same loss, same
-embedding-gradient shard, same loss after AdamW). What the reference checks with its CPU-gathered fp64 average
+embedding-gradient shard, same loss after AdamW); and the gradient reduce-scatter by the pull kernel over peer memory
+against the NCCL fp32 reduce-scatter (every shard bit-identical on two ranks). What the reference checks with its CPU-gathered fp64 average
 (scripts/check_triton_fsdp_v14.py:22-100)."""
 import os
 import subprocess
@@ -103,6 +104,34 @@ WORKER = textwrap.dedent('''
     assert s0 < l0
     rel = float((g0 - g1).norm() / g0.norm())
     assert rel < 2e-2, rel
+
+    # 3. the same step with gradients reduced by the pull kernel over peer memory: on two ranks the fp32 sum of the two
+    #    upcast bf16 gradients has one possible value, so every gradient shard equals the NCCL path's bit for bit
+    shards = []
+    for peer in (False, True):
+        torch.manual_seed(1234)
+        with torch.device(dev):
+            model = model_for_variant(cfg, "b200_fused")
+        comm = NcclCollectives()
+        model = shard_vocab_loss_model(model, keep_full_layers=4, checkpoint_every=1, skip_embedding_backward_gather=True,
+                                       fused_vocab_dw=True, communication=None, checkpoint_mode="selective",
+                                       layers_per_unit=[1, 1, 2], vocab_parallel_embedding=True)
+        hooks = configure(model, comm, peer_memory_reduce=peer)
+        for _ in range(3):                                   # three steps: both staging slots reused several times
+            model.zero_grad(set_to_none=True)
+            model(ids, labels=ids).loss.backward()
+        torch.cuda.synchronize()
+        shards.append({n: (q.grad.to_local() if hasattr(q.grad, "to_local") else q.grad).float().cpu().clone()
+                       for n, q in model.named_parameters()})
+        rs = hooks["reduce_scatter"]
+        assert rs.calls > 0 and rs.peer_calls == (rs.calls if peer else 0), (rs.calls, rs.peer_calls)
+        if hooks["peer_reducer"] is not None:
+            hooks["peer_reducer"].close()
+        configure(model, comm)                               # leaves no reducer installed behind
+        assert _abi.read_status() == 0
+    for name, want in shards[0].items():
+        assert torch.equal(want, shards[1][name]), name
+    sys.stdout.write("rank%%d peer-memory reduce equals NCCL on %%d tensors" %% (rank, len(shards[0])) + chr(10))
     dist.barrier(); dist.destroy_process_group()
     sys.stdout.write("rank" + str(rank) + "ok" + chr(10)); sys.stdout.flush()
 ''') % str(ROOT / "qwen3-triton_b200")
