@@ -306,6 +306,16 @@ def census(counter):
             sys.stderr.write("gemm %6d x %6d x %6d %-10s n=%3d total %8.3f ms avg %8.1f us %7.1f TFLOP/s\n" % (
                 m, n, k, lay, cnt, tot, tot / cnt * 1e3, 2.0 * m * n * k * cnt / tot / 1e9))
     gemm_ms = sum(by_name.get(n, 0.0) for n in GEMM_ENTRIES)
+    trace = os.environ.get("Q3_BENCH_TRACE")
+    if trace and counter.records:
+        # timeline of the census step: entry point, start (ms after the first call, same stream only) and duration
+        first = counter.records[0][2]
+        with open("%s.rank%s" % (trace, os.environ.get("RANK", "0")), "w") as f:
+            for name, a, s, e in counter.records:
+                try:
+                    f.write("%s %.4f %.4f\n" % (name, first.elapsed_time(s), s.elapsed_time(e)))
+                except Exception:
+                    f.write("%s nan %.4f\n" % (name, s.elapsed_time(e)))
     return by_name, flops, nbytes, gemm_ms
 
 
@@ -340,6 +350,10 @@ def build_single_gpu(cfg, device):
         model.fused_loss = os.environ.get("Q3_BENCH_FUSED_LOSS", "1") == "1"
     masters = MasterWeights(model).fuse_into_optimizer()
     opt = TritonAdamW(masters.parameters(), lr=1e-4, betas=(0.9, 0.95), weight_decay=0.1, block=16384)
+    if os.environ.get("Q3_BENCH_EARLY_ADAMW", "1") == "1":
+        # each decoder layer is updated on a side stream as soon as its backward is complete, beside the GEMMs of the
+        # layers below it; embedding, final norm and head are updated by opt.step()
+        opt.step_during_backward([masters.masters_of(layer) for layer in model.model.layers], masters.working_of)
     return model, masters, opt
 
 
@@ -554,6 +568,7 @@ def run_fsdp(args):
     peer_reduce = os.environ.get("Q3_BENCH_PEER_REDUCE", "1") == "1" and world in (2, 4, 8)
     hooks = configure(model, comm, pack_gradients_off_compute_stream=os.environ.get("Q3_BENCH_PACK_SIDE", "0") == "1",
                       peer_memory_reduce=peer_reduce)
+    peer_reduce = hooks["peer_reducer"] is not None        # False on every rank if the mappings could not be made
     decoder = [p for n, p in model.named_parameters() if not n.startswith("lm_head.")]
     opt = TritonAdamW([dict(params=decoder), dict(params=[model.lm_head.weight])], lr=1e-4, betas=(0.9, 0.95),
                       weight_decay=0.1, block=16384)

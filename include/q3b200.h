@@ -380,6 +380,14 @@ int q3_attn_path(const void* q, const void* k, const void* v, const void* out, i
 int q3_attn_bwd_group_split(int64_t B, int64_t Hq, int64_t Hkv, int64_t S);
 int q3_attn_bwd_group_policy(int policy);
 
+/* How the persistent GEMM kernels (every q3_gemm* / q3_linear* / q3_gate_up* / q3_down_dgrad* entry) hand out their
+ * 128-row output tiles: 1 (default) = each CTA draws its next tile from a device counter, 0 = CTA b takes tiles
+ * b, b + grid, ... . Drawn tiles keep a launch short when some SMs are held by a kernel of another stream (a
+ * collective during a data-parallel step): with the fixed stride the CTAs that start late still own a full share.
+ * Returns the previous policy (any other argument only queries); process-wide; results are bit-identical.
+ * The first GEMM call on a device allocates and zeroes the counters (32 KB): make it outside stream capture. */
+int q3_gemm_tile_schedule(int mode);
+
 /* ---- token-block data path and validation statistics ---------------------------------------- */
 
 /* out[i] = training ? ((first + i + offset) * stride + seed) mod n : first + i, for i in [0, count): the order in

@@ -25,6 +25,9 @@
 // Replaces, in the reference: qwen3_triton/kernels/linear.py:14-77 (_gemm / matmul),
 // kernels/mlp.py:14-32 and kernels/mlp_precision.py:17-35 (_gate_up).
 #include "tcgen05.cuh"
+#include <atomic>
+#include <mutex>
+#include <string.h>
 
 namespace q3 {
 
@@ -52,6 +55,9 @@ struct GemmParams {
   int a_mn, b_mn;   // operand is MN-major
   int prefetch;     // issue L2 prefetches ahead of the smem ring
   int* status;
+  // Tile hand-out. nullptr: CTA b works on tiles b, b + grid, ... (static). Otherwise {next tile, CTAs finished}, both
+  // zero at launch: every CTA draws its tiles from the counter, and the last CTA to finish zeroes the pair again.
+  int* sched;
   // grouped products that share one operand (seg_mode 0 = plain GEMM):
   //   1: segments along N  - B_i and C_i differ, A shared            (q/k/v projections of one input)
   //   2: segments along K  - A_i and B_i differ, one C               (sum of their input gradients)
@@ -91,6 +97,10 @@ template <int BN> struct Cfg {
   static constexpr int TMEM_COLS = 2 * BN;  // two accumulators
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
 };
+// Slots of the in-CTA tile queue (producer -> MMA issuer and epilogue warps). The producer runs at most one tile ahead
+// of the MMA issuer and the epilogue at most two behind it; the queue's own barriers make any depth correct.
+constexpr int kSched = 4;
+static_assert((2 * 6 + 6 + 2 * kSched) * 8 + kSched * 4 <= 256, "barrier area");
 
 __device__ __forceinline__ float silu_f(float g) { return g / (1.f + __expf(-g)); }
 
@@ -167,15 +177,34 @@ gemm_tc_kernel(const __grid_constant__ GemmMaps maps, const GemmParams p) {
   const uint32_t done_bar = bar0 + 8u * (2 * C::STAGES + 4);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * C::STAGES + 5);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  // tile queue: sfull[kSched], sempty[kSched], then the tile numbers
+  const uint32_t sbar0 = bar0 + 8u * (2 * C::STAGES + 6);
+  auto sfull_bar = [&](int i) { return sbar0 + 8u * i; };
+  auto sempty_bar = [&](int i) { return sbar0 + 8u * (kSched + i); };
+  volatile int* sched_tile = reinterpret_cast<volatile int*>(bars + 2 * C::STAGES + 6 + 2 * kSched);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int total_tiles = p.tiles_m * p.tiles_n;
+  // Consumer side of the tile queue (MMA issuer: one thread; epilogue: whole warps, lane 0 releases the slot).
+  // Returns the tile, -1 after the last one, -2 when a wait gave up.
+  uint32_t taken = 0;
+  auto next_tile = [&](bool whole_warp) -> int {
+    const int slot = taken % kSched;
+    const uint32_t ph = (taken / kSched) & 1u;
+    ++taken;
+    if (!mbar_wait(sfull_bar(slot), ph, abort_flag)) return -2;
+    const int t = sched_tile[slot];
+    if (whole_warp) __syncwarp();
+    if (!whole_warp || lane == 0) mbar_arrive(sempty_bar(slot));
+    return t;
+  };
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
     for (int s = 0; s < C::STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
     for (int a = 0; a < 2; ++a) { mbar_init(tfull_bar(a), 1); mbar_init(tempty_bar(a), 4); }
     mbar_init(done_bar, 1);
+    for (int i = 0; i < kSched; ++i) { mbar_init(sfull_bar(i), 1); mbar_init(sempty_bar(i), 5); }   // MMA + 4 warps
     fence_barrier_init();
     prefetch_tmap(&maps.a[0]);
     prefetch_tmap(&maps.b[0]);
@@ -193,9 +222,22 @@ gemm_tc_kernel(const __grid_constant__ GemmMaps maps, const GemmParams p) {
   if (warp == 0) {
     // ------------------------------------------------------------- TMA producer
     if (lane == 0) {
-      uint32_t it = 0;
-      bool ok = true;
-      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+      uint32_t it = 0, published = 0;
+      auto publish = [&](int t) -> bool {
+        const int slot = published % kSched;
+        const uint32_t ph = (published / kSched) & 1u;
+        ++published;
+        if (!mbar_wait(sempty_bar(slot), ph ^ 1u, abort_flag)) return false;
+        sched_tile[slot] = t;
+        mbar_arrive(sfull_bar(slot));   // release: the consumers' waits acquire
+        return true;
+      };
+      int tile = p.sched ? atomicAdd(p.sched, 1) : (int)blockIdx.x;
+      if (tile >= total_tiles) tile = -1;
+      bool ok = publish(tile);
+      while (ok && tile >= 0) {
+        // the next tile is drawn now and needed only after this tile's loads are issued
+        int next = p.sched ? atomicAdd(p.sched, 1) : tile + (int)gridDim.x;
         int mi, ni;
         tile_coords(tile, p.tiles_m, p.tiles_n, p.group_m, mi, ni);
         int m0 = mi * BM, n0 = ni * (GATE_UP ? BN / 2 : BN);
@@ -264,6 +306,19 @@ gemm_tc_kernel(const __grid_constant__ GemmMaps maps, const GemmParams p) {
             for (int j = 0; j < BN / 64; ++j) tma_load_2d(b_dst + j * (BK * 128), tmB, n0 + 64 * j, k0, full_bar(s));
           }
         }
+        if (!ok) break;
+        if (next >= total_tiles) next = -1;
+        ok = publish(next);
+        tile = next;
+      }
+      if (p.sched) {
+        // This CTA draws no more tiles. The last CTA of the grid to get here leaves the pair zeroed for the next launch.
+        __threadfence();
+        if (atomicAdd(p.sched + 1, 1) == (int)gridDim.x - 1) {
+          p.sched[0] = 0;
+          p.sched[1] = 0;
+          __threadfence();
+        }
       }
       // Do not leave the CTA while bulk copies may still be landing in its shared memory.
       const uint32_t pending = it < (uint32_t)C::STAGES ? it : (uint32_t)C::STAGES;
@@ -281,7 +336,7 @@ gemm_tc_kernel(const __grid_constant__ GemmMaps maps, const GemmParams p) {
       const uint32_t a_lbo = p.a_mn ? BK * 128 : 0, b_lbo = p.b_mn ? BK * 128 : 0;
       const uint32_t a_kadv = p.a_mn ? (UK * 128) >> 4 : (UK * 2) >> 4;  // descriptor units of 16 B
       const uint32_t b_kadv = p.b_mn ? (UK * 128) >> 4 : (UK * 2) >> 4;
-      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++tl) {
+      for (int tile = next_tile(false); tile >= 0 && ok; tile = next_tile(false), ++tl) {
         const int acc = tl & 1;
         const uint32_t aph = (tl >> 1) & 1u;
         if (!mbar_wait(tempty_bar(acc), aph ^ 1u, abort_flag)) { ok = false; break; }
@@ -312,7 +367,7 @@ gemm_tc_kernel(const __grid_constant__ GemmMaps maps, const GemmParams p) {
     const int q = warp & 3;  // TMEM lane quarter this warp may access
     uint32_t tl = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++tl) {
+    for (int tile = next_tile(true); tile >= 0 && ok; tile = next_tile(true), ++tl) {
       int mi, ni;
       tile_coords(tile, p.tiles_m, p.tiles_n, p.group_m, mi, ni);
       const int acc = tl & 1;
@@ -521,6 +576,43 @@ inline int pick_group_m(int tiles_m, int64_t K) {
   return (tiles_m >= kGroupMWide && wide_bytes <= (64ll << 20)) ? kGroupMWide : kGroupM;
 }
 
+// Tile hand-out policy: 1 = every CTA draws tiles from a device counter (default), 0 = static stride over the grid.
+// With the static stride a CTA that cannot become resident at once - its SM is held by a communication kernel of
+// another stream - keeps its whole share of tiles waiting, and the launch takes up to twice as long; drawn tiles go to
+// the CTAs that are running. Results do not depend on the policy: every tile is computed whole by one CTA.
+static std::atomic<int> g_tile_schedule{[] {
+  const char* e = getenv("Q3_GEMM_TILE_SCHEDULE");
+  return (e && !strcmp(e, "static")) ? 0 : 1;
+}()};
+constexpr unsigned kSchedPairs = 4096;
+
+// One zeroed {next tile, CTAs finished} pair for a launch on the current device, or nullptr (static policy). Pairs are
+// handed out round-robin; a pair is used again 4096 launches later, long after its launch zeroed it.
+inline int sched_pair(int** out) {
+  *out = nullptr;
+  if (!g_tile_schedule.load(std::memory_order_relaxed)) return Q3_OK;
+  static int* base[64] = {};
+  static std::mutex lock;
+  static std::atomic<unsigned> next{0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return Q3_ERR_CUDA;
+  int* b = __atomic_load_n(&base[dev], __ATOMIC_ACQUIRE);
+  if (!b) {
+    std::lock_guard<std::mutex> hold(lock);
+    b = base[dev];
+    if (!b) {
+      if (cudaMalloc(&b, kSchedPairs * 2 * sizeof(int)) != cudaSuccess) return Q3_ERR_CUDA;
+      if (cudaMemset(b, 0, kSchedPairs * 2 * sizeof(int)) != cudaSuccess || cudaDeviceSynchronize() != cudaSuccess) {
+        cudaFree(b);
+        return Q3_ERR_CUDA;
+      }
+      __atomic_store_n(&base[dev], b, __ATOMIC_RELEASE);
+    }
+  }
+  *out = b + 2 * (next.fetch_add(1, std::memory_order_relaxed) % kSchedPairs);
+  return Q3_OK;
+}
+
 template <int BN, typename TO, int EPI>
 int launch_gemm(const Operand& A, const Operand& B, const void* b2, GemmParams& p, bool bf16, cudaStream_t st) {
   constexpr bool GATE_UP = (EPI == EPI_GATE_UP);
@@ -557,6 +649,7 @@ int launch_gemm(const Operand& A, const Operand& B, const void* b2, GemmParams& 
   auto kern = gemm_tc_kernel<BN, TO, EPI>;
   static DeviceFlags configured = {};
   if (int rc2 = ensure_dynamic_smem(kern, C::SMEM_BYTES, &configured); rc2 != Q3_OK) return rc2;
+  if (int rc3 = sched_pair(&p.sched); rc3 != Q3_OK) return rc3;
   kern<<<grid, kGemmThreads, C::SMEM_BYTES, st>>>(maps, p);
   return launch_status();
 }
@@ -616,6 +709,7 @@ int launch_grouped(int mode, int count, const void* const* a, const void* const*
   auto kern = gemm_tc_kernel<BN, TO, EPI_STORE>;
   static DeviceFlags configured = {};
   if (int rc2 = ensure_dynamic_smem(kern, C::SMEM_BYTES, &configured); rc2 != Q3_OK) return rc2;
+  if (int rc3 = sched_pair(&p.sched); rc3 != Q3_OK) return rc3;
   kern<<<grid, kGemmThreads, C::SMEM_BYTES, st>>>(maps, p);
   return launch_status();
 }
@@ -862,4 +956,11 @@ extern "C" int q3_linear_ce_grad(const void* hidden, const void* weight_chunk, c
   cudaStream_t st = (cudaStream_t)stream;
   if (dtype == Q3_BF16) return tc::launch_gemm<256, __nv_bfloat16, tc::EPI_CE_GRAD>(A, B, nullptr, p, true, st);
   return tc::launch_gemm<256, __half, tc::EPI_CE_GRAD>(A, B, nullptr, p, false, st);
+}
+
+// 1: tiles drawn from a device counter (default), 0: static stride over the grid. Returns the previous policy;
+// any other value only queries. Q3_GEMM_TILE_SCHEDULE=static sets the initial policy.
+extern "C" int q3_gemm_tile_schedule(int mode) {
+  if (mode == 0 || mode == 1) return tc::g_tile_schedule.exchange(mode);
+  return tc::g_tile_schedule.load();
 }

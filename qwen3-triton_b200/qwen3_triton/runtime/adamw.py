@@ -125,10 +125,10 @@ class TritonAdamW(torch.optim.Optimizer):
             raise ValueError('Invalid local FP32 AdamW state')
         return m, v, step
 
-    def _rows_of(self, group):
+    def _rows_of(self, parameters):
         """(table rows, total blocks, device, tensors the kernel will modify) for the parameters that have a gradient."""
         rows, touched, blocks, device = [], [], 0, None
-        for parameter in group['params']:
+        for parameter in parameters:
             low_g = getattr(parameter, 'q3_lowp_grad', None)      # set by runtime/mixed_precision.py
             low_p = getattr(parameter, 'q3_lowp_copy', None)
             if parameter.grad is None and low_g is None:
@@ -159,14 +159,45 @@ class TritonAdamW(torch.optim.Optimizer):
 
     def _device_table(self, index, rows, columns, device):
         """Pointer table and per-tensor coefficient scratch on the device; rebuilt only when a pointer changed
-        (gradients re-allocated), since uploading it costs a synchronising copy."""
+        (gradients re-allocated). The upload goes through a pinned buffer and is asynchronous on the launching
+        stream, so that a changed pointer never stalls the host behind that stream's queued work."""
         key = tuple(r[:columns] for r in rows)
         cached = self._tables.get(index)
-        if cached is None or cached[0] != key:
-            meta = torch.tensor(key, dtype=torch.int64).to(device)
-            coeff = torch.empty((len(rows), 3), device=device, dtype=torch.float32)
-            cached = self._tables[index] = (key, meta, coeff)
-        return cached[1], cached[2]
+        if cached is None or cached['key'] != key:
+            if cached is None or cached['meta'].shape != (len(rows), columns):
+                cached = self._tables[index] = dict(
+                    host=torch.empty((len(rows), columns), dtype=torch.int64, pin_memory=True),
+                    meta=torch.empty((len(rows), columns), dtype=torch.int64, device=device),
+                    coeff=torch.empty((len(rows), 3), device=device, dtype=torch.float32), uploaded=None)
+            if cached['uploaded'] is not None:
+                cached['uploaded'].synchronize()           # the previous upload has long finished reading `host`
+            cached['host'].copy_(torch.tensor(key, dtype=torch.int64))
+            cached['meta'].copy_(cached['host'], non_blocking=True)
+            cached['uploaded'] = torch.cuda.Event()
+            cached['uploaded'].record()
+            cached['key'] = key
+        return cached['meta'], cached['coeff']
+
+    def _launch(self, index, group, parameters):
+        """One kernel launch on the current stream over those of `parameters` that have a gradient."""
+        rows, blocks, device, touched = self._rows_of(parameters)
+        if not rows:
+            return
+        low_dtypes = {r.lowp_dtype for r in rows if r.lowp_dtype}
+        if len(low_dtypes) > 1:
+            raise ValueError('One low-precision dtype per group')
+        beta1, beta2 = group['betas']
+        scalars = (float(group['lr']), float(beta1), float(beta2), float(group['weight_decay']), float(group['eps']))
+        if low_dtypes:
+            meta, coeff = self._device_table(index, rows, 9, device)
+            every_row_both = int(all(r.lowp_grad and r.lowp_copy for r in rows))
+            _abi.call('q3_adamw_multi_mp', meta.data_ptr(), coeff.data_ptr(), len(rows), blocks, self.block,
+                      low_dtypes.pop(), every_row_both, *scalars, _abi.stream())
+        else:
+            meta, coeff = self._device_table(index, rows, 7, device)
+            _abi.call('q3_adamw_multi', meta.data_ptr(), coeff.data_ptr(), len(rows), blocks, self.block, *scalars,
+                      _abi.stream())
+        torch.autograd.graph.increment_version(touched)
 
     @torch.no_grad()
     def step(self, closure=None):
@@ -177,26 +208,106 @@ class TritonAdamW(torch.optim.Optimizer):
         if getattr(self, 'grad_scale', None) is not None or getattr(self, 'found_inf', None) is not None:
             raise ValueError('GradScaler is not supported by this explicit BF16/FP32 path')
         for index, group in enumerate(self.param_groups):
-            rows, blocks, device, touched = self._rows_of(group)
-            if not rows:
-                continue
-            low_dtypes = {r.lowp_dtype for r in rows if r.lowp_dtype}
-            if len(low_dtypes) > 1:
-                raise ValueError('One low-precision dtype per group')
-            beta1, beta2 = group['betas']
-            scalars = (float(group['lr']), float(beta1), float(beta2), float(group['weight_decay']), float(group['eps']))
-            if low_dtypes:
-                meta, coeff = self._device_table(index, rows, 9, device)
-                every_row_both = int(all(r.lowp_grad and r.lowp_copy for r in rows))
-                _abi.call('q3_adamw_multi_mp', meta.data_ptr(), coeff.data_ptr(), len(rows), blocks, self.block,
-                          low_dtypes.pop(), every_row_both, *scalars, _abi.stream())
-            else:
-                meta, coeff = self._device_table(index, rows, 7, device)
-                _abi.call('q3_adamw_multi', meta.data_ptr(), coeff.data_ptr(), len(rows), blocks, self.block, *scalars,
-                          _abi.stream())
-            torch.autograd.graph.increment_version(touched)
+            self._launch(index, group, group['params'])
+        early = getattr(self, '_early', None)
+        if early is not None:
+            early.join()
         self.kernel_steps += 1
         return loss
+
+    # ------------------------------------------------------------------------------ update during backward
+    def step_during_backward(self, buckets, gradient_of=None):
+        """Update each bucket of parameters on a side stream as soon as the backward pass has produced the bucket's
+        last gradient, so that the update (bound by HBM bandwidth) runs beside the remaining backward GEMMs (bound by
+        the tensor cores) instead of after them. `step()` then updates whatever is left (parameters in no bucket, or
+        a bucket the backward pass did not complete) and makes the current stream wait for the side stream.
+
+        `buckets`: lists of this optimizer's parameters, e.g. one per decoder layer; every member must get a
+        gradient in every backward pass. `gradient_of(parameter)` returns the tensor whose `.grad` autograd fills for
+        that parameter (the bf16 working copy under runtime/mixed_precision.py; default: the parameter itself) -
+        when it is another tensor, its gradient is handed over as the parameter's `q3_lowp_grad` and cleared.
+
+        The result is the one `step()` alone gives: per-parameter step counters live on the device, the kernel is
+        elementwise, and a bucket is launched only after its last gradient is complete. Do not use with gradient
+        accumulation over several backward passes or with gradient clipping (both need all gradients first);
+        `early.enabled = False` on the returned object suspends it. The reference steps after backward only
+        (qwen3_triton/runtime/adamw.py:117-159)."""
+        if getattr(self, '_early', None) is not None:
+            raise ValueError('step_during_backward was already set up')
+        self._early = _EarlySteps(self, buckets, gradient_of or (lambda parameter: parameter))
+        return self._early
+
+
+class _EarlySteps:
+    def __init__(self, optimizer, buckets, gradient_of):
+        self.optimizer = optimizer
+        self.enabled = True
+        self.stream = None
+        self.launched = 0
+        self.handles = []
+        group_of = {id(p): (i, g) for i, g in enumerate(optimizer.param_groups) for p in g['params']}
+        seen = set()
+        for number, bucket in enumerate(buckets):
+            bucket = list(bucket)
+            if not bucket:
+                continue
+            groups = {group_of[id(p)][0] if id(p) in group_of else None for p in bucket}
+            if None in groups or len(groups) != 1:
+                raise ValueError('A bucket holds parameters of one parameter group of this optimizer')
+            if any(id(p) in seen for p in bucket):
+                raise ValueError('A parameter belongs to one bucket')
+            seen.update(id(p) for p in bucket)
+            index, group = group_of[id(bucket[0])]
+            state = dict(parameters=bucket, sources=[gradient_of(p) for p in bucket], waiting=len(bucket), group=group,
+                         key=('early', number, index))
+            for source in state['sources']:
+                if not source.requires_grad:
+                    raise ValueError('Every member of a bucket must receive a gradient')
+                self.handles.append(source.register_post_accumulate_grad_hook(self._hook(state)))
+
+    def _hook(self, state):
+        def fire(_):
+            if not self.enabled:
+                return
+            state['waiting'] -= 1
+            if state['waiting'] == 0:
+                state['waiting'] = len(state['parameters'])
+                self._launch(state)
+        return fire
+
+    @torch.no_grad()
+    def _launch(self, state):
+        current = torch.cuda.current_stream()
+        if self.stream is None or self.stream.device != current.device:
+            self.stream = torch.cuda.Stream(device=current.device)
+        for parameter, source in zip(state['parameters'], state['sources']):
+            if source is not parameter:
+                gradient = source.grad
+                parameter.q3_lowp_grad = gradient if gradient.is_contiguous() else gradient.contiguous()
+                source.grad = None
+        self.stream.wait_stream(current)            # every gradient of the bucket was produced by work queued so far
+        with torch.cuda.stream(self.stream):
+            self.optimizer._launch(state['key'], state['group'], state['parameters'])
+        for parameter, source in zip(state['parameters'], state['sources']):
+            # the side stream still reads the gradient: keep its memory from being handed out before that
+            if source is not parameter:
+                parameter.q3_lowp_grad.record_stream(self.stream)
+                parameter.q3_lowp_grad = None
+            elif parameter.grad is not None:
+                local(parameter.grad).record_stream(self.stream)
+                parameter.grad = None
+        self.launched += 1
+
+    def join(self):
+        if self.stream is not None:
+            torch.cuda.current_stream(self.stream.device).wait_stream(self.stream)
+
+    def remove(self):
+        for handle in self.handles:
+            handle.remove()
+        self.handles = []
+        self.join()
+        self.optimizer._early = None
 
 
 AdamW = TritonAdamW

@@ -93,14 +93,16 @@ def configure(model, communication, *, pack_kernels=True, pack_gradients_off_com
     `pack_gradients_off_compute_stream`: run the reduce-scatter copy-in on FSDP's reduce-scatter stream.
     `peer_memory_reduce`: reduce gradients with the pull kernel over peer memory (runtime/peer_reduce.py; one node,
     2 / 4 / 8 ranks, implies the copy-in on the reduce-scatter stream); the returned dict holds the reducer under
-    'peer_reducer' - call its close() before the process group is destroyed."""
+    'peer_reducer' - call its close() before the process group is destroyed. If any rank cannot allocate or map
+    the staging buffers, every rank falls back to the collective backend and 'peer_reducer' is None."""
     reducer = None
     if peer_memory_reduce:
         if not pack_kernels:
             raise ValueError('peer_memory_reduce needs the pack kernels')
         from .peer_reduce import PeerGradientReducer
         device = torch.device('cuda', torch.cuda.current_device())
-        reducer = PeerGradientReducer(communication.group, device, largest_unit_elements(model, communication.world))
+        reducer = PeerGradientReducer.create(communication.group, device,
+                                             largest_unit_elements(model, communication.world))
     if pack_kernels:
         from .ops import (install_fsdp_pack_kernels, pack_gradients_on_reduce_scatter_stream,
                           reduce_gradients_over_peer_memory)

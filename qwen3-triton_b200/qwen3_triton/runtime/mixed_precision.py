@@ -49,6 +49,17 @@ class MasterWeights:
     def parameters(self):
         return self.masters
 
+    def masters_of(self, module):
+        """The fp32 masters of `module`'s (working) parameters, in `module.parameters()` order."""
+        master_of = {id(w): m for m, w in zip(self.masters, self.working)}
+        return [master_of[id(w)] for w in module.parameters() if id(w) in master_of]
+
+    def working_of(self, master):
+        """The working copy autograd fills the gradient of (TritonAdamW.step_during_backward's `gradient_of`)."""
+        if not hasattr(self, '_working_of'):
+            self._working_of = {id(m): w for m, w in zip(self.masters, self.working)}
+        return self._working_of[id(master)]
+
     def release_grads(self):
         """Drop the low-precision gradients handed to the optimizer (call after optimizer.step()): otherwise they stay
         alive through the next backward, next to the new ones."""

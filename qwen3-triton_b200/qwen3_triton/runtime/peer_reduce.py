@@ -27,8 +27,22 @@ from .. import _abi
 class PeerGradientReducer:
     SLOTS = 2
 
+    @classmethod
+    def create(cls, group, device, capacity_elements):
+        """A reducer, or None on every rank when some rank could not allocate or map the staging buffers (ranks on
+        different nodes, peer access unavailable): the callers then stay on the collective backend."""
+        try:
+            reducer = cls(group, device, capacity_elements)
+        except (RuntimeError, ValueError) as error:
+            import warnings
+            warnings.warn('peer-memory gradient reduction unavailable: %s' % error)
+            reducer = None
+        return reducer if reducer is not None and reducer.usable else None
+
     def __init__(self, group, device, capacity_elements):
-        """`capacity_elements`: the largest number of (padded) gradient elements one FSDP unit hands over."""
+        """`capacity_elements`: the largest number of (padded) gradient elements one FSDP unit hands over. Collective:
+        every rank of `group` takes part in the handle exchange even if its own allocation failed; `usable` is the
+        same on all ranks afterwards."""
         self.group, self.device = group, torch.device(device)
         self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
         if self.world not in (2, 4, 8):
@@ -36,28 +50,38 @@ class PeerGradientReducer:
         self.capacity = (int(capacity_elements) + 8 * self.world - 1) // (8 * self.world) * (8 * self.world)
         lib = _abi.lib()
         self.own, self.peers, self.tables = [], [], []
+        failure = None
         with torch.cuda.device(self.device):
             for _ in range(self.SLOTS):
                 ptr, handle = ctypes.c_void_p(), ctypes.create_string_buffer(64)
-                _abi.check(lib.q3_peer_alloc(self.capacity * 2, ctypes.byref(ptr), handle), 'q3_peer_alloc')
+                if failure is None and lib.q3_peer_alloc(self.capacity * 2, ctypes.byref(ptr), handle) != 0:
+                    failure = 'allocation'
                 handles = [None] * self.world
-                dist.all_gather_object(handles, handle.raw, group=group)
+                dist.all_gather_object(handles, handle.raw if failure is None else None, group=group)
                 mapped = []
                 for r in range(self.world):
                     if r == self.rank:
                         mapped.append(ptr.value)
                         continue
                     peer = ctypes.c_void_p()
-                    _abi.check(lib.q3_peer_open(handles[r], ctypes.byref(peer)), 'q3_peer_open')
+                    if failure is None and (handles[r] is None or lib.q3_peer_open(handles[r], ctypes.byref(peer)) != 0):
+                        failure = 'mapping the buffer of rank %d' % r
                     mapped.append(peer.value)
                 self.own.append(ptr.value)
                 self.peers.append(mapped)
-                self.tables.append((ctypes.c_void_p * self.world)(*mapped))
+                self.tables.append((ctypes.c_void_p * self.world)(*[m or 0 for m in mapped]))
+        verdicts = [None] * self.world
+        dist.all_gather_object(verdicts, failure, group=group)
+        self.usable = all(v is None for v in verdicts)
+        self.closed = False
+        if not self.usable:
+            self.flag = None
+            self.close()
+            return
         self.flag = torch.zeros(1, device=self.device)
         self.next_slot = 0
         self.pending = {}           # data_ptr of FSDP's fp32 reduce-scatter input -> (slot, columns, dtype)
         self.units = 0
-        self.closed = False
 
     # -- called from the chunk_cat override, on the reduce-scatter stream
     def stage(self, tensors, out, launch, plan):
@@ -95,10 +119,11 @@ class PeerGradientReducer:
         dist.barrier(group=self.group)                        # nobody unmaps while a peer may still be reading
         lib = _abi.lib()
         with torch.cuda.device(self.device):
-            for slot in range(self.SLOTS):
+            for slot in range(len(self.peers)):
                 for r, address in enumerate(self.peers[slot]):
-                    if r != self.rank:
+                    if r != self.rank and address:
                         lib.q3_peer_close(ctypes.c_void_p(address))
             dist.barrier(group=self.group)
             for address in self.own:
-                lib.q3_peer_free(ctypes.c_void_p(address))
+                if address:
+                    lib.q3_peer_free(ctypes.c_void_p(address))

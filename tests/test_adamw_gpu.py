@@ -118,3 +118,61 @@ def test_mixed_precision_fusion_is_bit_identical_to_separate_cast_passes():
     for ma, mb, wa, wb in zip(mw_a.masters, mw_b.masters, mw_a.working, mw_b.working):
         assert torch.equal(ma, mb), float((ma - mb).abs().max())
         assert torch.equal(wa, wb) and wb.dtype == torch.bfloat16, float((wa.float() - wb.float()).abs().max())
+
+
+@pytest.mark.parametrize('mixed', [True, False])
+def test_updates_during_backward_equal_a_step_after_backward(mixed):
+    """Buckets updated on a side stream as soon as their last gradient exists, the rest by step(): bit-identical
+    parameters, moments and step counters to updating everything after backward - with bf16 working copies
+    (gradients handed over from the working copies) and with plain fp32 parameters."""
+    from qwen3_triton.runtime.adamw import TritonAdamW
+    from qwen3_triton.runtime.mixed_precision import MasterWeights
+
+    def build(early):
+        torch.manual_seed(11)
+        blocks = [torch.nn.Sequential(torch.nn.Linear(256, 384, bias=False), torch.nn.Linear(384, 256, bias=False))
+                  for _ in range(3)]
+        net = torch.nn.Sequential(*blocks, torch.nn.Linear(256, 32, bias=False)).cuda()
+        if mixed:
+            mw = MasterWeights(net).fuse_into_optimizer()
+            opt = TritonAdamW(mw.parameters(), **HYPER)
+            if early:
+                handle = opt.step_during_backward([mw.masters_of(b) for b in blocks], mw.working_of)
+        else:
+            mw = None
+            opt = TritonAdamW(net.parameters(), **HYPER)
+            if early:
+                handle = opt.step_during_backward([list(b.parameters()) for b in blocks])
+        return net, mw, opt, (handle if early else None)
+
+    def run(early):
+        net, mw, opt, handle = build(early)
+        g = torch.Generator().manual_seed(12)
+        for _ in range(4):
+            x = torch.randn(64, 256, generator=g).cuda()
+            if mixed:
+                mw.sync_working()
+                net(x.to(torch.bfloat16)).float().square().mean().backward()
+                mw.collect_grads()
+                opt.step()
+                mw.release_grads()
+            else:
+                net(x).square().mean().backward()
+                opt.step()
+                opt.zero_grad(set_to_none=True)
+        torch.cuda.synchronize()
+        if early:
+            assert handle.launched == 4 * 3
+        params = mw.masters if mixed else list(net.parameters())
+        state = [(opt.state[p]['step'].clone(), opt.state[p]['exp_avg'].clone(), opt.state[p]['exp_avg_sq'].clone())
+                 for p in params]
+        return [p.detach().clone() for p in params], state, ([w.detach().clone() for w in mw.working] if mixed else [])
+
+    late, early = run(False), run(True)
+    for a, b in zip(late[0], early[0]):
+        assert torch.equal(a, b)
+    for sa, sb in zip(late[1], early[1]):
+        assert all(torch.equal(x, y) for x, y in zip(sa, sb))
+        assert float(sa[0]) == 4.0
+    for a, b in zip(late[2], early[2]):
+        assert torch.equal(a, b)

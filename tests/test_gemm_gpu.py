@@ -54,6 +54,29 @@ def test_fp32_output_and_determinism():
     assert torch.equal(c, matmul(a, b, output_dtype=torch.float32))
 
 
+@pytest.mark.parametrize('M,N,K', [(128, 256, 64), (2048, 12288, 4096), (4096, 4096, 12288), (300, 1000, 520)])
+def test_tile_hand_out_policies_agree_bit_for_bit(M, N, K):
+    """Tiles drawn from the device counter (default) or taken with a fixed stride: every tile is computed whole by
+    one CTA, so the result cannot depend on the policy; and the counters must come back to zero, launch after launch
+    (forty launches in a row, then a different grid size)."""
+    from qwen3_triton import _abi
+    from qwen3_triton.kernels.linear import matmul
+    a, b = randn((M, K), 11, torch.bfloat16).cuda(), randn((K, N), 12, torch.bfloat16).cuda()
+    assert _abi.lib().q3_gemm_tile_schedule(-1) == 1
+    drawn = [matmul(a, b) for _ in range(40)]
+    small = matmul(a[:128], b)
+    previous = _abi.lib().q3_gemm_tile_schedule(0)
+    try:
+        assert previous == 1
+        strided, small_strided = matmul(a, b), matmul(a[:128], b)
+    finally:
+        _abi.lib().q3_gemm_tile_schedule(previous)
+    assert all(torch.equal(d, strided) for d in drawn)
+    assert torch.equal(small, small_strided)
+    close(strided, ref_mm(a, b).to(torch.bfloat16), scale=K ** 0.5, what='A*B')
+    assert _abi.read_status() == 0
+
+
 @pytest.mark.parametrize('dtype', [torch.bfloat16, torch.float16])
 @pytest.mark.parametrize('M,K,sizes', [(2048, 4096, (4096, 1024, 1024)), (300, 520, (192, 64, 320)), (129, 136, (448, 64)),
                                        (2048, 1024, (3072, 3072)), (2048, 4096, (12288, 12288)),
