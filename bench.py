@@ -350,7 +350,7 @@ def build_single_gpu(cfg, device):
         model.fused_loss = os.environ.get("Q3_BENCH_FUSED_LOSS", "1") == "1"
     masters = MasterWeights(model).fuse_into_optimizer()
     opt = TritonAdamW(masters.parameters(), lr=1e-4, betas=(0.9, 0.95), weight_decay=0.1, block=16384)
-    if os.environ.get("Q3_BENCH_EARLY_ADAMW", "1") == "1":
+    if os.environ.get("Q3_BENCH_EARLY_ADAMW", "0") == "1":
         # each decoder layer is updated on a side stream as soon as its backward is complete, beside the GEMMs of the
         # layers below it; embedding, final norm and head are updated by opt.step()
         opt.step_during_backward([masters.masters_of(layer) for layer in model.model.layers], masters.working_of)
@@ -451,6 +451,9 @@ def run_ours(args):
                    "global_batch": batch, "seq_len": seq, "parallelism": "single",
                    "l2": "inputs+weights >> L2 (%d GB bf16 weights)" % (16 if layers == 36 else 4),
                    "loss_head": "no logits in memory" if getattr(model, "fused_loss", False) else "materialised logits",
+                   "adamw": ("decoder layers updated during backward on a side stream (%d bucket launches so far), "
+                             "embedding / final norm / head after backward" % opt._early.launched
+                             if getattr(opt, "_early", None) is not None else "after backward"),
                    "mfu_of_%s_peak" % peak_kind: mfu, "last_loss": last, "device_status": status,
                    "peak_memory_gb": round(torch.cuda.max_memory_allocated() / 2 ** 30, 1)},
         "e2e": {"value": tokens / (e2e_ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": batch * seq * 8,
@@ -613,6 +616,14 @@ def run_fsdp(args):
         del yard, named
         opt.zero_grad(set_to_none=True)
 
+    early_adamw = os.environ.get("Q3_BENCH_EARLY_ADAMW", "0") == "1"
+    if early_adamw:
+        # the shards of the units reduced so far (and the head's weight) are updated on the reduce-scatter stream at
+        # the next unit's reduce-scatter, beside the backward pass of the units still to come; opt.step() does the rest
+        eligible = frozenset(id(p) for n, p in model.named_parameters()
+                             if n.startswith("model.layers.") or n.startswith("lm_head."))
+        hooks["reduce_scatter"].before_reduce = lambda: opt.step_pending(eligible)
+
     def timed(policy, steps, warmup):
         set_policy(policy)
         for i in range(warmup):
@@ -701,6 +712,8 @@ def run_fsdp(args):
                                                             (tokens / world / (v * 1e-3)) * flops_tok / (peak_tf * 1e12),
                                                         "steps": short} for p, v in others.items()},
                        "peak_memory_gb_rank0": peak_memory, "nccl_max_ctas": max_ctas or "default",
+                       "adamw": ("shards of reduced units updated during backward on the reduce-scatter stream, "
+                                 "the rest after backward" if early_adamw else "after backward"),
                        "gradient_reduce": ("pull kernel over peer memory, bf16 on the links, fp32 sums in rank order "
                                            "(%d of %d reduce-scatter calls)" % (hooks["reduce_scatter"].peer_calls,
                                                                                 hooks["reduce_scatter"].calls)

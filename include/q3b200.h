@@ -388,6 +388,14 @@ int q3_attn_bwd_group_policy(int policy);
  * The first GEMM call on a device allocates and zeroes the counters (32 KB): make it outside stream capture. */
 int q3_gemm_tile_schedule(int mode);
 
+/* Where an output has at least two 128-row tiles, the GEMM kernels run as pairs of CTAs (clusters of 2, tcgen05
+ * cta_group::2): the pair shares one 256 x 256 tile, each CTA stages its own 128 rows of A and half of B's rows, the
+ * MMAs read both CTAs' shared memory. A CTA then brings 32 KB per k-block into shared memory instead of 48 KB for the
+ * same tensor work - the single-CTA form is limited by that traffic to about 80 % of the tensor rate. No multicast
+ * loads are involved. 1 = pairs (default; tiles then go to the pairs with a fixed stride), 0 = single CTAs everywhere.
+ * Returns the previous policy (any other argument only queries); process-wide; results are bit-identical. */
+int q3_gemm_cta_pairs(int mode);
+
 /* ---- token-block data path and validation statistics ---------------------------------------- */
 
 /* out[i] = training ? ((first + i + offset) * stride + seed) mod n : first + i, for i in [0, count): the order in

@@ -221,6 +221,22 @@ def main():
                 report("gemm_q_dgrad", timer(lambda: matmul(dy, Bm)), flops=2.0 * M * N * K)
                 report("gemm_q_wgrad", timer(lambda: matmul(dy.t(), A)), flops=2.0 * M * N * K)
             del A, Bm
+    if want("step_gemm_vs_library"):
+        # The step's GEMM shapes at 2048 tokens per GPU in the three layouts of a linear layer, this library's kernel
+        # beside the vendor library's (torch.matmul -> cuBLASLt) on the same tensors: what part of the distance to the
+        # peak belongs to the shapes (16 row tiles, 1.73-wave schedules) and what part to the kernel.
+        tok = 2048
+        for label, n, k in (("qkv", 6144, 4096), ("o", 4096, 4096), ("gate|up", 24576, 4096), ("down", 4096, 12288)):
+            xa = torch.randn(tok, k, device=dev).to(bf)
+            wa = (torch.randn(n, k, device=dev) * 0.02).to(bf)
+            dya = torch.randn(tok, n, device=dev).to(bf)
+            fl = 2.0 * tok * n * k
+            for form, ours, theirs in (("fwd  X W^T", lambda: matmul(xa, wa.t()), lambda: torch.matmul(xa, wa.t())),
+                                       ("dgrad dY W", lambda: matmul(dya, wa), lambda: torch.matmul(dya, wa)),
+                                       ("wgrad dY^T X", lambda: matmul(dya.t(), xa), lambda: torch.matmul(dya.t(), xa))):
+                report("%s %s (this library)" % (label, form), timer(ours), flops=fl)
+                report("%s %s (cuBLASLt)" % (label, form), timer(theirs), flops=fl)
+            del xa, wa, dya
     if want("linear_ce"):
         from qwen3_triton.kernels.fused_loss import fused_linear_cross_entropy
         S = min(4096, T)

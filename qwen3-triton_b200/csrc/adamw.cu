@@ -104,8 +104,10 @@ template <typename L, bool BOTH>
 __global__ void __launch_bounds__(256, BOTH ? 5 : 4) adamw_update_mp_kernel(const int64_t* __restrict__ meta,
                                                               const float* __restrict__ coeff, int64_t rows, double lr,
                                                               double b1, double b2, double decay, double eps,
-                                                              int block_elems) {
-  const int64_t blk = blockIdx.x;
+                                                              int block_elems, int64_t total_blocks) {
+  // one block per CTA when the grid covers them all; a smaller grid (an update that runs beside compute kernels and
+  // must leave them most of the memory bandwidth) strides over the blocks
+  for (int64_t blk = blockIdx.x; blk < total_blocks; blk += gridDim.x) {
   int64_t lo = 0, hi = rows;
   while (lo + 1 < hi) {
     const int64_t mid = (lo + hi) >> 1;
@@ -164,6 +166,7 @@ __global__ void __launch_bounds__(256, BOTH ? 5 : 4) adamw_update_mp_kernel(cons
       if (plo) plo[i] = from_f32<L>(pp);
     }
   }
+  }
 }
 
 __global__ void adamw_prepare9_kernel(const int64_t* __restrict__ meta, float* __restrict__ coeff, int64_t rows,
@@ -192,9 +195,11 @@ extern "C" int q3_adamw_multi_mp(const int64_t* meta, float* coeff, int64_t n_te
   if (lowp_dtype != Q3_BF16 && lowp_dtype != Q3_F16) return Q3_ERR_DTYPE;
   cudaStream_t st = (cudaStream_t)stream;
   adamw_prepare9_kernel<<<(int)cdiv(n_tensors, 128), 128, 0, st>>>(meta, coeff, n_tensors, lr, beta1, beta2);
-#define Q3_MP(L, BOTH)                                                                                              \
-  adamw_update_mp_kernel<L, BOTH><<<(unsigned)total_blocks, 256, 0, st>>>(meta, coeff, n_tensors, lr, beta1, beta2, \
-                                                                           weight_decay, eps, block_elems)
+  static const int cap = [] { const char* e = getenv("Q3_ADAMW_CTAS"); return e ? atoi(e) : 0; }();
+  const unsigned grid = (unsigned)((cap > 0 && cap < total_blocks) ? cap : total_blocks);
+#define Q3_MP(L, BOTH)                                                                                    \
+  adamw_update_mp_kernel<L, BOTH><<<grid, 256, 0, st>>>(meta, coeff, n_tensors, lr, beta1, beta2, \
+                                                        weight_decay, eps, block_elems, total_blocks)
   if (lowp_dtype == Q3_BF16) { if (all_rows_lowp) Q3_MP(__nv_bfloat16, true); else Q3_MP(__nv_bfloat16, false); }
   else { if (all_rows_lowp) Q3_MP(__half, true); else Q3_MP(__half, false); }
 #undef Q3_MP

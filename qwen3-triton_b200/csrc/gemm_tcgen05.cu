@@ -89,11 +89,15 @@ __device__ __forceinline__ int seg_of(const GemmParams& p, int idx, int& start) 
   return seg;
 }
 
-template <int BN> struct Cfg {
+// PAIR: two CTAs (a cluster of 2) share one 256 x BN output tile. Each stages its own 128 rows of A and half of the B
+// rows, so a CTA moves 32 KB per k-block from L2 into shared memory instead of 48 KB for the same 128 x 256 x 64 of
+// MMA work: the single-CTA kernel is bound by that traffic at about 80 % of the tensor rate.
+template <int BN, bool PAIR = false> struct Cfg {
   static constexpr int A_BYTES = BM * BK * 2;
-  static constexpr int B_BYTES = BN * BK * 2;
+  static constexpr int B_ROWS = PAIR ? BN / 2 : BN;   // rows of the B tile staged by this CTA
+  static constexpr int B_BYTES = B_ROWS * BK * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr int STAGES = (BN == 256) ? 4 : 6;
+  static constexpr int STAGES = PAIR ? 6 : ((BN == 256) ? 4 : 6);
   static constexpr int TMEM_COLS = 2 * BN;  // two accumulators
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
 };
@@ -158,11 +162,15 @@ __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, 
 //   EPI_SWIGLU_BWD  A*B is dY of y = silu(G)*U, rounded to TO as the stored dY would be; stores dG and dU, never dY
 enum { EPI_STORE = 0, EPI_GATE_UP = 1, EPI_ACC_F32 = 2, EPI_CE_STATS = 3, EPI_CE_GRAD = 4, EPI_SWIGLU_BWD = 5 };
 
-template <int BN, typename TO, int EPI>
+template <int BN, typename TO, int EPI, bool PAIR = false>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tc_kernel(const __grid_constant__ GemmMaps maps, const GemmParams p) {
   constexpr bool GATE_UP = (EPI == EPI_GATE_UP);
-  using C = Cfg<BN>;
+  static_assert(!PAIR || BN == 256, "CTA pairs use the 256-column tile");
+  using C = Cfg<BN, PAIR>;
+  // PAIR: rank 0 of the cluster issues the MMAs and owns the barriers both CTAs report to (full, tempty)
+  const uint32_t rank = PAIR ? cluster_ctarank() : 0u;
+  const bool leader = rank == 0;
   extern __shared__ uint8_t smem_raw[];
   // 1024-byte alignment keeps the 128-byte swizzle phase identical for TMA and UMMA.
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -184,7 +192,17 @@ gemm_tc_kernel(const __grid_constant__ GemmMaps maps, const GemmParams p) {
   volatile int* sched_tile = reinterpret_cast<volatile int*>(bars + 2 * C::STAGES + 6 + 2 * kSched);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int total_tiles = p.tiles_m * p.tiles_n;
+  // PAIR: a tile is 256 rows (two consecutive 128-row tiles, one per CTA); tiles are handed out per pair, statically
+  const int tiles_m_sched = PAIR ? (p.tiles_m + 1) / 2 : p.tiles_m;
+  const int group_m_sched = PAIR ? (p.group_m + 1) / 2 : p.group_m;
+  const int total_tiles = tiles_m_sched * p.tiles_n;
+  const int first_static = PAIR ? (int)cluster_id_x() : (int)blockIdx.x;
+  const int stride_static = PAIR ? (int)cluster_count_x() : (int)gridDim.x;
+  // this CTA's 128-row tile and the N tile of a scheduled tile
+  auto coords_of = [&](int tile, int& mi, int& ni) {
+    tile_coords(tile, tiles_m_sched, p.tiles_n, group_m_sched, mi, ni);
+    if (PAIR) mi = 2 * mi + (int)rank;
+  };
   // Consumer side of the tile queue (MMA issuer: one thread; epilogue: whole warps, lane 0 releases the slot).
   // Returns the tile, -1 after the last one, -2 when a wait gave up.
   uint32_t taken = 0;
@@ -199,10 +217,15 @@ gemm_tc_kernel(const __grid_constant__ GemmMaps maps, const GemmParams p) {
     return t;
   };
 
+  // The producer thread draws its first tile before anything else: the counter's round trip to L2 runs beside the
+  // barrier set-up, the tensor-memory allocation and the CTA-wide sync below.
+  int first_tile = first_static;
+  if (!PAIR && threadIdx.x == 0 && p.sched) first_tile = atomicAdd(p.sched, 1);
   if (threadIdx.x == 0) {
     *abort_flag = 0;
     for (int s = 0; s < C::STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
-    for (int a = 0; a < 2; ++a) { mbar_init(tfull_bar(a), 1); mbar_init(tempty_bar(a), 4); }
+    // tempty: the four epilogue warps of every CTA that holds rows of the accumulator
+    for (int a = 0; a < 2; ++a) { mbar_init(tfull_bar(a), 1); mbar_init(tempty_bar(a), PAIR ? 8 : 4); }
     mbar_init(done_bar, 1);
     for (int i = 0; i < kSched; ++i) { mbar_init(sfull_bar(i), 1); mbar_init(sempty_bar(i), 5); }   // MMA + 4 warps
     fence_barrier_init();
@@ -211,11 +234,17 @@ gemm_tc_kernel(const __grid_constant__ GemmMaps maps, const GemmParams p) {
     if (GATE_UP) prefetch_tmap(&maps.b[1]);
   }
   if (warp == 1) {
-    tmem_alloc(smem_u32(tmem_slot), C::TMEM_COLS);
-    tmem_relinquish();
+    if (PAIR) {
+      tmem_alloc_pair(smem_u32(tmem_slot), C::TMEM_COLS);
+      tmem_relinquish_pair();
+    } else {
+      tmem_alloc(smem_u32(tmem_slot), C::TMEM_COLS);
+      tmem_relinquish();
+    }
   }
   tc_fence_before();
   __syncthreads();
+  if (PAIR) cluster_sync_all();   // the peer's barriers exist before anything is signalled across the pair
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
@@ -232,14 +261,17 @@ gemm_tc_kernel(const __grid_constant__ GemmMaps maps, const GemmParams p) {
         mbar_arrive(sfull_bar(slot));   // release: the consumers' waits acquire
         return true;
       };
-      int tile = p.sched ? atomicAdd(p.sched, 1) : (int)blockIdx.x;
+      int tile = first_tile;
       if (tile >= total_tiles) tile = -1;
       bool ok = publish(tile);
+      const bool draw = !PAIR && p.sched != nullptr;
+      // PAIR: both CTAs' loads are counted on the rank-0 CTA's full barriers
+      const uint32_t full0 = PAIR ? mapa_u32(full_bar(0), 0) : full_bar(0);
       while (ok && tile >= 0) {
         // the next tile is drawn now and needed only after this tile's loads are issued
-        int next = p.sched ? atomicAdd(p.sched, 1) : tile + (int)gridDim.x;
+        int next = draw ? atomicAdd(p.sched, 1) : tile + stride_static;
         int mi, ni;
-        tile_coords(tile, p.tiles_m, p.tiles_n, p.group_m, mi, ni);
+        coords_of(tile, mi, ni);
         int m0 = mi * BM, n0 = ni * (GATE_UP ? BN / 2 : BN);
         const CUtensorMap* tmA = &maps.a[0];
         const CUtensorMap* tmB = &maps.b[0];
@@ -281,7 +313,8 @@ gemm_tc_kernel(const __grid_constant__ GemmMaps maps, const GemmParams p) {
           if (p.prefetch && kb + kPrefetch < p.kblocks) prefetch(kb + kPrefetch);
           if (!mbar_wait(empty_bar(s), ph ^ 1u, abort_flag)) { ok = false; break; }
           const uint32_t a_dst = smem_base + s * C::STAGE_BYTES, b_dst = a_dst + C::A_BYTES;
-          mbar_expect_tx(full_bar(s), C::STAGE_BYTES);
+          if (!PAIR) mbar_expect_tx(full_bar(s), C::STAGE_BYTES);
+          else if (leader) mbar_expect_tx(full_bar(s), 2 * C::STAGE_BYTES);   // this CTA's bytes and the peer's
           int k0 = kb * BK;
           if (p.seg_mode == 2) {   // this k-block belongs to one (A_i, B_i) pair
             int start;
@@ -290,20 +323,41 @@ gemm_tc_kernel(const __grid_constant__ GemmMaps maps, const GemmParams p) {
             tmB = &maps.b[seg];
             k0 = (kb - start) * BK;
           }
-          if (!p.a_mn) {
-            tma_load_2d(a_dst, tmA, k0, m0, full_bar(s));
-          } else {
+          if constexpr (!PAIR) {
+            if (!p.a_mn) {
+              tma_load_2d(a_dst, tmA, k0, m0, full_bar(s));
+            } else {
 #pragma unroll
-            for (int j = 0; j < BM / 64; ++j) tma_load_2d(a_dst + j * (BK * 128), tmA, m0 + 64 * j, k0, full_bar(s));
-          }
-          if (GATE_UP) {
-            tma_load_2d(b_dst, tmB, k0, n0, full_bar(s));
-            tma_load_2d(b_dst + (BN / 2) * 128, tmB2, k0, n0, full_bar(s));
-          } else if (!p.b_mn) {
-            tma_load_2d(b_dst, tmB, k0, n0, full_bar(s));
-          } else {
+              for (int j = 0; j < BM / 64; ++j) tma_load_2d(a_dst + j * (BK * 128), tmA, m0 + 64 * j, k0, full_bar(s));
+            }
+            if (GATE_UP) {
+              tma_load_2d(b_dst, tmB, k0, n0, full_bar(s));
+              tma_load_2d(b_dst + (BN / 2) * 128, tmB2, k0, n0, full_bar(s));
+            } else if (!p.b_mn) {
+              tma_load_2d(b_dst, tmB, k0, n0, full_bar(s));
+            } else {
 #pragma unroll
-            for (int j = 0; j < BN / 64; ++j) tma_load_2d(b_dst + j * (BK * 128), tmB, n0 + 64 * j, k0, full_bar(s));
+              for (int j = 0; j < BN / 64; ++j) tma_load_2d(b_dst + j * (BK * 128), tmB, n0 + 64 * j, k0, full_bar(s));
+            }
+          } else {
+            // this CTA's 128 rows of A, and its half of the tile's B rows: columns [0,128) of the accumulator come
+            // from rank 0's shared memory, [128,256) from rank 1's (gate/up: rank 0 stages W_gate, rank 1 W_up)
+            const uint32_t bar = full0 + 8u * s;
+            if (!p.a_mn) {
+              tma_load_2d_pair(a_dst, tmA, k0, m0, bar);
+            } else {
+#pragma unroll
+              for (int j = 0; j < BM / 64; ++j) tma_load_2d_pair(a_dst + j * (BK * 128), tmA, m0 + 64 * j, k0, bar);
+            }
+            if (GATE_UP) {
+              tma_load_2d_pair(b_dst, rank ? tmB2 : tmB, k0, n0, bar);
+            } else if (!p.b_mn) {
+              tma_load_2d_pair(b_dst, tmB, k0, n0 + (int)rank * C::B_ROWS, bar);
+            } else {
+#pragma unroll
+              for (int j = 0; j < C::B_ROWS / 64; ++j)
+                tma_load_2d_pair(b_dst + j * (BK * 128), tmB, n0 + (int)rank * C::B_ROWS + 64 * j, k0, bar);
+            }
           }
         }
         if (!ok) break;
@@ -311,7 +365,7 @@ gemm_tc_kernel(const __grid_constant__ GemmMaps maps, const GemmParams p) {
         ok = publish(next);
         tile = next;
       }
-      if (p.sched) {
+      if (draw) {
         // This CTA draws no more tiles. The last CTA of the grid to get here leaves the pair zeroed for the next launch.
         __threadfence();
         if (atomicAdd(p.sched + 1, 1) == (int)gridDim.x - 1) {
@@ -320,8 +374,10 @@ gemm_tc_kernel(const __grid_constant__ GemmMaps maps, const GemmParams p) {
           __threadfence();
         }
       }
-      // Do not leave the CTA while bulk copies may still be landing in its shared memory.
-      const uint32_t pending = it < (uint32_t)C::STAGES ? it : (uint32_t)C::STAGES;
+      // Do not leave the CTA while bulk copies may still be landing in its shared memory. (PAIR, rank 1: its copies
+      // are counted on rank 0's barriers; they have landed once the MMAs that read them are done, which the
+      // epilogue of this CTA waits for, and both CTAs meet at the cluster barrier before they leave.)
+      const uint32_t pending = (PAIR && !leader) ? 0u : (it < (uint32_t)C::STAGES ? it : (uint32_t)C::STAGES);
       for (uint32_t j = it - pending; j < it; ++j) {
         const int s = j % C::STAGES;
         const uint32_t ph = (j / C::STAGES) & 1u;
@@ -336,7 +392,12 @@ gemm_tc_kernel(const __grid_constant__ GemmMaps maps, const GemmParams p) {
       const uint32_t a_lbo = p.a_mn ? BK * 128 : 0, b_lbo = p.b_mn ? BK * 128 : 0;
       const uint32_t a_kadv = p.a_mn ? (UK * 128) >> 4 : (UK * 2) >> 4;  // descriptor units of 16 B
       const uint32_t b_kadv = p.b_mn ? (UK * 128) >> 4 : (UK * 2) >> 4;
+      // PAIR: completion is reported to the same barrier of both CTAs (one commit each; empty: both producers may
+      // refill the stage, tfull: both epilogues may read their rows)
+      const uint32_t peer_empty0 = PAIR ? mapa_u32(empty_bar(0), 1) : 0u;
+      const uint32_t peer_tfull0 = PAIR ? mapa_u32(tfull_bar(0), 1) : 0u;
       for (int tile = next_tile(false); tile >= 0 && ok; tile = next_tile(false), ++tl) {
+        if (PAIR && !leader) continue;    // rank 1 issues nothing; its thread only keeps the tile queue moving
         const int acc = tl & 1;
         const uint32_t aph = (tl >> 1) & 1u;
         if (!mbar_wait(tempty_bar(acc), aph ^ 1u, abort_flag)) { ok = false; break; }
@@ -350,26 +411,48 @@ gemm_tc_kernel(const __grid_constant__ GemmMaps maps, const GemmParams p) {
           const uint32_t a_src = smem_base + s * C::STAGE_BYTES, b_src = a_src + C::A_BYTES;
           const uint64_t adesc = make_smem_desc(a_src, a_lbo, 1024);
           const uint64_t bdesc = make_smem_desc(b_src, b_lbo, 1024);
+          if constexpr (PAIR) {
 #pragma unroll
-          for (int k = 0; k < BK / UK; ++k)
-            mma_f16_ss(d_tmem, adesc + (uint64_t)(k * a_kadv), bdesc + (uint64_t)(k * b_kadv), p.idesc,
-                       (kb | k) != 0 ? 1u : 0u);
-          mma_commit(empty_bar(s));
+            for (int k = 0; k < BK / UK; ++k)
+              mma_f16_ss_pair(d_tmem, adesc + (uint64_t)(k * a_kadv), bdesc + (uint64_t)(k * b_kadv), p.idesc,
+                              (kb | k) != 0 ? 1u : 0u);
+            mma_commit_pair(empty_bar(s));
+            mma_commit_pair(peer_empty0 + 8u * s);
+          } else {
+#pragma unroll
+            for (int k = 0; k < BK / UK; ++k)
+              mma_f16_ss(d_tmem, adesc + (uint64_t)(k * a_kadv), bdesc + (uint64_t)(k * b_kadv), p.idesc,
+                         (kb | k) != 0 ? 1u : 0u);
+            mma_commit(empty_bar(s));
+          }
         }
-        if (ok) mma_commit(tfull_bar(acc));
+        if (ok) {
+          if constexpr (PAIR) {
+            mma_commit_pair(tfull_bar(acc));
+            mma_commit_pair(peer_tfull0 + 8u * acc);
+          } else {
+            mma_commit(tfull_bar(acc));
+          }
+        }
       }
       // Everything issued must have completed before tensor memory is released.
-      mma_commit(done_bar);
-      mbar_wait_drain(done_bar, 0);
+      if (!PAIR) {
+        mma_commit(done_bar);
+        mbar_wait_drain(done_bar, 0);
+      } else if (leader) {
+        mma_commit_pair(done_bar);
+        mbar_wait_drain(done_bar, 0);
+      }
     }
   } else {
     // ------------------------------------------------------------- epilogue (warps 2..5)
     const int q = warp & 3;  // TMEM lane quarter this warp may access
     uint32_t tl = 0;
     bool ok = true;
+    const uint32_t tempty0 = PAIR ? mapa_u32(tempty_bar(0), 0) : 0u;   // rank 0 collects both CTAs' releases
     for (int tile = next_tile(true); tile >= 0 && ok; tile = next_tile(true), ++tl) {
       int mi, ni;
-      tile_coords(tile, p.tiles_m, p.tiles_n, p.group_m, mi, ni);
+      coords_of(tile, mi, ni);
       const int acc = tl & 1;
       const uint32_t aph = (tl >> 1) & 1u;
       if (!mbar_wait(tfull_bar(acc), aph, abort_flag)) { ok = false; break; }
@@ -539,15 +622,20 @@ gemm_tc_kernel(const __grid_constant__ GemmMaps maps, const GemmParams p) {
       }
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(tempty_bar(acc));
+      if (lane == 0) {
+        if (PAIR) mbar_arrive_cluster(tempty0 + 8u * acc);
+        else mbar_arrive(tempty_bar(acc));
+      }
     }
   }
 
   tc_fence_before();
   __syncthreads();
+  if (PAIR) cluster_sync_all();   // neither CTA frees tensor memory or leaves while the other may still use the pair
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, C::TMEM_COLS);
+    if (PAIR) tmem_dealloc_pair(tmem_base, C::TMEM_COLS);
+    else tmem_dealloc(tmem_base, C::TMEM_COLS);
   }
   if (threadIdx.x == 0 && *abort_flag) flag_status(p.status, Q3_STATUS_WAIT_TIMEOUT);
 }
@@ -613,16 +701,72 @@ inline int sched_pair(int** out) {
   return Q3_OK;
 }
 
+// CTA pairs (two CTAs per 256-row tile, see Cfg): 1 = used wherever there are at least two 128-row tiles (default),
+// 0 = never. Q3_GEMM_CTA_PAIRS=0 sets the initial policy; q3_gemm_cta_pairs() switches at run time.
+static std::atomic<int> g_cta_pairs{[] {
+  const char* e = getenv("Q3_GEMM_CTA_PAIRS");
+  return (e && !strcmp(e, "0")) ? 0 : 1;
+}()};
+
+// Persistent launch of the single-CTA kernel (grid = min(tiles, SMs)) or of the pair kernel (clusters of 2, as many
+// as can be resident, at most one per 256-row tile).
+template <typename K1, typename K2>
+int launch_tiles(K1 single, K2 pair, bool use_pair, int smem_single, int smem_pair, DeviceFlags* cfg_single,
+                 DeviceFlags* cfg_pair, const GemmMaps& maps, GemmParams& p, cudaStream_t st) {
+  if (!use_pair) {
+    const int64_t tiles = (int64_t)p.tiles_m * p.tiles_n;
+    const int grid = (int)(tiles < sm_count() ? tiles : sm_count());
+    if (int rc = ensure_dynamic_smem(single, smem_single, cfg_single); rc != Q3_OK) return rc;
+    if (int rc = sched_pair(&p.sched); rc != Q3_OK) return rc;
+    single<<<grid, kGemmThreads, smem_single, st>>>(maps, p);
+    return launch_status();
+  }
+  if (int rc = ensure_dynamic_smem(pair, smem_pair, cfg_pair); rc != Q3_OK) return rc;
+  p.sched = nullptr;     // pairs take their tiles with a fixed stride
+  p.prefetch = 0;
+  const int64_t tiles = (int64_t)((p.tiles_m + 1) / 2) * p.tiles_n;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)sm_count(), 1, 1);
+  cfg.blockDim = dim3(kGemmThreads, 1, 1);
+  cfg.dynamicSmemBytes = (size_t)smem_pair;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  // as many pairs as can be resident at once (asked once per device), at most one per tile
+  static int resident[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return Q3_ERR_CUDA;
+  int room = __atomic_load_n(&resident[dev], __ATOMIC_ACQUIRE);
+  if (room == 0) {
+    if (cudaOccupancyMaxActiveClusters(&room, pair, &cfg) != cudaSuccess || room < 1) {
+      cudaGetLastError();
+      room = sm_count() / 2;
+    }
+    __atomic_store_n(&resident[dev], room, __ATOMIC_RELEASE);
+  }
+  cfg.gridDim = dim3((unsigned)(2 * (tiles < room ? tiles : (int64_t)room)), 1, 1);
+  cudaError_t e = cudaLaunchKernelEx(&cfg, pair, maps, p);
+  if (e != cudaSuccess) return Q3_ERR_CUDA - (int)e;
+  return launch_status();
+}
+
 template <int BN, typename TO, int EPI>
 int launch_gemm(const Operand& A, const Operand& B, const void* b2, GemmParams& p, bool bf16, cudaStream_t st) {
   constexpr bool GATE_UP = (EPI == EPI_GATE_UP);
   using C = Cfg<BN>;
+  const bool use_pair = BN == 256 && cdiv(p.M, BM) >= 2 && g_cta_pairs.load(std::memory_order_relaxed) != 0;
   GemmMaps maps;
   int rc;
   if (!A.mn_major) rc = make_tmap_2d(&maps.a[0], A.ptr, bf16, p.M, p.K, A.ld, BK, BM);
   else rc = make_tmap_2d(&maps.a[0], A.ptr, bf16, p.K, p.M, A.ld, 64, BK);
   if (rc != Q3_OK) return rc;
-  if (!B.mn_major) rc = make_tmap_2d(&maps.b[0], B.ptr, bf16, p.N, p.K, B.ld, BK, GATE_UP ? BN / 2 : BN);
+  // K-major B box: all BN rows of the tile, or (pairs, and the two halves of gate/up) 128 of them
+  if (!B.mn_major) rc = make_tmap_2d(&maps.b[0], B.ptr, bf16, p.N, p.K, B.ld, BK, (GATE_UP || use_pair) ? BN / 2 : BN);
   else rc = make_tmap_2d(&maps.b[0], B.ptr, bf16, p.K, p.N, B.ld, 64, BK);
   if (rc != Q3_OK) return rc;
   maps.a[1] = maps.a[2] = maps.a[0];
@@ -639,19 +783,19 @@ int launch_gemm(const Operand& A, const Operand& B, const void* b2, GemmParams& 
   p.group_m = pick_group_m(p.tiles_m, p.K);
   p.a_mn = A.mn_major;
   p.b_mn = B.mn_major;
-  p.idesc = make_idesc_f16(BM, BN, bf16, A.mn_major, B.mn_major);
+  p.idesc = make_idesc_f16(use_pair ? 2 * BM : BM, BN, bf16, A.mn_major, B.mn_major);
   {
     const char* e = getenv("Q3_GEMM_PREFETCH");
     p.prefetch = e ? atoi(e) : 0;   // measured slower on every shape tried; kept as an experiment switch
   }
-  const int64_t tiles = (int64_t)p.tiles_m * p.tiles_n;
-  const int grid = (int)(tiles < sm_count() ? tiles : sm_count());
-  auto kern = gemm_tc_kernel<BN, TO, EPI>;
-  static DeviceFlags configured = {};
-  if (int rc2 = ensure_dynamic_smem(kern, C::SMEM_BYTES, &configured); rc2 != Q3_OK) return rc2;
-  if (int rc3 = sched_pair(&p.sched); rc3 != Q3_OK) return rc3;
-  kern<<<grid, kGemmThreads, C::SMEM_BYTES, st>>>(maps, p);
-  return launch_status();
+  static DeviceFlags configured = {}, configured_pair = {};
+  if constexpr (BN == 256) {
+    return launch_tiles(gemm_tc_kernel<BN, TO, EPI, false>, gemm_tc_kernel<BN, TO, EPI, true>, use_pair, C::SMEM_BYTES,
+                        Cfg<BN, true>::SMEM_BYTES, &configured, &configured_pair, maps, p, st);
+  } else {
+    return launch_tiles(gemm_tc_kernel<BN, TO, EPI, false>, gemm_tc_kernel<BN, TO, EPI, false>, false, C::SMEM_BYTES,
+                        C::SMEM_BYTES, &configured, &configured_pair, maps, p, st);
+  }
 }
 
 // Up to three products that share an operand in one persistent launch (BN = 256, plain store epilogue):
@@ -671,12 +815,20 @@ int launch_grouped(int mode, int count, const void* const* a, const void* const*
   p.seg_mode = mode;
   int rc = Q3_OK;
   int64_t total = 0;
+  // mode 3 counts its 128-row tiles over all segments; the other modes have cdiv(M, 128) of them
+  int64_t row_tiles = cdiv(M, BM);
+  if (mode == 3) {
+    row_tiles = 0;
+    for (int i = 0; i < count; ++i) row_tiles += cdiv(sizes[i], BM);
+  }
+  const bool use_pair = row_tiles >= 2 && g_cta_pairs.load(std::memory_order_relaxed) != 0;
+  const int b_box_rows = use_pair ? BN / 2 : BN;     // K-major B (mode 1)
   for (int i = 0; i < 3; ++i) {
     const int j = i < count ? i : count - 1;    // unused slots repeat the last segment
     const int64_t sz = sizes[j];
     if (mode == 1) {
       if (i == 0) rc = make_tmap_2d(&maps.a[0], a[0], bf16, M, K, K, BK, BM);
-      if (rc == Q3_OK) rc = make_tmap_2d(&maps.b[i], b[j], bf16, sz, K, K, BK, BN);
+      if (rc == Q3_OK) rc = make_tmap_2d(&maps.b[i], b[j], bf16, sz, K, K, BK, b_box_rows);
       if (i > 0) maps.a[i] = maps.a[0];
       if (i < count) total += cdiv(sz, BN);
     } else if (mode == 2) {
@@ -702,16 +854,11 @@ int launch_grouped(int mode, int count, const void* const* a, const void* const*
   p.group_m = pick_group_m(p.tiles_m, (int64_t)p.kblocks * BK);
   p.a_mn = mode == 3;
   p.b_mn = mode != 1;
-  p.idesc = make_idesc_f16(BM, BN, bf16, p.a_mn != 0, p.b_mn != 0);
+  p.idesc = make_idesc_f16(use_pair ? 2 * BM : BM, BN, bf16, p.a_mn != 0, p.b_mn != 0);
   p.prefetch = 0;
-  const int64_t tiles = (int64_t)p.tiles_m * p.tiles_n;
-  const int grid = (int)(tiles < sm_count() ? tiles : sm_count());
-  auto kern = gemm_tc_kernel<BN, TO, EPI_STORE>;
-  static DeviceFlags configured = {};
-  if (int rc2 = ensure_dynamic_smem(kern, C::SMEM_BYTES, &configured); rc2 != Q3_OK) return rc2;
-  if (int rc3 = sched_pair(&p.sched); rc3 != Q3_OK) return rc3;
-  kern<<<grid, kGemmThreads, C::SMEM_BYTES, st>>>(maps, p);
-  return launch_status();
+  static DeviceFlags configured = {}, configured_pair = {};
+  return launch_tiles(gemm_tc_kernel<BN, TO, EPI_STORE, false>, gemm_tc_kernel<BN, TO, EPI_STORE, true>, use_pair,
+                      C::SMEM_BYTES, Cfg<BN, true>::SMEM_BYTES, &configured, &configured_pair, maps, p, st);
 }
 
 inline int pick_bn(int64_t M, int64_t N) {
@@ -963,4 +1110,11 @@ extern "C" int q3_linear_ce_grad(const void* hidden, const void* weight_chunk, c
 extern "C" int q3_gemm_tile_schedule(int mode) {
   if (mode == 0 || mode == 1) return tc::g_tile_schedule.exchange(mode);
   return tc::g_tile_schedule.load();
+}
+
+// 1: two CTAs share every 256-row tile wherever there are at least two 128-row tiles (default), 0: one CTA per
+// 128-row tile everywhere. Returns the previous policy; any other value only queries.
+extern "C" int q3_gemm_cta_pairs(int mode) {
+  if (mode == 0 || mode == 1) return tc::g_cta_pairs.exchange(mode);
+  return tc::g_cta_pairs.load();
 }

@@ -87,6 +87,7 @@ SIGNATURES = {
     "q3_attn_bwd_group_split": (I, [L, L, L, L]),
     "q3_attn_bwd_group_policy": (I, [I]),
     "q3_gemm_tile_schedule": (I, [I]),
+    "q3_gemm_cta_pairs": (I, [I]),
     "q3_selftest_wait_timeout": (I, [L, P, P, P]),
     "q3_peer_alloc": (I, [L, P, P]),
     "q3_peer_open": (I, [P, P]),

@@ -19,6 +19,8 @@ than Python can launch them. This module keeps the same math and the same parame
 Requires bf16/fp16 tensors and head_dim 128 (the tensor-core attention path); other shapes use the
 operator-level modules.
 """
+import os
+
 import torch
 
 from . import _abi
@@ -27,6 +29,45 @@ from ._model import Backbone, DecoderBlock
 
 def _empty(shape, like, dtype=None):
     return torch.empty(shape, device=like.device, dtype=dtype or like.dtype)
+
+
+class WeightGradientStream:
+    """Weight-gradient GEMMs of the fused layer's backward on a second stream.
+
+    In a linear layer's backward the input gradient (dY W) and the weight gradient (dY^T X) are independent, and each
+    is a persistent GEMM whose last wave leaves SMs idle (256 tiles on 148 SMs: 1.73 waves). Issued on two streams,
+    the CTAs of the second kernel become resident as those of the first run out of tiles, so the tail of one is filled
+    by the head of the other; this needs the GEMM tiles to be drawn from a counter (q3_gemm_tile_schedule(1)), or the
+    late CTAs would still own a full share. Nothing reads a weight gradient before the layer's backward returns, which
+    is where the streams are joined. Off by default: `WeightGradientStream.enabled = True` (or Q3_WGRAD_SIDE_STREAM=1)."""
+    enabled = os.environ.get('Q3_WGRAD_SIDE_STREAM', '0') == '1'
+    _streams = {}
+
+    @classmethod
+    def run(cls, fn, inputs):
+        """outputs = fn() on the side stream, ordered after the current stream's work so far."""
+        if not cls.enabled:
+            return fn()
+        main = torch.cuda.current_stream()
+        side = cls._streams.get(main.device)
+        if side is None:
+            side = cls._streams[main.device] = torch.cuda.Stream(device=main.device)
+        side.wait_stream(main)
+        with torch.cuda.stream(side):
+            outputs = fn()
+        for t in inputs:
+            t.record_stream(side)              # freed on the main stream while the side stream may still read it
+        for t in (outputs if isinstance(outputs, (list, tuple)) else [outputs]):
+            t.record_stream(main)              # allocated under the side stream, consumed on the main stream
+        return outputs
+
+    @classmethod
+    def join(cls):
+        if cls.enabled:
+            main = torch.cuda.current_stream()
+            side = cls._streams.get(main.device)
+            if side is not None:
+                main.wait_stream(side)
 
 
 def _gemm(a_ptr, a_sm, a_sk, b_ptr, b_sk, b_sn, m, n, k, like, out_dtype=None):
@@ -247,7 +288,7 @@ class FusedLayerFn(torch.autograd.Function):
         dm = g_m.reshape(t, hdim).contiguous()
         dres = g_x1.reshape(t, hdim).contiguous() if g_x1 is not None else None
         # MLP
-        dwd = mm_tn(dm, r['y'])
+        dwd = WeightGradientStream.run(lambda: mm_tn(dm, r['y']), (dm, r['y']))
         dg, du = torch.empty_like(r['g']), torch.empty_like(r['u'])
         if wd.shape[0] % 8 == 0 and wd.shape[1] % 8 == 0:
             # dY = dM @ W_down never leaves tensor memory: the GEMM epilogue turns it into dG, dU
@@ -260,12 +301,12 @@ class FusedLayerFn(torch.autograd.Function):
                       dg.numel(), _abi.dt(dg.dtype), _abi.stream())
             del dy
         dh2 = linear_group_dgrad([dg, du], [wg, wu])
-        dwg, dwu = linear_group_wgrad([dg, du], r['h2'])
+        dwg, dwu = WeightGradientStream.run(lambda: linear_group_wgrad([dg, du], r['h2']), (dg, du, r['h2']))
         del dg, du
         dx1, dw_post = _norm_bwd(r['x1'], w_post, dh2, dres, r['inv2'])
         # attention block
         do = mm_nn(dx1, wo)
-        dwo = mm_tn(dx1, r['o'])
+        dwo = WeightGradientStream.run(lambda: mm_tn(dx1, r['o']), (dx1, r['o']))
         dqn, dkn, dv = torch.empty_like(r['qn']), torch.empty_like(r['kn']), torch.empty_like(r['v'])
         ws = _abi.workspace(_abi.lib().q3_attn_bwd_workspace_bytes(b, hq, hk, s, d), dx1.device)
         _abi.call('q3_attn_bwd_bshd', r['qn'].data_ptr(), r['kn'].data_ptr(), r['v'].data_ptr(), r['o'].data_ptr(),
@@ -275,9 +316,10 @@ class FusedLayerFn(torch.autograd.Function):
         dq, dwqn, dk, dwkn = _qk_norm_rope_bwd(r['q'], r['k'], wqn, wkn, cos, sin, dqn, dkn, r['invq'], r['invk'],
                                                t, hq, hk, d)
         dh = linear_group_dgrad([dq, dk, dv], [wq, wk, wv])
-        dwq, dwk, dwv = linear_group_wgrad([dq, dk, dv], r['h'])
+        dwq, dwk, dwv = WeightGradientStream.run(lambda: linear_group_wgrad([dq, dk, dv], r['h']), (dq, dk, dv, r['h']))
         dx, dw_in = _norm_bwd(r['x'], w_in, dh, dx1, r['inv1'])
         dx = dx.view(ctx.shape)
+        WeightGradientStream.join()
         return (dx, dx if ctx.has_delta else None, None, None, None, None,
                 dw_in, dwq, dwk, dwv, dwo, dwqn, dwkn, dw_post, dwg, dwu, dwd)
 

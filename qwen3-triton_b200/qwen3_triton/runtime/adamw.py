@@ -50,6 +50,7 @@ class TritonAdamW(torch.optim.Optimizer):
         self.block = block
         self.kernel_steps = 0
         self._tables = {}
+        self._pending_streams, self._pending_calls = [], 0
 
     # ------------------------------------------------------------------------------------------ restore
     def _checked_entry(self, parameter, entry):
@@ -212,8 +213,39 @@ class TritonAdamW(torch.optim.Optimizer):
         early = getattr(self, '_early', None)
         if early is not None:
             early.join()
+        for stream in self._pending_streams:
+            torch.cuda.current_stream(stream.device).wait_stream(stream)
+        self._pending_streams, self._pending_calls = [], 0
         self.kernel_steps += 1
         return loss
+
+    @torch.no_grad()
+    def step_pending(self, eligible=None):
+        """Update, on the current stream, every parameter (of `eligible`, a collection of parameters, if given) that
+        has a gradient right now, and drop those gradients. Only for parameters whose gradient is complete as soon as
+        it exists (used once in the model), which holds for the shards FSDP assigns after a reduce-scatter. The
+        next `step()` updates the rest and makes its stream wait for this one. For sharded training: called from the
+        gradient reduce-scatter hook (runtime/fsdp.py, `before_reduce`), it updates the shards of the units reduced
+        so far on the reduce-scatter stream, beside the backward pass of the units still to come. Same result as
+        `step()` alone (see step_during_backward); same restrictions (one backward per step, no clipping)."""
+        current = torch.cuda.current_stream()
+        launched = False
+        if eligible is not None and not isinstance(eligible, (set, frozenset)):
+            eligible = {id(p) for p in eligible}
+        for index, group in enumerate(self.param_groups):
+            ready = [p for p in group['params'] if p.grad is not None and (eligible is None or id(p) in eligible)]
+            if not ready:
+                continue
+            self._launch(('pending', self._pending_calls, index), group, ready)
+            for parameter in ready:
+                local(parameter.grad).record_stream(current)
+                parameter.grad = None
+            launched = True
+        if launched:
+            self._pending_calls += 1
+            if all(current != s for s in self._pending_streams):
+                self._pending_streams.append(current)
+        return launched
 
     # ------------------------------------------------------------------------------ update during backward
     def step_during_backward(self, buckets, gradient_of=None):

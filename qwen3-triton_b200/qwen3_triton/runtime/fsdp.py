@@ -40,6 +40,7 @@ class TritonReduceScatter(_Allocation, ReduceScatter):
     def __init__(self, communication, peer_reducer=None):
         self.communication = communication
         self.peer_reducer = peer_reducer       # runtime/peer_reduce.py: gradients staged as bf16, pulled over NVLink
+        self.before_reduce = None              # e.g. TritonAdamW.step_pending: runs on the reduce-scatter stream
         self.calls = 0
         self.peer_calls = 0
 
@@ -55,6 +56,10 @@ class TritonReduceScatter(_Allocation, ReduceScatter):
         else:
             raise ValueError('FSDP SUM/AVG only')
         self.calls += 1
+        if self.before_reduce is not None:
+            # the gradient shards of the units reduced before this one are assigned by now, and the kernels that wrote
+            # them are earlier on this stream
+            self.before_reduce()
         if self.peer_reducer is not None and self.peer_reducer.staged(input_tensor):
             if operation != 'avg':
                 # with a gradient divide factor FSDP scales its fp32 buffer before a SUM; that buffer was never filled

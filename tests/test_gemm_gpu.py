@@ -77,6 +77,34 @@ def test_tile_hand_out_policies_agree_bit_for_bit(M, N, K):
     assert _abi.read_status() == 0
 
 
+@pytest.mark.parametrize('M,N,K', [(256, 256, 64), (2048, 4096, 4096), (384, 1000, 520), (129, 264, 72), (4096, 12288, 512)])
+def test_cta_pairs_and_single_ctas_agree_bit_for_bit(M, N, K):
+    """Two CTAs per 256-row tile (the default wherever there are two row tiles) against one CTA per 128-row tile: the
+    same products accumulated over k in the same order, so all three layouts of a linear layer, the fp32 output, the
+    fused gate/up kernel and the accumulating epilogue must agree exactly - odd row-tile counts (the second CTA of
+    the last pair has no rows) and ragged N and K included."""
+    from qwen3_triton import _abi
+    from qwen3_triton.kernels.linear import matmul
+    x, w = randn((M, K), 21, torch.bfloat16).cuda(), randn((N, K), 22, torch.bfloat16).cuda()
+    dy = randn((M, N), 23, torch.bfloat16).cuda()
+
+    def products():
+        return [matmul(x, w.t()), matmul(dy, w), matmul(dy.t(), x), matmul(x, w.t(), output_dtype=torch.float32)]
+
+    assert _abi.lib().q3_gemm_cta_pairs(-1) == 1
+    paired = products()
+    previous = _abi.lib().q3_gemm_cta_pairs(0)
+    try:
+        single = products()
+    finally:
+        _abi.lib().q3_gemm_cta_pairs(previous)
+    for a, b in zip(paired, single):
+        assert torch.equal(a, b), float((a.float() - b.float()).abs().max())
+    close(paired[0], ref_mm(x, w.t()).to(torch.bfloat16), scale=K ** 0.5, what='X*W^T by pairs')
+    close(paired[2], ref_mm(dy.t(), x).to(torch.bfloat16), scale=M ** 0.5, what='dY^T*X by pairs')
+    assert _abi.read_status() == 0
+
+
 @pytest.mark.parametrize('dtype', [torch.bfloat16, torch.float16])
 @pytest.mark.parametrize('M,K,sizes', [(2048, 4096, (4096, 1024, 1024)), (300, 520, (192, 64, 320)), (129, 136, (448, 64)),
                                        (2048, 1024, (3072, 3072)), (2048, 4096, (12288, 12288)),
