@@ -104,7 +104,7 @@ template <int BN, bool PAIR = false> struct Cfg {
 // Slots of the in-CTA tile queue (producer -> MMA issuer and epilogue warps). The producer runs at most one tile ahead
 // of the MMA issuer and the epilogue at most two behind it; the queue's own barriers make any depth correct.
 constexpr int kSched = 4;
-static_assert((2 * 6 + 6 + 2 * kSched) * 8 + kSched * 4 <= 256, "barrier area");
+static_assert((2 * 7 + 6 + 2 * kSched) * 8 + kSched * 4 <= 256, "barrier area");
 
 __device__ __forceinline__ float silu_f(float g) { return g / (1.f + __expf(-g)); }
 
@@ -192,7 +192,8 @@ gemm_tc_kernel(const __grid_constant__ GemmMaps maps, const GemmParams p) {
   volatile int* sched_tile = reinterpret_cast<volatile int*>(bars + 2 * C::STAGES + 6 + 2 * kSched);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  // PAIR: a tile is 256 rows (two consecutive 128-row tiles, one per CTA); tiles are handed out per pair, statically
+  // PAIR: a tile is 256 rows (two consecutive 128-row tiles, one per CTA); rank 0 decides the pair's next tile and
+  // puts it into both CTAs' tile queues
   const int tiles_m_sched = PAIR ? (p.tiles_m + 1) / 2 : p.tiles_m;
   const int group_m_sched = PAIR ? (p.group_m + 1) / 2 : p.group_m;
   const int total_tiles = tiles_m_sched * p.tiles_n;
@@ -205,29 +206,36 @@ gemm_tc_kernel(const __grid_constant__ GemmMaps maps, const GemmParams p) {
   };
   // Consumer side of the tile queue (MMA issuer: one thread; epilogue: whole warps, lane 0 releases the slot).
   // Returns the tile, -1 after the last one, -2 when a wait gave up.
+  // PAIR: every consumer of either CTA releases a slot on rank 0's barrier, where the publisher waits.
   uint32_t taken = 0;
+  const uint32_t sempty_lead0 = PAIR ? mapa_u32(sempty_bar(0), 0) : 0u;
   auto next_tile = [&](bool whole_warp) -> int {
     const int slot = taken % kSched;
     const uint32_t ph = (taken / kSched) & 1u;
     ++taken;
-    if (!mbar_wait(sfull_bar(slot), ph, abort_flag)) return -2;
+    if (PAIR ? !mbar_wait_cluster(sfull_bar(slot), ph, abort_flag) : !mbar_wait(sfull_bar(slot), ph, abort_flag))
+      return -2;
     const int t = sched_tile[slot];
     if (whole_warp) __syncwarp();
-    if (!whole_warp || lane == 0) mbar_arrive(sempty_bar(slot));
+    if (!whole_warp || lane == 0) {
+      if (PAIR) mbar_arrive_cluster(sempty_lead0 + 8u * slot);
+      else mbar_arrive(sempty_bar(slot));
+    }
     return t;
   };
 
   // The producer thread draws its first tile before anything else: the counter's round trip to L2 runs beside the
   // barrier set-up, the tensor-memory allocation and the CTA-wide sync below.
   int first_tile = first_static;
-  if (!PAIR && threadIdx.x == 0 && p.sched) first_tile = atomicAdd(p.sched, 1);
+  if (threadIdx.x == 0 && p.sched && leader) first_tile = atomicAdd(p.sched, 1);
   if (threadIdx.x == 0) {
     *abort_flag = 0;
     for (int s = 0; s < C::STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
     // tempty: the four epilogue warps of every CTA that holds rows of the accumulator
     for (int a = 0; a < 2; ++a) { mbar_init(tfull_bar(a), 1); mbar_init(tempty_bar(a), PAIR ? 8 : 4); }
     mbar_init(done_bar, 1);
-    for (int i = 0; i < kSched; ++i) { mbar_init(sfull_bar(i), 1); mbar_init(sempty_bar(i), 5); }   // MMA + 4 warps
+    // a slot is released by the MMA thread and the 4 epilogue warps (PAIR: of both CTAs, and rank 1's producer)
+    for (int i = 0; i < kSched; ++i) { mbar_init(sfull_bar(i), 1); mbar_init(sempty_bar(i), PAIR ? 11 : 5); }
     fence_barrier_init();
     prefetch_tmap(&maps.a[0]);
     prefetch_tmap(&maps.b[0]);
@@ -259,12 +267,19 @@ gemm_tc_kernel(const __grid_constant__ GemmMaps maps, const GemmParams p) {
         if (!mbar_wait(sempty_bar(slot), ph ^ 1u, abort_flag)) return false;
         sched_tile[slot] = t;
         mbar_arrive(sfull_bar(slot));   // release: the consumers' waits acquire
+        if (PAIR) {                     // the same into rank 1's queue
+          st_cluster_u32(mapa_u32(smem_u32(const_cast<int*>(&sched_tile[slot])), 1), (uint32_t)t);
+          mbar_arrive_cluster(mapa_u32(sfull_bar(slot), 1));
+        }
         return true;
       };
+      // PAIR, rank 1: the producer is one more reader of the queue rank 0 fills
       int tile = first_tile;
       if (tile >= total_tiles) tile = -1;
-      bool ok = publish(tile);
-      const bool draw = !PAIR && p.sched != nullptr;
+      bool ok = true;
+      if (leader) ok = publish(tile);
+      else { tile = next_tile(false); ok = tile > -2; }
+      const bool draw = leader && p.sched != nullptr;
       // PAIR: both CTAs' loads are counted on the rank-0 CTA's full barriers
       const uint32_t full0 = PAIR ? mapa_u32(full_bar(0), 0) : full_bar(0);
       while (ok && tile >= 0) {
@@ -361,14 +376,20 @@ gemm_tc_kernel(const __grid_constant__ GemmMaps maps, const GemmParams p) {
           }
         }
         if (!ok) break;
-        if (next >= total_tiles) next = -1;
-        ok = publish(next);
-        tile = next;
+        if (leader) {
+          if (next >= total_tiles) next = -1;
+          ok = publish(next);
+          tile = next;
+        } else {
+          tile = next_tile(false);
+          ok = tile > -2;
+        }
       }
       if (draw) {
-        // This CTA draws no more tiles. The last CTA of the grid to get here leaves the pair zeroed for the next launch.
+        // This CTA draws no more tiles. The last drawing CTA of the grid to get here leaves the counters zeroed for
+        // the next launch.
         __threadfence();
-        if (atomicAdd(p.sched + 1, 1) == (int)gridDim.x - 1) {
+        if (atomicAdd(p.sched + 1, 1) == stride_static - 1) {
           p.sched[0] = 0;
           p.sched[1] = 0;
           __threadfence();
@@ -722,7 +743,7 @@ int launch_tiles(K1 single, K2 pair, bool use_pair, int smem_single, int smem_pa
     return launch_status();
   }
   if (int rc = ensure_dynamic_smem(pair, smem_pair, cfg_pair); rc != Q3_OK) return rc;
-  p.sched = nullptr;     // pairs take their tiles with a fixed stride
+  if (int rc = sched_pair(&p.sched); rc != Q3_OK) return rc;
   p.prefetch = 0;
   const int64_t tiles = (int64_t)((p.tiles_m + 1) / 2) * p.tiles_n;
   cudaLaunchConfig_t cfg = {};
