@@ -570,7 +570,8 @@ def run_fsdp(args):
     # gradients reduced by the pull kernel over peer memory (bf16 on the links, fp32 sums) unless Q3_BENCH_PEER_REDUCE=0
     peer_reduce = os.environ.get("Q3_BENCH_PEER_REDUCE", "1") == "1" and world in (2, 4, 8)
     hooks = configure(model, comm, pack_gradients_off_compute_stream=os.environ.get("Q3_BENCH_PACK_SIDE", "0") == "1",
-                      peer_memory_reduce=peer_reduce)
+                      peer_memory_reduce=peer_reduce,
+                      copy_engine_gather=os.environ.get("Q3_BENCH_CE_GATHER", "1") == "1")
     peer_reduce = hooks["peer_reducer"] is not None        # False on every rank if the mappings could not be made
     decoder = [p for n, p in model.named_parameters() if not n.startswith("lm_head.")]
     opt = TritonAdamW([dict(params=decoder), dict(params=[model.lm_head.weight])], lr=1e-4, betas=(0.9, 0.95),
@@ -714,6 +715,9 @@ def run_fsdp(args):
                        "peak_memory_gb_rank0": peak_memory, "nccl_max_ctas": max_ctas or "default",
                        "adamw": ("shards of reduced units updated during backward on the reduce-scatter stream, "
                                  "the rest after backward" if early_adamw else "after backward"),
+                       "parameter_gather": ("copy-engine pulls from peer-mapped buffers (%d of %d all-gather calls)" % (
+                                                hooks["all_gather"].peer_calls, hooks["all_gather"].calls)
+                                            if hooks["peer_gather"] is not None else "NCCL all-gather"),
                        "gradient_reduce": ("pull kernel over peer memory, bf16 on the links, fp32 sums in rank order "
                                            "(%d of %d reduce-scatter calls)" % (hooks["reduce_scatter"].peer_calls,
                                                                                 hooks["reduce_scatter"].calls)
@@ -725,6 +729,8 @@ def run_fsdp(args):
             "roofline": roofline,
         }
         print(json.dumps(line), flush=True)
+    if hooks["peer_gather"] is not None:
+        hooks["peer_gather"].close()
     if hooks["peer_reducer"] is not None:
         hooks["peer_reducer"].close()
     dist.destroy_process_group()

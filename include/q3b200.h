@@ -430,6 +430,11 @@ int q3_peer_open(const void* handle64, void** ptr);
 int q3_peer_close(void* ptr);
 int q3_peer_free(void* ptr);
 
+/* One asynchronous device-to-device copy on `stream` (either pointer may come from q3_peer_open): a copy-engine
+ * transfer that occupies no SM. The parameter all-gather of runtime/peer_gather.py issues one per source rank, from
+ * the peer's mapped all-gather buffer into this rank's. Reference: qwen3_triton/runtime/collectives.py:88-137. */
+int q3_peer_copy(void* dst, const void* src, int64_t bytes, q3_stream_t stream);
+
 /* out[i] = scale * sum_r widen(peers[r][first + i]), i in [0, count): this rank's rows of every rank's 16-bit staging
  * buffer, pulled with plain peer loads, added in fp32 in rank order. `peers` is a HOST array of `world` (2, 4 or 8)
  * device pointers; first % 8 == 0. One kernel replaces the chunk-cat upcast and the fp32 ring reduce-scatter of a

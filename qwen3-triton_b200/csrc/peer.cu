@@ -111,6 +111,17 @@ extern "C" int q3_peer_free(void* ptr) {
   return e == cudaSuccess ? Q3_OK : Q3_ERR_CUDA - (int)e;
 }
 
+// One asynchronous device-to-device copy on `stream`; either side may be a pointer mapped with q3_peer_open, and the
+// transfer then runs on a copy engine over NVLink without occupying an SM (the all-gather of runtime/peer_gather.py:
+// one call per source rank).
+extern "C" int q3_peer_copy(void* dst, const void* src, int64_t bytes, q3_stream_t stream) {
+  if (!dst || !src) return Q3_ERR_ARG;
+  if (bytes < 0) return Q3_ERR_SHAPE;
+  if (bytes == 0) return Q3_OK;
+  cudaError_t e = cudaMemcpyAsync(dst, src, (size_t)bytes, cudaMemcpyDeviceToDevice, (cudaStream_t)stream);
+  return e == cudaSuccess ? Q3_OK : Q3_ERR_CUDA - (int)e;
+}
+
 // out [count] fp32 = scale * sum over ranks r of peers[r][first .. first + count) widened to fp32, added in rank order.
 // peers: host array of `world` device pointers (this rank's own staging buffer at index `rank`, the others mapped
 // with q3_peer_open), all holding the same [world * count]-element layout in `dtype` (bf16 or fp16). The caller

@@ -18,22 +18,60 @@ class _Allocation:
         return torch.empty(tuple(size), device=device, dtype=dtype)
 
 
+def _largest_unit(model, world):
+    """(elements, bytes in the unit's all-gather dtype) of the largest FSDP unit, parameters padded to the world size
+    along their first dimension."""
+    elements = nbytes = 0
+    for module in model.modules():
+        if not isinstance(module, FSDPModule):
+            continue
+        group = module._get_fsdp_state()._fsdp_param_group
+        if group is None:
+            continue
+        total = total_bytes = 0
+        for fsdp_param in group.fsdp_params:
+            shape = tuple(fsdp_param._orig_size)
+            first = shape[0] if shape else 1
+            rest = 1
+            for d in shape[1:]:
+                rest *= d
+            padded = -(-first // world) * world * rest
+            policy = getattr(group, 'mp_policy', None)
+            dtype = (policy.param_dtype if policy is not None else None) or fsdp_param.sharded_param.dtype
+            total += padded
+            total_bytes += padded * torch.empty((), dtype=dtype).element_size()
+        elements, nbytes = max(elements, total), max(nbytes, total_bytes)
+    return elements, nbytes
+
+
 def _same_group(group, communication):
     return dist.get_process_group_ranks(group) == dist.get_process_group_ranks(communication.group)
 
 
 class TritonAllGather(_Allocation, AllGather):
-    def __init__(self, communication):
+    def __init__(self, communication, peer_gather=None):
         self.communication = communication
+        self.peer_gather = peer_gather         # runtime/peer_gather.py: output buffers peers can read, copy-engine pulls
         self.calls = 0
+        self.peer_calls = 0
+
+    def allocate(self, size, *, dtype, device):
+        if self.peer_gather is not None:
+            buffer = self.peer_gather.allocate(tuple(size), dtype, device)
+            if buffer is not None:
+                return buffer
+        return torch.empty(tuple(size), device=device, dtype=dtype)
 
     def __call__(self, output_tensor, input_tensor, group, async_op=False):
         if async_op:
             raise ValueError('Stream/event ordered FSDP calls required')
         if not _same_group(group, self.communication):
             raise ValueError('FSDP mesh and communicator group differ')
-        self.communication.all_gather(output_tensor, input_tensor)
         self.calls += 1
+        if self.peer_gather is not None and self.peer_gather.gather(output_tensor, input_tensor):
+            self.peer_calls += 1
+            return
+        self.communication.all_gather(output_tensor, input_tensor)
 
 
 class TritonReduceScatter(_Allocation, ReduceScatter):
@@ -71,35 +109,20 @@ class TritonReduceScatter(_Allocation, ReduceScatter):
 
 
 def largest_unit_elements(model, world):
-    """Upper bound of the padded gradient elements one FSDP unit reduces: per unit, the parameters it manages, each
-    padded to a multiple of the world size along its first dimension."""
-    largest = 0
-    for module in model.modules():
-        if not isinstance(module, FSDPModule):
-            continue
-        group = module._get_fsdp_state()._fsdp_param_group
-        if group is None:
-            continue
-        total = 0
-        for fsdp_param in group.fsdp_params:
-            shape = tuple(fsdp_param._orig_size)
-            first = shape[0] if shape else 1
-            rest = 1
-            for d in shape[1:]:
-                rest *= d
-            total += -(-first // world) * world * rest
-        largest = max(largest, total)
-    return largest
+    """Upper bound of the padded gradient elements one FSDP unit reduces."""
+    return _largest_unit(model, world)[0]
 
 
 def configure(model, communication, *, pack_kernels=True, pack_gradients_off_compute_stream=False,
-              peer_memory_reduce=False):
+              peer_memory_reduce=False, copy_engine_gather=False):
     """Install the comm hooks on every FSDP unit and (by default) the pack/unpack kernels of runtime/ops.py.
     `pack_gradients_off_compute_stream`: run the reduce-scatter copy-in on FSDP's reduce-scatter stream.
     `peer_memory_reduce`: reduce gradients with the pull kernel over peer memory (runtime/peer_reduce.py; one node,
     2 / 4 / 8 ranks, implies the copy-in on the reduce-scatter stream); the returned dict holds the reducer under
     'peer_reducer' - call its close() before the process group is destroyed. If any rank cannot allocate or map
-    the staging buffers, every rank falls back to the collective backend and 'peer_reducer' is None."""
+    the staging buffers, every rank falls back to the collective backend and 'peer_reducer' is None.
+    `copy_engine_gather`: all-gather the parameters with copy-engine transfers from buffers the peers have mapped
+    (runtime/peer_gather.py; one node); 'peer_gather' in the returned dict, same close() rule and fallback."""
     reducer = None
     if peer_memory_reduce:
         if not pack_kernels:
@@ -114,7 +137,12 @@ def configure(model, communication, *, pack_kernels=True, pack_gradients_off_com
         install_fsdp_pack_kernels()
         pack_gradients_on_reduce_scatter_stream(model if (pack_gradients_off_compute_stream or reducer) else None)
         reduce_gradients_over_peer_memory(reducer)
-    ag = TritonAllGather(communication)
+    gatherer = None
+    if copy_engine_gather:
+        from .peer_gather import PeerAllGather
+        device = torch.device('cuda', torch.cuda.current_device())
+        gatherer = PeerAllGather.create(communication.group, device, _largest_unit(model, communication.world)[1])
+    ag = TritonAllGather(communication, gatherer)
     rs = TritonReduceScatter(communication, reducer)
     count = 0
     for module in model.modules():
@@ -124,4 +152,4 @@ def configure(model, communication, *, pack_kernels=True, pack_gradients_off_com
             count += 1
     if not count:
         raise ValueError('No FSDP units to configure')
-    return dict(all_gather=ag, reduce_scatter=rs, units=count, peer_reducer=reducer)
+    return dict(all_gather=ag, reduce_scatter=rs, units=count, peer_reducer=reducer, peer_gather=gatherer)

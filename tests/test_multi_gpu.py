@@ -105,9 +105,10 @@ WORKER = textwrap.dedent('''
     rel = float((g0 - g1).norm() / g0.norm())
     assert rel < 2e-2, rel
 
-    # 3. the same step with gradients reduced by the pull kernel over peer memory: on two ranks the fp32 sum of the two
-    #    upcast bf16 gradients has one possible value, so every gradient shard equals the NCCL path's bit for bit
-    shards = []
+    # 3. the same step with parameters gathered by copy-engine pulls and gradients reduced by the pull kernel over peer
+    #    memory: on two ranks the fp32 sum of the two upcast bf16 gradients has one possible value, so every gradient
+    #    shard equals the NCCL path's bit for bit
+    shards, losses = [], []
     for peer in (False, True):
         torch.manual_seed(1234)
         with torch.device(dev):
@@ -116,21 +117,25 @@ WORKER = textwrap.dedent('''
         model = shard_vocab_loss_model(model, keep_full_layers=4, checkpoint_every=1, skip_embedding_backward_gather=True,
                                        fused_vocab_dw=True, communication=None, checkpoint_mode="selective",
                                        layers_per_unit=[1, 1, 2], vocab_parallel_embedding=True)
-        hooks = configure(model, comm, peer_memory_reduce=peer)
+        hooks = configure(model, comm, peer_memory_reduce=peer, copy_engine_gather=peer)
         for _ in range(3):                                   # three steps: both staging slots reused several times
             model.zero_grad(set_to_none=True)
             model(ids, labels=ids).loss.backward()
         torch.cuda.synchronize()
         shards.append({n: (q.grad.to_local() if hasattr(q.grad, "to_local") else q.grad).float().cpu().clone()
                        for n, q in model.named_parameters()})
-        rs = hooks["reduce_scatter"]
+        rs, ag = hooks["reduce_scatter"], hooks["all_gather"]
         assert rs.calls > 0 and rs.peer_calls == (rs.calls if peer else 0), (rs.calls, rs.peer_calls)
-        if hooks["peer_reducer"] is not None:
-            hooks["peer_reducer"].close()
+        assert ag.calls > 0 and ag.peer_calls == (ag.calls if peer else 0), (ag.calls, ag.peer_calls)
+        losses.append(float(model(ids, labels=ids).loss))   # one more forward: gathered parameters are the same
+        for key in ("peer_gather", "peer_reducer"):
+            if hooks[key] is not None:
+                hooks[key].close()
         configure(model, comm)                               # leaves no reducer installed behind
         assert _abi.read_status() == 0
     for name, want in shards[0].items():
         assert torch.equal(want, shards[1][name]), name
+    assert losses[0] == losses[1], losses               # parameters gathered by copy engines: the same bits
     sys.stdout.write("rank%%d peer-memory reduce equals NCCL on %%d tensors" %% (rank, len(shards[0])) + chr(10))
     dist.barrier(); dist.destroy_process_group()
     sys.stdout.write("rank" + str(rank) + "ok" + chr(10)); sys.stdout.flush()
