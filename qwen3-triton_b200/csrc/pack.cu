@@ -19,6 +19,51 @@ namespace q3 {
 constexpr int kPackCols = 8;        // table columns
 constexpr int kPackCtasPerSm = 2;   // measured best overall of 2..12 (chunk-cat 5.6 TB/s, split 5.5, copy-in 4.6)
 
+// 8 elements with the streaming (evict-first) cache policy on both sides: these copies move gigabytes that nobody
+// re-reads from L2, beside GEMMs whose operand reuse lives in L2. With the default policy the gradient pack of one FSDP
+// unit evicted the activations of the weight-gradient GEMM running next to it, which then took 2.6 times as long.
+template <typename T> struct Stream8;
+template <> struct Stream8<float> {
+  static __device__ __forceinline__ void load(const float* p, float (&v)[8]) {
+    const float4 a = __ldcs(reinterpret_cast<const float4*>(p)), b = __ldcs(reinterpret_cast<const float4*>(p + 4));
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+  }
+  static __device__ __forceinline__ void store(float* p, const float (&v)[8]) {
+    __stcs(reinterpret_cast<float4*>(p), make_float4(v[0], v[1], v[2], v[3]));
+    __stcs(reinterpret_cast<float4*>(p + 4), make_float4(v[4], v[5], v[6], v[7]));
+  }
+};
+template <> struct Stream8<__nv_bfloat16> {
+  static __device__ __forceinline__ void load(const __nv_bfloat16* p, float (&v)[8]) {
+    const uint4 t = __ldcs(reinterpret_cast<const uint4*>(p));
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&t);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { const float2 f = __bfloat1622float2(h[i]); v[2 * i] = f.x; v[2 * i + 1] = f.y; }
+  }
+  static __device__ __forceinline__ void store(__nv_bfloat16* p, const float (&v)[8]) {
+    uint4 t;
+    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&t);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+    __stcs(reinterpret_cast<uint4*>(p), t);
+  }
+};
+template <> struct Stream8<__half> {
+  static __device__ __forceinline__ void load(const __half* p, float (&v)[8]) {
+    const uint4 t = __ldcs(reinterpret_cast<const uint4*>(p));
+    const __half2* h = reinterpret_cast<const __half2*>(&t);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { const float2 f = __half22float2(h[i]); v[2 * i] = f.x; v[2 * i + 1] = f.y; }
+  }
+  static __device__ __forceinline__ void store(__half* p, const float (&v)[8]) {
+    uint4 t;
+    __half2* h = reinterpret_cast<__half2*>(&t);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) h[i] = __floats2half2_rn(v[2 * i], v[2 * i + 1]);
+    __stcs(reinterpret_cast<uint4*>(p), t);
+  }
+};
+
 // One lane's share of one vectorised piece. A lane visits vectors first, first + stride, ...; its source and
 // destination offsets advance by constant steps with one conditional wrap to the next row, so the loop has no
 // division (index arithmetic, not DRAM, limited the divided form to 4.9 TB/s). IDX = unsigned when every offset of the
@@ -47,7 +92,7 @@ __device__ __forceinline__ void sweep_piece(const S* __restrict__ src, D* __rest
   };
   auto load = [&](IDX at, float (&v)[8]) {
     if (!CHECK || at + 8 <= valid) {
-      VecIO<S, 8>::load(src + at, v);
+      Stream8<S>::load(src + at, v);
     } else {
 #pragma unroll
       for (int j = 0; j < 8; ++j) v[j] = at + j < valid ? to_f32<S>(src[at + j]) : 0.f;
@@ -66,14 +111,14 @@ __device__ __forceinline__ void sweep_piece(const S* __restrict__ src, D* __rest
       advance();
     }
 #pragma unroll
-    for (int u = 0; u < U; ++u) VecIO<D, 8>::store(dst + d[u], v[u]);
+    for (int u = 0; u < U; ++u) Stream8<D>::store(dst + d[u], v[u]);
   }
   // Tail one vector at a time: predicating the batch instead (tried both on loads and on stores) cost more
   // registers or serialised the main loop and lost 5-30 % on whole-buffer copies.
   for (; left > 0; --left) {
     float v0[8];
     load(si, v0);
-    VecIO<D, 8>::store(dst + di, v0);
+    Stream8<D>::store(dst + di, v0);
     advance();
   }
 }

@@ -45,9 +45,10 @@ reduce_scatter_pull_kernel(const PeerTable peers, float* __restrict__ out, int64
 #pragma unroll
       for (int e = 0; e < 8; ++e) acc[e] += to_f32<T>(h[e]);
     }
+    // streaming stores as well as loads: a gigabyte-sized shard must not push the neighbouring GEMMs' operands out of L2
     float4* o = reinterpret_cast<float4*>(out + v * 8);
-    o[0] = make_float4(acc[0] * scale, acc[1] * scale, acc[2] * scale, acc[3] * scale);
-    o[1] = make_float4(acc[4] * scale, acc[5] * scale, acc[6] * scale, acc[7] * scale);
+    __stcs(o, make_float4(acc[0] * scale, acc[1] * scale, acc[2] * scale, acc[3] * scale));
+    __stcs(o + 1, make_float4(acc[4] * scale, acc[5] * scale, acc[6] * scale, acc[7] * scale));
   }
   // tail (count not a multiple of 8): the first threads of the grid, one element each
   const int64_t tail = nvec * 8 + blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
