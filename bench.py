@@ -571,7 +571,8 @@ def run_fsdp(args):
     peer_reduce = os.environ.get("Q3_BENCH_PEER_REDUCE", "1") == "1" and world in (2, 4, 8)
     hooks = configure(model, comm, pack_gradients_off_compute_stream=os.environ.get("Q3_BENCH_PACK_SIDE", "0") == "1",
                       peer_memory_reduce=peer_reduce,
-                      copy_engine_gather=os.environ.get("Q3_BENCH_CE_GATHER", "1") == "1")
+                      copy_engine_gather=os.environ.get("Q3_BENCH_CE_GATHER", "1") == "1",
+                      early_copy_out=os.environ.get("Q3_BENCH_EARLY_COPY_OUT", "0") == "1")
     peer_reduce = hooks["peer_reducer"] is not None        # False on every rank if the mappings could not be made
     decoder = [p for n, p in model.named_parameters() if not n.startswith("lm_head.")]
     opt = TritonAdamW([dict(params=decoder), dict(params=[model.lm_head.weight])], lr=1e-4, betas=(0.9, 0.95),
@@ -718,6 +719,8 @@ def run_fsdp(args):
                        "parameter_gather": ("copy-engine pulls from peer-mapped buffers (%d of %d all-gather calls)" % (
                                                 hooks["all_gather"].peer_calls, hooks["all_gather"].calls)
                                             if hooks["peer_gather"] is not None else "NCCL all-gather"),
+                       "parameter_copy_out": ("ahead of time on a side stream" if hooks["early_copy_out"]
+                                              else "on the compute stream (FSDP2's place)"),
                        "gradient_reduce": ("pull kernel over peer memory, bf16 on the links, fp32 sums in rank order "
                                            "(%d of %d reduce-scatter calls)" % (hooks["reduce_scatter"].peer_calls,
                                                                                 hooks["reduce_scatter"].calls)

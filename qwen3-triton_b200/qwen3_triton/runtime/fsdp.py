@@ -114,7 +114,7 @@ def largest_unit_elements(model, world):
 
 
 def configure(model, communication, *, pack_kernels=True, pack_gradients_off_compute_stream=False,
-              peer_memory_reduce=False, copy_engine_gather=False):
+              peer_memory_reduce=False, copy_engine_gather=False, early_copy_out=False):
     """Install the comm hooks on every FSDP unit and (by default) the pack/unpack kernels of runtime/ops.py.
     `pack_gradients_off_compute_stream`: run the reduce-scatter copy-in on FSDP's reduce-scatter stream.
     `peer_memory_reduce`: reduce gradients with the pull kernel over peer memory (runtime/peer_reduce.py; one node,
@@ -122,7 +122,10 @@ def configure(model, communication, *, pack_kernels=True, pack_gradients_off_com
     'peer_reducer' - call its close() before the process group is destroyed. If any rank cannot allocate or map
     the staging buffers, every rank falls back to the collective backend and 'peer_reducer' is None.
     `copy_engine_gather`: all-gather the parameters with copy-engine transfers from buffers the peers have mapped
-    (runtime/peer_gather.py; one node); 'peer_gather' in the returned dict, same close() rule and fallback."""
+    (runtime/peer_gather.py; one node); 'peer_gather' in the returned dict, same close() rule and fallback.
+    `early_copy_out`: split-copy the gathered parameters on a side stream as soon as their all-gather is issued
+    (runtime/early_copy_out.py; process-wide, needs the pack kernels); 'early_copy_out' in the returned dict tells
+    whether it is active."""
     reducer = None
     if peer_memory_reduce:
         if not pack_kernels:
@@ -137,6 +140,10 @@ def configure(model, communication, *, pack_kernels=True, pack_gradients_off_com
         install_fsdp_pack_kernels()
         pack_gradients_on_reduce_scatter_stream(model if (pack_gradients_off_compute_stream or reducer) else None)
         reduce_gradients_over_peer_memory(reducer)
+    early = False
+    if pack_kernels:
+        from . import early_copy_out as eco
+        early = eco.enable(bool(early_copy_out) and eco.install())
     gatherer = None
     if copy_engine_gather:
         from .peer_gather import PeerAllGather
@@ -152,4 +159,5 @@ def configure(model, communication, *, pack_kernels=True, pack_gradients_off_com
             count += 1
     if not count:
         raise ValueError('No FSDP units to configure')
-    return dict(all_gather=ag, reduce_scatter=rs, units=count, peer_reducer=reducer, peer_gather=gatherer)
+    return dict(all_gather=ag, reduce_scatter=rs, units=count, peer_reducer=reducer, peer_gather=gatherer,
+                early_copy_out=early)

@@ -148,16 +148,29 @@ def all_gather_copy_in(all_gather_inputs, all_gather_output, inp_split_sizes, al
     return all_gather_input, all_gather_output
 
 
-def split_with_sizes_copy(all_gather_output, all_gather_input_split_sizes, dim=0, *, out):
-    ok = (dim == 1 and all_gather_output.ndim == 2 and all_gather_output.is_contiguous()
+def launch_split_copy(all_gather_output, split_sizes, out):
+    """The kernel form of split_with_sizes_copy(dim=1) on the current stream; False (nothing launched) for inputs it
+    does not take."""
+    ok = (all_gather_output.ndim == 2 and all_gather_output.is_contiguous() and len(out) > 0
           and all_gather_output.dtype in _FLOATS and len({o.dtype for o in out}) == 1 and out[0].dtype in _FLOATS
           and all(o.is_contiguous() and o.ndim == 2 for o in out))
     if not ok:
-        torch.split_with_sizes_copy(all_gather_output, all_gather_input_split_sizes, dim=dim, out=out)
-        return
+        return False
     rows = plan_split(all_gather_output.data_ptr(), all_gather_output.element_size(), all_gather_output.shape[0],
-                      list(all_gather_input_split_sizes), [o.data_ptr() for o in out])
+                      list(split_sizes), [o.data_ptr() for o in out])
     _launch(rows, all_gather_output.dtype, out[0].dtype, all_gather_output.device)
+    return True
+
+
+def split_with_sizes_copy(all_gather_output, all_gather_input_split_sizes, dim=0, *, out):
+    if dim == 1 and all_gather_output.is_cuda:
+        from .early_copy_out import pending_event
+        event = pending_event(all_gather_output)
+        if event is not None:           # copied ahead of time on the copy-out stream (runtime/early_copy_out.py)
+            torch.cuda.current_stream(all_gather_output.device).wait_event(event)
+            return
+    if dim != 1 or not launch_split_copy(all_gather_output, all_gather_input_split_sizes, out):
+        torch.split_with_sizes_copy(all_gather_output, all_gather_input_split_sizes, dim=dim, out=out)
 
 
 _rs_root = None        # weak reference to the root FSDP module whose reduce-scatter stream takes the gradient pack

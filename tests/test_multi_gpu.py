@@ -105,8 +105,8 @@ WORKER = textwrap.dedent('''
     rel = float((g0 - g1).norm() / g0.norm())
     assert rel < 2e-2, rel
 
-    # 3. the same step with parameters gathered by copy-engine pulls and gradients reduced by the pull kernel over peer
-    #    memory: on two ranks the fp32 sum of the two upcast bf16 gradients has one possible value, so every gradient
+    # 3. the same step with parameters gathered by copy-engine pulls, split-copied ahead of time on a side stream, and
+    #    gradients reduced by the pull kernel over peer memory: on two ranks the fp32 sum of the two upcast bf16 gradients has one possible value, so every gradient
     #    shard equals the NCCL path's bit for bit
     shards, losses = [], []
     for peer in (False, True):
@@ -117,7 +117,8 @@ WORKER = textwrap.dedent('''
         model = shard_vocab_loss_model(model, keep_full_layers=4, checkpoint_every=1, skip_embedding_backward_gather=True,
                                        fused_vocab_dw=True, communication=None, checkpoint_mode="selective",
                                        layers_per_unit=[1, 1, 2], vocab_parallel_embedding=True)
-        hooks = configure(model, comm, peer_memory_reduce=peer, copy_engine_gather=peer)
+        hooks = configure(model, comm, peer_memory_reduce=peer, copy_engine_gather=peer, early_copy_out=peer)
+        assert hooks["early_copy_out"] == peer
         for _ in range(3):                                   # three steps: both staging slots reused several times
             model.zero_grad(set_to_none=True)
             model(ids, labels=ids).loss.backward()
@@ -131,7 +132,10 @@ WORKER = textwrap.dedent('''
         for key in ("peer_gather", "peer_reducer"):
             if hooks[key] is not None:
                 hooks[key].close()
-        configure(model, comm)                               # leaves no reducer installed behind
+        if peer:
+            from qwen3_triton.runtime import early_copy_out
+            assert early_copy_out.statistics()["early_copies"] >= 4 * 3      # every unit, every step
+        configure(model, comm)                               # leaves no reducer installed behind, early copy-out off
         assert _abi.read_status() == 0
     for name, want in shards[0].items():
         assert torch.equal(want, shards[1][name]), name
