@@ -144,3 +144,45 @@ def test_fsdp_pack_plans_against_reference_semantics():
     table, _ = ops.finalize(rows)
     run(table, torch.bfloat16, torch.float32)
     assert torch.equal(got, ref)
+
+
+def test_peer_reduce_layout_bf16_staging_then_ordered_fp32_sum():
+    """The data path of the peer-memory gradient reduction, restated on the CPU: every rank packs its bf16 gradients
+    with the chunk-cat table into a [world, columns] bf16 staging buffer; rank r's result is the fp32 sum, in rank
+    order, of row r of every rank's buffer, times 1/world. It must equal what FSDP2 computes: chunk-cat with upcast
+    into fp32, then an averaging reduce-scatter (here: the mean over ranks of row r)."""
+    import ctypes
+    from qwen3_triton.runtime import ops
+
+    def run(table, src_dtype, dst_dtype):
+        for src, dst, r, c, ss, ds, valid, _vec in table:
+            s = torch.frombuffer((ctypes.c_char * (max(valid, 1) * src_dtype.itemsize)).from_address(src), dtype=src_dtype)
+            d = torch.frombuffer((ctypes.c_char * (((r - 1) * ds + c) * dst_dtype.itemsize)).from_address(dst), dtype=dst_dtype)
+            for i in range(r):
+                for j in range(c):
+                    k = i * ss + j
+                    d[i * ds + j] = s[k].to(dst_dtype) if k < valid else 0
+
+    world = 4
+    shapes = ((8, 3), (6, 2), (9,), (4, 4))                      # 6 and 9 rows need padding to the world size
+    g = torch.Generator().manual_seed(3)
+    grads = [[torch.randn(s, generator=g).to(torch.bfloat16) for s in shapes] for _ in range(world)]
+    staged, reference = [], []
+    for rank_grads in grads:
+        _, cols = ops.plan_chunk_cat([tuple(t.shape) for t in rank_grads], [t.data_ptr() for t in rank_grads], 0, 2, world)
+        buf = torch.full((world, cols), float('nan'), dtype=torch.bfloat16)
+        rows, _ = ops.plan_chunk_cat([tuple(t.shape) for t in rank_grads], [t.data_ptr() for t in rank_grads],
+                                     buf.data_ptr(), 2, world)
+        run(ops.finalize(rows)[0], torch.bfloat16, torch.bfloat16)
+        staged.append(buf)
+        ref = torch.zeros(world, cols)
+        torch._chunk_cat([t.float() for t in rank_grads], 0, world, out=ref)
+        reference.append(ref)
+    for r in range(world):
+        pulled = torch.zeros(staged[0].shape[1])
+        for buf in staged:                                        # rank order, fp32 accumulation
+            pulled = pulled + buf[r].float()
+        pulled = pulled * (1.0 / world)
+        want = torch.stack([ref[r] for ref in reference]).sum(0) / world
+        torch.testing.assert_close(pulled, want, rtol=1e-6, atol=1e-7)
+        assert not torch.isnan(pulled).any()
