@@ -15,8 +15,20 @@
 //              of two TMEM accumulators, releases stages with tcgen05.commit
 //   warps 2-5: epilogue    - tcgen05.ld the finished accumulator (32 lanes per warp), convert and
 //              store while the MMA warp already works on the next tile in the other accumulator
-// Tiles are visited in grouped-M order so that CTAs running together share operand tiles in L2.
-// TMA loads are plain per-CTA loads (no cluster multicast).
+// Tiles are visited in grouped-M order so that CTAs running together share operand tiles in L2, and are
+// drawn from a device counter, so that a CTA that starts late (its SM held by a kernel of another stream)
+// does not own a fixed share of the work.
+//
+// Where the output has at least two 128-row tiles the kernel runs as CTA pairs (template argument PAIR,
+// clusters of 2, tcgen05 cta_group::2): the pair owns a 256x256 tile, each CTA stages its own 128 rows of A
+// and half of the B rows and keeps its 128 accumulator rows in its own tensor memory; the rank-0 CTA issues
+// M=256 MMAs that read both CTAs' shared memory. Per k-block a CTA then fetches 32 KB instead of 48 KB for the
+// same tensor work, which is what limited the single-CTA form to about 80 % tensor-pipe activity.
+// Barriers across the pair: loads of both CTAs are counted on rank 0's `full` barrier (armed by rank 0 with
+// both CTAs' bytes); rank 0 commits `empty` and `tfull` once to each CTA; the epilogue warps of both CTAs
+// release an accumulator on rank 0's `tempty`; rank 0 publishes every tile into both CTAs' tile queues.
+// A cluster barrier before the first and after the last cross-CTA signal. All TMA loads are plain per-CTA
+// loads: every CTA fetches what it stages itself.
 //
 // The fused gate/up variant loads W_gate and W_up rows into one 256-row B tile, so one N=256 MMA
 // produces gate in accumulator columns [0,128) and up in [128,256); its epilogue stores G, U and
