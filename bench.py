@@ -572,7 +572,8 @@ def run_fsdp(args):
     hooks = configure(model, comm, pack_gradients_off_compute_stream=os.environ.get("Q3_BENCH_PACK_SIDE", "0") == "1",
                       peer_memory_reduce=peer_reduce,
                       copy_engine_gather=os.environ.get("Q3_BENCH_CE_GATHER", "1") == "1",
-                      early_copy_out=os.environ.get("Q3_BENCH_EARLY_COPY_OUT", "0") == "1")
+                      early_copy_out=os.environ.get("Q3_BENCH_EARLY_COPY_OUT", "0") == "1",
+                      gradients_in_staging=os.environ.get("Q3_BENCH_GRAD_HOMES", "1") == "1")
     peer_reduce = hooks["peer_reducer"] is not None        # False on every rank if the mappings could not be made
     decoder = [p for n, p in model.named_parameters() if not n.startswith("lm_head.")]
     opt = TritonAdamW([dict(params=decoder), dict(params=[model.lm_head.weight])], lr=1e-4, betas=(0.9, 0.95),
@@ -721,6 +722,12 @@ def run_fsdp(args):
                                             if hooks["peer_gather"] is not None else "NCCL all-gather"),
                        "parameter_copy_out": ("ahead of time on a side stream" if hooks["early_copy_out"]
                                               else "on the compute stream (FSDP2's place)"),
+                       "gradient_pack": ("%d of %d weight gradients written by their GEMMs into the staging buffer, "
+                                         "%d copied there" % (hooks["peer_reducer"].born_in_place,
+                                                              hooks["peer_reducer"].born_in_place
+                                                              + hooks["peer_reducer"].copied_home,
+                                                              hooks["peer_reducer"].copied_home)
+                                         if hooks["gradient_homes"] else "one pack kernel per FSDP unit"),
                        "gradient_reduce": ("pull kernel over peer memory, bf16 on the links, fp32 sums in rank order "
                                            "(%d of %d reduce-scatter calls)" % (hooks["reduce_scatter"].peer_calls,
                                                                                 hooks["reduce_scatter"].calls)

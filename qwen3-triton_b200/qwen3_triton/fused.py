@@ -70,8 +70,38 @@ class WeightGradientStream:
                 main.wait_stream(side)
 
 
-def _gemm(a_ptr, a_sm, a_sk, b_ptr, b_sk, b_sn, m, n, k, like, out_dtype=None):
-    out = _empty((m, n), like, out_dtype)
+class GradientHomes:
+    """Where the fused layer's backward may put its weight gradients. `provider` (runtime/peer_reduce.py:
+    PeerGradientReducer after register_units) hands out views inside the buffer the gradient reduction reads, so that
+    the gradients need no packing pass; None: ordinary tensors."""
+    provider = None
+
+    @classmethod
+    def handles(cls, layer):
+        """Per weight of `layer.weights()`: the provider's handle of that parameter's home, or None."""
+        provider = cls.provider
+        if provider is None:
+            return None
+        a, m = layer.self_attn, layer.mlp
+        owners = (layer.input_layernorm, a.q_proj, a.k_proj, a.v_proj, a.o_proj, a.q_norm, a.k_norm,
+                  layer.post_attention_layernorm, m.gate_proj, m.up_proj, m.down_proj)
+        handles = tuple(provider.home(owner, 'weight') for owner in owners)
+        return handles if any(h is not None for h in handles) else None
+
+    @classmethod
+    def view(cls, handles, position, shape, like):
+        """The home of weight number `position` if it has one of this shape and dtype, else a fresh tensor."""
+        provider = cls.provider
+        if provider is not None and handles is not None and handles[position] is not None:
+            t = provider.gradient_view(handles[position], like.dtype)
+            if t is not None and tuple(t.shape) == tuple(shape) and t.device == like.device:
+                return t
+        return _empty(shape, like)
+
+
+def _gemm(a_ptr, a_sm, a_sk, b_ptr, b_sk, b_sn, m, n, k, like, out_dtype=None, out=None):
+    if out is None:
+        out = _empty((m, n), like, out_dtype)
     _abi.call('q3_gemm', a_ptr, a_sm, a_sk, b_ptr, b_sk, b_sn, out.data_ptr(), m, n, k, _abi.dt(like.dtype),
               _abi.dt(out.dtype), _abi.status_word(like.device).data_ptr(), _abi.stream())
     return out
@@ -87,9 +117,10 @@ def mm_nn(dy, w):
     return _gemm(dy.data_ptr(), dy.shape[1], 1, w.data_ptr(), w.shape[1], 1, dy.shape[0], w.shape[1], dy.shape[1], dy)
 
 
-def mm_tn(dy, x):
+def mm_tn(dy, x, out=None):
     """dy[M,N]^T @ x[M,K] -> [N,K]"""
-    return _gemm(dy.data_ptr(), 1, dy.shape[1], x.data_ptr(), x.shape[1], 1, dy.shape[1], x.shape[1], dy.shape[0], dy)
+    return _gemm(dy.data_ptr(), 1, dy.shape[1], x.data_ptr(), x.shape[1], 1, dy.shape[1], x.shape[1], dy.shape[0], dy,
+                 out=out)
 
 
 def _grouped_ok(x, weights):
@@ -121,11 +152,11 @@ def linear_group_dgrad(dys, weights):
     return dx
 
 
-def linear_group_wgrad(dys, x):
-    """[dy.T @ x for dy in dys] in one launch."""
+def linear_group_wgrad(dys, x, outs=None):
+    """[dy.T @ x for dy in dys] in one launch; `outs`: tensors to write into."""
     if not all(dy.shape[1] % 8 == 0 for dy in dys) or x.shape[1] % 8:
-        return [mm_tn(dy, x) for dy in dys]
-    dws = [_empty((dy.shape[1], x.shape[1]), x) for dy in dys]
+        return [mm_tn(dy, x, out=None if outs is None else outs[i]) for i, dy in enumerate(dys)]
+    dws = outs if outs is not None else [_empty((dy.shape[1], x.shape[1]), x) for dy in dys]
     dp, gp, n = _abi.pointer_array(dys), _abi.pointer_array(dws), _abi.size_array([dy.shape[1] for dy in dys])
     _abi.call('q3_linear_wgrad_grouped', dp, x.data_ptr(), gp, n, len(dys), x.shape[0], x.shape[1], _abi.dt(x.dtype),
               _abi.status_word(x.device).data_ptr(), _abi.stream())
@@ -250,7 +281,7 @@ def recompute_cheap(r, cos, sin, w, meta):
 
 class FusedLayerFn(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, resid, delta, cos, sin, meta, recompute, *weights):
+    def forward(ctx, resid, delta, cos, sin, meta, recompute, homes, *weights):
         b, s, hq, hk, d, eps = meta
         shape = resid.shape
         r2 = resid.reshape(-1, shape[-1])
@@ -258,6 +289,7 @@ class FusedLayerFn(torch.autograd.Function):
         r = layer_forward(r2, d2, cos, sin, weights, meta)
         recompute = int(recompute)
         ctx.meta, ctx.recompute, ctx.shape, ctx.has_delta = meta, recompute, shape, delta is not None
+        ctx.homes = homes
         if recompute == 2:
             ctx.save_for_backward(r2, d2 if d2 is not None else r2, cos, sin, *weights)
         elif recompute == 1:
@@ -288,7 +320,13 @@ class FusedLayerFn(torch.autograd.Function):
         dm = g_m.reshape(t, hdim).contiguous()
         dres = g_x1.reshape(t, hdim).contiguous() if g_x1 is not None else None
         # MLP
-        dwd = WeightGradientStream.run(lambda: mm_tn(dm, r['y']), (dm, r['y']))
+        homes = ctx.homes
+
+        def home(position, weight):
+            # the parameter's place in the buffer the gradient reduction reads, or a fresh tensor
+            return GradientHomes.view(homes, position, weight.shape, dm)
+
+        dwd = WeightGradientStream.run(lambda: mm_tn(dm, r['y'], out=home(10, wd)), (dm, r['y']))
         dg, du = torch.empty_like(r['g']), torch.empty_like(r['u'])
         if wd.shape[0] % 8 == 0 and wd.shape[1] % 8 == 0:
             # dY = dM @ W_down never leaves tensor memory: the GEMM epilogue turns it into dG, dU
@@ -301,12 +339,13 @@ class FusedLayerFn(torch.autograd.Function):
                       dg.numel(), _abi.dt(dg.dtype), _abi.stream())
             del dy
         dh2 = linear_group_dgrad([dg, du], [wg, wu])
-        dwg, dwu = WeightGradientStream.run(lambda: linear_group_wgrad([dg, du], r['h2']), (dg, du, r['h2']))
+        dwg, dwu = WeightGradientStream.run(
+            lambda: linear_group_wgrad([dg, du], r['h2'], outs=[home(8, wg), home(9, wu)]), (dg, du, r['h2']))
         del dg, du
         dx1, dw_post = _norm_bwd(r['x1'], w_post, dh2, dres, r['inv2'])
         # attention block
         do = mm_nn(dx1, wo)
-        dwo = WeightGradientStream.run(lambda: mm_tn(dx1, r['o']), (dx1, r['o']))
+        dwo = WeightGradientStream.run(lambda: mm_tn(dx1, r['o'], out=home(4, wo)), (dx1, r['o']))
         dqn, dkn, dv = torch.empty_like(r['qn']), torch.empty_like(r['kn']), torch.empty_like(r['v'])
         ws = _abi.workspace(_abi.lib().q3_attn_bwd_workspace_bytes(b, hq, hk, s, d), dx1.device)
         _abi.call('q3_attn_bwd_bshd', r['qn'].data_ptr(), r['kn'].data_ptr(), r['v'].data_ptr(), r['o'].data_ptr(),
@@ -316,11 +355,13 @@ class FusedLayerFn(torch.autograd.Function):
         dq, dwqn, dk, dwkn = _qk_norm_rope_bwd(r['q'], r['k'], wqn, wkn, cos, sin, dqn, dkn, r['invq'], r['invk'],
                                                t, hq, hk, d)
         dh = linear_group_dgrad([dq, dk, dv], [wq, wk, wv])
-        dwq, dwk, dwv = WeightGradientStream.run(lambda: linear_group_wgrad([dq, dk, dv], r['h']), (dq, dk, dv, r['h']))
+        dwq, dwk, dwv = WeightGradientStream.run(
+            lambda: linear_group_wgrad([dq, dk, dv], r['h'], outs=[home(1, wq), home(2, wk), home(3, wv)]),
+            (dq, dk, dv, r['h']))
         dx, dw_in = _norm_bwd(r['x'], w_in, dh, dx1, r['inv1'])
         dx = dx.view(ctx.shape)
         WeightGradientStream.join()
-        return (dx, dx if ctx.has_delta else None, None, None, None, None,
+        return (dx, dx if ctx.has_delta else None, None, None, None, None, None,
                 dw_in, dwq, dwk, dwv, dwo, dwqn, dwkn, dw_post, dwg, dwu, dwd)
 
 
@@ -346,7 +387,8 @@ class FusedDecoderLayer(DecoderBlock):
         cos, sin = rope
         b, s, _ = resid.shape
         meta = (b, s, self.heads, self.kv_heads, self.head_dim, float(self.input_layernorm.eps))
-        return FusedLayerFn.apply(resid, delta, cos, sin, meta, self.recompute, *self.weights())
+        return FusedLayerFn.apply(resid, delta, cos, sin, meta, self.recompute, GradientHomes.handles(self),
+                                  *self.weights())
 
 
 def _final_norm(resid, delta, scale):

@@ -114,7 +114,8 @@ def largest_unit_elements(model, world):
 
 
 def configure(model, communication, *, pack_kernels=True, pack_gradients_off_compute_stream=False,
-              peer_memory_reduce=False, copy_engine_gather=False, early_copy_out=False):
+              peer_memory_reduce=False, copy_engine_gather=False, early_copy_out=False,
+              gradients_in_staging=False):
     """Install the comm hooks on every FSDP unit and (by default) the pack/unpack kernels of runtime/ops.py.
     `pack_gradients_off_compute_stream`: run the reduce-scatter copy-in on FSDP's reduce-scatter stream.
     `peer_memory_reduce`: reduce gradients with the pull kernel over peer memory (runtime/peer_reduce.py; one node,
@@ -123,6 +124,9 @@ def configure(model, communication, *, pack_kernels=True, pack_gradients_off_com
     the staging buffers, every rank falls back to the collective backend and 'peer_reducer' is None.
     `copy_engine_gather`: all-gather the parameters with copy-engine transfers from buffers the peers have mapped
     (runtime/peer_gather.py; one node); 'peer_gather' in the returned dict, same close() rule and fallback.
+    `gradients_in_staging` (with `peer_memory_reduce`): the fused decoder layers write their weight gradients straight
+    into the staging buffer the reduction reads, so nothing is packed ('gradient_homes' in the returned dict = number
+    of FSDP units set up that way; process-wide: qwen3_triton.fused.GradientHomes).
     `early_copy_out`: split-copy the gathered parameters on a side stream as soon as their all-gather is issued
     (runtime/early_copy_out.py; process-wide, needs the pack kernels); 'early_copy_out' in the returned dict tells
     whether it is active."""
@@ -134,6 +138,11 @@ def configure(model, communication, *, pack_kernels=True, pack_gradients_off_com
         device = torch.device('cuda', torch.cuda.current_device())
         reducer = PeerGradientReducer.create(communication.group, device,
                                              largest_unit_elements(model, communication.world))
+    from .. import fused
+    homes = 0
+    if reducer is not None and gradients_in_staging:
+        homes = reducer.register_units(model)
+    fused.GradientHomes.provider = reducer if homes else None
     if pack_kernels:
         from .ops import (install_fsdp_pack_kernels, pack_gradients_on_reduce_scatter_stream,
                           reduce_gradients_over_peer_memory)
@@ -160,4 +169,4 @@ def configure(model, communication, *, pack_kernels=True, pack_gradients_off_com
     if not count:
         raise ValueError('No FSDP units to configure')
     return dict(all_gather=ag, reduce_scatter=rs, units=count, peer_reducer=reducer, peer_gather=gatherer,
-                early_copy_out=early)
+                early_copy_out=early, gradient_homes=homes)

@@ -176,3 +176,37 @@ def test_updates_during_backward_equal_a_step_after_backward(mixed):
         assert float(sa[0]) == 4.0
     for a, b in zip(late[2], early[2]):
         assert torch.equal(a, b)
+
+
+def test_step_pending_on_another_stream_then_step_equals_one_step():
+    """step_pending(eligible) updates the eligible parameters that have a gradient on the current (side) stream and
+    drops those gradients; step() updates the rest and waits for that stream: the same state as one step()."""
+    from qwen3_triton.runtime.adamw import TritonAdamW
+
+    def build():
+        g = torch.Generator().manual_seed(21)
+        params = [torch.nn.Parameter(torch.randn(s, generator=g).cuda()) for s in ((300, 70), (1024,), (64, 64), (5,))]
+        return params, TritonAdamW(params, **HYPER)
+
+    (pa, oa), (pb, ob) = build(), build()
+    side = torch.cuda.Stream()
+    g = torch.Generator().manual_seed(22)
+    for _ in range(3):
+        grads = [torch.randn(p.shape, generator=g).cuda() * 1e-2 for p in pa]
+        for p, q, gr in zip(pa, pb, grads):
+            p.grad, q.grad = gr.clone(), gr.clone()
+        oa.step()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            assert ob.step_pending(pb[:2]) is True           # only the first two are eligible
+            assert ob.step_pending(pb[:2]) is False          # nothing left with a gradient among them
+        assert pb[0].grad is None and pb[1].grad is None and pb[2].grad is not None
+        ob.step()
+        ob.zero_grad(set_to_none=True)
+        oa.zero_grad(set_to_none=True)
+    torch.cuda.synchronize()
+    for p, q in zip(pa, pb):
+        assert torch.equal(p, q)
+        for key in ('step', 'exp_avg', 'exp_avg_sq'):
+            assert torch.equal(oa.state[p][key], ob.state[q][key]), key
+        assert float(oa.state[p]['step']) == 3.0

@@ -160,6 +160,38 @@ def test_fused_decoder_layers_match_operator_graph_and_oracle(seq):
         assert rel_l2(g_f[n], g_o[n]) < 4e-2, n
 
 
+def test_weight_gradients_on_a_second_stream_change_nothing():
+    """fused.WeightGradientStream (off by default): the four weight-gradient GEMMs of a layer's backward issued on a
+    side stream, joined before the layer's backward returns. Same kernels on the same inputs: every gradient must be
+    bit-identical, three steps in a row (the side stream's tensors are reused through the allocator)."""
+    from qwen3_triton import fused, model_for_variant
+    c = small_d128_config()
+    state = {k: v.to(torch.bfloat16).float() for k, v in recipe.seeded_state(c, seed=7, norm_jitter=0.1).items()}
+    ids = recipe.seeded_ids(c, batch=2, seq=256, seed=8).cuda()
+
+    def run(side):
+        model = model_for_variant(c, 'b200_fused')
+        model.load_hf_state_dict({k: v.clone() for k, v in state.items()})
+        model = model.to('cuda', torch.bfloat16)
+        previous = fused.WeightGradientStream.enabled
+        fused.WeightGradientStream.enabled = side
+        try:
+            for _ in range(3):
+                model.zero_grad(set_to_none=True)
+                out = model(ids, labels=ids)
+                out.loss.backward()
+            torch.cuda.synchronize()
+        finally:
+            fused.WeightGradientStream.enabled = previous
+        return out.loss.detach().clone(), {n: p.grad.clone() for n, p in model.named_parameters()}
+
+    loss_a, grads_a = run(False)
+    loss_b, grads_b = run(True)
+    assert torch.equal(loss_a, loss_b)
+    for n in grads_a:
+        assert torch.equal(grads_a[n], grads_b[n]), n
+
+
 @pytest.mark.parametrize('B,S,H,V,chunk', [(2, 33, 256, 1000, 256), (1, 300, 512, 4104, 1024), (3, 17, 128, 520, 16384)])
 def test_fused_linear_cross_entropy_matches_materialised_path(B, S, H, V, chunk):
     """hidden -> loss without logits in memory == causal_cross_entropy(linear(hidden, W)) and the fp32 oracle."""

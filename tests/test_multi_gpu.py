@@ -109,7 +109,7 @@ WORKER = textwrap.dedent('''
     #    gradients reduced by the pull kernel over peer memory: on two ranks the fp32 sum of the two upcast bf16 gradients has one possible value, so every gradient
     #    shard equals the NCCL path's bit for bit
     shards, losses = [], []
-    for peer in (False, True):
+    for peer in (False, True, "homes"):
         torch.manual_seed(1234)
         with torch.device(dev):
             model = model_for_variant(cfg, "b200_fused")
@@ -117,8 +117,10 @@ WORKER = textwrap.dedent('''
         model = shard_vocab_loss_model(model, keep_full_layers=4, checkpoint_every=1, skip_embedding_backward_gather=True,
                                        fused_vocab_dw=True, communication=None, checkpoint_mode="selective",
                                        layers_per_unit=[1, 1, 2], vocab_parallel_embedding=True)
-        hooks = configure(model, comm, peer_memory_reduce=peer, copy_engine_gather=peer, early_copy_out=peer)
-        assert hooks["early_copy_out"] == peer
+        hooks = configure(model, comm, peer_memory_reduce=bool(peer), copy_engine_gather=bool(peer),
+                          early_copy_out=peer is True, gradients_in_staging=peer == "homes")
+        assert hooks["early_copy_out"] == (peer is True)
+        assert (hooks["gradient_homes"] > 0) == (peer == "homes")
         for _ in range(3):                                   # three steps: both staging slots reused several times
             model.zero_grad(set_to_none=True)
             model(ids, labels=ids).loss.backward()
@@ -132,14 +134,19 @@ WORKER = textwrap.dedent('''
         for key in ("peer_gather", "peer_reducer"):
             if hooks[key] is not None:
                 hooks[key].close()
-        if peer:
+        if peer is True:
             from qwen3_triton.runtime import early_copy_out
             assert early_copy_out.statistics()["early_copies"] >= 4 * 3      # every unit, every step
+        if peer == "homes":
+            # the seven matrices of each of the 4 layers are written by their GEMMs into the staging buffer, 3 steps
+            assert hooks["peer_reducer"].born_in_place == 3 * 4 * 7, hooks["peer_reducer"].born_in_place
+            assert hooks["peer_reducer"].copied_home > 0               # norm weights are copied to their homes
         configure(model, comm)                               # leaves no reducer installed behind, early copy-out off
         assert _abi.read_status() == 0
-    for name, want in shards[0].items():
-        assert torch.equal(want, shards[1][name]), name
-    assert losses[0] == losses[1], losses               # parameters gathered by copy engines: the same bits
+    for other in shards[1:]:
+        for name, want in shards[0].items():
+            assert torch.equal(want, other[name]), name
+    assert losses[0] == losses[1] == losses[2], losses  # parameters gathered by copy engines: the same bits
     sys.stdout.write("rank%%d peer-memory reduce equals NCCL on %%d tensors" %% (rank, len(shards[0])) + chr(10))
     dist.barrier(); dist.destroy_process_group()
     sys.stdout.write("rank" + str(rank) + "ok" + chr(10)); sys.stdout.flush()
