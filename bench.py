@@ -573,7 +573,8 @@ def run_fsdp(args):
                       peer_memory_reduce=peer_reduce,
                       copy_engine_gather=os.environ.get("Q3_BENCH_CE_GATHER", "1") == "1",
                       early_copy_out=os.environ.get("Q3_BENCH_EARLY_COPY_OUT", "0") == "1",
-                      gradients_in_staging=os.environ.get("Q3_BENCH_GRAD_HOMES", "1") == "1")
+                      gradients_in_staging=os.environ.get("Q3_BENCH_GRAD_HOMES", "1") == "1",
+                      gather_into_parameters=os.environ.get("Q3_BENCH_DIRECT_GATHER", "0") == "1")
     peer_reduce = hooks["peer_reducer"] is not None        # False on every rank if the mappings could not be made
     decoder = [p for n, p in model.named_parameters() if not n.startswith("lm_head.")]
     opt = TritonAdamW([dict(params=decoder), dict(params=[model.lm_head.weight])], lr=1e-4, betas=(0.9, 0.95),
@@ -720,7 +721,9 @@ def run_fsdp(args):
                        "parameter_gather": ("copy-engine pulls from peer-mapped buffers (%d of %d all-gather calls)" % (
                                                 hooks["all_gather"].peer_calls, hooks["all_gather"].calls)
                                             if hooks["peer_gather"] is not None else "NCCL all-gather"),
-                       "parameter_copy_out": ("ahead of time on a side stream" if hooks["early_copy_out"]
+                       "parameter_copy_out": ("none: pieces gathered straight into the parameters"
+                                              if hooks["gather_into_parameters"] else
+                                              "ahead of time on a side stream" if hooks["early_copy_out"]
                                               else "on the compute stream (FSDP2's place)"),
                        "gradient_pack": ("%d of %d weight gradients written by their GEMMs into the staging buffer, "
                                          "%d copied there" % (hooks["peer_reducer"].born_in_place,

@@ -434,6 +434,10 @@ int q3_peer_free(void* ptr);
  * transfer that occupies no SM. The parameter all-gather of runtime/peer_gather.py issues one per source rank, from
  * the peer's mapped all-gather buffer into this rank's. Reference: qwen3_triton/runtime/collectives.py:88-137. */
 int q3_peer_copy(void* dst, const void* src, int64_t bytes, q3_stream_t stream);
+/* `count` such copies issued in order on `stream`; dst, src, bytes are HOST arrays. Used to deliver every rank's shard
+ * of every parameter of an FSDP unit straight into the parameter's tensor (no rank-major buffer to split afterwards). */
+int q3_peer_copy_many(void* const* dst, const void* const* src, const int64_t* bytes, int64_t count,
+                      q3_stream_t stream);
 
 /* out[i] = scale * sum_r widen(peers[r][first + i]), i in [0, count): this rank's rows of every rank's 16-bit staging
  * buffer, pulled with plain peer loads, added in fp32 in rank order. `peers` is a HOST array of `world` (2, 4 or 8)

@@ -123,6 +123,22 @@ extern "C" int q3_peer_copy(void* dst, const void* src, int64_t bytes, q3_stream
   return e == cudaSuccess ? Q3_OK : Q3_ERR_CUDA - (int)e;
 }
 
+// `count` such copies, issued one after the other on `stream` (host arrays of pointers and sizes): the all-gather that
+// delivers every rank's shard of every parameter straight into the parameter's own tensor.
+extern "C" int q3_peer_copy_many(void* const* dst, const void* const* src, const int64_t* bytes, int64_t count,
+                                 q3_stream_t stream) {
+  if (!dst || !src || !bytes) return Q3_ERR_ARG;
+  if (count < 0) return Q3_ERR_SHAPE;
+  for (int64_t i = 0; i < count; ++i) {
+    if (bytes[i] < 0) return Q3_ERR_SHAPE;
+    if (bytes[i] == 0) continue;
+    if (!dst[i] || !src[i]) return Q3_ERR_ARG;
+    cudaError_t e = cudaMemcpyAsync(dst[i], src[i], (size_t)bytes[i], cudaMemcpyDeviceToDevice, (cudaStream_t)stream);
+    if (e != cudaSuccess) return Q3_ERR_CUDA - (int)e;
+  }
+  return Q3_OK;
+}
+
 // out [count] fp32 = scale * sum over ranks r of peers[r][first .. first + count) widened to fp32, added in rank order.
 // peers: host array of `world` device pointers (this rank's own staging buffer at index `rank`, the others mapped
 // with q3_peer_open), all holding the same [world * count]-element layout in `dtype` (bf16 or fp16). The caller

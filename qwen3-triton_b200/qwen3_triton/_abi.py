@@ -94,6 +94,7 @@ SIGNATURES = {
     "q3_peer_close": (I, [P]),
     "q3_peer_free": (I, [P]),
     "q3_peer_copy": (I, [P, P, L, P]),
+    "q3_peer_copy_many": (I, [P, P, P, L, P]),
     "q3_reduce_scatter_pull": (I, [P, I, P, L, L, D, I, P]),
     "q3_inf_positions": (I, [P, L, L, L, P]),
     "q3_kv_append": (I, [P, P, P, P, L, L, L, L, L, L, I, P]),

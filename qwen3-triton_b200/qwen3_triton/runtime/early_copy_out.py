@@ -19,7 +19,8 @@ nothing otherwise. The reference leaves the copy where FSDP2 puts it (qwen3_trit
 """
 import torch
 
-_state = dict(installed=False, enabled=False, stream=None, done={}, copies=0, original=None)
+_state = dict(installed=False, enabled=False, stream=None, done={}, copies=0, original=None, gatherer=None,
+              delivered=0)
 
 
 def pending_event(all_gather_output):
@@ -28,7 +29,19 @@ def pending_event(all_gather_output):
 
 
 def statistics():
-    return dict(enabled=_state['enabled'], early_copies=_state['copies'])
+    return dict(enabled=_state['enabled'], early_copies=_state['copies'], direct_deliveries=_state['delivered'])
+
+
+def deliver_through(gatherer):
+    """With a runtime/peer_gather.py:PeerAllGather given here (and the wrapper installed), an all-gather is finished by
+    the wrapper: every rank's piece of every parameter is copied straight into the parameter's tensor, and FSDP2's
+    split-copy finds nothing left to do. None: back to rank-major rows and a split-copy."""
+    if _state['gatherer'] is not None:
+        _state['gatherer'].direct = False
+    _state['gatherer'] = gatherer if (gatherer is not None and _state['installed']) else None
+    if _state['gatherer'] is not None:
+        _state['gatherer'].direct = True
+    return _state['gatherer'] is not None
 
 
 def enable(flag=True):
@@ -57,7 +70,10 @@ def install():
     def unshard(self, async_op=False):
         had_result = self._all_gather_result is not None
         original(self, async_op)
-        if _state['enabled'] and not had_result:
+        gatherer = _state['gatherer']
+        if gatherer is not None and gatherer.deferred is not None:
+            _deliver_now(self, gatherer)          # must run: the hook left the rows of this all-gather uncopied
+        elif _state['enabled'] and not had_result:
             try:
                 _copy_out_now(self)
             except Exception:
@@ -68,6 +84,47 @@ def install():
     _state['original'] = original
     _state['installed'] = True
     return True
+
+
+def _outputs_of(group, result, world, device):
+    """The unit's parameter tensors, allocated now (FSDP2's copy-out makes the same calls later and finds them)."""
+    outs = []
+    for numels, dtypes, fsdp_param in zip(result.param_all_gather_input_numels, result.param_all_gather_input_dtypes,
+                                          group.fsdp_params):
+        fsdp_param.init_all_gather_outputs(numels, dtypes, world, device, force_recreate=False)
+        fsdp_param.alloc_all_gather_outputs()
+        outs.extend(fsdp_param.all_gather_outputs)
+    return outs
+
+
+def _deliver_now(group, gatherer):
+    result = group._all_gather_result
+    stream = gatherer.deferred['stream']
+    output = result.all_gather_output if result is not None else None
+    usable = (result is not None and result.all_gather_event is not None and result.all_gather_work is None
+              and output.data_ptr() == gatherer.deferred['output']
+              and all(p.fsdp_placement.dim == 0 for p in group.fsdp_params))
+    if not usable:
+        event = gatherer.deliver([], [None])          # rows into the rank-major buffer
+        if result is not None:
+            with torch.cuda.stream(stream):
+                group._all_gather_result = result._replace(all_gather_event=stream.record_event())
+        return
+    world = group._all_gather_process_group.size()
+    outs = _outputs_of(group, result, world, output.device)
+    compute = torch.cuda.current_stream(output.device)
+    if stream != compute:
+        stream.wait_stream(compute)                   # the outputs' memory is free in compute-stream order only
+    event = gatherer.deliver(list(result.all_gather_input_split_sizes), outs)
+    if event is None:                                 # rows copied instead: FSDP2 splits them, after this event
+        with torch.cuda.stream(stream):
+            group._all_gather_result = result._replace(all_gather_event=stream.record_event())
+        return
+    for t in outs:
+        t.record_stream(stream)
+    group._all_gather_result = result._replace(all_gather_event=event)
+    _state['done'][output.data_ptr()] = event         # the split-copy override: nothing left to copy
+    _state['delivered'] += 1
 
 
 def _copy_out_now(group):
@@ -82,12 +139,7 @@ def _copy_out_now(group):
     world = group._all_gather_process_group.size()
     if world < 2 or any(p.fsdp_placement.dim != 0 for p in group.fsdp_params):
         return
-    outs = []
-    for numels, dtypes, fsdp_param in zip(result.param_all_gather_input_numels, result.param_all_gather_input_dtypes,
-                                          group.fsdp_params):
-        fsdp_param.init_all_gather_outputs(numels, dtypes, world, output.device, force_recreate=False)
-        fsdp_param.alloc_all_gather_outputs()
-        outs.extend(fsdp_param.all_gather_outputs)
+    outs = _outputs_of(group, result, world, output.device)
     views = [t.view(world, -1) for t in outs]
     compute = torch.cuda.current_stream(output.device)
     stream = _state['stream']

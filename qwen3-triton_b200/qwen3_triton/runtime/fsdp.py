@@ -115,7 +115,7 @@ def largest_unit_elements(model, world):
 
 def configure(model, communication, *, pack_kernels=True, pack_gradients_off_compute_stream=False,
               peer_memory_reduce=False, copy_engine_gather=False, early_copy_out=False,
-              gradients_in_staging=False):
+              gradients_in_staging=False, gather_into_parameters=False):
     """Install the comm hooks on every FSDP unit and (by default) the pack/unpack kernels of runtime/ops.py.
     `pack_gradients_off_compute_stream`: run the reduce-scatter copy-in on FSDP's reduce-scatter stream.
     `peer_memory_reduce`: reduce gradients with the pull kernel over peer memory (runtime/peer_reduce.py; one node,
@@ -127,6 +127,9 @@ def configure(model, communication, *, pack_kernels=True, pack_gradients_off_com
     `gradients_in_staging` (with `peer_memory_reduce`): the fused decoder layers write their weight gradients straight
     into the staging buffer the reduction reads, so nothing is packed ('gradient_homes' in the returned dict = number
     of FSDP units set up that way; process-wide: qwen3_triton.fused.GradientHomes).
+    `gather_into_parameters` (with `copy_engine_gather`): every rank's piece of every parameter is copied straight
+    into the parameter's tensor (one copy-engine transfer each), so FSDP2's split-copy of the rank-major buffer has
+    nothing to do; needs the unshard wrapper of runtime/early_copy_out.py ('gather_into_parameters' in the result).
     `early_copy_out`: split-copy the gathered parameters on a side stream as soon as their all-gather is issued
     (runtime/early_copy_out.py; process-wide, needs the pack kernels); 'early_copy_out' in the returned dict tells
     whether it is active."""
@@ -158,6 +161,10 @@ def configure(model, communication, *, pack_kernels=True, pack_gradients_off_com
         from .peer_gather import PeerAllGather
         device = torch.device('cuda', torch.cuda.current_device())
         gatherer = PeerAllGather.create(communication.group, device, _largest_unit(model, communication.world)[1])
+    direct = False
+    if pack_kernels:
+        direct = eco.deliver_through(gatherer if (gather_into_parameters and gatherer is not None and eco.install())
+                                     else None)
     ag = TritonAllGather(communication, gatherer)
     rs = TritonReduceScatter(communication, reducer)
     count = 0
@@ -169,4 +176,4 @@ def configure(model, communication, *, pack_kernels=True, pack_gradients_off_com
     if not count:
         raise ValueError('No FSDP units to configure')
     return dict(all_gather=ag, reduce_scatter=rs, units=count, peer_reducer=reducer, peer_gather=gatherer,
-                early_copy_out=early, gradient_homes=homes)
+                early_copy_out=early, gradient_homes=homes, gather_into_parameters=direct)

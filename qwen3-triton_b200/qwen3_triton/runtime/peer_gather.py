@@ -92,6 +92,9 @@ class PeerAllGather:
         self.next_slot = 0
         self.by_pointer = {}
         self.gathers = 0
+        self.delivered = 0
+        self.direct = False          # set by runtime/fsdp.py:configure when the unshard wrapper delivers the pieces
+        self.deferred = None
         self.flag = None
         if not self.usable:
             self.close()
@@ -129,12 +132,57 @@ class PeerAllGather:
                 or output_tensor.numel() * output_tensor.element_size() != row * self.world):
             raise ValueError('All-gather input must be this rank\'s row of the output buffer')
         dist.all_reduce(self.flag, group=self.group)       # every rank's row is written before anyone reads it
-        stream = _abi.stream()
+        self.gathers += 1
+        if self.direct:
+            # the rows are not copied here: `deliver` (called by the wrapper of FSDP2's unshard, which knows the unit's
+            # parameter tensors) sends every piece straight to its parameter
+            self.deferred = dict(index=index, row=row, output=output_tensor.data_ptr(),
+                                 stream=torch.cuda.current_stream(self.device), itemsize=input_tensor.element_size())
+            return True
+        self._copy_rows(index, row, output_tensor.data_ptr(), _abi.stream())
+        return True
+
+    def _copy_rows(self, index, row, output, stream):
         for step in range(1, self.world):
             r = (self.rank + step) % self.world             # ranks start on different peers
-            _abi.call('q3_peer_copy', output_tensor.data_ptr() + r * row, self.peers[index][r] + r * row, row, stream)
-        self.gathers += 1
-        return True
+            _abi.call('q3_peer_copy', output + r * row, self.peers[index][r] + r * row, row, stream)
+
+    def deliver(self, split_sizes, outs):
+        """Finish the all-gather whose barrier `gather` has just issued. `outs[i]`: the contiguous tensor of
+        world x split_sizes[i] elements FSDP2 would fill by splitting the rank-major buffer. Every rank's piece of
+        every parameter goes there directly (one copy-engine transfer each, this rank's own pieces included), on the
+        all-gather stream; returns the event behind the last copy - the rank-major buffer then needs no split-copy.
+        If the tensors are not what the row layout implies, the rows are copied into the rank-major buffer instead
+        and None is returned (FSDP2 splits as usual)."""
+        d, self.deferred = self.deferred, None
+        if d is None:
+            return None
+        itemsize, row, index = d['itemsize'], d['row'], d['index']
+        sizes = [int(n) for n in split_sizes]
+        fits = (len(outs) == len(sizes) and sum(sizes) * itemsize == row
+                and all(o.is_contiguous() and o.element_size() == itemsize and o.numel() == self.world * n
+                        for o, n in zip(outs, sizes)))
+        with torch.cuda.stream(d['stream']):
+            if not fits:
+                self._copy_rows(index, row, d['output'], _abi.stream())
+                return None
+            count = len(sizes) * self.world
+            dst, src, nbytes = (ctypes.c_void_p * count)(), (ctypes.c_void_p * count)(), (ctypes.c_int64 * count)()
+            k, offset = 0, 0
+            for o, n in zip(outs, sizes):
+                piece = n * itemsize
+                for step in range(self.world):
+                    r = (self.rank + step) % self.world
+                    dst[k] = o.data_ptr() + r * piece
+                    src[k] = self.peers[index][r] + r * row + offset
+                    nbytes[k] = piece
+                    k += 1
+                offset += piece
+            _abi.call('q3_peer_copy_many', dst, src, nbytes, count, _abi.stream())
+            event = torch.cuda.Event()
+            event.record()
+        self.delivered += 1
+        return event
 
     def close(self):
         if self.closed:

@@ -118,7 +118,9 @@ WORKER = textwrap.dedent('''
                                        fused_vocab_dw=True, communication=None, checkpoint_mode="selective",
                                        layers_per_unit=[1, 1, 2], vocab_parallel_embedding=True)
         hooks = configure(model, comm, peer_memory_reduce=bool(peer), copy_engine_gather=bool(peer),
-                          early_copy_out=peer is True, gradients_in_staging=peer == "homes")
+                          early_copy_out=peer is True, gradients_in_staging=peer == "homes",
+                          gather_into_parameters=peer == "homes")
+        assert hooks["gather_into_parameters"] == (peer == "homes")
         assert hooks["early_copy_out"] == (peer is True)
         assert (hooks["gradient_homes"] > 0) == (peer == "homes")
         for _ in range(3):                                   # three steps: both staging slots reused several times
@@ -141,6 +143,8 @@ WORKER = textwrap.dedent('''
             # the seven matrices of each of the 4 layers are written by their GEMMs into the staging buffer, 3 steps
             assert hooks["peer_reducer"].born_in_place == 3 * 4 * 7, hooks["peer_reducer"].born_in_place
             assert hooks["peer_reducer"].copied_home > 0               # norm weights are copied to their homes
+            # every all-gather delivered its pieces straight into the parameter tensors
+            assert hooks["peer_gather"].delivered == hooks["all_gather"].peer_calls > 0
         configure(model, comm)                               # leaves no reducer installed behind, early copy-out off
         assert _abi.read_status() == 0
     for other in shards[1:]:
