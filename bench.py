@@ -8,10 +8,12 @@ cross-entropy + backward + AdamW every step, bf16 compute with fp32 master weigh
 token ids, weights ~ N(0, 0.02)):
   N = 1  the full 36-layer model on one GPU, unsharded (falls back to a 4-layer slice at 4 x 2048 when the GPU
          has less than 160 GiB free);
-  N > 1  (launched with torch.distributed.run) the same model under FSDP2: bf16 parameter all-gather, fp32 gradient
-         reduce-scatter, vocabulary-parallel lm_head + cross-entropy, per-layer activation recomputation
-         ("full", the contract configuration; the "selective" and "none" policies are timed after it and reported
-         under config.other_recompute_policies).
+  N > 1  (launched with torch.distributed.run) the same model under FSDP2: bf16 parameter all-gather (copy-engine
+         transfers from peer-mapped buffers; Q3_BENCH_CE_GATHER=0: NCCL), fp32 gradient reduce-scatter (one pull
+         kernel over peer memory per unit, weight gradients written by their GEMMs straight into its staging buffer;
+         Q3_BENCH_PEER_REDUCE=0: NCCL), vocabulary-parallel lm_head + cross-entropy, per-layer activation
+         recomputation ("full", the contract configuration; the "selective" and "none" policies are timed after it
+         and reported under config.other_recompute_policies).
 The loss head never writes the [tokens, vocab] logits (Q3_BENCH_FUSED_LOSS=0 selects the materialising head).
 
 `value` = tokens/s over all GPUs with the token ids already resident in HBM; `e2e.value` = the same step driven
@@ -42,7 +44,8 @@ UNIT = "tokens/s"
 # kernels launched by one call of each C-ABI entry (for the gpu_launches claim)
 LAUNCHES = {"q3_rmsnorm_bwd": 2, "q3_add_rmsnorm_bwd": 2, "q3_norm_rope_bwd": 2, "q3_adamw_multi": 2, "q3_ce_fwd": 2,
             "q3_attn_bwd": 3, "q3_vce_finish": 2, "q3_embedding_bwd": 2, "q3_embedding_shard_bwd": 2,
-            "q3_qk_norm_rope_bwd": 3, "q3_attn_bwd_bshd": 3}
+            "q3_qk_norm_rope_bwd": 3, "q3_attn_bwd_bshd": 3, "q3_adamw_multi_mp": 2,
+            "q3_peer_copy": 0, "q3_peer_copy_many": 0}      # copy-engine transfers are not kernels
 
 GEMM_ENTRIES = ("q3_gemm", "q3_gemm_acc", "q3_gemm_acc_f32", "q3_gate_up_swiglu_fwd", "q3_linear_fwd_grouped",
                 "q3_linear_dgrad_grouped", "q3_linear_wgrad_grouped", "q3_down_dgrad_swiglu_bwd", "q3_linear_ce_stats",
