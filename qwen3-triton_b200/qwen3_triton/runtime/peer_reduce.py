@@ -98,6 +98,7 @@ class PeerGradientReducer:
         self.layouts = []                        # per registered FSDP unit: homes of its parameters
         self.home_of = {}                        # (id(module), parameter name) -> (layout index, position in it)
         self.claimed = {}                        # layout index -> slot, from the first gradient view to the reduce
+        self.handed = set()                      # (layout index, position) given out since the unit's slot was claimed
         self.slot_views = None                   # one 16-bit tensor per slot over the staging memory
         self.born_in_place = 0
         self.copied_home = 0
@@ -172,9 +173,14 @@ class PeerGradientReducer:
         if handle is None or self.closed or dtype not in (torch.bfloat16, torch.float16):
             return None
         index, position = handle
+        if (index, position) in self.handed:
+            # a second backward pass before the unit was reduced (gradient accumulation): the home holds the first
+            # pass's gradient, which autograd is about to add to - the new one needs memory of its own
+            return None
         slot = self.claimed.get(index)
         if slot is None:
             slot = self.claimed[index] = self._claim()
+        self.handed.add((index, position))
         h = self.layouts[index]['homes'][position]
         return self.slot_views[slot][h['home']:h['home'] + h['numel']].view(dtype).view(h['shape'])
 
@@ -204,6 +210,7 @@ class PeerGradientReducer:
         if index is not None and self.layouts[index]['columns'] == out.shape[1]:
             layout = self.layouts[index]
             slot = self.claimed.pop(index, None)
+            self.handed = {key for key in self.handed if key[0] != index}
             if slot is None:
                 slot = self._claim()
             base = self.own[slot]
@@ -222,6 +229,7 @@ class PeerGradientReducer:
         # of gradients is not the registered one, e.g. a parameter without gradient; that slot was never offered to the
         # peers and needs no release)
         self.claimed.clear()
+        self.handed.clear()
         rows, cols = plan([tuple(t.shape) for t in tensors], [t.data_ptr() for t in tensors], 0, 2, self.world)
         if cols * self.world > self.capacity or cols != out.shape[1] or cols % 8:
             return False
