@@ -186,3 +186,23 @@ def test_peer_reduce_layout_bf16_staging_then_ordered_fp32_sum():
         want = torch.stack([ref[r] for ref in reference]).sum(0) / world
         torch.testing.assert_close(pulled, want, rtol=1e-6, atol=1e-7)
         assert not torch.isnan(pulled).any()
+
+
+def test_unshard_wrapper_finds_the_fsdp2_internals_it_needs():
+    """runtime/early_copy_out.py reaches into FSDP2 (FSDPParamGroup.unshard, FSDPParam.init/alloc_all_gather_outputs,
+    AllGatherResult as a named tuple with an `all_gather_event` field). With this torch they must be there; the wrapper
+    is installed once, is inactive until enabled, and delivers nothing without a gatherer."""
+    from torch.distributed.fsdp._fully_shard._fsdp_collectives import AllGatherResult
+    from torch.distributed.fsdp._fully_shard._fsdp_param_group import FSDPParamGroup
+    from qwen3_triton.runtime import early_copy_out as eco
+    before = FSDPParamGroup.unshard
+    assert eco.install() is True
+    wrapped = FSDPParamGroup.unshard
+    assert eco.install() is True and FSDPParamGroup.unshard is wrapped          # idempotent
+    assert wrapped is not before
+    stats = eco.statistics()
+    assert stats['enabled'] is False and stats['early_copies'] == 0 and stats['direct_deliveries'] == 0
+    assert eco.deliver_through(None) is False
+    assert {'all_gather_output', 'all_gather_event', 'all_gather_work', 'param_all_gather_input_numels',
+            'param_all_gather_input_dtypes', 'all_gather_input_split_sizes'} <= set(AllGatherResult._fields)
+    assert eco.pending_event(torch.zeros(1)) is None
